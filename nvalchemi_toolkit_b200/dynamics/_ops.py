@@ -1,0 +1,330 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Integrator / thermostat / reduction operators (Python entry points).
+
+Names and argument orders follow the reference's torch custom ops
+(``nvalchemi/dynamics/_ops/*.py``, ``dynamics/hooks/_utils.py:58-170``,
+``hooks/periodic.py:42-66``).  Every function mutates its first arguments in place exactly as the
+reference op does.  With the native library loaded (always on a GPU machine) the work is done by
+``torch.ops.nvalchemi.*`` kernels, which cover both CUDA and CPU tensors; without it (CPU-only
+machine, library not built) an equivalent torch expression runs.
+
+Time quantities are in internal units (``sqrt(amu A^2 / eV)``); temperatures passed to the
+kernels are ``k_B T`` in eV.
+"""
+from __future__ import annotations
+
+import torch
+
+from nvalchemi_toolkit_b200.dynamics._units import KB_EV
+from nvalchemi_toolkit_b200.ops import _native
+
+
+def _nat(t: torch.Tensor) -> bool:
+    return _native.require(t)
+
+
+def _i32(b: torch.Tensor) -> torch.Tensor:
+    return b if b.dtype == torch.int32 else b.to(torch.int32)
+
+
+def _to_per_system(value: float | torch.Tensor, m: int, device: torch.device, dtype: torch.dtype) -> torch.Tensor:
+    """Broadcast a scalar (or ``[M]`` tensor) to a contiguous ``[M]`` tensor."""
+    if isinstance(value, torch.Tensor):
+        return value.to(device=device, dtype=dtype).reshape(-1).expand(m).contiguous()
+    return torch.full((m,), float(value), device=device, dtype=dtype)
+
+
+# ------------------------------------------------------------------------ velocity Verlet
+def vv_position_update(positions, velocities, forces, masses, dt, batch_idx) -> None:
+    """``r += v dt + (F/2m) dt^2;  v += (F/2m) dt`` with per-system ``dt[M]``."""
+    if _nat(positions):
+        torch.ops.nvalchemi.vv_position_update(positions, velocities, forces.contiguous(), masses, dt, _i32(batch_idx))
+        return
+    h = dt[batch_idx.long()].unsqueeze(-1)
+    a = forces / masses.unsqueeze(-1)
+    positions.add_(velocities * h + 0.5 * a * h * h)
+    velocities.add_(0.5 * a * h)
+
+
+def vv_velocity_finalize(velocities, forces_new, masses, dt, batch_idx) -> None:
+    """``v += (F_new/2m) dt``."""
+    if _nat(velocities):
+        torch.ops.nvalchemi.vv_velocity_finalize(velocities, forces_new.contiguous(), masses, dt, _i32(batch_idx))
+        return
+    h = dt[batch_idx.long()].unsqueeze(-1)
+    velocities.add_(0.5 * h * forces_new / masses.unsqueeze(-1))
+
+
+# ------------------------------------------------------------------------ Langevin (BAOAB)
+def langevin_half_step(positions, velocities, forces, masses, dt, temperature, friction, random_seed, batch_idx,
+                       atom_ids=None) -> None:
+    """B-A-O-A part of BAOAB.  ``temperature`` is ``k_B T`` in eV per system; noise is a
+    counter-based Philox stream keyed by ``(random_seed, atom index)`` so results do not depend on
+    launch geometry (``atom_ids`` supplies global indices under domain decomposition)."""
+    if _nat(positions):
+        torch.ops.nvalchemi.langevin_half_step(positions, velocities, forces.contiguous(), masses, dt, temperature,
+                                               friction, int(random_seed), _i32(batch_idx), atom_ids)
+        return
+    b = batch_idx.long()
+    h = dt[b].unsqueeze(-1)
+    im = 1.0 / masses.unsqueeze(-1)
+    gen = torch.Generator(device="cpu").manual_seed(int(random_seed))
+    noise = torch.randn(positions.shape, generator=gen, dtype=torch.float64).to(positions)
+    c1 = torch.exp(-friction[b] * dt[b]).unsqueeze(-1)
+    c2 = torch.sqrt((1.0 - c1 * c1) * temperature[b].unsqueeze(-1) * im)
+    velocities.add_(0.5 * h * forces * im)
+    positions.add_(0.5 * h * velocities)
+    velocities.mul_(c1).add_(c2 * noise)
+    positions.add_(0.5 * h * velocities)
+
+
+def langevin_finalize(velocities, forces_new, masses, dt, batch_idx) -> None:
+    vv_velocity_finalize(velocities, forces_new, masses, dt, batch_idx)
+
+
+# ------------------------------------------------------------------------ kinetic energy etc.
+def compute_kinetic_energy(velocities, masses, batch_idx, num_systems: int) -> torch.Tensor:
+    """Per-system ``sum_i m_i v_i^2 / 2`` → ``[M]`` (fp64 accumulation)."""
+    if _nat(velocities):
+        return torch.ops.nvalchemi.compute_kinetic_energy(velocities.contiguous(), masses, _i32(batch_idx), num_systems)
+    ke = 0.5 * masses.double() * (velocities.double() ** 2).sum(-1)
+    out = torch.zeros(num_systems, dtype=torch.float64, device=velocities.device)
+    return out.index_add_(0, batch_idx.long(), ke).to(velocities.dtype)
+
+
+def compute_temperature(kinetic_energy: torch.Tensor, num_atoms_per_system: torch.Tensor) -> torch.Tensor:
+    """``T = 2 KE / (3 N k_B)`` in kelvin."""
+    return 2.0 * kinetic_energy / (3.0 * num_atoms_per_system.to(kinetic_energy.dtype).clamp_min(1) * KB_EV)
+
+
+def momentum_sums(velocities, masses, batch_idx, num_systems: int) -> torch.Tensor:
+    """``[M,4]`` fp64: ``(sum m v_x, sum m v_y, sum m v_z, sum m)``."""
+    if _nat(velocities):
+        return torch.ops.nvalchemi.momentum_sums(velocities.contiguous(), masses, _i32(batch_idx), num_systems)
+    mv = torch.cat([masses.double().unsqueeze(-1) * velocities.double(), masses.double().unsqueeze(-1)], dim=1)
+    return torch.zeros(num_systems, 4, dtype=torch.float64, device=velocities.device).index_add_(0, batch_idx.long(), mv)
+
+
+def _shift_scale(velocities, shift, scale, batch_idx) -> None:
+    if _nat(velocities):
+        torch.ops.nvalchemi.velocity_shift_scale(velocities, shift.contiguous(), scale.contiguous(), _i32(batch_idx))
+        return
+    b = batch_idx.long()
+    velocities.sub_(shift[b]).mul_(scale[b].unsqueeze(-1))
+
+
+def remove_com_motion(velocities, masses, batch_idx, num_systems: int) -> None:
+    s = momentum_sums(velocities, masses, batch_idx, num_systems)
+    vcom = (s[:, :3] / s[:, 3:].clamp_min(1e-30)).to(velocities.dtype)
+    _shift_scale(velocities, vcom, torch.ones(num_systems, dtype=velocities.dtype, device=velocities.device), batch_idx)
+
+
+def velocity_rescale(velocities, scale_factor, batch_idx) -> None:
+    m = scale_factor.shape[0]
+    _shift_scale(velocities, torch.zeros(m, 3, dtype=velocities.dtype, device=velocities.device),
+                 scale_factor.to(velocities.dtype), batch_idx)
+
+
+def initialize_velocities(velocities, masses, temperature, batch_idx, random_seed: int = 42, remove_com: bool = True,
+                          remove_rotations: bool = False, rescale: bool = True, positions=None, atom_ids=None) -> None:
+    """Maxwell-Boltzmann draw at ``temperature`` (kelvin, scalar or ``[M]``), optional COM/rotation
+    removal and exact rescale to the target temperature (3N degrees of freedom, as ``compute_temperature``)."""
+    m = int(batch_idx.max().item()) + 1 if batch_idx.numel() else 0
+    dev, dtype = velocities.device, velocities.dtype
+    kT = _to_per_system(temperature, m, dev, dtype) * KB_EV
+    b32 = _i32(batch_idx)
+    if _nat(velocities):
+        torch.ops.nvalchemi.maxwell_boltzmann(velocities, masses, kT, b32, int(random_seed), atom_ids)
+    else:
+        gen = torch.Generator(device="cpu").manual_seed(int(random_seed))
+        z = torch.randn(velocities.shape, generator=gen, dtype=torch.float64).to(velocities)
+        velocities.copy_(z * torch.sqrt(kT[batch_idx.long()] / masses).unsqueeze(-1))
+    if remove_com:
+        remove_com_motion(velocities, masses, batch_idx, m)
+    if remove_rotations and positions is not None:
+        _remove_rotations(velocities, positions, masses, batch_idx, m)
+    if rescale:
+        ke = compute_kinetic_energy(velocities, masses, batch_idx, m)
+        n_at = torch.bincount(batch_idx.long(), minlength=m)
+        t_now = compute_temperature(ke, n_at)
+        t_target = kT / KB_EV
+        scale = torch.where(t_now > 0, torch.sqrt(t_target / t_now.clamp_min(1e-30)), torch.ones_like(t_now))
+        velocity_rescale(velocities, scale, batch_idx)
+
+
+def _remove_rotations(velocities, positions, masses, batch_idx, m: int) -> None:
+    b = batch_idx.long()
+    md = masses.double().unsqueeze(-1)
+    msum = torch.zeros(m, 1, dtype=torch.float64, device=positions.device).index_add_(0, b, md)
+    com = torch.zeros(m, 3, dtype=torch.float64, device=positions.device).index_add_(0, b, md * positions.double()) / msum
+    r = positions.double() - com[b]
+    L = torch.zeros(m, 3, dtype=torch.float64, device=positions.device).index_add_(
+        0, b, md * torch.cross(r, velocities.double(), dim=-1))
+    r2 = (r * r).sum(-1, keepdim=True)
+    eye = torch.eye(3, dtype=torch.float64, device=positions.device)
+    inertia_i = md.unsqueeze(-1) * (r2.unsqueeze(-1) * eye - r.unsqueeze(-1) * r.unsqueeze(-2))
+    inertia = torch.zeros(m, 3, 3, dtype=torch.float64, device=positions.device).index_add_(0, b, inertia_i)
+    omega = torch.linalg.solve(inertia + 1e-12 * eye, L.unsqueeze(-1)).squeeze(-1)
+    velocities.sub_(torch.cross(omega[b], r, dim=-1).to(velocities.dtype))
+
+
+# ------------------------------------------------------------------------ FIRE
+def fire_step(positions, velocities, forces, masses, alpha, dt, n_steps_positive, alpha_start, f_alpha, dt_min, dt_max,
+              maxstep, n_min, f_dec, f_inc, uphill_flag, *, vf=None, vv=None, ff=None, batch_idx=None,
+              compute_reductions: bool = True) -> None:
+    """One FIRE iteration (power test, velocity mixing, adaptive ``dt``/``alpha``, kick, capped drift).
+
+    With ``compute_reductions=False`` the caller supplies ``vf, vv, ff`` already summed (for example
+    across ranks of a domain decomposition), mirroring the reference seam
+    (``nvalchemi/dynamics/_ops/fire.py:245-363``)."""
+    m = alpha.shape[0]
+    dev, dtype = positions.device, positions.dtype
+    if batch_idx is None:
+        batch_idx = torch.zeros(positions.shape[0], dtype=torch.int32, device=dev)
+    vf = vf if vf is not None else torch.zeros(m, dtype=dtype, device=dev)
+    vv = vv if vv is not None else torch.zeros(m, dtype=dtype, device=dev)
+    ff = ff if ff is not None else torch.zeros(m, dtype=dtype, device=dev)
+    if _nat(positions):
+        torch.ops.nvalchemi._fire_step_op(positions, velocities, forces.contiguous(), masses, alpha, dt, alpha_start,
+                                          f_alpha, dt_min, dt_max, maxstep, n_steps_positive, n_min, f_dec, f_inc,
+                                          uphill_flag, vf, vv, ff, _i32(batch_idx), compute_reductions)
+        return
+    b = batch_idx.long()
+    if compute_reductions:
+        z = torch.zeros(m, dtype=torch.float64, device=dev)
+        vf.copy_(z.clone().index_add_(0, b, (velocities.double() * forces.double()).sum(-1)))
+        vv.copy_(z.clone().index_add_(0, b, (velocities.double() ** 2).sum(-1)))
+        ff.copy_(z.clone().index_add_(0, b, (forces.double() ** 2).sum(-1)))
+    pos_power = vf > 0
+    n_steps_positive.copy_(torch.where(pos_power, n_steps_positive + 1, torch.zeros_like(n_steps_positive)))
+    grow = pos_power & (n_steps_positive > n_min)
+    keep = torch.where(pos_power, 1.0 - alpha, torch.zeros_like(alpha))
+    mix = torch.where(pos_power & (ff > 0), alpha * torch.sqrt(vv / ff.clamp_min(1e-300)), torch.zeros_like(alpha))
+    dt.copy_(torch.where(grow, torch.minimum(dt * f_inc, dt_max), torch.where(pos_power, dt, torch.maximum(dt * f_dec, dt_min))))
+    alpha.copy_(torch.where(grow, alpha * f_alpha, torch.where(pos_power, alpha, alpha_start)))
+    h = dt[b].unsqueeze(-1)
+    velocities.mul_(keep[b].unsqueeze(-1)).add_(mix[b].unsqueeze(-1) * forces).add_(h * forces / masses.unsqueeze(-1))
+    dr = h * velocities
+    dn = dr.norm(dim=-1)
+    mx = torch.zeros(m, dtype=dn.dtype, device=dev).scatter_reduce(0, b, dn, "amax", include_self=True)
+    scale = torch.where(mx > maxstep, maxstep / mx.clamp_min(1e-30), torch.ones_like(mx))
+    positions.add_(scale[b].unsqueeze(-1) * dr)
+
+
+def fire_update(velocities, forces, alpha, dt, n_steps_positive, alpha_start, f_alpha, dt_min, dt_max, n_min, f_dec,
+                f_inc, *, vf=None, vv=None, ff=None, batch_idx=None, compute_reductions: bool = True) -> None:
+    """FIRE velocity mixing and controller update only (no kick, no drift); used by variable-cell FIRE."""
+    m = alpha.shape[0]
+    dev = velocities.device
+    b = (batch_idx if batch_idx is not None else torch.zeros(velocities.shape[0], dtype=torch.int32, device=dev)).long()
+    if compute_reductions or vf is None:
+        z = torch.zeros(m, dtype=torch.float64, device=dev)
+        rvf = z.clone().index_add_(0, b, (velocities.double() * forces.double()).sum(-1)).to(velocities.dtype)
+        rvv = z.clone().index_add_(0, b, (velocities.double() ** 2).sum(-1)).to(velocities.dtype)
+        rff = z.clone().index_add_(0, b, (forces.double() ** 2).sum(-1)).to(velocities.dtype)
+        for dst, src in ((vf, rvf), (vv, rvv), (ff, rff)):
+            if dst is not None:
+                dst.copy_(src)
+        vf, vv, ff = rvf, rvv, rff
+    pos_power = vf > 0
+    n_steps_positive.copy_(torch.where(pos_power, n_steps_positive + 1, torch.zeros_like(n_steps_positive)))
+    grow = pos_power & (n_steps_positive > n_min)
+    keep = torch.where(pos_power, 1.0 - alpha, torch.zeros_like(alpha))
+    mix = torch.where(pos_power & (ff > 0), alpha * torch.sqrt(vv / ff.clamp_min(1e-300)), torch.zeros_like(alpha))
+    dt.copy_(torch.where(grow, torch.minimum(dt * f_inc, dt_max), torch.where(pos_power, dt, torch.maximum(dt * f_dec, dt_min))))
+    alpha.copy_(torch.where(grow, alpha * f_alpha, torch.where(pos_power, alpha, alpha_start)))
+    velocities.mul_(keep[b].unsqueeze(-1)).add_(mix[b].unsqueeze(-1) * forces)
+
+
+# ------------------------------------------------------------------------ segmented reductions
+_MODES = {"sum": 0, "max": 1, "min": 2, "mean": 3}
+
+
+def _segmented(values: torch.Tensor, idx: torch.Tensor, num_segments: int, mode: str) -> torch.Tensor:
+    if _nat(values):
+        return torch.ops.nvalchemi.segmented_reduce(values, idx, int(num_segments), _MODES[mode])
+    flat = values.reshape(values.shape[0], -1)
+    ix = idx.long().unsqueeze(-1).expand_as(flat)
+    out = torch.zeros(num_segments, flat.shape[1], dtype=flat.dtype, device=flat.device)
+    if mode == "sum":
+        out = out.double().scatter_add_(0, ix, flat.double()).to(flat.dtype)
+    elif mode == "mean":
+        cnt = torch.bincount(idx.long(), minlength=num_segments).clamp_min(1).unsqueeze(-1)
+        out = (out.double().scatter_add_(0, ix, flat.double()) / cnt).to(flat.dtype)
+    else:
+        out = out.scatter_reduce(0, ix, flat, "amax" if mode == "max" else "amin", include_self=False)
+    return out.reshape((num_segments,) + tuple(values.shape[1:]))
+
+
+def segmented_sum(values, idx, num_segments):
+    return _segmented(values, idx, num_segments, "sum")
+
+
+def segmented_max(values, idx, num_segments):
+    return _segmented(values, idx, num_segments, "max")
+
+
+def segmented_min(values, idx, num_segments):
+    return _segmented(values, idx, num_segments, "min")
+
+
+def segmented_mean(values, idx, num_segments):
+    return _segmented(values, idx, num_segments, "mean")
+
+
+# ------------------------------------------------------------------------ cells
+def compute_cell_inverse(cell: torch.Tensor) -> torch.Tensor:
+    return torch.linalg.inv(cell)
+
+
+def wrap_positions(positions, cell, batch_idx, pbc=None) -> torch.Tensor:
+    """Positions wrapped into the cell along periodic directions (out of place)."""
+    b = cell.shape[0]
+    if pbc is None:
+        pbc = torch.ones(b, 3, dtype=torch.bool, device=positions.device)
+    inv = torch.linalg.inv(cell)
+    if _nat(positions):
+        return torch.ops.nvalchemi.wrap_positions(positions.contiguous(), cell.contiguous(), inv.contiguous(),
+                                                  pbc.contiguous(), _i32(batch_idx))
+    bi = batch_idx.long()
+    frac = torch.einsum("ni,nij->nj", positions, inv[bi])
+    frac = torch.where(pbc[bi], frac - torch.floor(frac), frac)
+    return torch.einsum("ni,nij->nj", frac, cell[bi])
+
+
+def align_cell(positions, cell, batch_idx) -> None:
+    """Rotate each system so its cell becomes lower-triangular (``a`` along x, ``b`` in xy); in place.
+
+    Fractional coordinates are preserved.  Reference: ``nvalchemi/dynamics/_ops/cell_align.py:46-125``."""
+    q, r = torch.linalg.qr(cell.transpose(-1, -2))  # cell^T = Q R  -> cell = R^T Q^T
+    sign = torch.sign(torch.diagonal(r, dim1=-2, dim2=-1))
+    sign = torch.where(sign == 0, torch.ones_like(sign), sign)
+    q = q * sign.unsqueeze(-2)
+    r = r * sign.unsqueeze(-1)
+    new_cell = r.transpose(-1, -2)
+    positions.copy_(torch.einsum("ni,nij->nj", positions, q[batch_idx.long()]))
+    cell.copy_(new_cell)
+
+
+def batch_neighbor_list_rebuild_inplace(reference_positions, current_positions, batch_idx, rebuild_flags,
+                                        skin_distance_threshold: float, update_reference_positions: bool, cell,
+                                        cell_inv, pbc) -> None:
+    """Set ``rebuild_flags[s]`` when any atom of system ``s`` moved more than the threshold (minimum image)."""
+    if _nat(current_positions):
+        torch.ops.nvalchemi.neighbor_rebuild_check(reference_positions, current_positions.contiguous(), _i32(batch_idx),
+                                                   rebuild_flags, float(skin_distance_threshold),
+                                                   bool(update_reference_positions), cell.contiguous(),
+                                                   cell_inv.contiguous(), pbc.contiguous())
+        return
+    bi = batch_idx.long()
+    d = current_positions - reference_positions
+    frac = torch.einsum("ni,nij->nj", d, cell_inv[bi])
+    frac = torch.where(pbc[bi], frac - torch.floor(frac + 0.5), frac)
+    d = torch.einsum("ni,nij->nj", frac, cell[bi])
+    moved = (d * d).sum(-1) > skin_distance_threshold ** 2
+    flags = torch.zeros_like(rebuild_flags).index_put_((bi,), moved, accumulate=True) if False else \
+        torch.zeros(rebuild_flags.shape[0], dtype=torch.int32, device=d.device).index_add_(0, bi, moved.int()) > 0
+    rebuild_flags.logical_or_(flags)
+    if update_reference_positions:
+        sel = rebuild_flags[bi]
+        reference_positions[sel] = current_positions[sel]

@@ -1,0 +1,90 @@
+# SPDX-License-Identifier: Apache-2.0
+"""AtomicData / Batch behaviour (mirrors the reference's test/data suite in spirit)."""
+import pytest
+import torch
+
+from nvalchemi_toolkit_b200 import AtomicData, Batch
+from tests.helpers import random_batch, random_molecule
+
+
+def test_atomic_data_defaults_and_validation():
+    d = AtomicData(atomic_numbers=torch.tensor([1, 8, 1]), positions=torch.zeros(3, 3))
+    assert d.atomic_masses.shape == (3,) and abs(float(d.atomic_masses[1]) - 15.999) < 1e-3
+    assert d.velocities.shape == (3, 3) and d.atom_categories.dtype == torch.long
+    with pytest.raises(ValueError):
+        AtomicData(atomic_numbers=torch.tensor([1, 8]), positions=torch.zeros(3, 3))
+    with pytest.raises(ValueError):
+        AtomicData(atomic_numbers=torch.tensor([1, 8]), positions=torch.zeros(2, 3), forces=torch.zeros(3, 3))
+
+
+def test_atomic_data_dtype_cast_warns():
+    with pytest.warns(UserWarning):
+        d = AtomicData(atomic_numbers=torch.tensor([1]), positions=torch.zeros(1, 3), forces=torch.zeros(1, 3, dtype=torch.float64))
+    assert d.forces.dtype == torch.float32
+
+
+def test_chemical_hash_is_order_invariant():
+    a = random_molecule(6, 1)
+    perm = torch.randperm(6)
+    b = AtomicData(atomic_numbers=a.atomic_numbers[perm], positions=a.positions[perm])
+    assert a.chemical_hash == b.chemical_hash
+    c = AtomicData(atomic_numbers=a.atomic_numbers, positions=a.positions + 0.1)
+    assert a.chemical_hash != c.chemical_hash
+
+
+def test_batch_roundtrip_and_offsets(device):
+    sizes = [3, 5, 2]
+    data = [random_molecule(n, i, n_edges=4, periodic=True) for i, n in enumerate(sizes)]
+    b = Batch.from_data_list(data, device=device)
+    assert b.num_graphs == 3 and b.num_nodes == 10 and b.num_edges == 12
+    assert b.batch_ptr.tolist() == [0, 3, 8, 10] and b.batch_idx.dtype == torch.int32
+    assert b.cell.shape == (3, 3, 3) and b.energy.shape == (3, 1)
+    for i, d in enumerate(data):
+        got = b.get_data(i)
+        assert torch.equal(got.neighbor_list.cpu(), d.neighbor_list)
+        assert torch.allclose(got.positions.cpu(), d.positions)
+    sel = b.index_select([2, 0])
+    assert sel.num_nodes == 5
+    assert torch.equal(sel.neighbor_list[:4].cpu(), data[2].neighbor_list)
+    assert torch.equal(sel.neighbor_list[4:].cpu(), data[0].neighbor_list + 2)
+
+
+def test_put_defrag_trim(device):
+    b = random_batch([3, 5, 2], n_edges=3, periodic=True, device=device)
+    ref = [b.get_data(i) for i in range(3)]
+    buf = Batch.empty(num_systems=4, num_nodes=8, num_edges=12, template=b, device=device)
+    assert buf.num_graphs == 0
+    buf.put(b, torch.tensor([True, True, True], device=device))
+    assert b._copied_mask.tolist() == [True, True, False]  # third does not fit in 8 atoms
+    assert buf.num_graphs == 2 and buf.num_nodes == 8
+    assert torch.equal(buf.get_data(1).neighbor_list.cpu(), ref[1].neighbor_list.cpu())
+    b.defrag()
+    assert b.num_graphs == 1 and torch.equal(b.neighbor_list.cpu(), ref[2].neighbor_list.cpu())
+    buf.defrag(torch.tensor([True, False], device=device))
+    assert buf.num_graphs == 1 and buf.system_capacity == 4
+    assert torch.allclose(buf.positions.cpu(), ref[1].positions.cpu())
+    assert torch.equal(buf.neighbor_list.cpu(), ref[1].neighbor_list.cpu())
+    t = buf.trim(torch.tensor([True], device=device))
+    assert t is None
+
+
+def test_append_add_key_and_moves():
+    b = random_batch([3, 4], n_edges=2)
+    other = random_batch([5], seed=9, n_edges=2)
+    b.append(other)
+    assert b.num_graphs == 3 and b.num_nodes == 12 and int(b.neighbor_list[-2:].min()) >= 7
+    b.add_key("status", torch.zeros(3, 1, dtype=torch.long), level="system")
+    assert b.status.shape == (3, 1)
+    with pytest.raises(KeyError):
+        b.add_key("status", torch.zeros(3, 1, dtype=torch.long), level="system")
+    c = b.clone().to(dtype=torch.float64)
+    assert c.positions.dtype == torch.float64 and c.atomic_numbers.dtype == torch.long
+    assert "positions" in b and len(b) == 3
+    assert b[1].num_nodes == 4 and b[[0, 2]].num_graphs == 2
+
+
+def test_from_raw_dicts_skips_validation():
+    dicts = [{"positions": torch.zeros(2, 3), "atomic_numbers": torch.tensor([1, 1]), "energy": torch.zeros(1, 1),
+              "my_field": torch.ones(2, 4)} for _ in range(3)]
+    b = Batch.from_raw_dicts(dicts, field_levels={"my_field": "node"})
+    assert b.my_field.shape == (6, 4) and b.num_graphs == 3

@@ -1,0 +1,103 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Step loop, hooks, convergence, stage fusion and integrator physics on the demo model."""
+import pytest
+import torch
+
+from nvalchemi_toolkit_b200.dynamics import (FIRE, NVE, ConvergenceHook, DemoDynamics, DynamicsStage, FusedStage,
+                                             NVTLangevin, _ops)
+from nvalchemi_toolkit_b200.models import DemoModelWrapper
+from tests.helpers import random_batch
+
+
+class RecordingHook:
+    def __init__(self, stage, frequency=1):
+        self.stage, self.frequency, self.calls = stage, frequency, []
+
+    def __call__(self, ctx, stage):
+        self.calls.append((ctx.step_count, stage))
+
+
+def test_stage_order_and_frequency():
+    b = random_batch([4, 6])
+    hooks = [RecordingHook(s) for s in DynamicsStage if s != DynamicsStage.ON_CONVERGE]
+    every2 = RecordingHook(DynamicsStage.AFTER_STEP, frequency=2)
+    dyn = DemoDynamics(DemoModelWrapper(), n_steps=4, dt=0.01, hooks=hooks + [every2])
+    dyn.run(b)
+    assert all(len(h.calls) == 4 for h in hooks)
+    assert [c[0] for c in every2.calls] == [0, 2]
+    with pytest.raises(ValueError):
+        dyn.register_hook(RecordingHook(DynamicsStage.AFTER_STEP, frequency=0))
+
+    class Other:
+        frequency, stage = 1, None
+
+        def __call__(self, ctx, stage):
+            pass
+
+    with pytest.raises(TypeError):
+        dyn.register_hook(Other())
+
+
+def test_nve_energy_conservation(device):
+    torch.manual_seed(0)
+    b = random_batch([int(n) for n in torch.randint(8, 33, (16,))], device=device)
+    _ops.initialize_velocities(b.velocities, b.atomic_masses, 300.0, b.batch_idx, random_seed=0)
+    model = DemoModelWrapper().to(device)
+    dyn = NVE(model, dt=0.5)
+    dyn.compute(b)
+    ke = _ops.compute_kinetic_energy(b.velocities, b.atomic_masses, b.batch_idx, b.num_graphs)
+    e0 = b.energy.squeeze(-1) + ke
+    dyn.run(b, 100)
+    ke = _ops.compute_kinetic_energy(b.velocities, b.atomic_masses, b.batch_idx, b.num_graphs)
+    drift = ((b.energy.squeeze(-1) + ke) - e0).abs().max()
+    assert float(drift) < 5e-3
+    assert dyn.step_count == 100 and not b.positions.requires_grad
+
+
+def test_langevin_thermalises(device):
+    b = random_batch([32] * 8, device=device)
+
+    class Zero(DemoModelWrapper):
+        def forward(self, data, **kw):
+            return {"energy": torch.zeros(data.num_graphs, 1, device=data.device), "forces": torch.zeros_like(data.positions)}
+
+    dyn = NVTLangevin(Zero().to(device), dt=1.0, temperature=300.0, friction=0.1, random_seed=1)
+    b["forces"] = torch.zeros_like(b.positions)
+    dyn.run(b, 300)
+    ke = _ops.compute_kinetic_energy(b.velocities, b.atomic_masses, b.batch_idx, b.num_graphs)
+    t = _ops.compute_temperature(ke, b.num_nodes_per_graph).mean()
+    assert 240 < float(t) < 360
+
+
+def test_fire_reduces_forces_and_converges():
+    b = random_batch([10, 12])
+    model = DemoModelWrapper()
+    probe = FIRE(model, dt=0.1)
+    probe.compute(b)
+    f0 = float(b.forces.norm(dim=-1).max())
+    dyn = FIRE(model, dt=0.5, convergence_hook=ConvergenceHook.from_fmax(0.5 * f0))
+    dyn.run(b, 2000)
+    assert float(b.forces.norm(dim=-1).max()) <= 0.5 * f0 + 1e-7
+    assert dyn.step_count < 2000
+
+
+def test_frozen_systems_do_not_move():
+    b = random_batch([5, 5])
+    b.add_key("status", torch.tensor([[0], [1]]), level="system")
+    p1 = b.positions[5:].clone()
+    dyn = DemoDynamics(DemoModelWrapper(), n_steps=3, dt=0.05)
+    dyn.compute(b)
+    dyn.run(b)
+    assert torch.equal(b.positions[5:], p1) and not torch.equal(b.positions[:5], b.positions[:5] * 0 + p1[:5])
+
+
+def test_fused_stage_migrates_status():
+    b = random_batch([6, 6, 6])
+    model = DemoModelWrapper()
+    relax = FIRE(model, dt=0.1, convergence_hook=ConvergenceHook.from_fmax(1e9))  # converges at once
+    md = NVE(model, dt=0.5, n_steps=3)
+    fused = relax + md
+    assert isinstance(fused, FusedStage) and fused.exit_status == 2
+    out = fused.run(b, n_steps=10)
+    assert out.status.reshape(-1).tolist() == [2, 2, 2]
+    assert fused.step_count == 3  # the migration step already counts toward the MD budget (as in the reference)
