@@ -1,0 +1,308 @@
+// SPDX-License-Identifier: Apache-2.0
+// TF32 GEMM on the 5th-generation tensor cores: C[M,N] = act(alpha * A[M,K] @ Bt[N,K]^T).
+//
+// Used for the dense channel mixes of the native MACE (radial MLP, o3 linear layers, readouts),
+// i.e. the ops the reference runs through cuBLAS / cuEquivariance indexed_linear
+// (nvalchemi/models/mace.py:408-410).  Structure of one CTA (one 128 x BN output tile):
+//   warp 0   : TMA producer  - cp.async.bulk.tensor 2D loads of the A and B k-blocks into a
+//              128B-swizzled shared-memory ring, completion on "full" mbarriers;
+//   warp 1   : allocates TMEM, then one elected lane issues tcgen05.mma (kind::tf32,
+//              cta_group::1, M=128, N=BN, K=8) with the accumulator in TMEM and releases ring
+//              slots with tcgen05.commit on "empty" mbarriers;
+//   warps 2-5: epilogue - tcgen05.ld (32x32b) of the accumulator rows, scale / activation,
+//              vectorised global stores.
+// Every mbarrier wait is bounded; on expiry the kernel records an error code in `err`, skips the
+// remaining work, releases its TMEM and returns (no trap, no endless spin).
+#include "common.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+namespace nva {
+using at::Tensor;
+
+constexpr int BM = 128;
+constexpr int BK = 32;      // 32 tf32 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 8;   // tf32 MMA depth
+constexpr int STAGES = 3;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: returns false (and records `code`) when the phase does not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  atomicExch(err, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row groups
+// 1024 bytes apart (SBO), descriptor version 1 (Blackwell).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)0 << 16;                         // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024u >> 4) << 32;              // stride byte offset
+  d |= (uint64_t)1 << 46;                         // descriptor version
+  d |= (uint64_t)2 << 61;                         // layout: SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::tf32: fp32 accumulate, A and B both K-major, shape M x N.
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N) {
+  return (1u << 4)                    // D format = F32
+         | (2u << 7)                  // A format = TF32
+         | (2u << 10)                 // B format = TF32
+         | ((uint32_t)(N >> 3) << 17)  // N / 8
+         | ((uint32_t)(M >> 4) << 24); // M / 16
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+constexpr float kSiluNorm = 1.6790176868438721f;
+
+template <int BN>
+__global__ void __launch_bounds__(192) gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                        const __grid_constant__ CUtensorMap tmB,
+                                                        float* __restrict__ C, int M, int N, int K, int64_t ldc,
+                                                        float alpha, int act, int* __restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr uint32_t A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4, STAGE_BYTES = A_BYTES + B_BYTES;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar0 = base + STAGES * STAGE_BYTES;  // full[STAGES], empty[STAGES], tmem_full
+  const uint32_t tmem_slot = bar0 + (2 * STAGES + 1) * 8;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  const uint32_t accum_bar = bar0 + 8u * (2 * STAGES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // 1D grid, N-tiles fastest: the CTAs that share an A row-block run together and hit it in L2
+  const int n_tiles = (N + BN - 1) / BN;
+  const int m0 = (int)(blockIdx.x / n_tiles) * BM, n0 = (int)(blockIdx.x % n_tiles) * BN;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        int s = kb % STAGES;
+        if (!mbar_wait(empty_bar(s), ((kb / STAGES) & 1) ^ 1, err, 1)) break;
+        mbar_expect_tx(full_bar(s), STAGE_BYTES);
+        uint32_t sa = base + s * STAGE_BYTES;
+        tma_load_2d(sa, &tmA, kb * BK, m0, full_bar(s));
+        tma_load_2d(sa + A_BYTES, &tmB, kb * BK, n0, full_bar(s));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        int s = kb % STAGES;
+        ok = mbar_wait(full_bar(s), (kb / STAGES) & 1, err, 2);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t sa = base + s * STAGE_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          uint64_t da = umma_desc_sw128(sa + k * UMMA_K * 4);
+          uint64_t db = umma_desc_sw128(sa + A_BYTES + k * UMMA_K * 4);
+          umma_tf32(tmem_base, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar(s));  // slot reusable once these MMAs have read it
+      }
+      umma_commit(accum_bar);       // accumulator complete (or abandoned) - releases the epilogue
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    if (mbar_wait(accum_bar, 0, err, 3)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      int row = m0 + q * 32 + lane;
+      bool vec_ok = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+#pragma unroll 1
+      for (int cb = 0; cb < BN / 32; ++cb) {
+        float v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), v);
+        int col0 = n0 + cb * 32;
+        if (row < M && col0 < N) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = v[j] * alpha;
+            if (act == 1) x = x / (1.f + __expf(-x)) * kSiluNorm;
+            v[j] = x;
+          }
+          float* dst = C + (int64_t)row * ldc + col0;
+          if (vec_ok && col0 + 32 <= N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = v[j];
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    C10_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    TORCH_CHECK(p != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available");
+    fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  return fn;
+}
+
+// 2D fp32 row-major [rows, cols] with row stride `ld` elements; box = [box_rows, BK], 128B swizzle.
+static CUtensorMap make_map(const float* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  CUtensorMap m;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = get_encode()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+  return m;
+}
+
+static Tensor& error_word(const at::Device& dev) {
+  static std::vector<Tensor> words(64);
+  Tensor& w = words[dev.index() < 0 ? 0 : dev.index()];
+  if (!w.defined()) w = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(dev));
+  return w;
+}
+
+// a [M,K] (row stride lda, K contiguous), bt [N,K] contiguous -> c [M,N] (new, contiguous) or into `out`.
+Tensor gemm_tf32_impl(const Tensor& a, const Tensor& bt, double alpha, int64_t act, const c10::optional<Tensor>& out) {
+  TORCH_CHECK(a.is_cuda() && bt.is_cuda() && a.scalar_type() == at::kFloat && bt.scalar_type() == at::kFloat,
+              "gemm_tf32 expects float32 CUDA tensors");
+  TORCH_CHECK(a.dim() == 2 && bt.dim() == 2 && a.size(1) == bt.size(1), "gemm_tf32: shapes [M,K] x [N,K]");
+  TORCH_CHECK(a.stride(1) == 1 && bt.stride(1) == 1, "gemm_tf32: K must be the contiguous axis");
+  c10::cuda::CUDAGuard guard(a.device());
+  int64_t M = a.size(0), K = a.size(1), N = bt.size(0);
+  int64_t lda = a.stride(0), ldb = bt.stride(0);
+  TORCH_CHECK(K % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0, "gemm_tf32: K and row strides must be multiples of 4");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(bt.data_ptr()) & 15) == 0,
+              "gemm_tf32: operands must be 16-byte aligned");
+  Tensor c = out.has_value() ? *out : at::empty({M, N}, a.options());
+  TORCH_CHECK(c.size(0) == M && c.size(1) == N && c.stride(1) == 1, "gemm_tf32: bad output");
+  if (M == 0 || N == 0) return c;
+  if (K == 0) return c.zero_();
+  int bn = N <= 64 ? 64 : 128;
+  CUtensorMap ma = make_map(a.data_ptr<float>(), M, K, lda, BM);
+  CUtensorMap mb = make_map(bt.data_ptr<float>(), N, K, ldb, bn);
+  int64_t tiles = ((N + bn - 1) / bn) * ((M + BM - 1) / BM);
+  TORCH_CHECK(tiles < (int64_t)2147483647, "gemm_tf32: too many tiles");
+  dim3 grid((unsigned)tiles);
+  int* err = error_word(a.device()).data_ptr<int>();
+  auto st = at::cuda::getCurrentCUDAStream();
+  if (bn == 64) {
+    size_t smem = STAGES * (BM * BK * 4 + 64 * BK * 4) + 1024 + 256;
+    static bool set64 = false;
+    if (!set64) { C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_tf32_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set64 = true; }
+    gemm_tf32_kernel<64><<<grid, 192, smem, st>>>(ma, mb, c.data_ptr<float>(), (int)M, (int)N, (int)K, c.stride(0),
+                                                  (float)alpha, (int)act, err);
+  } else {
+    size_t smem = STAGES * (BM * BK * 4 + 128 * BK * 4) + 1024 + 256;
+    static bool set128 = false;
+    if (!set128) { C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_tf32_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set128 = true; }
+    gemm_tf32_kernel<128><<<grid, 192, smem, st>>>(ma, mb, c.data_ptr<float>(), (int)M, (int)N, (int)K, c.stride(0),
+                                                   (float)alpha, (int)act, err);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return c;
+}
+
+Tensor gemm_tf32(const Tensor& a, const Tensor& bt, double alpha, int64_t act) {
+  return gemm_tf32_impl(a, bt, alpha, act, c10::nullopt);
+}
+void gemm_tf32_out(const Tensor& a, const Tensor& bt, double alpha, int64_t act, Tensor out) {
+  gemm_tf32_impl(a, bt, alpha, act, out);
+}
+
+// Reads (and clears) the error word: 0 = no bounded wait expired since the last call.
+int64_t gemm_error_status(const Tensor& like) {
+  Tensor& w = error_word(like.device());
+  int64_t v = w.item<int>();
+  if (v != 0) w.zero_();
+  return v;
+}
+
+}  // namespace nva
+
+TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
+  m.def("gemm_tf32(Tensor a, Tensor bt, float alpha=1.0, int act=0) -> Tensor", &nva::gemm_tf32);
+  m.def("gemm_tf32_out(Tensor a, Tensor bt, float alpha, int act, Tensor(a!) out) -> ()", &nva::gemm_tf32_out);
+  m.def("gemm_error_status(Tensor like) -> int", &nva::gemm_error_status);
+}

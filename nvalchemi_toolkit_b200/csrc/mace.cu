@@ -1,0 +1,513 @@
+// SPDX-License-Identifier: Apache-2.0
+// Native MACE kernels for sm_100a: edge radial features, fused (geometry + channel-wise tensor
+// product + neighbour aggregation) convolution forward/backward, symmetric contraction
+// forward/backward.  They replace the e3nn / cuEquivariance ops the reference reaches through
+// mace-torch (nvalchemi/models/mace.py:205-332,403-411).
+//
+// Layout: node features [N, n_lm, C] with the channel fastest; one CUDA thread owns one channel of
+// one receiver atom, so all global accesses are coalesced over channels and the aggregation over
+// neighbours happens in registers (edges are stored CSR by receiver: no atomics in the forward).
+// Edge vectors point sender -> receiver: vec = r_i - (r_j + S @ cell).
+#include "common.cuh"
+#include "mace_tables.h"
+
+namespace nva {
+using at::Tensor;
+
+constexpr int kEdgeTile = 32;
+
+struct EdgeGeom {  // per-edge quantities shared by the channels of a block
+  float Y[16];
+  float n[3];
+  float rinv;
+};
+
+__device__ __forceinline__ void sh_l3(float x, float y, float z, float* Y) {
+  const float s3 = 1.7320508075688772f, s5 = 2.23606797749979f, s15 = 3.872983346207417f,
+              s70 = 8.366600265340756f, s105 = 10.246950765959598f, s42 = 6.48074069840786f,
+              s7 = 2.6457513110645907f;
+  float x2 = x * x, y2 = y * y, z2 = z * z;
+  Y[0] = 1.f;
+  Y[1] = s3 * y; Y[2] = s3 * z; Y[3] = s3 * x;
+  Y[4] = s15 * x * y; Y[5] = s15 * y * z; Y[6] = 0.5f * s5 * (2.f * z2 - x2 - y2); Y[7] = s15 * x * z;
+  Y[8] = 0.5f * s15 * (x2 - y2);
+  Y[9] = 0.25f * s70 * y * (3.f * x2 - y2); Y[10] = s105 * x * y * z;
+  Y[11] = 0.25f * s42 * y * (4.f * z2 - x2 - y2); Y[12] = 0.5f * s7 * z * (2.f * z2 - 3.f * x2 - 3.f * y2);
+  Y[13] = 0.25f * s42 * x * (4.f * z2 - x2 - y2); Y[14] = 0.5f * s105 * z * (x2 - y2);
+  Y[15] = 0.25f * s70 * x * (x2 - 3.f * y2);
+}
+
+// g += sum_b dY[b] * dY_b/dn (gradient of the homogeneous polynomials w.r.t. the unit vector),
+// s = sum_b l_b dY[b] Y[b]  (Euler term of the projection onto the sphere)
+__device__ __forceinline__ void sh_l3_vjp(float x, float y, float z, const float* Y, const float* dY, float* g,
+                                          float& s) {
+  const float s3 = 1.7320508075688772f, s5 = 2.23606797749979f, s15 = 3.872983346207417f,
+              s70 = 8.366600265340756f, s105 = 10.246950765959598f, s42 = 6.48074069840786f,
+              s7 = 2.6457513110645907f;
+  float x2 = x * x, y2 = y * y, z2 = z * z;
+  float gx = 0.f, gy = 0.f, gz = 0.f;
+  gy += s3 * dY[1]; gz += s3 * dY[2]; gx += s3 * dY[3];
+  gx += s15 * y * dY[4]; gy += s15 * x * dY[4];
+  gy += s15 * z * dY[5]; gz += s15 * y * dY[5];
+  gx += -s5 * x * dY[6]; gy += -s5 * y * dY[6]; gz += 2.f * s5 * z * dY[6];
+  gx += s15 * z * dY[7]; gz += s15 * x * dY[7];
+  gx += s15 * x * dY[8]; gy += -s15 * y * dY[8];
+  gx += 0.25f * s70 * 6.f * x * y * dY[9]; gy += 0.25f * s70 * (3.f * x2 - 3.f * y2) * dY[9];
+  gx += s105 * y * z * dY[10]; gy += s105 * x * z * dY[10]; gz += s105 * x * y * dY[10];
+  gx += 0.25f * s42 * (-2.f * x * y) * dY[11]; gy += 0.25f * s42 * (4.f * z2 - x2 - 3.f * y2) * dY[11];
+  gz += 0.25f * s42 * 8.f * y * z * dY[11];
+  gx += 0.5f * s7 * (-6.f * x * z) * dY[12]; gy += 0.5f * s7 * (-6.f * y * z) * dY[12];
+  gz += 0.5f * s7 * (6.f * z2 - 3.f * x2 - 3.f * y2) * dY[12];
+  gx += 0.25f * s42 * (4.f * z2 - 3.f * x2 - y2) * dY[13]; gy += 0.25f * s42 * (-2.f * x * y) * dY[13];
+  gz += 0.25f * s42 * 8.f * x * z * dY[13];
+  gx += 0.5f * s105 * 2.f * x * z * dY[14]; gy += 0.5f * s105 * (-2.f * y * z) * dY[14];
+  gz += 0.5f * s105 * (x2 - y2) * dY[14];
+  gx += 0.25f * s70 * (3.f * x2 - 3.f * y2) * dY[15]; gy += 0.25f * s70 * (-6.f * x * y) * dY[15];
+  g[0] = gx; g[1] = gy; g[2] = gz;
+  float s1 = dY[1] * Y[1] + dY[2] * Y[2] + dY[3] * Y[3];
+  float s2 = dY[4] * Y[4] + dY[5] * Y[5] + dY[6] * Y[6] + dY[7] * Y[7] + dY[8] * Y[8];
+  float s3_ = dY[9] * Y[9] + dY[10] * Y[10] + dY[11] * Y[11] + dY[12] * Y[12] + dY[13] * Y[13] + dY[14] * Y[14] +
+              dY[15] * Y[15];
+  s = s1 + 2.f * s2 + 3.f * s3_;
+}
+
+__device__ __forceinline__ void edge_vector(const float* __restrict__ pos, const float* __restrict__ cell,
+                                            const int* __restrict__ batch_idx, int i, int j,
+                                            const int* __restrict__ S, float* v) {
+  const float* H = cell + 9 * batch_idx[i];
+  float s0 = (float)S[0], s1 = (float)S[1], s2 = (float)S[2];
+  v[0] = pos[3 * i] - (pos[3 * j] + s0 * H[0] + s1 * H[3] + s2 * H[6]);
+  v[1] = pos[3 * i + 1] - (pos[3 * j + 1] + s0 * H[1] + s1 * H[4] + s2 * H[7]);
+  v[2] = pos[3 * i + 2] - (pos[3 * j + 2] + s0 * H[2] + s1 * H[5] + s2 * H[8]);
+}
+
+// ---- radial features: Bessel * polynomial cutoff and their derivative w.r.t. r ----------------
+// out [E_chunk, 2, nb]: row 0 = features, row 1 = d/dr (zero features beyond r_max).
+__global__ void edge_radial_kernel(int64_t e0, int64_t ne, const float* __restrict__ pos,
+                                   const float* __restrict__ cell, const int* __restrict__ batch_idx,
+                                   const int* __restrict__ erecv, const int* __restrict__ esend,
+                                   const int* __restrict__ eS, float rmax, int nb, int p, bool with_grad,
+                                   float* __restrict__ out) {
+  int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (t >= ne) return;
+  int64_t e = e0 + t;
+  float v[3];
+  edge_vector(pos, cell, batch_idx, erecv[e], esend[e], eS + 3 * e, v);
+  float r = sqrtf(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]);
+  int stride = with_grad ? 2 * nb : nb;
+  float* o = out + t * stride;
+  if (r >= rmax || r <= 0.f) {
+    for (int k = 0; k < stride; ++k) o[k] = 0.f;
+    return;
+  }
+  float x = r / rmax, fp = (float)p;
+  float xp = powf(x, fp - 1.f);  // x^(p-1)
+  float env = 1.f - 0.5f * (fp + 1.f) * (fp + 2.f) * xp * x + fp * (fp + 2.f) * xp * x * x -
+              0.5f * fp * (fp + 1.f) * xp * x * x * x;
+  float denv = (-0.5f * (fp + 1.f) * (fp + 2.f) * fp * xp + fp * (fp + 2.f) * (fp + 1.f) * xp * x -
+                0.5f * fp * (fp + 1.f) * (fp + 2.f) * xp * x * x) / rmax;
+  float pref = sqrtf(2.f / rmax), rinv = 1.f / r;
+  for (int k = 0; k < nb; ++k) {
+    float w = (float)(k + 1) * 3.14159265358979323846f / rmax;
+    float sn, cs;
+    sincosf(w * r, &sn, &cs);
+    float b = pref * sn * rinv;
+    o[k] = b * env;
+    if (with_grad) o[nb + k] = (pref * w * cs * rinv - b * rinv) * env + b * denv;
+  }
+}
+
+// ---- convolution forward -------------------------------------------------------------------------
+// mid[i, :, c] = sum_{e in edges(i)} TP(u[sender(e), :, c], Y(e), R[e, :, c])      (thread = channel)
+template <int NIN, int NPATH, int NMID, bool L1>
+__global__ void __launch_bounds__(256) conv_fwd_kernel(
+    int i0, const float* __restrict__ u, const float* __restrict__ pos, const float* __restrict__ cell,
+    const int* __restrict__ batch_idx, const int* __restrict__ eptr, const int* __restrict__ esend,
+    const int* __restrict__ eS, const float* __restrict__ R, int64_t e_chunk0, float rmax, int C,
+    float* __restrict__ mid) {
+  __shared__ float sY[kEdgeTile][16];
+  __shared__ int sj[kEdgeTile];
+  int i = i0 + blockIdx.x;
+  int c = threadIdx.x;
+  float acc[NMID];
+#pragma unroll
+  for (int o = 0; o < NMID; ++o) acc[o] = 0.f;
+  int eb = eptr[i], ee = eptr[i + 1];
+  for (int base = eb; base < ee; base += kEdgeTile) {
+    int nt = min(kEdgeTile, ee - base);
+    if (threadIdx.x < nt) {
+      int e = base + threadIdx.x;
+      int j = esend[e];
+      float v[3];
+      edge_vector(pos, cell, batch_idx, i, j, eS + 3 * e, v);
+      float r = sqrtf(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]);
+      bool ok = r < rmax && r > 0.f;
+      float ri = ok ? 1.f / r : 0.f;
+      sh_l3(v[0] * ri, v[1] * ri, v[2] * ri, sY[threadIdx.x]);
+      sj[threadIdx.x] = ok ? j : -1;
+    }
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      int j = sj[t];
+      if (j < 0) continue;
+      float h[NIN], Rv[NPATH];
+      const float* up = u + (int64_t)j * NIN * C + c;
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) h[a] = __ldg(up + a * C);
+      const float* rp = R + ((int64_t)(base + t) - e_chunk0) * NPATH * C + c;
+#pragma unroll
+      for (int p = 0; p < NPATH; ++p) Rv[p] = __ldg(rp + p * C);
+      const float* Y = sY[t];
+      if (L1) { MACE_L1_FWD(h, Y, Rv, acc); } else { MACE_L0_FWD(h, Y, Rv, acc); }
+    }
+    __syncthreads();
+  }
+  float* mp = mid + (int64_t)i * NMID * C + c;
+#pragma unroll
+  for (int o = 0; o < NMID; ++o) mp[o * C] = acc[o];
+}
+
+// ---- convolution backward ------------------------------------------------------------------------
+// Given G = dE/dmid: du[sender] += ..., dE/dvec per edge -> grad_pos (receiver +, sender -), optional
+// per-system virial sum_e vec (x) dE/dvec.  RD holds [R | dR/dr] per edge: [E_chunk, 2, NPATH, C].
+template <int NIN, int NPATH, int NMID, bool L1, bool NEED_DU>
+__global__ void __launch_bounds__(256) conv_bwd_kernel(
+    int i0, const float* __restrict__ u, const float* __restrict__ G, const float* __restrict__ pos,
+    const float* __restrict__ cell, const int* __restrict__ batch_idx, const int* __restrict__ eptr,
+    const int* __restrict__ esend, const int* __restrict__ eS, const float* __restrict__ RD, int64_t e_chunk0,
+    float rmax, int C, float* __restrict__ du, float* __restrict__ grad_pos, double* __restrict__ virial) {
+  __shared__ EdgeGeom sg[kEdgeTile];
+  __shared__ float sv[kEdgeTile][3];
+  __shared__ int sj[kEdgeTile];
+  __shared__ float sred[kEdgeTile][8][3];
+  int i = i0 + blockIdx.x;
+  int c = threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  float Gr[NMID];
+  const float* gp = G + (int64_t)i * NMID * C + c;
+#pragma unroll
+  for (int o = 0; o < NMID; ++o) Gr[o] = gp[o * C];
+  int eb = eptr[i], ee = eptr[i + 1];
+  float fi[3] = {0.f, 0.f, 0.f};
+  float vir[9] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int base = eb; base < ee; base += kEdgeTile) {
+    int nt = min(kEdgeTile, ee - base);
+    if (threadIdx.x < nt) {
+      int e = base + threadIdx.x;
+      int j = esend[e];
+      float v[3];
+      edge_vector(pos, cell, batch_idx, i, j, eS + 3 * e, v);
+      float r = sqrtf(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]);
+      bool ok = r < rmax && r > 0.f;
+      float ri = ok ? 1.f / r : 0.f;
+      EdgeGeom& g = sg[threadIdx.x];
+      g.n[0] = v[0] * ri; g.n[1] = v[1] * ri; g.n[2] = v[2] * ri; g.rinv = ri;
+      sh_l3(g.n[0], g.n[1], g.n[2], g.Y);
+      sv[threadIdx.x][0] = v[0]; sv[threadIdx.x][1] = v[1]; sv[threadIdx.x][2] = v[2];
+      sj[threadIdx.x] = ok ? j : -1;
+    }
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      int j = sj[t];
+      float f[3] = {0.f, 0.f, 0.f};
+      if (j >= 0) {
+        float h[NIN], Rv[NPATH], dh[NIN], dY[16], S[NPATH];
+        const float* up = u + (int64_t)j * NIN * C + c;
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) { h[a] = __ldg(up + a * C); dh[a] = 0.f; }
+        const float* rp = RD + ((int64_t)(base + t) - e_chunk0) * 2 * NPATH * C + c;
+#pragma unroll
+        for (int p = 0; p < NPATH; ++p) Rv[p] = __ldg(rp + p * C);
+#pragma unroll
+        for (int b = 0; b < 16; ++b) dY[b] = 0.f;
+        const EdgeGeom& g = sg[t];
+        const float* Y = g.Y;
+        if (L1) { MACE_L1_BWD(h, Y, Rv, Gr, dh, dY, S); } else { MACE_L0_BWD(h, Y, Rv, Gr, dh, dY, S); }
+        float q = 0.f;
+#pragma unroll
+        for (int p = 0; p < NPATH; ++p) q = fmaf(S[p], __ldg(rp + (NPATH + p) * C), q);
+        float gy[3], s;
+        sh_l3_vjp(g.n[0], g.n[1], g.n[2], Y, dY, gy, s);
+#pragma unroll
+        for (int d = 0; d < 3; ++d) f[d] = (gy[d] - s * g.n[d]) * g.rinv + q * g.n[d];
+        if (NEED_DU) {
+          float* dp = du + (int64_t)j * NIN * C + c;
+#pragma unroll
+          for (int a = 0; a < NIN; ++a) atomicAdd(dp + a * C, dh[a]);
+        }
+      }
+#pragma unroll
+      for (int d = 0; d < 3; ++d) {
+        float x = f[d];
+        for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
+        if (lane == 0) sred[t][warp][d] = x;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < nt) {
+      int j = sj[threadIdx.x];
+      if (j >= 0) {
+        float f[3] = {0.f, 0.f, 0.f};
+        for (int w = 0; w < nwarp; ++w)
+          for (int d = 0; d < 3; ++d) f[d] += sred[threadIdx.x][w][d];
+        for (int d = 0; d < 3; ++d) {
+          atomicAdd(grad_pos + 3 * (int64_t)j + d, -f[d]);
+          fi[d] += f[d];
+        }
+        if (virial != nullptr)
+          for (int a = 0; a < 3; ++a)
+            for (int b = 0; b < 3; ++b) vir[3 * a + b] += sv[threadIdx.x][a] * f[b];
+      }
+    }
+    __syncthreads();
+  }
+  // threads 0..31 of warp 0 hold per-edge partial sums for the receiver: reduce and commit
+  if (warp == 0) {
+    for (int d = 0; d < 3; ++d) {
+      float x = fi[d];
+      for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
+      if (lane == 0) atomicAdd(grad_pos + 3 * (int64_t)i + d, x);
+    }
+    if (virial != nullptr) {
+      for (int k = 0; k < 9; ++k) {
+        float x = vir[k];
+        for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
+        if (lane == 0) atomicAdd(virial + 9 * (int64_t)batch_idx[i] + k, (double)x);
+      }
+    }
+  }
+}
+
+// ---- symmetric contraction -----------------------------------------------------------------------
+// out[n, M, c] = sum_nu sum_eta W_nu[z_n, eta, c] * sum_terms coef * prod x[n, idx, c]
+struct SymTable {
+  const unsigned int* idx; const float* coef; const unsigned short* grp; int nterms; int nbasis;
+};
+
+template <int NU>
+__device__ __forceinline__ void sym_accumulate(const SymTable t, int dL, const float* x /*smem [16][blockDim]*/,
+                                               int stride, const float* __restrict__ w, int C, float* out) {
+  // terms are sorted by group = eta*dL + M
+  int k = 0;
+  while (k < t.nterms) {
+    int g = t.grp[k];
+    float acc = 0.f;
+    while (k < t.nterms && t.grp[k] == g) {
+      unsigned int id = t.idx[k];
+      float m = x[(id & 255u) * stride];
+      if (NU >= 2) m *= x[((id >> 8) & 255u) * stride];
+      if (NU >= 3) m *= x[((id >> 16) & 255u) * stride];
+      acc = fmaf(t.coef[k], m, acc);
+      ++k;
+    }
+    int eta = g / dL, M = g - eta * dL;
+    out[M] = fmaf(__ldg(w + eta * C), acc, out[M]);
+  }
+}
+
+template <int NU>
+__device__ __forceinline__ void sym_backward(const SymTable t, int dL, const float* x, float* dx, int stride,
+                                             const float* __restrict__ w, int C, const float* gout) {
+  for (int k = 0; k < t.nterms; ++k) {
+    int g = t.grp[k];
+    int eta = g / dL, M = g - eta * dL;
+    float s = t.coef[k] * __ldg(w + eta * C) * gout[M];
+    unsigned int id = t.idx[k];
+    int a = id & 255u, b = (id >> 8) & 255u, cc = (id >> 16) & 255u;
+    if (NU == 1) {
+      dx[a * stride] += s;
+    } else if (NU == 2) {
+      float xa = x[a * stride], xb = x[b * stride];
+      dx[a * stride] += s * xb;
+      dx[b * stride] += s * xa;
+    } else {
+      float xa = x[a * stride], xb = x[b * stride], xc = x[cc * stride];
+      dx[a * stride] += s * xb * xc;
+      dx[b * stride] += s * xa * xc;
+      dx[cc * stride] += s * xa * xb;
+    }
+  }
+}
+
+__device__ __forceinline__ SymTable sym_table(int nu, int L) {
+  SymTable t;
+  if (L == 0) {
+    if (nu == 1) t = {mace_sym_1_0_idx, mace_sym_1_0_coef, mace_sym_1_0_grp, MACE_SYM_1_0_NTERMS, MACE_SYM_1_0_NBASIS};
+    else if (nu == 2) t = {mace_sym_2_0_idx, mace_sym_2_0_coef, mace_sym_2_0_grp, MACE_SYM_2_0_NTERMS, MACE_SYM_2_0_NBASIS};
+    else t = {mace_sym_3_0_idx, mace_sym_3_0_coef, mace_sym_3_0_grp, MACE_SYM_3_0_NTERMS, MACE_SYM_3_0_NBASIS};
+  } else {
+    if (nu == 1) t = {mace_sym_1_1_idx, mace_sym_1_1_coef, mace_sym_1_1_grp, MACE_SYM_1_1_NTERMS, MACE_SYM_1_1_NBASIS};
+    else if (nu == 2) t = {mace_sym_2_1_idx, mace_sym_2_1_coef, mace_sym_2_1_grp, MACE_SYM_2_1_NTERMS, MACE_SYM_2_1_NBASIS};
+    else t = {mace_sym_3_1_idx, mace_sym_3_1_coef, mace_sym_3_1_grp, MACE_SYM_3_1_NTERMS, MACE_SYM_3_1_NBASIS};
+  }
+  return t;
+}
+
+// weights are packed per L as [Z, nb1 + nb2 + nb3, C] (degree blocks in that order, degrees above
+// `correlation` are simply absent from the loop).
+template <bool BWD>
+__global__ void symcon_kernel(int64_t n_nodes, int C, int lmax_out, int correlation, const float* __restrict__ x,
+                              const int* __restrict__ species, const float* __restrict__ w0,
+                              const float* __restrict__ w1, int nbtot0, int nbtot1, float* __restrict__ out,
+                              const float* __restrict__ gout, float* __restrict__ dx) {
+  extern __shared__ float smem[];  // [16][blockDim] x, and for BWD another [16][blockDim] dx
+  int tid = threadIdx.x;
+  int64_t gidx = blockIdx.x * (int64_t)blockDim.x + tid;
+  int64_t n = gidx / C;
+  int c = (int)(gidx - n * C);
+  if (n >= n_nodes) return;
+  int stride = blockDim.x;
+  float* xs = smem + tid;
+  float* dxs = smem + 16 * stride + tid;
+  const float* xp = x + n * 16 * C + c;
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    xs[k * stride] = xp[k * C];
+    if (BWD) dxs[k * stride] = 0.f;
+  }
+  int z = species[n];
+  int nout = (lmax_out + 1) * (lmax_out + 1);
+  int ooff = 0;
+  for (int L = 0; L <= lmax_out; ++L) {
+    int dL = 2 * L + 1;
+    const float* w = (L == 0 ? w0 + (int64_t)z * nbtot0 * C : w1 + (int64_t)z * nbtot1 * C) + c;
+    float o[3] = {0.f, 0.f, 0.f};
+    float go[3] = {0.f, 0.f, 0.f};
+    if (BWD)
+      for (int M = 0; M < dL; ++M) go[M] = gout[(n * nout + ooff + M) * C + c];
+    int boff = 0;
+    for (int nu = 1; nu <= correlation; ++nu) {
+      SymTable t = sym_table(nu, L);
+      const float* wn = w + (int64_t)boff * C;
+      if (!BWD) {
+        if (nu == 1) sym_accumulate<1>(t, dL, xs, stride, wn, C, o);
+        else if (nu == 2) sym_accumulate<2>(t, dL, xs, stride, wn, C, o);
+        else sym_accumulate<3>(t, dL, xs, stride, wn, C, o);
+      } else {
+        if (nu == 1) sym_backward<1>(t, dL, xs, dxs, stride, wn, C, go);
+        else if (nu == 2) sym_backward<2>(t, dL, xs, dxs, stride, wn, C, go);
+        else sym_backward<3>(t, dL, xs, dxs, stride, wn, C, go);
+      }
+      boff += t.nbasis;
+    }
+    if (!BWD)
+      for (int M = 0; M < dL; ++M) out[(n * nout + ooff + M) * C + c] = o[M];
+    ooff += dL;
+  }
+  if (BWD) {
+    float* dp = dx + n * 16 * C + c;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) dp[k * C] = dxs[k * stride];
+  }
+}
+
+// ---- host wrappers -------------------------------------------------------------------------------
+Tensor mace_edge_radial(const Tensor& pos, const Tensor& cell, const Tensor& batch_idx, const Tensor& erecv,
+                        const Tensor& esend, const Tensor& eS, int64_t e0, int64_t ne, double rmax, int64_t nb,
+                        int64_t p, bool with_grad) {
+  c10::cuda::CUDAGuard guard(pos.device());
+  Tensor out = at::empty({ne, with_grad ? 2 : 1, nb}, pos.options());
+  if (ne == 0) return out;
+  edge_radial_kernel<<<(unsigned)((ne + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      e0, ne, pos.data_ptr<float>(), cell.data_ptr<float>(), batch_idx.data_ptr<int>(), erecv.data_ptr<int>(),
+      esend.data_ptr<int>(), eS.data_ptr<int>(), (float)rmax, (int)nb, (int)p, with_grad, out.data_ptr<float>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+void mace_conv_fwd(const Tensor& u, const Tensor& pos, const Tensor& cell, const Tensor& batch_idx,
+                   const Tensor& eptr, const Tensor& esend, const Tensor& eS, const Tensor& R, int64_t i0,
+                   int64_t ni, int64_t e_chunk0, double rmax, Tensor mid) {
+  c10::cuda::CUDAGuard guard(pos.device());
+  NVA_CHECK_CONTIG(u); NVA_CHECK_CONTIG(R); NVA_CHECK_CONTIG(mid);
+  int C = (int)u.size(2), nin = (int)u.size(1);
+  TORCH_CHECK(C % 32 == 0 && C <= 256, "channels must be a multiple of 32 and <= 256");
+  if (ni == 0) return;
+  auto st = at::cuda::getCurrentCUDAStream();
+#define NVA_ARGS (int)i0, u.data_ptr<float>(), pos.data_ptr<float>(), cell.data_ptr<float>(), batch_idx.data_ptr<int>(), \
+    eptr.data_ptr<int>(), esend.data_ptr<int>(), eS.data_ptr<int>(), R.data_ptr<float>(), e_chunk0, (float)rmax, C, \
+    mid.data_ptr<float>()
+  if (nin == 1) {
+    TORCH_CHECK(mid.size(1) == MACE_L0_NMID && R.size(1) == MACE_L0_NPATH, "layer-0 shapes");
+    conv_fwd_kernel<MACE_L0_NIN, MACE_L0_NPATH, MACE_L0_NMID, false><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
+  } else {
+    TORCH_CHECK(nin == 4 && mid.size(1) == MACE_L1_NMID && R.size(1) == MACE_L1_NPATH, "layer-1 shapes");
+    conv_fwd_kernel<MACE_L1_NIN, MACE_L1_NPATH, MACE_L1_NMID, true><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
+  }
+#undef NVA_ARGS
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void mace_conv_bwd(const Tensor& u, const Tensor& G, const Tensor& pos, const Tensor& cell,
+                   const Tensor& batch_idx, const Tensor& eptr, const Tensor& esend, const Tensor& eS,
+                   const Tensor& RD, int64_t i0, int64_t ni, int64_t e_chunk0, double rmax,
+                   const c10::optional<Tensor>& du, Tensor grad_pos, const c10::optional<Tensor>& virial) {
+  c10::cuda::CUDAGuard guard(pos.device());
+  NVA_CHECK_CONTIG(u); NVA_CHECK_CONTIG(RD); NVA_CHECK_CONTIG(G);
+  int C = (int)u.size(2), nin = (int)u.size(1);
+  TORCH_CHECK(C % 32 == 0 && C <= 256, "channels must be a multiple of 32 and <= 256");
+  if (ni == 0) return;
+  auto st = at::cuda::getCurrentCUDAStream();
+  float* dup = du.has_value() ? du->data_ptr<float>() : nullptr;
+  double* vp = virial.has_value() ? virial->data_ptr<double>() : nullptr;
+#define NVA_ARGS (int)i0, u.data_ptr<float>(), G.data_ptr<float>(), pos.data_ptr<float>(), cell.data_ptr<float>(), \
+    batch_idx.data_ptr<int>(), eptr.data_ptr<int>(), esend.data_ptr<int>(), eS.data_ptr<int>(), RD.data_ptr<float>(), \
+    e_chunk0, (float)rmax, C, dup, grad_pos.data_ptr<float>(), vp
+  if (nin == 1) {
+    if (dup) conv_bwd_kernel<MACE_L0_NIN, MACE_L0_NPATH, MACE_L0_NMID, false, true><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
+    else conv_bwd_kernel<MACE_L0_NIN, MACE_L0_NPATH, MACE_L0_NMID, false, false><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
+  } else {
+    if (dup) conv_bwd_kernel<MACE_L1_NIN, MACE_L1_NPATH, MACE_L1_NMID, true, true><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
+    else conv_bwd_kernel<MACE_L1_NIN, MACE_L1_NPATH, MACE_L1_NMID, true, false><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
+  }
+#undef NVA_ARGS
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+Tensor mace_symcon_fwd(const Tensor& x, const Tensor& species, const Tensor& w0, const c10::optional<Tensor>& w1,
+                       int64_t lmax_out, int64_t correlation) {
+  c10::cuda::CUDAGuard guard(x.device());
+  NVA_CHECK_CONTIG(x); NVA_CHECK_CONTIG(w0);
+  int64_t n = x.size(0);
+  int C = (int)x.size(2);
+  int nout = (int)((lmax_out + 1) * (lmax_out + 1));
+  Tensor out = at::empty({n, nout, C}, x.options());
+  if (n == 0) return out;
+  int threads = 128;
+  int64_t total = n * C;
+  size_t smem = 16 * threads * sizeof(float);
+  symcon_kernel<false><<<(unsigned)((total + threads - 1) / threads), threads, smem, at::cuda::getCurrentCUDAStream()>>>(
+      n, C, (int)lmax_out, (int)correlation, x.data_ptr<float>(), species.data_ptr<int>(), w0.data_ptr<float>(),
+      w1.has_value() ? w1->data_ptr<float>() : nullptr, (int)w0.size(1), w1.has_value() ? (int)w1->size(1) : 0,
+      out.data_ptr<float>(), nullptr, nullptr);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+Tensor mace_symcon_bwd(const Tensor& x, const Tensor& species, const Tensor& w0, const c10::optional<Tensor>& w1,
+                       int64_t lmax_out, int64_t correlation, const Tensor& gout) {
+  c10::cuda::CUDAGuard guard(x.device());
+  NVA_CHECK_CONTIG(x); NVA_CHECK_CONTIG(gout);
+  int64_t n = x.size(0);
+  int C = (int)x.size(2);
+  Tensor dx = at::empty_like(x);
+  if (n == 0) return dx;
+  int threads = 128;
+  int64_t total = n * C;
+  size_t smem = 32 * threads * sizeof(float);
+  symcon_kernel<true><<<(unsigned)((total + threads - 1) / threads), threads, smem, at::cuda::getCurrentCUDAStream()>>>(
+      n, C, (int)lmax_out, (int)correlation, x.data_ptr<float>(), species.data_ptr<int>(), w0.data_ptr<float>(),
+      w1.has_value() ? w1->data_ptr<float>() : nullptr, (int)w0.size(1), w1.has_value() ? (int)w1->size(1) : 0,
+      nullptr, gout.data_ptr<float>(), dx.data_ptr<float>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return dx;
+}
+
+}  // namespace nva
+
+TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
+  m.def("mace_edge_radial(Tensor pos, Tensor cell, Tensor batch_idx, Tensor erecv, Tensor esend, Tensor eS, int e0, int ne, float rmax, int nb, int p, bool with_grad) -> Tensor", &nva::mace_edge_radial);
+  m.def("mace_conv_fwd(Tensor u, Tensor pos, Tensor cell, Tensor batch_idx, Tensor eptr, Tensor esend, Tensor eS, Tensor R, int i0, int ni, int e_chunk0, float rmax, Tensor(a!) mid) -> ()", &nva::mace_conv_fwd);
+  m.def("mace_conv_bwd(Tensor u, Tensor G, Tensor pos, Tensor cell, Tensor batch_idx, Tensor eptr, Tensor esend, Tensor eS, Tensor RD, int i0, int ni, int e_chunk0, float rmax, Tensor(a!)? du, Tensor(b!) grad_pos, Tensor(c!)? virial) -> ()", &nva::mace_conv_bwd);
+  m.def("mace_symcon_fwd(Tensor x, Tensor species, Tensor w0, Tensor? w1, int lmax_out, int correlation) -> Tensor", &nva::mace_symcon_fwd);
+  m.def("mace_symcon_bwd(Tensor x, Tensor species, Tensor w0, Tensor? w1, int lmax_out, int correlation, Tensor gout) -> Tensor", &nva::mace_symcon_bwd);
+}

@@ -17,6 +17,7 @@ import torch
 
 from nvalchemi_toolkit_b200.dynamics._units import KB_EV
 from nvalchemi_toolkit_b200.ops import _native
+from nvalchemi_toolkit_b200.ops._native_counter import ops as _nops
 
 
 def _nat(t: torch.Tensor) -> bool:
@@ -38,7 +39,7 @@ def _to_per_system(value: float | torch.Tensor, m: int, device: torch.device, dt
 def vv_position_update(positions, velocities, forces, masses, dt, batch_idx) -> None:
     """``r += v dt + (F/2m) dt^2;  v += (F/2m) dt`` with per-system ``dt[M]``."""
     if _nat(positions):
-        torch.ops.nvalchemi.vv_position_update(positions, velocities, forces.contiguous(), masses, dt, _i32(batch_idx))
+        _nops.vv_position_update(positions, velocities, forces.contiguous(), masses, dt, _i32(batch_idx))
         return
     h = dt[batch_idx.long()].unsqueeze(-1)
     a = forces / masses.unsqueeze(-1)
@@ -49,7 +50,7 @@ def vv_position_update(positions, velocities, forces, masses, dt, batch_idx) -> 
 def vv_velocity_finalize(velocities, forces_new, masses, dt, batch_idx) -> None:
     """``v += (F_new/2m) dt``."""
     if _nat(velocities):
-        torch.ops.nvalchemi.vv_velocity_finalize(velocities, forces_new.contiguous(), masses, dt, _i32(batch_idx))
+        _nops.vv_velocity_finalize(velocities, forces_new.contiguous(), masses, dt, _i32(batch_idx))
         return
     h = dt[batch_idx.long()].unsqueeze(-1)
     velocities.add_(0.5 * h * forces_new / masses.unsqueeze(-1))
@@ -62,7 +63,7 @@ def langevin_half_step(positions, velocities, forces, masses, dt, temperature, f
     counter-based Philox stream keyed by ``(random_seed, atom index)`` so results do not depend on
     launch geometry (``atom_ids`` supplies global indices under domain decomposition)."""
     if _nat(positions):
-        torch.ops.nvalchemi.langevin_half_step(positions, velocities, forces.contiguous(), masses, dt, temperature,
+        _nops.langevin_half_step(positions, velocities, forces.contiguous(), masses, dt, temperature,
                                                friction, int(random_seed), _i32(batch_idx), atom_ids)
         return
     b = batch_idx.long()
@@ -86,7 +87,7 @@ def langevin_finalize(velocities, forces_new, masses, dt, batch_idx) -> None:
 def compute_kinetic_energy(velocities, masses, batch_idx, num_systems: int) -> torch.Tensor:
     """Per-system ``sum_i m_i v_i^2 / 2`` → ``[M]`` (fp64 accumulation)."""
     if _nat(velocities):
-        return torch.ops.nvalchemi.compute_kinetic_energy(velocities.contiguous(), masses, _i32(batch_idx), num_systems)
+        return _nops.compute_kinetic_energy(velocities.contiguous(), masses, _i32(batch_idx), num_systems)
     ke = 0.5 * masses.double() * (velocities.double() ** 2).sum(-1)
     out = torch.zeros(num_systems, dtype=torch.float64, device=velocities.device)
     return out.index_add_(0, batch_idx.long(), ke).to(velocities.dtype)
@@ -100,14 +101,14 @@ def compute_temperature(kinetic_energy: torch.Tensor, num_atoms_per_system: torc
 def momentum_sums(velocities, masses, batch_idx, num_systems: int) -> torch.Tensor:
     """``[M,4]`` fp64: ``(sum m v_x, sum m v_y, sum m v_z, sum m)``."""
     if _nat(velocities):
-        return torch.ops.nvalchemi.momentum_sums(velocities.contiguous(), masses, _i32(batch_idx), num_systems)
+        return _nops.momentum_sums(velocities.contiguous(), masses, _i32(batch_idx), num_systems)
     mv = torch.cat([masses.double().unsqueeze(-1) * velocities.double(), masses.double().unsqueeze(-1)], dim=1)
     return torch.zeros(num_systems, 4, dtype=torch.float64, device=velocities.device).index_add_(0, batch_idx.long(), mv)
 
 
 def _shift_scale(velocities, shift, scale, batch_idx) -> None:
     if _nat(velocities):
-        torch.ops.nvalchemi.velocity_shift_scale(velocities, shift.contiguous(), scale.contiguous(), _i32(batch_idx))
+        _nops.velocity_shift_scale(velocities, shift.contiguous(), scale.contiguous(), _i32(batch_idx))
         return
     b = batch_idx.long()
     velocities.sub_(shift[b]).mul_(scale[b].unsqueeze(-1))
@@ -134,7 +135,7 @@ def initialize_velocities(velocities, masses, temperature, batch_idx, random_see
     kT = _to_per_system(temperature, m, dev, dtype) * KB_EV
     b32 = _i32(batch_idx)
     if _nat(velocities):
-        torch.ops.nvalchemi.maxwell_boltzmann(velocities, masses, kT, b32, int(random_seed), atom_ids)
+        _nops.maxwell_boltzmann(velocities, masses, kT, b32, int(random_seed), atom_ids)
     else:
         gen = torch.Generator(device="cpu").manual_seed(int(random_seed))
         z = torch.randn(velocities.shape, generator=gen, dtype=torch.float64).to(velocities)
@@ -185,7 +186,7 @@ def fire_step(positions, velocities, forces, masses, alpha, dt, n_steps_positive
     vv = vv if vv is not None else torch.zeros(m, dtype=dtype, device=dev)
     ff = ff if ff is not None else torch.zeros(m, dtype=dtype, device=dev)
     if _nat(positions):
-        torch.ops.nvalchemi._fire_step_op(positions, velocities, forces.contiguous(), masses, alpha, dt, alpha_start,
+        _nops._fire_step_op(positions, velocities, forces.contiguous(), masses, alpha, dt, alpha_start,
                                           f_alpha, dt_min, dt_max, maxstep, n_steps_positive, n_min, f_dec, f_inc,
                                           uphill_flag, vf, vv, ff, _i32(batch_idx), compute_reductions)
         return
@@ -242,7 +243,7 @@ _MODES = {"sum": 0, "max": 1, "min": 2, "mean": 3}
 
 def _segmented(values: torch.Tensor, idx: torch.Tensor, num_segments: int, mode: str) -> torch.Tensor:
     if _nat(values):
-        return torch.ops.nvalchemi.segmented_reduce(values, idx, int(num_segments), _MODES[mode])
+        return _nops.segmented_reduce(values, idx, int(num_segments), _MODES[mode])
     flat = values.reshape(values.shape[0], -1)
     ix = idx.long().unsqueeze(-1).expand_as(flat)
     out = torch.zeros(num_segments, flat.shape[1], dtype=flat.dtype, device=flat.device)
@@ -284,7 +285,7 @@ def wrap_positions(positions, cell, batch_idx, pbc=None) -> torch.Tensor:
         pbc = torch.ones(b, 3, dtype=torch.bool, device=positions.device)
     inv = torch.linalg.inv(cell)
     if _nat(positions):
-        return torch.ops.nvalchemi.wrap_positions(positions.contiguous(), cell.contiguous(), inv.contiguous(),
+        return _nops.wrap_positions(positions.contiguous(), cell.contiguous(), inv.contiguous(),
                                                   pbc.contiguous(), _i32(batch_idx))
     bi = batch_idx.long()
     frac = torch.einsum("ni,nij->nj", positions, inv[bi])
@@ -311,7 +312,7 @@ def batch_neighbor_list_rebuild_inplace(reference_positions, current_positions, 
                                         cell_inv, pbc) -> None:
     """Set ``rebuild_flags[s]`` when any atom of system ``s`` moved more than the threshold (minimum image)."""
     if _nat(current_positions):
-        torch.ops.nvalchemi.neighbor_rebuild_check(reference_positions, current_positions.contiguous(), _i32(batch_idx),
+        _nops.neighbor_rebuild_check(reference_positions, current_positions.contiguous(), _i32(batch_idx),
                                                    rebuild_flags, float(skin_distance_threshold),
                                                    bool(update_reference_positions), cell.contiguous(),
                                                    cell_inv.contiguous(), pbc.contiguous())

@@ -10,7 +10,7 @@ def __getattr__(name: str):
     import importlib
 
     lazy = {"LennardJonesModelWrapper": "lj", "DFTD3ModelWrapper": "dftd3", "EwaldModelWrapper": "ewald",
-            "PMEModelWrapper": "pme", "MACEWrapper": "mace", "MACE": "mace", "PipelineModelWrapper": "pipeline",
+            "PMEModelWrapper": "pme", "MACEWrapper": "mace", "MACE": "mace", "MACEConfig": "mace", "PipelineModelWrapper": "pipeline",
             "PipelineGroup": "pipeline", "PipelineStep": "pipeline", "AIMNet2Wrapper": "aimnet2", "UMAWrapper": "uma"}
     if name in lazy:
         return getattr(importlib.import_module(f"nvalchemi_toolkit_b200.models.{lazy[name]}"), name)

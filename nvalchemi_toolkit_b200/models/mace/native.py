@@ -1,0 +1,278 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Energy + analytic forces of the native MACE through the sm_100a kernels.
+
+The backward pass is written out by hand (no autograd graph): every layer keeps only the tensors its
+adjoint needs (``u``, the aggregated message ``msg`` and the post-product features), the radial weights are
+recomputed per receiver chunk, and forces come from the adjoint of the fused convolution kernel.  This is
+the path used by MD and relaxation; the differentiable torch path in :mod:`model` is the oracle.
+
+Replaces, for the reference's MACE wrapper (``nvalchemi/models/mace.py:872-910``), the e3nn/cuEquivariance
+forward plus ``torch.autograd.grad`` for forces.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+from nvalchemi_toolkit_b200.models.mace.model import SILU_NORM
+from nvalchemi_toolkit_b200.ops import _native, gemm
+
+from nvalchemi_toolkit_b200.ops._native_counter import ops  # noqa: E402
+
+#: upper bound on the radial-weight scratch per chunk (bytes); [E_chunk, 2, P, C] floats in the backward
+CHUNK_BYTES = 2 << 30
+
+
+@dataclass
+class EdgeCSR:
+    """Receiver-major edge list derived from the dense neighbour matrix."""
+
+    eptr: torch.Tensor   # [N+1] int32
+    esend: torch.Tensor  # [E] int32
+    erecv: torch.Tensor  # [E] int32
+    eS: torch.Tensor     # [E,3] int32 (integer images of the sender)
+    eptr_host: list[int] | None = None
+    num_edges: int = 0
+
+
+def build_csr(nm: torch.Tensor, num: torch.Tensor, shifts: torch.Tensor | None) -> EdgeCSR:
+    n, k = nm.shape
+    cnt = num.clamp_max(k).to(torch.int32)
+    valid = torch.arange(k, device=nm.device, dtype=torch.int32)[None, :] < cnt[:, None]
+    esend = nm[valid].to(torch.int32).contiguous()
+    e = esend.numel()
+    eptr = torch.zeros(n + 1, dtype=torch.int32, device=nm.device)
+    torch.cumsum(cnt, 0, out=eptr[1:])
+    erecv = torch.repeat_interleave(torch.arange(n, device=nm.device, dtype=torch.int32), cnt.long(), output_size=e)
+    eS = shifts[valid].to(torch.int32).contiguous() if shifts is not None else \
+        torch.zeros(e, 3, dtype=torch.int32, device=nm.device)
+    return EdgeCSR(eptr, esend, erecv, eS, None, e)
+
+
+def csr_from_edge_index(edge_index: torch.Tensor, unit_shifts: torch.Tensor | None, n: int) -> EdgeCSR:
+    """COO (sender, receiver) → receiver-major CSR.  ``unit_shifts`` follow the MACE convention
+    (``vec = r_recv - r_send + S @ cell``); the kernels use ``vec = r_i - (r_j + S' @ cell)`` so ``S' = -S``."""
+    send, recv = edge_index[0].long(), edge_index[1].long()
+    order = torch.argsort(recv, stable=True)
+    cnt = torch.bincount(recv, minlength=n).to(torch.int32)
+    eptr = torch.zeros(n + 1, dtype=torch.int32, device=send.device)
+    torch.cumsum(cnt, 0, out=eptr[1:])
+    eS = (-unit_shifts[order]).round().to(torch.int32).contiguous() if unit_shifts is not None else \
+        torch.zeros(order.numel(), 3, dtype=torch.int32, device=send.device)
+    return EdgeCSR(eptr, send[order].to(torch.int32).contiguous(), recv[order].to(torch.int32).contiguous(), eS,
+                   None, int(order.numel()))
+
+
+def _chunks(csr: EdgeCSR, n: int, bytes_per_edge: int) -> list[tuple[int, int, int, int]]:
+    """Receiver ranges ``(i0, i1, e0, e1)`` whose radial scratch stays below ``CHUNK_BYTES``."""
+    max_edges = max(CHUNK_BYTES // max(bytes_per_edge, 1), 1024)
+    if csr.num_edges <= max_edges:
+        return [(0, n, 0, csr.num_edges)]
+    if csr.eptr_host is None:
+        csr.eptr_host = csr.eptr.cpu().tolist()  # one host copy per neighbour-list build
+    ptr = csr.eptr_host
+    out, i0 = [], 0
+    import bisect
+
+    while i0 < n:
+        i1 = bisect.bisect_right(ptr, ptr[i0] + max_edges, lo=i0 + 1, hi=n + 1) - 1
+        i1 = max(i1, i0 + 1)
+        out.append((i0, i1, ptr[i0], ptr[i1]))
+        i0 = i1
+    return out
+
+
+def _silu_and_grad(a: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    s = torch.sigmoid(a)
+    return a * s * SILU_NORM, s * (1.0 + a * (1.0 - s)) * SILU_NORM
+
+
+def _radial_weights(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool) -> torch.Tensor:
+    """``ef [E, 1|2, nb]`` → ``[E, 1|2, P*C]``: MLP value and (forward-mode) derivative w.r.t. the distance."""
+    if not with_grad:
+        x = ef[:, 0]
+        for k, w in enumerate(ws):
+            x = gemm.matmul(x, w)
+            if k < len(ws) - 1:
+                x = torch.nn.functional.silu(x).mul_(SILU_NORM)
+        return x.unsqueeze(1)
+    x, t = ef[:, 0], ef[:, 1]
+    for k, w in enumerate(ws[:-1]):
+        a = gemm.matmul(x, w)
+        ta = gemm.matmul(t, w)
+        x, g = _silu_and_grad(a)
+        t = g * ta
+    xt = torch.stack([x, t], dim=1)  # [E, 2, H]
+    out = gemm.matmul(xt.reshape(-1, xt.shape[-1]), ws[-1])
+    return out.reshape(x.shape[0], 2, -1)
+
+
+def _per_l_linear(x: torch.Tensor, w: torch.Tensor, ls: list[int], transpose: bool = False) -> torch.Tensor:
+    c = x.shape[-1]
+    out = torch.empty_like(x)
+    off = 0
+    for i, l in enumerate(ls):
+        d = 2 * l + 1
+        wi = w[i] / math.sqrt(c)
+        out[:, off: off + d] = gemm.matmul(x[:, off: off + d], wi.t() if transpose else wi)
+        off += d
+    return out
+
+
+def _skip(ip: Any, h: torch.Tensor, species: torch.Tensor, nz: int, transpose: bool = False) -> torch.Tensor:
+    """Element-dependent channel mix ``sc[:, l] = h[:, l] @ W[l, z]`` (or its adjoint)."""
+    c = h.shape[-1]
+    src_ls, dst_ls = (ip.l_out, ip.l_in) if transpose else (ip.l_in, ip.l_out)
+    n_dst = sum(2 * l + 1 for l in dst_ls)
+    out = h.new_zeros(h.shape[0], n_dst, c)
+    for z in range(nz):
+        rows = None if nz == 1 else torch.nonzero(species == z).squeeze(1)
+        if rows is not None and rows.numel() == 0:
+            continue
+        hz = h if rows is None else h[rows]
+        oz = out if rows is None else h.new_zeros(rows.numel(), n_dst, c)
+        for i, l in enumerate(ip.l_out):
+            if l not in ip.l_in:
+                continue
+            so = sum(2 * k + 1 for k in src_ls[: src_ls.index(l)])
+            do = sum(2 * k + 1 for k in dst_ls[: dst_ls.index(l)])
+            w = ip.skip[i, z] / math.sqrt(c * nz)
+            d = 2 * l + 1
+            oz[:, do: do + d] = gemm.matmul(hz[:, so: so + d], w.t() if transpose else w)
+        if rows is not None:
+            out[rows] = oz
+    return out
+
+
+def _linear_mid(ip: Any, mid: torch.Tensor, avg: float, lmax: int) -> torch.Tensor:
+    n, _, c = mid.shape
+    out = mid.new_empty(n, (lmax + 1) ** 2, c)
+    for l in range(lmax + 1):
+        npl, d = ip.paths_per_l[l], 2 * l + 1
+        blk = mid[:, ip.mid_off[l]: ip.mid_off[l] + d * npl].reshape(n, d, npl * c)
+        w = ip.linear[l] / (math.sqrt(npl * c) * avg)
+        out[:, l * l: l * l + d] = gemm.matmul(blk, w)
+    return out
+
+
+def _linear_mid_bwd(ip: Any, dmsg: torch.Tensor, avg: float, lmax: int) -> torch.Tensor:
+    n, _, c = dmsg.shape
+    dmid = dmsg.new_empty(n, ip.n_mid, c)
+    for l in range(lmax + 1):
+        npl, d = ip.paths_per_l[l], 2 * l + 1
+        w = ip.linear[l] / (math.sqrt(npl * c) * avg)
+        res = gemm.matmul(dmsg[:, l * l: l * l + d], w.t())  # [n, d, npl*c]
+        dmid[:, ip.mid_off[l]: ip.mid_off[l] + d * npl] = res.reshape(n, d * npl, c)
+    return dmid
+
+
+def _sym_weights(ip: Any, corr: int) -> tuple[torch.Tensor, torch.Tensor | None]:
+    packs = []
+    for L in ip.l_out:
+        packs.append(torch.cat([ip.sym[f"w{nu}_{L}"] for nu in range(1, corr + 1)], dim=1).contiguous())
+    return packs[0], (packs[1] if len(packs) > 1 else None)
+
+
+@torch.no_grad()
+def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, batch: torch.Tensor,
+            num_graphs: int, compute_force: bool, compute_stress: bool) -> dict[str, torch.Tensor | None]:
+    _native.require(data["positions"])
+    cfg = model.config
+    pos = data["positions"].detach().contiguous()
+    n = pos.shape[0]
+    dev = pos.device
+    cell = data.get("cell")
+    if cell is None:
+        cell = torch.eye(3, device=dev, dtype=pos.dtype).expand(num_graphs, 3, 3)
+    cell = cell.detach().to(pos.dtype).contiguous()
+    b32 = batch.to(torch.int32).contiguous()
+    sp32 = species.to(torch.int32).contiguous()
+    csr = data.get("_csr")
+    if csr is None:
+        if data.get("neighbor_matrix") is not None:
+            csr = build_csr(data["neighbor_matrix"], data["num_neighbors"], data.get("neighbor_matrix_shifts"))
+        else:
+            csr = csr_from_edge_index(data["edge_index"], data.get("unit_shifts"), n)
+    C, nz, lmax = cfg.channels, len(cfg.atomic_numbers), cfg.max_ell
+    rmax, nb, pc = float(cfg.r_max), cfg.num_bessel, cfg.num_polynomial_cutoff
+    geom = (pos, cell, b32, csr.erecv, csr.esend, csr.eS)
+
+    h = (model.node_embedding / math.sqrt(nz))[species].unsqueeze(1).contiguous()
+    node_e = pos.new_zeros(n)
+    saved = []
+    for ip in model.interactions:
+        ws = [w / math.sqrt(w.shape[0]) for w in ip.radial]
+        P = len(ip.paths)
+        sc = _skip(ip, h, species, nz)
+        u = _per_l_linear(h, ip.linear_up, ip.l_in).contiguous()
+        mid = pos.new_empty(n, ip.n_mid, C)
+        for (i0, i1, e0, e1) in _chunks(csr, n, 4 * P * C):
+            ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, False)
+            R = _radial_weights(ws, ef, False).reshape(e1 - e0, P, C)
+            ops.mace_conv_fwd(u, pos, cell, b32, csr.eptr, csr.esend, csr.eS, R, i0, i1 - i0, e0, rmax, mid)
+            del ef, R
+        msg = _linear_mid(ip, mid, cfg.avg_num_neighbors, lmax)
+        del mid
+        w0, w1 = _sym_weights(ip, cfg.correlation)
+        B = ops.mace_symcon_fwd(msg, sp32, w0, w1, max(ip.l_out), cfg.correlation)
+        h_new = _per_l_linear(B, ip.product_linear, ip.l_out) + sc
+        s = h_new[:, 0]
+        if ip.last:
+            a = gemm.matmul(s, ip.readout_w1 / math.sqrt(C))
+            y, gy = _silu_and_grad(a)
+            w2 = ip.readout_w2 / math.sqrt(ip.readout_w2.shape[0])
+            node_e += y @ w2
+            ro = (gy * w2, None)
+        else:
+            node_e += s @ (ip.readout_w1 / math.sqrt(C))
+            ro = (None, None)
+        saved.append((ip, u, msg, ws, w0, w1, ro))
+        h = h_new
+        del B, sc
+    scale, shift = model.scale.to(pos.dtype), model.shift.to(pos.dtype)
+    node_e = model.atomic_energies.to(pos.dtype)[species] + node_e * scale + shift
+    energy = torch.zeros(num_graphs, dtype=torch.float64, device=dev).index_add_(0, batch, node_e.double()).to(pos.dtype)
+    out: dict[str, torch.Tensor | None] = {"energy": energy, "node_energy": node_e, "forces": None, "stress": None,
+                                            "hessian": None}
+    if not (compute_force or compute_stress):
+        return out
+
+    grad_pos = torch.zeros_like(pos)
+    strain_grad = torch.zeros(num_graphs, 9, dtype=torch.float64, device=dev) if compute_stress else None
+    dh: torch.Tensor | None = None
+    for li in range(len(saved) - 1, -1, -1):
+        ip, u, msg, ws, w0, w1, ro = saved[li]
+        n_out = sum(2 * l + 1 for l in ip.l_out)
+        dh_tot = pos.new_zeros(n, n_out, C) if dh is None else dh
+        if ip.last:
+            dh_tot[:, 0] += gemm.matmul(ro[0], (ip.readout_w1 / math.sqrt(C)).t()) * scale
+        else:
+            dh_tot[:, 0] += (ip.readout_w1 / math.sqrt(C)) * scale
+        dB = _per_l_linear(dh_tot, ip.product_linear, ip.l_out, transpose=True).contiguous()
+        dmsg = ops.mace_symcon_bwd(msg, sp32, w0, w1, max(ip.l_out), cfg.correlation, dB)
+        del dB
+        dmid = _linear_mid_bwd(ip, dmsg, cfg.avg_num_neighbors, lmax)
+        del dmsg
+        P = len(ip.paths)
+        du = torch.zeros_like(u) if li > 0 else None
+        for (i0, i1, e0, e1) in _chunks(csr, n, 8 * P * C):
+            ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, True)
+            RD = _radial_weights(ws, ef, True).reshape(e1 - e0, 2, P, C)
+            ops.mace_conv_bwd(u, dmid, pos, cell, b32, csr.eptr, csr.esend, csr.eS, RD, i0, i1 - i0, e0, rmax, du,
+                              grad_pos, strain_grad)
+            del ef, RD
+        del dmid
+        if li > 0:
+            dh = _per_l_linear(du, ip.linear_up, ip.l_in, transpose=True) + _skip(ip, dh_tot, species, nz, transpose=True)
+        saved[li] = None
+    out["forces"] = -grad_pos
+    if compute_stress:
+        vol = torch.linalg.det(cell).abs().double()
+        sg = strain_grad.reshape(num_graphs, 3, 3)
+        sg = 0.5 * (sg + sg.transpose(-1, -2))
+        out["stress"] = (sg / vol[:, None, None]).to(pos.dtype)
+        out["virial"] = (-sg).to(pos.dtype)
+    return out

@@ -1,0 +1,34 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Counting proxy over ``torch.ops.nvalchemi``: every call of one of this package's native operators is tallied
+(benchmarks report the tally as the number of native operator launches in the timed region)."""
+from __future__ import annotations
+
+import torch
+
+_count = 0
+
+
+class _Ops:
+    def __getattr__(self, name: str):
+        fn = getattr(torch.ops.nvalchemi, name)
+
+        def call(*a, **k):
+            global _count
+            _count += 1
+            return fn(*a, **k)
+
+        call.__name__ = name
+        object.__setattr__(self, name, call)
+        return call
+
+
+ops = _Ops()
+
+
+def reset() -> None:
+    global _count
+    _count = 0
+
+
+def count() -> int:
+    return _count

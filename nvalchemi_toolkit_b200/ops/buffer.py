@@ -15,6 +15,7 @@ from __future__ import annotations
 import torch
 
 from nvalchemi_toolkit_b200.ops import _native
+from nvalchemi_toolkit_b200.ops._native_counter import ops as _nops
 
 
 def expand_segments(starts: torch.Tensor, lens: torch.Tensor) -> torch.Tensor:
@@ -25,7 +26,7 @@ def expand_segments(starts: torch.Tensor, lens: torch.Tensor) -> torch.Tensor:
     if total == 0:
         return starts.new_zeros(0)
     if starts.is_cuda and _native.require(starts):
-        return torch.ops.nvalchemi.expand_segments(starts, lens, total)
+        return _nops.expand_segments(starts, lens, total)
     excl = torch.cumsum(lens, 0) - lens
     base = torch.repeat_interleave(starts - excl, lens, output_size=total)
     return base + torch.arange(total, device=starts.device)
@@ -38,7 +39,7 @@ def copy_rows(src: torch.Tensor, src_rows: torch.Tensor, dst: torch.Tensor, dst_
     if dst.dtype != src.dtype:
         src = src.to(dst.dtype)
     if dst.is_cuda and _native.require(dst) and src.is_contiguous() and dst.is_contiguous():
-        torch.ops.nvalchemi.copy_rows(src, src_rows.long(), dst, dst_rows.long())
+        _nops.copy_rows(src, src_rows.long(), dst, dst_rows.long())
         return
     dst[dst_rows] = src[src_rows]
 
@@ -49,7 +50,7 @@ def compact_rows(buf: torch.Tensor, keep: torch.Tensor, dst_rows: torch.Tensor, 
     if n:
         if buf.is_cuda and _native.require(buf) and buf.is_contiguous():
             tmp = torch.empty((n,) + tuple(buf.shape[1:]), dtype=buf.dtype, device=buf.device)
-            torch.ops.nvalchemi.copy_rows(buf, keep.long(), tmp, dst_rows.long())
+            _nops.copy_rows(buf, keep.long(), tmp, dst_rows.long())
             buf[:n].copy_(tmp)
         else:
             buf[:n] = buf[keep]
