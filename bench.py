@@ -236,8 +236,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cells", type=int, default=64, help="conventional fcc cells per edge (64 -> 1,048,576 atoms)")
-    ap.add_argument("--skin", type=float, default=0.5)
-    ap.add_argument("--max-neighbors", type=int, default=80)
+    ap.add_argument("--skin", type=float, default=0.0, help="Verlet skin; 0 rebuilds the list every step (cheaper than the extra edges at this size)")
+    ap.add_argument("--max-neighbors", type=int, default=64)
     args = ap.parse_args()
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:

@@ -177,26 +177,44 @@ __global__ void __launch_bounds__(192) gemm_tf32_kernel(const __grid_constant__ 
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     if (mbar_wait(accum_bar, 0, err, 3)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      int row = m0 + q * 32 + lane;
-      bool vec_ok = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+      // The ring is idle once the accumulator is complete: reuse it as a per-warp staging tile
+      // [32 rows][BN floats] so that global stores are full-row coalesced.  float4 slots are XOR-swizzled
+      // by (row & 7): conflict-free for the row-per-lane writes and for the row-wide reads.
+      constexpr int SPR = BN / 4;                      // float4 slots per row
+      float4* stage = reinterpret_cast<float4*>(smem_raw + (base - smem_u32(smem_raw))) + q * 32 * SPR;
 #pragma unroll 1
       for (int cb = 0; cb < BN / 32; ++cb) {
         float v[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), v);
-        int col0 = n0 + cb * 32;
-        if (row < M && col0 < N) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = v[j] * alpha;
-            if (act == 1) x = x / (1.f + __expf(-x)) * kSiluNorm;
-            v[j] = x;
-          }
-          float* dst = C + (int64_t)row * ldc + col0;
-          if (vec_ok && col0 + 32 <= N) {
+        for (int j = 0; j < 32; ++j) {
+          float x = v[j] * alpha;
+          if (act == 1) x = x / (1.f + __expf(-x)) * kSiluNorm;
+          v[j] = x;
+        }
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        for (int g = 0; g < 8; ++g)
+          stage[lane * SPR + ((cb * 8 + g) ^ (lane & 7))] = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+      }
+      __syncwarp();
+      const bool vec_ok = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+      constexpr int RPI = 32 / SPR;                    // rows written per warp instruction
+      const int slot = lane % SPR, rsub = lane / SPR;
+#pragma unroll 4
+      for (int r0 = 0; r0 < 32; r0 += RPI) {
+        int r = r0 + rsub;
+        int row = m0 + q * 32 + r;
+        int col = n0 + 4 * slot;
+        if (row < M && col < N) {
+          float4 val = stage[r * SPR + (slot ^ (r & 7))];
+          float* dst = C + (int64_t)row * ldc + col;
+          if (vec_ok && col + 4 <= N) {
+            *reinterpret_cast<float4*>(dst) = val;
           } else {
-            for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = v[j];
+            dst[0] = val.x;
+            if (col + 1 < N) dst[1] = val.y;
+            if (col + 2 < N) dst[2] = val.z;
+            if (col + 3 < N) dst[3] = val.w;
           }
         }
       }

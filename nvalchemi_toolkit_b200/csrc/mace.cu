@@ -124,9 +124,11 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(
     int i0, const float* __restrict__ u, const float* __restrict__ pos, const float* __restrict__ cell,
     const int* __restrict__ batch_idx, const int* __restrict__ eptr, const int* __restrict__ esend,
     const int* __restrict__ eS, const float* __restrict__ R, int64_t e_chunk0, float rmax, int C,
-    float* __restrict__ mid) {
+    float* __restrict__ mid, const int* __restrict__ home_rank, const int* __restrict__ home_row,
+    const int64_t* __restrict__ u_ptrs) {
   __shared__ float sY[kEdgeTile][16];
   __shared__ int sj[kEdgeTile];
+  __shared__ const float* sup[kEdgeTile];  // sender feature row (local, or a peer GPU's row over NVLink)
   int i = i0 + blockIdx.x;
   int c = threadIdx.x;
   float acc[NMID];
@@ -145,13 +147,17 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(
       float ri = ok ? 1.f / r : 0.f;
       sh_l3(v[0] * ri, v[1] * ri, v[2] * ri, sY[threadIdx.x]);
       sj[threadIdx.x] = ok ? j : -1;
+      const float* ub = u;
+      int64_t jr = j;
+      if (home_rank != nullptr) { ub = reinterpret_cast<const float*>(u_ptrs[home_rank[j]]); jr = home_row[j]; }
+      sup[threadIdx.x] = ub + jr * NIN * C;
     }
     __syncthreads();
     for (int t = 0; t < nt; ++t) {
       int j = sj[t];
       if (j < 0) continue;
       float h[NIN], Rv[NPATH];
-      const float* up = u + (int64_t)j * NIN * C + c;
+      const float* up = sup[t] + c;
 #pragma unroll
       for (int a = 0; a < NIN; ++a) h[a] = __ldg(up + a * C);
       const float* rp = R + ((int64_t)(base + t) - e_chunk0) * NPATH * C + c;
@@ -170,22 +176,31 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(
 // ---- convolution backward ------------------------------------------------------------------------
 // Given G = dE/dmid: du[sender] += ..., dE/dvec per edge -> grad_pos (receiver +, sender -), optional
 // per-system virial sum_e vec (x) dE/dvec.  RD holds [R | dR/dr] per edge: [E_chunk, 2, NPATH, C].
-template <int NIN, int NPATH, int NMID, bool L1, bool NEED_DU>
+template <int NIN, int NPATH, int NMID, int NT, bool L1, bool NEED_DU>
 __global__ void __launch_bounds__(256) conv_bwd_kernel(
     int i0, const float* __restrict__ u, const float* __restrict__ G, const float* __restrict__ pos,
     const float* __restrict__ cell, const int* __restrict__ batch_idx, const int* __restrict__ eptr,
     const int* __restrict__ esend, const int* __restrict__ eS, const float* __restrict__ RD, int64_t e_chunk0,
-    float rmax, int C, float* __restrict__ du, float* __restrict__ grad_pos, double* __restrict__ virial) {
+    float rmax, int C, float* __restrict__ du, float* __restrict__ grad_pos, double* __restrict__ virial,
+    const int* __restrict__ home_rank, const int* __restrict__ home_row, const int64_t* __restrict__ u_ptrs,
+    const int64_t* __restrict__ du_ptrs, const int64_t* __restrict__ gpos_ptrs) {
   __shared__ EdgeGeom sg[kEdgeTile];
+  __shared__ const float* sup[kEdgeTile];
+  __shared__ float* sdup[kEdgeTile];
+  __shared__ float* sgp[kEdgeTile];
   __shared__ float sv[kEdgeTile][3];
   __shared__ int sj[kEdgeTile];
   __shared__ float sred[kEdgeTile][8][3];
   int i = i0 + blockIdx.x;
   int c = threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-  float Gr[NMID];
-  const float* gp = G + (int64_t)i * NMID * C + c;
+  float T[NT];  // G contracted with the coupling coefficients: constant over the receiver's edges
+  {
+    float Gr[NMID];
+    const float* gp = G + (int64_t)i * NMID * C + c;
 #pragma unroll
-  for (int o = 0; o < NMID; ++o) Gr[o] = gp[o * C];
+    for (int o = 0; o < NMID; ++o) Gr[o] = gp[o * C];
+    if (L1) { MACE_L1_BWD_PREP(Gr, T); } else { MACE_L0_BWD_PREP(Gr, T); }
+  }
   int eb = eptr[i], ee = eptr[i + 1];
   float fi[3] = {0.f, 0.f, 0.f};
   float vir[9] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -204,6 +219,20 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(
       sh_l3(g.n[0], g.n[1], g.n[2], g.Y);
       sv[threadIdx.x][0] = v[0]; sv[threadIdx.x][1] = v[1]; sv[threadIdx.x][2] = v[2];
       sj[threadIdx.x] = ok ? j : -1;
+      const float* ub = u;
+      float* dub = du;
+      float* gpb = grad_pos;
+      int64_t jr = j;
+      if (home_rank != nullptr) {
+        int hr = home_rank[j];
+        jr = home_row[j];
+        ub = reinterpret_cast<const float*>(u_ptrs[hr]);
+        if (NEED_DU) dub = reinterpret_cast<float*>(du_ptrs[hr]);
+        gpb = reinterpret_cast<float*>(gpos_ptrs[hr]);
+      }
+      sup[threadIdx.x] = ub + jr * NIN * C;
+      sdup[threadIdx.x] = NEED_DU ? dub + jr * NIN * C : nullptr;
+      sgp[threadIdx.x] = gpb + 3 * jr;
     }
     __syncthreads();
     for (int t = 0; t < nt; ++t) {
@@ -211,7 +240,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(
       float f[3] = {0.f, 0.f, 0.f};
       if (j >= 0) {
         float h[NIN], Rv[NPATH], dh[NIN], dY[16], S[NPATH];
-        const float* up = u + (int64_t)j * NIN * C + c;
+        const float* up = sup[t] + c;
 #pragma unroll
         for (int a = 0; a < NIN; ++a) { h[a] = __ldg(up + a * C); dh[a] = 0.f; }
         const float* rp = RD + ((int64_t)(base + t) - e_chunk0) * 2 * NPATH * C + c;
@@ -221,7 +250,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(
         for (int b = 0; b < 16; ++b) dY[b] = 0.f;
         const EdgeGeom& g = sg[t];
         const float* Y = g.Y;
-        if (L1) { MACE_L1_BWD(h, Y, Rv, Gr, dh, dY, S); } else { MACE_L0_BWD(h, Y, Rv, Gr, dh, dY, S); }
+        if (L1) { MACE_L1_BWD_EDGE(h, Y, Rv, T, dh, dY, S); } else { MACE_L0_BWD_EDGE(h, Y, Rv, T, dh, dY, S); }
         float q = 0.f;
 #pragma unroll
         for (int p = 0; p < NPATH; ++p) q = fmaf(S[p], __ldg(rp + (NPATH + p) * C), q);
@@ -230,7 +259,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(
 #pragma unroll
         for (int d = 0; d < 3; ++d) f[d] = (gy[d] - s * g.n[d]) * g.rinv + q * g.n[d];
         if (NEED_DU) {
-          float* dp = du + (int64_t)j * NIN * C + c;
+          float* dp = sdup[t] + c;
 #pragma unroll
           for (int a = 0; a < NIN; ++a) atomicAdd(dp + a * C, dh[a]);
         }
@@ -250,7 +279,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(
         for (int w = 0; w < nwarp; ++w)
           for (int d = 0; d < 3; ++d) f[d] += sred[threadIdx.x][w][d];
         for (int d = 0; d < 3; ++d) {
-          atomicAdd(grad_pos + 3 * (int64_t)j + d, -f[d]);
+          atomicAdd(sgp[threadIdx.x] + d, -f[d]);
           fi[d] += f[d];
         }
         if (virial != nullptr)
@@ -278,126 +307,96 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(
 }
 
 // ---- symmetric contraction -----------------------------------------------------------------------
-// out[n, M, c] = sum_nu sum_eta W_nu[z_n, eta, c] * sum_terms coef * prod x[n, idx, c]
-struct SymTable {
-  const unsigned int* idx; const float* coef; const unsigned short* grp; int nterms; int nbasis;
-};
-
-template <int NU>
-__device__ __forceinline__ void sym_accumulate(const SymTable t, int dL, const float* x /*smem [16][blockDim]*/,
-                                               int stride, const float* __restrict__ w, int C, float* out) {
-  // terms are sorted by group = eta*dL + M
-  int k = 0;
-  while (k < t.nterms) {
-    int g = t.grp[k];
-    float acc = 0.f;
-    while (k < t.nterms && t.grp[k] == g) {
-      unsigned int id = t.idx[k];
-      float m = x[(id & 255u) * stride];
-      if (NU >= 2) m *= x[((id >> 8) & 255u) * stride];
-      if (NU >= 3) m *= x[((id >> 16) & 255u) * stride];
-      acc = fmaf(t.coef[k], m, acc);
-      ++k;
-    }
-    int eta = g / dL, M = g - eta * dL;
-    out[M] = fmaf(__ldg(w + eta * C), acc, out[M]);
-  }
-}
-
-template <int NU>
-__device__ __forceinline__ void sym_backward(const SymTable t, int dL, const float* x, float* dx, int stride,
-                                             const float* __restrict__ w, int C, const float* gout) {
-  for (int k = 0; k < t.nterms; ++k) {
-    int g = t.grp[k];
-    int eta = g / dL, M = g - eta * dL;
-    float s = t.coef[k] * __ldg(w + eta * C) * gout[M];
-    unsigned int id = t.idx[k];
-    int a = id & 255u, b = (id >> 8) & 255u, cc = (id >> 16) & 255u;
-    if (NU == 1) {
-      dx[a * stride] += s;
-    } else if (NU == 2) {
-      float xa = x[a * stride], xb = x[b * stride];
-      dx[a * stride] += s * xb;
-      dx[b * stride] += s * xa;
-    } else {
-      float xa = x[a * stride], xb = x[b * stride], xc = x[cc * stride];
-      dx[a * stride] += s * xb * xc;
-      dx[b * stride] += s * xa * xc;
-      dx[cc * stride] += s * xa * xb;
-    }
-  }
-}
-
-__device__ __forceinline__ SymTable sym_table(int nu, int L) {
-  SymTable t;
-  if (L == 0) {
-    if (nu == 1) t = {mace_sym_1_0_idx, mace_sym_1_0_coef, mace_sym_1_0_grp, MACE_SYM_1_0_NTERMS, MACE_SYM_1_0_NBASIS};
-    else if (nu == 2) t = {mace_sym_2_0_idx, mace_sym_2_0_coef, mace_sym_2_0_grp, MACE_SYM_2_0_NTERMS, MACE_SYM_2_0_NBASIS};
-    else t = {mace_sym_3_0_idx, mace_sym_3_0_coef, mace_sym_3_0_grp, MACE_SYM_3_0_NTERMS, MACE_SYM_3_0_NBASIS};
-  } else {
-    if (nu == 1) t = {mace_sym_1_1_idx, mace_sym_1_1_coef, mace_sym_1_1_grp, MACE_SYM_1_1_NTERMS, MACE_SYM_1_1_NBASIS};
-    else if (nu == 2) t = {mace_sym_2_1_idx, mace_sym_2_1_coef, mace_sym_2_1_grp, MACE_SYM_2_1_NTERMS, MACE_SYM_2_1_NBASIS};
-    else t = {mace_sym_3_1_idx, mace_sym_3_1_coef, mace_sym_3_1_grp, MACE_SYM_3_1_NTERMS, MACE_SYM_3_1_NBASIS};
-  }
-  return t;
-}
-
-// weights are packed per L as [Z, nb1 + nb2 + nb3, C] (degree blocks in that order, degrees above
-// `correlation` are simply absent from the loop).
+// out[n, M, c] = sum_nu sum_eta W_nu[z_n, eta, c] * P_{nu,eta,M}(x[n, :, c]); the polynomials P are emitted as
+// straight-line code (mace_tables.h), x and its gradient stay in registers.  Weights are packed per L as
+// [Z, nb1 + nb2 + nb3, C] (degree blocks in that order).
+#define W(k) __ldg(wp + (k) * C)
 template <bool BWD>
-__global__ void symcon_kernel(int64_t n_nodes, int C, int lmax_out, int correlation, const float* __restrict__ x,
-                              const int* __restrict__ species, const float* __restrict__ w0,
-                              const float* __restrict__ w1, int nbtot0, int nbtot1, float* __restrict__ out,
-                              const float* __restrict__ gout, float* __restrict__ dx) {
-  extern __shared__ float smem[];  // [16][blockDim] x, and for BWD another [16][blockDim] dx
-  int tid = threadIdx.x;
-  int64_t gidx = blockIdx.x * (int64_t)blockDim.x + tid;
+__global__ void __launch_bounds__(128) symcon_kernel(int64_t n_nodes, int C, int lmax_out, int correlation,
+                                                     const float* __restrict__ xg, const int* __restrict__ species,
+                                                     const float* __restrict__ w0, const float* __restrict__ w1,
+                                                     int nbtot0, int nbtot1, float* __restrict__ outg,
+                                                     const float* __restrict__ gout, float* __restrict__ dxg) {
+  int64_t gidx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int64_t n = gidx / C;
   int c = (int)(gidx - n * C);
   if (n >= n_nodes) return;
-  int stride = blockDim.x;
-  float* xs = smem + tid;
-  float* dxs = smem + 16 * stride + tid;
-  const float* xp = x + n * 16 * C + c;
+  float x[16], dx[16];
+  const float* xp = xg + n * 16 * C + c;
 #pragma unroll
-  for (int k = 0; k < 16; ++k) {
-    xs[k * stride] = xp[k * C];
-    if (BWD) dxs[k * stride] = 0.f;
-  }
+  for (int k = 0; k < 16; ++k) { x[k] = xp[k * C]; dx[k] = 0.f; }
   int z = species[n];
   int nout = (lmax_out + 1) * (lmax_out + 1);
-  int ooff = 0;
-  for (int L = 0; L <= lmax_out; ++L) {
-    int dL = 2 * L + 1;
-    const float* w = (L == 0 ? w0 + (int64_t)z * nbtot0 * C : w1 + (int64_t)z * nbtot1 * C) + c;
-    float o[3] = {0.f, 0.f, 0.f};
-    float go[3] = {0.f, 0.f, 0.f};
-    if (BWD)
-      for (int M = 0; M < dL; ++M) go[M] = gout[(n * nout + ooff + M) * C + c];
-    int boff = 0;
-    for (int nu = 1; nu <= correlation; ++nu) {
-      SymTable t = sym_table(nu, L);
-      const float* wn = w + (int64_t)boff * C;
-      if (!BWD) {
-        if (nu == 1) sym_accumulate<1>(t, dL, xs, stride, wn, C, o);
-        else if (nu == 2) sym_accumulate<2>(t, dL, xs, stride, wn, C, o);
-        else sym_accumulate<3>(t, dL, xs, stride, wn, C, o);
-      } else {
-        if (nu == 1) sym_backward<1>(t, dL, xs, dxs, stride, wn, C, go);
-        else if (nu == 2) sym_backward<2>(t, dL, xs, dxs, stride, wn, C, go);
-        else sym_backward<3>(t, dL, xs, dxs, stride, wn, C, go);
-      }
-      boff += t.nbasis;
+  {
+    const float* wp = w0 + (int64_t)z * nbtot0 * C + c;
+    float out[1] = {0.f};
+    float g[1] = {0.f};
+    if (BWD) g[0] = gout[(n * nout) * C + c];
+    if (!BWD) { MACE_SYM_FWD_1_0(x, out); } else { MACE_SYM_BWD_1_0(x, g, dx); }
+    wp += MACE_SYM_1_0_NBASIS * C;
+    if (correlation >= 2) {
+      if (!BWD) { MACE_SYM_FWD_2_0(x, out); } else { MACE_SYM_BWD_2_0(x, g, dx); }
+      wp += MACE_SYM_2_0_NBASIS * C;
     }
-    if (!BWD)
-      for (int M = 0; M < dL; ++M) out[(n * nout + ooff + M) * C + c] = o[M];
-    ooff += dL;
+    if (correlation >= 3) {
+      if (!BWD) { MACE_SYM_FWD_3_0(x, out); } else { MACE_SYM_BWD_3_0(x, g, dx); }
+    }
+    if (!BWD) outg[(n * nout) * C + c] = out[0];
+  }
+  if (lmax_out >= 1) {
+    const float* wp = w1 + (int64_t)z * nbtot1 * C + c;
+    float out[3] = {0.f, 0.f, 0.f};
+    float g[3] = {0.f, 0.f, 0.f};
+    if (BWD) {
+#pragma unroll
+      for (int M = 0; M < 3; ++M) g[M] = gout[(n * nout + 1 + M) * C + c];
+    }
+    if (!BWD) { MACE_SYM_FWD_1_1(x, out); } else { MACE_SYM_BWD_1_1(x, g, dx); }
+    wp += MACE_SYM_1_1_NBASIS * C;
+    if (correlation >= 2) {
+      if (!BWD) { MACE_SYM_FWD_2_1(x, out); } else { MACE_SYM_BWD_2_1(x, g, dx); }
+      wp += MACE_SYM_2_1_NBASIS * C;
+    }
+    if (correlation >= 3) {
+      if (!BWD) { MACE_SYM_FWD_3_1(x, out); } else { MACE_SYM_BWD_3_1(x, g, dx); }
+    }
+    if (!BWD) {
+#pragma unroll
+      for (int M = 0; M < 3; ++M) outg[(n * nout + 1 + M) * C + c] = out[M];
+    }
   }
   if (BWD) {
-    float* dp = dx + n * 16 * C + c;
+    float* dp = dxg + n * 16 * C + c;
 #pragma unroll
-    for (int k = 0; k < 16; ++k) dp[k * C] = dxs[k * stride];
+    for (int k = 0; k < 16; ++k) dp[k * C] = dx[k];
   }
+}
+#undef W
+
+// ---- radial MLP activation with forward-mode tangent ---------------------------------------------
+// a [E, 2, H] in place: row 0 <- silu(a0) * norm, row 1 <- silu'(a0) * norm * a1.
+__global__ void silu_tangent_kernel(int64_t total, int H, float* __restrict__ a) {
+  int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  int64_t e = t / H;
+  int k = (int)(t - e * H);
+  float* p = a + e * 2 * H + k;
+  float x = p[0], tx = p[H];
+  float s = 1.f / (1.f + __expf(-x));
+  const float norm = 1.6790176868438721f;
+  p[0] = x * s * norm;
+  p[H] = s * (1.f + x * (1.f - s)) * norm * tx;
+}
+
+void mace_silu_tangent_(Tensor a) {
+  c10::cuda::CUDAGuard guard(a.device());
+  NVA_CHECK_CONTIG(a);
+  TORCH_CHECK(a.dim() == 3 && a.size(1) == 2, "expected [E, 2, H]");
+  int64_t total = a.size(0) * a.size(2);
+  if (total == 0) return;
+  silu_tangent_kernel<<<(unsigned)((total + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      total, (int)a.size(2), a.data_ptr<float>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 // ---- host wrappers -------------------------------------------------------------------------------
@@ -416,7 +415,8 @@ Tensor mace_edge_radial(const Tensor& pos, const Tensor& cell, const Tensor& bat
 
 void mace_conv_fwd(const Tensor& u, const Tensor& pos, const Tensor& cell, const Tensor& batch_idx,
                    const Tensor& eptr, const Tensor& esend, const Tensor& eS, const Tensor& R, int64_t i0,
-                   int64_t ni, int64_t e_chunk0, double rmax, Tensor mid) {
+                   int64_t ni, int64_t e_chunk0, double rmax, Tensor mid, const c10::optional<Tensor>& home_rank,
+                   const c10::optional<Tensor>& home_row, const c10::optional<Tensor>& u_ptrs) {
   c10::cuda::CUDAGuard guard(pos.device());
   NVA_CHECK_CONTIG(u); NVA_CHECK_CONTIG(R); NVA_CHECK_CONTIG(mid);
   int C = (int)u.size(2), nin = (int)u.size(1);
@@ -425,7 +425,8 @@ void mace_conv_fwd(const Tensor& u, const Tensor& pos, const Tensor& cell, const
   auto st = at::cuda::getCurrentCUDAStream();
 #define NVA_ARGS (int)i0, u.data_ptr<float>(), pos.data_ptr<float>(), cell.data_ptr<float>(), batch_idx.data_ptr<int>(), \
     eptr.data_ptr<int>(), esend.data_ptr<int>(), eS.data_ptr<int>(), R.data_ptr<float>(), e_chunk0, (float)rmax, C, \
-    mid.data_ptr<float>()
+    mid.data_ptr<float>(), home_rank.has_value() ? home_rank->data_ptr<int>() : nullptr, \
+    home_row.has_value() ? home_row->data_ptr<int>() : nullptr, u_ptrs.has_value() ? u_ptrs->data_ptr<int64_t>() : nullptr
   if (nin == 1) {
     TORCH_CHECK(mid.size(1) == MACE_L0_NMID && R.size(1) == MACE_L0_NPATH, "layer-0 shapes");
     conv_fwd_kernel<MACE_L0_NIN, MACE_L0_NPATH, MACE_L0_NMID, false><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
@@ -440,7 +441,10 @@ void mace_conv_fwd(const Tensor& u, const Tensor& pos, const Tensor& cell, const
 void mace_conv_bwd(const Tensor& u, const Tensor& G, const Tensor& pos, const Tensor& cell,
                    const Tensor& batch_idx, const Tensor& eptr, const Tensor& esend, const Tensor& eS,
                    const Tensor& RD, int64_t i0, int64_t ni, int64_t e_chunk0, double rmax,
-                   const c10::optional<Tensor>& du, Tensor grad_pos, const c10::optional<Tensor>& virial) {
+                   const c10::optional<Tensor>& du, Tensor grad_pos, const c10::optional<Tensor>& virial,
+                   const c10::optional<Tensor>& home_rank, const c10::optional<Tensor>& home_row,
+                   const c10::optional<Tensor>& u_ptrs, const c10::optional<Tensor>& du_ptrs,
+                   const c10::optional<Tensor>& gpos_ptrs) {
   c10::cuda::CUDAGuard guard(pos.device());
   NVA_CHECK_CONTIG(u); NVA_CHECK_CONTIG(RD); NVA_CHECK_CONTIG(G);
   int C = (int)u.size(2), nin = (int)u.size(1);
@@ -451,13 +455,16 @@ void mace_conv_bwd(const Tensor& u, const Tensor& G, const Tensor& pos, const Te
   double* vp = virial.has_value() ? virial->data_ptr<double>() : nullptr;
 #define NVA_ARGS (int)i0, u.data_ptr<float>(), G.data_ptr<float>(), pos.data_ptr<float>(), cell.data_ptr<float>(), \
     batch_idx.data_ptr<int>(), eptr.data_ptr<int>(), esend.data_ptr<int>(), eS.data_ptr<int>(), RD.data_ptr<float>(), \
-    e_chunk0, (float)rmax, C, dup, grad_pos.data_ptr<float>(), vp
+    e_chunk0, (float)rmax, C, dup, grad_pos.data_ptr<float>(), vp, \
+    home_rank.has_value() ? home_rank->data_ptr<int>() : nullptr, home_row.has_value() ? home_row->data_ptr<int>() : nullptr, \
+    u_ptrs.has_value() ? u_ptrs->data_ptr<int64_t>() : nullptr, du_ptrs.has_value() ? du_ptrs->data_ptr<int64_t>() : nullptr, \
+    gpos_ptrs.has_value() ? gpos_ptrs->data_ptr<int64_t>() : nullptr
   if (nin == 1) {
-    if (dup) conv_bwd_kernel<MACE_L0_NIN, MACE_L0_NPATH, MACE_L0_NMID, false, true><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
-    else conv_bwd_kernel<MACE_L0_NIN, MACE_L0_NPATH, MACE_L0_NMID, false, false><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
+    if (dup) conv_bwd_kernel<MACE_L0_NIN, MACE_L0_NPATH, MACE_L0_NMID, MACE_L0_NT, false, true><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
+    else conv_bwd_kernel<MACE_L0_NIN, MACE_L0_NPATH, MACE_L0_NMID, MACE_L0_NT, false, false><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
   } else {
-    if (dup) conv_bwd_kernel<MACE_L1_NIN, MACE_L1_NPATH, MACE_L1_NMID, true, true><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
-    else conv_bwd_kernel<MACE_L1_NIN, MACE_L1_NPATH, MACE_L1_NMID, true, false><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
+    if (dup) conv_bwd_kernel<MACE_L1_NIN, MACE_L1_NPATH, MACE_L1_NMID, MACE_L1_NT, true, true><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
+    else conv_bwd_kernel<MACE_L1_NIN, MACE_L1_NPATH, MACE_L1_NMID, MACE_L1_NT, true, false><<<(unsigned)ni, C, 0, st>>>(NVA_ARGS);
   }
 #undef NVA_ARGS
   C10_CUDA_KERNEL_LAUNCH_CHECK();
@@ -474,8 +481,7 @@ Tensor mace_symcon_fwd(const Tensor& x, const Tensor& species, const Tensor& w0,
   if (n == 0) return out;
   int threads = 128;
   int64_t total = n * C;
-  size_t smem = 16 * threads * sizeof(float);
-  symcon_kernel<false><<<(unsigned)((total + threads - 1) / threads), threads, smem, at::cuda::getCurrentCUDAStream()>>>(
+  symcon_kernel<false><<<(unsigned)((total + threads - 1) / threads), threads, 0, at::cuda::getCurrentCUDAStream()>>>(
       n, C, (int)lmax_out, (int)correlation, x.data_ptr<float>(), species.data_ptr<int>(), w0.data_ptr<float>(),
       w1.has_value() ? w1->data_ptr<float>() : nullptr, (int)w0.size(1), w1.has_value() ? (int)w1->size(1) : 0,
       out.data_ptr<float>(), nullptr, nullptr);
@@ -493,8 +499,7 @@ Tensor mace_symcon_bwd(const Tensor& x, const Tensor& species, const Tensor& w0,
   if (n == 0) return dx;
   int threads = 128;
   int64_t total = n * C;
-  size_t smem = 32 * threads * sizeof(float);
-  symcon_kernel<true><<<(unsigned)((total + threads - 1) / threads), threads, smem, at::cuda::getCurrentCUDAStream()>>>(
+  symcon_kernel<true><<<(unsigned)((total + threads - 1) / threads), threads, 0, at::cuda::getCurrentCUDAStream()>>>(
       n, C, (int)lmax_out, (int)correlation, x.data_ptr<float>(), species.data_ptr<int>(), w0.data_ptr<float>(),
       w1.has_value() ? w1->data_ptr<float>() : nullptr, (int)w0.size(1), w1.has_value() ? (int)w1->size(1) : 0,
       nullptr, gout.data_ptr<float>(), dx.data_ptr<float>());
@@ -506,8 +511,9 @@ Tensor mace_symcon_bwd(const Tensor& x, const Tensor& species, const Tensor& w0,
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("mace_edge_radial(Tensor pos, Tensor cell, Tensor batch_idx, Tensor erecv, Tensor esend, Tensor eS, int e0, int ne, float rmax, int nb, int p, bool with_grad) -> Tensor", &nva::mace_edge_radial);
-  m.def("mace_conv_fwd(Tensor u, Tensor pos, Tensor cell, Tensor batch_idx, Tensor eptr, Tensor esend, Tensor eS, Tensor R, int i0, int ni, int e_chunk0, float rmax, Tensor(a!) mid) -> ()", &nva::mace_conv_fwd);
-  m.def("mace_conv_bwd(Tensor u, Tensor G, Tensor pos, Tensor cell, Tensor batch_idx, Tensor eptr, Tensor esend, Tensor eS, Tensor RD, int i0, int ni, int e_chunk0, float rmax, Tensor(a!)? du, Tensor(b!) grad_pos, Tensor(c!)? virial) -> ()", &nva::mace_conv_bwd);
+  m.def("mace_conv_fwd(Tensor u, Tensor pos, Tensor cell, Tensor batch_idx, Tensor eptr, Tensor esend, Tensor eS, Tensor R, int i0, int ni, int e_chunk0, float rmax, Tensor(a!) mid, Tensor? home_rank=None, Tensor? home_row=None, Tensor? u_ptrs=None) -> ()", &nva::mace_conv_fwd);
+  m.def("mace_conv_bwd(Tensor u, Tensor G, Tensor pos, Tensor cell, Tensor batch_idx, Tensor eptr, Tensor esend, Tensor eS, Tensor RD, int i0, int ni, int e_chunk0, float rmax, Tensor(a!)? du, Tensor(b!) grad_pos, Tensor(c!)? virial, Tensor? home_rank=None, Tensor? home_row=None, Tensor? u_ptrs=None, Tensor? du_ptrs=None, Tensor? gpos_ptrs=None) -> ()", &nva::mace_conv_bwd);
+  m.def("mace_silu_tangent_(Tensor(a!) a) -> ()", &nva::mace_silu_tangent_);
   m.def("mace_symcon_fwd(Tensor x, Tensor species, Tensor w0, Tensor? w1, int lmax_out, int correlation) -> Tensor", &nva::mace_symcon_fwd);
   m.def("mace_symcon_bwd(Tensor x, Tensor species, Tensor w0, Tensor? w1, int lmax_out, int correlation, Tensor gout) -> Tensor", &nva::mace_symcon_bwd);
 }

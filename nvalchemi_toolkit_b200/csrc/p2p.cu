@@ -1,0 +1,149 @@
+// SPDX-License-Identifier: Apache-2.0
+// Peer-to-peer communication kernels over NVLink (symmetric buffers mapped into every rank):
+//   * p2p_barrier      - flag exchange between ranks with a bounded wait (status word on expiry);
+//   * halo_push_rows   - packs boundary rows (+ periodic image shift) and stores them straight into the
+//                        peers' ghost rows (replaces the count all_gather + all_to_all_v of the reference's
+//                        halo build, nvalchemi/distributed/_core/particle_halo.py:279-368);
+//   * p2p_allreduce    - one-shot sum over all ranks' symmetric buffers with a fused scale (gradient
+//                        all-reduce with the loss-scale division and cast folded in; reference: PyTorch DDP
+//                        bucketed NCCL all-reduce, nvalchemi/training/hooks/ddp.py:277-301).
+// Peer memory is only ever touched with plain ld/st/red instructions issued by these kernels.
+#include "common.cuh"
+
+namespace nva {
+using at::Tensor;
+
+// One block, `world` threads.  Thread t publishes `epoch` into rank t's flag row (slot = my rank) and then
+// waits until rank t's publication shows up in my own row.  All earlier device-side writes of this rank to
+// peer memory are ordered before the flag by the system-scope fence.
+__global__ void p2p_barrier_kernel(const int64_t* __restrict__ flag_ptrs, int rank, int world, int epoch,
+                                   int* __restrict__ err) {
+  int t = threadIdx.x;
+  __threadfence_system();
+  __syncthreads();
+  if (t < world) {
+    volatile int* peer = reinterpret_cast<volatile int*>(flag_ptrs[t]);
+    peer[rank] = epoch;
+    __threadfence_system();
+    volatile int* mine = reinterpret_cast<volatile int*>(flag_ptrs[rank]);
+    bool ok = false;
+    for (int it = 0; it < 4000000; ++it) {  // ~1 s at 250 ns per probe
+      if (mine[t] >= epoch) { ok = true; break; }
+      __nanosleep(250);
+    }
+    if (!ok) atomicExch(err, 100 + t);
+  }
+  __threadfence_system();
+}
+
+void p2p_barrier(const Tensor& flag_ptrs, int64_t rank, int64_t world, int64_t epoch, Tensor err) {
+  c10::cuda::CUDAGuard guard(flag_ptrs.device());
+  TORCH_CHECK(world <= 32, "p2p_barrier supports up to 32 ranks");
+  p2p_barrier_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(flag_ptrs.data_ptr<int64_t>(), (int)rank, (int)world,
+                                                                     (int)epoch, err.data_ptr<int>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// dst_r[dst_row[k], :] = src[idx[k], :] (+ shift[k, :]) with dst_r = base pointer of rank peer[k].
+__global__ void halo_push_kernel(int64_t n_send, int D, const float* __restrict__ src, const int* __restrict__ idx,
+                                 const int* __restrict__ dst_row, const int* __restrict__ peer,
+                                 const float* __restrict__ shift, const int64_t* __restrict__ dst_ptrs) {
+  int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (t >= n_send * D) return;
+  int64_t k = t / D;
+  int d = (int)(t - k * D);
+  float v = src[(int64_t)idx[k] * D + d];
+  if (shift != nullptr) v += shift[k * D + d];
+  float* dst = reinterpret_cast<float*>(dst_ptrs[peer[k]]);
+  dst[(int64_t)dst_row[k] * D + d] = v;
+}
+
+void halo_push_rows(const Tensor& src, const Tensor& idx, const Tensor& dst_row, const Tensor& peer,
+                    const c10::optional<Tensor>& shift, const Tensor& dst_ptrs) {
+  c10::cuda::CUDAGuard guard(src.device());
+  NVA_CHECK_CONTIG(src);
+  int64_t n = idx.size(0);
+  if (n == 0) return;
+  int D = (int)(src.numel() / src.size(0));
+  int64_t total = n * D;
+  halo_push_kernel<<<(unsigned)((total + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      n, D, src.data_ptr<float>(), idx.data_ptr<int>(), dst_row.data_ptr<int>(), peer.data_ptr<int>(),
+      shift.has_value() ? shift->data_ptr<float>() : nullptr, dst_ptrs.data_ptr<int64_t>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// out[i] = scale * sum_r buf_r[i]; every rank reads all peers (one-shot all-reduce; sized for the
+// latency-bound few-MB gradient buckets of MLIP training).  float4 path when aligned.
+__global__ void p2p_allreduce_kernel(int64_t n, const int64_t* __restrict__ buf_ptrs, int world, float scale,
+                                     float* __restrict__ out) {
+  int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  if (i + 4 <= n) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(buf_ptrs[r]) + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    *reinterpret_cast<float4*>(out + i) = acc;
+  } else {
+    for (int64_t k = i; k < n; ++k) {
+      float acc = 0.f;
+      for (int r = 0; r < world; ++r) acc += reinterpret_cast<const float*>(buf_ptrs[r])[k];
+      out[k] = acc * scale;
+    }
+  }
+}
+
+void p2p_allreduce(const Tensor& buf_ptrs, int64_t world, double scale, Tensor out) {
+  c10::cuda::CUDAGuard guard(out.device());
+  int64_t n = out.numel();
+  if (n == 0) return;
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0, "p2p_allreduce: output must be 16-byte aligned");
+  int64_t threads = (n + 3) / 4;
+  p2p_allreduce_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      n, buf_ptrs.data_ptr<int64_t>(), (int)world, (float)scale, out.data_ptr<float>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+}  // namespace nva
+
+TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
+  m.def("p2p_barrier(Tensor flag_ptrs, int rank, int world, int epoch, Tensor(a!) err) -> ()", &nva::p2p_barrier);
+  m.def("halo_push_rows(Tensor src, Tensor idx, Tensor dst_row, Tensor peer, Tensor? shift, Tensor dst_ptrs) -> ()", &nva::halo_push_rows);
+  m.def("p2p_allreduce(Tensor buf_ptrs, int world, float scale, Tensor(a!) out) -> ()", &nva::p2p_allreduce);
+}
+
+namespace nva {
+// Ghost refresh by pull: dst[row0 + g, :] = src_{home_rank[g]}[home_row[g], :] (+ shift[g, :]).  The consumer reads
+// the owners' rows over NVLink; no send lists or counts have to be negotiated.
+__global__ void halo_pull_kernel(int64_t n_ghost, int D, float* __restrict__ dst, int64_t row0,
+                                 const int* __restrict__ home_rank, const int* __restrict__ home_row,
+                                 const float* __restrict__ shift, const int64_t* __restrict__ src_ptrs) {
+  int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (t >= n_ghost * D) return;
+  int64_t g = t / D;
+  int d = (int)(t - g * D);
+  const float* src = reinterpret_cast<const float*>(src_ptrs[home_rank[g]]);
+  float v = src[(int64_t)home_row[g] * D + d];
+  if (shift != nullptr) v += shift[g * D + d];
+  dst[(row0 + g) * D + d] = v;
+}
+
+void halo_pull_rows(at::Tensor dst, int64_t row0, const at::Tensor& home_rank, const at::Tensor& home_row,
+                    const c10::optional<at::Tensor>& shift, const at::Tensor& src_ptrs) {
+  c10::cuda::CUDAGuard guard(dst.device());
+  int64_t n = home_rank.size(0);
+  if (n == 0) return;
+  int D = (int)(dst.numel() / dst.size(0));
+  int64_t total = n * D;
+  halo_pull_kernel<<<(unsigned)((total + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      n, D, dst.data_ptr<float>(), row0, home_rank.data_ptr<int>(), home_row.data_ptr<int>(),
+      shift.has_value() ? shift->data_ptr<float>() : nullptr, src_ptrs.data_ptr<int64_t>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+}  // namespace nva
+
+TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
+  m.def("halo_pull_rows(Tensor(a!) dst, int row0, Tensor home_rank, Tensor home_row, Tensor? shift, Tensor src_ptrs) -> ()", &nva::halo_pull_rows);
+}

@@ -36,6 +36,7 @@ class EdgeCSR:
     eS: torch.Tensor     # [E,3] int32 (integer images of the sender)
     eptr_host: list[int] | None = None
     num_edges: int = 0
+    max_count: int = 0   # largest neighbour count seen (a value above the matrix width signals overflow)
 
 
 def build_csr(nm: torch.Tensor, num: torch.Tensor, shifts: torch.Tensor | None) -> EdgeCSR:
@@ -49,7 +50,8 @@ def build_csr(nm: torch.Tensor, num: torch.Tensor, shifts: torch.Tensor | None) 
     erecv = torch.repeat_interleave(torch.arange(n, device=nm.device, dtype=torch.int32), cnt.long(), output_size=e)
     eS = shifts[valid].to(torch.int32).contiguous() if shifts is not None else \
         torch.zeros(e, 3, dtype=torch.int32, device=nm.device)
-    return EdgeCSR(eptr, esend, erecv, eS, None, e)
+    mx = int(num.max()) if n else 0  # one host read per neighbour-list build (also sizes the edge arrays)
+    return EdgeCSR(eptr, esend, erecv, eS, None, e, mx)
 
 
 def csr_from_edge_index(edge_index: torch.Tensor, unit_shifts: torch.Tensor | None, n: int) -> EdgeCSR:
@@ -91,34 +93,36 @@ def _silu_and_grad(a: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
 
 
 def _radial_weights(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool) -> torch.Tensor:
-    """``ef [E, 1|2, nb]`` → ``[E, 1|2, P*C]``: MLP value and (forward-mode) derivative w.r.t. the distance."""
+    """``ef [E, 1|2, nb]`` → ``[E, 1|2, P*C]``: MLP value and (forward-mode) derivative w.r.t. the distance.
+
+    Value and tangent rows are interleaved ``[E, 2, H]`` so that each layer is one GEMM over ``2E`` rows followed by
+    one fused activation kernel; without the tangent the activation runs in the GEMM epilogue."""
+    e = ef.shape[0]
     if not with_grad:
         x = ef[:, 0]
         for k, w in enumerate(ws):
-            x = gemm.matmul(x, w)
-            if k < len(ws) - 1:
-                x = torch.nn.functional.silu(x).mul_(SILU_NORM)
+            x = gemm.matmul(x, w, act=1 if k < len(ws) - 1 else 0)
         return x.unsqueeze(1)
-    x, t = ef[:, 0], ef[:, 1]
-    for k, w in enumerate(ws[:-1]):
-        a = gemm.matmul(x, w)
-        ta = gemm.matmul(t, w)
-        x, g = _silu_and_grad(a)
-        t = g * ta
-    xt = torch.stack([x, t], dim=1)  # [E, 2, H]
-    out = gemm.matmul(xt.reshape(-1, xt.shape[-1]), ws[-1])
-    return out.reshape(x.shape[0], 2, -1)
+    xt = ef
+    for w in ws[:-1]:
+        xt = gemm.matmul(xt.reshape(2 * e, -1), w).reshape(e, 2, -1)
+        ops.mace_silu_tangent_(xt)
+    return gemm.matmul(xt.reshape(2 * e, -1), ws[-1]).reshape(e, 2, -1)
 
 
-def _per_l_linear(x: torch.Tensor, w: torch.Tensor, ls: list[int], transpose: bool = False) -> torch.Tensor:
+def _per_l_linear(x: torch.Tensor, w: torch.Tensor, ls: list[int], transpose: bool = False,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """Per-irrep channel mix on ``[N, n_lm, C]``: one GEMM per ``lm`` row, reading and writing the strided slices in
+    place (no gather / scatter copies)."""
     c = x.shape[-1]
-    out = torch.empty_like(x)
+    out = torch.empty_like(x) if out is None else out
     off = 0
     for i, l in enumerate(ls):
-        d = 2 * l + 1
         wi = w[i] / math.sqrt(c)
-        out[:, off: off + d] = gemm.matmul(x[:, off: off + d], wi.t() if transpose else wi)
-        off += d
+        wi = wi.t() if transpose else wi
+        for m in range(2 * l + 1):
+            gemm.matmul(x[:, off + m], wi, out=out[:, off + m])
+        off += 2 * l + 1
     return out
 
 
@@ -140,32 +144,39 @@ def _skip(ip: Any, h: torch.Tensor, species: torch.Tensor, nz: int, transpose: b
             so = sum(2 * k + 1 for k in src_ls[: src_ls.index(l)])
             do = sum(2 * k + 1 for k in dst_ls[: dst_ls.index(l)])
             w = ip.skip[i, z] / math.sqrt(c * nz)
-            d = 2 * l + 1
-            oz[:, do: do + d] = gemm.matmul(hz[:, so: so + d], w.t() if transpose else w)
+            w = w.t() if transpose else w
+            for m in range(2 * l + 1):
+                gemm.matmul(hz[:, so + m], w, out=oz[:, do + m])
         if rows is not None:
             out[rows] = oz
     return out
 
 
 def _linear_mid(ip: Any, mid: torch.Tensor, avg: float, lmax: int) -> torch.Tensor:
+    """``mid [N, n_mid, C]`` (components ordered ``(l, m, path)``) → ``msg [N, 16, C]``: for every ``lm`` one GEMM with
+    ``K = paths(l) * C`` straight from the strided slice of ``mid``."""
     n, _, c = mid.shape
     out = mid.new_empty(n, (lmax + 1) ** 2, c)
+    flat = mid.reshape(n, -1)
     for l in range(lmax + 1):
-        npl, d = ip.paths_per_l[l], 2 * l + 1
-        blk = mid[:, ip.mid_off[l]: ip.mid_off[l] + d * npl].reshape(n, d, npl * c)
+        npl = ip.paths_per_l[l]
         w = ip.linear[l] / (math.sqrt(npl * c) * avg)
-        out[:, l * l: l * l + d] = gemm.matmul(blk, w)
+        for m in range(2 * l + 1):
+            o = (ip.mid_off[l] + m * npl) * c
+            gemm.matmul(flat[:, o: o + npl * c], w, out=out[:, l * l + m])
     return out
 
 
 def _linear_mid_bwd(ip: Any, dmsg: torch.Tensor, avg: float, lmax: int) -> torch.Tensor:
     n, _, c = dmsg.shape
     dmid = dmsg.new_empty(n, ip.n_mid, c)
+    flat = dmid.reshape(n, -1)
     for l in range(lmax + 1):
-        npl, d = ip.paths_per_l[l], 2 * l + 1
-        w = ip.linear[l] / (math.sqrt(npl * c) * avg)
-        res = gemm.matmul(dmsg[:, l * l: l * l + d], w.t())  # [n, d, npl*c]
-        dmid[:, ip.mid_off[l]: ip.mid_off[l] + d * npl] = res.reshape(n, d * npl, c)
+        npl = ip.paths_per_l[l]
+        wt = (ip.linear[l] / (math.sqrt(npl * c) * avg)).t()
+        for m in range(2 * l + 1):
+            o = (ip.mid_off[l] + m * npl) * c
+            gemm.matmul(dmsg[:, l * l + m], wt, out=flat[:, o: o + npl * c])
     return dmid
 
 
@@ -178,11 +189,20 @@ def _sym_weights(ip: Any, corr: int) -> tuple[torch.Tensor, torch.Tensor | None]
 
 @torch.no_grad()
 def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, batch: torch.Tensor,
-            num_graphs: int, compute_force: bool, compute_stress: bool) -> dict[str, torch.Tensor | None]:
+            num_graphs: int, compute_force: bool, compute_stress: bool, dd: Any = None
+            ) -> dict[str, torch.Tensor | None]:
+    """Energy (+ forces, stress) with the native kernels.
+
+    ``dd`` (optional) is a domain-decomposition view: node-level tensors then cover the ``dd.n_owned`` owned atoms,
+    ``positions`` additionally holds ghost rows, sender features of ghost atoms are gathered from the owning GPU inside
+    the convolution kernels (``dd.home_rank`` / ``dd.home_row`` + peer pointer tables), and the adjoint scatters feature
+    and position gradients of ghosts back to their owners with reductions over NVLink.  ``dd.barrier()`` separates the
+    phases.  The returned energy is then the partial sum over owned atoms."""
     _native.require(data["positions"])
     cfg = model.config
     pos = data["positions"].detach().contiguous()
-    n = pos.shape[0]
+    n_local = pos.shape[0]
+    n = dd.n_owned if dd is not None else n_local
     dev = pos.device
     cell = data.get("cell")
     if cell is None:
@@ -193,26 +213,41 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
     csr = data.get("_csr")
     if csr is None:
         if data.get("neighbor_matrix") is not None:
-            csr = build_csr(data["neighbor_matrix"], data["num_neighbors"], data.get("neighbor_matrix_shifts"))
+            csr = build_csr(data["neighbor_matrix"][:n], data["num_neighbors"][:n],
+                            None if data.get("neighbor_matrix_shifts") is None else data["neighbor_matrix_shifts"][:n])
         else:
             csr = csr_from_edge_index(data["edge_index"], data.get("unit_shifts"), n)
     C, nz, lmax = cfg.channels, len(cfg.atomic_numbers), cfg.max_ell
     rmax, nb, pc = float(cfg.r_max), cfg.num_bessel, cfg.num_polynomial_cutoff
     geom = (pos, cell, b32, csr.erecv, csr.esend, csr.eS)
+    hr = dd.home_rank if dd is not None else None
+    hw = dd.home_row if dd is not None else None
+    if dd is not None:
+        dd.gpos.zero_()
 
     h = (model.node_embedding / math.sqrt(nz))[species].unsqueeze(1).contiguous()
     node_e = pos.new_zeros(n)
     saved = []
-    for ip in model.interactions:
+    for li, ip in enumerate(model.interactions):
         ws = [w / math.sqrt(w.shape[0]) for w in ip.radial]
         P = len(ip.paths)
         sc = _skip(ip, h, species, nz)
-        u = _per_l_linear(h, ip.linear_up, ip.l_in).contiguous()
+        u_ptrs = du = du_ptrs = None
+        if dd is not None:
+            u, u_ptrs = dd.feature_buffer(f"u{li}", (n, h.shape[1], C))
+            _per_l_linear(h, ip.linear_up, ip.l_in, out=u)
+            if li > 0 and compute_force:
+                du, du_ptrs = dd.feature_buffer(f"du{li}", (n, h.shape[1], C))
+                du.zero_()
+            dd.barrier()  # every rank's u (and zeroed du / gradient buffers) is in place before peers touch it
+        else:
+            u = _per_l_linear(h, ip.linear_up, ip.l_in).contiguous()
         mid = pos.new_empty(n, ip.n_mid, C)
         for (i0, i1, e0, e1) in _chunks(csr, n, 4 * P * C):
             ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, False)
             R = _radial_weights(ws, ef, False).reshape(e1 - e0, P, C)
-            ops.mace_conv_fwd(u, pos, cell, b32, csr.eptr, csr.esend, csr.eS, R, i0, i1 - i0, e0, rmax, mid)
+            ops.mace_conv_fwd(u, pos, cell, b32, csr.eptr, csr.esend, csr.eS, R, i0, i1 - i0, e0, rmax, mid, hr, hw,
+                              u_ptrs)
             del ef, R
         msg = _linear_mid(ip, mid, cfg.avg_num_neighbors, lmax)
         del mid
@@ -229,22 +264,23 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         else:
             node_e += s @ (ip.readout_w1 / math.sqrt(C))
             ro = (None, None)
-        saved.append((ip, u, msg, ws, w0, w1, ro))
+        saved.append((ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs))
         h = h_new
         del B, sc
     scale, shift = model.scale.to(pos.dtype), model.shift.to(pos.dtype)
     node_e = model.atomic_energies.to(pos.dtype)[species] + node_e * scale + shift
-    energy = torch.zeros(num_graphs, dtype=torch.float64, device=dev).index_add_(0, batch, node_e.double()).to(pos.dtype)
+    energy = torch.zeros(num_graphs, dtype=torch.float64, device=dev).index_add_(0, batch[:n], node_e.double()).to(pos.dtype)
     out: dict[str, torch.Tensor | None] = {"energy": energy, "node_energy": node_e, "forces": None, "stress": None,
                                             "hessian": None}
     if not (compute_force or compute_stress):
         return out
 
-    grad_pos = torch.zeros_like(pos)
+    grad_pos = dd.gpos if dd is not None else torch.zeros_like(pos)
+    gp_ptrs = dd.gpos_ptrs if dd is not None else None
     strain_grad = torch.zeros(num_graphs, 9, dtype=torch.float64, device=dev) if compute_stress else None
     dh: torch.Tensor | None = None
     for li in range(len(saved) - 1, -1, -1):
-        ip, u, msg, ws, w0, w1, ro = saved[li]
+        ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs = saved[li]
         n_out = sum(2 * l + 1 for l in ip.l_out)
         dh_tot = pos.new_zeros(n, n_out, C) if dh is None else dh
         if ip.last:
@@ -257,18 +293,21 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         dmid = _linear_mid_bwd(ip, dmsg, cfg.avg_num_neighbors, lmax)
         del dmsg
         P = len(ip.paths)
-        du = torch.zeros_like(u) if li > 0 else None
+        if dd is None:
+            du = torch.zeros_like(u) if li > 0 else None
         for (i0, i1, e0, e1) in _chunks(csr, n, 8 * P * C):
             ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, True)
             RD = _radial_weights(ws, ef, True).reshape(e1 - e0, 2, P, C)
             ops.mace_conv_bwd(u, dmid, pos, cell, b32, csr.eptr, csr.esend, csr.eS, RD, i0, i1 - i0, e0, rmax, du,
-                              grad_pos, strain_grad)
+                              grad_pos, strain_grad, hr, hw, u_ptrs, du_ptrs, gp_ptrs)
             del ef, RD
         del dmid
+        if dd is not None:
+            dd.barrier()  # feature / position gradients pushed by peers have landed
         if li > 0:
             dh = _per_l_linear(du, ip.linear_up, ip.l_in, transpose=True) + _skip(ip, dh_tot, species, nz, transpose=True)
         saved[li] = None
-    out["forces"] = -grad_pos
+    out["forces"] = -grad_pos[:n]
     if compute_stress:
         vol = torch.linalg.det(cell).abs().double()
         sg = strain_grad.reshape(num_graphs, 3, 3)

@@ -313,28 +313,53 @@ def write_header(path: str) -> None:
             for o, exprs in by_out.items():
                 body.append(f"  acc[{o}] = fmaf(R[{p}], {' + '.join(exprs)}, acc[{o}]);")
         lines += [f"#define MACE_{tag}_FWD(h, Y, R, acc) do {{ \\"] + [b + " \\" for b in body] + ["} while (0)", ""]
-        # backward: S[p] = sum coef*h*Y*G ; dh[a] += R[p]*coef*Y[b]*G[o] ; dY[b] += R[p]*coef*h[a]*G[o]
-        body = []
+        # backward, two stages.  Per receiver: T[(p,a,b)] = sum_c coef[a,b,c] * G[out(p,c)] (G is shared by all edges
+        # of the receiver).  Per edge and path: A_a = sum_b T_ab Y_b;  S_p = sum_a h_a A_a;  dh_a += R_p A_a;
+        # dY_b += R_p sum_a T_ab h_a.
+        prep, edge, k = [], [], 0
         for p, tl in enumerate(terms):
-            body.append(f"  {{ float s_ = 0.f, t_; const float r_ = R[{p}];")
+            pairs: dict[tuple[int, int], list[str]] = {}
             for (a, b, c, coef) in tl:
-                o = out_index[p][c]
-                body.append(f"    t_ = {coef:.9e}f*G[{o}]; s_ = fmaf(t_*h[{a}], Y[{b}], s_); "
-                            f"dh[{a}] = fmaf(r_*t_, Y[{b}], dh[{a}]); dY[{b}] = fmaf(r_*t_, h[{a}], dY[{b}]);")
-            body.append(f"    S[{p}] = s_; }}")
-        lines += [f"#define MACE_{tag}_BWD(h, Y, R, G, dh, dY, S) do {{ \\"] + [b + " \\" for b in body] + \
+                pairs.setdefault((a, b), []).append(f"{coef:.9e}f*G[{out_index[p][c]}]")
+            tindex = {}
+            for (a, b), exprs in pairs.items():
+                prep.append(f"  T[{k}] = {' + '.join(exprs)};")
+                tindex[(a, b)] = k
+                k += 1
+            edge.append(f"  {{ float s_ = 0.f, v_; const float r_ = R[{p}];")
+            for a in sorted({ab[0] for ab in tindex}):
+                expr = " + ".join(f"T[{tindex[(a, b)]}]*Y[{b}]" for (aa, b) in tindex if aa == a)
+                edge.append(f"    v_ = {expr}; s_ = fmaf(h[{a}], v_, s_); dh[{a}] = fmaf(r_, v_, dh[{a}]);")
+            for b in sorted({ab[1] for ab in tindex}):
+                expr = " + ".join(f"T[{tindex[(a, bb)]}]*h[{a}]" for (a, bb) in tindex if bb == b)
+                edge.append(f"    v_ = {expr}; dY[{b}] = fmaf(r_, v_, dY[{b}]);")
+            edge.append(f"    S[{p}] = s_; }}")
+        lines += [f"#define MACE_{tag}_NT {k}",
+                  f"#define MACE_{tag}_BWD_PREP(G, T) do {{ \\"] + [t + " \\" for t in prep] + ["} while (0)"]
+        lines += [f"#define MACE_{tag}_BWD_EDGE(h, Y, R, T, dh, dY, S) do {{ \\"] + [t + " \\" for t in edge] + \
                  ["} while (0)", ""]
-    # symmetric contraction tables: flat arrays of (i,j,k packed), coef, and group boundaries per (eta, M)
+    # symmetric contraction: straight-line polynomial evaluation (x[16], gradients dx[16] live in registers).
+    # W(k) must expand to the weight of basis element k of the (nu, L) block for the thread's (element, channel).
     for L in (0, 1):
         for nu in (1, 2, 3):
             nb, terms = sym_terms(nu, L)
-            idx = ", ".join(str(sum(v << (8 * q) for q, v in enumerate(m))) for (_, _, m, _) in terms) or "0"
-            cf = ", ".join(f"{c:.9e}f" for (_, _, _, c) in terms) or "0.f"
-            grp = ", ".join(str(e * (2 * L + 1) + M) for (e, M, _, _) in terms) or "0"
-            lines += [f"#define MACE_SYM_{nu}_{L}_NBASIS {nb}", f"#define MACE_SYM_{nu}_{L}_NTERMS {len(terms)}",
-                      f"static __device__ const unsigned int mace_sym_{nu}_{L}_idx[] = {{{idx}}};",
-                      f"static __device__ const float mace_sym_{nu}_{L}_coef[] = {{{cf}}};",
-                      f"static __device__ const unsigned short mace_sym_{nu}_{L}_grp[] = {{{grp}}};", ""]
+            lines.append(f"#define MACE_SYM_{nu}_{L}_NBASIS {nb}")
+            groups: dict[tuple[int, int], list[tuple[tuple[int, ...], float]]] = {}
+            for (e, M, mono, coef) in terms:
+                groups.setdefault((e, M), []).append((mono, coef))
+            fwd, bwd = [], []
+            for (e, M), tl in groups.items():
+                expr = " + ".join(f"{coef:.9e}f*" + "*".join(f"x[{i}]" for i in mono) for mono, coef in tl)
+                fwd.append(f"  out[{M}] = fmaf(W({e}), {expr}, out[{M}]);")
+                bwd.append(f"  {{ const float s_ = W({e})*g[{M}];")
+                for mono, coef in tl:
+                    for q in range(len(mono)):
+                        rest = [f"x[{i}]" for k, i in enumerate(mono) if k != q]
+                        fac = "*".join([f"{coef:.9e}f"] + rest)
+                        bwd.append(f"    dx[{mono[q]}] = fmaf(s_, {fac}, dx[{mono[q]}]);")
+                bwd.append("  }")
+            lines += [f"#define MACE_SYM_FWD_{nu}_{L}(x, out) do {{ \\"] + [t + " \\" for t in fwd] + ["} while (0)"]
+            lines += [f"#define MACE_SYM_BWD_{nu}_{L}(x, g, dx) do {{ \\"] + [t + " \\" for t in bwd] + ["} while (0)", ""]
     with open(path, "w") as f:
         f.write("\n".join(lines) + "\n")
 

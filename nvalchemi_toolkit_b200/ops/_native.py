@@ -53,7 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         name="nvalchemi_b200_C",
         sources=sources(),
         extra_cflags=["-O3", "-fopenmp", "-std=c++17"],
-        extra_cuda_cflags=["-O3", "-lineinfo", "-std=c++17", "--extended-lambda", "-Xcompiler", "-fopenmp"] + ARCH_FLAGS,
+        extra_cuda_cflags=["-O3", "-lineinfo", "-std=c++17", "--extended-lambda", "-Xcompiler", "-fopenmp", "-Xptxas", "-v"] + ARCH_FLAGS,
         extra_ldflags=["-L/usr/lib/x86_64-linux-gnu", "-l:libgomp.so.1"],
         extra_include_paths=[CSRC],
         build_directory=build_dir,

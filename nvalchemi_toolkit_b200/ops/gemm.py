@@ -37,25 +37,43 @@ def _eligible(x2: torch.Tensor, k: int) -> bool:
             and x2.shape[0] > 0 and _native.available())
 
 
-def matmul(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0, act: int = 0) -> torch.Tensor:
-    """``act(alpha * x @ w)``; ``act``: 0 none, 1 SiLU scaled to unit second moment."""
+def _tma_ok(t: torch.Tensor) -> bool:
+    return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 4 == 0 and t.data_ptr() % 16 == 0
+
+
+def matmul(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0, act: int = 0, out: torch.Tensor | None = None
+           ) -> torch.Tensor:
+    """``act(alpha * x @ w)``; ``act``: 0 none, 1 SiLU scaled to unit second moment.
+
+    ``x`` may be a strided 2-D view (rows ``stride(0)`` apart, unit inner stride) and ``out`` a strided 2-D view: both
+    are addressed in place by the TMA descriptors / the epilogue, so slices of wider feature tensors need no copies."""
     k, n = w.shape
     lead = x.shape[:-1]
-    x2 = x.reshape(-1, k)
+    x2 = x if x.dim() == 2 else x.reshape(-1, k)
     if _eligible(x2, k):
-        if x2.stride(1) != 1 or x2.stride(0) % 4 != 0 or x2.data_ptr() % 16 != 0:
+        if not _tma_ok(x2):
             x2 = x2.contiguous()
         wt = w.t().contiguous()  # [N, K], K-major B operand; weights are small
-        out = _nops.gemm_tf32(x2, wt, float(alpha), int(act))
         _counters["tcgen05"] += 1
-        return out.reshape(*lead, n)
+        if out is not None and out.dim() == 2 and out.stride(1) == 1:
+            _nops.gemm_tf32_out(x2, wt, float(alpha), int(act), out)
+            return out
+        res = _nops.gemm_tf32(x2, wt, float(alpha), int(act)).reshape(*lead, n)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
     _counters["library"] += 1
-    out = torch.matmul(x2, w)
+    res = torch.matmul(x2, w)
     if alpha != 1.0:
-        out = out * alpha
+        res = res * alpha
     if act == 1:
-        out = torch.nn.functional.silu(out) * 1.6790176868438721
-    return out.reshape(*lead, n)
+        res = torch.nn.functional.silu(res) * 1.6790176868438721
+    res = res.reshape(*lead, n)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
 
 
 def check_errors(like: torch.Tensor) -> int:

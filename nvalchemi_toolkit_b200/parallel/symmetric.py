@@ -1,0 +1,79 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Symmetric memory arenas and the peer-to-peer context used by the fused communication kernels.
+
+One arena = one allocation of ``torch.distributed._symmetric_memory`` per rank, made with identical sizes on every
+rank and exchanged once (``rendezvous``); sub-buffers are carved out with identical offsets everywhere, so the address
+of a peer's sub-buffer is ``peer_base + offset`` and no further handshakes are needed.  Kernels receive the table of
+peer addresses as an ``int64[world]`` device tensor and touch peer memory with plain loads, stores and reductions
+over NVLink (never with TMA).
+
+The reference has no counterpart: all its communication goes through ``torch.distributed`` collectives
+(``nvalchemi/distributed/_core/gather_primitives.py``).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from nvalchemi_toolkit_b200.ops._native_counter import ops as _nops
+
+
+class SymmetricArena:
+    """Bump allocator over a peer-mapped buffer.  All ranks must perform the same sequence of ``alloc`` calls."""
+
+    def __init__(self, nbytes: int, device: torch.device, group: dist.ProcessGroup | None = None) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.device = device
+        self.nbytes = int((nbytes + 255) // 256 * 256)
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.offset = 0
+        self.buf.zero_()
+
+    def alloc(self, shape: tuple[int, ...], dtype: torch.dtype = torch.float32) -> tuple[torch.Tensor, torch.Tensor]:
+        """Returns ``(local view, int64[world] device tensor with every rank's address of the same sub-buffer)``."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty(0, dtype=dtype).element_size()
+        off = (self.offset + 255) // 256 * 256
+        if off + nbytes > self.nbytes:
+            raise MemoryError(f"symmetric arena exhausted: need {off + nbytes} bytes, have {self.nbytes}")
+        self.offset = off + nbytes
+        view = self.buf[off: off + nbytes].view(dtype).reshape(shape)
+        ptrs = torch.tensor([b + off for b in self.base_ptrs], dtype=torch.int64, device=self.device)
+        return view, ptrs
+
+    def reset(self) -> None:
+        self.offset = 0
+
+
+class P2PContext:
+    """Arena + flag-based barrier with a bounded wait and a status word."""
+
+    def __init__(self, arena_bytes: int, device: torch.device, group: dist.ProcessGroup | None = None) -> None:
+        self.arena = SymmetricArena(arena_bytes + 4096, device, group)
+        self.world, self.rank, self.device = self.arena.world, self.arena.rank, device
+        self.flags, self.flag_ptrs = self.arena.alloc((64,), torch.int32)
+        self.err = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.persistent_offset = self.arena.offset
+        torch.cuda.synchronize(device)
+        dist.barrier(self.arena.group)
+
+    def barrier(self) -> None:
+        """Device-side rendezvous on the current stream: orders this rank's earlier peer writes before the peers'
+        later reads.  A peer that does not arrive within about a second sets ``status()`` instead of hanging."""
+        self.epoch += 1
+        _nops.p2p_barrier(self.flag_ptrs, self.rank, self.world, self.epoch, self.err)
+
+    def status(self) -> int:
+        return int(self.err.item())
+
+    def release_transient(self) -> None:
+        self.arena.offset = self.persistent_offset

@@ -1,0 +1,96 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Slab domain decomposition over 2 GPUs against the single-GPU evaluation of the same system."""
+import os
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _worker(rank: int, world: int, port: int, q) -> None:
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                          NCCL_NVLS_ENABLE="0")
+        import torch.distributed as dist
+
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from nvalchemi_toolkit_b200 import Batch
+        from nvalchemi_toolkit_b200.distributed.slab_md import SlabDomainMD
+        from nvalchemi_toolkit_b200.dynamics import NVTLangevin
+        from nvalchemi_toolkit_b200.models.mace import MACE, MACEConfig, MACEWrapper
+        from nvalchemi_toolkit_b200.ops import gemm
+        from tests.helpers import fcc_supercell
+
+        gemm.set_precision("fp32")
+        torch.manual_seed(0)
+        cfg = MACEConfig(atomic_numbers=[29], channels=32, avg_num_neighbors=42.0)
+        model = MACE(cfg).to(dev)
+        cells = 8
+        d = fcc_supercell(cells, noise=0.08, seed=3)
+        n = d.num_nodes
+        gid = torch.arange(n)
+        from nvalchemi_toolkit_b200.dynamics import _ops
+
+        vel = torch.zeros(n, 3, device=dev)
+        mass = d.atomic_masses.to(dev)
+        _ops.initialize_velocities(vel, mass, 300.0, torch.zeros(n, dtype=torch.int32, device=dev), random_seed=1,
+                                   remove_com=False, rescale=False)
+        sim = SlabDomainMD(model, d.cell[0], n, dev, dt=1.0, temperature=300.0, friction=0.01, seed=7, halo_skin=1.0,
+                           max_neighbors=64)
+        lo, hi = rank * n // world, (rank + 1) * n // world  # arbitrary initial split: ownership is re-derived
+        sim.set_owned(d.positions[lo:hi], vel[lo:hi], mass[lo:hi], d.atomic_numbers[lo:hi], gid[lo:hi])
+        e_dd = sim.energy()
+        g0 = sim.gather()
+        # single-GPU reference of the same system on this rank
+        b = Batch.from_data_list([d], device=dev)
+        b["velocities"] = vel.clone()
+        w = MACEWrapper(model)
+        dyn = NVTLangevin(w, dt=1.0, temperature=300.0, friction=0.01, random_seed=7, hooks=w.make_neighbor_hooks(64))
+        from nvalchemi_toolkit_b200.dynamics import DynamicsStage
+
+        dyn._call_hooks(DynamicsStage.BEFORE_COMPUTE, b)
+        dyn.compute(b)
+        res = {"e_err": abs(e_dd - float(b.energy)), "e": float(b.energy),
+               "f_err": float((g0["forces"] - b.forces).abs().max()), "f": float(b.forces.abs().max())}
+        sim.run(3)
+        dyn.run(b, 3)
+        g1 = sim.gather()
+        wrapped = _ops.wrap_positions(b.positions, b.cell, b.batch_idx)
+        dp = g1["positions"] - wrapped
+        L = float(d.cell[0, 0, 0])
+        dp = dp - L * torch.round(dp / L)
+        res.update(x_err=float(dp.abs().max()), v_err=float((g1["velocities"] - b.velocities).abs().max()),
+                   status=sim.p2p.status(), ghosts=sim.n_ghost, owned=sim.n_owned, gemm=gemm.check_errors(b.positions))
+        q.put((rank, res))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as exc:  # pragma: no cover
+        import traceback
+
+        q.put((rank, {"error": f"{type(exc).__name__}: {exc}\\n{traceback.format_exc()}"}))
+
+
+def test_slab_dd_matches_single_gpu():
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, 29533, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=600) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        if p.is_alive():
+            p.terminate()
+    for r, res in results.items():
+        assert "error" not in res, res["error"]
+        assert res["status"] == 0 and res["gemm"] == 0
+        assert res["owned"] > 0 and res["ghosts"] > 0
+        assert res["e_err"] < 1e-3 * max(1.0, abs(res["e"]))
+        assert res["f_err"] < 2e-4 * max(1.0, res["f"])
+        assert res["x_err"] < 1e-4 and res["v_err"] < 1e-4
