@@ -1,0 +1,9 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Dynamics hooks: safety, monitoring, constraints, snapshots, logging (reference ``nvalchemi/dynamics/hooks``)."""
+from nvalchemi_toolkit_b200.dynamics.hooks.library import (
+    AlignCellHook, ConvergedSnapshotHook, EnergyDriftMonitorHook, FreezeAtomsHook, LoggingHook, MaxForceClampHook,
+    NaNDetectorHook, SnapshotHook,
+)
+
+__all__ = ["AlignCellHook", "ConvergedSnapshotHook", "EnergyDriftMonitorHook", "FreezeAtomsHook", "LoggingHook",
+           "MaxForceClampHook", "NaNDetectorHook", "SnapshotHook"]
