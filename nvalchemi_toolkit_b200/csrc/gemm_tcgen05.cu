@@ -24,7 +24,6 @@ using at::Tensor;
 constexpr int BM = 128;
 constexpr int BK = 32;      // 32 tf32 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 8;   // tf32 MMA depth
-constexpr int STAGES = 3;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -106,7 +105,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 
 constexpr float kSiluNorm = 1.6790176868438721f;
 
-template <int BN>
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(192) gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA,
                                                         const __grid_constant__ CUtensorMap tmB,
                                                         float* __restrict__ C, int M, int N, int K, int64_t ldc,
@@ -189,7 +188,14 @@ __global__ void __launch_bounds__(192) gemm_tf32_kernel(const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           float x = v[j] * alpha;
-          if (act == 1) x = x / (1.f + __expf(-x)) * kSiluNorm;
+          if (act == 1) {
+            x = x / (1.f + __expf(-x)) * kSiluNorm;
+          } else if (act == 2) {
+            // rows alternate (value, tangent): even rows get silu(a), odd rows silu'(a_even) * t
+            float a = __shfl_sync(0xffffffffu, x, lane & ~1);
+            float sg = 1.f / (1.f + __expf(-a));
+            x = (lane & 1) ? sg * (1.f + a * (1.f - sg)) * kSiluNorm * x : a * sg * kSiluNorm;
+          }
           v[j] = x;
         }
 #pragma unroll
@@ -285,19 +291,26 @@ Tensor gemm_tf32_impl(const Tensor& a, const Tensor& bt, double alpha, int64_t a
   dim3 grid((unsigned)tiles);
   int* err = error_word(a.device()).data_ptr<int>();
   auto st = at::cuda::getCurrentCUDAStream();
+  // short-K problems (radial MLP, K <= 64) need only two ring slots: 64 KB of shared memory, three CTAs per SM
+  const bool short_k = K <= 2 * BK;
+#define NVA_LAUNCH(BN_, ST_)                                                                                        \
+  do {                                                                                                              \
+    size_t smem = (size_t)ST_ * (BM * BK * 4 + BN_ * BK * 4) + 1024 + 256;                                          \
+    static bool configured = false;                                                                                 \
+    if (!configured) {                                                                                              \
+      C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_tf32_kernel<BN_, ST_>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                          (int)smem));                                                              \
+      configured = true;                                                                                            \
+    }                                                                                                               \
+    gemm_tf32_kernel<BN_, ST_><<<grid, 192, smem, st>>>(ma, mb, c.data_ptr<float>(), (int)M, (int)N, (int)K,        \
+                                                        c.stride(0), (float)alpha, (int)act, err);                  \
+  } while (0)
   if (bn == 64) {
-    size_t smem = STAGES * (BM * BK * 4 + 64 * BK * 4) + 1024 + 256;
-    static bool set64 = false;
-    if (!set64) { C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_tf32_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set64 = true; }
-    gemm_tf32_kernel<64><<<grid, 192, smem, st>>>(ma, mb, c.data_ptr<float>(), (int)M, (int)N, (int)K, c.stride(0),
-                                                  (float)alpha, (int)act, err);
+    if (short_k) NVA_LAUNCH(64, 2); else NVA_LAUNCH(64, 4);
   } else {
-    size_t smem = STAGES * (BM * BK * 4 + 128 * BK * 4) + 1024 + 256;
-    static bool set128 = false;
-    if (!set128) { C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_tf32_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set128 = true; }
-    gemm_tf32_kernel<128><<<grid, 192, smem, st>>>(ma, mb, c.data_ptr<float>(), (int)M, (int)N, (int)K, c.stride(0),
-                                                   (float)alpha, (int)act, err);
+    if (short_k) NVA_LAUNCH(128, 2); else NVA_LAUNCH(128, 3);
   }
+#undef NVA_LAUNCH
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return c;
 }

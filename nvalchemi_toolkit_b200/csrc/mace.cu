@@ -150,19 +150,33 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(
       const float* ub = u;
       int64_t jr = j;
       if (home_rank != nullptr) { ub = reinterpret_cast<const float*>(u_ptrs[home_rank[j]]); jr = home_row[j]; }
-      sup[threadIdx.x] = ub + jr * NIN * C;
+      sup[threadIdx.x] = ub + jr * NIN * C;  // rows of cut-off edges are loaded (prefetch) but never used
     }
     __syncthreads();
+    // software pipeline: the loads of edge t+1 are in flight while edge t is being contracted
+    float h[NIN], Rv[NPATH], hn[NIN], Rn[NPATH];
+    {
+      const float* up = sup[0] + c;
+      const float* rp = R + ((int64_t)base - e_chunk0) * NPATH * C + c;
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) hn[a] = __ldg(up + a * C);
+#pragma unroll
+      for (int p = 0; p < NPATH; ++p) Rn[p] = __ldg(rp + p * C);
+    }
     for (int t = 0; t < nt; ++t) {
-      int j = sj[t];
-      if (j < 0) continue;
-      float h[NIN], Rv[NPATH];
-      const float* up = sup[t] + c;
 #pragma unroll
-      for (int a = 0; a < NIN; ++a) h[a] = __ldg(up + a * C);
-      const float* rp = R + ((int64_t)(base + t) - e_chunk0) * NPATH * C + c;
+      for (int a = 0; a < NIN; ++a) h[a] = hn[a];
 #pragma unroll
-      for (int p = 0; p < NPATH; ++p) Rv[p] = __ldg(rp + p * C);
+      for (int p = 0; p < NPATH; ++p) Rv[p] = Rn[p];
+      if (t + 1 < nt) {
+        const float* up = sup[t + 1] + c;
+        const float* rp = R + ((int64_t)(base + t + 1) - e_chunk0) * NPATH * C + c;
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) hn[a] = __ldg(up + a * C);
+#pragma unroll
+        for (int p = 0; p < NPATH; ++p) Rn[p] = __ldg(rp + p * C);
+      }
+      if (sj[t] < 0) continue;
       const float* Y = sY[t];
       if (L1) { MACE_L1_FWD(h, Y, Rv, acc); } else { MACE_L0_FWD(h, Y, Rv, acc); }
     }
@@ -235,17 +249,35 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(
       sgp[threadIdx.x] = gpb + 3 * jr;
     }
     __syncthreads();
+    float hn[NIN], Rn[2 * NPATH];
+    {
+      const float* up = sup[0] + c;
+      const float* rp = RD + ((int64_t)base - e_chunk0) * 2 * NPATH * C + c;
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) hn[a] = __ldg(up + a * C);
+#pragma unroll
+      for (int p = 0; p < 2 * NPATH; ++p) Rn[p] = __ldg(rp + p * C);
+    }
     for (int t = 0; t < nt; ++t) {
       int j = sj[t];
       float f[3] = {0.f, 0.f, 0.f};
+      float h[NIN], Rv[NPATH], Rd[NPATH];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) h[a] = hn[a];
+#pragma unroll
+      for (int p = 0; p < NPATH; ++p) { Rv[p] = Rn[p]; Rd[p] = Rn[NPATH + p]; }
+      if (t + 1 < nt) {
+        const float* up = sup[t + 1] + c;
+        const float* rp = RD + ((int64_t)(base + t + 1) - e_chunk0) * 2 * NPATH * C + c;
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) hn[a] = __ldg(up + a * C);
+#pragma unroll
+        for (int p = 0; p < 2 * NPATH; ++p) Rn[p] = __ldg(rp + p * C);
+      }
       if (j >= 0) {
-        float h[NIN], Rv[NPATH], dh[NIN], dY[16], S[NPATH];
-        const float* up = sup[t] + c;
+        float dh[NIN], dY[16], S[NPATH];
 #pragma unroll
-        for (int a = 0; a < NIN; ++a) { h[a] = __ldg(up + a * C); dh[a] = 0.f; }
-        const float* rp = RD + ((int64_t)(base + t) - e_chunk0) * 2 * NPATH * C + c;
-#pragma unroll
-        for (int p = 0; p < NPATH; ++p) Rv[p] = __ldg(rp + p * C);
+        for (int a = 0; a < NIN; ++a) dh[a] = 0.f;
 #pragma unroll
         for (int b = 0; b < 16; ++b) dY[b] = 0.f;
         const EdgeGeom& g = sg[t];
@@ -253,7 +285,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(
         if (L1) { MACE_L1_BWD_EDGE(h, Y, Rv, T, dh, dY, S); } else { MACE_L0_BWD_EDGE(h, Y, Rv, T, dh, dY, S); }
         float q = 0.f;
 #pragma unroll
-        for (int p = 0; p < NPATH; ++p) q = fmaf(S[p], __ldg(rp + (NPATH + p) * C), q);
+        for (int p = 0; p < NPATH; ++p) q = fmaf(S[p], Rd[p], q);
         float gy[3], s;
         sh_l3_vjp(g.n[0], g.n[1], g.n[2], Y, dY, gy, s);
 #pragma unroll

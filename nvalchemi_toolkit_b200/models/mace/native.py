@@ -105,8 +105,11 @@ def _radial_weights(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool) -
         return x.unsqueeze(1)
     xt = ef
     for w in ws[:-1]:
-        xt = gemm.matmul(xt.reshape(2 * e, -1), w).reshape(e, 2, -1)
-        ops.mace_silu_tangent_(xt)
+        if w.shape[0] >= 32 and gemm.get_precision() == "tf32":
+            xt = gemm.matmul(xt.reshape(2 * e, -1), w, act=2).reshape(e, 2, -1)  # activation + tangent in the epilogue
+        else:
+            xt = gemm.matmul(xt.reshape(2 * e, -1), w).reshape(e, 2, -1)
+            ops.mace_silu_tangent_(xt)
     return gemm.matmul(xt.reshape(2 * e, -1), ws[-1]).reshape(e, 2, -1)
 
 

@@ -43,7 +43,8 @@ def _tma_ok(t: torch.Tensor) -> bool:
 
 def matmul(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0, act: int = 0, out: torch.Tensor | None = None
            ) -> torch.Tensor:
-    """``act(alpha * x @ w)``; ``act``: 0 none, 1 SiLU scaled to unit second moment.
+    """``act(alpha * x @ w)``; ``act``: 0 none, 1 SiLU scaled to unit second moment, 2 the same for rows that
+    alternate (value, tangent): even rows get ``silu(a)``, odd rows ``silu'(a_even) * t``.
 
     ``x`` may be a strided 2-D view (rows ``stride(0)`` apart, unit inner stride) and ``out`` a strided 2-D view: both
     are addressed in place by the TMA descriptors / the epilogue, so slices of wider feature tensors need no copies."""
@@ -69,6 +70,10 @@ def matmul(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0, act: int = 0, o
         res = res * alpha
     if act == 1:
         res = torch.nn.functional.silu(res) * 1.6790176868438721
+    elif act == 2:  # rows alternate (value, tangent)
+        a, t = res[0::2], res[1::2]
+        s = torch.sigmoid(a)
+        res = torch.stack([a * s, s * (1.0 + a * (1.0 - s)) * t], dim=1).reshape(res.shape) * 1.6790176868438721
     res = res.reshape(*lead, n)
     if out is not None:
         out.copy_(res)

@@ -110,6 +110,12 @@ def test_tcgen05_gemm_matches_fp32(m, n, k):
     out2 = gemm.matmul(a, w, alpha=0.5, act=1)
     ref2 = torch.nn.functional.silu(0.5 * ref) * 1.6790176868438721
     assert float((out2 - ref2).abs().max() / ref2.abs().max()) < 3e-3
+    if m % 2 == 0:  # interleaved (value, tangent) rows: activation and its derivative in the epilogue
+        out3 = gemm.matmul(a, w, act=2)
+        av, tv = ref[0::2], ref[1::2]
+        sg = torch.sigmoid(av)
+        ref3 = torch.stack([av * sg, sg * (1 + av * (1 - sg)) * tv], dim=1).reshape(ref.shape) * 1.6790176868438721
+        assert float((out3 - ref3).abs().max() / ref3.abs().max()) < 6e-3
 
 
 @pytest.mark.gpu
