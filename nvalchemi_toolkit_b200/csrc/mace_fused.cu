@@ -1,0 +1,493 @@
+// SPDX-License-Identifier: Apache-2.0
+// Fused MACE convolution for sm_100a: the output layer of the radial MLP runs on the tensor cores INSIDE the
+// convolution kernel and its result never leaves the SM.
+//
+//   R[e, (p, c)] = sum_k h3[e, k] * W4[k, (p, c)]            (tcgen05.mma kind::tf32, accumulator in TMEM)
+//   mid[i, :, c] = sum_{e -> i} TP(u[sender(e), :, c], Y(e), R[e, :, c])   (CUDA cores, thread = channel)
+//
+// One persistent CTA per SM.  The A operand of the MMA is W4^T restricted to a group of at most five paths
+// ([paths*128, 64] fp32 = 160 KB, loaded once by TMA and kept resident); the B operand is a tile of 16 edges of the
+// hidden activations h3 (backward: 16 edges x (value, d/dr) = 32 rows), streamed by TMA through a two-slot ring.
+// D = [128 channels x (paths * rows)] lives in TMEM, double-buffered, so the tensor-core work of tile t+1 overlaps the
+// tensor-product arithmetic of tile t.  Thread c of the four compute warps owns TMEM lane c = channel c and reads its
+// radial weights with tcgen05.ld (one or two columns per edge and path).  Warp 4 allocates TMEM, issues TMA and MMA.
+// Replaces: cuEquivariance fused_tensor_product + the cuBLAS radial MLP output layer of the reference's MACE path
+// (nvalchemi/models/mace.py:205-287,403-411), and removes the [E, paths*C] radial-weight round trip through HBM.
+// Every mbarrier wait is bounded; on expiry an error code is recorded and the CTA drains and frees its TMEM.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "mace_device.cuh"
+#include "mace_tables.h"
+#include "tcgen05_utils.cuh"
+
+namespace nva {
+using at::Tensor;
+
+constexpr int FT = 16;          // edges per tile
+constexpr int RECV_BLOCK = 32;  // receivers per work item
+
+template <int LAYER, int GROUP>
+struct GroupSpec;
+template <>
+struct GroupSpec<0, 0> {
+  static constexpr int NIN = MACE_L0_NIN, NP = MACE_L0G0_NP, NACC = MACE_L0G0_NACC, NT = MACE_L0G0_NT, NMID = MACE_L0_NMID;
+  static __device__ __forceinline__ int mid(int k) { constexpr int m[] = MACE_L0G0_MIDS; return m[k]; }
+  static __device__ __forceinline__ void fwd(const float* h, const float* Y, const float* R, float* acc) { MACE_L0G0_FWD(h, Y, R, acc); }
+  static __device__ __forceinline__ void prep(const float* G, float* T) { MACE_L0G0_BWD_PREP(G, T); }
+  static __device__ __forceinline__ void edge(const float* h, const float* Y, const float* R, const float* T, float* dh, float* dY, float* S) { MACE_L0G0_BWD_EDGE(h, Y, R, T, dh, dY, S); }
+};
+template <>
+struct GroupSpec<1, 0> {
+  static constexpr int NIN = MACE_L1_NIN, NP = MACE_L1G0_NP, NACC = MACE_L1G0_NACC, NT = MACE_L1G0_NT, NMID = MACE_L1_NMID;
+  static __device__ __forceinline__ int mid(int k) { constexpr int m[] = MACE_L1G0_MIDS; return m[k]; }
+  static __device__ __forceinline__ void fwd(const float* h, const float* Y, const float* R, float* acc) { MACE_L1G0_FWD(h, Y, R, acc); }
+  static __device__ __forceinline__ void prep(const float* G, float* T) { MACE_L1G0_BWD_PREP(G, T); }
+  static __device__ __forceinline__ void edge(const float* h, const float* Y, const float* R, const float* T, float* dh, float* dY, float* S) { MACE_L1G0_BWD_EDGE(h, Y, R, T, dh, dY, S); }
+};
+template <>
+struct GroupSpec<1, 1> {
+  static constexpr int NIN = MACE_L1_NIN, NP = MACE_L1G1_NP, NACC = MACE_L1G1_NACC, NT = MACE_L1G1_NT, NMID = MACE_L1_NMID;
+  static __device__ __forceinline__ int mid(int k) { constexpr int m[] = MACE_L1G1_MIDS; return m[k]; }
+  static __device__ __forceinline__ void fwd(const float* h, const float* Y, const float* R, float* acc) { MACE_L1G1_FWD(h, Y, R, acc); }
+  static __device__ __forceinline__ void prep(const float* G, float* T) { MACE_L1G1_BWD_PREP(G, T); }
+  static __device__ __forceinline__ void edge(const float* h, const float* Y, const float* R, const float* T, float* dh, float* dY, float* S) { MACE_L1G1_BWD_EDGE(h, Y, R, T, dh, dY, S); }
+};
+
+struct FusedArgs {
+  int i0, ni;                 // receiver range of this launch
+  int64_t e_chunk0;           // first edge covered by the h3 tensor map
+  const float* u;
+  const float* pos;
+  const float* cell;
+  const int* batch_idx;
+  const int* eptr;
+  const int* esend;
+  const int* eS;
+  float rmax;
+  float* mid;                 // forward output
+  const float* G;             // backward: dE/dmid
+  float* du;                  // backward: feature gradient (may be null)
+  float* grad_pos;
+  double* virial;
+  const int* home_rank;
+  const int* home_row;
+  const int64_t* u_ptrs;
+  const int64_t* du_ptrs;
+  const int64_t* gpos_ptrs;
+  int* err;
+};
+
+__device__ __forceinline__ void named_bar_sync128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// BWD = false: forward.  BWD = true: adjoint (B rows alternate value / radial derivative, N = 32).
+template <int LAYER, int GROUP, bool BWD, bool NEED_DU>
+__global__ void __launch_bounds__(160, 1) conv_fused_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                            const __grid_constant__ CUtensorMap tmH, FusedArgs a) {
+  using G = GroupSpec<LAYER, GROUP>;
+  constexpr int NIN = G::NIN, NP = G::NP, NACC = G::NACC, NT = G::NT, NMID = G::NMID;
+  constexpr int C = 128;
+  constexpr int NROW = BWD ? 2 * FT : FT;            // B rows (= MMA N) per tile
+  constexpr uint32_t A_BYTES = NP * 2 * 128 * 128;   // NP paths x 2 k-blocks x [128 rows x 128 B]
+  constexpr uint32_t B_BYTES = 2 * NROW * 128;       // 2 k-blocks x [NROW rows x 128 B]
+  constexpr uint32_t TCOLS = NP * NROW;              // TMEM columns per buffer
+  constexpr uint32_t TALLOC = 2 * TCOLS <= 128 ? 128 : (2 * TCOLS <= 256 ? 256 : 512);
+  static_assert(2 * TCOLS <= 512, "TMEM budget");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sA = base, sB = base + A_BYTES;
+  const uint32_t bar0 = sB + 2 * B_BYTES;
+  const uint32_t a_full = bar0, b_full0 = bar0 + 8, b_empty0 = bar0 + 24, t_full0 = bar0 + 40, t_empty0 = bar0 + 56;
+  const uint32_t tmem_slot = bar0 + 72;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  // per-tile edge data (generic pointers)
+  struct TileEdge {
+    float Y[16]; float n[3]; float rinv; float v[3];
+    int recv; int j; const float* up; float* dup; float* gpj;
+  };
+  TileEdge* te = reinterpret_cast<TileEdge*>(gen + A_BYTES + 2 * B_BYTES + 128);
+  float (*sred)[4][3] = reinterpret_cast<float (*)[4][3]>(reinterpret_cast<uint8_t*>(te) + sizeof(TileEdge) * FT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(sred) + sizeof(float) * FT * 12);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwork = (a.ni + RECV_BLOCK - 1) / RECV_BLOCK;
+
+  if (threadIdx.x == 0) {
+    mbar_init(a_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(b_full0 + 8 * s, 1); mbar_init(b_empty0 + 8 * s, 1);
+      mbar_init(t_full0 + 8 * s, 1); mbar_init(t_empty0 + 8 * s, 4);
+    }
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TALLOC) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA + MMA issuer
+    if (lane == 0) {
+      mbar_expect_tx(a_full, A_BYTES);
+      for (int p = 0; p < NP; ++p)
+        for (int kb = 0; kb < 2; ++kb)
+          tma_load_2d(sA + (p * 2 + kb) * 128 * 128, &tmW, kb * 32, p * 128, a_full);
+      bool ok = mbar_wait(a_full, 0, a.err, 11);
+      constexpr uint32_t idesc = umma_idesc_tf32(128, NROW);
+      int t = 0;  // global tile counter of this CTA (selects ring slot / TMEM buffer and mbarrier phase)
+      // two-deep software pipeline over all tiles of all work items: B(t+1) is requested before MMA(t)
+      int w = blockIdx.x, tt = 0, nt_w = 0;
+      int64_t row0_w = 0;
+      auto open_work = [&](int ww) {
+        int i0 = a.i0 + ww * RECV_BLOCK, i1 = min(i0 + RECV_BLOCK, a.i0 + a.ni);
+        int e0 = a.eptr[i0], e1 = a.eptr[i1];
+        nt_w = (e1 - e0 + FT - 1) / FT;
+        row0_w = (int64_t)e0 - a.e_chunk0;
+      };
+      auto issue_b = [&](int tcount, int64_t erow) -> bool {
+        int s = tcount & 1;
+        if (!mbar_wait(b_empty0 + 8 * s, ((tcount >> 1) & 1) ^ 1, a.err, 12)) return false;
+        mbar_expect_tx(b_full0 + 8 * s, B_BYTES);
+        int y = (int)(BWD ? 2 * erow : erow);
+        tma_load_2d(sB + s * B_BYTES, &tmH, 0, y, b_full0 + 8 * s);
+        tma_load_2d(sB + s * B_BYTES + NROW * 128, &tmH, 32, y, b_full0 + 8 * s);
+        return true;
+      };
+      // iterator over (work item, tile) pairs one step ahead of the MMA
+      int pw = w, ptt = 0, pnt = 0;
+      int64_t prow0 = 0;
+      bool p_valid = false;
+      auto advance_prefetch = [&]() {
+        // moves (pw, ptt) to the next existing tile; sets p_valid
+        while (pw < nwork) {
+          if (!p_valid) {
+            int i0 = a.i0 + pw * RECV_BLOCK, i1 = min(i0 + RECV_BLOCK, a.i0 + a.ni);
+            int e0 = a.eptr[i0], e1 = a.eptr[i1];
+            pnt = (e1 - e0 + FT - 1) / FT;
+            prow0 = (int64_t)e0 - a.e_chunk0;
+            ptt = 0;
+            p_valid = true;
+          } else {
+            ++ptt;
+          }
+          if (ptt < pnt) return;
+          p_valid = false;
+          pw += gridDim.x;
+        }
+      };
+      int tp = 0;  // tiles requested so far
+      advance_prefetch();
+      if (ok && pw < nwork) { ok = issue_b(tp, prow0 + (int64_t)ptt * FT); ++tp; }
+      for (; ok && w < nwork; w += gridDim.x) {
+        open_work(w);
+        for (tt = 0; tt < nt_w && ok; ++tt, ++t) {
+          advance_prefetch();
+          if (pw < nwork) { ok = issue_b(tp, prow0 + (int64_t)ptt * FT); ++tp; if (!ok) break; }
+          int s = t & 1;
+          ok = mbar_wait(b_full0 + 8 * s, (t >> 1) & 1, a.err, 13) && mbar_wait(t_empty0 + 8 * s, ((t >> 1) & 1) ^ 1, a.err, 14);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          for (int p = 0; p < NP; ++p) {
+            uint32_t d = tmem_base + s * TCOLS + p * NROW;
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                uint64_t da = umma_desc_sw128(sA + (p * 2 + kb) * 128 * 128 + k * UMMA_K * 4);
+                uint64_t db = umma_desc_sw128(sB + s * B_BYTES + kb * NROW * 128 + k * UMMA_K * 4);
+                umma_tf32(d, da, db, idesc, (kb | k) ? 1u : 0u);
+              }
+          }
+          umma_commit(b_empty0 + 8 * s);
+          umma_commit(t_full0 + 8 * s);
+        }
+      }
+      if (!ok) abort_flag[0] = 1;
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warps (thread = channel)
+    const int c = threadIdx.x;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    int t = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < nwork && ok; w += gridDim.x) {
+      int wi0 = a.i0 + w * RECV_BLOCK, wi1 = min(wi0 + RECV_BLOCK, a.i0 + a.ni);
+      int e0 = a.eptr[wi0], e1 = a.eptr[wi1];
+      int nt_w = (e1 - e0 + FT - 1) / FT;
+      int cur = -1;        // receiver whose accumulators are live
+      int next_recv = wi0; // receiver lookup cursor for tile preparation
+      float acc[BWD ? 1 : NACC];
+      float T[BWD ? NT : 1];
+      for (int tt = 0; tt < nt_w && ok; ++tt, ++t) {
+        int s = t & 1;
+        int tile_e0 = e0 + tt * FT;
+        // ---- per-edge geometry by the first FT threads
+        if (threadIdx.x < FT) {
+          int e = tile_e0 + threadIdx.x;
+          TileEdge& q = te[threadIdx.x];
+          if (e < e1) {
+            int i = next_recv;
+            while (a.eptr[i + 1] <= e) ++i;  // edges are receiver-major: short forward scan
+            int j = a.esend[e];
+            float v[3];
+            edge_vector(a.pos, a.cell, a.batch_idx, i, j, a.eS + 3 * e, v);
+            float r = sqrtf(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]);
+            bool in = r < a.rmax && r > 0.f;
+            float ri = in ? 1.f / r : 0.f;
+            q.n[0] = v[0] * ri; q.n[1] = v[1] * ri; q.n[2] = v[2] * ri; q.rinv = ri;
+            q.v[0] = v[0]; q.v[1] = v[1]; q.v[2] = v[2];
+            sh_l3(q.n[0], q.n[1], q.n[2], q.Y);
+            q.recv = i;
+            q.j = in ? j : -1;
+            const float* ub = a.u;
+            float* dub = a.du;
+            float* gpb = a.grad_pos;
+            int64_t jr = j;
+            if (a.home_rank != nullptr) {
+              int hr = a.home_rank[j];
+              jr = a.home_row[j];
+              ub = reinterpret_cast<const float*>(a.u_ptrs[hr]);
+              if (BWD && NEED_DU) dub = reinterpret_cast<float*>(a.du_ptrs[hr]);
+              if (BWD) gpb = reinterpret_cast<float*>(a.gpos_ptrs[hr]);
+            }
+            q.up = ub + jr * NIN * C;
+            q.dup = (BWD && NEED_DU) ? dub + jr * NIN * C : nullptr;
+            q.gpj = BWD ? gpb + 3 * jr : nullptr;
+          } else {
+            q.recv = -1; q.j = -1; q.up = a.u;
+          }
+        }
+        if (threadIdx.x == 0) abort_flag[1] = abort_flag[0];  // snapshot: every compute thread sees the same value
+        named_bar_sync128();
+        {  // advance the receiver cursor past this tile (same value in every thread)
+          int last = min(tile_e0 + FT, e1) - 1;
+          while (a.eptr[next_recv + 1] <= last) ++next_recv;
+        }
+        if (abort_flag[1]) { ok = false; break; }
+        ok = mbar_wait(t_full0 + 8 * s, (t >> 1) & 1, a.err, 15);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tb = lane_addr + s * TCOLS;
+        // ---- edge loop with the TMEM / global operands of edge n+1 in flight during edge n
+        float Rn[BWD ? 2 * NP : NP], hn[NIN];
+        auto fetch = [&](int n) {
+#pragma unroll
+          for (int p = 0; p < NP; ++p) {
+            if (BWD) tmem_ld_x2(tb + p * NROW + 2 * n, Rn[p], Rn[NP + p]);
+            else tmem_ld_x1(tb + p * NROW + n, Rn[p]);
+          }
+          const float* up = te[n].up + c;
+#pragma unroll
+          for (int k = 0; k < NIN; ++k) hn[k] = __ldg(up + k * C);
+        };
+        fetch(0);
+        for (int n = 0; n < FT; ++n) {
+          float Rv[NP], Rd[BWD ? NP : 1], h[NIN];
+          tmem_ld_wait();
+#pragma unroll
+          for (int p = 0; p < NP; ++p) { Rv[p] = Rn[p]; if (BWD) Rd[p] = Rn[NP + p]; }
+#pragma unroll
+          for (int k = 0; k < NIN; ++k) h[k] = hn[k];
+          if (n + 1 < FT) fetch(n + 1);
+          const TileEdge& q = te[n];
+          int i = q.recv;
+          if (i != cur) {  // uniform across the CTA
+            if (!BWD && cur >= 0) {
+              float* mp = a.mid + (int64_t)cur * NMID * C + c;
+#pragma unroll
+              for (int k = 0; k < NACC; ++k) mp[G::mid(k) * C] = acc[k];
+            }
+            cur = i;
+            if (i >= 0) {
+              if (!BWD) {
+#pragma unroll
+                for (int k = 0; k < NACC; ++k) acc[k] = 0.f;
+              } else {
+                float Gr[NACC];
+                const float* gp = a.G + (int64_t)i * NMID * C + c;
+#pragma unroll
+                for (int k = 0; k < NACC; ++k) Gr[k] = gp[G::mid(k) * C];
+                G::prep(Gr, T);
+              }
+            }
+          }
+          if (!BWD) {
+            if (q.j >= 0) G::fwd(h, q.Y, Rv, acc);
+          } else {
+            float f[3] = {0.f, 0.f, 0.f};
+            if (q.j >= 0) {
+              float dh[NIN], dY[16], S[NP];
+#pragma unroll
+              for (int k = 0; k < NIN; ++k) dh[k] = 0.f;
+#pragma unroll
+              for (int b = 0; b < 16; ++b) dY[b] = 0.f;
+              G::edge(h, q.Y, Rv, T, dh, dY, S);
+              float qq = 0.f;
+#pragma unroll
+              for (int p = 0; p < NP; ++p) qq = fmaf(S[p], Rd[p], qq);
+              float gy[3], sdot;
+              sh_l3_vjp(q.n[0], q.n[1], q.n[2], q.Y, dY, gy, sdot);
+#pragma unroll
+              for (int d = 0; d < 3; ++d) f[d] = (gy[d] - sdot * q.n[d]) * q.rinv + qq * q.n[d];
+              if (NEED_DU) {
+                float* dp = q.dup + c;
+#pragma unroll
+                for (int k = 0; k < NIN; ++k) atomicAdd(dp + k * C, dh[k]);
+              }
+            }
+#pragma unroll
+            for (int d = 0; d < 3; ++d) {
+              float x = f[d];
+              for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
+              if (lane == 0) sred[n][warp][d] = x;
+            }
+          }
+        }
+        // all TMEM reads of this buffer are complete (every load was waited for): hand it back to the MMA warp
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(t_empty0 + 8 * s);
+        if (BWD) {
+          named_bar_sync128();
+          if (threadIdx.x < FT) {
+            const TileEdge& q = te[threadIdx.x];
+            if (q.j >= 0) {
+              float f[3] = {0.f, 0.f, 0.f};
+              for (int ww = 0; ww < 4; ++ww)
+                for (int d = 0; d < 3; ++d) f[d] += sred[threadIdx.x][ww][d];
+              for (int d = 0; d < 3; ++d) {
+                atomicAdd(q.gpj + d, -f[d]);
+                atomicAdd(a.grad_pos + 3 * (int64_t)q.recv + d, f[d]);
+              }
+              if (a.virial != nullptr) {
+                double* vp = a.virial + 9 * (int64_t)a.batch_idx[q.recv];
+                for (int x = 0; x < 3; ++x)
+                  for (int y = 0; y < 3; ++y) atomicAdd(vp + 3 * x + y, (double)(q.v[x] * f[y]));
+              }
+            }
+          }
+        }
+        named_bar_sync128();  // tile edge data may be overwritten
+      }
+      if (!BWD && cur >= 0 && ok) {
+        float* mp = a.mid + (int64_t)cur * NMID * C + c;
+#pragma unroll
+        for (int k = 0; k < NACC; ++k) mp[G::mid(k) * C] = acc[k];
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 4) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TALLOC) : "memory");
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 fused_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    C10_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    TORCH_CHECK(p != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available");
+    fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  return fn;
+}
+
+static CUtensorMap fused_map(const float* ptr, int64_t rows, int box_rows) {
+  CUtensorMap m;
+  cuuint64_t dims[2] = {64, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {64 * 4};
+  cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fused_encode()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+  return m;
+}
+
+template <int LAYER, int GROUP, bool BWD, bool NEED_DU>
+static void launch_fused(const CUtensorMap& mw, const CUtensorMap& mh, const FusedArgs& a, int sms) {
+  using G = GroupSpec<LAYER, GROUP>;
+  constexpr int NROW = BWD ? 2 * FT : FT;
+  size_t smem = (size_t)G::NP * 2 * 128 * 128 + 2 * (2 * NROW * 128) + 128 + FT * 160 + FT * 48 + 64 + 1024 + 256;
+  auto kern = conv_fused_kernel<LAYER, GROUP, BWD, NEED_DU>;
+  static bool configured = false;
+  if (!configured) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  int nwork = (a.ni + RECV_BLOCK - 1) / RECV_BLOCK;
+  int grid = std::min(nwork, sms);
+  kern<<<grid, 160, smem, at::cuda::getCurrentCUDAStream()>>>(mw, mh, a);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// wg: [NP*128, 64] = rows of W4^T for the group's paths (path-major); h3: [rows, 64] hidden activations of the chunk's
+// edges (backward: value / derivative rows interleaved).  `mid_or_G` is the output (forward) or dE/dmid (backward).
+void mace_conv_fused(int64_t layer, int64_t group, bool backward, const Tensor& wg, const Tensor& h3, const Tensor& u,
+                     const Tensor& pos, const Tensor& cell, const Tensor& batch_idx, const Tensor& eptr,
+                     const Tensor& esend, const Tensor& eS, int64_t i0, int64_t ni, int64_t e_chunk0, double rmax,
+                     Tensor mid_or_G, const c10::optional<Tensor>& du, const c10::optional<Tensor>& grad_pos,
+                     const c10::optional<Tensor>& virial, const c10::optional<Tensor>& home_rank,
+                     const c10::optional<Tensor>& home_row, const c10::optional<Tensor>& u_ptrs,
+                     const c10::optional<Tensor>& du_ptrs, const c10::optional<Tensor>& gpos_ptrs, Tensor err) {
+  c10::cuda::CUDAGuard guard(pos.device());
+  NVA_CHECK_CONTIG(wg); NVA_CHECK_CONTIG(h3); NVA_CHECK_CONTIG(u); NVA_CHECK_CONTIG(mid_or_G);
+  TORCH_CHECK(u.size(2) == 128, "the fused convolution is specialised for 128 channels");
+  TORCH_CHECK(wg.size(1) == 64 && h3.size(-1) == 64, "the fused convolution expects a 64-wide last hidden layer");
+  if (ni == 0) return;
+  FusedArgs a;
+  a.i0 = (int)i0; a.ni = (int)ni; a.e_chunk0 = e_chunk0;
+  a.u = u.data_ptr<float>(); a.pos = pos.data_ptr<float>(); a.cell = cell.data_ptr<float>();
+  a.batch_idx = batch_idx.data_ptr<int>(); a.eptr = eptr.data_ptr<int>(); a.esend = esend.data_ptr<int>();
+  a.eS = eS.data_ptr<int>(); a.rmax = (float)rmax;
+  a.mid = backward ? nullptr : mid_or_G.data_ptr<float>();
+  a.G = backward ? mid_or_G.data_ptr<float>() : nullptr;
+  a.du = du.has_value() ? du->data_ptr<float>() : nullptr;
+  a.grad_pos = grad_pos.has_value() ? grad_pos->data_ptr<float>() : nullptr;
+  a.virial = virial.has_value() ? virial->data_ptr<double>() : nullptr;
+  a.home_rank = home_rank.has_value() ? home_rank->data_ptr<int>() : nullptr;
+  a.home_row = home_row.has_value() ? home_row->data_ptr<int>() : nullptr;
+  a.u_ptrs = u_ptrs.has_value() ? u_ptrs->data_ptr<int64_t>() : nullptr;
+  a.du_ptrs = du_ptrs.has_value() ? du_ptrs->data_ptr<int64_t>() : nullptr;
+  a.gpos_ptrs = gpos_ptrs.has_value() ? gpos_ptrs->data_ptr<int64_t>() : nullptr;
+  a.err = err.data_ptr<int>();
+  int64_t hrows = h3.numel() / 64;
+  CUtensorMap mw = fused_map(wg.data_ptr<float>(), wg.size(0), 128);
+  CUtensorMap mh = fused_map(h3.data_ptr<float>(), hrows, backward ? 2 * FT : FT);
+  int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  bool need_du = backward && a.du != nullptr;
+#define NVA_CASE(L_, G_)                                                                       \
+  if (layer == L_ && group == G_) {                                                            \
+    if (!backward) launch_fused<L_, G_, false, false>(mw, mh, a, sms);                         \
+    else if (need_du) launch_fused<L_, G_, true, true>(mw, mh, a, sms);                        \
+    else launch_fused<L_, G_, true, false>(mw, mh, a, sms);                                    \
+    return;                                                                                    \
+  }
+  NVA_CASE(0, 0)
+  NVA_CASE(1, 0)
+  NVA_CASE(1, 1)
+#undef NVA_CASE
+  TORCH_CHECK(false, "mace_conv_fused: unknown (layer, group)");
+}
+
+}  // namespace nva
+
+TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
+  m.def("mace_conv_fused(int layer, int group, bool backward, Tensor wg, Tensor h3, Tensor u, Tensor pos, Tensor cell, Tensor batch_idx, Tensor eptr, Tensor esend, Tensor eS, int i0, int ni, int e_chunk0, float rmax, Tensor(a!) mid_or_G, Tensor(b!)? du, Tensor(c!)? grad_pos, Tensor(d!)? virial, Tensor? home_rank, Tensor? home_row, Tensor? u_ptrs, Tensor? du_ptrs, Tensor? gpos_ptrs, Tensor(e!) err) -> ()", &nva::mace_conv_fused);
+}

@@ -113,6 +113,48 @@ def _radial_weights(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool) -
     return gemm.matmul(xt.reshape(2 * e, -1), ws[-1]).reshape(e, 2, -1)
 
 
+#: run the last radial layer on the tensor cores inside the convolution kernel (radial weights stay in TMEM)
+FUSED = True
+_err_words: dict[torch.device, torch.Tensor] = {}
+
+
+def fused_error_status(device: torch.device) -> int:
+    """Status word of the fused convolution kernels (0 = no bounded wait expired)."""
+    w = _err_words.get(device)
+    return 0 if w is None else int(w.item())
+
+
+def _fused_ok(model: Any, ip: Any) -> bool:
+    return (FUSED and gemm.get_precision() == "tf32" and model.config.channels == 128 and ip.radial[-1].shape[0] == 64
+            and len(ip.radial) >= 2)
+
+
+def _hidden(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool) -> torch.Tensor:
+    """Radial MLP up to its last hidden layer: ``[E, 64]`` or, with the tangent, ``[E, 2, 64]`` (rows interleaved)."""
+    e = ef.shape[0]
+    if not with_grad:
+        x = ef[:, 0]
+        for w in ws[:-1]:
+            x = gemm.matmul(x, w, act=1)
+        return x.contiguous()
+    xt = ef
+    for w in ws[:-1]:
+        if w.shape[0] >= 32:
+            xt = gemm.matmul(xt.reshape(2 * e, -1), w, act=2).reshape(e, 2, -1)
+        else:
+            xt = gemm.matmul(xt.reshape(2 * e, -1), w).reshape(e, 2, -1)
+            ops.mace_silu_tangent_(xt)
+    return xt.contiguous()
+
+
+def _group_weights(ip: Any, w_last: torch.Tensor, c: int) -> list[torch.Tensor]:
+    """Rows of ``W4^T`` ([paths*C, 64]) gathered per path group of the fused kernel."""
+    from nvalchemi_toolkit_b200.models.mace import o3
+
+    wt = w_last.t().contiguous().reshape(len(ip.paths), c, -1)
+    return [wt[g].reshape(len(g) * c, -1).contiguous() for g in o3.path_groups(ip.l_in)]
+
+
 def _per_l_linear(x: torch.Tensor, w: torch.Tensor, ls: list[int], transpose: bool = False,
                   out: torch.Tensor | None = None) -> torch.Tensor:
     """Per-irrep channel mix on ``[N, n_lm, C]``: one GEMM per ``lm`` row, reading and writing the strided slices in
@@ -245,13 +287,28 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
             dd.barrier()  # every rank's u (and zeroed du / gradient buffers) is in place before peers touch it
         else:
             u = _per_l_linear(h, ip.linear_up, ip.l_in).contiguous()
-        mid = pos.new_empty(n, ip.n_mid, C)
-        for (i0, i1, e0, e1) in _chunks(csr, n, 4 * P * C):
-            ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, False)
-            R = _radial_weights(ws, ef, False).reshape(e1 - e0, P, C)
-            ops.mace_conv_fwd(u, pos, cell, b32, csr.eptr, csr.esend, csr.eS, R, i0, i1 - i0, e0, rmax, mid, hr, hw,
-                              u_ptrs)
-            del ef, R
+        fused = _fused_ok(model, ip)
+        if fused:
+            err = _err_words.setdefault(dev, torch.zeros(1, dtype=torch.int32, device=dev))
+            wgs = _group_weights(ip, ws[-1], C)
+            mid = pos.new_zeros(n, ip.n_mid, C)
+            for (i0, i1, e0, e1) in _chunks(csr, n, 4 * 64):
+                ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, False)
+                h3 = _hidden(ws, ef, False)
+                for g, wg in enumerate(wgs):
+                    ops.mace_conv_fused(0 if ip.l_in == [0] else 1, g, False, wg, h3, u, pos, cell, b32, csr.eptr, csr.esend,
+                                        csr.eS, i0, i1 - i0, e0, rmax, mid, None, None, None, hr, hw, u_ptrs, None, None,
+                                        err)
+                del ef, h3
+        else:
+            wgs = None
+            mid = pos.new_empty(n, ip.n_mid, C)
+            for (i0, i1, e0, e1) in _chunks(csr, n, 4 * P * C):
+                ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, False)
+                R = _radial_weights(ws, ef, False).reshape(e1 - e0, P, C)
+                ops.mace_conv_fwd(u, pos, cell, b32, csr.eptr, csr.esend, csr.eS, R, i0, i1 - i0, e0, rmax, mid, hr, hw,
+                                  u_ptrs)
+                del ef, R
         msg = _linear_mid(ip, mid, cfg.avg_num_neighbors, lmax)
         del mid
         w0, w1 = _sym_weights(ip, cfg.correlation)
@@ -267,7 +324,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         else:
             node_e += s @ (ip.readout_w1 / math.sqrt(C))
             ro = (None, None)
-        saved.append((ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs))
+        saved.append((ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs, wgs))
         h = h_new
         del B, sc
     scale, shift = model.scale.to(pos.dtype), model.shift.to(pos.dtype)
@@ -283,7 +340,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
     strain_grad = torch.zeros(num_graphs, 9, dtype=torch.float64, device=dev) if compute_stress else None
     dh: torch.Tensor | None = None
     for li in range(len(saved) - 1, -1, -1):
-        ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs = saved[li]
+        ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs, wgs = saved[li]
         n_out = sum(2 * l + 1 for l in ip.l_out)
         dh_tot = pos.new_zeros(n, n_out, C) if dh is None else dh
         if ip.last:
@@ -298,12 +355,23 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         P = len(ip.paths)
         if dd is None:
             du = torch.zeros_like(u) if li > 0 else None
-        for (i0, i1, e0, e1) in _chunks(csr, n, 8 * P * C):
-            ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, True)
-            RD = _radial_weights(ws, ef, True).reshape(e1 - e0, 2, P, C)
-            ops.mace_conv_bwd(u, dmid, pos, cell, b32, csr.eptr, csr.esend, csr.eS, RD, i0, i1 - i0, e0, rmax, du,
-                              grad_pos, strain_grad, hr, hw, u_ptrs, du_ptrs, gp_ptrs)
-            del ef, RD
+        if wgs is not None:
+            err = _err_words[dev]
+            for (i0, i1, e0, e1) in _chunks(csr, n, 8 * 64):
+                ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, True)
+                h3 = _hidden(ws, ef, True)
+                for g, wg in enumerate(wgs):
+                    ops.mace_conv_fused(0 if ip.l_in == [0] else 1, g, True, wg, h3, u, pos, cell, b32, csr.eptr, csr.esend,
+                                        csr.eS, i0, i1 - i0, e0, rmax, dmid, du, grad_pos, strain_grad, hr, hw, u_ptrs,
+                                        du_ptrs, gp_ptrs, err)
+                del ef, h3
+        else:
+            for (i0, i1, e0, e1) in _chunks(csr, n, 8 * P * C):
+                ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, True)
+                RD = _radial_weights(ws, ef, True).reshape(e1 - e0, 2, P, C)
+                ops.mace_conv_bwd(u, dmid, pos, cell, b32, csr.eptr, csr.esend, csr.eS, RD, i0, i1 - i0, e0, rmax, du,
+                                  grad_pos, strain_grad, hr, hw, u_ptrs, du_ptrs, gp_ptrs)
+                del ef, RD
         del dmid
         if dd is not None:
             dd.barrier()  # feature / position gradients pushed by peers have landed

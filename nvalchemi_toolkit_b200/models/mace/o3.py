@@ -283,6 +283,24 @@ def sym_terms(nu: int, L: int) -> tuple[int, list[tuple[int, int, tuple[int, ...
     return int(U.shape[0]), terms
 
 
+def path_groups(l_in: list[int]) -> list[list[int]]:
+    """Split of the tensor-product paths into groups whose last-layer radial weights ([paths*C, 64] fp32) fit in the
+    shared memory of one CTA of the fused convolution kernel (at most 5 paths = 160 KB).  Groups are balanced by the
+    number of coupling terms."""
+    paths = conv_paths(l_in)
+    if len(paths) <= 5:
+        return [list(range(len(paths)))]
+    terms = conv_terms(paths, l_in)
+    order = sorted(range(len(paths)), key=lambda p: -len(terms[p]))
+    groups: list[list[int]] = [[], []]
+    load = [0, 0]
+    for p in order:
+        g = 0 if (load[0] <= load[1] and len(groups[0]) < 5) or len(groups[1]) >= 5 else 1
+        groups[g].append(p)
+        load[g] += len(terms[p])
+    return [sorted(g) for g in groups]
+
+
 def write_header(path: str) -> None:
     """Emit ``mace_tables.h``: unrolled tensor-product bodies and symmetric-contraction term tables."""
     lines = ["// SPDX-License-Identifier: Apache-2.0",
@@ -338,6 +356,56 @@ def write_header(path: str) -> None:
                   f"#define MACE_{tag}_BWD_PREP(G, T) do {{ \\"] + [t + " \\" for t in prep] + ["} while (0)"]
         lines += [f"#define MACE_{tag}_BWD_EDGE(h, Y, R, T, dh, dY, S) do {{ \\"] + [t + " \\" for t in edge] + \
                  ["} while (0)", ""]
+    # ---- per-group variants for the fused (tensor-core radial weights in TMEM) convolution kernel.  Local path index q
+    # runs over the group's paths; accumulators / gradients are compacted to the group's mid components.
+    for tag, l_in in (("L0", [0]), ("L1", [0, 1])):
+        paths = conv_paths(l_in)
+        terms = conv_terms(paths, l_in)
+        offs, npl, nmid = mid_layout(paths)
+        seen = [0] * (LMAX + 1)
+        out_index = []
+        for (l1, l2, l3) in paths:
+            k = seen[l3]
+            seen[l3] += 1
+            out_index.append([offs[l3] + m3 * npl[l3] + k for m3 in range(2 * l3 + 1)])
+        for gi, grp in enumerate(path_groups(l_in)):
+            gt = f"{tag}G{gi}"
+            mids = sorted({o for p in grp for o in out_index[p]})
+            loc = {o: k for k, o in enumerate(mids)}
+            lines += [f"// ---- {gt}: paths {grp} -> {len(mids)} mid components",
+                      f"#define MACE_{gt}_NP {len(grp)}", f"#define MACE_{gt}_NACC {len(mids)}",
+                      f"#define MACE_{gt}_PATHS {{{', '.join(str(p) for p in grp)}}}",
+                      f"#define MACE_{gt}_MIDS {{{', '.join(str(o) for o in mids)}}}"]
+            body = []
+            for q, p in enumerate(grp):
+                by_out: dict[int, list[str]] = {}
+                for (a_, b_, c_, coef) in terms[p]:
+                    by_out.setdefault(loc[out_index[p][c_]], []).append(f"{coef:.9e}f*h[{a_}]*Y[{b_}]")
+                for o, exprs in by_out.items():
+                    body.append(f"  acc[{o}] = fmaf(R[{q}], {' + '.join(exprs)}, acc[{o}]);")
+            lines += [f"#define MACE_{gt}_FWD(h, Y, R, acc) do {{ \\"] + [t + " \\" for t in body] + ["} while (0)"]
+            prep, edge, k = [], [], 0
+            for q, p in enumerate(grp):
+                pairs: dict[tuple[int, int], list[str]] = {}
+                for (a_, b_, c_, coef) in terms[p]:
+                    pairs.setdefault((a_, b_), []).append(f"{coef:.9e}f*G[{loc[out_index[p][c_]]}]")
+                tindex = {}
+                for (a_, b_), exprs in pairs.items():
+                    prep.append(f"  T[{k}] = {' + '.join(exprs)};")
+                    tindex[(a_, b_)] = k
+                    k += 1
+                edge.append(f"  {{ float s_ = 0.f, v_; const float r_ = R[{q}];")
+                for a_ in sorted({ab[0] for ab in tindex}):
+                    expr = " + ".join(f"T[{tindex[(a_, b_)]}]*Y[{b_}]" for (aa, b_) in tindex if aa == a_)
+                    edge.append(f"    v_ = {expr}; s_ = fmaf(h[{a_}], v_, s_); dh[{a_}] = fmaf(r_, v_, dh[{a_}]);")
+                for b_ in sorted({ab[1] for ab in tindex}):
+                    expr = " + ".join(f"T[{tindex[(a_, bb)]}]*h[{a_}]" for (a_, bb) in tindex if bb == b_)
+                    edge.append(f"    v_ = {expr}; dY[{b_}] = fmaf(r_, v_, dY[{b_}]);")
+                edge.append(f"    S[{q}] = s_; }}")
+            lines += [f"#define MACE_{gt}_NT {k}",
+                      f"#define MACE_{gt}_BWD_PREP(G, T) do {{ \\"] + [t + " \\" for t in prep] + ["} while (0)"]
+            lines += [f"#define MACE_{gt}_BWD_EDGE(h, Y, R, T, dh, dY, S) do {{ \\"] + [t + " \\" for t in edge] + \
+                     ["} while (0)", ""]
     # symmetric contraction: straight-line polynomial evaluation (x[16], gradients dx[16] live in registers).
     # W(k) must expand to the weight of basis element k of the (nu, L) block for the thread's (element, channel).
     for L in (0, 1):

@@ -150,6 +150,41 @@ def test_native_matches_oracle(precision):
 
 
 @pytest.mark.gpu
+def test_fused_tensor_core_convolution_matches_unfused():
+    """128-channel model: radial weights produced by tcgen05 inside the convolution kernel vs the GEMM + SIMT path."""
+    from nvalchemi_toolkit_b200.models.mace import native
+
+    torch.manual_seed(5)
+    cfg = MACEConfig(atomic_numbers=[29, 28], channels=128, avg_num_neighbors=40.0)
+    model = MACE(cfg, backend="auto").cuda()
+    d1, d2 = fcc_supercell(3, noise=0.1), fcc_supercell(2, a=3.9, noise=0.1, seed=7)
+    d2.__dict__["atomic_numbers"] = torch.where(torch.arange(d2.num_nodes) % 2 == 0, 29, 28)
+    w = MACEWrapper(model)
+    w.model_config.active_outputs = {"energy", "forces", "stress"}
+    outs = {}
+    for fused in (True, False):
+        b = Batch.from_data_list([d1, d2], device="cuda")
+        compute_neighbors(b, config=w.model_config.neighbor_config)
+        native.FUSED = fused
+        try:
+            outs[fused] = w(b)
+        finally:
+            native.FUSED = True
+    assert native.fused_error_status(torch.device("cuda", 0)) == 0 and gemm.check_errors(b.positions) == 0
+    ref, got = outs[False], outs[True]
+    assert float((got["energy"] - ref["energy"]).abs().max()) < 2e-3 * max(1.0, float(ref["energy"].abs().max()))
+    assert float((got["forces"] - ref["forces"]).abs().max()) < 5e-3 * float(ref["forces"].abs().max())
+    assert float((got["stress"] - ref["stress"]).abs().max()) < 5e-3 * float(ref["stress"].abs().max())
+    oracle = MACE(cfg, backend="torch").double().cuda()
+    oracle.load_state_dict({k: v.double() for k, v in model.state_dict().items()})
+    wo = MACEWrapper(oracle)
+    bo = Batch.from_data_list([d1, d2], device="cuda").to(dtype=torch.float64)
+    compute_neighbors(bo, config=wo.model_config.neighbor_config)
+    exact = wo(bo)
+    assert float((got["forces"].double() - exact["forces"]).abs().max()) < 2e-2 * float(exact["forces"].abs().max())
+
+
+@pytest.mark.gpu
 def test_neighbor_matrix_gpu_matches_cpu():
     b = Batch.from_data_list([fcc_supercell(4), fcc_supercell(1, a=3.0, seed=5)])
     compute_neighbors(b, 5.0)
