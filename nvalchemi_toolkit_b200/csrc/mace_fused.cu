@@ -80,11 +80,15 @@ struct FusedArgs {
   int* err;
 };
 
-__device__ __forceinline__ void named_bar_sync128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+template <int NTHREADS>
+__device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NTHREADS) : "memory"); }
 
 // BWD = false: forward.  BWD = true: adjoint (B rows alternate value / radial derivative, N = 32).
-template <int LAYER, int GROUP, bool BWD, bool NEED_DU>
-__global__ void __launch_bounds__(160, 1) conv_fused_kernel(const __grid_constant__ CUtensorMap tmW,
+// NG warp-groups of 128 compute threads share one tile: group g takes edges g, g+NG, ... (all groups can read all 128
+// TMEM lanes because warp w reaches lanes 32*(w%4)..), keeps its own partial sums and adds them to `mid` with
+// reductions.  Four compute warps alone would leave the SM's schedulers with one warp each.
+template <int LAYER, int GROUP, bool BWD, bool NEED_DU, int NG>
+__global__ void __launch_bounds__(128 * NG + 32, 1) conv_fused_kernel(const __grid_constant__ CUtensorMap tmW,
                                                             const __grid_constant__ CUtensorMap tmH, FusedArgs a) {
   using G = GroupSpec<LAYER, GROUP>;
   constexpr int NIN = G::NIN, NP = G::NP, NACC = G::NACC, NT = G::NT, NMID = G::NMID;
@@ -113,20 +117,22 @@ __global__ void __launch_bounds__(160, 1) conv_fused_kernel(const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(sred) + sizeof(float) * FT * 12);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int MMA_WARP = 4 * NG;
+  constexpr int NCOMP = 128 * NG;
   const int nwork = (a.ni + RECV_BLOCK - 1) / RECV_BLOCK;
 
   if (threadIdx.x == 0) {
     mbar_init(a_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(b_full0 + 8 * s, 1); mbar_init(b_empty0 + 8 * s, 1);
-      mbar_init(t_full0 + 8 * s, 1); mbar_init(t_empty0 + 8 * s, 4);
+      mbar_init(t_full0 + 8 * s, 1); mbar_init(t_empty0 + 8 * s, 4 * NG);
     }
     abort_flag[0] = 0;
     abort_flag[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TALLOC) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -136,7 +142,7 @@ __global__ void __launch_bounds__(160, 1) conv_fused_kernel(const __grid_constan
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
-  if (warp == 4) {
+  if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ TMA + MMA issuer
     if (lane == 0) {
       mbar_expect_tx(a_full, A_BYTES);
@@ -217,8 +223,9 @@ __global__ void __launch_bounds__(160, 1) conv_fused_kernel(const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ compute warps (thread = channel)
-    const int c = threadIdx.x;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const int c = threadIdx.x & 127;
+    const int grp = warp >> 2, wq = warp & 3;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     int t = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < nwork && ok; w += gridDim.x) {
@@ -269,7 +276,7 @@ __global__ void __launch_bounds__(160, 1) conv_fused_kernel(const __grid_constan
           }
         }
         if (threadIdx.x == 0) abort_flag[1] = abort_flag[0];  // snapshot: every compute thread sees the same value
-        named_bar_sync128();
+        compute_bar_sync<NCOMP>();
         {  // advance the receiver cursor past this tile (same value in every thread)
           int last = min(tile_e0 + FT, e1) - 1;
           while (a.eptr[next_recv + 1] <= last) ++next_recv;
@@ -291,22 +298,22 @@ __global__ void __launch_bounds__(160, 1) conv_fused_kernel(const __grid_constan
 #pragma unroll
           for (int k = 0; k < NIN; ++k) hn[k] = __ldg(up + k * C);
         };
-        fetch(0);
-        for (int n = 0; n < FT; ++n) {
+        fetch(grp);
+        for (int n = grp; n < FT; n += NG) {
           float Rv[NP], Rd[BWD ? NP : 1], h[NIN];
           tmem_ld_wait();
 #pragma unroll
           for (int p = 0; p < NP; ++p) { Rv[p] = Rn[p]; if (BWD) Rd[p] = Rn[NP + p]; }
 #pragma unroll
           for (int k = 0; k < NIN; ++k) h[k] = hn[k];
-          if (n + 1 < FT) fetch(n + 1);
+          if (n + NG < FT) fetch(n + NG);
           const TileEdge& q = te[n];
           int i = q.recv;
           if (i != cur) {  // uniform across the CTA
             if (!BWD && cur >= 0) {
               float* mp = a.mid + (int64_t)cur * NMID * C + c;
 #pragma unroll
-              for (int k = 0; k < NACC; ++k) mp[G::mid(k) * C] = acc[k];
+              for (int k = 0; k < NACC; ++k) atomicAdd(mp + G::mid(k) * C, acc[k]);
             }
             cur = i;
             if (i >= 0) {
@@ -350,7 +357,7 @@ __global__ void __launch_bounds__(160, 1) conv_fused_kernel(const __grid_constan
             for (int d = 0; d < 3; ++d) {
               float x = f[d];
               for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
-              if (lane == 0) sred[n][warp][d] = x;
+              if (lane == 0) sred[n][wq][d] = x;
             }
           }
         }
@@ -359,7 +366,7 @@ __global__ void __launch_bounds__(160, 1) conv_fused_kernel(const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(t_empty0 + 8 * s);
         if (BWD) {
-          named_bar_sync128();
+          compute_bar_sync<NCOMP>();
           if (threadIdx.x < FT) {
             const TileEdge& q = te[threadIdx.x];
             if (q.j >= 0) {
@@ -378,18 +385,18 @@ __global__ void __launch_bounds__(160, 1) conv_fused_kernel(const __grid_constan
             }
           }
         }
-        named_bar_sync128();  // tile edge data may be overwritten
+        compute_bar_sync<NCOMP>();  // tile edge data may be overwritten
       }
       if (!BWD && cur >= 0 && ok) {
         float* mp = a.mid + (int64_t)cur * NMID * C + c;
 #pragma unroll
-        for (int k = 0; k < NACC; ++k) mp[G::mid(k) * C] = acc[k];
+        for (int k = 0; k < NACC; ++k) atomicAdd(mp + G::mid(k) * C, acc[k]);
       }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 4) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TALLOC) : "memory");
   }
 }
@@ -425,7 +432,8 @@ static void launch_fused(const CUtensorMap& mw, const CUtensorMap& mh, const Fus
   using G = GroupSpec<LAYER, GROUP>;
   constexpr int NROW = BWD ? 2 * FT : FT;
   size_t smem = (size_t)G::NP * 2 * 128 * 128 + 2 * (2 * NROW * 128) + 128 + FT * 160 + FT * 48 + 64 + 1024 + 256;
-  auto kern = conv_fused_kernel<LAYER, GROUP, BWD, NEED_DU>;
+  constexpr int NG = BWD ? 3 : 4;
+  auto kern = conv_fused_kernel<LAYER, GROUP, BWD, NEED_DU, NG>;
   static bool configured = false;
   if (!configured) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -433,7 +441,7 @@ static void launch_fused(const CUtensorMap& mw, const CUtensorMap& mh, const Fus
   }
   int nwork = (a.ni + RECV_BLOCK - 1) / RECV_BLOCK;
   int grid = std::min(nwork, sms);
-  kern<<<grid, 160, smem, at::cuda::getCurrentCUDAStream()>>>(mw, mh, a);
+  kern<<<grid, 128 * NG + 32, smem, at::cuda::getCurrentCUDAStream()>>>(mw, mh, a);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
