@@ -97,6 +97,16 @@ __device__ __forceinline__ void seg_atomic_add(double* out, int seg, double v) {
   }
 }
 
+// Atomic += on a double from device code or from an OpenMP loop.
+__host__ __device__ inline void atomic_add_f64(double* p, double v) {
+#ifdef __CUDA_ARCH__
+  atomicAdd(p, v);
+#else
+#pragma omp atomic
+  *p += v;
+#endif
+}
+
 inline void check_same_device(const at::Tensor& a, const at::Tensor& b) {
   TORCH_CHECK(a.device() == b.device(), "tensors must be on the same device");
 }

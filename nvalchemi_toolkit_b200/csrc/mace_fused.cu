@@ -88,7 +88,7 @@ __device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, %
 // TMEM lanes because warp w reaches lanes 32*(w%4)..), keeps its own partial sums and adds them to `mid` with
 // reductions.  Four compute warps alone would leave the SM's schedulers with one warp each.
 template <int LAYER, int GROUP, bool BWD, bool NEED_DU, int NG>
-__global__ void __launch_bounds__(128 * NG + 32, 1) conv_fused_kernel(const __grid_constant__ CUtensorMap tmW,
+__global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __grid_constant__ CUtensorMap tmW,
                                                             const __grid_constant__ CUtensorMap tmH, FusedArgs a) {
   using G = GroupSpec<LAYER, GROUP>;
   constexpr int NIN = G::NIN, NP = G::NP, NACC = G::NACC, NT = G::NT, NMID = G::NMID;
@@ -105,20 +105,20 @@ __global__ void __launch_bounds__(128 * NG + 32, 1) conv_fused_kernel(const __gr
   const uint32_t sA = base, sB = base + A_BYTES;
   const uint32_t bar0 = sB + 2 * B_BYTES;
   const uint32_t a_full = bar0, b_full0 = bar0 + 8, b_empty0 = bar0 + 24, t_full0 = bar0 + 40, t_empty0 = bar0 + 56;
-  const uint32_t tmem_slot = bar0 + 72;
+  constexpr int GR = 4;  // depth of the edge-geometry ring
+  const uint32_t g_full0 = bar0 + 72, g_empty0 = bar0 + 72 + 8 * GR;
+  const uint32_t tmem_slot = bar0 + 72 + 16 * GR;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   // per-tile edge data (generic pointers)
   struct TileEdge {
-    float Y[16]; float n[3]; float rinv; float v[3];
+    float Y[16]; float n[3]; float rinv; float v[3]; float f[3];
     int recv; int j; const float* up; float* dup; float* gpj;
   };
-  TileEdge* te = reinterpret_cast<TileEdge*>(gen + A_BYTES + 2 * B_BYTES + 128);
-  float (*sred)[4][3] = reinterpret_cast<float (*)[4][3]>(reinterpret_cast<uint8_t*>(te) + sizeof(TileEdge) * FT);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(sred) + sizeof(float) * FT * 12);
+  TileEdge* te = reinterpret_cast<TileEdge*>(gen + A_BYTES + 2 * B_BYTES + 256);  // [GR][FT]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(te) + sizeof(TileEdge) * FT * GR);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int MMA_WARP = 4 * NG;
-  constexpr int NCOMP = 128 * NG;
+  constexpr int MMA_WARP = 4 * NG, GEO_WARP = 4 * NG + 1;
   const int nwork = (a.ni + RECV_BLOCK - 1) / RECV_BLOCK;
 
   if (threadIdx.x == 0) {
@@ -127,6 +127,7 @@ __global__ void __launch_bounds__(128 * NG + 32, 1) conv_fused_kernel(const __gr
       mbar_init(b_full0 + 8 * s, 1); mbar_init(b_empty0 + 8 * s, 1);
       mbar_init(t_full0 + 8 * s, 1); mbar_init(t_empty0 + 8 * s, 4 * NG);
     }
+    for (int s = 0; s < GR; ++s) { mbar_init(g_full0 + 8 * s, 1); mbar_init(g_empty0 + 8 * s, 4 * NG); }
     abort_flag[0] = 0;
     abort_flag[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -221,28 +222,42 @@ __global__ void __launch_bounds__(128 * NG + 32, 1) conv_fused_kernel(const __gr
       }
       if (!ok) abort_flag[0] = 1;
     }
-  } else {
-    // ------------------------------------------------------------------ compute warps (thread = channel)
-    const int c = threadIdx.x & 127;
-    const int grp = warp >> 2, wq = warp & 3;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
+  } else if (warp == GEO_WARP) {
+    // ------------------------------------------------------------------ edge geometry producer (runs GR tiles ahead)
     int t = 0;
     bool ok = true;
+    auto flush_forces = [&](int slot) {  // position gradients of a consumed tile: one lane per edge
+      if (BWD && lane < FT) {
+        TileEdge& q = te[slot * FT + lane];
+        if (q.j >= 0) {
+          for (int d = 0; d < 3; ++d) {
+            atomicAdd(q.gpj + d, -q.f[d]);
+            atomicAdd(a.grad_pos + 3 * (int64_t)q.recv + d, q.f[d]);
+          }
+          if (a.virial != nullptr) {
+            double* vp = a.virial + 9 * (int64_t)a.batch_idx[q.recv];
+            for (int x = 0; x < 3; ++x)
+              for (int y = 0; y < 3; ++y) atomicAdd(vp + 3 * x + y, (double)(q.v[x] * q.f[y]));
+          }
+        }
+      }
+    };
     for (int w = blockIdx.x; w < nwork && ok; w += gridDim.x) {
       int wi0 = a.i0 + w * RECV_BLOCK, wi1 = min(wi0 + RECV_BLOCK, a.i0 + a.ni);
       int e0 = a.eptr[wi0], e1 = a.eptr[wi1];
       int nt_w = (e1 - e0 + FT - 1) / FT;
-      int cur = -1;        // receiver whose accumulators are live
-      int next_recv = wi0; // receiver lookup cursor for tile preparation
-      float acc[BWD ? 1 : NACC];
-      float T[BWD ? NT : 1];
+      int next_recv = wi0;
       for (int tt = 0; tt < nt_w && ok; ++tt, ++t) {
-        int s = t & 1;
+        int gs = t & (GR - 1);
+        ok = mbar_wait(g_empty0 + 8 * gs, ((t / GR) & 1) ^ 1, a.err, 16);
+        if (!ok) break;
+        if (t >= GR) flush_forces(gs);
+        __syncwarp();
         int tile_e0 = e0 + tt * FT;
-        // ---- per-edge geometry by the first FT threads
-        if (threadIdx.x < FT) {
-          int e = tile_e0 + threadIdx.x;
-          TileEdge& q = te[threadIdx.x];
+        if (lane < FT) {
+          int e = tile_e0 + lane;
+          TileEdge& q = te[gs * FT + lane];
+          q.f[0] = 0.f; q.f[1] = 0.f; q.f[2] = 0.f;
           if (e < e1) {
             int i = next_recv;
             while (a.eptr[i + 1] <= e) ++i;  // edges are receiver-major: short forward scan
@@ -272,21 +287,48 @@ __global__ void __launch_bounds__(128 * NG + 32, 1) conv_fused_kernel(const __gr
             q.dup = (BWD && NEED_DU) ? dub + jr * NIN * C : nullptr;
             q.gpj = BWD ? gpb + 3 * jr : nullptr;
           } else {
-            q.recv = -1; q.j = -1; q.up = a.u;
+            q.recv = -1; q.j = -1; q.up = a.u; q.dup = nullptr; q.gpj = nullptr;
           }
         }
-        if (threadIdx.x == 0) abort_flag[1] = abort_flag[0];  // snapshot: every compute thread sees the same value
-        compute_bar_sync<NCOMP>();
-        {  // advance the receiver cursor past this tile (same value in every thread)
+        {
           int last = min(tile_e0 + FT, e1) - 1;
           while (a.eptr[next_recv + 1] <= last) ++next_recv;
         }
-        if (abort_flag[1]) { ok = false; break; }
-        ok = mbar_wait(t_full0 + 8 * s, (t >> 1) & 1, a.err, 15);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(g_full0 + 8 * gs);
+      }
+    }
+    // drain: the last (up to GR) tiles still hold unflushed position gradients
+    if (BWD) {
+      int first = t > GR ? t - GR : 0;
+      for (int tl = first; tl < t; ++tl) {
+        if (ok && !mbar_wait(g_empty0 + 8 * (tl & (GR - 1)), (tl / GR) & 1, a.err, 17)) ok = false;
+        if (ok) flush_forces(tl & (GR - 1));
+      }
+    }
+    if (!ok && lane == 0) abort_flag[0] = 1;
+  } else {
+    // ------------------------------------------------------------------ compute warps (thread = channel)
+    const int c = threadIdx.x & 127;
+    const int grp = warp >> 2, wq = warp & 3;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
+    int t = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < nwork && ok; w += gridDim.x) {
+      int wi0 = a.i0 + w * RECV_BLOCK, wi1 = min(wi0 + RECV_BLOCK, a.i0 + a.ni);
+      int e0 = a.eptr[wi0], e1 = a.eptr[wi1];
+      int nt_w = (e1 - e0 + FT - 1) / FT;
+      int cur = -1;  // receiver whose accumulators are live in this warp-group
+      float acc[BWD ? 1 : NACC];
+      float T[BWD ? NT : 1];
+      for (int tt = 0; tt < nt_w && ok; ++tt, ++t) {
+        int s = t & 1, gs = t & (GR - 1);
+        ok = mbar_wait(g_full0 + 8 * gs, (t / GR) & 1, a.err, 18) && mbar_wait(t_full0 + 8 * s, (t >> 1) & 1, a.err, 15);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        TileEdge* tile = te + gs * FT;
         const uint32_t tb = lane_addr + s * TCOLS;
-        // ---- edge loop with the TMEM / global operands of edge n+1 in flight during edge n
+        // edge loop with the TMEM / global operands of this group's next edge in flight during the current one
         float Rn[BWD ? 2 * NP : NP], hn[NIN];
         auto fetch = [&](int n) {
 #pragma unroll
@@ -294,7 +336,7 @@ __global__ void __launch_bounds__(128 * NG + 32, 1) conv_fused_kernel(const __gr
             if (BWD) tmem_ld_x2(tb + p * NROW + 2 * n, Rn[p], Rn[NP + p]);
             else tmem_ld_x1(tb + p * NROW + n, Rn[p]);
           }
-          const float* up = te[n].up + c;
+          const float* up = tile[n].up + c;
 #pragma unroll
           for (int k = 0; k < NIN; ++k) hn[k] = __ldg(up + k * C);
         };
@@ -307,9 +349,9 @@ __global__ void __launch_bounds__(128 * NG + 32, 1) conv_fused_kernel(const __gr
 #pragma unroll
           for (int k = 0; k < NIN; ++k) h[k] = hn[k];
           if (n + NG < FT) fetch(n + NG);
-          const TileEdge& q = te[n];
+          TileEdge& q = tile[n];
           int i = q.recv;
-          if (i != cur) {  // uniform across the CTA
+          if (i != cur) {  // uniform across the warp-group
             if (!BWD && cur >= 0) {
               float* mp = a.mid + (int64_t)cur * NMID * C + c;
 #pragma unroll
@@ -331,61 +373,37 @@ __global__ void __launch_bounds__(128 * NG + 32, 1) conv_fused_kernel(const __gr
           }
           if (!BWD) {
             if (q.j >= 0) G::fwd(h, q.Y, Rv, acc);
-          } else {
-            float f[3] = {0.f, 0.f, 0.f};
-            if (q.j >= 0) {
-              float dh[NIN], dY[16], S[NP];
+          } else if (q.j >= 0) {  // uniform across the warp
+            float dh[NIN], dY[16], S[NP], f[3];
 #pragma unroll
-              for (int k = 0; k < NIN; ++k) dh[k] = 0.f;
+            for (int k = 0; k < NIN; ++k) dh[k] = 0.f;
 #pragma unroll
-              for (int b = 0; b < 16; ++b) dY[b] = 0.f;
-              G::edge(h, q.Y, Rv, T, dh, dY, S);
-              float qq = 0.f;
+            for (int b = 0; b < 16; ++b) dY[b] = 0.f;
+            G::edge(h, q.Y, Rv, T, dh, dY, S);
+            float qq = 0.f;
 #pragma unroll
-              for (int p = 0; p < NP; ++p) qq = fmaf(S[p], Rd[p], qq);
-              float gy[3], sdot;
-              sh_l3_vjp(q.n[0], q.n[1], q.n[2], q.Y, dY, gy, sdot);
+            for (int p = 0; p < NP; ++p) qq = fmaf(S[p], Rd[p], qq);
+            float gy[3], sdot;
+            sh_l3_vjp(q.n[0], q.n[1], q.n[2], q.Y, dY, gy, sdot);
 #pragma unroll
-              for (int d = 0; d < 3; ++d) f[d] = (gy[d] - sdot * q.n[d]) * q.rinv + qq * q.n[d];
-              if (NEED_DU) {
-                float* dp = q.dup + c;
+            for (int d = 0; d < 3; ++d) f[d] = (gy[d] - sdot * q.n[d]) * q.rinv + qq * q.n[d];
+            if (NEED_DU) {
+              float* dp = q.dup + c;
 #pragma unroll
-                for (int k = 0; k < NIN; ++k) atomicAdd(dp + k * C, dh[k]);
-              }
+              for (int k = 0; k < NIN; ++k) atomicAdd(dp + k * C, dh[k]);
             }
 #pragma unroll
             for (int d = 0; d < 3; ++d) {
               float x = f[d];
               for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
-              if (lane == 0) sred[n][wq][d] = x;
+              if (lane == 0) atomicAdd(&q.f[d], x);  // shared-memory reduction over the four warps of the group
             }
           }
         }
-        // all TMEM reads of this buffer are complete (every load was waited for): hand it back to the MMA warp
+        // every TMEM load of this buffer was waited for: hand the buffer and the geometry slot back
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(t_empty0 + 8 * s);
-        if (BWD) {
-          compute_bar_sync<NCOMP>();
-          if (threadIdx.x < FT) {
-            const TileEdge& q = te[threadIdx.x];
-            if (q.j >= 0) {
-              float f[3] = {0.f, 0.f, 0.f};
-              for (int ww = 0; ww < 4; ++ww)
-                for (int d = 0; d < 3; ++d) f[d] += sred[threadIdx.x][ww][d];
-              for (int d = 0; d < 3; ++d) {
-                atomicAdd(q.gpj + d, -f[d]);
-                atomicAdd(a.grad_pos + 3 * (int64_t)q.recv + d, f[d]);
-              }
-              if (a.virial != nullptr) {
-                double* vp = a.virial + 9 * (int64_t)a.batch_idx[q.recv];
-                for (int x = 0; x < 3; ++x)
-                  for (int y = 0; y < 3; ++y) atomicAdd(vp + 3 * x + y, (double)(q.v[x] * f[y]));
-              }
-            }
-          }
-        }
-        compute_bar_sync<NCOMP>();  // tile edge data may be overwritten
+        if (lane == 0) { mbar_arrive(t_empty0 + 8 * s); mbar_arrive(g_empty0 + 8 * gs); }
       }
       if (!BWD && cur >= 0 && ok) {
         float* mp = a.mid + (int64_t)cur * NMID * C + c;
@@ -431,7 +449,7 @@ template <int LAYER, int GROUP, bool BWD, bool NEED_DU>
 static void launch_fused(const CUtensorMap& mw, const CUtensorMap& mh, const FusedArgs& a, int sms) {
   using G = GroupSpec<LAYER, GROUP>;
   constexpr int NROW = BWD ? 2 * FT : FT;
-  size_t smem = (size_t)G::NP * 2 * 128 * 128 + 2 * (2 * NROW * 128) + 128 + FT * 160 + FT * 48 + 64 + 1024 + 256;
+  size_t smem = (size_t)G::NP * 2 * 128 * 128 + 2 * (2 * NROW * 128) + 256 + 4 * FT * 160 + 64 + 1024 + 256;
   constexpr int NG = BWD ? 3 : 4;
   auto kern = conv_fused_kernel<LAYER, GROUP, BWD, NEED_DU, NG>;
   static bool configured = false;
@@ -441,7 +459,7 @@ static void launch_fused(const CUtensorMap& mw, const CUtensorMap& mh, const Fus
   }
   int nwork = (a.ni + RECV_BLOCK - 1) / RECV_BLOCK;
   int grid = std::min(nwork, sms);
-  kern<<<grid, 128 * NG + 32, smem, at::cuda::getCurrentCUDAStream()>>>(mw, mh, a);
+  kern<<<grid, 128 * NG + 64, smem, at::cuda::getCurrentCUDAStream()>>>(mw, mh, a);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

@@ -65,16 +65,7 @@ std::tuple<Tensor, Tensor, Tensor> lj_energy_forces(const Tensor& pos, const Ten
         double gx = de * dx / rr, gy = de * dy / rr, gz = de * dz / rr;  // dE_pair/d(r_j - r_i)
         fx += gx; fy += gy; fz += gz;  // F_i = +grad w.r.t. the displacement
         if (half_list) {
-#ifdef __CUDA_ARCH__
-          atomicAdd(F + 3 * j, -gx); atomicAdd(F + 3 * j + 1, -gy); atomicAdd(F + 3 * j + 2, -gz);
-#else
-#pragma omp atomic
-          F[3 * j] -= gx;
-#pragma omp atomic
-          F[3 * j + 1] -= gy;
-#pragma omp atomic
-          F[3 * j + 2] -= gz;
-#endif
+          atomic_add_f64(F + 3 * j, -gx); atomic_add_f64(F + 3 * j + 1, -gy); atomic_add_f64(F + 3 * j + 2, -gz);
         }
         // virial W = -dE/d(strain) = -sum_pairs d (x) dE/dd ; full lists see every pair twice
         double d[3] = {dx, dy, dz}, g[3] = {gx, gy, gz};
@@ -82,21 +73,8 @@ std::tuple<Tensor, Tensor, Tensor> lj_energy_forces(const Tensor& pos, const Ten
           for (int c = 0; c < 3; ++c) vir[3 * a + c] -= wgt * d[a] * g[c];
       }
       E[i] = ei;
-#ifdef __CUDA_ARCH__
-      atomicAdd(F + 3 * i, fx); atomicAdd(F + 3 * i + 1, fy); atomicAdd(F + 3 * i + 2, fz);
-      for (int a = 0; a < 9; ++a) atomicAdd(W + 9 * s + a, vir[a]);
-#else
-#pragma omp atomic
-      F[3 * i] += fx;
-#pragma omp atomic
-      F[3 * i + 1] += fy;
-#pragma omp atomic
-      F[3 * i + 2] += fz;
-      for (int a = 0; a < 9; ++a) {
-#pragma omp atomic
-        W[9 * s + a] += vir[a];
-      }
-#endif
+      atomic_add_f64(F + 3 * i, fx); atomic_add_f64(F + 3 * i + 1, fy); atomic_add_f64(F + 3 * i + 2, fz);
+      for (int a = 0; a < 9; ++a) atomic_add_f64(W + 9 * s + a, vir[a]);
     });
   });
   return {e.to(pos.scalar_type()), f.to(pos.scalar_type()), w.to(pos.scalar_type())};

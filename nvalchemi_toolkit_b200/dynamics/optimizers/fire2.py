@@ -93,8 +93,8 @@ class _CellFilterMixin:
         vol = torch.linalg.det(cell).abs()
         n_at = batch.num_nodes_per_graph.to(cell.dtype)
         factor = n_at if self.cell_factor is None else torch.full_like(n_at, self.cell_factor)
-        # dE/dcell = V * inv(cell)^T... in strain form: force on the cell rows = V * (cell @ sigma) / factor
-        cell_force = (vol[:, None, None] * torch.matmul(cell, stress)) / factor[:, None, None]
+        # dE/d(strain) = V sigma (sigma tensile positive), so the generalised force on the cell rows is -V cell @ sigma
+        cell_force = -(vol[:, None, None] * torch.matmul(cell, stress)) / factor[:, None, None]
         frac = torch.einsum("ni,nij->nj", batch.positions, torch.linalg.inv(cell)[batch.batch_idx.long()])
         old_cell = cell.clone()
         step_fn(cell_force)
