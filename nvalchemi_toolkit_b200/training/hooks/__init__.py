@@ -1,0 +1,10 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Training hooks (reference ``nvalchemi/training/hooks``)."""
+from nvalchemi_toolkit_b200.training.hooks.library import (
+    CheckpointHook, DDPHook, EMAHook, FusedGradAllReduceHook, GradientAccumulationHook, GradientClipHook,
+    LossSpikeSkipHook, MixedPrecisionHook, ModulePatchHook, TrainableParameterHook, TrainingUpdateOrchestrator,
+)
+
+__all__ = ["CheckpointHook", "DDPHook", "EMAHook", "FusedGradAllReduceHook", "GradientAccumulationHook",
+           "GradientClipHook", "LossSpikeSkipHook", "MixedPrecisionHook", "ModulePatchHook", "TrainableParameterHook",
+           "TrainingUpdateOrchestrator"]

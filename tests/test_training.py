@@ -1,0 +1,149 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Training loop: stage order, losses, update hooks, checkpoints/resume, data-parallel gradient all-reduce (gloo)."""
+import os
+
+import pytest
+import torch
+
+from nvalchemi_toolkit_b200 import Batch
+from nvalchemi_toolkit_b200.models import DemoModelWrapper
+from nvalchemi_toolkit_b200.training import (ComposedLossFunction, EnergyMSELoss, ForceMSELoss, LinearWeight,
+                                             OptimizerConfig, TrainingStage, TrainingStrategy, ValidationConfig)
+from nvalchemi_toolkit_b200.training.hooks import (CheckpointHook, EMAHook, FusedGradAllReduceHook,
+                                                   GradientAccumulationHook, GradientClipHook, LossSpikeSkipHook,
+                                                   TrainableParameterHook)
+from tests.helpers import random_molecule
+
+
+def _dataset(n=12, seed=0):
+    torch.manual_seed(seed)
+    teacher = DemoModelWrapper()
+    out = []
+    for i in range(n):
+        d = random_molecule(6 + i % 3, seed * 100 + i)
+        b = Batch.from_data_list([d])
+        o = teacher(b)
+        d.__dict__["energy"] = o["energy"].detach().reshape(1, 1)
+        d.__dict__["forces"] = o["forces"].detach()
+        out.append(d)
+    return out
+
+
+def _loader(data, bs=4):
+    return [Batch.from_data_list(data[i:i + bs]) for i in range(0, len(data), bs)]
+
+
+def _strategy(**kw):
+    torch.manual_seed(1)
+    loss = EnergyMSELoss() + 10.0 * ForceMSELoss()
+    if "num_steps" not in kw:
+        kw.setdefault("num_epochs", 2)
+    return TrainingStrategy(DemoModelWrapper(), OptimizerConfig(kwargs={"lr": 3e-3}), loss, devices=["cpu"], **kw)
+
+
+class Recorder:
+    frequency = 1
+
+    def __init__(self):
+        self.stage, self.seen = None, []
+
+    def _runs_on_stage(self, stage):
+        return stage not in (TrainingStage.DO_BACKWARD, TrainingStage.DO_OPTIMIZER_STEP)
+
+    def __call__(self, ctx, stage):
+        self.seen.append(stage)
+
+
+def test_loss_decreases_and_stage_order():
+    rec = Recorder()
+    st = _strategy(num_epochs=15, hooks=[rec, GradientClipHook(5.0)])
+    loader = _loader(_dataset())
+    st.train_batch(loader[0])
+    first = float(st.last_losses["total_loss"])
+    per_batch = [s for s in rec.seen if s not in (TrainingStage.SETUP,)]
+    names = [s.name for s in per_batch]
+    assert names == ["BEFORE_BATCH", "BEFORE_FORWARD", "AFTER_FORWARD", "BEFORE_LOSS", "AFTER_LOSS", "BEFORE_BACKWARD",
+                     "AFTER_BACKWARD", "BEFORE_OPTIMIZER_STEP", "AFTER_OPTIMIZER_STEP", "AFTER_BATCH"]
+    st.run(loader)
+    assert float(st.last_losses["total_loss"]) < 0.5 * first
+    assert st.epoch_count == 15 and st.step_count == 15 * 3  # the manual batch counted as the first of epoch 0
+
+
+def test_loss_composition_and_schedules():
+    l = EnergyMSELoss(weight=LinearWeight(0.0, 1.0, 10)) + 2.0 * ForceMSELoss()
+    assert isinstance(l, ComposedLossFunction) and len(l.terms) == 2
+    assert l.terms[0].weight_at(5, 0) == pytest.approx(0.5) and l.terms[1].weight_at(0, 0) == 2.0
+    spec = l.to_spec()
+    l2 = ComposedLossFunction.from_spec(spec)
+    assert l2.terms[0].weight_at(10, 0) == pytest.approx(1.0) and l2.required_predictions() == {"energy", "forces"}
+
+
+def test_accumulation_and_spike_skip():
+    st = _strategy(num_steps=4, hooks=[GradientAccumulationHook(2), LossSpikeSkipHook(factor=1e9)])
+    loader = _loader(_dataset(), bs=2)
+    st.run(loader)
+    assert st.step_count == 4 and st.batch_count == 8
+
+
+def test_checkpoint_resume_reproduces_run(tmp_path):
+    data = _dataset()
+    loader = _loader(data)
+    ref = _strategy(num_epochs=2, hooks=[EMAHook(decay=0.9)])
+    ref.run(loader)
+    a = _strategy(num_epochs=1, hooks=[EMAHook(decay=0.9), CheckpointHook(tmp_path / "ck", every_n_epochs=1)])
+    a.run(loader)
+    assert (tmp_path / "ck" / "manifest.json").exists() and (tmp_path / "ck" / "models" / "main" / "spec.json").exists()
+    b = _strategy(num_epochs=2, hooks=[EMAHook(decay=0.9)])
+    b.load_checkpoint(tmp_path / "ck")
+    assert b.epoch_count == 1 and b.step_count == 3
+    b.run(loader)
+    for p, q in zip(ref.models["main"].parameters(), b.models["main"].parameters()):
+        assert torch.allclose(p, q, atol=1e-6)
+    assert b.step_count == ref.step_count == 6
+
+
+def test_validation_and_trainable_filter():
+    data = _dataset()
+    st = _strategy(num_epochs=1, validation_config=ValidationConfig(data=_loader(data[:4]), every_n_epochs=1),
+                   hooks=[TrainableParameterHook([r"projection"])])
+    st.run(_loader(data))
+    assert st.last_validation is not None and "total_loss" in st.last_validation and st.last_validation["num_graphs"] == 4
+    frozen = [n for n, p in st.models["main"].named_parameters() if not p.requires_grad]
+    assert frozen and all("projection" not in n for n in frozen)
+
+
+def _dp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        data = _dataset(8)
+        st = _strategy(num_steps=3, hooks=[FusedGradAllReduceHook()])
+        for step in range(3):  # rank r, step s: graphs [4 (s % 2) + 2 r, +2): equal counts per rank
+            lo = 4 * (step % 2) + 2 * rank
+            st.train_batch(Batch.from_data_list(data[lo: lo + 2]))
+        q.put((rank, [p.detach().reshape(-1).tolist() for p in st.models["main"].parameters()]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fused_gradient_allreduce_matches_single_process():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_dp_worker, args=(r, 2, 29588, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+    for a, b in zip(res[0], res[1]):
+        assert torch.allclose(torch.tensor(a), torch.tensor(b), atol=1e-7)  # ranks stay in lock-step
+    data = _dataset(8)
+    st = _strategy(num_steps=3)
+    for step in range(3):
+        st.train_batch(Batch.from_data_list(data[4 * (step % 2): 4 * (step % 2) + 4]))
+    for a, b in zip(res[0], st.models["main"].parameters()):
+        assert torch.allclose(torch.tensor(a), b.detach().reshape(-1), atol=5e-3)  # Adam amplifies rounding of tiny gradients
