@@ -1,0 +1,293 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Datapipes: readers, datasets with prefetch, a batching dataloader, multi-dataset sampling, transforms.
+
+Reference: ``nvalchemi/data/datapipes/{backends/base,dataset,dataloader,multidataset,in_memory_dataset,samplers}.py`` and
+``data/transforms/compose.py``.  A ``Reader`` returns raw dictionaries of tensors plus metadata; ``Dataset`` turns them
+into ``AtomicData`` (or keeps them raw for ``Batch.from_raw_dicts``), prefetching with a thread pool and, on CUDA, a side
+stream; ``DataLoader`` assembles ``Batch`` objects, reads several batches per window (``prefetch_factor``), supports
+``set_epoch`` (shuffle seed), ``set_epoch_step`` (mid-epoch resume) and ``set_distributed`` (rank sharding)."""
+from __future__ import annotations
+
+import abc
+import concurrent.futures as cf
+import math
+from typing import Any, Callable, Iterator, Sequence
+
+import torch
+
+from nvalchemi_toolkit_b200.data.atomic_data import AtomicData
+from nvalchemi_toolkit_b200.data.batch import Batch
+
+
+class Reader(abc.ABC):
+    """Random-access source of samples."""
+
+    @abc.abstractmethod
+    def __len__(self) -> int: ...
+
+    @abc.abstractmethod
+    def read(self, idx: int) -> tuple[dict[str, torch.Tensor], dict[str, Any]]: ...
+
+    def read_many(self, indices: Sequence[int]) -> list[tuple[dict[str, torch.Tensor], dict[str, Any]]]:
+        return [self.read(i) for i in indices]
+
+    @property
+    def field_levels(self) -> dict[str, str]:
+        return {}
+
+    def get_metadata(self, idx: int) -> tuple[int, int]:
+        d, m = self.read(idx)
+        return int(d["positions"].shape[0]), int(m.get("num_edges", 0))
+
+
+class Compose:
+    """Chain of ``(data, meta) -> (data, meta)`` transforms."""
+
+    def __init__(self, transforms: Sequence[Callable]) -> None:
+        self.transforms = list(transforms)
+
+    def __call__(self, data: Any, meta: dict[str, Any]) -> tuple[Any, dict[str, Any]]:
+        for t in self.transforms:
+            data, meta = t(data, meta)
+        return data, meta
+
+    def __add__(self, other: "Compose | Callable") -> "Compose":
+        return Compose(self.transforms + (other.transforms if isinstance(other, Compose) else [other]))
+
+    def __len__(self) -> int:
+        return len(self.transforms)
+
+
+def _to_atomic_data(d: dict[str, torch.Tensor], levels: dict[str, str]) -> AtomicData:
+    known = {k: v for k, v in d.items() if k in AtomicData.model_fields}
+    data = AtomicData(**known)
+    for k, v in d.items():
+        if k in known:
+            continue
+        lvl = levels.get(k, "node")
+        {"node": data.add_node_property, "edge": data.add_edge_property, "system": data.add_system_property}[lvl](k, v)
+    return data
+
+
+class Dataset:
+    """Samples as ``(AtomicData, metadata)``; implements the sampler protocol (``get_metadata``)."""
+
+    def __init__(self, reader: Reader, transform: Callable | None = None, device: str | torch.device = "cpu",
+                 num_workers: int = 2, raw: bool = False) -> None:
+        self.reader, self.transform, self.device, self.raw = reader, transform, torch.device(device), raw
+        self._pool = cf.ThreadPoolExecutor(max_workers=max(1, num_workers))
+        self._stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+
+    def __len__(self) -> int:
+        return len(self.reader)
+
+    def get_metadata(self, idx: int) -> tuple[int, int]:
+        return self.reader.get_metadata(idx)
+
+    def _finish(self, d: dict[str, torch.Tensor], meta: dict[str, Any]) -> tuple[Any, dict[str, Any]]:
+        if self._stream is not None:
+            with torch.cuda.stream(self._stream):
+                d = {k: v.pin_memory().to(self.device, non_blocking=True) for k, v in d.items()}
+            meta = {**meta, "_event": self._stream.record_event()}
+        item: Any = d if self.raw else _to_atomic_data(d, self.reader.field_levels)
+        if self.transform is not None:
+            item, meta = self.transform(item, meta)
+        return item, meta
+
+    def __getitem__(self, idx: int) -> tuple[Any, dict[str, Any]]:
+        return self._finish(*self.reader.read(idx))
+
+    def fetch(self, indices: Sequence[int]) -> "cf.Future[list[tuple[Any, dict[str, Any]]]]":
+        """Asynchronous fused read of several samples (one reader window)."""
+        return self._pool.submit(lambda: [self._finish(d, m) for d, m in self.reader.read_many(list(indices))])
+
+
+class InMemoryDataset(Dataset):
+    """Dataset over a list of ``AtomicData`` kept in memory (optionally resident on the device)."""
+
+    class _ListReader(Reader):
+        def __init__(self, items: Sequence[AtomicData]) -> None:
+            self.items = list(items)
+
+        def __len__(self) -> int:
+            return len(self.items)
+
+        def read(self, idx: int) -> tuple[dict[str, torch.Tensor], dict[str, Any]]:
+            d = self.items[idx]
+            return d._tensor_items(), {"index": idx, "num_atoms": d.num_nodes, "num_edges": d.num_edges}
+
+        def get_metadata(self, idx: int) -> tuple[int, int]:
+            return self.items[idx].num_nodes, self.items[idx].num_edges
+
+    def __init__(self, items: Sequence[AtomicData], transform: Callable | None = None,
+                 device: str | torch.device = "cpu") -> None:
+        items = [d.to(device) for d in items] if torch.device(device).type != "cpu" else list(items)
+        super().__init__(self._ListReader(items), transform=transform, device="cpu", num_workers=1)
+        self.items = items
+
+    def __getitem__(self, idx: int) -> tuple[Any, dict[str, Any]]:
+        item, meta = self.items[idx].clone(), {"index": idx}
+        return self.transform(item, meta) if self.transform is not None else (item, meta)
+
+    @classmethod
+    def from_dataset(cls, ds: Dataset, device: str | torch.device = "cpu") -> "InMemoryDataset":
+        return cls([ds[i][0] for i in range(len(ds))], device=device)
+
+
+class MultiDataset:
+    """Concatenation of datasets with per-dataset sampling weights."""
+
+    def __init__(self, datasets: Sequence[Dataset], weights: Sequence[float] | None = None) -> None:
+        self.datasets = list(datasets)
+        self.weights = list(weights) if weights is not None else [1.0] * len(self.datasets)
+        self.offsets = [0]
+        for d in self.datasets:
+            self.offsets.append(self.offsets[-1] + len(d))
+
+    def __len__(self) -> int:
+        return self.offsets[-1]
+
+    def locate(self, idx: int) -> tuple[int, int]:
+        for k in range(len(self.datasets)):
+            if idx < self.offsets[k + 1]:
+                return k, idx - self.offsets[k]
+        raise IndexError(idx)
+
+    def __getitem__(self, idx: int) -> tuple[Any, dict[str, Any]]:
+        k, j = self.locate(idx)
+        item, meta = self.datasets[k][j]
+        return item, {**meta, "dataset": k}
+
+    def get_metadata(self, idx: int) -> tuple[int, int]:
+        k, j = self.locate(idx)
+        return self.datasets[k].get_metadata(j)
+
+
+class MultiDatasetSampler:
+    """Draws ``num_samples`` global indices: dataset by weight, then uniformly inside it; shards over ranks."""
+
+    def __init__(self, multi: MultiDataset, num_samples: int | None = None, seed: int = 0, rank: int = 0,
+                 world_size: int = 1) -> None:
+        self.multi, self.seed, self.rank, self.world_size, self.epoch = multi, seed, rank, world_size, 0
+        self.num_samples = num_samples if num_samples is not None else len(multi)
+
+    def set_epoch(self, epoch: int) -> None:
+        self.epoch = epoch
+
+    def __len__(self) -> int:
+        return math.ceil(self.num_samples / self.world_size)
+
+    def __iter__(self) -> Iterator[int]:
+        g = torch.Generator().manual_seed(self.seed + self.epoch)
+        w = torch.tensor(self.multi.weights, dtype=torch.float64)
+        which = torch.multinomial(w / w.sum(), self.num_samples, replacement=True, generator=g)
+        sizes = torch.tensor([len(d) for d in self.multi.datasets])
+        inner = (torch.rand(self.num_samples, generator=g) * sizes[which]).long()
+        idx = (torch.tensor(self.multi.offsets[:-1])[which] + inner).tolist()
+        return iter(idx[self.rank:: self.world_size])
+
+
+class MultiDatasetBatchSampler:
+    """Batches of indices from a :class:`MultiDatasetSampler`."""
+
+    def __init__(self, sampler: MultiDatasetSampler, batch_size: int, drop_last: bool = False) -> None:
+        self.sampler, self.batch_size, self.drop_last = sampler, batch_size, drop_last
+
+    def set_epoch(self, epoch: int) -> None:
+        self.sampler.set_epoch(epoch)
+
+    def __iter__(self) -> Iterator[list[int]]:
+        buf: list[int] = []
+        for i in self.sampler:
+            buf.append(i)
+            if len(buf) == self.batch_size:
+                yield buf
+                buf = []
+        if buf and not self.drop_last:
+            yield buf
+
+    def __len__(self) -> int:
+        n = len(self.sampler)
+        return n // self.batch_size if self.drop_last else math.ceil(n / self.batch_size)
+
+
+class DataLoader:
+    """Yields ``Batch`` objects; reads ``prefetch_factor`` batches per window ahead of consumption."""
+
+    def __init__(self, dataset: Any, batch_size: int = 1, shuffle: bool = False, drop_last: bool = False,
+                 prefetch_factor: int = 2, seed: int = 0, batch_sampler: Any = None,
+                 device: str | torch.device | None = None) -> None:
+        self.dataset, self.batch_size, self.shuffle, self.drop_last = dataset, batch_size, shuffle, drop_last
+        self.prefetch_factor, self.seed, self.batch_sampler = max(1, prefetch_factor), seed, batch_sampler
+        self.device = torch.device(device) if device is not None else None
+        self.epoch, self.start_step = 0, 0
+        self.rank, self.world_size = 0, 1
+
+    def set_epoch(self, epoch: int) -> None:
+        self.epoch = epoch
+        if self.batch_sampler is not None and hasattr(self.batch_sampler, "set_epoch"):
+            self.batch_sampler.set_epoch(epoch)
+
+    def set_epoch_step(self, step: int) -> None:
+        """Skip the first ``step`` batches of the next iteration (resume in the middle of an epoch)."""
+        self.start_step = int(step)
+
+    def set_distributed(self, rank: int, world_size: int) -> None:
+        self.rank, self.world_size = rank, world_size
+
+    def _batches(self) -> list[list[int]]:
+        if self.batch_sampler is not None:
+            return list(self.batch_sampler)
+        n = len(self.dataset)
+        order = torch.randperm(n, generator=torch.Generator().manual_seed(self.seed + self.epoch)).tolist() \
+            if self.shuffle else list(range(n))
+        if self.world_size > 1:
+            per = math.ceil(n / self.world_size)
+            order = (order + order[: per * self.world_size - n])[self.rank:: self.world_size]
+        out = [order[i: i + self.batch_size] for i in range(0, len(order), self.batch_size)]
+        if self.drop_last and out and len(out[-1]) < self.batch_size:
+            out.pop()
+        return out
+
+    def __len__(self) -> int:
+        return len(self._batches())
+
+    def _collate(self, items: list[tuple[Any, dict[str, Any]]]) -> Batch:
+        for _, m in items:
+            ev = m.get("_event") if isinstance(m, dict) else None
+            if ev is not None:
+                torch.cuda.current_stream().wait_event(ev)
+        first = items[0][0]
+        if isinstance(first, dict):
+            levels = getattr(getattr(self.dataset, "reader", None), "field_levels", {})
+            b = Batch.from_raw_dicts([it for it, _ in items], field_levels=levels)
+        else:
+            b = Batch.from_data_list([it for it, _ in items])
+        return b.to(self.device, non_blocking=True) if self.device is not None else b
+
+    def __iter__(self) -> Iterator[Batch]:
+        batches = self._batches()[self.start_step:]
+        self.start_step = 0
+        fetch = getattr(self.dataset, "fetch", None)
+        if fetch is None:
+            for idx in batches:
+                yield self._collate([self.dataset[i] for i in idx])
+            return
+        pending: list[Any] = []
+        it = iter(batches)
+
+        def submit() -> None:
+            window = [b for b in (next(it, None) for _ in range(self.prefetch_factor)) if b is not None]
+            if window:
+                flat = [i for b in window for i in b]
+                pending.append((window, fetch(flat)))
+
+        submit()
+        while pending:
+            window, fut = pending.pop(0)
+            submit()  # the next window is read while this one is consumed
+            items = fut.result()
+            pos = 0
+            for b in window:
+                yield self._collate(items[pos: pos + len(b)])
+                pos += len(b)

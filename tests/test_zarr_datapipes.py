@@ -1,0 +1,111 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Zarr v3 store layout, append / delete / defragment, coalesced reads, datapipes and the IO CLI."""
+import json
+
+import pytest
+import torch
+
+from nvalchemi_toolkit_b200 import Batch
+from nvalchemi_toolkit_b200.data.datapipes import (Compose, DataLoader, Dataset, InMemoryDataset, MultiDataset,
+                                                   MultiDatasetBatchSampler, MultiDatasetSampler)
+from nvalchemi_toolkit_b200.data.zarr_store import (AtomicDataZarrReader, AtomicDataZarrWriter, ZarrArray, ZarrArrayConfig,
+                                                    ZarrWriteConfig)
+from nvalchemi_toolkit_b200.dynamics.sampler import SizeAwareSampler
+from nvalchemi_toolkit_b200.dynamics.sinks import ZarrData
+from tests.helpers import random_molecule
+
+
+def _data(n=7):
+    return [random_molecule(3 + i, i, n_edges=2 + i, periodic=True) for i in range(n)]
+
+
+@pytest.mark.parametrize("compressor", [None, "gzip"])
+def test_store_layout_and_roundtrip(tmp_path, compressor):
+    data = _data()
+    cfg = ZarrWriteConfig(core=ZarrArrayConfig(chunk_rows=8, compressor=compressor))
+    w = AtomicDataZarrWriter(tmp_path / "s.zarr", cfg)
+    w.append(Batch.from_data_list(data[:4]))
+    w.append(Batch.from_data_list(data[4:]))
+    root = json.loads((tmp_path / "s.zarr" / "zarr.json").read_text())
+    assert root["zarr_format"] == 3 and root["attributes"]["num_samples"] == 7
+    assert root["attributes"]["fields"]["core"]["positions"] == "atom"
+    assert root["attributes"]["fields"]["core"]["cell"] == "system"
+    meta = json.loads((tmp_path / "s.zarr" / "core" / "cell" / "zarr.json").read_text())
+    assert meta["shape"] == [7, 3, 3] and meta["codecs"][0]["name"] == "bytes"
+    assert ZarrArray(tmp_path / "s.zarr" / "meta" / "atoms_ptr").read().tolist()[:3] == [0, 3, 7]
+    r = AtomicDataZarrReader(tmp_path / "s.zarr")
+    assert len(r) == 7 and r.get_metadata(2) == (5, 4)
+    for i in (0, 3, 6):
+        d, m = r.read(i)
+        assert torch.allclose(d["positions"], data[i].positions) and torch.equal(d["neighbor_list"], data[i].neighbor_list)
+        assert d["cell"].shape == (1, 3, 3)
+    many = r.read_many([1, 4, 5])
+    assert torch.allclose(many[1][0]["positions"], data[4].positions)
+
+
+def test_delete_defragment_and_custom(tmp_path):
+    data = _data()
+    w = AtomicDataZarrWriter(tmp_path / "s.zarr")
+    w.append(Batch.from_data_list(data))
+    w.add_custom("labels", torch.arange(7), level="system")
+    w.delete([1, 5])
+    r = AtomicDataZarrReader(tmp_path / "s.zarr")
+    assert len(r) == 5 and torch.allclose(r.read(1)[0]["positions"], data[2].positions)
+    assert r.read_custom("labels").tolist() == list(range(7))
+    w.defragment()
+    r.refresh()
+    assert r.num_total == 5 and torch.allclose(r.read(4)[0]["positions"], data[6].positions)
+
+
+def test_dataloader_epochs_resume_and_sharding(tmp_path):
+    data = _data(10)
+    w = AtomicDataZarrWriter(tmp_path / "s.zarr")
+    w.append(Batch.from_data_list(data))
+    ds = Dataset(AtomicDataZarrReader(tmp_path / "s.zarr"), transform=Compose([lambda d, m: (d, {**m, "seen": True})]))
+    item, meta = ds[2]
+    assert meta["seen"] and item.num_nodes == 5
+    dl = DataLoader(ds, batch_size=4, shuffle=True, seed=3, prefetch_factor=2)
+    dl.set_epoch(0)
+    sizes0 = [b.num_nodes for b in dl]
+    dl.set_epoch(0)
+    assert [b.num_nodes for b in dl] == sizes0 and len(dl) == 3
+    dl.set_epoch(1)
+    dl.set_epoch(0)
+    dl.set_epoch_step(2)
+    assert [b.num_nodes for b in dl] == sizes0[2:]
+    a, b = DataLoader(ds, batch_size=2), DataLoader(ds, batch_size=2)
+    a.set_distributed(0, 2)
+    b.set_distributed(1, 2)
+    assert sum(x.num_graphs for x in a) == sum(x.num_graphs for x in b) == 5
+    raw = DataLoader(Dataset(AtomicDataZarrReader(tmp_path / "s.zarr"), raw=True), batch_size=5)
+    first = next(iter(raw))
+    assert first.num_graphs == 5 and first.cell.shape == (5, 3, 3)
+
+
+def test_multidataset_sampler_and_inflight_sampler():
+    a, b = InMemoryDataset(_data(4)), InMemoryDataset(_data(6))
+    multi = MultiDataset([a, b], weights=[1.0, 3.0])
+    assert len(multi) == 10 and multi[5][1]["dataset"] == 1
+    s = MultiDatasetSampler(multi, num_samples=400, seed=1)
+    idx = list(s)
+    frac_b = sum(1 for i in idx if i >= 4) / len(idx)
+    assert 0.6 < frac_b < 0.9
+    bs = MultiDatasetBatchSampler(MultiDatasetSampler(multi, num_samples=10, rank=0, world_size=2), batch_size=2)
+    assert len(list(bs)) == len(bs) == 3
+    dl = DataLoader(multi, batch_sampler=bs)
+    assert sum(x.num_graphs for x in dl) == 5
+    sampler = SizeAwareSampler(a, max_atoms=12, max_batch_size=3)
+    assert sampler.build_initial_batch().num_nodes <= 12
+
+
+def test_zarr_sink_and_cli(tmp_path):
+    sink = ZarrData(tmp_path / "sink.zarr")
+    batch = Batch.from_data_list(_data(3))
+    sink.write(batch, mask=torch.tensor([True, False, True]))
+    assert len(sink) == 2 and sink.read().num_graphs == 2
+    from nvalchemi_toolkit_b200.data import io_test
+
+    res = io_test.main(["roundtrip", "--samples", "400", "--store", str(tmp_path), "--compressor", "gzip", "--chunk-rows", "4096"])
+    assert res["roundtrip_ok"] and res["compression_ratio"] > 1.0
+    res2 = io_test.main(["read", res["store"]])
+    assert res2["samples"] == 400
