@@ -1,0 +1,49 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Domain-decomposition configuration (reference ``nvalchemi/distributed/config.py:31-173``)."""
+from __future__ import annotations
+
+from enum import Enum
+from typing import Any
+
+from pydantic import BaseModel, ConfigDict, model_validator
+
+
+class StrategyKind(str, Enum):
+    HALO = "halo"
+    GRAPH_PARTITION = "graph_partition"
+
+
+class HookScope(str, Enum):
+    """Where a dynamics hook runs under domain decomposition: on each rank's local atoms, on the gathered global
+    batch (every rank), or on the gathered batch of rank 0 only."""
+
+    LOCAL = "local"
+    GLOBAL = "global"
+    RANK_ZERO = "rank_zero"
+
+
+class DomainConfig(BaseModel):
+    model_config = ConfigDict(arbitrary_types_allowed=True)
+    cutoff: float
+    skin: float = 0.0
+    ghost_width: float | None = None          # None -> cutoff + skin (times the model's number of message passes)
+    strategy: StrategyKind = StrategyKind.HALO
+    compile: bool = False                      # accepted for API parity; kernels are hand-written, nothing is traced
+    require_nondegenerate: bool = True
+    mesh: Any = None
+    mesh_dim: str = "domain"
+    grid_dims: tuple[int, int, int] | None = None
+    scripted_marshal: bool = False
+    migration_hysteresis: float | None = None  # None -> skin / 2; must stay below skin
+
+    @model_validator(mode="after")
+    def _defaults(self) -> "DomainConfig":
+        if self.cutoff <= 0:
+            raise ValueError("cutoff must be positive")
+        if self.ghost_width is None:
+            self.__dict__["ghost_width"] = self.cutoff + self.skin
+        if self.migration_hysteresis is None:
+            self.__dict__["migration_hysteresis"] = 0.5 * self.skin
+        if self.skin > 0 and not self.migration_hysteresis < self.skin:
+            raise ValueError("migration_hysteresis must be smaller than skin")
+        return self

@@ -1,0 +1,93 @@
+# SPDX-License-Identifier: Apache-2.0
+"""``DistributedModel``: evaluates any ``BaseModelMixin`` wrapper on a :class:`ShardedBatch`.
+
+Reference: ``nvalchemi/distributed/distributed_model.py:120-380`` and ``output_consolidation.py`` (reverse-halo force
+correction, sums of per-system quantities).  The model runs unchanged on the padded (owned + ghost) cluster; the spec
+selects how results are consolidated:
+
+* ``DIRECT_MASKED``: ghost rows get an empty neighbour list; owned rows are complete as computed.
+* ``WEIGHTED_ENERGY``: the model differentiates ``sum_i w_i e_i`` (``w = 1`` owned, ``0`` ghost); gradients that land on
+  ghost rows are returned to the owners with a reverse halo exchange.
+* ``REPLICATED``: no neighbours involved; the model runs on the owned rows only.
+
+Per-system sums (energy, virial, stress) are all-reduced; every rank ends up with the full values.
+"""
+from __future__ import annotations
+
+from types import SimpleNamespace
+from typing import Any
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from nvalchemi_toolkit_b200.distributed.config import DomainConfig
+from nvalchemi_toolkit_b200.distributed.sharded_batch import ShardedBatch
+from nvalchemi_toolkit_b200.distributed.spec import Consolidation, MLIPSpec
+from nvalchemi_toolkit_b200.hooks.neighbor_list import NeighborListHook
+
+
+def consolidate_outputs(out: dict, sharded: ShardedBatch, spec: MLIPSpec) -> dict:
+    """Owned-row views of node outputs (with the reverse-halo correction) and globally summed system outputs."""
+    n = sharded.n_owned
+    res: dict[str, Any] = {}
+    for key, value in out.items():
+        if not isinstance(value, torch.Tensor):
+            res[key] = value
+            continue
+        if key in spec.extensive_outputs:
+            v = value.detach().clone()
+            if sharded.world > 1:
+                dist.all_reduce(v, group=sharded.group)
+            res[key] = v
+        elif value.dim() >= 1 and value.shape[0] == n + sharded.n_ghost:
+            own = value.detach()[:n].clone()
+            if key == "forces" and spec.consolidation == Consolidation.WEIGHTED_ENERGY:
+                sharded.halo.reverse_add(value.detach()[n:], own)  # collective: every rank takes part
+            res[key] = own
+        else:
+            res[key] = value.detach()
+    return res
+
+
+class DistributedModel(nn.Module):
+    def __init__(self, model: Any, config: DomainConfig, spec: MLIPSpec | None = None, group: Any = None,
+                 max_neighbors: int | None = None) -> None:
+        super().__init__()
+        self.model, self.config, self.group = model, config, group
+        self.spec = spec if spec is not None else model.distribution_spec(config.strategy)
+        if self.spec is None:
+            raise ValueError(f"{type(model).__name__} declares no distribution spec; pass spec=MLIPSpec(...)")
+        self.model_config = model.model_config
+        nc = self.model_config.neighbor_config
+        self.neighbor_hook = NeighborListHook(nc, skin=config.skin, max_neighbors=max_neighbors) if nc is not None else None
+        if nc is not None and self.spec.requires_full_list and nc.half_list:
+            raise ValueError("domain decomposition needs a full neighbour list (each owned row must be complete)")
+        self._halo_builds = -1
+
+    def forward(self, sharded: ShardedBatch, **kwargs: Any) -> dict:
+        spec = self.spec
+        if spec.consolidation == Consolidation.REPLICATED:
+            out = self.model(sharded.owned, **kwargs)
+            return consolidate_outputs(dict(out), _NoGhost(sharded), spec)
+        padded = sharded.padded_batch()
+        if self.neighbor_hook is not None:
+            if sharded.halo.num_builds != self._halo_builds:  # ghost rows changed identity: start from a fresh list
+                self.neighbor_hook._bufs = None
+                self._halo_builds = sharded.halo.num_builds
+            self.neighbor_hook(SimpleNamespace(batch=padded), None)
+            if spec.consolidation == Consolidation.DIRECT_MASKED:
+                padded.num_neighbors[sharded.n_owned:] = 0
+        out = self.model(padded, **kwargs)
+        return consolidate_outputs(dict(out), sharded, spec)
+
+
+class _NoGhost:
+    """View of a sharded batch for models evaluated on owned rows only."""
+
+    def __init__(self, sharded: ShardedBatch) -> None:
+        self._s = sharded
+        self.n_ghost = 0
+
+    def __getattr__(self, name: str) -> Any:
+        return getattr(self._s, name)

@@ -1,0 +1,164 @@
+# SPDX-License-Identifier: Apache-2.0
+"""``DomainParallel``: run any dynamics object on one system split over ranks.
+
+Reference: ``nvalchemi/distributed/domain_parallel.py:200-975`` and ``_dynamics_coordinator.py:40-170``.  The wrapped
+dynamics object keeps integrating an ordinary :class:`Batch` (its rank's owned atoms); this class replaces the model
+evaluation with a :class:`DistributedModel` forward, re-partitions when the neighbour skin is exhausted (atoms that left
+the sub-domain migrate with all their per-atom fields), installs the cross-rank sums that thermostats and optimisers
+need, and runs hooks registered with a :class:`HookScope` on the gathered global batch.
+"""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from nvalchemi_toolkit_b200.data.batch import Batch
+from nvalchemi_toolkit_b200.distributed.config import DomainConfig, HookScope
+from nvalchemi_toolkit_b200.distributed.distributed_model import DistributedModel
+from nvalchemi_toolkit_b200.distributed.halo import _world
+from nvalchemi_toolkit_b200.distributed.sharded_batch import ShardedBatch
+from nvalchemi_toolkit_b200.distributed.spec import MLIPSpec
+from nvalchemi_toolkit_b200.dynamics.base import DynamicsStage
+from nvalchemi_toolkit_b200.hooks.core import DynamicsContext
+
+
+class DynamicsCoordinator:
+    """Installs cross-rank reductions into the seams integrators expose (kinetic-energy sum and atom count for
+    Nose-Hoover chains, ``v.f / v.v / f.f`` sums and the step-length maximum for FIRE variants)."""
+
+    def __init__(self, dynamics: Any, group: Any = None) -> None:
+        self.dynamics, self.group = dynamics, group
+        _, self.world = _world(group)
+        if self.world == 1:
+            return
+        for name in ("ke_reduce", "count_reduce", "reduce"):
+            if hasattr(dynamics, name):
+                setattr(dynamics, name, self.sum)
+        if hasattr(dynamics, "reduce_max"):
+            dynamics.reduce_max = self.max
+        if hasattr(dynamics, "compute_reductions"):
+            dynamics.compute_reductions = False
+
+    def sum(self, t: torch.Tensor) -> torch.Tensor:
+        t = t.clone()
+        dist.all_reduce(t, group=self.group)
+        return t
+
+    def max(self, t: torch.Tensor) -> torch.Tensor:
+        t = t.clone()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return t
+
+    def before_pre_update(self, batch: Batch) -> None:
+        """FIRE (first variant) takes its three sums as inputs when it does not compute them itself."""
+        dyn = self.dynamics
+        if self.world == 1 or not hasattr(dyn, "compute_reductions") or getattr(dyn, "_state", None) is None:
+            return
+        s = dyn._state
+        v, f = batch.velocities.double(), batch.forces.double()
+        sums = torch.stack([(v * f).sum(), (v * v).sum(), (f * f).sum()])
+        dist.all_reduce(sums, group=self.group)
+        for key, val in zip(("vf", "vv", "ff"), sums):
+            s[key].fill_(float(val))
+
+
+class DomainParallel:
+    def __init__(self, dynamics: Any, config: DomainConfig, spec: MLIPSpec | None = None, group: Any = None,
+                 max_neighbors: int | None = None) -> None:
+        self.dynamics, self.config, self.group = dynamics, config, group
+        self.rank, self.world = _world(group)
+        self.model = DistributedModel(dynamics.model, config, spec, group, max_neighbors=max_neighbors)
+        self.spec = self.model.spec
+        self.coordinator = DynamicsCoordinator(dynamics, group)
+        self.sharded: ShardedBatch | None = None
+        self._scoped: list[tuple[Any, DynamicsStage, HookScope]] = []
+        self.num_rebuilds = 0
+
+    # ---- set-up ---------------------------------------------------------------
+    def partition(self, batch: Batch) -> ShardedBatch:
+        self.sharded = ShardedBatch.from_batch(batch, self.config, self.spec, self.group)
+        return self.sharded
+
+    def register_hook(self, hook: Any, stage: DynamicsStage | None = None, scope: HookScope = HookScope.LOCAL) -> None:
+        stage = stage if stage is not None else getattr(hook, "stage", DynamicsStage.AFTER_STEP)
+        if scope == HookScope.LOCAL:
+            self.dynamics.register_hook(hook, stage) if stage is not None else self.dynamics.register_hook(hook)
+        else:
+            self._scoped.append((hook, stage, scope))
+
+    def _call_scoped(self, stage: DynamicsStage) -> None:
+        due = [(h, sc) for h, st, sc in self._scoped
+               if st == stage and self.dynamics.step_count % max(1, getattr(h, "frequency", 1)) == 0]
+        if not due:
+            return
+        want_all = any(sc == HookScope.GLOBAL for _, sc in due)
+        full = self.sharded.gather(dst=None if want_all else 0)
+        for hook, scope in due:
+            if scope == HookScope.GLOBAL or self.rank == 0:
+                ctx = DynamicsContext(batch=full, step_count=self.dynamics.step_count, model=self.dynamics.model,
+                                      converged_mask=None, global_rank=self.rank, workflow=self.dynamics)
+                hook(ctx, stage)
+
+    # ---- stepping -------------------------------------------------------------
+    def compute(self) -> dict:
+        """Distributed forward; results are written into the owned batch like ``BaseDynamics.compute`` does."""
+        sh, dyn = self.sharded, self.dynamics
+        if sh.needs_rebuild():
+            sh.rebuild()
+            self.num_rebuilds += 1
+        out = self.model(sh)
+        dyn._validate_model_outputs(out)
+        owned = sh.owned
+        for key, attr in dyn._OUTPUT_KEY_TO_BATCH_ATTR.items():
+            value = out.get(key)
+            if value is None:
+                continue
+            if attr == "energy" and value.dim() == 1:
+                value = value.unsqueeze(-1)
+            owned[attr] = value
+        dyn._last_outputs = out
+        return out
+
+    def step(self) -> ShardedBatch:
+        sh, dyn = self.sharded, self.dynamics
+        if sh is None:
+            raise RuntimeError("call partition(batch) first")
+        dyn._ensure_state_initialized(sh.owned)
+        for stage, fn in ((DynamicsStage.BEFORE_STEP, None), (DynamicsStage.BEFORE_PRE_UPDATE, "pre"),
+                          (DynamicsStage.AFTER_PRE_UPDATE, None), (DynamicsStage.BEFORE_COMPUTE, "compute"),
+                          (DynamicsStage.AFTER_COMPUTE, None), (DynamicsStage.BEFORE_POST_UPDATE, "post"),
+                          (DynamicsStage.AFTER_POST_UPDATE, None), (DynamicsStage.AFTER_STEP, None)):
+            dyn._call_hooks(stage, sh.owned)
+            self._call_scoped(stage)
+            if fn == "pre":
+                self.coordinator.before_pre_update(sh.owned)
+                dyn.pre_update(sh.owned)
+            elif fn == "compute":
+                self.compute()  # may replace sh.owned (migration); later stages see the new batch
+            elif fn == "post":
+                dyn.post_update(sh.owned)
+        dyn.step_count += 1
+        return sh
+
+    def run(self, batch: Batch | ShardedBatch | None = None, n_steps: int | None = None) -> ShardedBatch:
+        if isinstance(batch, ShardedBatch):
+            self.sharded = batch
+        elif batch is not None:
+            self.partition(batch)
+        n = n_steps if n_steps is not None else self.dynamics.n_steps
+        if n is None:
+            raise ValueError("No step count provided")
+        if getattr(self.sharded.owned, "forces", None) is None or self.dynamics.step_count == 0:
+            self.compute()  # integrators need forces at the first half-kick
+        self.dynamics._open_hooks()
+        try:
+            for _ in range(n):
+                self.step()
+        finally:
+            self.dynamics._close_hooks()
+        return self.sharded
+
+    def gather(self, dst: int | None = None) -> Batch | None:
+        return self.sharded.gather(dst)

@@ -1,0 +1,85 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Differentiable halo primitives and the explicit ``ShardTensor`` container.
+
+Reference: ``nvalchemi/distributed/ops.py:110-720`` and ``_core/shard_tensor.py``.  The reference subclasses
+``torch.Tensor`` and intercepts ``index_select`` / ``scatter_add`` through ``__torch_dispatch__``; here the same data
+movement is exposed as explicit autograd functions, which is what a hand-written distributed forward (or a training
+step across sub-domains) calls:
+
+* :func:`halo_forward`: ghost rows from owners; its backward adds ghost-row gradients back into the owners.
+* :func:`halo_scatter_correct`: after a scatter-add over local edges, partial sums that landed on ghost rows are
+  added into their owners; its backward forwards owner gradients to the ghosts.
+"""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+
+from nvalchemi_toolkit_b200.distributed.halo import HaloExchange
+
+
+class _HaloForward(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, owned: torch.Tensor, halo: HaloExchange) -> torch.Tensor:
+        ctx.halo = halo
+        return torch.cat([owned, halo.forward(owned)])
+
+    @staticmethod
+    def backward(ctx: Any, grad: torch.Tensor) -> tuple[torch.Tensor, None]:
+        n = grad.shape[0] - ctx.halo.n_ghost
+        own = grad[:n].clone()
+        ctx.halo.reverse_add(grad[n:].contiguous(), own)
+        return own, None
+
+
+class _HaloScatterCorrect(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, padded: torch.Tensor, halo: HaloExchange) -> torch.Tensor:
+        ctx.halo = halo
+        n = padded.shape[0] - halo.n_ghost
+        own = padded[:n].clone()
+        halo.reverse_add(padded[n:].contiguous(), own)
+        return own
+
+    @staticmethod
+    def backward(ctx: Any, grad: torch.Tensor) -> tuple[torch.Tensor, None]:
+        return torch.cat([grad, ctx.halo.forward(grad.contiguous())]), None
+
+
+def halo_forward(owned: torch.Tensor, halo: HaloExchange) -> torch.Tensor:
+    return _HaloForward.apply(owned, halo)
+
+
+def halo_scatter_correct(padded: torch.Tensor, halo: HaloExchange) -> torch.Tensor:
+    return _HaloScatterCorrect.apply(padded, halo)
+
+
+class ShardTensor:
+    """A per-atom tensor split by sub-domain: ``local`` holds the owned rows; :meth:`padded` appends current ghost
+    rows, :meth:`fold` returns ghost-row partial sums to the owners, :meth:`full_tensor` gathers all ranks' rows in
+    global-id order.  An explicit container, not a ``torch.Tensor`` subclass."""
+
+    def __init__(self, local: torch.Tensor, sharded: Any) -> None:
+        self.local, self.sharded = local, sharded
+
+    @property
+    def n_owned(self) -> int:
+        return self.local.shape[0]
+
+    def to_local(self) -> torch.Tensor:
+        return self.local
+
+    def padded(self) -> torch.Tensor:
+        return halo_forward(self.local, self.sharded.halo)
+
+    @staticmethod
+    def fold(padded: torch.Tensor, sharded: Any) -> "ShardTensor":
+        return ShardTensor(halo_scatter_correct(padded, sharded.halo), sharded)
+
+    def full_tensor(self) -> torch.Tensor:
+        from nvalchemi_toolkit_b200.distributed.halo import all_gather_rows
+
+        rows, _ = all_gather_rows(self.local.detach().contiguous(), self.sharded.group)
+        ids, _ = all_gather_rows(self.sharded.global_ids, self.sharded.group)
+        return rows[torch.argsort(ids)]

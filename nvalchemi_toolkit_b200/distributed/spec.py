@@ -1,0 +1,83 @@
+# SPDX-License-Identifier: Apache-2.0
+"""``MLIPSpec``: what the domain-decomposition layer needs to know about a model.
+
+The reference (``nvalchemi/distributed/spec.py:50-410``) describes, per model, which tensors are node/edge/system
+sharded and which dispatch interceptions (halo refresh after scatter, halo-receiver edge masks, MACE reshape and
+autograd workarounds) keep a traced forward correct.  Nothing is traced or intercepted here; the distributed forward is
+an explicit ghost-atom evaluation, so the spec reduces to three facts:
+
+* ``message_passes``: how many neighbour hops influence an atom's energy; ghosts are kept within
+  ``message_passes * (cutoff + skin)`` of the sub-domain, which makes every owned atom's energy exact;
+* ``consolidation``: how per-rank results combine.  ``DIRECT_MASKED`` suits kernels that produce forces directly from a
+  full neighbour list: ghost rows get an empty neighbour list, so every owned row is complete and nothing is counted
+  twice.  ``WEIGHTED_ENERGY`` suits differentiated models: the model sums node energies with per-atom weights (1 owned,
+  0 ghost), differentiates that sum with respect to all local positions, and the ghost rows' gradients are added to
+  their owners (reverse halo);
+* which outputs are per-node and which are extensive per-system sums.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from enum import Enum
+
+from nvalchemi_toolkit_b200.distributed.config import StrategyKind
+
+
+class Consolidation(str, Enum):
+    DIRECT_MASKED = "direct_masked"
+    WEIGHTED_ENERGY = "weighted_energy"
+    REPLICATED = "replicated"       # the model needs no neighbours (per-atom terms only)
+
+
+@dataclass(frozen=True)
+class MLIPSpec:
+    name: str
+    strategy: StrategyKind = StrategyKind.HALO
+    message_passes: int = 1
+    consolidation: Consolidation = Consolidation.WEIGHTED_ENERGY
+    node_energy_key: str = "atomic_energies"
+    requires_full_list: bool = True
+    node_outputs: tuple[str, ...] = ("forces", "atomic_energies", "charges", "node_embeddings")
+    extensive_outputs: tuple[str, ...] = ("energy", "virial", "stress")
+    needs_total_charge: bool = False
+    notes: str = ""
+    extra: dict = field(default_factory=dict)
+
+    def ghost_width(self, cutoff: float, skin: float = 0.0) -> float:
+        return max(1, self.message_passes) * (cutoff + skin)
+
+    def with_(self, **changes: object) -> "MLIPSpec":
+        from dataclasses import replace
+
+        return replace(self, **changes)
+
+
+SPEC_LJ_HALO = MLIPSpec("lennard_jones", message_passes=1, consolidation=Consolidation.DIRECT_MASKED)
+SPEC_PAIR_HALO = MLIPSpec("pair_potential", message_passes=1, consolidation=Consolidation.DIRECT_MASKED)
+SPEC_DFTD3_HALO = MLIPSpec("dftd3", message_passes=2, consolidation=Consolidation.WEIGHTED_ENERGY,
+                           notes="coordination numbers need one hop, the dispersion sum a second")
+SPEC_EWALD_REAL_HALO = MLIPSpec("ewald_real_space", message_passes=1, consolidation=Consolidation.DIRECT_MASKED,
+                                needs_total_charge=True,
+                                notes="reciprocal-space part is evaluated on replicated structure factors")
+SPEC_MACE_HALO = MLIPSpec("mace", message_passes=2, consolidation=Consolidation.WEIGHTED_ENERGY)
+SPEC_MACE_CUEQ_HALO = SPEC_MACE_HALO.with_(name="mace_cueq")
+SPEC_AIMNET2_HALO = MLIPSpec("aimnet2", message_passes=3, consolidation=Consolidation.WEIGHTED_ENERGY,
+                             needs_total_charge=True)
+SPEC_DEMO = MLIPSpec("demo", message_passes=0, consolidation=Consolidation.REPLICATED)
+SPEC_MACE_GRAPH_PARTITION = MLIPSpec("mace_graph_partition", strategy=StrategyKind.GRAPH_PARTITION, message_passes=2,
+                                     consolidation=Consolidation.WEIGHTED_ENERGY)
+SPEC_AIMNET2_GRAPH_PARTITION = MLIPSpec("aimnet2_graph_partition", strategy=StrategyKind.GRAPH_PARTITION,
+                                        message_passes=3, consolidation=Consolidation.WEIGHTED_ENERGY,
+                                        needs_total_charge=True)
+
+_REGISTRY = {s.name: s for s in (SPEC_LJ_HALO, SPEC_PAIR_HALO, SPEC_DFTD3_HALO, SPEC_EWALD_REAL_HALO, SPEC_MACE_HALO,
+                                 SPEC_MACE_CUEQ_HALO, SPEC_AIMNET2_HALO, SPEC_DEMO, SPEC_MACE_GRAPH_PARTITION,
+                                 SPEC_AIMNET2_GRAPH_PARTITION)}
+
+
+def get_spec(name: str) -> MLIPSpec:
+    return _REGISTRY[name]
+
+
+def register_spec(spec: MLIPSpec) -> None:
+    _REGISTRY[spec.name] = spec

@@ -71,6 +71,7 @@ class NVTNoseHoover(BaseDynamics):
         self._tau_init = fs_to_internal_time(thermostat_time)
         self.chain_length, self.yoshida_order = chain_length, yoshida_order
         self.ke_reduce = None  # a domain-decomposition coordinator may install a cross-rank sum here
+        self.count_reduce = None  # ... and the cross-rank atom count (degrees of freedom)
 
     def _make_new_state(self, n: int, template_batch: Batch) -> dict[str, torch.Tensor]:
         dev, dtype = template_batch.device, template_batch.positions.dtype
@@ -89,6 +90,8 @@ class NVTNoseHoover(BaseDynamics):
         if self.ke_reduce is not None:
             ke2 = self.ke_reduce(ke2)
         ndof = 3.0 * batch.num_nodes_per_graph.to(ke2.dtype)
+        if self.count_reduce is not None:
+            ndof = self.count_reduce(ndof)
         Q = nhc_compute_masses(ndof, s["kT"], s["tau"], self.chain_length)
         scale = nhc_chain_update(ke2, s["eta"], s["eta_dot"], Q, s["kT"], ndof, s["dt"], self.yoshida_order)
         _ops.velocity_rescale(batch.velocities, scale, batch.batch_idx)

@@ -17,7 +17,7 @@ from nvalchemi_toolkit_b200.dynamics.base import BaseDynamics
 
 
 def fire2_step_coord(positions, velocities, forces, batch_idx, alpha, dt, nsteps_inc, *, delaystep, dtgrow, dtshrink,
-                     alphashrink, alpha0, tmax, tmin, maxstep, reduce=None) -> None:
+                     alphashrink, alpha0, tmax, tmin, maxstep, reduce=None, reduce_max=None) -> None:
     m = alpha.shape[0]
     b = batch_idx.long()
     z = torch.zeros(m, dtype=torch.float64, device=positions.device)
@@ -43,6 +43,8 @@ def fire2_step_coord(positions, velocities, forces, batch_idx, alpha, dt, nsteps
     velocities.mul_((1.0 - alpha)[b].unsqueeze(-1)).add_(mix * forces)
     dr = h * velocities
     mx = torch.zeros(m, dtype=dr.dtype, device=dr.device).scatter_reduce(0, b, dr.norm(dim=-1), "amax", include_self=True)
+    if reduce_max is not None:
+        mx = reduce_max(mx)
     scale = torch.where(mx > maxstep, maxstep / mx.clamp_min(1e-30), torch.ones_like(mx))
     positions.add_(scale[b].unsqueeze(-1) * dr)
 
@@ -60,7 +62,8 @@ class FIRE2(BaseDynamics):
         self._dt_init = dt
         self.hp = dict(delaystep=delaystep, dtgrow=dtgrow, dtshrink=dtshrink, alphashrink=alphashrink, alpha0=alpha0,
                        tmax=tmax, tmin=tmin, maxstep=maxstep)
-        self.reduce = None
+        self.reduce = None      # cross-rank sum installed by a domain-decomposition coordinator
+        self.reduce_max = None  # cross-rank maximum (step-length limiter)
 
     def _make_new_state(self, n: int, template_batch: Batch) -> dict[str, torch.Tensor]:
         dev, dtype = template_batch.device, template_batch.positions.dtype
@@ -74,7 +77,7 @@ class FIRE2(BaseDynamics):
     def pre_update(self, batch: Batch) -> None:
         s = self._state
         fire2_step_coord(batch.positions, batch.velocities, batch.forces, batch.batch_idx, s["alpha"], s["dt"],
-                         s["nsteps_inc"], reduce=self.reduce, **self.hp)
+                         s["nsteps_inc"], reduce=self.reduce, reduce_max=self.reduce_max, **self.hp)
 
     def post_update(self, batch: Batch) -> None:
         pass

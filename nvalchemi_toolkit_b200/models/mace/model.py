@@ -293,7 +293,8 @@ class MACE(nn.Module):
         if self._use_native(positions, training) and not compute_hessian:
             from nvalchemi_toolkit_b200.models.mace import native
 
-            return native.forward(self, data, species, batch.long(), num_graphs, compute_force, compute_stress)
+            return native.forward(self, data, species, batch.long(), num_graphs, compute_force, compute_stress,
+                                  energy_weights=data.get("energy_weights"))
         sender, receiver, shifts = self._edges_from(data, positions, batch.long(), cell)
         need_grad = compute_force or compute_stress or compute_hessian
         with torch.enable_grad() if need_grad else torch.no_grad():
@@ -317,7 +318,8 @@ class MACE(nn.Module):
                     pos = pos.detach().requires_grad_(True)
                 pos_in = pos
             node_e = self.node_energies_torch(pos_in, species, sender, receiver, shifts)
-            energy = pos.new_zeros(num_graphs).index_add_(0, batch.long(), node_e)
+            ew = data.get("energy_weights")  # per-atom weights of the energy sum (domain decomposition: 0 on ghosts)
+            energy = pos.new_zeros(num_graphs).index_add_(0, batch.long(), node_e if ew is None else node_e * ew.to(node_e.dtype))
             out: dict[str, torch.Tensor | None] = {"energy": energy, "node_energy": node_e, "forces": None,
                                                     "stress": None, "hessian": None}
             if compute_force and strain is not None:

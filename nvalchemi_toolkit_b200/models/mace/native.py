@@ -234,7 +234,8 @@ def _sym_weights(ip: Any, corr: int) -> tuple[torch.Tensor, torch.Tensor | None]
 
 @torch.no_grad()
 def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, batch: torch.Tensor,
-            num_graphs: int, compute_force: bool, compute_stress: bool, dd: Any = None
+            num_graphs: int, compute_force: bool, compute_stress: bool, dd: Any = None,
+            energy_weights: torch.Tensor | None = None
             ) -> dict[str, torch.Tensor | None]:
     """Energy (+ forces, stress) with the native kernels.
 
@@ -329,7 +330,9 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         del B, sc
     scale, shift = model.scale.to(pos.dtype), model.shift.to(pos.dtype)
     node_e = model.atomic_energies.to(pos.dtype)[species] + node_e * scale + shift
-    energy = torch.zeros(num_graphs, dtype=torch.float64, device=dev).index_add_(0, batch[:n], node_e.double()).to(pos.dtype)
+    ew = None if energy_weights is None else energy_weights[:n].to(pos.dtype)
+    e_sum = node_e if ew is None else node_e * ew
+    energy = torch.zeros(num_graphs, dtype=torch.float64, device=dev).index_add_(0, batch[:n], e_sum.double()).to(pos.dtype)
     out: dict[str, torch.Tensor | None] = {"energy": energy, "node_energy": node_e, "forces": None, "stress": None,
                                             "hessian": None}
     if not (compute_force or compute_stress):
@@ -344,9 +347,10 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         n_out = sum(2 * l + 1 for l in ip.l_out)
         dh_tot = pos.new_zeros(n, n_out, C) if dh is None else dh
         if ip.last:
-            dh_tot[:, 0] += gemm.matmul(ro[0], (ip.readout_w1 / math.sqrt(C)).t()) * scale
+            seed = gemm.matmul(ro[0], (ip.readout_w1 / math.sqrt(C)).t()) * scale
         else:
-            dh_tot[:, 0] += (ip.readout_w1 / math.sqrt(C)) * scale
+            seed = ((ip.readout_w1 / math.sqrt(C)) * scale).expand(n, C)
+        dh_tot[:, 0] += seed if ew is None else seed * ew[:, None]
         dB = _per_l_linear(dh_tot, ip.product_linear, ip.l_out, transpose=True).contiguous()
         dmsg = ops.mace_symcon_bwd(msg, sp32, w0, w1, max(ip.l_out), cfg.correlation, dB)
         del dB

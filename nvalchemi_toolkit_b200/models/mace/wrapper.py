@@ -51,7 +51,7 @@ class MACEWrapper(nn.Module, BaseModelMixin):
         if cell is not None:
             cell = cell.reshape(nb, 3, 3)
         out: dict[str, Any] = {"positions": pos, "atomic_numbers": data.atomic_numbers, "batch": batch, "ptr": ptr,
-                               "cell": cell, "num_graphs": nb}
+                               "cell": cell, "num_graphs": nb, "energy_weights": getattr(data, "energy_weights", None)}
         nm = getattr(data, "neighbor_matrix", None)
         if nm is not None and self.model_config.neighbor_config.format == NeighborListFormat.MATRIX:
             out.update(neighbor_matrix=nm, num_neighbors=data.num_neighbors,
@@ -97,6 +97,13 @@ class MACEWrapper(nn.Module, BaseModelMixin):
             _, feats = self.model.node_energies_torch(inputs["positions"], species, send, recv, sh, return_features=True)
         data["node_embeddings"] = torch.cat([f.reshape(f.shape[0], -1) for f in feats[:1]], dim=-1)
         return data
+
+    def distribution_spec(self, strategy: Any = None) -> Any:
+        from nvalchemi_toolkit_b200.distributed import spec as _spec
+
+        if strategy is not None and str(getattr(strategy, "value", strategy)) == "graph_partition":
+            return _spec.SPEC_MACE_GRAPH_PARTITION
+        return _spec.SPEC_MACE_HALO.with_(message_passes=len(self.model.interactions))
 
     def checkpoint_spec(self) -> dict:
         from dataclasses import asdict

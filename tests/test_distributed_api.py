@@ -1,0 +1,247 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Generic domain-decomposition layer: partitioner, halo plan, sharded batch, distributed model, DomainParallel.
+
+Multi-rank cases run as gloo processes on CPU and are compared with the single-process result."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from nvalchemi_toolkit_b200 import Batch
+from nvalchemi_toolkit_b200.distributed import (DistributedModel, DomainConfig, DomainParallel, HookScope, IndexPartitioner,
+                                                ShardedBatch, SpatialPartitioner, factor_grid, halo_forward,
+                                                halo_scatter_correct)
+from nvalchemi_toolkit_b200.dynamics import NVE
+from nvalchemi_toolkit_b200.hooks import NeighborListHook
+from nvalchemi_toolkit_b200.models.lj import LennardJonesModelWrapper
+from tests.helpers import fcc_supercell
+
+A = 5.26  # fcc argon-like lattice constant for the LJ cases
+
+
+def _lj_batch(n_cells=4, noise=0.05, seed=0, velocities=0.0):
+    d = fcc_supercell(n_cells, a=A, z=18, noise=noise, seed=seed, dtype=torch.float64)
+    b = Batch.from_data_list([d])
+    g = torch.Generator().manual_seed(seed + 1)
+    b["velocities"] = velocities * torch.randn(b.num_nodes, 3, generator=g, dtype=torch.float64)
+    return b
+
+
+def _lj():
+    m = LennardJonesModelWrapper(epsilon=0.0104, sigma=3.4, cutoff=6.0, switch_width=1.0)
+    m.model_config.active_outputs = {"energy", "forces", "stress"}
+    return m
+
+
+def _reference(model, batch, skin=0.0):
+    from types import SimpleNamespace
+
+    hook = NeighborListHook(model.model_config.neighbor_config, skin=skin)
+    hook(SimpleNamespace(batch=batch), None)
+    return model(batch)
+
+
+def test_factor_grid_and_partitioner():
+    assert factor_grid(8, (10.0, 10.0, 10.0)) == (2, 2, 2)
+    assert factor_grid(4, (40.0, 10.0, 10.0)) == (4, 1, 1)
+    cell, pbc = torch.eye(3) * 20.0, torch.tensor([True, True, True])
+    part = SpatialPartitioner(cell, pbc, 4, cutoff=5.0, grid_dims=(2, 2, 1), hysteresis=0.5)
+    pos = torch.tensor([[1.0, 1.0, 1.0], [11.0, 1.0, 3.0], [1.0, 11.0, 3.0], [19.0, 19.0, 0.0], [-1.0, 1.0, 1.0]])
+    assert part.assign_atoms_to_ranks(pos).tolist() == [0, 2, 1, 3, 2]
+    assert part.neighbor_ranks(0) == [1, 2, 3]
+    # an atom just outside its owner's box stays with the owner (hysteresis), farther out it does not
+    owner = torch.tensor([0, 0])
+    keep = part.keeps_owner(torch.tensor([[10.3, 1.0, 1.0], [10.8, 1.0, 1.0]]), owner)
+    assert keep.tolist() == [True, False]
+    keep = part.keeps_owner(torch.tensor([[19.8, 1.0, 1.0]]), torch.tensor([0]))  # across the periodic boundary
+    assert keep.tolist() == [True]
+    ip = IndexPartitioner(10, 3)
+    assert [ip.block(r) for r in range(3)] == [(0, 4), (4, 7), (7, 10)]
+    assert ip.owner(torch.tensor([0, 3, 4, 9])).tolist() == [0, 0, 1, 2]
+
+
+def test_single_rank_periodic_images_match_pbc_model():
+    batch = _lj_batch(3)
+    model = _lj()
+    ref = _reference(model, batch.clone())
+    cfg = DomainConfig(cutoff=6.0, skin=0.0)
+    sh = ShardedBatch.from_batch(batch, cfg, model.distribution_spec())
+    assert sh.n_owned == batch.num_nodes and sh.n_ghost > 0
+    out = DistributedModel(model, cfg)(sh)
+    assert torch.allclose(out["forces"], ref["forces"], atol=1e-10)
+    assert torch.allclose(out["energy"], ref["energy"], atol=1e-9)
+    assert torch.allclose(out["stress"], ref["stress"], atol=1e-10)
+
+
+def test_single_rank_weighted_energy_mace_matches_pbc_model():
+    from nvalchemi_toolkit_b200.models.mace import MACEWrapper
+    from nvalchemi_toolkit_b200.models.mace.model import MACE, MACEConfig
+
+    torch.manual_seed(0)
+    d = fcc_supercell(2, a=3.61, z=29, noise=0.08, seed=3, dtype=torch.float64)
+    batch = Batch.from_data_list([d])
+    model = MACEWrapper(MACE(MACEConfig(r_max=3.0, channels=8, max_ell=3, atomic_numbers=[29], radial_mlp=[16, 16],
+                                        avg_num_neighbors=12.0), backend="torch")).double()
+    model.model_config.active_outputs = {"energy", "forces", "stress"}
+    ref = _reference(model, batch.clone())
+    cfg = DomainConfig(cutoff=3.0, skin=0.0)
+    sh = ShardedBatch.from_batch(batch, cfg, model.distribution_spec())
+    out = DistributedModel(model, cfg)(sh)
+    assert torch.allclose(out["energy"].reshape(-1), ref["energy"].reshape(-1), atol=1e-8)
+    assert torch.allclose(out["forces"], ref["forces"], atol=1e-8)
+    assert torch.allclose(out["stress"].reshape(3, 3), ref["stress"].reshape(3, 3), atol=1e-8)
+
+
+def test_halo_autograd_primitives_single_rank():
+    batch = _lj_batch(2)
+    cfg = DomainConfig(cutoff=4.0)
+    sh = ShardedBatch.from_batch(batch, cfg)
+    x = torch.randn(sh.n_owned, 3, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(sh.n_owned + sh.n_ghost, 3, dtype=torch.float64)
+    (halo_forward(x, sh.halo) * w).sum().backward()
+    expect = w[: sh.n_owned].clone().index_add_(0, sh.halo.send_index, w[sh.n_owned:])
+    assert torch.allclose(x.grad, expect)
+    p = torch.randn(sh.n_owned + sh.n_ghost, 2, dtype=torch.float64, requires_grad=True)
+    y = halo_scatter_correct(p, sh.halo)
+    assert torch.allclose(y, p[: sh.n_owned].detach().clone().index_add_(0, sh.halo.send_index, p[sh.n_owned:].detach()))
+    v = torch.randn_like(y)
+    (y * v).sum().backward()
+    assert torch.allclose(p.grad, torch.cat([v, v[sh.halo.send_index]]))
+
+
+# ------------------------------------------------------------------ multi-rank (gloo)
+def _md_worker(rank, world, port, q, n_steps, vel, skin, grid):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        batch = _lj_batch(4, velocities=vel)
+        dyn = NVE(_lj(), dt=2.0)
+        cfg = DomainConfig(cutoff=6.0, skin=skin, grid_dims=grid)
+        dp = DomainParallel(dyn, cfg)
+        seen = []
+
+        class Probe:
+            frequency, stage = 5, None
+
+            def __call__(self, ctx, stage):
+                seen.append((ctx.step_count, ctx.batch.num_nodes))
+
+        from nvalchemi_toolkit_b200.dynamics.base import DynamicsStage
+
+        dp.register_hook(Probe(), DynamicsStage.AFTER_STEP, HookScope.RANK_ZERO)
+        sh = dp.run(batch, n_steps=n_steps)
+        full = dp.gather()
+        q.put((rank, full.positions.tolist(), full.velocities.tolist(), float(full.energy.reshape(-1)[0]), sh.num_migrated,
+               dp.num_rebuilds, seen, sh.n_owned))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run_md(world, port, n_steps, vel, skin, grid):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_md_worker, args=(r, world, port, q, n_steps, vel, skin, grid)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(world):
+        item = q.get(timeout=240)
+        res[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=30)
+    return res
+
+
+def _single_md(n_steps, vel):
+    batch = _lj_batch(4, velocities=vel)
+    model = _lj()
+    from nvalchemi_toolkit_b200.dynamics.base import DynamicsStage
+
+    dyn = NVE(model, dt=2.0, hooks=[NeighborListHook(model.model_config.neighbor_config, skin=0.0,
+                                                     stage=DynamicsStage.BEFORE_COMPUTE)])
+
+    dyn._call_hooks(DynamicsStage.BEFORE_COMPUTE, batch)
+    dyn.compute(batch)
+    dyn.run(batch, n_steps=n_steps)
+    return batch
+
+
+@pytest.mark.parametrize("world,grid", [(2, None), (4, (2, 2, 1))])
+def test_domain_parallel_nve_matches_single_process(world, grid):
+    n_steps, vel = 20, 0.02
+    res = _run_md(world, 29610 + world, n_steps, vel, 1.0, grid)
+    ref = _single_md(n_steps, vel)
+    pos0 = torch.tensor(res[0][0], dtype=torch.float64)
+    for r in range(1, world):  # every rank gathers the same global batch
+        assert torch.equal(pos0, torch.tensor(res[r][0], dtype=torch.float64))
+    assert torch.allclose(pos0, ref.positions, atol=1e-9)
+    assert torch.allclose(torch.tensor(res[0][1], dtype=torch.float64), ref.velocities, atol=1e-9)
+    assert abs(res[0][2] - float(ref.energy.reshape(-1)[0])) < 1e-9
+    assert sum(res[r][6] for r in range(world)) == ref.num_nodes
+    assert res[0][5] == [(0, 256), (5, 256), (10, 256), (15, 256)] and res[1][5] == []
+    assert res[0][4] < n_steps  # the skin spared most rebuilds
+
+
+def test_domain_parallel_migration_keeps_trajectory():
+    n_steps, vel = 30, 0.25  # fast atoms: several cross sub-domain boundaries
+    res = _run_md(2, 29640, n_steps, vel, 0.6, None)
+    ref = _single_md(n_steps, vel)
+    assert res[0][3] > 0  # atoms changed owner
+    assert torch.allclose(torch.tensor(res[0][0], dtype=torch.float64), ref.positions, atol=1e-8)
+    assert sum(res[r][6] for r in range(2)) == ref.num_nodes
+
+
+def _mace_model():
+    from nvalchemi_toolkit_b200.models.mace import MACEWrapper
+    from nvalchemi_toolkit_b200.models.mace.model import MACE, MACEConfig
+
+    torch.manual_seed(0)
+    model = MACEWrapper(MACE(MACEConfig(r_max=3.0, channels=8, max_ell=3, atomic_numbers=[29], radial_mlp=[16, 16],
+                                        avg_num_neighbors=12.0), backend="torch")).double()
+    model.model_config.active_outputs = {"energy", "forces", "stress"}
+    return model
+
+
+def _mace_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        batch = Batch.from_data_list([fcc_supercell(4, a=3.61, z=29, noise=0.08, seed=3, dtype=torch.float64)])
+        model = _mace_model()
+        cfg = DomainConfig(cutoff=3.0, skin=0.0)
+        sh = ShardedBatch.from_batch(batch, cfg, model.distribution_spec())
+        out = DistributedModel(model, cfg)(sh)
+        from nvalchemi_toolkit_b200.distributed import ShardTensor
+
+        forces = ShardTensor(out["forces"], sh).full_tensor()
+        q.put((rank, forces.tolist(), out["energy"].reshape(-1).tolist(), out["stress"].reshape(-1).tolist(), sh.n_ghost))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_weighted_energy_reverse_halo_two_ranks():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_mace_worker, args=(r, 2, 29655, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(2):
+        item = q.get(timeout=240)
+        res[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=30)
+    batch = Batch.from_data_list([fcc_supercell(4, a=3.61, z=29, noise=0.08, seed=3, dtype=torch.float64)])
+    ref = _reference(_mace_model(), batch)
+    for r in range(2):
+        assert torch.allclose(torch.tensor(res[r][0], dtype=torch.float64), ref["forces"], atol=1e-8)
+        assert abs(res[r][1][0] - float(ref["energy"].detach().reshape(-1)[0])) < 1e-8
+        assert torch.allclose(torch.tensor(res[r][2], dtype=torch.float64), ref["stress"].reshape(-1), atol=1e-8)
+        assert res[r][3] > 0
