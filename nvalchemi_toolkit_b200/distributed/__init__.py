@@ -14,13 +14,13 @@ from nvalchemi_toolkit_b200.distributed.spec import (Consolidation, MLIPSpec, SP
                                                      register_spec)
 from nvalchemi_toolkit_b200.distributed.halo import HaloExchange, all_gather_rows, all_to_all_rows
 from nvalchemi_toolkit_b200.distributed.sharded_batch import ShardedBatch
-from nvalchemi_toolkit_b200.distributed.distributed_model import DistributedModel, consolidate_outputs
+from nvalchemi_toolkit_b200.distributed.distributed_model import DistributedModel, DistributedPipelineModel, consolidate_outputs
 from nvalchemi_toolkit_b200.distributed.domain_parallel import DomainParallel, DynamicsCoordinator
 from nvalchemi_toolkit_b200.distributed.ops import ShardTensor, halo_forward, halo_scatter_correct
 from nvalchemi_toolkit_b200.distributed import helpers
 
 __all__ = ["DomainConfig", "HookScope", "StrategyKind", "SpatialPartitioner", "IndexPartitioner", "factor_grid", "MLIPSpec",
-           "Consolidation", "get_spec", "register_spec", "HaloExchange", "ShardedBatch", "DistributedModel",
+           "Consolidation", "get_spec", "register_spec", "HaloExchange", "ShardedBatch", "DistributedModel", "DistributedPipelineModel",
            "consolidate_outputs", "DomainParallel", "DynamicsCoordinator", "ShardTensor", "halo_forward",
            "halo_scatter_correct", "helpers", "all_gather_rows", "all_to_all_rows", "SPEC_LJ_HALO", "SPEC_PAIR_HALO",
            "SPEC_DFTD3_HALO", "SPEC_EWALD_REAL_HALO", "SPEC_MACE_HALO", "SPEC_MACE_CUEQ_HALO", "SPEC_AIMNET2_HALO",

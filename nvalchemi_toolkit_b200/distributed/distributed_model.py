@@ -27,9 +27,11 @@ from nvalchemi_toolkit_b200.distributed.spec import Consolidation, MLIPSpec
 from nvalchemi_toolkit_b200.hooks.neighbor_list import NeighborListHook
 
 
-def consolidate_outputs(out: dict, sharded: ShardedBatch, spec: MLIPSpec) -> dict:
+def consolidate_outputs(out: dict, sharded: ShardedBatch, spec: MLIPSpec, halo: Any = None) -> dict:
     """Owned-row views of node outputs (with the reverse-halo correction) and globally summed system outputs."""
     n = sharded.n_owned
+    halo = halo if halo is not None else sharded.halo
+    n_ghost = halo.n_ghost if spec.consolidation != Consolidation.REPLICATED else 0
     res: dict[str, Any] = {}
     for key, value in out.items():
         if not isinstance(value, torch.Tensor):
@@ -40,10 +42,10 @@ def consolidate_outputs(out: dict, sharded: ShardedBatch, spec: MLIPSpec) -> dic
             if sharded.world > 1:
                 dist.all_reduce(v, group=sharded.group)
             res[key] = v
-        elif value.dim() >= 1 and value.shape[0] == n + sharded.n_ghost:
+        elif value.dim() >= 1 and value.shape[0] == n + n_ghost:
             own = value.detach()[:n].clone()
             if key == "forces" and spec.consolidation == Consolidation.WEIGHTED_ENERGY:
-                sharded.halo.reverse_add(value.detach()[n:], own)  # collective: every rank takes part
+                halo.reverse_add(value.detach()[n:], own)  # collective: every rank takes part
             res[key] = own
         else:
             res[key] = value.detach()
@@ -52,9 +54,9 @@ def consolidate_outputs(out: dict, sharded: ShardedBatch, spec: MLIPSpec) -> dic
 
 class DistributedModel(nn.Module):
     def __init__(self, model: Any, config: DomainConfig, spec: MLIPSpec | None = None, group: Any = None,
-                 max_neighbors: int | None = None) -> None:
+                 max_neighbors: int | None = None, own_halo: bool = False) -> None:
         super().__init__()
-        self.model, self.config, self.group = model, config, group
+        self.model, self.config, self.group, self.own_halo = model, config, group, own_halo
         self.spec = spec if spec is not None else model.distribution_spec(config.strategy)
         if self.spec is None:
             raise ValueError(f"{type(model).__name__} declares no distribution spec; pass spec=MLIPSpec(...)")
@@ -69,25 +71,49 @@ class DistributedModel(nn.Module):
         spec = self.spec
         if spec.consolidation == Consolidation.REPLICATED:
             out = self.model(sharded.owned, **kwargs)
-            return consolidate_outputs(dict(out), _NoGhost(sharded), spec)
-        padded = sharded.padded_batch()
+            return consolidate_outputs(dict(out), sharded, spec)
+        halo = sharded.halo_for(spec.ghost_width(self.config.cutoff, self.config.skin)) if self.own_halo else sharded.halo
+        padded = sharded.padded_batch(halo)
         if self.neighbor_hook is not None:
-            if sharded.halo.num_builds != self._halo_builds:  # ghost rows changed identity: start from a fresh list
+            if halo.num_builds != self._halo_builds:  # ghost rows changed identity: start from a fresh list
                 self.neighbor_hook._bufs = None
-                self._halo_builds = sharded.halo.num_builds
+                self._halo_builds = halo.num_builds
             self.neighbor_hook(SimpleNamespace(batch=padded), None)
             if spec.consolidation == Consolidation.DIRECT_MASKED:
                 padded.num_neighbors[sharded.n_owned:] = 0
         out = self.model(padded, **kwargs)
-        return consolidate_outputs(dict(out), sharded, spec)
+        return consolidate_outputs(dict(out), sharded, spec, halo)
 
 
-class _NoGhost:
-    """View of a sharded batch for models evaluated on owned rows only."""
+class DistributedPipelineModel(nn.Module):
+    """Domain-decomposed ``PipelineModelWrapper``: every member of a direct group is evaluated with a halo of its own
+    depth over the one owned partition, and the consolidated member outputs are summed like the pipeline does.
+    Reference: ``nvalchemi/distributed/distributed_pipeline.py:65-448``.  Groups that differentiate a summed energy
+    through wires are not decomposed here (evaluate such members in direct groups)."""
 
-    def __init__(self, sharded: ShardedBatch) -> None:
-        self._s = sharded
-        self.n_ghost = 0
+    def __init__(self, pipeline: Any, config: DomainConfig, group: Any = None, max_neighbors: int | None = None) -> None:
+        super().__init__()
+        from nvalchemi_toolkit_b200.models._utils import sum_outputs
 
-    def __getattr__(self, name: str) -> Any:
-        return getattr(self._s, name)
+        self.pipeline, self.config, self._sum = pipeline, config, sum_outputs
+        self.model_config = pipeline.model_config
+        self.members = nn.ModuleList()
+        for g in pipeline.groups:
+            if g.use_autograd:
+                raise NotImplementedError("autograd groups are not domain-decomposed; use direct groups")
+            for s in g.steps:
+                if s.wire:
+                    raise NotImplementedError("wired members are not domain-decomposed")
+                nc = s.model.model_config.neighbor_config
+                member_cfg = config.model_copy(update={"cutoff": nc.cutoff if nc is not None else config.cutoff,
+                                                       "ghost_width": None})
+                member_cfg = DomainConfig(**{k: v for k, v in member_cfg.model_dump().items() if k != "ghost_width"})
+                self.members.append(DistributedModel(s.model, member_cfg, group=group, max_neighbors=max_neighbors,
+                                                     own_halo=True))
+        deepest = max(m.spec.ghost_width(m.config.cutoff, m.config.skin) for m in self.members)
+        self.spec = MLIPSpec("pipeline", message_passes=1, consolidation=Consolidation.WEIGHTED_ENERGY)
+        self.required_ghost_width = deepest
+
+    def forward(self, sharded: ShardedBatch, **kwargs: Any) -> dict:
+        outs = [m(sharded, **kwargs) for m in self.members]
+        return self._sum(*outs, additive_keys=frozenset(self.pipeline.additive_keys))

@@ -16,7 +16,7 @@ import torch.distributed as dist
 
 from nvalchemi_toolkit_b200.data.batch import Batch
 from nvalchemi_toolkit_b200.distributed.config import DomainConfig, HookScope
-from nvalchemi_toolkit_b200.distributed.distributed_model import DistributedModel
+from nvalchemi_toolkit_b200.distributed.distributed_model import DistributedModel, DistributedPipelineModel
 from nvalchemi_toolkit_b200.distributed.halo import _world
 from nvalchemi_toolkit_b200.distributed.sharded_batch import ShardedBatch
 from nvalchemi_toolkit_b200.distributed.spec import MLIPSpec
@@ -69,8 +69,16 @@ class DomainParallel:
                  max_neighbors: int | None = None) -> None:
         self.dynamics, self.config, self.group = dynamics, config, group
         self.rank, self.world = _world(group)
-        self.model = DistributedModel(dynamics.model, config, spec, group, max_neighbors=max_neighbors)
-        self.spec = self.model.spec
+        from nvalchemi_toolkit_b200.models.pipeline import PipelineModelWrapper
+
+        if isinstance(dynamics.model, PipelineModelWrapper):
+            self.model = DistributedPipelineModel(dynamics.model, config, group, max_neighbors=max_neighbors)
+            self.config = config = config.model_copy(update={"ghost_width": max(config.ghost_width,
+                                                                                 self.model.required_ghost_width)})
+            self.spec = None  # the sharded batch takes its halo width from the config
+        else:
+            self.model = DistributedModel(dynamics.model, config, spec, group, max_neighbors=max_neighbors)
+            self.spec = self.model.spec
         self.coordinator = DynamicsCoordinator(dynamics, group)
         self.sharded: ShardedBatch | None = None
         self._scoped: list[tuple[Any, DynamicsStage, HookScope]] = []

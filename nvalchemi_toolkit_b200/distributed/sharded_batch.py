@@ -56,8 +56,9 @@ class ShardedBatch:
         if width > 0.0 and self.world > 1:
             width += config.migration_hysteresis  # owned atoms may sit this far outside their owner's box
         self.halo = HaloExchange(partitioner, width, group)
+        self._extra_halos: dict[float, HaloExchange] = {}
         self._ref_positions: torch.Tensor | None = None
-        self._ghost_static: dict[str, torch.Tensor] = {}
+        self._ghost_static: dict[int, dict[str, torch.Tensor]] = {}
         self.num_migrated = 0
         self.rebuild(migrate=False)
 
@@ -101,12 +102,35 @@ class ShardedBatch:
         m[: self.n_owned] = True
         return m
 
-    def padded_batch(self) -> Batch:
+    def halo_for(self, ghost_width: float) -> HaloExchange:
+        """A ghost plan of its own width over the same owned partition (members of a composite model need different
+        halo depths; a short-ranged member should not pay for the deepest one)."""
+        width = float(ghost_width)
+        if width > 0.0 and self.world > 1:
+            width += self.config.migration_hysteresis
+        if abs(width - self.halo.width) < 1e-12:
+            return self.halo
+        if width > self.halo.width:
+            raise ValueError("a member halo cannot be wider than the sharded batch's own halo")
+        key = round(width, 9)
+        if key not in self._extra_halos:
+            halo = HaloExchange(self.partitioner, width, self.group)
+            halo.build(self.owned.positions.detach(), self.global_ids)
+            self._extra_halos[key] = halo
+            self._ghost_static[id(halo)] = self._static_for(halo)
+        return self._extra_halos[key]
+
+    def _static_for(self, halo: HaloExchange) -> dict[str, torch.Tensor]:
+        return {k: halo.forward(getattr(self.owned, k)) for k in _GHOST_STATIC
+                if getattr(self.owned, k, None) is not None and getattr(self.owned, k).shape[0] == self.n_owned}
+
+    def padded_batch(self, halo: HaloExchange | None = None) -> Batch:
         """Owned rows followed by ghost rows, open boundaries, current positions."""
+        halo = halo if halo is not None else self.halo
         pos = self.owned.positions
-        allpos = torch.cat([self.halo.owned_positions(pos, self.cell), self.halo.forward_positions(pos, self.cell)])
+        allpos = torch.cat([halo.owned_positions(pos, self.cell), halo.forward_positions(pos, self.cell)])
         node = {"positions": allpos}
-        for k, ghost in self._ghost_static.items():
+        for k, ghost in self._ghost_static[id(halo)].items():
             node[k] = torch.cat([getattr(self.owned, k), ghost])
         system = {k: v for k, v in _system_fields(self.owned).items() if k in ("cell", "total_charge", "spin")}
         system["pbc"] = torch.zeros(1, 3, dtype=torch.bool, device=pos.device)
@@ -149,9 +173,10 @@ class ShardedBatch:
                 self.owned = _make_batch(fields, _system_fields(self.owned), self.owned)
                 self.num_migrated += int(total)
         self.halo.build(self.owned.positions.detach(), self.global_ids)
-        self._ghost_static = {k: self.halo.forward(getattr(self.owned, k)) for k in _GHOST_STATIC
-                              if getattr(self.owned, k, None) is not None
-                              and getattr(self.owned, k).shape[0] == self.n_owned}
+        self._ghost_static = {id(self.halo): self._static_for(self.halo)}
+        for halo in self._extra_halos.values():
+            halo.build(self.owned.positions.detach(), self.global_ids)
+            self._ghost_static[id(halo)] = self._static_for(halo)
         self._ref_positions = self.owned.positions.detach().clone()
 
     # ---- gathering -----------------------------------------------------------

@@ -88,5 +88,13 @@ class DemoModelWrapper(nn.Module, BaseModelMixin):
                 out["forces"] = -g
         return self.adapt_output(out, data)
 
+    def checkpoint_spec(self) -> dict:
+        return {"cls": "nvalchemi_toolkit_b200.models.demo.DemoModelWrapper", "config": {"hidden_dim": self.model.hidden_dim}}
+
+    def distribution_spec(self, strategy: Any = None) -> Any:
+        from nvalchemi_toolkit_b200.distributed.spec import SPEC_DEMO
+
+        return SPEC_DEMO
+
     def export_model(self, path: Any, as_state_dict: bool = False) -> None:
         torch.save(self.model.state_dict() if as_state_dict else self.model, path)

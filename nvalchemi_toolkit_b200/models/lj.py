@@ -86,6 +86,11 @@ class LennardJonesModelWrapper(nn.Module, BaseModelMixin):
         out["stress"] = -out["virial"] / vol[:, None, None]
         return self.adapt_output(out, data)
 
+    def checkpoint_spec(self) -> dict:
+        return {"cls": "nvalchemi_toolkit_b200.models.lj.LennardJonesModelWrapper",
+                "config": {"epsilon": self.epsilon, "sigma": self.sigma, "cutoff": self.cutoff,
+                           "switch_width": self.switch_width, "half_list": self.half_list}}
+
     def distribution_spec(self, strategy: Any = None) -> Any:
         from nvalchemi_toolkit_b200.distributed.spec import SPEC_LJ_HALO
 

@@ -297,7 +297,8 @@ class MACE(nn.Module):
                                   energy_weights=data.get("energy_weights"))
         sender, receiver, shifts = self._edges_from(data, positions, batch.long(), cell)
         need_grad = compute_force or compute_stress or compute_hessian
-        with torch.enable_grad() if need_grad else torch.no_grad():
+        keep_graph = need_grad or training or (positions.requires_grad and torch.is_grad_enabled())
+        with torch.enable_grad() if keep_graph else torch.no_grad():
             pos = positions
             strain = None
             if compute_stress and cell is not None:

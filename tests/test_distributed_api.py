@@ -245,3 +245,45 @@ def test_weighted_energy_reverse_halo_two_ranks():
         assert abs(res[r][1][0] - float(ref["energy"].detach().reshape(-1)[0])) < 1e-8
         assert torch.allclose(torch.tensor(res[r][2], dtype=torch.float64), ref["stress"].reshape(-1), atol=1e-8)
         assert res[r][3] > 0
+
+
+def _pipe_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        pipe = _lj() + LennardJonesModelWrapper(epsilon=0.02, sigma=3.0, cutoff=3.5, switch_width=0.5)
+        pipe.model_config.active_outputs = {"energy", "forces"}
+        dp = DomainParallel(NVE(pipe, dt=2.0), DomainConfig(cutoff=6.0, skin=0.5))
+        sh = dp.run(_lj_batch(4, velocities=0.05), n_steps=8)
+        widths = sorted([sh.halo.width] + [h.width for h in sh._extra_halos.values()])
+        q.put((rank, dp.gather().positions.tolist(), widths))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_domain_parallel_pipeline_model_uses_member_halos():
+    import torch.multiprocessing as mp
+
+    from nvalchemi_toolkit_b200.dynamics.base import DynamicsStage
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_pipe_worker, args=(r, 2, 29671, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(2):
+        item = q.get(timeout=240)
+        res[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=30)
+    pipe = _lj() + LennardJonesModelWrapper(epsilon=0.02, sigma=3.0, cutoff=3.5, switch_width=0.5)
+    pipe.model_config.active_outputs = {"energy", "forces"}
+    batch = _lj_batch(4, velocities=0.05)
+    dyn = NVE(pipe, dt=2.0, hooks=pipe.make_neighbor_hooks())
+    dyn._call_hooks(DynamicsStage.BEFORE_COMPUTE, batch)
+    dyn.compute(batch)
+    dyn.run(batch, n_steps=8)
+    assert torch.allclose(torch.tensor(res[0][0], dtype=torch.float64), batch.positions, atol=1e-9)
+    assert len(res[0][1]) == 2 and res[0][1][0] < res[0][1][1]  # the short-ranged member got a shallower halo
