@@ -20,7 +20,7 @@ from nvalchemi_toolkit_b200.distributed.halo import HaloExchange, _world, all_ga
 from nvalchemi_toolkit_b200.distributed.partitioner import SpatialPartitioner
 from nvalchemi_toolkit_b200.distributed.spec import MLIPSpec
 
-_GHOST_STATIC = ("atomic_numbers", "charges", "atom_categories")
+_GHOST_STATIC = ("atomic_numbers", "charges", "node_charges", "atom_categories")
 
 
 def _node_fields(batch: Batch) -> dict[str, torch.Tensor]:
@@ -137,7 +137,9 @@ class ShardedBatch:
         weights = torch.zeros(allpos.shape[0], dtype=pos.dtype, device=pos.device)
         weights[: self.n_owned] = 1.0
         node["energy_weights"] = weights
-        return _make_batch(node, system, self.owned)
+        padded = _make_batch(node, system, self.owned)
+        object.__setattr__(padded, "_dd", (self.group, self.world))  # models with global sums reduce over this group
+        return padded
 
     # ---- maintenance ---------------------------------------------------------
     def needs_rebuild(self) -> bool:
