@@ -1,0 +1,14 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Reporting stack: orchestrator hook, scalar extraction, Rich / TensorBoard / JSON-lines reporters."""
+from nvalchemi_toolkit_b200.hooks.reporting._core import (DEFAULT_REPORT_STAGES, Reporter, ReporterMessage,
+                                                         ReportingErrorPolicy, ReportingOrchestrator, ReportingState,
+                                                         ScalarSnapshot, collect_scalars, extract_dynamics_scalars,
+                                                         extract_loss_scalars, extract_optimizer_lr_scalars,
+                                                         extract_progress_scalars, reduce_scalars_across_ranks)
+from nvalchemi_toolkit_b200.hooks.reporting._reporters import (JSONLReporter, RichLayout, RichReporter,
+                                                              TensorBoardReporter, sparkline)
+
+__all__ = ["DEFAULT_REPORT_STAGES", "Reporter", "ReporterMessage", "ReportingErrorPolicy", "ReportingOrchestrator",
+           "ReportingState", "ScalarSnapshot", "collect_scalars", "extract_dynamics_scalars", "extract_loss_scalars",
+           "extract_optimizer_lr_scalars", "extract_progress_scalars", "reduce_scalars_across_ranks", "JSONLReporter",
+           "RichLayout", "RichReporter", "TensorBoardReporter", "sparkline"]

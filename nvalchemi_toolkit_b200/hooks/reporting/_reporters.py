@@ -1,0 +1,212 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Reporters: a Rich live dashboard, a TensorBoard writer and a JSON-lines file.
+
+Reference: ``nvalchemi/hooks/reporting/_rich.py`` (live table + history plots, layouts for training and dynamics),
+``_tensorboard.py`` (scalar writer with optional cross-rank reduction, rank-zero gating, injectable writer)."""
+from __future__ import annotations
+
+import json
+from collections import deque
+from enum import Enum
+from pathlib import Path
+from typing import Any, Mapping, Sequence
+
+from nvalchemi_toolkit_b200._optional import OptionalDependency
+from nvalchemi_toolkit_b200.hooks.reporting._core import (ReportingState, ScalarCallback, ScalarSnapshot, collect_scalars,
+                                                         reduce_scalars_across_ranks)
+
+_BARS = " ▁▂▃▄▅▆▇█"
+
+
+def sparkline(values: Sequence[float], width: int = 40) -> str:
+    vals = [v for v in values if v == v][-width:]
+    if not vals:
+        return ""
+    lo, hi = min(vals), max(vals)
+    span = (hi - lo) or 1.0
+    return "".join(_BARS[1 + int((v - lo) / span * (len(_BARS) - 2))] for v in vals)
+
+
+class RichLayout(str, Enum):
+    AUTO = "auto"
+    TRAIN = "train"
+    DYNAMICS = "dynamics"
+    COMPACT = "compact"
+
+
+_LAYOUT_KEYS = {RichLayout.TRAIN: ("loss/", "lr/", "validation/", "progress/"),
+                RichLayout.DYNAMICS: ("dynamics/", "progress/"), RichLayout.COMPACT: ("loss/total", "dynamics/fmax", "progress/step")}
+_LAYOUT_PLOTS = {RichLayout.TRAIN: ("loss/total",), RichLayout.DYNAMICS: ("dynamics/fmax", "dynamics/temperature"),
+                 RichLayout.COMPACT: ()}
+
+
+class _ScalarReporterBase:
+    def __init__(self, custom_scalars: Mapping[str, ScalarCallback] | None, include_losses: bool,
+                 include_optimizer_lrs: bool, include_dynamics_scalars: bool | None, rank_reduction: str | None,
+                 rank_zero_only: bool) -> None:
+        self.custom_scalars, self.include_losses = custom_scalars, include_losses
+        self.include_optimizer_lrs, self.include_dynamics_scalars = include_optimizer_lrs, include_dynamics_scalars
+        self.rank_reduction = None if rank_reduction is None else str(getattr(rank_reduction, "name", rank_reduction)).lower()
+        if self.rank_reduction == "avg":
+            self.rank_reduction = "mean"
+        self.rank_zero_only = rank_zero_only
+        self.requires_all_ranks = self.rank_reduction is not None  # a collective runs inside report()
+
+    def snapshot(self, ctx: Any, stage: Enum, state: ReportingState) -> ScalarSnapshot:
+        snap = collect_scalars(ctx, stage, state, include_losses=self.include_losses,
+                               include_optimizer_lrs=self.include_optimizer_lrs,
+                               include_dynamics_scalars=self.include_dynamics_scalars, custom_scalars=self.custom_scalars)
+        if self.rank_reduction is not None:
+            snap.scalars = reduce_scalars_across_ranks(snap.scalars, self.rank_reduction)
+        return snap
+
+    def _is_writer_rank(self) -> bool:
+        import torch.distributed as dist
+
+        return not self.rank_zero_only or not (dist.is_available() and dist.is_initialized()) or dist.get_rank() == 0
+
+
+class RichReporter(_ScalarReporterBase):
+    def __init__(self, *, custom_scalars: Mapping[str, ScalarCallback] | None = None, include_losses: bool = True,
+                 include_optimizer_lrs: bool = True, include_dynamics_scalars: bool | None = None,
+                 rank_reduction: str | None = None, title: str = "nvalchemi report", precision: int = 6,
+                 max_scalars: int | None = None, history_size: int = 200, layout: RichLayout | str | None = None,
+                 plot_keys: Sequence[str] | None = None, max_plots: int = 3, plot_height: int = 8,
+                 refresh_per_second: float = 2.0, console: Any = None, screen: bool = False, transient: bool = False,
+                 rank_zero_only: bool = True, strict_layout: bool = False) -> None:
+        super().__init__(custom_scalars, include_losses, include_optimizer_lrs, include_dynamics_scalars, rank_reduction,
+                         rank_zero_only)
+        self.title, self.precision, self.max_scalars = title, precision, max_scalars
+        self.layout = RichLayout(layout) if layout is not None else RichLayout.AUTO
+        self.plot_keys, self.max_plots, self.plot_height = plot_keys, max_plots, plot_height
+        self.refresh_per_second, self.console, self.screen, self.transient = refresh_per_second, console, screen, transient
+        self.strict_layout = strict_layout
+        self.history: dict[str, deque[float]] = {}
+        self._history_size = history_size
+        self._live: Any = None
+        self.last_snapshot: ScalarSnapshot | None = None
+
+    def _resolve_layout(self, snap: ScalarSnapshot) -> RichLayout:
+        if self.layout != RichLayout.AUTO:
+            return self.layout
+        return RichLayout.TRAIN if any(k.startswith("loss/") for k in snap.scalars) else RichLayout.DYNAMICS
+
+    def _select(self, snap: ScalarSnapshot, layout: RichLayout) -> list[tuple[str, float]]:
+        prefixes = _LAYOUT_KEYS[layout]
+        chosen = [(k, v) for k, v in sorted(snap.scalars.items()) if any(k.startswith(p) for p in prefixes)]
+        extra = [(k, v) for k, v in sorted(snap.scalars.items()) if (k, v) not in chosen]
+        if self.strict_layout:
+            extra = []
+        rows = chosen + extra
+        return rows[: self.max_scalars] if self.max_scalars is not None else rows
+
+    def render(self, snap: ScalarSnapshot, state: ReportingState) -> Any:
+        from rich.console import Group
+        from rich.panel import Panel
+        from rich.table import Table
+
+        layout = self._resolve_layout(snap)
+        table = Table(title=f"{self.title}  step {snap.step}" + (f"  epoch {snap.epoch}" if snap.epoch is not None else ""),
+                      expand=True)
+        table.add_column("scalar")
+        table.add_column("value", justify="right")
+        table.add_column("history")
+        for k, v in self._select(snap, layout):
+            table.add_row(k, f"{v:.{self.precision}g}", sparkline(self.history.get(k, ()), 30))
+        parts: list[Any] = [table]
+        keys = list(self.plot_keys) if self.plot_keys is not None else list(_LAYOUT_PLOTS[layout])
+        for k in keys[: self.max_plots]:
+            if k in self.history and len(self.history[k]) > 1:
+                h = list(self.history[k])
+                parts.append(Panel(sparkline(h, 80), title=f"{k}  min {min(h):.4g}  max {max(h):.4g}", height=3))
+        recent = [m for m in list(state.messages)[-3:]]
+        if recent:
+            parts.append(Panel("\n".join(f"[{m.level}] {m.text}" for m in recent), title="messages"))
+        return Group(*parts)
+
+    def __enter__(self) -> "RichReporter":
+        if self._is_writer_rank():
+            from rich.live import Live
+
+            self._live = Live(console=self.console, refresh_per_second=self.refresh_per_second, screen=self.screen,
+                              transient=self.transient)
+            self._live.__enter__()
+        return self
+
+    def __exit__(self, *exc: Any) -> None:
+        if self._live is not None:
+            self._live.__exit__(*exc)
+            self._live = None
+
+    def report(self, ctx: Any, stage: Enum, state: ReportingState) -> None:
+        snap = self.snapshot(ctx, stage, state)
+        if not self._is_writer_rank():
+            return
+        for k, v in snap.scalars.items():
+            self.history.setdefault(k, deque(maxlen=self._history_size)).append(v)
+        self.last_snapshot = snap
+        view = self.render(snap, state)
+        if self._live is not None:
+            self._live.update(view)
+        else:
+            from rich.console import Console
+
+            (self.console or Console()).print(view)
+
+
+class TensorBoardReporter(_ScalarReporterBase):
+    def __init__(self, log_dir: str | Path, *, custom_scalars: Mapping[str, ScalarCallback] | None = None,
+                 include_losses: bool = True, include_optimizer_lrs: bool = True, rank_reduction: str | None = None,
+                 tag_prefix: str | None = None, flush: bool = True, rank_zero_only: bool = True, writer: Any = None) -> None:
+        super().__init__(custom_scalars, include_losses, include_optimizer_lrs, None, rank_reduction, rank_zero_only)
+        self.log_dir, self.tag_prefix, self.flush = Path(log_dir), tag_prefix, flush
+        self._writer, self._owns_writer = writer, writer is None
+
+    def _get_writer(self) -> Any:
+        if self._writer is None:
+            OptionalDependency.TENSORBOARD.import_module()
+            from torch.utils.tensorboard import SummaryWriter
+
+            self.log_dir.mkdir(parents=True, exist_ok=True)
+            self._writer = SummaryWriter(log_dir=str(self.log_dir))
+        return self._writer
+
+    def report(self, ctx: Any, stage: Enum, state: ReportingState) -> None:
+        snap = self.snapshot(ctx, stage, state)
+        if not self._is_writer_rank():
+            return
+        w = self._get_writer()
+        for k, v in snap.scalars.items():
+            w.add_scalar(f"{self.tag_prefix}/{k}" if self.tag_prefix else k, v, global_step=snap.step)
+        if self.flush and hasattr(w, "flush"):
+            w.flush()
+
+    def close(self) -> None:
+        if self._writer is not None and self._owns_writer:
+            self._writer.close()
+            self._writer = None
+
+
+class JSONLReporter(_ScalarReporterBase):
+    """One JSON object per event; convenient for batch jobs without a terminal."""
+
+    def __init__(self, path: str | Path, *, custom_scalars: Mapping[str, ScalarCallback] | None = None,
+                 rank_reduction: str | None = None, rank_zero_only: bool = True) -> None:
+        super().__init__(custom_scalars, True, True, None, rank_reduction, rank_zero_only)
+        self.path = Path(path)
+        self._fh: Any = None
+
+    def report(self, ctx: Any, stage: Enum, state: ReportingState) -> None:
+        snap = self.snapshot(ctx, stage, state)
+        if not self._is_writer_rank():
+            return
+        if self._fh is None:
+            self.path.parent.mkdir(parents=True, exist_ok=True)
+            self._fh = open(self.path, "a", encoding="utf-8")
+        self._fh.write(json.dumps(snap.as_dict()) + "\n")
+        self._fh.flush()
+
+    def close(self) -> None:
+        if self._fh is not None:
+            self._fh.close()
+            self._fh = None
