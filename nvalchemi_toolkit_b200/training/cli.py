@@ -1,0 +1,351 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Command line for training jobs: ``python -m nvalchemi_toolkit_b200.training.cli <group> <command>``.
+
+Reference: ``nvalchemi/training/cli.py:165-2229``: click groups ``train`` (``run`` / ``resume``), ``finetune``,
+``init`` (write a template job file), ``schema`` (JSON schema of the job file), ``spec`` (``validate`` / ``show``); a job
+is a ``TrainingJobSpec`` read from JSON or YAML; a run ends with a report (final losses, learning-rate curve,
+warnings).  Classes are named by dotted import paths; nothing is unpickled.
+"""
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+from typing import Any
+
+import click
+import torch
+from pydantic import BaseModel, ConfigDict, Field, model_validator
+
+from nvalchemi_toolkit_b200._serialization import import_from_path
+
+
+class ComponentSpec(BaseModel):
+    """``cls`` (dotted path) called with ``kwargs``; ``checkpoint`` (optional) is passed to ``cls.from_checkpoint``."""
+
+    model_config = ConfigDict(populate_by_name=True)
+    cls: str
+    kwargs: dict[str, Any] = Field(default_factory=dict)
+    checkpoint: str | None = None
+
+    def build(self) -> Any:
+        klass = import_from_path(self.cls)
+        if self.checkpoint is not None:
+            return klass.from_checkpoint(self.checkpoint, **self.kwargs)
+        return klass(**self.kwargs)
+
+
+class DataSpec(BaseModel):
+    train: str
+    validation: str | None = None
+    batch_size: int = 8
+    shuffle: bool = True
+    drop_last: bool = False
+    num_workers: int = 2
+    neighbor_cutoff: float | None = None  # build neighbour data per batch when the store has none
+
+
+class OptimizerSpec(BaseModel):
+    cls: str = "torch.optim.Adam"
+    kwargs: dict[str, Any] = Field(default_factory=lambda: {"lr": 1e-3})
+    scheduler_cls: str | None = None
+    scheduler_kwargs: dict[str, Any] = Field(default_factory=dict)
+    scheduler_metric: str | None = None
+    scheduler_interval: str = "step"
+
+
+class ValidationSpec(BaseModel):
+    every_n_steps: int | None = None
+    every_n_epochs: int | None = 1
+
+
+class ReportingSpec(BaseModel):
+    rich: bool = False
+    tensorboard_dir: str | None = None
+    jsonl: str | None = "metrics.jsonl"
+    frequency: int = 1
+
+
+class FineTuneSpec(BaseModel):
+    checkpoint: str
+    trainable: list[str] = Field(default_factory=list)
+    strict: bool = False
+
+
+class TrainingJobSpec(BaseModel):
+    model: ComponentSpec
+    data: DataSpec
+    loss: list[dict[str, Any]] = Field(default_factory=lambda: [
+        {"cls": "EnergyMSELoss", "weight": 1.0}, {"cls": "ForceMSELoss", "weight": 10.0}])
+    optimizer: OptimizerSpec = Field(default_factory=OptimizerSpec)
+    num_epochs: int | None = None
+    num_steps: int | None = None
+    hooks: list[ComponentSpec] = Field(default_factory=list)
+    validation: ValidationSpec | None = None
+    reporting: ReportingSpec = Field(default_factory=ReportingSpec)
+    finetune: FineTuneSpec | None = None
+    output_dir: str = "runs/job"
+    checkpoint_every_n_steps: int | None = None
+    checkpoint_every_n_epochs: int | None = 1
+    devices: list[str] | None = None
+    seed: int = 0
+    active_outputs: list[str] = Field(default_factory=lambda: ["energy", "forces"])
+
+    @model_validator(mode="after")
+    def _one_budget(self) -> "TrainingJobSpec":
+        if (self.num_epochs is None) == (self.num_steps is None):
+            raise ValueError("give exactly one of num_epochs / num_steps")
+        return self
+
+    @classmethod
+    def from_file(cls, path: str | Path) -> "TrainingJobSpec":
+        path = Path(path)
+        text = path.read_text()
+        if path.suffix in (".yaml", ".yml"):
+            import yaml
+
+            return cls.model_validate(yaml.safe_load(text))
+        return cls.model_validate(json.loads(text))
+
+    def to_file(self, path: str | Path) -> None:
+        path = Path(path)
+        data = self.model_dump(mode="json")
+        if path.suffix in (".yaml", ".yml"):
+            import yaml
+
+            path.write_text(yaml.safe_dump(data, sort_keys=False))
+        else:
+            path.write_text(json.dumps(data, indent=2))
+
+
+def template_spec() -> TrainingJobSpec:
+    return TrainingJobSpec(
+        model=ComponentSpec(cls="nvalchemi_toolkit_b200.models.mace.MACEWrapper",
+                            kwargs={"atomic_numbers": [1, 6, 8], "channels": 64, "r_max": 5.0}),
+        data=DataSpec(train="data/train.zarr", validation="data/val.zarr", batch_size=16, neighbor_cutoff=5.0),
+        num_epochs=10, validation=ValidationSpec(every_n_epochs=1),
+        optimizer=OptimizerSpec(kwargs={"lr": 1e-3}, scheduler_cls="torch.optim.lr_scheduler.ExponentialLR",
+                                scheduler_kwargs={"gamma": 0.999}))
+
+
+# ---- building and running ------------------------------------------------------------------------------------------
+class _NeighborTransform:
+    """Adds neighbour data to each batch (stores written without edges)."""
+
+    def __init__(self, loader: Any, config: Any) -> None:
+        self.loader, self.config = loader, config
+
+    def __len__(self) -> int:
+        return len(self.loader)
+
+    def __iter__(self) -> Any:
+        from nvalchemi_toolkit_b200 import neighbors as nb
+
+        for batch in self.loader:
+            nb.compute_neighbors(batch, config=self.config)
+            yield batch
+
+    def __getattr__(self, name: str) -> Any:
+        return getattr(self.loader, name)
+
+
+def _loader(path: str, data: DataSpec, model: Any, shuffle: bool, seed: int) -> Any:
+    from nvalchemi_toolkit_b200.data.datapipes import DataLoader, Dataset
+    from nvalchemi_toolkit_b200.data.zarr_store import AtomicDataZarrReader
+
+    ds = Dataset(AtomicDataZarrReader(path), num_workers=data.num_workers)
+    loader = DataLoader(ds, batch_size=data.batch_size, shuffle=shuffle, drop_last=data.drop_last, seed=seed)
+    nc = getattr(getattr(model, "model_config", None), "neighbor_config", None)
+    if nc is not None and data.neighbor_cutoff is not None:
+        return _NeighborTransform(loader, nc)
+    return loader
+
+
+def build_job(spec: TrainingJobSpec) -> tuple[Any, Any, Any]:
+    """``(strategy, train_loader, validation_loader)`` for a job file."""
+    from nvalchemi_toolkit_b200.hooks.reporting import JSONLReporter, ReportingOrchestrator, RichReporter, TensorBoardReporter
+    from nvalchemi_toolkit_b200.training import ComposedLossFunction, OptimizerConfig, TrainingStrategy, ValidationConfig
+    from nvalchemi_toolkit_b200.training.finetune import FineTuningStrategy
+    from nvalchemi_toolkit_b200.training.hooks.library import CheckpointHook
+
+    torch.manual_seed(spec.seed)
+    model = spec.model.build()
+    if hasattr(model, "model_config"):
+        model.model_config.active_outputs = set(spec.active_outputs)
+    out = Path(spec.output_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    train = _loader(spec.data.train, spec.data, model, spec.data.shuffle, spec.seed)
+    val = _loader(spec.data.validation, spec.data, model, False, spec.seed) if spec.data.validation else None
+    hooks: list[Any] = [h.build() for h in spec.hooks]
+    hooks.append(CheckpointHook(out / "checkpoints", every_n_steps=spec.checkpoint_every_n_steps,
+                                every_n_epochs=spec.checkpoint_every_n_epochs))
+    reporters: list[Any] = []
+    rep = spec.reporting
+    if rep.rich:
+        reporters.append(RichReporter(title=f"training {out.name}"))
+    if rep.tensorboard_dir:
+        reporters.append(TensorBoardReporter(rep.tensorboard_dir))
+    if rep.jsonl:
+        reporters.append(JSONLReporter(out / rep.jsonl))
+    if reporters:
+        hooks.append(ReportingOrchestrator(reporters, frequency=rep.frequency, error_policy="warn"))
+    vcfg = None
+    if spec.validation is not None and val is not None:
+        vcfg = ValidationConfig(data=val, every_n_steps=spec.validation.every_n_steps,
+                                every_n_epochs=spec.validation.every_n_epochs)
+    kw = dict(optimizer_configs=OptimizerConfig(**spec.optimizer.model_dump()), loss_fn=ComposedLossFunction.from_spec(spec.loss),
+              num_epochs=spec.num_epochs, num_steps=spec.num_steps, hooks=hooks, validation_config=vcfg,
+              devices=spec.devices)
+    if spec.finetune is not None:
+        strategy = FineTuningStrategy(model, checkpoint=spec.finetune.checkpoint, trainable=spec.finetune.trainable or None,
+                                      strict=spec.finetune.strict, **kw)
+    else:
+        strategy = TrainingStrategy(model, **kw)
+    return strategy, train, val
+
+
+def final_report(strategy: Any, spec: TrainingJobSpec, console: Any = None) -> dict[str, Any]:
+    """Summary table, learning-rate curve and warnings; also written to ``report.json`` in the output directory."""
+    from rich.console import Console
+    from rich.table import Table
+
+    from nvalchemi_toolkit_b200.hooks.reporting import ReportingOrchestrator, sparkline
+
+    out = Path(spec.output_dir)
+    summary: dict[str, Any] = {"steps": strategy.step_count, "epochs": strategy.epoch_count,
+                               "losses": {k: float(v) for k, v in (strategy.last_losses or {}).items()
+                                          if isinstance(v, torch.Tensor) and v.numel() == 1},
+                               "validation": {k: float(v) for k, v in (strategy.last_validation or {}).items()
+                                              if isinstance(v, (int, float)) or (isinstance(v, torch.Tensor) and v.numel() == 1)},
+                               "warnings": []}
+    lr_curve: list[float] = []
+    metrics = out / (spec.reporting.jsonl or "metrics.jsonl")
+    if metrics.exists():
+        for line in metrics.read_text().splitlines():
+            row = json.loads(line)
+            if "lr/opt0" in row:
+                lr_curve.append(row["lr/opt0"])
+    for hook in strategy.hooks:
+        if isinstance(hook, ReportingOrchestrator):
+            summary["warnings"] += [m.text for m in hook.state.messages if m.level in ("warning", "error")]
+    if summary["losses"] and any(v != v for v in summary["losses"].values()):
+        summary["warnings"].append("a loss term is NaN")
+    summary["lr_curve"] = lr_curve[-200:]
+    table = Table(title=f"job {out.name}: {summary['steps']} steps, {summary['epochs']} epochs")
+    table.add_column("quantity")
+    table.add_column("value", justify="right")
+    for k, v in summary["losses"].items():
+        table.add_row(f"loss/{k}", f"{v:.6g}")
+    for k, v in summary["validation"].items():
+        table.add_row(f"validation/{k}", f"{v:.6g}")
+    if lr_curve:
+        table.add_row("learning rate", f"{lr_curve[0]:.3g} → {lr_curve[-1]:.3g}  {sparkline(lr_curve, 40)}")
+    for w in summary["warnings"]:
+        table.add_row("warning", w)
+    (console or Console()).print(table)
+    (out / "report.json").write_text(json.dumps(summary, indent=2))
+    return summary
+
+
+def run_job(spec: TrainingJobSpec, resume: bool = False, console: Any = None) -> dict[str, Any]:
+    strategy, train, val = build_job(spec)
+    out = Path(spec.output_dir)
+    spec.to_file(out / "job.json")
+    if resume:
+        ckpt_dir = out / "checkpoints"
+        if not (ckpt_dir / "manifest.json").exists():
+            raise click.ClickException(f"nothing to resume from in {ckpt_dir}")
+        strategy.load_checkpoint(ckpt_dir)
+    strategy.run(train, val)
+    return final_report(strategy, spec, console)
+
+
+# ---- click groups ----------------------------------------------------------------------------------------------------
+@click.group()
+def main() -> None:
+    """Training jobs described by a JSON / YAML file."""
+
+
+@main.group()
+def train() -> None:
+    """Run or resume a training job."""
+
+
+@train.command("run")
+@click.argument("job", type=click.Path(exists=True))
+@click.option("--output-dir", default=None, help="override the job file's output_dir")
+def train_run(job: str, output_dir: str | None) -> None:
+    spec = TrainingJobSpec.from_file(job)
+    if output_dir:
+        spec.output_dir = output_dir
+    run_job(spec)
+
+
+@train.command("resume")
+@click.argument("job", type=click.Path(exists=True))
+@click.option("--output-dir", default=None)
+def train_resume(job: str, output_dir: str | None) -> None:
+    spec = TrainingJobSpec.from_file(job)
+    if output_dir:
+        spec.output_dir = output_dir
+    run_job(spec, resume=True)
+
+
+@main.command("finetune")
+@click.argument("job", type=click.Path(exists=True))
+@click.option("--checkpoint", default=None, help="weights to start from (overrides finetune.checkpoint)")
+@click.option("--trainable", multiple=True, help="parameter-name patterns that stay trainable")
+def finetune(job: str, checkpoint: str | None, trainable: tuple[str, ...]) -> None:
+    """Run a job as fine-tuning from a checkpoint."""
+    spec = TrainingJobSpec.from_file(job)
+    base = spec.finetune or (FineTuneSpec(checkpoint=checkpoint) if checkpoint else None)
+    if base is None:
+        raise click.ClickException("no checkpoint: give --checkpoint or a finetune section")
+    if checkpoint:
+        base.checkpoint = checkpoint
+    if trainable:
+        base.trainable = list(trainable)
+    spec.finetune = base
+    run_job(spec)
+
+
+@main.command("init")
+@click.argument("path", type=click.Path())
+@click.option("--force", is_flag=True)
+def init(path: str, force: bool) -> None:
+    """Write a template job file (JSON or YAML by extension)."""
+    if Path(path).exists() and not force:
+        raise click.ClickException(f"{path} exists (use --force)")
+    template_spec().to_file(path)
+    click.echo(f"wrote {path}")
+
+
+@main.command("schema")
+def schema() -> None:
+    """Print the JSON schema of a job file."""
+    click.echo(json.dumps(TrainingJobSpec.model_json_schema(), indent=2))
+
+
+@main.group()
+def spec() -> None:
+    """Inspect job files."""
+
+
+@spec.command("validate")
+@click.argument("job", type=click.Path(exists=True))
+def spec_validate(job: str) -> None:
+    try:
+        TrainingJobSpec.from_file(job)
+    except Exception as exc:  # noqa: BLE001 - report every validation problem the same way
+        raise click.ClickException(f"invalid job file: {exc}") from exc
+    click.echo("ok")
+
+
+@spec.command("show")
+@click.argument("job", type=click.Path(exists=True))
+def spec_show(job: str) -> None:
+    click.echo(json.dumps(TrainingJobSpec.from_file(job).model_dump(mode="json"), indent=2))
+
+
+if __name__ == "__main__":
+    sys.exit(main())

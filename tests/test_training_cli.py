@@ -1,0 +1,78 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Training CLI: job files, init/schema/spec commands, run + resume + fine-tune on a small Zarr data set."""
+import json
+
+import pytest
+import torch
+from click.testing import CliRunner
+
+from nvalchemi_toolkit_b200 import Batch
+from nvalchemi_toolkit_b200.data.zarr_store import AtomicDataZarrWriter
+from nvalchemi_toolkit_b200.training import cli
+from tests.test_training import _dataset
+
+
+def _store(path, n, seed):
+    AtomicDataZarrWriter(path).append(Batch.from_data_list(_dataset(n, seed)))
+
+
+def _job(tmp_path, **kw):
+    _store(tmp_path / "train.zarr", 12, 0)
+    _store(tmp_path / "val.zarr", 4, 1)
+    spec = cli.TrainingJobSpec(
+        model=cli.ComponentSpec(cls="nvalchemi_toolkit_b200.models.demo.DemoModelWrapper", kwargs={"hidden_dim": 16}),
+        data=cli.DataSpec(train=str(tmp_path / "train.zarr"), validation=str(tmp_path / "val.zarr"), batch_size=4, shuffle=False),
+        output_dir=str(tmp_path / "run"), devices=["cpu"], validation=cli.ValidationSpec(every_n_epochs=1),
+        optimizer=cli.OptimizerSpec(kwargs={"lr": 1e-2}, scheduler_cls="torch.optim.lr_scheduler.ExponentialLR",
+                                    scheduler_kwargs={"gamma": 0.9}), **kw)
+    path = tmp_path / "job.yaml"
+    spec.to_file(path)
+    return path
+
+
+def test_init_schema_and_spec_commands(tmp_path):
+    r = CliRunner()
+    out = r.invoke(cli.main, ["init", str(tmp_path / "t.json")])
+    assert out.exit_code == 0 and json.loads((tmp_path / "t.json").read_text())["model"]["cls"].endswith("MACEWrapper")
+    assert r.invoke(cli.main, ["init", str(tmp_path / "t.json")]).exit_code != 0  # refuses to overwrite
+    assert r.invoke(cli.main, ["spec", "validate", str(tmp_path / "t.json")]).output.strip() == "ok"
+    schema = json.loads(r.invoke(cli.main, ["schema"]).output)
+    assert "num_epochs" in schema["properties"] and "model" in schema["required"]
+    bad = tmp_path / "bad.json"
+    bad.write_text(json.dumps({"model": {"cls": "x.Y"}, "data": {"train": "a"}, "num_epochs": 1, "num_steps": 5}))
+    res = r.invoke(cli.main, ["spec", "validate", str(bad)])
+    assert res.exit_code != 0 and "exactly one" in res.output
+    shown = json.loads(r.invoke(cli.main, ["spec", "show", str(tmp_path / "t.json")]).output)
+    assert shown["data"]["neighbor_cutoff"] == 5.0
+
+
+def test_run_resume_and_finetune(tmp_path):
+    job = _job(tmp_path, num_epochs=2)
+    r = CliRunner()
+    res = r.invoke(cli.main, ["train", "run", str(job)])
+    assert res.exit_code == 0, res.output
+    run = tmp_path / "run"
+    report = json.loads((run / "report.json").read_text())
+    assert report["steps"] == 6 and report["epochs"] == 2 and "total_loss" in report["losses"]
+    assert len(report["lr_curve"]) == 6 and report["lr_curve"][-1] < report["lr_curve"][0]
+    assert (run / "checkpoints" / "manifest.json").exists() and (run / "job.json").exists()
+    rows = [json.loads(l) for l in (run / "metrics.jsonl").read_text().splitlines()]
+    assert rows[-1]["loss/total"] < rows[0]["loss/total"]
+    # resume with a larger budget continues from the stored counters
+    spec = cli.TrainingJobSpec.from_file(job)
+    spec.num_epochs = 3
+    spec.to_file(job)
+    res = r.invoke(cli.main, ["train", "resume", str(job)])
+    assert res.exit_code == 0, res.output
+    assert json.loads((run / "report.json").read_text())["steps"] == 9
+    # fine-tune only the projection head from the exported weights
+    from nvalchemi_toolkit_b200.models.demo import DemoModelWrapper
+
+    w = DemoModelWrapper(hidden_dim=16)
+    torch.save(w.model.state_dict(), tmp_path / "w.pt")
+    spec.output_dir, spec.num_epochs = str(tmp_path / "ft"), 1
+    spec.to_file(job)
+    res = r.invoke(cli.main, ["finetune", str(job), "--checkpoint", str(tmp_path / "w.pt"), "--trainable", "projection"])
+    assert res.exit_code == 0, res.output
+    assert json.loads((tmp_path / "ft" / "report.json").read_text())["steps"] == 3
+    assert r.invoke(cli.main, ["train", "resume", str(job), "--output-dir", str(tmp_path / "nothing")]).exit_code != 0
