@@ -72,7 +72,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_system(cells: int, device, seed: int = 0):
+def build_system(cells: int, device, seed: int = 0, atom_order: str = "lattice"):
     import torch
 
     from nvalchemi_toolkit_b200 import AtomicData, Batch
@@ -84,6 +84,10 @@ def build_system(cells: int, device, seed: int = 0):
     grid = torch.stack(torch.meshgrid(r, r, r, indexing="ij"), -1).reshape(-1, 1, 3)
     pos = ((grid + base[None]).reshape(-1, 3) * a)
     pos = pos + 0.05 * torch.randn(pos.shape, generator=g, device=device)
+    if atom_order == "morton":
+        from nvalchemi_toolkit_b200.utils.spatial import morton_order
+
+        pos = pos[morton_order(pos, torch.eye(3, device=device) * a * cells, 4.0)].contiguous()
     n = pos.shape[0]
     data = AtomicData.model_construct(
         atomic_numbers=torch.full((n,), 29, dtype=torch.long, device=device), positions=pos,
@@ -130,11 +134,12 @@ def run_ours(args) -> dict:
     if world > 1:
         from nvalchemi_toolkit_b200.distributed.slab_md import SlabDomainMD
 
-        sim = SlabDomainMD.for_benchmark(cells=cells, device=device, skin=args.skin, max_neighbors=args.max_neighbors)
+        sim = SlabDomainMD.for_benchmark(cells=cells, device=device, skin=args.skin, max_neighbors=args.max_neighbors,
+                                         atom_order=args.atom_order)
         step, sync_energy, e2e_step, counts = sim.step, sim.energy, sim.host_driven_step, sim.e2e_bytes()
         parallelism = f"dd{world} (slabs along x, halo 10 A)"
     else:
-        batch = build_system(cells, device)
+        batch = build_system(cells, device, atom_order=args.atom_order)
         dyn, wrapper = build_dynamics(device, args.skin, args.max_neighbors)
         _ops.initialize_velocities(batch.velocities, batch.atomic_masses, 300.0, batch.batch_idx, random_seed=1)
         dyn._call_hooks(type(dyn)._stage_type.BEFORE_COMPUTE, batch)
@@ -200,7 +205,7 @@ def run_ours(args) -> dict:
         "vs_baseline": None, "dtype": "fp32 (tf32 tensor-core channel mixes)", "data": "synthetic",
         "config": {"model": "MACE 2 layers 128x0e+128x1o lmax3 corr3 8 Bessel rc=5A (random init)",
                    "global_batch": n_atoms_total, "seq_len": None, "parallelism": parallelism, "atoms": n_atoms_total,
-                   "dt_fs": 1.0, "thermostat": "Langevin 300K gamma=0.01/fs", "neighbor_skin_A": args.skin,
+                   "dt_fs": 1.0, "thermostat": "Langevin 300K gamma=0.01/fs", "neighbor_skin_A": args.skin, "atom_order": args.atom_order,
                    "l2_policy": "per-step working set (node features, edge lists) is tens of GB, far larger than the 126 MB L2"},
         "clocks": clocks,
         "e2e": {"value": n_atoms_total * args.steps / (ms_e2e * 1e-3), "unit": "atom-steps/s",
@@ -238,6 +243,8 @@ def main() -> None:
     ap.add_argument("--cells", type=int, default=64, help="conventional fcc cells per edge (64 -> 1,048,576 atoms)")
     ap.add_argument("--skin", type=float, default=0.0, help="Verlet skin; 0 rebuilds the list every step (cheaper than the extra edges at this size)")
     ap.add_argument("--max-neighbors", type=int, default=64)
+    ap.add_argument("--atom-order", default="lattice", choices=["lattice", "morton"],
+                    help="memory order of the synthetic atoms: x-major lattice order or a Z-curve over 4 A bins")
     args = ap.parse_args()
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:

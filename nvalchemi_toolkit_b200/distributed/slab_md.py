@@ -311,7 +311,7 @@ class SlabDomainMD:
     # ------------------------------------------------------------------ benchmark helpers
     @classmethod
     def for_benchmark(cls, cells: int, device: torch.device, skin: float = 0.0, max_neighbors: int = 64,
-                      halo_skin: float = 1.0) -> "SlabDomainMD":
+                      halo_skin: float = 1.0, atom_order: str = "lattice") -> "SlabDomainMD":
         """fcc Cu supercell of ``cells^3`` conventional cells; every rank generates only its own slab."""
         from nvalchemi_toolkit_b200.models.mace import MACE, MACEConfig
 
@@ -334,6 +334,11 @@ class SlabDomainMD:
         gid = torch.arange(n, device=device) + 4 * cells * cells * x0
         g = torch.Generator(device=device).manual_seed(1000 + rank)
         pos = pos + 0.05 * torch.randn(pos.shape, generator=g, device=device) + 0.01
+        if atom_order == "morton":  # memory order along a Z-curve: neighbour gathers stay in L2
+            from nvalchemi_toolkit_b200.utils.spatial import morton_order
+
+            perm = morton_order(pos, cell.to(device), 4.0)
+            pos, gid = pos[perm].contiguous(), gid[perm].contiguous()
         mass = torch.full((n,), 63.546, device=device)
         vel = torch.zeros_like(pos)
         _ops.initialize_velocities(vel, mass, 300.0, torch.zeros(n, dtype=torch.int32, device=device), random_seed=1,

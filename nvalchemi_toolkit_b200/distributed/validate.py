@@ -1,0 +1,145 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Checks that a model evaluates identically with and without domain decomposition.
+
+Reference: ``nvalchemi/distributed/validate/*.py`` (``trace_and_validate``: reference run → spawn N ranks → diff →
+suggested fixes; halo-completeness check).  Here: :func:`check_halo_completeness` verifies that every owned atom sees
+the same number of neighbours in its padded sub-domain as in the full system; :func:`trace_and_validate` runs the
+model once on the whole batch and once on ``world_size`` gloo ranks on CPU, compares energy / forces / stress, and, if
+they differ, tries the usual repairs (a deeper halo; the other consolidation mode) and reports which one works.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field, replace
+from types import SimpleNamespace
+from typing import Any, Callable
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class ValidationReport:
+    ok: bool
+    max_abs_diff: dict[str, float]
+    world_size: int
+    spec_name: str
+    suggestion: str | None = None
+    attempts: list[dict[str, Any]] = field(default_factory=list)
+
+    def __str__(self) -> str:
+        head = "PASS" if self.ok else "FAIL"
+        diffs = ", ".join(f"{k} {v:.3e}" for k, v in self.max_abs_diff.items())
+        tail = f"; suggestion: {self.suggestion}" if self.suggestion else ""
+        return f"[{head}] {self.spec_name} on {self.world_size} ranks: {diffs}{tail}"
+
+
+def check_halo_completeness(sharded: Any, cutoff: float, global_batch: Any) -> tuple[bool, int]:
+    """``(complete, number of owned atoms with missing neighbours)`` for one rank's padded sub-domain."""
+    from nvalchemi_toolkit_b200 import neighbors as nb
+
+    padded = sharded.padded_batch()
+    nb.compute_neighbors(padded, cutoff)
+    full = global_batch.clone()
+    nb.compute_neighbors(full, cutoff)
+    want = full.num_neighbors[sharded.global_ids.to(full.device)]
+    got = padded.num_neighbors[: sharded.n_owned]
+    missing = int((got.cpu() != want.cpu()).sum())
+    return missing == 0, missing
+
+
+def _reference(model: Any, batch: Any) -> dict:
+    for h in model.make_neighbor_hooks():
+        h(SimpleNamespace(batch=batch), None)
+    return {k: v.detach().clone() for k, v in model(batch).items() if isinstance(v, torch.Tensor)}
+
+
+def _worker(rank: int, world: int, port: int, q: Any, model_factory: Callable, batch_factory: Callable, cfg_kwargs: dict,
+            spec: Any) -> None:
+    from nvalchemi_toolkit_b200.distributed import DistributedModel, DomainConfig, ShardedBatch, ShardTensor
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        model, batch = model_factory(), batch_factory()
+        cfg = DomainConfig(**cfg_kwargs)
+        use = spec if spec is not None else model.distribution_spec()
+        sh = ShardedBatch.from_batch(batch, cfg, use)
+        out = DistributedModel(model, cfg, use)(sh)
+        res = {}
+        for k, v in out.items():
+            if not isinstance(v, torch.Tensor):
+                continue
+            res[k] = (ShardTensor(v, sh).full_tensor() if v.dim() >= 1 and v.shape[0] == sh.n_owned and k not in
+                      use.extensive_outputs else v).tolist()
+        complete, missing = check_halo_completeness(sh, cfg.cutoff, batch) if model.model_config.neighbor_config else (True, 0)
+        if rank == 0:
+            q.put((res, missing))
+        else:
+            q.put((None, missing))
+    finally:
+        dist.destroy_process_group()
+
+
+def _spawn(world: int, port: int, model_factory: Callable, batch_factory: Callable, cfg_kwargs: dict, spec: Any
+           ) -> tuple[dict, int]:
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, model_factory, batch_factory, cfg_kwargs, spec))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=30)
+    res = next(r for r, _ in got if r is not None)
+    return res, sum(m for _, m in got)
+
+
+def _diff(ref: dict, res: dict, keys: tuple[str, ...]) -> dict[str, float]:
+    out = {}
+    for k in keys:
+        if k in ref and k in res:
+            a, b = ref[k].double().reshape(-1), torch.tensor(res[k], dtype=torch.float64).reshape(-1)
+            out[k] = float((a - b).abs().max()) if a.numel() == b.numel() else float("inf")
+    return out
+
+
+def trace_and_validate(model_factory: Callable, batch_factory: Callable, world_size: int = 2, *, cutoff: float,
+                       skin: float = 0.0, spec: Any = None, atol: float = 1e-6, port: int = 29733,
+                       keys: tuple[str, ...] = ("energy", "forces", "stress"), auto_fix: bool = True) -> ValidationReport:
+    """``model_factory`` / ``batch_factory`` must be importable top-level callables (they run in spawned processes)."""
+    from nvalchemi_toolkit_b200.distributed.spec import Consolidation
+
+    model = model_factory()
+    ref = _reference(model, batch_factory())
+    base = spec if spec is not None else model.distribution_spec()
+    cfg = {"cutoff": cutoff, "skin": skin}
+    attempts = []
+
+    def attempt(s: Any, label: str, p: int) -> tuple[bool, dict[str, float]]:
+        res, missing = _spawn(world_size, p, model_factory, batch_factory, cfg, s)
+        d = _diff(ref, res, keys)
+        ok = all(v <= atol for v in d.values())
+        attempts.append({"label": label, "ok": ok, "diff": d, "atoms_with_missing_neighbors": missing})
+        return ok, d
+
+    ok, d = attempt(base, "declared spec", port)
+    suggestion = None
+    if not ok and auto_fix:
+        fixes = [(replace(base, message_passes=base.message_passes + 1), f"message_passes={base.message_passes + 1} (deeper halo)")]
+        other = Consolidation.WEIGHTED_ENERGY if base.consolidation == Consolidation.DIRECT_MASKED else Consolidation.DIRECT_MASKED
+        fixes.append((replace(base, consolidation=other), f"consolidation={other.value}"))
+        for i, (s, label) in enumerate(fixes):
+            try:
+                fixed, _ = attempt(s, label, port + 1 + i)
+            except Exception as exc:  # noqa: BLE001 - a repair that cannot run is just not a repair
+                attempts.append({"label": label, "ok": False, "error": repr(exc)})
+                continue
+            if fixed:
+                suggestion = label
+                break
+    return ValidationReport(ok, d, world_size, base.name, suggestion, attempts)

@@ -287,3 +287,75 @@ def test_domain_parallel_pipeline_model_uses_member_halos():
     dyn.run(batch, n_steps=8)
     assert torch.allclose(torch.tensor(res[0][0], dtype=torch.float64), batch.positions, atol=1e-9)
     assert len(res[0][1]) == 2 and res[0][1][0] < res[0][1][1]  # the short-ranged member got a shallower halo
+
+
+def _val_lj():
+    return _lj()
+
+
+def _val_batch():
+    return _lj_batch(4)
+
+
+def test_trace_and_validate_passes_and_suggests_a_deeper_halo():
+    from nvalchemi_toolkit_b200.distributed.spec import Consolidation, MLIPSpec
+    from nvalchemi_toolkit_b200.distributed.validate import trace_and_validate
+
+    rep = trace_and_validate(_val_lj, _val_batch, 2, cutoff=6.0, port=29741)
+    assert rep.ok and rep.attempts[0]["atoms_with_missing_neighbors"] == 0 and "PASS" in str(rep)
+    # a spec that claims no neighbour dependence gets no ghosts: wrong forces, and the repair is a deeper halo
+    bad = MLIPSpec("too_shallow", message_passes=0, consolidation=Consolidation.DIRECT_MASKED)
+    rep = trace_and_validate(_val_lj, _val_batch, 2, cutoff=6.0, spec=bad, port=29751)
+    assert not rep.ok and rep.suggestion == "message_passes=1 (deeper halo)"
+
+
+def _gp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nvalchemi_toolkit_b200.distributed.strategy import get_strategy
+        from nvalchemi_toolkit_b200.distributed.config import StrategyKind
+
+        torch.set_num_threads(1)
+        out = {}
+        for name, model, batch in (("lj", _lj(), _lj_batch(3)), ("mace", _mace_model(), Batch.from_data_list(
+                [fcc_supercell(3, a=3.61, z=29, noise=0.08, seed=3, dtype=torch.float64)]))):
+            strat = get_strategy(DomainConfig(cutoff=6.0, strategy=StrategyKind.GRAPH_PARTITION))
+            res = strat.run_forward(model, batch, model.distribution_spec())
+            out[name] = {k: res[k].tolist() for k in ("energy", "forces")}
+        q.put((rank, out))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_graph_partition_strategy_matches_single_process():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_gp_worker, args=(r, 2, 29761, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=240) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+    refs = {"lj": _reference(_lj(), _lj_batch(3)),
+            "mace": _reference(_mace_model(), Batch.from_data_list(
+                [fcc_supercell(3, a=3.61, z=29, noise=0.08, seed=3, dtype=torch.float64)]))}
+    for name, ref in refs.items():
+        for r in range(2):
+            assert torch.allclose(torch.tensor(res[r][name]["forces"], dtype=torch.float64), ref["forces"].detach(), atol=1e-8)
+            assert torch.allclose(torch.tensor(res[r][name]["energy"], dtype=torch.float64), ref["energy"].detach(), atol=1e-8)
+
+
+def test_shard_routing_tables():
+    from nvalchemi_toolkit_b200.distributed.context import (NOT_DISTRIBUTED, DistributedContext, ShardRouting,
+                                                            activate_dd_context, current_dd_context)
+
+    r = ShardRouting.from_assignment(torch.tensor([1, 0, 1, 2, 0]), 3)
+    assert r.counts.tolist() == [2, 2, 1] and r.local_index.tolist() == [0, 0, 1, 0, 1]
+    assert r.to_flat(torch.tensor([1, 4, 0, 2, 3])).tolist() == [0, 1, 2, 3, 4] and r.global_ids_of(1).tolist() == [0, 2]
+    assert current_dd_context() is NOT_DISTRIBUTED
+    with activate_dd_context(DistributedContext(rank=1, world_size=4, n_owned=3, n_padded=5, is_halo=True)) as c:
+        assert current_dd_context().n_ghost == 2 and c.is_halo
+    assert current_dd_context().world_size == 1
