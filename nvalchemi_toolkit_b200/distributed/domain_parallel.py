@@ -87,7 +87,13 @@ class DomainParallel:
     # ---- set-up ---------------------------------------------------------------
     def partition(self, batch: Batch) -> ShardedBatch:
         self.sharded = ShardedBatch.from_batch(batch, self.config, self.spec, self.group)
+        self._sync_atom_ids()
         return self.sharded
+
+    def _sync_atom_ids(self) -> None:
+        """Stochastic integrators draw noise per *global* atom id, so trajectories do not depend on the decomposition."""
+        if hasattr(self.dynamics, "atom_ids"):
+            self.dynamics.atom_ids = self.sharded.global_ids
 
     def register_hook(self, hook: Any, stage: DynamicsStage | None = None, scope: HookScope = HookScope.LOCAL) -> None:
         stage = stage if stage is not None else getattr(hook, "stage", DynamicsStage.AFTER_STEP)
@@ -116,6 +122,7 @@ class DomainParallel:
         if sh.needs_rebuild():
             sh.rebuild()
             self.num_rebuilds += 1
+            self._sync_atom_ids()
         out = self.model(sh)
         dyn._validate_model_outputs(out)
         owned = sh.owned
@@ -153,6 +160,7 @@ class DomainParallel:
     def run(self, batch: Batch | ShardedBatch | None = None, n_steps: int | None = None) -> ShardedBatch:
         if isinstance(batch, ShardedBatch):
             self.sharded = batch
+            self._sync_atom_ids()
         elif batch is not None:
             self.partition(batch)
         n = n_steps if n_steps is not None else self.dynamics.n_steps

@@ -337,7 +337,11 @@ class BaseDynamics(HookRegistryMixin, _CommunicationMixin):
         mask = None
         if self._last_converged is not None and batch is not None:
             mask = torch.zeros(batch.num_graphs, dtype=torch.bool, device=batch.device)
-            mask[self._last_converged] = True
+            idx = self._last_converged
+            if idx.numel() and int(idx.max()) >= batch.num_graphs:
+                idx = idx[:0]  # the batch was refilled or compacted since; the old indices name other systems
+                self._last_converged = None
+            mask[idx] = True
         return DynamicsContext(batch=batch, step_count=self.step_count, model=self.model, converged_mask=mask,
                                global_rank=self.global_rank, workflow=self)
 
@@ -695,22 +699,21 @@ class FusedStage(BaseDynamics):
             while True:
                 batch, _ = self.step(batch)
                 if self.sampler is not None and (step_num + 1) % self.refill_frequency == 0:
-                    n_before = batch.num_graphs
                     result = self.refill_check(batch, self.exit_status)
                     if result is None:
                         self.active_batch = None
                         return None
                     if result is not batch:
                         batch = result
-                        if self.init_fn is not None and batch.num_graphs:
-                            pass
+                        self._last_converged = None  # system indices changed with the refill
+                        for _, d in self.sub_stages:
+                            d._last_converged = None
                         # forces of replacement systems are unknown: evaluate before the next pre_update
                         self._call_hooks(DynamicsStage.BEFORE_COMPUTE, batch)
                         for _, d in self.sub_stages:
                             d._call_hooks(DynamicsStage.BEFORE_COMPUTE, batch)
                         self.compute(batch)
                     self.active_batch = batch
-                    del n_before
                 elif self.sampler is None and (step_num + 1) % self.convergence_check_frequency == 0 \
                         and self.all_complete(batch, self.exit_status):
                     break

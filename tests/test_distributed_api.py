@@ -359,3 +359,42 @@ def test_shard_routing_tables():
     with activate_dd_context(DistributedContext(rank=1, world_size=4, n_owned=3, n_padded=5, is_halo=True)) as c:
         assert current_dd_context().n_ghost == 2 and c.is_halo
     assert current_dd_context().world_size == 1
+
+
+def _langevin_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nvalchemi_toolkit_b200.dynamics import NVTLangevin
+
+        torch.set_num_threads(1)
+        dp = DomainParallel(NVTLangevin(_lj(), dt=2.0, temperature=80.0, friction=0.05, random_seed=11),
+                            DomainConfig(cutoff=6.0, skin=0.6))
+        dp.run(_lj_batch(4, velocities=0.05), n_steps=15)
+        q.put((rank, dp.gather().positions.tolist()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_langevin_noise_follows_global_atom_ids():
+    import torch.multiprocessing as mp
+
+    from nvalchemi_toolkit_b200.dynamics import NVTLangevin
+    from nvalchemi_toolkit_b200.dynamics.base import DynamicsStage
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_langevin_worker, args=(r, 2, 29781, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=240) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+    batch = _lj_batch(4, velocities=0.05)
+    model = _lj()
+    dyn = NVTLangevin(model, dt=2.0, temperature=80.0, friction=0.05, random_seed=11,
+                      hooks=[NeighborListHook(model.model_config.neighbor_config, stage=DynamicsStage.BEFORE_COMPUTE)])
+    dyn._call_hooks(DynamicsStage.BEFORE_COMPUTE, batch)
+    dyn.compute(batch)
+    dyn.run(batch, n_steps=15)
+    assert torch.allclose(torch.tensor(res[0], dtype=torch.float64), batch.positions, atol=1e-9)

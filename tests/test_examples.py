@@ -1,0 +1,24 @@
+# SPDX-License-Identifier: Apache-2.0
+"""The example scripts run to completion (each in its own interpreter, CPU)."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+FAST = ["basic/01_atomic_data_and_batch.py", "basic/02_neighbor_lists.py", "basic/04_batched_fire_relaxation.py",
+        "intermediate/06_inflight_batching.py", "intermediate/07_zarr_and_dataloader.py",
+        "intermediate/08_train_a_model.py", "advanced/10_ewald_vs_pme.py", "advanced/11_variable_cell_relaxation.py",
+        "distributed/12_domain_parallel_md.py"]
+
+
+@pytest.mark.parametrize("script", FAST)
+def test_example_runs(script):
+    env = dict(os.environ, PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="")
+    env.pop("RANK", None)
+    res = subprocess.run([sys.executable, str(ROOT / "examples" / script)], env=env, capture_output=True, text=True,
+                         timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert res.stdout.strip()
