@@ -331,6 +331,22 @@ class AtomicData(BaseModel, DataMixin):
         kw.update(extra)
         return cls(**kw).to(device)
 
+    def to_atoms(self) -> Any:
+        """An ``ase.Atoms`` with positions, cell, pbc, masses, velocities (needs ``ase``)."""
+        from nvalchemi_toolkit_b200._optional import OptionalDependency
+
+        ase = OptionalDependency.ASE.import_module()
+        kw: dict[str, Any] = {"numbers": self.atomic_numbers.cpu().numpy(), "positions": self.positions.detach().cpu().numpy()}
+        if getattr(self, "cell", None) is not None:
+            kw["cell"] = self.cell.detach().reshape(3, 3).cpu().numpy()
+            kw["pbc"] = self.pbc.reshape(3).cpu().numpy() if getattr(self, "pbc", None) is not None else False
+        atoms = ase.Atoms(**kw)
+        if getattr(self, "atomic_masses", None) is not None:
+            atoms.set_masses(self.atomic_masses.detach().cpu().numpy())
+        if getattr(self, "velocities", None) is not None:
+            atoms.set_velocities(self.velocities.detach().cpu().numpy())
+        return atoms
+
     @classmethod
     def from_structure(cls, structure: Any, dtype: torch.dtype = torch.float32,
                        device: str | torch.device = "cpu", **extra: Any) -> "AtomicData":
