@@ -159,6 +159,7 @@ class ShardedBatch:
 
     def rebuild(self, migrate: bool = True) -> None:
         """Re-derive ownership (with hysteresis), move rows that changed owner, and rebuild the ghost plan."""
+        self.partitioner.update_cell(self.cell)  # barostats change the cell; fractional boxes stay as they are
         if migrate and self.world > 1:
             pos = self.owned.positions.detach()
             here = torch.full((self.n_owned,), self.rank, dtype=torch.long, device=pos.device)

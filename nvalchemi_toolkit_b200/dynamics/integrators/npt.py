@@ -46,6 +46,8 @@ class NPT(BaseDynamics):
         self._temperature_init, self._pressure_init = temperature, pressure
         self._tau_b, self._tau_t = fs_to_internal_time(barostat_time), fs_to_internal_time(thermostat_time)
         self.pressure_coupling, self.chain_length = pressure_coupling, chain_length
+        self.ke_reduce = None     # cross-rank sums installed by a domain-decomposition coordinator
+        self.count_reduce = None
         if "stress" not in model.model_config.active_outputs:
             model.model_config.active_outputs = set(model.model_config.active_outputs) | {"stress"}
 
@@ -65,7 +67,8 @@ class NPT(BaseDynamics):
 
     # -- pieces ------------------------------------------------------------------
     def _ndof(self, batch: Batch) -> torch.Tensor:
-        return 3.0 * batch.num_nodes_per_graph.to(batch.positions.dtype)
+        n = 3.0 * batch.num_nodes_per_graph.to(batch.positions.dtype)
+        return n if self.count_reduce is None else self.count_reduce(n)
 
     def _barostat_mass(self, batch: Batch) -> torch.Tensor:
         s = self._state
@@ -77,6 +80,8 @@ class NPT(BaseDynamics):
         s, m = self._state, batch.num_graphs
         ndof = self._ndof(batch)
         ke2 = 2.0 * _ops.compute_kinetic_energy(batch.velocities, batch.atomic_masses, batch.batch_idx, m)
+        if self.ke_reduce is not None:
+            ke2 = self.ke_reduce(ke2)
         Q = nhc_compute_masses(ndof, s["kT"], s["tau_t"], self.chain_length)
         scale = nhc_chain_update(ke2, s["eta"], s["eta_dot"], Q, s["kT"], ndof, s["dt"])
         _ops.velocity_rescale(batch.velocities, scale, batch.batch_idx)
@@ -92,6 +97,8 @@ class NPT(BaseDynamics):
         cell = batch.cell.reshape(m, 3, 3)
         vol = torch.linalg.det(cell).abs()
         K = compute_kinetic_tensor(batch.velocities, batch.atomic_masses, batch.batch_idx, m)
+        if self.ke_reduce is not None:
+            K = self.ke_reduce(K)
         stress = getattr(batch, "stress", None)
         stress = torch.zeros_like(K) if stress is None else stress.reshape(m, 3, 3)
         P = compute_pressure_tensor(K, stress, vol)

@@ -398,3 +398,46 @@ def test_langevin_noise_follows_global_atom_ids():
     dyn.compute(batch)
     dyn.run(batch, n_steps=15)
     assert torch.allclose(torch.tensor(res[0], dtype=torch.float64), batch.positions, atol=1e-9)
+
+
+def _npt_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nvalchemi_toolkit_b200.dynamics import NPT
+
+        torch.set_num_threads(1)
+        dp = DomainParallel(NPT(_lj(), dt=2.0, temperature=60.0, pressure=0.0, barostat_time=200.0, thermostat_time=50.0),
+                            DomainConfig(cutoff=6.0, skin=0.6))
+        dp.run(_lj_batch(4, velocities=0.05), n_steps=12)
+        full = dp.gather()
+        q.put((rank, full.positions.tolist(), full.cell.reshape(3, 3).tolist()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_npt_barostat_under_domain_decomposition():
+    import torch.multiprocessing as mp
+
+    from nvalchemi_toolkit_b200.dynamics import NPT
+    from nvalchemi_toolkit_b200.dynamics.base import DynamicsStage
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_npt_worker, args=(r, 2, 29791, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict((r, (pos, cell)) for r, pos, cell in (q.get(timeout=240) for _ in range(2)))
+    for p in procs:
+        p.join(timeout=30)
+    batch = _lj_batch(4, velocities=0.05)
+    model = _lj()
+    dyn = NPT(model, dt=2.0, temperature=60.0, pressure=0.0, barostat_time=200.0, thermostat_time=50.0,
+              hooks=[NeighborListHook(model.model_config.neighbor_config, stage=DynamicsStage.BEFORE_COMPUTE)])
+    dyn._call_hooks(DynamicsStage.BEFORE_COMPUTE, batch)
+    dyn.compute(batch)
+    dyn.run(batch, n_steps=12)
+    cell = torch.tensor(res[0][1], dtype=torch.float64)
+    assert float((cell - batch.cell.reshape(3, 3)).abs().max()) < 1e-9 and float((cell - torch.eye(3) * A * 4).abs().max()) > 1e-4
+    assert torch.allclose(torch.tensor(res[0][0], dtype=torch.float64), batch.positions, atol=1e-8)
+    assert res[0][1] == res[1][1]
