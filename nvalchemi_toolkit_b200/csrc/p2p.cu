@@ -147,3 +147,43 @@ void halo_pull_rows(at::Tensor dst, int64_t row0, const at::Tensor& home_rank, c
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("halo_pull_rows(Tensor(a!) dst, int row0, Tensor home_rank, Tensor home_row, Tensor? shift, Tensor src_ptrs) -> ()", &nva::halo_pull_rows);
 }
+
+namespace nva {
+// Two-shot all-reduce through the NVSwitch: rank r owns slice r of the buffer, reduces it ACROSS ALL RANKS with one
+// multimem.ld_reduce per 16 bytes (the switch adds the peers' copies), applies `scale`, and multimem.st writes the
+// result back into every rank's buffer.  `mc_ptr` is the multicast address of the symmetric buffer.  The caller puts a
+// p2p_barrier before (all inputs written) and after (all slices stored).  n4 = number of float4 elements.
+__global__ void multimem_allreduce_kernel(int64_t n4, uint64_t mc_ptr, int rank, int world, float scale) {
+  int64_t per = (n4 + world - 1) / world;
+  int64_t lo = per * rank, hi = lo + per < n4 ? lo + per : n4;
+  for (int64_t i = lo + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < hi; i += (int64_t)gridDim.x * blockDim.x) {
+    uint64_t addr = mc_ptr + (uint64_t)i * 16u;
+    float x, y, z, w;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(x), "=f"(y), "=f"(z), "=f"(w)
+                 : "l"(addr)
+                 : "memory");
+    x *= scale; y *= scale; z *= scale; w *= scale;
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x), "f"(y), "f"(z), "f"(w)
+                 : "memory");
+  }
+}
+
+void multimem_allreduce(int64_t mc_ptr, int64_t byte_offset, int64_t numel, int64_t rank, int64_t world, double scale,
+                        const at::Tensor& like) {
+  c10::cuda::CUDAGuard guard(like.device());
+  TORCH_CHECK(mc_ptr != 0, "multimem_allreduce: no multicast address (NVLS not available for this buffer)");
+  TORCH_CHECK(numel % 4 == 0 && byte_offset % 16 == 0, "multimem_allreduce works on 16-byte aligned float4 groups");
+  int64_t n4 = numel / 4;
+  if (n4 == 0) return;
+  int64_t per = (n4 + world - 1) / world;
+  int blocks = (int)std::min<int64_t>((per + 255) / 256, 4 * 148);
+  multimem_allreduce_kernel<<<blocks > 0 ? blocks : 1, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      n4, (uint64_t)mc_ptr + (uint64_t)byte_offset, (int)rank, (int)world, (float)scale);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+}  // namespace nva
+
+TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
+  m.def("multimem_allreduce(int mc_ptr, int byte_offset, int numel, int rank, int world, float scale, Tensor like) -> ()", &nva::multimem_allreduce);
+}

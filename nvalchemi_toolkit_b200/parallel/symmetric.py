@@ -32,6 +32,7 @@ class SymmetricArena:
         self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
         self.handle = symm_mem.rendezvous(self.buf, self.group)
         self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)  # 0: no NVLS multicast for this buffer
         self.offset = 0
         self.buf.zero_()
 
@@ -48,6 +49,10 @@ class SymmetricArena:
         view = self.buf[off: off + nbytes].view(dtype).reshape(shape)
         ptrs = torch.tensor([b + off for b in self.base_ptrs], dtype=torch.int64, device=self.device)
         return view, ptrs
+
+    def offset_of(self, view: torch.Tensor) -> int:
+        """Byte offset of a sub-buffer returned by :meth:`alloc` inside the arena."""
+        return int(view.data_ptr() - self.buf.data_ptr())
 
     def reset(self) -> None:
         self.offset = 0
@@ -74,6 +79,31 @@ class P2PContext:
 
     def status(self) -> int:
         return int(self.err.item())
+
+    def allreduce_(self, view: torch.Tensor, scale: float = 1.0, out: torch.Tensor | None = None,
+                   use_multimem: bool | None = None) -> torch.Tensor:
+        """Sum a symmetric sub-buffer over all ranks (times ``scale``).
+
+        With an NVLS multicast mapping the reduction runs in the switch (``multimem.ld_reduce`` / ``multimem.st``, each
+        rank reducing one slice) and the result is left IN PLACE in every rank's buffer; otherwise every rank reads all
+        peers' buffers and writes ``out``.  Both are bracketed by flag barriers with bounded waits."""
+        import os
+
+        n = view.numel()
+        if use_multimem is None:
+            use_multimem = self.arena.multicast_ptr != 0 and n % 4 == 0 and os.environ.get("NVA_MULTIMEM", "1") != "0"
+        self.barrier()
+        if use_multimem:
+            _nops.multimem_allreduce(self.arena.multicast_ptr, self.arena.offset_of(view), n, self.rank, self.world,
+                                     float(scale), view)
+            result = view
+        else:
+            ptrs = torch.tensor([b + self.arena.offset_of(view) for b in self.arena.base_ptrs], dtype=torch.int64,
+                                device=self.device)
+            result = out if out is not None else torch.empty_like(view)
+            _nops.p2p_allreduce(ptrs, self.world, float(scale), result)
+        self.barrier()
+        return result
 
     def release_transient(self) -> None:
         self.arena.offset = self.persistent_offset

@@ -112,8 +112,10 @@ class FusedGradAllReduceHook(_Base):
         if dev.type == "cuda" and dist.get_backend() == "nccl":
             from nvalchemi_toolkit_b200.parallel.symmetric import P2PContext
 
-            self._p2p = P2PContext(4 * n + 4096, dev)
-            self._flat, self._ptrs = self._p2p.arena.alloc((n,), torch.float32)
+            n_pad = (n + 3) // 4 * 4  # float4 groups for the multimem path
+            self._p2p = P2PContext(4 * n_pad + 4096, dev)
+            self._flat, self._ptrs = self._p2p.arena.alloc((n_pad,), torch.float32)
+            n = n_pad
             self._out = torch.empty(n, dtype=torch.float32, device=dev)
         else:
             self._flat = torch.zeros(n, dtype=torch.float32, device=dev)
@@ -136,10 +138,8 @@ class FusedGradAllReduceHook(_Base):
         if self._p2p is not None:
             from nvalchemi_toolkit_b200.ops._native_counter import ops
 
-            self._p2p.barrier()   # every rank's buffer is complete
-            ops.p2p_allreduce(self._ptrs, world, scale, self._out)
-            self._p2p.barrier()   # nobody overwrites its buffer while a peer still reads it
-            result = self._out
+            # barrier - reduce (in the NVSwitch when a multicast mapping exists, else by peer loads) - barrier
+            result = self._p2p.allreduce_(self._flat, scale, out=self._out)
         else:
             dist.all_reduce(self._flat)
             result = self._flat.mul_(scale)
