@@ -10,6 +10,10 @@ _count = 0
 
 class _Ops:
     def __getattr__(self, name: str):
+        from nvalchemi_toolkit_b200.ops import _native
+
+        if not _native.available():  # loads the in-tree library on first use
+            raise RuntimeError("native extension is not built: run `python -m nvalchemi_toolkit_b200.ops.build`")
         fn = getattr(torch.ops.nvalchemi, name)
 
         def call(*a, **k):
