@@ -122,13 +122,21 @@ def run_case(case: BenchmarkCase) -> dict[str, Any]:
     rank, world = _world()
     size = case.size
     while True:
+        oom, result = False, None
         try:
-            return _run(case, size, device, dtype, rank, world)
+            result = _run(case, size, device, dtype, rank, world)
         except torch.cuda.OutOfMemoryError:
+            oom = True
             torch.cuda.empty_cache()
-            if size <= case.min_size:
-                return {"name": case.name, "status": "oom", "size": size}
-            size = max(case.min_size, size - max(1, size // 4))  # shrink by a quarter and try again
+        if world > 1:  # one rank out of memory means every rank skips this size (nobody waits in a collective alone)
+            flag = torch.tensor([1.0 if oom else 0.0], device=device if dist.get_backend() == "nccl" else "cpu")
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            oom = bool(flag > 0)
+        if not oom:
+            return result
+        if size <= case.min_size:
+            return {"name": case.name, "status": "oom", "size": size}
+        size = max(case.min_size, size - max(1, size // 4))  # shrink by a quarter and try again
 
 
 def _run(case: BenchmarkCase, size: int, device: torch.device, dtype: torch.dtype, rank: int, world: int) -> dict[str, Any]:
@@ -189,17 +197,36 @@ def _run(case: BenchmarkCase, size: int, device: torch.device, dtype: torch.dtyp
     return record
 
 
-def load_cases(path: str) -> list[BenchmarkCase]:
+def _apply_override(doc: dict, dotted: str, value: str) -> None:
+    """``defaults.steps=20`` or ``cases.0.size=8``; values are parsed as YAML scalars."""
+    import yaml
+
+    node: Any = doc
+    keys = dotted.split(".")
+    for k in keys[:-1]:
+        node = node[int(k)] if isinstance(node, list) else node.setdefault(k, {})
+    last = keys[-1]
+    parsed = yaml.safe_load(value)
+    if isinstance(node, list):
+        node[int(last)] = parsed
+    else:
+        node[last] = parsed
+
+
+def load_cases(path: str, overrides: list[str] | None = None) -> list[BenchmarkCase]:
     import yaml
 
     with open(path, encoding="utf-8") as fh:
         doc = yaml.safe_load(fh)
+    for item in overrides or []:
+        key, _, value = item.partition("=")
+        _apply_override(doc, key, value)
     defaults = doc.get("defaults", {})
     return [BenchmarkCase(**{**defaults, **c}) for c in doc["cases"]]
 
 
-def run_config(path: str, output: str | None = None) -> list[dict[str, Any]]:
-    results = [run_case(c) for c in load_cases(path)]
+def run_config(path: str, output: str | None = None, overrides: list[str] | None = None) -> list[dict[str, Any]]:
+    results = [run_case(c) for c in load_cases(path, overrides)]
     if output and _world()[0] == 0:
         with open(output, "w", encoding="utf-8") as fh:
             for r in results:
@@ -214,13 +241,15 @@ def main(argv: list[str] | None = None) -> int:
     ap = argparse.ArgumentParser(description="config-driven model-forward / NVT benchmarks")
     ap.add_argument("config")
     ap.add_argument("--output", default=None)
+    ap.add_argument("--set", dest="overrides", action="append", default=[], metavar="dotted.key=value",
+                    help="override a config entry, e.g. --set defaults.steps=20 --set cases.0.size=8")
     args = ap.parse_args(argv)
     if "RANK" in os.environ and int(os.environ.get("WORLD_SIZE", "1")) > 1 and not dist.is_initialized():
         backend = "nccl" if torch.cuda.is_available() else "gloo"
         if backend == "nccl":
             torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         dist.init_process_group(backend)
-    for r in run_config(args.config, args.output):
+    for r in run_config(args.config, args.output, args.overrides):
         if _world()[0] == 0:
             print(json.dumps(r))
     if dist.is_initialized():

@@ -14,6 +14,7 @@ Per-system sums (energy, virial, stress) are all-reduced; every rank ends up wit
 """
 from __future__ import annotations
 
+import os
 from types import SimpleNamespace
 from typing import Any
 
@@ -31,12 +32,18 @@ def consolidate_outputs(out: dict, sharded: ShardedBatch, spec: MLIPSpec, halo: 
     """Owned-row views of node outputs (with the reverse-halo correction) and globally summed system outputs."""
     n = sharded.n_owned
     halo = halo if halo is not None else sharded.halo
+    debug = os.environ.get("NVA_CONSOLIDATE_DEBUG", "0") not in ("", "0") and sharded.rank == 0
     n_ghost = halo.n_ghost if spec.consolidation != Consolidation.REPLICATED else 0
     res: dict[str, Any] = {}
     for key, value in out.items():
         if not isinstance(value, torch.Tensor):
             res[key] = value
             continue
+        if debug:
+            rule = "all-reduce" if key in spec.extensive_outputs else ("owned rows" + (
+                " + reverse halo" if key == "forces" and spec.consolidation == Consolidation.WEIGHTED_ENERGY else "")
+                if value.dim() >= 1 and value.shape[0] == n + n_ghost else "pass-through")
+            print(f"[consolidate] {key}: shape {tuple(value.shape)} -> {rule}", flush=True)
         if key in spec.extensive_outputs:
             v = value.detach().clone()
             if sharded.world > 1:

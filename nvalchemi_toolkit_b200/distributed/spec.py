@@ -51,6 +51,34 @@ class MLIPSpec:
 
         return replace(self, **changes)
 
+    def to_dict(self) -> dict:
+        from dataclasses import asdict
+
+        d = asdict(self)
+        d["strategy"], d["consolidation"] = self.strategy.value, self.consolidation.value
+        d["node_outputs"], d["extensive_outputs"] = list(self.node_outputs), list(self.extensive_outputs)
+        return d
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "MLIPSpec":
+        d = dict(d)
+        d["strategy"], d["consolidation"] = StrategyKind(d["strategy"]), Consolidation(d["consolidation"])
+        d["node_outputs"], d["extensive_outputs"] = tuple(d["node_outputs"]), tuple(d["extensive_outputs"])
+        return cls(**d)
+
+    def save(self, path: str) -> None:
+        import json
+
+        with open(path, "w", encoding="utf-8") as fh:
+            json.dump(self.to_dict(), fh, indent=2)
+
+    @classmethod
+    def load(cls, path: str) -> "MLIPSpec":
+        import json
+
+        with open(path, encoding="utf-8") as fh:
+            return cls.from_dict(json.load(fh))
+
 
 SPEC_LJ_HALO = MLIPSpec("lennard_jones", message_passes=1, consolidation=Consolidation.DIRECT_MASKED)
 SPEC_PAIR_HALO = MLIPSpec("pair_potential", message_passes=1, consolidation=Consolidation.DIRECT_MASKED)

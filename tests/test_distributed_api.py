@@ -441,3 +441,52 @@ def test_npt_barostat_under_domain_decomposition():
     assert float((cell - batch.cell.reshape(3, 3)).abs().max()) < 1e-9 and float((cell - torch.eye(3) * A * 4).abs().max()) > 1e-4
     assert torch.allclose(torch.tensor(res[0][0], dtype=torch.float64), batch.positions, atol=1e-8)
     assert res[0][1] == res[1][1]
+
+
+def _coll_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nvalchemi_toolkit_b200.distributed.collectives import (distributed_index_select, distributed_scatter_add,
+                                                                    gather_to_replicate)
+        from nvalchemi_toolkit_b200.distributed.context import ShardRouting
+
+        owner = torch.tensor([0, 2, 1, 0, 2, 2, 1, 0, 1, 2])
+        routing = ShardRouting.from_assignment(owner, world)
+        mine = routing.global_ids_of(rank)
+        table = torch.arange(10, dtype=torch.float64)[:, None] * torch.tensor([1.0, 10.0])
+        local = table[mine].clone()
+        ask = torch.tensor([9, 0, 4, 4, 7][rank:]) if rank else torch.tensor([3, 8, 1])
+        got = distributed_index_select(local, ask, routing)
+        ok_sel = torch.equal(got, table[ask])
+        acc = torch.zeros(mine.numel(), 2, dtype=torch.float64)
+        distributed_scatter_add(acc, torch.tensor([0, 5, 5, 8]), torch.full((4, 2), float(rank + 1), dtype=torch.float64), routing)
+        full = gather_to_replicate(acc, mine)
+        q.put((rank, ok_sel, full[:, 0].tolist()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_collectives_by_global_id_and_spec_roundtrip(tmp_path):
+    import torch.multiprocessing as mp
+
+    from nvalchemi_toolkit_b200.distributed import SPEC_MACE_HALO, MLIPSpec
+    from nvalchemi_toolkit_b200.distributed._runtime import collective_device, resolve_global_rank, resolve_world_size
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_coll_worker, args=(r, 3, 29841, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    res = {r: (ok, full) for r, ok, full in (q.get(timeout=120) for _ in range(3))}
+    for p in procs:
+        p.join(timeout=30)
+    want = [0.0] * 10
+    want[0], want[5], want[8] = 6.0, 12.0, 6.0  # every rank adds (rank+1) once to ids 0 and 8, twice to id 5
+    for r in range(3):
+        assert res[r][0] and res[r][1] == want
+    SPEC_MACE_HALO.save(tmp_path / "spec.json")
+    assert MLIPSpec.load(tmp_path / "spec.json") == SPEC_MACE_HALO
+    assert resolve_world_size() == 1 and resolve_global_rank() == 0 and collective_device().type == "cpu"
+    with pytest.warns(DeprecationWarning):
+        from nvalchemi_toolkit_b200.dynamics.hooks.profiling import StageTimingHook  # noqa: F401
