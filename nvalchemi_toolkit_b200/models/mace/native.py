@@ -129,8 +129,35 @@ def _fused_ok(model: Any, ip: Any) -> bool:
             and len(ip.radial) >= 2)
 
 
+#: run the hidden layers of the radial MLP as one tensor-core kernel (activations never leave the SM)
+FUSED_RADIAL = True
+
+
+def _split_tf32(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``w = hi + lo`` with ``hi`` exactly representable in tf32 (low 13 mantissa bits cleared)."""
+    hi = (w.contiguous().view(torch.int32) & -8192).view(torch.float32)
+    return hi, w - hi
+
+
+def _hidden_fused(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool) -> torch.Tensor | None:
+    if not (FUSED_RADIAL and ef.is_cuda and ef.dtype == torch.float32 and gemm.get_precision() == "tf32" and len(ws) == 4
+            and tuple(ws[0].shape) == (8, 64) and tuple(ws[1].shape) == (64, 64) and tuple(ws[2].shape) == (64, 64)):
+        return None
+    hi, lo = _split_tf32(ws[0].t().contiguous())           # [64, 8]
+    w1t = torch.zeros(64, 32, dtype=torch.float32, device=ef.device)
+    w1t[:, 0:8], w1t[:, 8:16], w1t[:, 16:24] = hi, hi, lo
+    err = _err_words.setdefault(ef.device, torch.zeros(1, dtype=torch.int32, device=ef.device))
+    rows = ef if with_grad else ef[:, 0]
+    out = ops.mace_radial_hidden(rows.reshape(-1, 8).contiguous(), w1t, ws[1].t().contiguous(), ws[2].t().contiguous(),
+                                 bool(with_grad), err)
+    return out.reshape(ef.shape[0], 2, 64) if with_grad else out
+
+
 def _hidden(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool) -> torch.Tensor:
     """Radial MLP up to its last hidden layer: ``[E, 64]`` or, with the tangent, ``[E, 2, 64]`` (rows interleaved)."""
+    fused = _hidden_fused(ws, ef, with_grad)
+    if fused is not None:
+        return fused
     e = ef.shape[0]
     if not with_grad:
         x = ef[:, 0]

@@ -65,3 +65,42 @@ def test_buffer_primitives():
         dst = torch.zeros(6, width, device="cuda", dtype=dtype)
         buffer.copy_rows(src, torch.tensor([8, 1, 4], device="cuda"), dst, torch.tensor([0, 5, 2], device="cuda"))
         assert torch.equal(dst[[0, 5, 2]], src[[8, 1, 4]]) and not dst[[1, 3, 4]].any()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows", [1, 130, 5000])
+def test_fused_radial_mlp_matches_fp32_reference(rows):
+    """8 -> 64 -> 64 -> 64 with SiLU, value rows and (value, d/dr) row pairs, against float64 PyTorch."""
+    from nvalchemi_toolkit_b200.models.mace import native
+    from nvalchemi_toolkit_b200.models.mace.model import SILU_NORM
+
+    torch.manual_seed(rows)
+    dev = "cuda"
+    ws = [torch.randn(8, 64, device=dev) / 8 ** 0.5, torch.randn(64, 64, device=dev) / 8, torch.randn(64, 64, device=dev) / 8,
+          torch.randn(64, 640, device=dev) / 8]
+    ef = torch.randn(rows, 2, 8, device=dev)
+
+    def ref(x, t):
+        x, t = x.double(), t.double()
+        for w in ws[:3]:
+            z, zt = x @ w.double(), t @ w.double()
+            s = torch.sigmoid(z)
+            x, t = z * s * SILU_NORM, s * (1 + z * (1 - s)) * SILU_NORM * zt
+        return x, t
+
+    want_v, want_t = ref(ef[:, 0], ef[:, 1])
+    got = native._hidden_fused(ws, ef, True)
+    assert got is not None and got.shape == (rows, 2, 64)
+    scale = float(want_v.abs().max())
+    assert float((got[:, 0].double() - want_v).abs().max()) < 4e-3 * scale
+    assert float((got[:, 1].double() - want_t).abs().max()) < 4e-3 * float(want_t.abs().max())
+    val = native._hidden_fused(ws, ef[:, :1].contiguous(), False)
+    assert float((val.double() - want_v).abs().max()) < 4e-3 * scale
+    assert native.fused_error_status(torch.device(dev)) == 0
+    # the first layer alone keeps fp32 accuracy thanks to the hi/lo split of inputs and weights
+    one = native._hidden_fused([ws[0], torch.eye(64, device=dev), torch.eye(64, device=dev), ws[3]], ef[:, :1].contiguous(), False)
+    z = ef[:, 0].double() @ ws[0].double()
+    l1 = z * torch.sigmoid(z) * SILU_NORM
+    for _ in range(2):  # the two identity layers still apply the activation (and tf32 rounding of their input)
+        l1 = l1 * torch.sigmoid(l1) * SILU_NORM
+    assert float((one.double() - l1).abs().max()) < 2e-3 * float(l1.abs().max())
