@@ -63,6 +63,44 @@ __device__ __forceinline__ void sh_l3_vjp(float x, float y, float z, const float
   s = s1 + 2.f * s2 + 3.f * s3_;
 }
 
+// M[b][d] (row-major [16][3]) such that the force on the edge direction is  f[d] = sum_b dY[b] * M[b][d]:
+// M = (dY_b/dn_d - l_b Y_b n_d) / r, the Jacobian of the harmonics projected onto the sphere and scaled by 1/r.
+// Computed once per edge; consumers then need 48 multiply-adds instead of re-deriving the polynomials per channel.
+__device__ __forceinline__ void sh_l3_force_matrix(float x, float y, float z, float rinv, const float* Y, float* M) {
+  const float s3 = 1.7320508075688772f, s5 = 2.23606797749979f, s15 = 3.872983346207417f,
+              s70 = 8.366600265340756f, s105 = 10.246950765959598f, s42 = 6.48074069840786f,
+              s7 = 2.6457513110645907f;
+  float x2 = x * x, y2 = y * y, z2 = z * z;
+  float J[48];
+#pragma unroll
+  for (int k = 0; k < 48; ++k) J[k] = 0.f;
+  J[3 * 1 + 1] = s3; J[3 * 2 + 2] = s3; J[3 * 3 + 0] = s3;
+  J[3 * 4 + 0] = s15 * y; J[3 * 4 + 1] = s15 * x;
+  J[3 * 5 + 1] = s15 * z; J[3 * 5 + 2] = s15 * y;
+  J[3 * 6 + 0] = -s5 * x; J[3 * 6 + 1] = -s5 * y; J[3 * 6 + 2] = 2.f * s5 * z;
+  J[3 * 7 + 0] = s15 * z; J[3 * 7 + 2] = s15 * x;
+  J[3 * 8 + 0] = s15 * x; J[3 * 8 + 1] = -s15 * y;
+  J[3 * 9 + 0] = 0.25f * s70 * 6.f * x * y; J[3 * 9 + 1] = 0.25f * s70 * (3.f * x2 - 3.f * y2);
+  J[3 * 10 + 0] = s105 * y * z; J[3 * 10 + 1] = s105 * x * z; J[3 * 10 + 2] = s105 * x * y;
+  J[3 * 11 + 0] = 0.25f * s42 * (-2.f * x * y); J[3 * 11 + 1] = 0.25f * s42 * (4.f * z2 - x2 - 3.f * y2);
+  J[3 * 11 + 2] = 0.25f * s42 * 8.f * y * z;
+  J[3 * 12 + 0] = 0.5f * s7 * (-6.f * x * z); J[3 * 12 + 1] = 0.5f * s7 * (-6.f * y * z);
+  J[3 * 12 + 2] = 0.5f * s7 * (6.f * z2 - 3.f * x2 - 3.f * y2);
+  J[3 * 13 + 0] = 0.25f * s42 * (4.f * z2 - 3.f * x2 - y2); J[3 * 13 + 1] = 0.25f * s42 * (-2.f * x * y);
+  J[3 * 13 + 2] = 0.25f * s42 * 8.f * x * z;
+  J[3 * 14 + 0] = 0.5f * s105 * 2.f * x * z; J[3 * 14 + 1] = 0.5f * s105 * (-2.f * y * z);
+  J[3 * 14 + 2] = 0.5f * s105 * (x2 - y2);
+  J[3 * 15 + 0] = 0.25f * s70 * (3.f * x2 - 3.f * y2); J[3 * 15 + 1] = 0.25f * s70 * (-6.f * x * y);
+  const float n[3] = {x, y, z};
+#pragma unroll
+  for (int b = 0; b < 16; ++b) {
+    float l = b == 0 ? 0.f : (b < 4 ? 1.f : (b < 9 ? 2.f : 3.f));
+    float ly = l * Y[b];
+#pragma unroll
+    for (int d = 0; d < 3; ++d) M[3 * b + d] = (J[3 * b + d] - ly * n[d]) * rinv;
+  }
+}
+
 __device__ __forceinline__ void edge_vector(const float* __restrict__ pos, const float* __restrict__ cell,
                                             const int* __restrict__ batch_idx, int i, int j,
                                             const int* __restrict__ S, float* v) {

@@ -110,10 +110,12 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
   const uint32_t tmem_slot = bar0 + 72 + 16 * GR;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   // per-tile edge data (generic pointers)
-  struct TileEdge {
+  struct __align__(16) TileEdge {
+    float M[48];  // backward: maps dE/dY to the force along the edge (see sh_l3_force_matrix); 16-byte aligned rows
     float Y[16]; float n[3]; float rinv; float v[3]; float f[3];
     int recv; int j; const float* up; float* dup; float* gpj;
   };
+  static_assert(sizeof(TileEdge) <= 336, "shared-memory budget of the geometry ring");
   TileEdge* te = reinterpret_cast<TileEdge*>(gen + A_BYTES + 2 * B_BYTES + 256);  // [GR][FT]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(te) + sizeof(TileEdge) * FT * GR);
 
@@ -270,6 +272,7 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
             q.n[0] = v[0] * ri; q.n[1] = v[1] * ri; q.n[2] = v[2] * ri; q.rinv = ri;
             q.v[0] = v[0]; q.v[1] = v[1]; q.v[2] = v[2];
             sh_l3(q.n[0], q.n[1], q.n[2], q.Y);
+            if (BWD) sh_l3_force_matrix(q.n[0], q.n[1], q.n[2], ri, q.Y, q.M);
             q.recv = i;
             q.j = in ? j : -1;
             const float* ub = a.u;
@@ -383,10 +386,18 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
             float qq = 0.f;
 #pragma unroll
             for (int p = 0; p < NP; ++p) qq = fmaf(S[p], Rd[p], qq);
-            float gy[3], sdot;
-            sh_l3_vjp(q.n[0], q.n[1], q.n[2], q.Y, dY, gy, sdot);
+            // f = qq n + dY . M with the per-edge matrix prepared by the producer warp (48 multiply-adds)
+            f[0] = qq * q.n[0]; f[1] = qq * q.n[1]; f[2] = qq * q.n[2];
+            const float4* Mp = reinterpret_cast<const float4*>(q.M);
 #pragma unroll
-            for (int d = 0; d < 3; ++d) f[d] = (gy[d] - sdot * q.n[d]) * q.rinv + qq * q.n[d];
+            for (int g4 = 0; g4 < 4; ++g4) {  // 4 harmonics = 12 entries = 3 float4 per iteration
+              float4 m0 = Mp[3 * g4], m1 = Mp[3 * g4 + 1], m2 = Mp[3 * g4 + 2];
+              const float* dy = dY + 4 * g4;
+              f[0] = fmaf(dy[0], m0.x, f[0]); f[1] = fmaf(dy[0], m0.y, f[1]); f[2] = fmaf(dy[0], m0.z, f[2]);
+              f[0] = fmaf(dy[1], m0.w, f[0]); f[1] = fmaf(dy[1], m1.x, f[1]); f[2] = fmaf(dy[1], m1.y, f[2]);
+              f[0] = fmaf(dy[2], m1.z, f[0]); f[1] = fmaf(dy[2], m1.w, f[1]); f[2] = fmaf(dy[2], m2.x, f[2]);
+              f[0] = fmaf(dy[3], m2.y, f[0]); f[1] = fmaf(dy[3], m2.z, f[1]); f[2] = fmaf(dy[3], m2.w, f[2]);
+            }
             if (NEED_DU) {
               float* dp = q.dup + c;
 #pragma unroll
@@ -449,7 +460,7 @@ template <int LAYER, int GROUP, bool BWD, bool NEED_DU>
 static void launch_fused(const CUtensorMap& mw, const CUtensorMap& mh, const FusedArgs& a, int sms) {
   using G = GroupSpec<LAYER, GROUP>;
   constexpr int NROW = BWD ? 2 * FT : FT;
-  size_t smem = (size_t)G::NP * 2 * 128 * 128 + 2 * (2 * NROW * 128) + 256 + 4 * FT * 160 + 64 + 1024 + 256;
+  size_t smem = (size_t)G::NP * 2 * 128 * 128 + 2 * (2 * NROW * 128) + 256 + 4 * FT * 336 + 64 + 1024 + 256;
   constexpr int NG = BWD ? 3 : 4;
   auto kern = conv_fused_kernel<LAYER, GROUP, BWD, NEED_DU, NG>;
   static bool configured = false;

@@ -102,12 +102,14 @@ __global__ void __launch_bounds__(128) radial_mlp_kernel(const __grid_constant__
 #pragma unroll
     for (int j = 0; j < 64; ++j) {
       float x = v[j];
+      // sigmoid by ex2.approx + rcp.approx (two special-function instructions; an IEEE division costs ~10 more)
       if (TANGENT) {
         float a = __shfl_sync(0xffffffffu, x, lane & ~1);  // pre-activation of the value row of this pair
-        float sg = 1.f / (1.f + __expf(-a));
-        x = (lane & 1) ? sg * (1.f + a * (1.f - sg)) * kRadialSiluNorm * x : a * sg * kRadialSiluNorm;
+        float sg = __fdividef(kRadialSiluNorm, 1.f + __expf(-a));   // norm * sigmoid(a)
+        float dv = fmaf(a, kRadialSiluNorm - sg, kRadialSiluNorm);  // norm * (1 + a (1 - sigmoid))
+        x = (lane & 1) ? sg * dv * (1.f / kRadialSiluNorm) * x : a * sg;
       } else {
-        x = x / (1.f + __expf(-x)) * kRadialSiluNorm;
+        x = x * __fdividef(kRadialSiluNorm, 1.f + __expf(-x));
       }
       v[j] = x;
     }
@@ -194,6 +196,17 @@ static CUtensorMap weight_map(const float* ptr, int64_t k) {  // [64 rows, k] ro
   return m;
 }
 
+template <bool TANGENT>
+static void launch_radial(const CUtensorMap& m1, const CUtensorMap& m2, const CUtensorMap& m3, const float* ef, int64_t rows,
+                          float* out, int* err, int grid, size_t smem) {
+  static bool configured = false;  // one flag per kernel instantiation
+  if (!configured) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(radial_mlp_kernel<TANGENT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  radial_mlp_kernel<TANGENT><<<grid, 128, smem, at::cuda::getCurrentCUDAStream()>>>(m1, m2, m3, ef, rows, out, err);
+}
+
 // ef: [rows, 8] basis rows (with `tangent`: value and d/dr rows interleaved, rows even); w1t: [64, 32] = first layer
 // transposed, columns (W_hi, W_hi, W_lo, 0) with W_hi the tf32-representable part of the weight; w2t, w3t: [64, 64]
 // transposed layers.  Returns [rows, 64].
@@ -214,17 +227,8 @@ Tensor mace_radial_hidden(const Tensor& ef, const Tensor& w1t, const Tensor& w2t
   int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   int64_t ntiles = (rows + 127) / 128;
   int grid = (int)std::min<int64_t>(ntiles, 3 * (int64_t)sms);
-  auto launch = [&](auto kern) {
-    static bool configured = false;
-    if (!configured) {
-      C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      configured = true;
-    }
-    kern<<<grid, 128, smem, at::cuda::getCurrentCUDAStream()>>>(m1, m2, m3, ef.data_ptr<float>(), rows,
-                                                                  out.data_ptr<float>(), err.data_ptr<int>());
-  };
-  if (tangent) launch(radial_mlp_kernel<true>);
-  else launch(radial_mlp_kernel<false>);
+  if (tangent) launch_radial<true>(m1, m2, m3, ef.data_ptr<float>(), rows, out.data_ptr<float>(), err.data_ptr<int>(), grid, smem);
+  else launch_radial<false>(m1, m2, m3, ef.data_ptr<float>(), rows, out.data_ptr<float>(), err.data_ptr<int>(), grid, smem);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return out;
 }
