@@ -36,6 +36,9 @@ struct GroupSpec<0, 0> {
   static constexpr int NIN = MACE_L0_NIN, NP = MACE_L0G0_NP, NACC = MACE_L0G0_NACC, NT = MACE_L0G0_NT, NMID = MACE_L0_NMID;
   static __device__ __forceinline__ int mid(int k) { constexpr int m[] = MACE_L0G0_MIDS; return m[k]; }
   static __device__ __forceinline__ void fwd(const float* h, const float* Y, const float* R, float* acc) { MACE_L0G0_FWD(h, Y, R, acc); }
+  static constexpr int NZ = MACE_L0G0_NZ;
+  static __device__ __forceinline__ void zprep(const float* Y, float* Z) { MACE_L0G0_ZPREP(Y, Z); }
+  static __device__ __forceinline__ void fwdz(const float* h, const float* Z, const float* R, float* acc) { MACE_L0G0_FWDZ(h, Z, R, acc); }
   static __device__ __forceinline__ void prep(const float* G, float* T) { MACE_L0G0_BWD_PREP(G, T); }
   static __device__ __forceinline__ void edge(const float* h, const float* Y, const float* R, const float* T, float* dh, float* dY, float* S) { MACE_L0G0_BWD_EDGE(h, Y, R, T, dh, dY, S); }
 };
@@ -44,6 +47,9 @@ struct GroupSpec<1, 0> {
   static constexpr int NIN = MACE_L1_NIN, NP = MACE_L1G0_NP, NACC = MACE_L1G0_NACC, NT = MACE_L1G0_NT, NMID = MACE_L1_NMID;
   static __device__ __forceinline__ int mid(int k) { constexpr int m[] = MACE_L1G0_MIDS; return m[k]; }
   static __device__ __forceinline__ void fwd(const float* h, const float* Y, const float* R, float* acc) { MACE_L1G0_FWD(h, Y, R, acc); }
+  static constexpr int NZ = MACE_L1G0_NZ;
+  static __device__ __forceinline__ void zprep(const float* Y, float* Z) { MACE_L1G0_ZPREP(Y, Z); }
+  static __device__ __forceinline__ void fwdz(const float* h, const float* Z, const float* R, float* acc) { MACE_L1G0_FWDZ(h, Z, R, acc); }
   static __device__ __forceinline__ void prep(const float* G, float* T) { MACE_L1G0_BWD_PREP(G, T); }
   static __device__ __forceinline__ void edge(const float* h, const float* Y, const float* R, const float* T, float* dh, float* dY, float* S) { MACE_L1G0_BWD_EDGE(h, Y, R, T, dh, dY, S); }
 };
@@ -52,6 +58,9 @@ struct GroupSpec<1, 1> {
   static constexpr int NIN = MACE_L1_NIN, NP = MACE_L1G1_NP, NACC = MACE_L1G1_NACC, NT = MACE_L1G1_NT, NMID = MACE_L1_NMID;
   static __device__ __forceinline__ int mid(int k) { constexpr int m[] = MACE_L1G1_MIDS; return m[k]; }
   static __device__ __forceinline__ void fwd(const float* h, const float* Y, const float* R, float* acc) { MACE_L1G1_FWD(h, Y, R, acc); }
+  static constexpr int NZ = MACE_L1G1_NZ;
+  static __device__ __forceinline__ void zprep(const float* Y, float* Z) { MACE_L1G1_ZPREP(Y, Z); }
+  static __device__ __forceinline__ void fwdz(const float* h, const float* Z, const float* R, float* acc) { MACE_L1G1_FWDZ(h, Z, R, acc); }
   static __device__ __forceinline__ void prep(const float* G, float* T) { MACE_L1G1_BWD_PREP(G, T); }
   static __device__ __forceinline__ void edge(const float* h, const float* Y, const float* R, const float* T, float* dh, float* dY, float* S) { MACE_L1G1_BWD_EDGE(h, Y, R, T, dh, dY, S); }
 };
@@ -111,11 +120,14 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   // per-tile edge data (generic pointers)
   struct __align__(16) TileEdge {
-    float M[48];  // backward: maps dE/dY to the force along the edge (see sh_l3_force_matrix); 16-byte aligned rows
+    // backward: M maps dE/dY to the force along the edge (see sh_l3_force_matrix); forward: the same slot holds
+    // Z[k] = coef_k * Y[b_k], the channel-independent factor of every coupling term of the path group
+    float M[48];
     float Y[16]; float n[3]; float rinv; float v[3]; float f[3];
     int recv; int j; const float* up; float* dup; float* gpj;
   };
   static_assert(sizeof(TileEdge) <= 336, "shared-memory budget of the geometry ring");
+  static_assert(G::NZ <= 48, "coupling-term factors share the slot of the force matrix");
   TileEdge* te = reinterpret_cast<TileEdge*>(gen + A_BYTES + 2 * B_BYTES + 256);  // [GR][FT]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(te) + sizeof(TileEdge) * FT * GR);
 
@@ -273,6 +285,7 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
             q.v[0] = v[0]; q.v[1] = v[1]; q.v[2] = v[2];
             sh_l3(q.n[0], q.n[1], q.n[2], q.Y);
             if (BWD) sh_l3_force_matrix(q.n[0], q.n[1], q.n[2], ri, q.Y, q.M);
+            else G::zprep(q.Y, q.M);
             q.recv = i;
             q.j = in ? j : -1;
             const float* ub = a.u;
@@ -375,7 +388,7 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
             }
           }
           if (!BWD) {
-            if (q.j >= 0) G::fwd(h, q.Y, Rv, acc);
+            if (q.j >= 0) G::fwdz(h, q.M, Rv, acc);
           } else if (q.j >= 0) {  // uniform across the warp
             float dh[NIN], dY[16], S[NP], f[3];
 #pragma unroll

@@ -384,6 +384,20 @@ def write_header(path: str) -> None:
                 for o, exprs in by_out.items():
                     body.append(f"  acc[{o}] = fmaf(R[{q}], {' + '.join(exprs)}, acc[{o}]);")
             lines += [f"#define MACE_{gt}_FWD(h, Y, R, acc) do {{ \\"] + [t + " \\" for t in body] + ["} while (0)"]
+            # forward with the channel-independent factors hoisted: Z[k] = coef * Y[b] is prepared once per edge, the
+            # per-channel work is one multiply-add per coupling term
+            zprep, zbody, kz = [], [], 0
+            for q, p in enumerate(grp):
+                by_out_z: dict[int, list[str]] = {}
+                for (a_, b_, c_, coef) in terms[p]:
+                    zprep.append(f"  Z[{kz}] = {coef:.9e}f*Y[{b_}];")
+                    by_out_z.setdefault(loc[out_index[p][c_]], []).append(f"h[{a_}]*Z[{kz}]")
+                    kz += 1
+                for o, exprs in by_out_z.items():
+                    zbody.append(f"  acc[{o}] = fmaf(R[{q}], {' + '.join(exprs)}, acc[{o}]);")
+            lines += [f"#define MACE_{gt}_NZ {kz}",
+                      f"#define MACE_{gt}_ZPREP(Y, Z) do {{ \\"] + [t + " \\" for t in zprep] + ["} while (0)"]
+            lines += [f"#define MACE_{gt}_FWDZ(h, Z, R, acc) do {{ \\"] + [t + " \\" for t in zbody] + ["} while (0)"]
             prep, edge, k = [], [], 0
             for q, p in enumerate(grp):
                 pairs: dict[tuple[int, int], list[str]] = {}
