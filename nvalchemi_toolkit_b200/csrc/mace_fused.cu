@@ -416,11 +416,18 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
 #pragma unroll
               for (int k = 0; k < NIN; ++k) atomicAdd(dp + k * C, dh[k]);
             }
-#pragma unroll
-            for (int d = 0; d < 3; ++d) {
-              float x = f[d];
-              for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
-              if (lane == 0) atomicAdd(&q.f[d], x);  // shared-memory reduction over the four warps of the group
+            {
+              // warp sum of the three components with 6 shuffles instead of 15: the first two butterfly stages also
+              // split the components over lane groups (lanes 0-7 end up with x, 8-15 with y, 16-23 with z)
+              const bool b16 = lane & 16, b8 = lane & 8;
+              float k0 = (b16 ? f[2] : f[0]) + __shfl_xor_sync(0xffffffffu, b16 ? f[0] : f[2], 16);
+              float k1 = (b16 ? 0.f : f[1]) + __shfl_xor_sync(0xffffffffu, b16 ? f[1] : 0.f, 16);
+              float k = (b8 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, b8 ? k0 : k1, 8);
+              k += __shfl_xor_sync(0xffffffffu, k, 4);
+              k += __shfl_xor_sync(0xffffffffu, k, 2);
+              k += __shfl_xor_sync(0xffffffffu, k, 1);
+              // shared-memory reduction over the warps of the group: lane 0 holds x, lane 8 y, lane 16 z
+              if ((lane & 7) == 0 && lane < 24) atomicAdd(&q.f[lane >> 3], k);
             }
           }
         }
