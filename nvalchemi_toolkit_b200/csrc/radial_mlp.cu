@@ -8,8 +8,9 @@
 // epilogue of layer l reads the accumulator row of its thread from TMEM (tcgen05.ld), applies the activation and writes
 // the row into shared memory in the K-major swizzled layout that tcgen05.mma expects for the A operand of layer l+1.
 // Only the basis functions (32 B per row) are read from and the last hidden layer (256 B per row) is written to HBM;
-// the unfused chain moved five 256-byte rows per edge.  With `TANGENT`, rows alternate (value, d/dr): the tangent
-// row's activation is silu'(z_value) * z_tangent, fetched from the neighbouring lane by a shuffle.
+// the unfused chain moved five 256-byte rows per edge.  With `TANGENT`, global rows alternate (value, d/dr); inside a
+// tile the value rows occupy lanes 0-63 and the tangent rows lanes 64-127, and silu'(z_value) travels from the value
+// thread to its tangent partner through shared memory.
 // Replaces the first three torch.nn.Linear + SiLU layers of the reference's radial network (mace-torch RadialMLP,
 // used through nvalchemi/models/mace.py:205-287).  Waits are bounded; failures are reported through `err`.
 #include "common.cuh"
@@ -99,19 +100,41 @@ __global__ void __launch_bounds__(128) radial_mlp_kernel(const __grid_constant__
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     tmem_ld32(lane_addr, v);
     tmem_ld32(lane_addr + 32, v + 32);
+    // sigmoid by ex2.approx + rcp.approx (two special-function instructions; an IEEE division costs ~10 more)
+    if (!TANGENT) {
 #pragma unroll
-    for (int j = 0; j < 64; ++j) {
-      float x = v[j];
-      // sigmoid by ex2.approx + rcp.approx (two special-function instructions; an IEEE division costs ~10 more)
-      if (TANGENT) {
-        float a = __shfl_sync(0xffffffffu, x, lane & ~1);  // pre-activation of the value row of this pair
-        float sg = __fdividef(kRadialSiluNorm, 1.f + __expf(-a));   // norm * sigmoid(a)
-        float dv = fmaf(a, kRadialSiluNorm - sg, kRadialSiluNorm);  // norm * (1 + a (1 - sigmoid))
-        x = (lane & 1) ? sg * dv * (1.f / kRadialSiluNorm) * x : a * sg;
-      } else {
-        x = x * __fdividef(kRadialSiluNorm, 1.f + __expf(-x));
+      for (int j = 0; j < 64; ++j) v[j] = v[j] * __fdividef(kRadialSiluNorm, 1.f + __expf(-v[j]));
+    } else {
+      // rows 0-63 of the tile are value rows, rows 64-127 the matching tangent rows.  The value thread of an edge
+      // computes silu(z) for itself and leaves silu'(z) in the (free) activation row of its tangent partner, which
+      // picks it up after a barrier: no shuffles, and the special-function work is done once per edge.
+      if (t < 64) {
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float fac[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float a = v[kb * 32 + 4 * j + q];
+              float sg = __fdividef(kRadialSiluNorm, 1.f + __expf(-a));       // norm * sigmoid(a)
+              fac[q] = sg * fmaf(a, 1.f - sg * (1.f / kRadialSiluNorm), 1.f);  // norm * silu'(a)
+              v[kb * 32 + 4 * j + q] = a * sg;
+            }
+            *reinterpret_cast<float4*>(act + kb * ACT_KB + sw128_off(t + 64, j)) = make_float4(fac[0], fac[1], fac[2], fac[3]);
+          }
       }
-      v[j] = x;
+      __syncthreads();
+      if (t >= 64) {
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 fac = *reinterpret_cast<const float4*>(act + kb * ACT_KB + sw128_off(t, j));
+            v[kb * 32 + 4 * j] *= fac.x; v[kb * 32 + 4 * j + 1] *= fac.y;
+            v[kb * 32 + 4 * j + 2] *= fac.z; v[kb * 32 + 4 * j + 3] *= fac.w;
+          }
+      }
     }
     return true;
   };
@@ -125,7 +148,9 @@ __global__ void __launch_bounds__(128) radial_mlp_kernel(const __grid_constant__
   };
 
   for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-    const int64_t row = tile * 128 + t;
+    // TANGENT: the tile covers 64 edges; thread t < 64 owns the value row of edge t, thread t >= 64 the tangent row of
+    // edge t - 64 (global rows interleave value and tangent)
+    const int64_t row = TANGENT ? tile * 128 + 2 * (t & 63) + (t >> 6) : tile * 128 + t;
     // basis functions of this thread's row -> A operand (K = 8 padded with zeros to one 32-column k-block)
     float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
     if (row < rows) {
