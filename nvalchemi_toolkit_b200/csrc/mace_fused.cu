@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
     // Z[k] = coef_k * Y[b_k], the channel-independent factor of every coupling term of the path group
     float M[48];
     float Y[16]; float n[3]; float rinv; float v[3]; float f[3];
-    int recv; int j; const float* up; float* dup; float* gpj;
+    int recv; int j; int dup_local; int pad_; const float* up; float* dup; float* gpj;
   };
   static_assert(sizeof(TileEdge) <= 336, "shared-memory budget of the geometry ring");
   static_assert(G::NZ <= 48, "coupling-term factors share the slot of the force matrix");
@@ -301,9 +301,10 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
             }
             q.up = ub + jr * NIN * C;
             q.dup = (BWD && NEED_DU) ? dub + jr * NIN * C : nullptr;
+            q.dup_local = dub == a.du ? 1 : 0;
             q.gpj = BWD ? gpb + 3 * jr : nullptr;
           } else {
-            q.recv = -1; q.j = -1; q.up = a.u; q.dup = nullptr; q.gpj = nullptr;
+            q.recv = -1; q.j = -1; q.up = a.u; q.dup = nullptr; q.gpj = nullptr; q.dup_local = 0;
           }
         }
         {
@@ -412,9 +413,16 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
               f[0] = fmaf(dy[3], m2.y, f[0]); f[1] = fmaf(dy[3], m2.z, f[1]); f[2] = fmaf(dy[3], m2.w, f[2]);
             }
             if (NEED_DU) {
-              float* dp = q.dup + c;
+              // du is laid out [row][channel][component]: the thread's NIN = 4 gradients are 16 contiguous bytes and go
+              // out as ONE vector reduction when the row is in this GPU's memory (a quarter of the L2 atomic
+              // operations, which bound this kernel); rows of other GPUs get scalar reductions over NVLink
+              float* dp = q.dup + c * NIN;
+              if (NIN == 4 && q.dup_local) {
+                atomicAdd(reinterpret_cast<float4*>(dp), make_float4(dh[0], dh[NIN > 1 ? 1 : 0], dh[NIN > 2 ? 2 : 0], dh[NIN > 3 ? 3 : 0]));
+              } else {
 #pragma unroll
-              for (int k = 0; k < NIN; ++k) atomicAdd(dp + k * C, dh[k]);
+                for (int k = 0; k < NIN; ++k) atomicAdd(dp + k, dh[k]);
+              }
             }
             {
               // warp sum of the three components with 6 shuffles instead of 15: the first two butterfly stages also

@@ -284,6 +284,8 @@ class BaseDynamics(HookRegistryMixin, _CommunicationMixin):
             raise TypeError(f"Expected a `BaseModelMixin` instance, got {type(model).__name__}. Please wrap your "
                             "model with a `BaseModelMixin` subclass.")
         self.model = model
+        if isinstance(model, torch.nn.Module):
+            model.eval()  # dynamics is inference: wrappers with hand-written kernels only use them outside training mode
         self.step_count = 0
         if isinstance(convergence_hook, dict):
             convergence_hook = ConvergenceHook(**convergence_hook)

@@ -406,6 +406,9 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         del dmid
         if dd is not None:
             dd.barrier()  # feature / position gradients pushed by peers have landed
+        if li > 0 and wgs is not None:
+            # the fused kernel accumulates the feature gradient as [row, channel, component] (vector reductions)
+            du = du.view(du.shape[0], C, du.shape[1]).transpose(1, 2).contiguous()
         if li > 0:
             dh = _per_l_linear(du, ip.linear_up, ip.l_in, transpose=True) + _skip(ip, dh_tot, species, nz, transpose=True)
         saved[li] = None
