@@ -8,7 +8,7 @@ import torch
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
-def _worker(rank: int, world: int, port: int, q) -> None:
+def _worker(rank: int, world: int, port: int, q, channels: int = 32) -> None:
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                           NCCL_NVLS_ENABLE="0")
@@ -24,9 +24,9 @@ def _worker(rank: int, world: int, port: int, q) -> None:
         from nvalchemi_toolkit_b200.ops import gemm
         from tests.helpers import fcc_supercell
 
-        gemm.set_precision("fp32")
+        gemm.set_precision("fp32" if channels != 128 else "tf32")  # 128 channels: the fused tensor-core convolution
         torch.manual_seed(0)
-        cfg = MACEConfig(atomic_numbers=[29], channels=32, avg_num_neighbors=42.0)
+        cfg = MACEConfig(atomic_numbers=[29], channels=channels, avg_num_neighbors=42.0)
         model = MACE(cfg).to(dev)
         cells = 8
         d = fcc_supercell(cells, noise=0.08, seed=3)
@@ -73,13 +73,14 @@ def _worker(rank: int, world: int, port: int, q) -> None:
         q.put((rank, {"error": f"{type(exc).__name__}: {exc}\\n{traceback.format_exc()}"}))
 
 
-def test_slab_dd_matches_single_gpu():
+@pytest.mark.parametrize("channels", [32, 128])
+def test_slab_dd_matches_single_gpu(channels):
     import torch.multiprocessing as mp
 
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, world, 29533, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, 29533 + channels, q, channels)) for r in range(world)]
     for p in procs:
         p.start()
     results = dict(q.get(timeout=600) for _ in range(world))
@@ -91,6 +92,7 @@ def test_slab_dd_matches_single_gpu():
         assert "error" not in res, res["error"]
         assert res["status"] == 0 and res["gemm"] == 0
         assert res["owned"] > 0 and res["ghosts"] > 0
-        assert res["e_err"] < 1e-3 * max(1.0, abs(res["e"]))
-        assert res["f_err"] < 2e-4 * max(1.0, res["f"])
-        assert res["x_err"] < 1e-4 and res["v_err"] < 1e-4
+        tol = 1.0 if channels != 128 else 30.0  # tf32 channel mixes against the float32 PyTorch reference
+        assert res["e_err"] < 1e-3 * tol * max(1.0, abs(res["e"]))
+        assert res["f_err"] < 2e-4 * tol * max(1.0, res["f"])
+        assert res["x_err"] < 1e-4 * tol and res["v_err"] < 1e-4 * tol
