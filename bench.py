@@ -136,7 +136,10 @@ def run_ours(args) -> dict:
 
         sim = SlabDomainMD.for_benchmark(cells=cells, device=device, skin=args.skin, max_neighbors=args.max_neighbors,
                                          atom_order=args.atom_order)
-        step, sync_energy, e2e_step, counts = sim.step, sim.energy, sim.host_driven_step, sim.e2e_bytes()
+        step, sync_energy, e2e_step = sim.step, sim.energy, sim.host_driven_step
+        per_rank = torch.tensor(sim.e2e_bytes(), dtype=torch.int64, device=device)
+        dist.all_reduce(per_rank)  # bytes of the whole job per step (every rank moves its own atoms)
+        counts = tuple(int(x) for x in per_rank.tolist())
         parallelism = f"dd{world} (slabs along x, halo 10 A)"
     else:
         batch = build_system(cells, device, atom_order=args.atom_order)
