@@ -490,3 +490,50 @@ def test_collectives_by_global_id_and_spec_roundtrip(tmp_path):
     assert resolve_world_size() == 1 and resolve_global_rank() == 0 and collective_device().type == "cpu"
     with pytest.warns(DeprecationWarning):
         from nvalchemi_toolkit_b200.dynamics.hooks.profiling import StageTimingHook  # noqa: F401
+
+
+def _fire_worker(rank, world, port, q, kind):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nvalchemi_toolkit_b200.dynamics import FIRE, FIRE2, NVTNoseHoover
+
+        torch.set_num_threads(1)
+        dyn = {"fire2": lambda: FIRE2(_lj(), dt=0.05), "fire": lambda: FIRE(_lj(), dt=1.0),
+               "nhc": lambda: NVTNoseHoover(_lj(), dt=2.0, temperature=60.0, thermostat_time=40.0)}[kind]()
+        dp = DomainParallel(dyn, DomainConfig(cutoff=6.0, skin=0.6))
+        dp.run(_lj_batch(4, noise=0.15, velocities=0.03 if kind == "nhc" else 0.0), n_steps=15)
+        full = dp.gather()
+        q.put((rank, full.positions.tolist()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("kind", ["fire2", "fire", "nhc"])
+def test_global_reductions_of_optimisers_and_thermostats(kind):
+    """FIRE's v.f / v.v / f.f sums and step limiter, and the Nose-Hoover kinetic energy and degrees of freedom, are
+    global quantities: two ranks must reproduce the single-process trajectory."""
+    import torch.multiprocessing as mp
+
+    from nvalchemi_toolkit_b200.dynamics import FIRE, FIRE2, NVTNoseHoover
+    from nvalchemi_toolkit_b200.dynamics.base import DynamicsStage
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29860 + ["fire2", "fire", "nhc"].index(kind)
+    procs = [ctx.Process(target=_fire_worker, args=(r, 2, port, q, kind)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=240) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+    model = _lj()
+    hook = NeighborListHook(model.model_config.neighbor_config, stage=DynamicsStage.BEFORE_COMPUTE)
+    dyn = {"fire2": lambda: FIRE2(model, dt=0.05, hooks=[hook]), "fire": lambda: FIRE(model, dt=1.0, hooks=[hook]),
+           "nhc": lambda: NVTNoseHoover(model, dt=2.0, temperature=60.0, thermostat_time=40.0, hooks=[hook])}[kind]()
+    batch = _lj_batch(4, noise=0.15, velocities=0.03 if kind == "nhc" else 0.0)
+    dyn._call_hooks(DynamicsStage.BEFORE_COMPUTE, batch)
+    dyn.compute(batch)
+    dyn.run(batch, n_steps=15)
+    got = torch.tensor(res[0], dtype=torch.float64)
+    assert float((got - batch.positions).abs().max()) < (1e-8 if kind != "fire" else 1e-6)
