@@ -18,10 +18,11 @@ from nvalchemi_toolkit_b200.distributed.distributed_model import DistributedMode
 from nvalchemi_toolkit_b200.distributed.domain_parallel import DomainParallel, DynamicsCoordinator
 from nvalchemi_toolkit_b200.distributed.ops import ShardTensor, halo_forward, halo_scatter_correct
 from nvalchemi_toolkit_b200.distributed import helpers
+from nvalchemi_toolkit_b200.distributed.pipeline2d import DomainPipeline
 
 __all__ = ["DomainConfig", "HookScope", "StrategyKind", "SpatialPartitioner", "IndexPartitioner", "factor_grid", "MLIPSpec",
            "Consolidation", "get_spec", "register_spec", "HaloExchange", "ShardedBatch", "DistributedModel", "DistributedPipelineModel",
-           "consolidate_outputs", "DomainParallel", "DynamicsCoordinator", "ShardTensor", "halo_forward",
+           "consolidate_outputs", "DomainParallel", "DomainPipeline", "DynamicsCoordinator", "ShardTensor", "halo_forward",
            "halo_scatter_correct", "helpers", "all_gather_rows", "all_to_all_rows", "SPEC_LJ_HALO", "SPEC_PAIR_HALO",
            "SPEC_DFTD3_HALO", "SPEC_EWALD_REAL_HALO", "SPEC_MACE_HALO", "SPEC_MACE_CUEQ_HALO", "SPEC_AIMNET2_HALO",
            "SPEC_DEMO", "SPEC_MACE_GRAPH_PARTITION", "SPEC_AIMNET2_GRAPH_PARTITION"]

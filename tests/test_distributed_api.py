@@ -537,3 +537,54 @@ def test_global_reductions_of_optimisers_and_thermostats(kind):
     dyn.run(batch, n_steps=15)
     got = torch.tensor(res[0], dtype=torch.float64)
     assert float((got - batch.positions).abs().max()) < (1e-8 if kind != "fire" else 1e-6)
+
+
+def _p2d_inputs():
+    out = []
+    for seed in (0, 1, 2):
+        b = _lj_batch(4, noise=0.12, seed=seed, velocities=0.0)
+        out.append(b)
+    return out
+
+
+def _p2d_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nvalchemi_toolkit_b200.distributed.pipeline2d import DomainPipeline
+        from nvalchemi_toolkit_b200.dynamics import FIRE2
+
+        torch.set_num_threads(1)
+        inputs = _p2d_inputs()
+        pipe = DomainPipeline([lambda: FIRE2(_lj(), dt=0.05), lambda: NVE(_lj(), dt=2.0)], n_steps=[10, 5],
+                              config=DomainConfig(cutoff=6.0, skin=0.6), domain_size=2, template=inputs[0])
+        res = pipe.run(inputs if rank == 0 else None)
+        q.put((rank, pipe.stage, pipe.num_processed, [r.positions.tolist() for r in res]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_pipeline_of_domain_decomposed_stages():
+    import torch.multiprocessing as mp
+
+    from nvalchemi_toolkit_b200.dynamics import FIRE2
+    from nvalchemi_toolkit_b200.dynamics.base import DynamicsStage
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_p2d_worker, args=(r, 4, 29881, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    res = {r: (st, n, out) for r, st, n, out in (q.get(timeout=300) for _ in range(4))}
+    for p in procs:
+        p.join(timeout=30)
+    assert [res[r][0] for r in range(4)] == [0, 0, 1, 1] and all(res[r][1] == 3 for r in range(4))
+    assert len(res[2][2]) == 3 and res[0][2] == [] and res[3][2] == []
+    for k, batch in enumerate(_p2d_inputs()):  # the same two stages applied one after the other in one process
+        for make, n in ((lambda m, h: FIRE2(m, dt=0.05, hooks=[h]), 10), (lambda m, h: NVE(m, dt=2.0, hooks=[h]), 5)):
+            model = _lj()
+            dyn = make(model, NeighborListHook(model.model_config.neighbor_config, stage=DynamicsStage.BEFORE_COMPUTE))
+            dyn._call_hooks(DynamicsStage.BEFORE_COMPUTE, batch)
+            dyn.compute(batch)
+            dyn.run(batch, n_steps=n)
+        assert torch.allclose(torch.tensor(res[2][2][k], dtype=torch.float64), batch.positions, atol=1e-8)
