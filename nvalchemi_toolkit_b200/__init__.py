@@ -9,3 +9,4 @@ __version__ = "0.1.0"
 
 from nvalchemi_toolkit_b200._typing import AtomCategory  # noqa: F401
 from nvalchemi_toolkit_b200.data import AtomicData, Batch  # noqa: F401
+from nvalchemi_toolkit_b200.ops import compat as _compat  # noqa: F401,E402  registers the reference's operator names

@@ -101,3 +101,28 @@ def test_fused_stage_migrates_status():
     out = fused.run(b, n_steps=10)
     assert out.status.reshape(-1).tolist() == [2, 2, 2]
     assert fused.step_count == 3  # the migration step already counts toward the MD budget (as in the reference)
+
+
+def test_reference_operator_names_are_callable():
+    """Call sites written against ``torch.ops.nvalchemi.*`` / ``torch.ops.nvalchemi_hooks.*`` keep working."""
+    import torch
+
+    import nvalchemi_toolkit_b200  # noqa: F401  (registers the operators)
+    from nvalchemi_toolkit_b200.ops import compat
+
+    assert {"initialize_velocities", "velocity_rescale", "remove_com_motion", "compute_temperature", "align_cell",
+            "lj_energy_forces_batch", "per_system_reduce", "segmented_sum", "wrap_positions"} <= set(compat.registered_names())
+    n, m = 12, 3
+    vel = torch.zeros(n, 3, dtype=torch.float64)
+    masses = torch.full((n,), 12.0, dtype=torch.float64)
+    batch_idx = torch.arange(m, dtype=torch.int32).repeat_interleave(4)
+    torch.ops.nvalchemi.initialize_velocities(vel, masses, torch.full((m,), 300.0, dtype=torch.float64), batch_idx, 7)
+    ke = torch.ops.nvalchemi_hooks.compute_kinetic_energy(vel, masses, batch_idx, m)
+    temp = torch.ops.nvalchemi.compute_temperature(ke, torch.full((m,), 4))
+    assert torch.allclose(temp, torch.full((m,), 300.0, dtype=torch.float64), rtol=1e-6)
+    torch.ops.nvalchemi.velocity_rescale(vel, torch.full((m,), 2.0, dtype=torch.float64), batch_idx)
+    assert torch.allclose(torch.ops.nvalchemi_hooks.compute_kinetic_energy(vel, masses, batch_idx, m), 4 * ke)
+    s = torch.ops.nvalchemi_hooks.segmented_sum(torch.ones(n, 2, dtype=torch.float64), batch_idx, m)
+    assert torch.equal(s, torch.full((m, 2), 4.0, dtype=torch.float64))
+    assert torch.equal(torch.ops.nvalchemi.per_system_reduce(torch.ones(n, dtype=torch.float64), batch_idx, m),
+                       torch.full((m,), 4.0, dtype=torch.float64))
