@@ -88,3 +88,22 @@ def test_from_raw_dicts_skips_validation():
               "my_field": torch.ones(2, 4)} for _ in range(3)]
     b = Batch.from_raw_dicts(dicts, field_levels={"my_field": "node"})
     assert b.my_field.shape == (6, 4) and b.num_graphs == 3
+
+
+def test_reference_package_name_alias():
+    from nvalchemi_toolkit_b200 import compat
+
+    compat.install_alias()
+    try:
+        import nvalchemi  # noqa: F401
+        from nvalchemi.data import AtomicData as A
+        from nvalchemi.dynamics import NVE as N
+        from nvalchemi.models.lj import LennardJonesModelWrapper as L
+
+        import nvalchemi_toolkit_b200 as real
+        from nvalchemi_toolkit_b200.dynamics import NVE
+        from nvalchemi_toolkit_b200.models.lj import LennardJonesModelWrapper
+
+        assert nvalchemi is real and A is real.AtomicData and N is NVE and L is LennardJonesModelWrapper
+    finally:
+        compat.remove_alias()
