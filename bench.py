@@ -140,7 +140,7 @@ def run_ours(args) -> dict:
         per_rank = torch.tensor(sim.e2e_bytes(), dtype=torch.int64, device=device)
         dist.all_reduce(per_rank)  # bytes of the whole job per step (every rank moves its own atoms)
         counts = tuple(int(x) for x in per_rank.tolist())
-        parallelism = f"dd{world} (slabs along x, halo 10 A)"
+        parallelism = f"dd{world} (slabs along x, ghost senders within 5 A cutoff + 1 A skin)"
     else:
         batch = build_system(cells, device, atom_order=args.atom_order)
         dyn, wrapper = build_dynamics(device, args.skin, args.max_neighbors)
@@ -197,6 +197,15 @@ def run_ours(args) -> dict:
     ms = timed(step, args.steps)
     launches = _native_counter.count()
     clocks = sampler.stop() if rank == 0 else {}
+    if world > 1 and args.phase_times:
+        sim.profile = True
+        for _ in range(3):
+            step()
+        phases = sim.phase_summary()
+        sim.profile = False
+        if rank == 0:
+            print("phase ms:", {k: round(v, 2) for k, v in phases.items()}, "owned", sim.n_owned, "ghost", sim.n_ghost,
+                  file=sys.stderr, flush=True)
     for _ in range(min(args.warmup, 2)):
         e2e_step()
     ms_e2e = timed(e2e_step, args.steps)
@@ -246,6 +255,7 @@ def main() -> None:
     ap.add_argument("--cells", type=int, default=64, help="conventional fcc cells per edge (64 -> 1,048,576 atoms)")
     ap.add_argument("--skin", type=float, default=0.0, help="Verlet skin; 0 rebuilds the list every step (cheaper than the extra edges at this size)")
     ap.add_argument("--max-neighbors", type=int, default=64)
+    ap.add_argument("--phase-times", action="store_true", help="multi-GPU: also print per-phase CUDA-event times of rank 0")
     ap.add_argument("--atom-order", default="lattice", choices=["lattice", "morton"],
                     help="memory order of the synthetic atoms: x-major lattice order or a Z-curve over 4 A bins")
     args = ap.parse_args()

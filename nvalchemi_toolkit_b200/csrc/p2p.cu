@@ -187,3 +187,37 @@ void multimem_allreduce(int64_t mc_ptr, int64_t byte_offset, int64_t numel, int6
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("multimem_allreduce(int mc_ptr, int byte_offset, int numel, int rank, int world, float scale, Tensor like) -> ()", &nva::multimem_allreduce);
 }
+
+namespace nva {
+// Reverse halo: dst_{home_rank[g]}[home_row[g], :] += src[row0 + g, :].  Gradients that the local kernels accumulated on
+// ghost rows travel to the owners once per row (instead of one NVLink reduction per edge from inside the convolution).
+__global__ void halo_push_add_kernel(int64_t n_ghost, int D, const float* __restrict__ src, int64_t row0,
+                                     const int* __restrict__ home_rank, const int* __restrict__ home_row,
+                                     const int64_t* __restrict__ dst_ptrs) {
+  int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (t >= n_ghost * D) return;
+  int64_t g = t / D;
+  int d = (int)(t - g * D);
+  float v = src[(row0 + g) * D + d];
+  if (v == 0.f) return;
+  float* dst = reinterpret_cast<float*>(dst_ptrs[home_rank[g]]);
+  atomicAdd(dst + (int64_t)home_row[g] * D + d, v);
+}
+
+void halo_push_add_rows(const at::Tensor& src, int64_t row0, const at::Tensor& home_rank, const at::Tensor& home_row,
+                        const at::Tensor& dst_ptrs) {
+  c10::cuda::CUDAGuard guard(src.device());
+  NVA_CHECK_CONTIG(src);
+  int64_t n = home_rank.size(0);
+  if (n == 0) return;
+  int D = (int)(src.numel() / src.size(0));
+  int64_t total = n * D;
+  halo_push_add_kernel<<<(unsigned)((total + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      n, D, src.data_ptr<float>(), row0, home_rank.data_ptr<int>(), home_row.data_ptr<int>(), dst_ptrs.data_ptr<int64_t>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+}  // namespace nva
+
+TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
+  m.def("halo_push_add_rows(Tensor src, int row0, Tensor home_rank, Tensor home_row, Tensor dst_ptrs) -> ()", &nva::halo_push_add_rows);
+}

@@ -59,6 +59,23 @@ class _DDView:
     def gpos_ptrs(self) -> torch.Tensor:
         return self.o.gpos_ptrs
 
+    #: ghost rows of node features are copied from their owners once per layer (bulk pull at NVLink bandwidth) and ghost
+    #: rows of the gradients are returned once per layer (bulk push); with False the convolution kernels touch peer
+    #: memory per edge instead
+    prefetch = True
+
+    @property
+    def n_local(self) -> int:
+        return self.o.n_owned + self.o.n_ghost
+
+    @property
+    def ghost_home_rank(self) -> torch.Tensor:
+        return self.o.ghost_home_rank
+
+    @property
+    def ghost_home_row(self) -> torch.Tensor:
+        return self.o.ghost_home_row
+
     def feature_buffer(self, key: str, shape: tuple[int, ...]) -> tuple[torch.Tensor, torch.Tensor]:
         buf, ptrs = self.o.feat[key]
         n = shape[0]
@@ -101,13 +118,15 @@ class SlabDomainMD:
         self.cap_owned = int(density_rows * 1.15) + 4096
         ghost_est = 2.0 * self.h_frac * self.n_total
         self.cap_local = self.cap_owned + int(ghost_est * 1.3) + 4096
-        nbytes = 4 * (3 * self.cap_local + 3 * self.cap_owned + self.cap_owned * C * (1 + 2 * nlm_hidden)) + (1 << 16)
+        nbytes = 4 * (3 * self.cap_local + 3 * self.cap_local + self.cap_local * C * (1 + 2 * nlm_hidden)) + (1 << 16)
         self.p2p = P2PContext(nbytes, device, self.group)
         a = self.p2p.arena
         self.pos_buf, self.pos_ptrs = a.alloc((self.cap_local, 3))
-        self.gpos_buf, self.gpos_ptrs = a.alloc((self.cap_owned, 3))
-        self.feat = {"u0": a.alloc((self.cap_owned, 1, C)), "u1": a.alloc((self.cap_owned, nlm_hidden, C)),
-                     "du1": a.alloc((self.cap_owned, nlm_hidden, C))}
+        # row capacity = owned + ghost: owners keep their rows at the front (peers address them by owner row), ghost rows
+        # behind them hold the copies pulled from / the gradients to be pushed to the owners
+        self.gpos_buf, self.gpos_ptrs = a.alloc((self.cap_local, 3))
+        self.feat = {"u0": a.alloc((self.cap_local, 1, C)), "u1": a.alloc((self.cap_local, nlm_hidden, C)),
+                     "du1": a.alloc((self.cap_local, nlm_hidden, C))}
         self.view = _DDView(self)
         self.n_owned = 0
         self.n_ghost = 0
@@ -223,6 +242,30 @@ class SlabDomainMD:
         self.num_topology_builds += 1
         self.p2p.barrier()
 
+    # ------------------------------------------------------------------ optional phase timing (CUDA events)
+    def _phase(self, name: str) -> Any:
+        import contextlib
+
+        if not getattr(self, "profile", False):
+            return contextlib.nullcontext()
+        owner = self
+
+        class _Timer:
+            def __enter__(self) -> None:
+                self.a, self.b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                self.a.record()
+
+            def __exit__(self, *exc: Any) -> None:
+                self.b.record()
+                owner.__dict__.setdefault("_phase_events", {}).setdefault(name, []).append((self.a, self.b))
+
+        return _Timer()
+
+    def phase_summary(self) -> dict[str, float]:
+        """Milliseconds per recorded occurrence of every phase (set ``self.profile = True`` before stepping)."""
+        torch.cuda.synchronize(self.device)
+        return {k: sum(a.elapsed_time(b) for a, b in v) / max(1, len(v)) for k, v in getattr(self, "_phase_events", {}).items()}
+
     # ------------------------------------------------------------------ one force evaluation
     def refresh_ghosts(self) -> None:
         self.p2p.barrier()  # every rank finished moving its owned atoms
@@ -230,24 +273,27 @@ class SlabDomainMD:
                              self.pos_ptrs)
 
     def compute_forces(self) -> None:
-        self.refresh_ghosts()
+        with self._phase("ghost_positions"):
+            self.refresh_ghosts()
         n_local = self.n_owned + self.n_ghost
         pos_local = self.pos_buf[:n_local]
         cell = self.cell.reshape(1, 3, 3)
         k = self.max_neighbors
-        while True:
-            if self._nl is None or self._nl[0].shape != (n_local, k):
-                self._nl = (torch.empty(n_local, k, dtype=torch.int32, device=self.device),
-                            torch.empty(n_local, dtype=torch.int32, device=self.device),
-                            torch.empty(n_local, k, 3, dtype=torch.int32, device=self.device))
-            nm, num, sh = _nb.neighbor_matrix(pos_local, cell, self.pbc, self.batch_idx, self.batch_ptr, self.cutoff, k,
-                                              False, out=self._nl)
-            csr = native.build_csr(nm[: self.n_owned], num[: self.n_owned], sh[: self.n_owned])
-            if csr.max_count <= k:
-                break
-            k = self.max_neighbors = ((int(csr.max_count * 1.25) + 15) // 16) * 16
+        with self._phase("neighbors"):
+            while True:
+                if self._nl is None or self._nl[0].shape != (n_local, k):
+                    self._nl = (torch.empty(n_local, k, dtype=torch.int32, device=self.device),
+                                torch.empty(n_local, dtype=torch.int32, device=self.device),
+                                torch.empty(n_local, k, 3, dtype=torch.int32, device=self.device))
+                nm, num, sh = _nb.neighbor_matrix(pos_local, cell, self.pbc, self.batch_idx, self.batch_ptr, self.cutoff, k,
+                                                  False, out=self._nl)
+                csr = native.build_csr(nm[: self.n_owned], num[: self.n_owned], sh[: self.n_owned])
+                if csr.max_count <= k:
+                    break
+                k = self.max_neighbors = ((int(csr.max_count * 1.25) + 15) // 16) * 16
         data = {"positions": pos_local, "cell": cell, "_csr": csr}
-        out = native.forward(self.model, data, self.species, self.batch_idx.long(), 1, True, False, dd=self.view)
+        with self._phase("model"):
+            out = native.forward(self.model, data, self.species, self.batch_idx.long(), 1, True, False, dd=self.view)
         self.forces = out["forces"]
         self.last_energy_local = out["energy"]
 
@@ -264,6 +310,8 @@ class SlabDomainMD:
             self.rebuild_topology()
         pos = self.pos
         b = self.owned_batch_idx
+        timer = self._phase("integrate_and_flags")
+        timer.__enter__()
         if self.gamma is not None:
             _ops.langevin_half_step(pos, self.vel, self.forces, self.mass, self.dt, self.kT, self.gamma,
                                     self.seed + self.step_count, b, self.gid)
@@ -279,6 +327,7 @@ class SlabDomainMD:
         self._flag_host.copy_(fl, non_blocking=True)
         self._flag_event = torch.cuda.Event()
         self._flag_event.record()
+        timer.__exit__(None, None, None)
         self.compute_forces()
         _ops.vv_velocity_finalize(self.vel, self.forces, self.mass, self.dt, b)
         self.step_count += 1

@@ -293,8 +293,10 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
     C, nz, lmax = cfg.channels, len(cfg.atomic_numbers), cfg.max_ell
     rmax, nb, pc = float(cfg.r_max), cfg.num_bessel, cfg.num_polynomial_cutoff
     geom = (pos, cell, b32, csr.erecv, csr.esend, csr.eS)
-    hr = dd.home_rank if dd is not None else None
-    hw = dd.home_row if dd is not None else None
+    pull = dd is not None and getattr(dd, "prefetch", False)  # ghost rows copied / returned in bulk, kernels stay local
+    hr = dd.home_rank if dd is not None and not pull else None
+    hw = dd.home_row if dd is not None and not pull else None
+    n_rows = dd.n_local if pull else n  # rows of the feature / gradient buffers the kernels see
     if dd is not None:
         dd.gpos.zero_()
 
@@ -307,12 +309,16 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         sc = _skip(ip, h, species, nz)
         u_ptrs = du = du_ptrs = None
         if dd is not None:
-            u, u_ptrs = dd.feature_buffer(f"u{li}", (n, h.shape[1], C))
-            _per_l_linear(h, ip.linear_up, ip.l_in, out=u)
+            u, u_ptrs = dd.feature_buffer(f"u{li}", (n_rows, h.shape[1], C))
+            _per_l_linear(h, ip.linear_up, ip.l_in, out=u[:n])
             if li > 0 and compute_force:
-                du, du_ptrs = dd.feature_buffer(f"du{li}", (n, h.shape[1], C))
+                du, du_ptrs = dd.feature_buffer(f"du{li}", (n_rows, h.shape[1], C))
                 du.zero_()
             dd.barrier()  # every rank's u (and zeroed du / gradient buffers) is in place before peers touch it
+            if pull:
+                ops.halo_pull_rows(u, n, dd.ghost_home_rank, dd.ghost_home_row, None, u_ptrs)
+                pull_ptrs = (u_ptrs, du_ptrs)
+                u_ptrs = du_ptrs = None  # the convolution kernels read and write local rows only
         else:
             u = _per_l_linear(h, ip.linear_up, ip.l_in).contiguous()
         fused = _fused_ok(model, ip)
@@ -352,7 +358,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         else:
             node_e += s @ (ip.readout_w1 / math.sqrt(C))
             ro = (None, None)
-        saved.append((ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs, wgs))
+        saved.append((ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs if not pull else pull_ptrs[1], wgs))
         h = h_new
         del B, sc
     scale, shift = model.scale.to(pos.dtype), model.shift.to(pos.dtype)
@@ -366,11 +372,12 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         return out
 
     grad_pos = dd.gpos if dd is not None else torch.zeros_like(pos)
-    gp_ptrs = dd.gpos_ptrs if dd is not None else None
+    gp_ptrs = dd.gpos_ptrs if dd is not None and not pull else None
     strain_grad = torch.zeros(num_graphs, 9, dtype=torch.float64, device=dev) if compute_stress else None
     dh: torch.Tensor | None = None
     for li in range(len(saved) - 1, -1, -1):
         ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs, wgs = saved[li]
+        k_du_ptrs = None if pull else du_ptrs  # pointer table handed to the kernels (none: local rows only)
         n_out = sum(2 * l + 1 for l in ip.l_out)
         dh_tot = pos.new_zeros(n, n_out, C) if dh is None else dh
         if ip.last:
@@ -394,18 +401,27 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
                 for g, wg in enumerate(wgs):
                     ops.mace_conv_fused(0 if ip.l_in == [0] else 1, g, True, wg, h3, u, pos, cell, b32, csr.eptr, csr.esend,
                                         csr.eS, i0, i1 - i0, e0, rmax, dmid, du, grad_pos, strain_grad, hr, hw, u_ptrs,
-                                        du_ptrs, gp_ptrs, err)
+                                        k_du_ptrs, gp_ptrs, err)
                 del ef, h3
         else:
             for (i0, i1, e0, e1) in _chunks(csr, n, 8 * P * C):
                 ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, True)
                 RD = _radial_weights(ws, ef, True).reshape(e1 - e0, 2, P, C)
                 ops.mace_conv_bwd(u, dmid, pos, cell, b32, csr.eptr, csr.esend, csr.eS, RD, i0, i1 - i0, e0, rmax, du,
-                                  grad_pos, strain_grad, hr, hw, u_ptrs, du_ptrs, gp_ptrs)
+                                  grad_pos, strain_grad, hr, hw, u_ptrs, k_du_ptrs, gp_ptrs)
                 del ef, RD
         del dmid
+        if pull:
+            # return what was accumulated on ghost rows to the owners, once per row
+            dd.barrier()  # owners finished their own accumulation
+            if li > 0:
+                ops.halo_push_add_rows(du, n, dd.ghost_home_rank, dd.ghost_home_row, du_ptrs)
+            if li == 0:
+                ops.halo_push_add_rows(grad_pos[:dd.n_local], n, dd.ghost_home_rank, dd.ghost_home_row, dd.gpos_ptrs)
         if dd is not None:
             dd.barrier()  # feature / position gradients pushed by peers have landed
+        if li > 0 and dd is not None:
+            du = du[:n]
         if li > 0 and wgs is not None:
             # the fused kernel accumulates the feature gradient as [row, channel, component] (vector reductions)
             du = du.view(du.shape[0], C, du.shape[1]).transpose(1, 2).contiguous()
