@@ -104,3 +104,28 @@ def test_fused_radial_mlp_matches_fp32_reference(rows):
     for _ in range(2):  # the two identity layers still apply the activation (and tf32 rounding of their input)
         l1 = l1 * torch.sigmoid(l1) * SILU_NORM
     assert float((one.double() - l1).abs().max()) < 2e-3 * float(l1.abs().max())
+
+
+@pytest.mark.gpu
+def test_halo_pull_and_push_add_rows_single_device():
+    """Row gather from / reduction into 'peer' buffers addressed through a pointer table (one device: the table points at
+    two local buffers that stand in for two ranks)."""
+    dev = "cuda"
+    torch.manual_seed(0)
+    a, b = torch.randn(10, 6, device=dev), torch.randn(8, 6, device=dev)
+    ptrs = torch.tensor([a.data_ptr(), b.data_ptr()], dtype=torch.int64, device=dev)
+    home_rank = torch.tensor([1, 0, 1, 1, 0], dtype=torch.int32, device=dev)
+    home_row = torch.tensor([7, 2, 0, 7, 9], dtype=torch.int32, device=dev)
+    dst = torch.zeros(9, 6, device=dev)
+    shift = torch.arange(30, dtype=torch.float32, device=dev).reshape(5, 6)
+    torch.ops.nvalchemi.halo_pull_rows(dst, 4, home_rank, home_row, shift, ptrs)
+    want = torch.stack([b[7], a[2], b[0], b[7], a[9]]) + shift
+    assert torch.equal(dst[4:], want) and float(dst[:4].abs().sum()) == 0
+    a0, b0 = a.clone(), b.clone()
+    src = torch.randn(9, 6, device=dev)
+    torch.ops.nvalchemi.halo_push_add_rows(src, 4, home_rank, home_row, ptrs)
+    a0[2] += src[5]
+    a0[9] += src[8]
+    b0[7] += src[4] + src[7]
+    b0[0] += src[6]
+    assert torch.allclose(a, a0, atol=1e-6) and torch.allclose(b, b0, atol=1e-6)
