@@ -83,6 +83,7 @@ struct FusedArgs {
   double* virial;
   const int* home_rank;
   const int* home_row;
+  const int* row_map;         // optional: sender j reads feature row row_map[j] (rows shared by many atoms, e.g. per species)
   const int64_t* u_ptrs;
   const int64_t* du_ptrs;
   const int64_t* gpos_ptrs;
@@ -299,7 +300,7 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
               if (BWD && NEED_DU) dub = reinterpret_cast<float*>(a.du_ptrs[hr]);
               if (BWD) gpb = reinterpret_cast<float*>(a.gpos_ptrs[hr]);
             }
-            q.up = ub + jr * NIN * C;
+            q.up = ub + (a.row_map != nullptr ? (int64_t)a.row_map[j] : jr) * NIN * C;
             q.dup = (BWD && NEED_DU) ? dub + jr * NIN * C : nullptr;
             q.dup_local = dub == a.du ? 1 : 0;
             q.gpj = BWD ? gpb + 3 * jr : nullptr;
@@ -510,7 +511,8 @@ void mace_conv_fused(int64_t layer, int64_t group, bool backward, const Tensor& 
                      Tensor mid_or_G, const c10::optional<Tensor>& du, const c10::optional<Tensor>& grad_pos,
                      const c10::optional<Tensor>& virial, const c10::optional<Tensor>& home_rank,
                      const c10::optional<Tensor>& home_row, const c10::optional<Tensor>& u_ptrs,
-                     const c10::optional<Tensor>& du_ptrs, const c10::optional<Tensor>& gpos_ptrs, Tensor err) {
+                     const c10::optional<Tensor>& du_ptrs, const c10::optional<Tensor>& gpos_ptrs, Tensor err,
+                     const c10::optional<Tensor>& row_map) {
   c10::cuda::CUDAGuard guard(pos.device());
   NVA_CHECK_CONTIG(wg); NVA_CHECK_CONTIG(h3); NVA_CHECK_CONTIG(u); NVA_CHECK_CONTIG(mid_or_G);
   TORCH_CHECK(u.size(2) == 128, "the fused convolution is specialised for 128 channels");
@@ -528,6 +530,8 @@ void mace_conv_fused(int64_t layer, int64_t group, bool backward, const Tensor& 
   a.virial = virial.has_value() ? virial->data_ptr<double>() : nullptr;
   a.home_rank = home_rank.has_value() ? home_rank->data_ptr<int>() : nullptr;
   a.home_row = home_row.has_value() ? home_row->data_ptr<int>() : nullptr;
+  a.row_map = row_map.has_value() ? row_map->data_ptr<int>() : nullptr;
+  TORCH_CHECK(!(row_map.has_value() && home_rank.has_value()), "row_map addresses local feature rows only");
   a.u_ptrs = u_ptrs.has_value() ? u_ptrs->data_ptr<int64_t>() : nullptr;
   a.du_ptrs = du_ptrs.has_value() ? du_ptrs->data_ptr<int64_t>() : nullptr;
   a.gpos_ptrs = gpos_ptrs.has_value() ? gpos_ptrs->data_ptr<int64_t>() : nullptr;
@@ -554,5 +558,5 @@ void mace_conv_fused(int64_t layer, int64_t group, bool backward, const Tensor& 
 }  // namespace nva
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
-  m.def("mace_conv_fused(int layer, int group, bool backward, Tensor wg, Tensor h3, Tensor u, Tensor pos, Tensor cell, Tensor batch_idx, Tensor eptr, Tensor esend, Tensor eS, int i0, int ni, int e_chunk0, float rmax, Tensor(a!) mid_or_G, Tensor(b!)? du, Tensor(c!)? grad_pos, Tensor(d!)? virial, Tensor? home_rank, Tensor? home_row, Tensor? u_ptrs, Tensor? du_ptrs, Tensor? gpos_ptrs, Tensor(e!) err) -> ()", &nva::mace_conv_fused);
+  m.def("mace_conv_fused(int layer, int group, bool backward, Tensor wg, Tensor h3, Tensor u, Tensor pos, Tensor cell, Tensor batch_idx, Tensor eptr, Tensor esend, Tensor eS, int i0, int ni, int e_chunk0, float rmax, Tensor(a!) mid_or_G, Tensor(b!)? du, Tensor(c!)? grad_pos, Tensor(d!)? virial, Tensor? home_rank, Tensor? home_row, Tensor? u_ptrs, Tensor? du_ptrs, Tensor? gpos_ptrs, Tensor(e!) err, Tensor? row_map=None) -> ()", &nva::mace_conv_fused);
 }

@@ -73,6 +73,11 @@ class _DDView:
         return self.o.ghost_home_rank
 
     @property
+    def species_local(self) -> torch.Tensor:
+        """Species index of owned and ghost rows (the first interaction reads a per-species feature table)."""
+        return self.o.species_local
+
+    @property
     def ghost_home_row(self) -> torch.Tensor:
         return self.o.ghost_home_row
 
@@ -217,6 +222,7 @@ class SlabDomainMD:
         self.z = z_all[mine].contiguous()
         self.gid = gid[mine].contiguous()
         self.species = self.model.species_index(self.z)
+        self.species_local = torch.cat([self.species, self.model.species_index(z_all[g_idx])]).contiguous()
         self.pos_buf[:n_owned] = pos_w[mine]
         self.ref_pos = pos_w[mine].clone()
         self.forces = torch.zeros(n_owned, 3, device=self.device)

@@ -307,8 +307,16 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         ws = [w / math.sqrt(w.shape[0]) for w in ip.radial]
         P = len(ip.paths)
         sc = _skip(ip, h, species, nz)
-        u_ptrs = du = du_ptrs = None
-        if dd is not None:
+        u_ptrs = du = du_ptrs = row_map = None
+        # The input of the first interaction is the species embedding: its rows are identical for all atoms of a
+        # species.  The fused kernels then read a [species, 1, C] table through a per-atom row map instead of
+        # gathering per-atom rows from a multi-hundred-MB array (and no ghost rows have to be exchanged).
+        sp_local = species if dd is None else getattr(dd, "species_local", None)
+        if li == 0 and ip.l_in == [0] and _fused_ok(model, ip) and sp_local is not None and (dd is None or pull):
+            table = model.node_embedding.to(pos.dtype) / math.sqrt(nz)
+            u = (table @ (ip.linear_up[0] / math.sqrt(C))).unsqueeze(1).contiguous()
+            row_map = sp_local.to(torch.int32).contiguous()
+        elif dd is not None:
             u, u_ptrs = dd.feature_buffer(f"u{li}", (n_rows, h.shape[1], C))
             _per_l_linear(h, ip.linear_up, ip.l_in, out=u[:n])
             if li > 0 and compute_force:
@@ -332,7 +340,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
                 for g, wg in enumerate(wgs):
                     ops.mace_conv_fused(0 if ip.l_in == [0] else 1, g, False, wg, h3, u, pos, cell, b32, csr.eptr, csr.esend,
                                         csr.eS, i0, i1 - i0, e0, rmax, mid, None, None, None, hr, hw, u_ptrs, None, None,
-                                        err)
+                                        err, row_map)
                 del ef, h3
         else:
             wgs = None
@@ -358,7 +366,8 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         else:
             node_e += s @ (ip.readout_w1 / math.sqrt(C))
             ro = (None, None)
-        saved.append((ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs if not pull else pull_ptrs[1], wgs))
+        saved.append((ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs if not (pull and row_map is None) else pull_ptrs[1], wgs,
+                      row_map))
         h = h_new
         del B, sc
     scale, shift = model.scale.to(pos.dtype), model.shift.to(pos.dtype)
@@ -376,7 +385,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
     strain_grad = torch.zeros(num_graphs, 9, dtype=torch.float64, device=dev) if compute_stress else None
     dh: torch.Tensor | None = None
     for li in range(len(saved) - 1, -1, -1):
-        ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs, wgs = saved[li]
+        ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs, wgs, row_map = saved[li]
         k_du_ptrs = None if pull else du_ptrs  # pointer table handed to the kernels (none: local rows only)
         n_out = sum(2 * l + 1 for l in ip.l_out)
         dh_tot = pos.new_zeros(n, n_out, C) if dh is None else dh
@@ -401,7 +410,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
                 for g, wg in enumerate(wgs):
                     ops.mace_conv_fused(0 if ip.l_in == [0] else 1, g, True, wg, h3, u, pos, cell, b32, csr.eptr, csr.esend,
                                         csr.eS, i0, i1 - i0, e0, rmax, dmid, du, grad_pos, strain_grad, hr, hw, u_ptrs,
-                                        k_du_ptrs, gp_ptrs, err)
+                                        k_du_ptrs, gp_ptrs, err, row_map)
                 del ef, h3
         else:
             for (i0, i1, e0, e1) in _chunks(csr, n, 8 * P * C):

@@ -172,10 +172,11 @@ def test_fused_tensor_core_convolution_matches_unfused():
             native.FUSED = True
     assert native.fused_error_status(torch.device("cuda", 0)) == 0 and gemm.check_errors(b.positions) == 0
     ref, got = outs[False], outs[True]
-    # both paths round the same operands to tf32 in different places: measured 3e-6 / 2e-4 / 1e-5
-    assert float((got["energy"] - ref["energy"]).abs().max()) < 5e-5 * max(1.0, float(ref["energy"].abs().max()))
+    # the two paths round different operands to tf32 (the fused one keeps the first layer's input features in fp32):
+    # measured 2e-4 / 2e-4 / 1e-3
+    assert float((got["energy"] - ref["energy"]).abs().max()) < 1e-3 * max(1.0, float(ref["energy"].abs().max()))
     assert float((got["forces"] - ref["forces"]).abs().max()) < 1.5e-3 * float(ref["forces"].abs().max())
-    assert float((got["stress"] - ref["stress"]).abs().max()) < 2e-4 * float(ref["stress"].abs().max())
+    assert float((got["stress"] - ref["stress"]).abs().max()) < 3e-3 * float(ref["stress"].abs().max())
     oracle = MACE(cfg, backend="torch").double().cuda()
     oracle.load_state_dict({k: v.double() for k, v in model.state_dict().items()})
     wo = MACEWrapper(oracle)
@@ -183,6 +184,10 @@ def test_fused_tensor_core_convolution_matches_unfused():
     compute_neighbors(bo, config=wo.model_config.neighbor_config)
     exact = wo(bo)
     assert float((got["forces"].double() - exact["forces"]).abs().max()) < 2e-2 * float(exact["forces"].abs().max())
+    # against the float64 oracle the fused path must not be worse than the unfused one (both are tf32-limited)
+    e_fused = float((got["energy"].double() - exact["energy"]).abs().max())
+    e_unfused = float((ref["energy"].double() - exact["energy"]).abs().max())
+    assert e_fused < max(2.0 * e_unfused, 2e-4 * float(exact["energy"].abs().max()))
     err = {k: float((got[k] - ref[k]).abs().max() / ref[k].abs().max()) for k in ("energy", "forces", "stress")}
     print("fused vs unfused relative errors:", err, "| vs float64 oracle (forces):",
           float((got["forces"].double() - exact["forces"]).abs().max() / exact["forces"].abs().max()))
