@@ -26,7 +26,6 @@
 namespace nva {
 using at::Tensor;
 
-constexpr int FT = 16;          // edges per tile
 constexpr int RECV_BLOCK = 32;  // receivers per work item
 
 template <int LAYER, int GROUP>
@@ -97,7 +96,11 @@ __device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, %
 // NG warp-groups of 128 compute threads share one tile: group g takes edges g, g+NG, ... (all groups can read all 128
 // TMEM lanes because warp w reaches lanes 32*(w%4)..), keeps its own partial sums and adds them to `mid` with
 // reductions.  Four compute warps alone would leave the SM's schedulers with one warp each.
-template <int LAYER, int GROUP, bool BWD, bool NEED_DU, int NG>
+// FT = edges per tile = N of the MMAs (backward: 2 FT).  One tcgen05.mma with M = 128 occupies the tensor pipe for about
+// 128 cycles whatever its N (measured: ~175 cycles per instruction at N = 16 and N = 32 alike), so the radial-weight
+// GEMM costs paths x 8 x 128 / FT cycles per edge: FT is made as large as the 512 TMEM columns allow with two buffers
+// of paths x N columns.
+template <int LAYER, int GROUP, bool BWD, bool NEED_DU, int NG, int FT>
 __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __grid_constant__ CUtensorMap tmW,
                                                             const __grid_constant__ CUtensorMap tmH, FusedArgs a) {
   using G = GroupSpec<LAYER, GROUP>;
@@ -115,7 +118,7 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
   const uint32_t sA = base, sB = base + A_BYTES;
   const uint32_t bar0 = sB + 2 * B_BYTES;
   const uint32_t a_full = bar0, b_full0 = bar0 + 8, b_empty0 = bar0 + 24, t_full0 = bar0 + 40, t_empty0 = bar0 + 56;
-  constexpr int GR = 4;  // depth of the edge-geometry ring
+  constexpr int GR = FT <= 32 ? 4 : 2;  // depth of the edge-geometry ring (tiles)
   const uint32_t g_full0 = bar0 + 72, g_empty0 = bar0 + 72 + 8 * GR;
   const uint32_t tmem_slot = bar0 + 72 + 16 * GR;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
@@ -242,8 +245,9 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
     int t = 0;
     bool ok = true;
     auto flush_forces = [&](int slot) {  // position gradients of a consumed tile: one lane per edge
-      if (BWD && lane < FT) {
-        TileEdge& q = te[slot * FT + lane];
+      if (BWD)
+      for (int l = lane; l < FT; l += 32) {
+        TileEdge& q = te[slot * FT + l];
         if (q.j >= 0) {
           for (int d = 0; d < 3; ++d) {
             atomicAdd(q.gpj + d, -q.f[d]);
@@ -263,15 +267,15 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
       int nt_w = (e1 - e0 + FT - 1) / FT;
       int next_recv = wi0;
       for (int tt = 0; tt < nt_w && ok; ++tt, ++t) {
-        int gs = t & (GR - 1);
+        int gs = t % GR;
         ok = mbar_wait(g_empty0 + 8 * gs, ((t / GR) & 1) ^ 1, a.err, 16);
         if (!ok) break;
         if (t >= GR) flush_forces(gs);
         __syncwarp();
         int tile_e0 = e0 + tt * FT;
-        if (lane < FT) {
-          int e = tile_e0 + lane;
-          TileEdge& q = te[gs * FT + lane];
+        for (int l = lane; l < FT; l += 32) {
+          int e = tile_e0 + l;
+          TileEdge& q = te[gs * FT + l];
           q.f[0] = 0.f; q.f[1] = 0.f; q.f[2] = 0.f;
           if (e < e1) {
             int i = next_recv;
@@ -320,8 +324,8 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
     if (BWD) {
       int first = t > GR ? t - GR : 0;
       for (int tl = first; tl < t; ++tl) {
-        if (ok && !mbar_wait(g_empty0 + 8 * (tl & (GR - 1)), (tl / GR) & 1, a.err, 17)) ok = false;
-        if (ok) flush_forces(tl & (GR - 1));
+        if (ok && !mbar_wait(g_empty0 + 8 * (tl % GR), (tl / GR) & 1, a.err, 17)) ok = false;
+        if (ok) flush_forces(tl % GR);
       }
     }
     if (!ok && lane == 0) abort_flag[0] = 1;
@@ -340,7 +344,7 @@ __global__ void __launch_bounds__(128 * NG + 64, 1) conv_fused_kernel(const __gr
       float acc[BWD ? 1 : NACC];
       float T[BWD ? NT : 1];
       for (int tt = 0; tt < nt_w && ok; ++tt, ++t) {
-        int s = t & 1, gs = t & (GR - 1);
+        int s = t & 1, gs = t % GR;
         ok = mbar_wait(g_full0 + 8 * gs, (t / GR) & 1, a.err, 18) && mbar_wait(t_full0 + 8 * s, (t >> 1) & 1, a.err, 15);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -485,13 +489,22 @@ static CUtensorMap fused_map(const float* ptr, int64_t rows, int box_rows) {
   return m;
 }
 
+// tile size: two TMEM buffers of paths x N columns must fit in 512 columns (N = FT forward, 2 FT backward)
+template <int LAYER, bool BWD>
+struct TileSize { static constexpr int FT = LAYER == 0 ? (BWD ? 32 : 64) : (BWD ? 24 : 48); };
+
 template <int LAYER, int GROUP, bool BWD, bool NEED_DU>
-static void launch_fused(const CUtensorMap& mw, const CUtensorMap& mh, const FusedArgs& a, int sms) {
+static void launch_fused(const float* wg, int64_t wrows, const float* h3, int64_t hrows, const FusedArgs& a, int sms) {
   using G = GroupSpec<LAYER, GROUP>;
+  constexpr int FT = TileSize<LAYER, BWD>::FT;
   constexpr int NROW = BWD ? 2 * FT : FT;
-  size_t smem = (size_t)G::NP * 2 * 128 * 128 + 2 * (2 * NROW * 128) + 256 + 4 * FT * 336 + 64 + 1024 + 256;
+  constexpr int GR = FT <= 32 ? 4 : 2;
+  static_assert(2 * G::NP * NROW <= 512, "TMEM budget");
+  CUtensorMap mw = fused_map(wg, wrows, 128);
+  CUtensorMap mh = fused_map(h3, hrows, NROW);
+  size_t smem = (size_t)G::NP * 2 * 128 * 128 + 2 * (2 * NROW * 128) + 256 + GR * FT * 336 + 64 + 1024 + 256;
   constexpr int NG = BWD ? 3 : 4;
-  auto kern = conv_fused_kernel<LAYER, GROUP, BWD, NEED_DU, NG>;
+  auto kern = conv_fused_kernel<LAYER, GROUP, BWD, NEED_DU, NG, FT>;
   static bool configured = false;
   if (!configured) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -536,16 +549,15 @@ void mace_conv_fused(int64_t layer, int64_t group, bool backward, const Tensor& 
   a.du_ptrs = du_ptrs.has_value() ? du_ptrs->data_ptr<int64_t>() : nullptr;
   a.gpos_ptrs = gpos_ptrs.has_value() ? gpos_ptrs->data_ptr<int64_t>() : nullptr;
   a.err = err.data_ptr<int>();
-  int64_t hrows = h3.numel() / 64;
-  CUtensorMap mw = fused_map(wg.data_ptr<float>(), wg.size(0), 128);
-  CUtensorMap mh = fused_map(h3.data_ptr<float>(), hrows, backward ? 2 * FT : FT);
+  const int64_t hrows = h3.numel() / 64, wrows = wg.size(0);
+  const float *wp = wg.data_ptr<float>(), *hp = h3.data_ptr<float>();
   int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   bool need_du = backward && a.du != nullptr;
 #define NVA_CASE(L_, G_)                                                                       \
   if (layer == L_ && group == G_) {                                                            \
-    if (!backward) launch_fused<L_, G_, false, false>(mw, mh, a, sms);                         \
-    else if (need_du) launch_fused<L_, G_, true, true>(mw, mh, a, sms);                        \
-    else launch_fused<L_, G_, true, false>(mw, mh, a, sms);                                    \
+    if (!backward) launch_fused<L_, G_, false, false>(wp, wrows, hp, hrows, a, sms);                         \
+    else if (need_du) launch_fused<L_, G_, true, true>(wp, wrows, hp, hrows, a, sms);                        \
+    else launch_fused<L_, G_, true, false>(wp, wrows, hp, hrows, a, sms);                                    \
     return;                                                                                    \
   }
   NVA_CASE(0, 0)
