@@ -386,15 +386,17 @@ def write_header(path: str) -> None:
             lines += [f"#define MACE_{gt}_FWD(h, Y, R, acc) do {{ \\"] + [t + " \\" for t in body] + ["} while (0)"]
             # forward with the channel-independent factors hoisted: Z[k] = coef * Y[b] is prepared once per edge, the
             # per-channel work is one multiply-add per coupling term
+            # per channel: a = R[q] * h[a_] once per (path, input component), then one multiply-add per coupling term
             zprep, zbody, kz = [], [], 0
             for q, p in enumerate(grp):
-                by_out_z: dict[int, list[str]] = {}
+                zbody.append("  { " + " ".join(f"const float a{a_}_ = R[{q}]*h[{a_}];"
+                                               for a_ in sorted({t[0] for t in terms[p]})))
                 for (a_, b_, c_, coef) in terms[p]:
                     zprep.append(f"  Z[{kz}] = {coef:.9e}f*Y[{b_}];")
-                    by_out_z.setdefault(loc[out_index[p][c_]], []).append(f"h[{a_}]*Z[{kz}]")
+                    o = loc[out_index[p][c_]]
+                    zbody.append(f"    acc[{o}] = fmaf(a{a_}_, Z[{kz}], acc[{o}]);")
                     kz += 1
-                for o, exprs in by_out_z.items():
-                    zbody.append(f"  acc[{o}] = fmaf(R[{q}], {' + '.join(exprs)}, acc[{o}]);")
+                zbody.append("  }")
             lines += [f"#define MACE_{gt}_NZ {kz}",
                       f"#define MACE_{gt}_ZPREP(Y, Z) do {{ \\"] + [t + " \\" for t in zprep] + ["} while (0)"]
             lines += [f"#define MACE_{gt}_FWDZ(h, Z, R, acc) do {{ \\"] + [t + " \\" for t in zbody] + ["} while (0)"]
@@ -412,9 +414,10 @@ def write_header(path: str) -> None:
                 for a_ in sorted({ab[0] for ab in tindex}):
                     expr = " + ".join(f"T[{tindex[(a_, b_)]}]*Y[{b_}]" for (aa, b_) in tindex if aa == a_)
                     edge.append(f"    v_ = {expr}; s_ = fmaf(h[{a_}], v_, s_); dh[{a_}] = fmaf(r_, v_, dh[{a_}]);")
-                for b_ in sorted({ab[1] for ab in tindex}):
-                    expr = " + ".join(f"T[{tindex[(a_, bb)]}]*h[{a_}]" for (a_, bb) in tindex if bb == b_)
-                    edge.append(f"    v_ = {expr}; dY[{b_}] = fmaf(r_, v_, dY[{b_}]);")
+                # dY_b += sum_a T_ab * (r h_a): the product r h_a is formed once per input component
+                edge.append("    " + " ".join(f"const float a{a_}_ = r_*h[{a_}];" for a_ in sorted({ab[0] for ab in tindex})))
+                for (a_, b_), ti in tindex.items():
+                    edge.append(f"    dY[{b_}] = fmaf(T[{ti}], a{a_}_, dY[{b_}]);")
                 edge.append(f"    S[{q}] = s_; }}")
             lines += [f"#define MACE_{gt}_NT {k}",
                       f"#define MACE_{gt}_BWD_PREP(G, T) do {{ \\"] + [t + " \\" for t in prep] + ["} while (0)"]
