@@ -4,6 +4,12 @@
 Two layers: a generic, backend-agnostic API (``DomainParallel`` / ``ShardedBatch`` / ``DistributedModel`` / ``MLIPSpec``;
 any model wrapper, NCCL or gloo) and the single-node peer-memory engine for the native MACE path
 (``slab_md.SlabDomainMD``: ghost features read from the owner GPU inside the convolution kernels).
+
+The generic layer evaluates a model either on a ghost layer as deep as its receptive field (nothing inside the model is
+touched) or, with ``MLIPSpec(refresh_per_layer=True)``, on a ghost layer one cutoff deep whose feature rows are
+refreshed from their owners before every message-passing layer (``dispatch.HaloDispatchMode`` intercepts the model's
+dim-0 gathers and scatters; ``storage_policy`` says what a gather / scatter has to do; ``dispatch.OpAdapter`` gives
+opaque fused operators the same treatment).  ``graph_padder`` keeps per-rank shapes fixed for CUDA-graph replay.
 """
 from nvalchemi_toolkit_b200.distributed.config import DomainConfig, HookScope, StrategyKind
 from nvalchemi_toolkit_b200.distributed.partitioner import IndexPartitioner, SpatialPartitioner, factor_grid
@@ -16,7 +22,15 @@ from nvalchemi_toolkit_b200.distributed.halo import HaloExchange, all_gather_row
 from nvalchemi_toolkit_b200.distributed.sharded_batch import ShardedBatch
 from nvalchemi_toolkit_b200.distributed.distributed_model import DistributedModel, DistributedPipelineModel, consolidate_outputs
 from nvalchemi_toolkit_b200.distributed.domain_parallel import DomainParallel, DynamicsCoordinator
-from nvalchemi_toolkit_b200.distributed.ops import ShardTensor, halo_forward, halo_scatter_correct
+from nvalchemi_toolkit_b200.distributed.ops import (ShardTensor, distributed_all_reduce, gather_replicate, halo_forward,
+                                                    halo_scatter_correct, per_system_reduce)
+from nvalchemi_toolkit_b200.distributed.storage_policy import (GraphParallelPolicy, HaloStoragePolicy, PlainShard,
+                                                               RefreshOnlyHaloPolicy, StoragePolicy, policy_from_dict,
+                                                               policy_to_dict)
+from nvalchemi_toolkit_b200.distributed.dispatch import (AdapterRegistry, FunctionAdapter, HaloDispatchMode, MethodAdapter,
+                                                         ModuleForwardAdapter, OpAdapter, current_dispatch)
+from nvalchemi_toolkit_b200.distributed.graph_padder import (COOPadder, DenseBatchPadder, DensePadder, GraphPadder,
+                                                             cap_agreement_group, resolve_cap)
 from nvalchemi_toolkit_b200.distributed import helpers
 from nvalchemi_toolkit_b200.distributed.pipeline2d import DomainPipeline
 
@@ -25,4 +39,8 @@ __all__ = ["DomainConfig", "HookScope", "StrategyKind", "SpatialPartitioner", "I
            "consolidate_outputs", "DomainParallel", "DomainPipeline", "DynamicsCoordinator", "ShardTensor", "halo_forward",
            "halo_scatter_correct", "helpers", "all_gather_rows", "all_to_all_rows", "SPEC_LJ_HALO", "SPEC_PAIR_HALO",
            "SPEC_DFTD3_HALO", "SPEC_EWALD_REAL_HALO", "SPEC_MACE_HALO", "SPEC_MACE_CUEQ_HALO", "SPEC_AIMNET2_HALO",
-           "SPEC_DEMO", "SPEC_MACE_GRAPH_PARTITION", "SPEC_AIMNET2_GRAPH_PARTITION"]
+           "SPEC_DEMO", "SPEC_MACE_GRAPH_PARTITION", "SPEC_AIMNET2_GRAPH_PARTITION", "distributed_all_reduce",
+           "gather_replicate", "per_system_reduce", "StoragePolicy", "PlainShard", "HaloStoragePolicy",
+           "RefreshOnlyHaloPolicy", "GraphParallelPolicy", "policy_to_dict", "policy_from_dict", "HaloDispatchMode",
+           "current_dispatch", "OpAdapter", "FunctionAdapter", "MethodAdapter", "ModuleForwardAdapter", "AdapterRegistry",
+           "GraphPadder", "COOPadder", "DensePadder", "DenseBatchPadder", "resolve_cap", "cap_agreement_group"]

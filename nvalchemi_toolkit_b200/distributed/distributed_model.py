@@ -73,6 +73,7 @@ class DistributedModel(nn.Module):
         if nc is not None and self.spec.requires_full_list and nc.half_list:
             raise ValueError("domain decomposition needs a full neighbour list (each owned row must be complete)")
         self._halo_builds = -1
+        self.last_dispatch_stats: dict = {}
 
     def forward(self, sharded: ShardedBatch, **kwargs: Any) -> dict:
         spec = self.spec
@@ -86,10 +87,27 @@ class DistributedModel(nn.Module):
                 self.neighbor_hook._bufs = None
                 self._halo_builds = halo.num_builds
             self.neighbor_hook(SimpleNamespace(batch=padded), None)
-            if spec.consolidation == Consolidation.DIRECT_MASKED:
-                padded.num_neighbors[sharded.n_owned:] = 0
-        out = self.model(padded, **kwargs)
+            if spec.consolidation == Consolidation.DIRECT_MASKED or (spec.refresh_per_layer and not self._policy_folds()):
+                padded.num_neighbors[sharded.n_owned:] = 0  # ghost atoms send, they do not receive
+        if spec.refresh_per_layer and halo.n_ghost > 0:
+            from nvalchemi_toolkit_b200.distributed.dispatch import HaloDispatchMode
+
+            with HaloDispatchMode(halo, sharded.n_owned, self._policy(), group=sharded.group,
+                                  global_ids=sharded.global_ids) as mode:
+                out = self.model(padded, **kwargs)
+            self.last_dispatch_stats = dict(mode.stats)
+        else:
+            out = self.model(padded, **kwargs)
         return consolidate_outputs(dict(out), sharded, spec, halo)
+
+    def _policy(self) -> Any:
+        from nvalchemi_toolkit_b200.distributed.storage_policy import RefreshOnlyHaloPolicy, policy_from_dict
+
+        d = self.spec.storage_policy
+        return policy_from_dict(d) if d is not None else RefreshOnlyHaloPolicy()
+
+    def _policy_folds(self) -> bool:
+        return getattr(self._policy(), "scatter_mode", "local") != "local"
 
 
 class DistributedPipelineModel(nn.Module):

@@ -47,6 +47,67 @@ class _HaloScatterCorrect(torch.autograd.Function):
         return torch.cat([grad, ctx.halo.forward(grad.contiguous())]), None
 
 
+class _GatherReplicate(torch.autograd.Function):
+    """All ranks' rows concatenated in rank order; the adjoint sums every rank's gradient of this rank's rows."""
+
+    @staticmethod
+    def forward(ctx: Any, owned: torch.Tensor, group: Any) -> torch.Tensor:
+        from nvalchemi_toolkit_b200.distributed.halo import _world, all_gather_rows
+
+        rows, counts = all_gather_rows(owned.contiguous(), group)
+        rank, _ = _world(group)
+        ctx.group, ctx.start, ctx.n = group, int(sum(counts[:rank])), owned.shape[0]
+        return rows
+
+    @staticmethod
+    def backward(ctx: Any, grad: torch.Tensor) -> tuple[torch.Tensor, None]:
+        import torch.distributed as dist
+
+        g = grad.contiguous().clone()
+        if dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
+            dist.all_reduce(g, group=ctx.group)
+        return g[ctx.start: ctx.start + ctx.n], None
+
+
+def gather_replicate(owned: torch.Tensor, group: Any = None) -> torch.Tensor:
+    """Differentiable all-gather of row blocks (rank order)."""
+    return _GatherReplicate.apply(owned, group)
+
+
+def per_system_reduce(values: torch.Tensor, index: torch.Tensor, n_systems: int, group: Any = None) -> torch.Tensor:
+    """Sum of OWNED per-atom values per system, all-reduced over the ranks (reference
+    ``nvalchemi/distributed/_core/per_system.py:68-213``); differentiable: every rank's gradient of the replicated
+    result is summed before it flows back to the local rows."""
+    local = values.new_zeros((n_systems,) + tuple(values.shape[1:])).index_add(0, index.long(), values)
+    return _AllReduceSum.apply(local, group)
+
+
+class _AllReduceSum(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, group: Any) -> torch.Tensor:
+        import torch.distributed as dist
+
+        ctx.group = group
+        y = x.contiguous().clone()
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx: Any, grad: torch.Tensor) -> tuple[torch.Tensor, None]:
+        import torch.distributed as dist
+
+        g = grad.contiguous().clone()
+        if dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
+            dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+def distributed_all_reduce(x: torch.Tensor, group: Any = None) -> torch.Tensor:
+    """Differentiable sum over the ranks of the group."""
+    return _AllReduceSum.apply(x, group)
+
+
 def halo_forward(owned: torch.Tensor, halo: HaloExchange) -> torch.Tensor:
     return _HaloForward.apply(owned, halo)
 

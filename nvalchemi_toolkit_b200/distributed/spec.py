@@ -14,6 +14,10 @@ an explicit ghost-atom evaluation, so the spec reduces to three facts:
   0 ghost), differentiates that sum with respect to all local positions, and the ghost rows' gradients are added to
   their owners (reverse halo);
 * which outputs are per-node and which are extensive per-system sums.
+
+``refresh_per_layer=True`` selects the other design (the reference's default): a ghost layer one cutoff deep whose
+feature rows are refreshed from the owners before each message-passing layer, by intercepting the model's gathers and
+scatters (``distributed/dispatch.py``); deeper models then exchange features instead of recomputing a wider halo.
 """
 from __future__ import annotations
 
@@ -42,8 +46,15 @@ class MLIPSpec:
     needs_total_charge: bool = False
     notes: str = ""
     extra: dict = field(default_factory=dict)
+    #: ghost layer one cutoff deep; ghost rows of node features are refreshed from their owners before every gather
+    #: (``distributed/dispatch.py``) instead of being recomputed from a ``message_passes``-deep ghost layer
+    refresh_per_layer: bool = False
+    #: serialised storage policy of node features under ``refresh_per_layer`` (``None``: refresh only)
+    storage_policy: dict | None = None
 
     def ghost_width(self, cutoff: float, skin: float = 0.0) -> float:
+        if self.refresh_per_layer:
+            return cutoff + skin
         return max(1, self.message_passes) * (cutoff + skin)
 
     def with_(self, **changes: object) -> "MLIPSpec":
