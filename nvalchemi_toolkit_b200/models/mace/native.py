@@ -12,6 +12,7 @@ forward plus ``torch.autograd.grad`` for forces.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Any
 
@@ -182,6 +183,28 @@ def _group_weights(ip: Any, w_last: torch.Tensor, c: int) -> list[torch.Tensor]:
     return [wt[g].reshape(len(g) * c, -1).contiguous() for g in o3.path_groups(ip.l_in)]
 
 
+#: first interaction in factorised form (``csrc/mace_l0.cu``): per-receiver moments of (harmonic x hidden radial
+#: activation) per sender species, then one K = 64 GEMM; used while the number of species keeps the moments small
+L0_MOMENTS = os.environ.get("NVA_L0_MOMENTS", "1") != "0"
+L0_MOMENTS_MAX_SPECIES = 4
+
+
+def _l0_weights(ip: Any, w_last: torch.Tensor, table: torch.Tensor, c: int, avg: float) -> list[torch.Tensor]:
+    """Per ``l`` the ``[species, 64, C]`` matrices that take the moments ``A[i, s, lm, :]`` straight to the message
+    ``msg[i, lm, :]``: (last radial layer of path ``l``) x diag(species feature) x (channel mix of ``l``)."""
+    from nvalchemi_toolkit_b200.models.mace import o3
+
+    terms = o3.conv_terms(ip.paths, ip.l_in)
+    w4 = w_last.reshape(w_last.shape[0], len(ip.paths), c)
+    out = []
+    for p, (l1, l2, l3) in enumerate(ip.paths):
+        assert l1 == 0 and l2 == l3 == p and ip.paths_per_l[l3] == 1
+        assert all(a_ == 0 and b_ == l3 * l3 + c_ and abs(coef - terms[p][0][3]) < 1e-12 for (a_, b_, c_, coef) in terms[p])
+        lin = ip.linear[l3] / (math.sqrt(c) * avg)
+        out.append(torch.stack([(w4[:, p, :] * (terms[p][0][3] * table[s_])) @ lin for s_ in range(table.shape[0])]))
+    return out
+
+
 def _per_l_linear(x: torch.Tensor, w: torch.Tensor, ls: list[int], transpose: bool = False,
                   out: torch.Tensor | None = None) -> torch.Tensor:
     """Per-irrep channel mix on ``[N, n_lm, C]``: one GEMM per ``lm`` row, reading and writing the strided slices in
@@ -330,7 +353,24 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         else:
             u = _per_l_linear(h, ip.linear_up, ip.l_in).contiguous()
         fused = _fused_ok(model, ip)
-        if fused:
+        l0w = None
+        if row_map is not None and L0_MOMENTS and nz <= L0_MOMENTS_MAX_SPECIES and lmax == 3 and ws[-1].shape[0] == 64:
+            l0w = _l0_weights(ip, ws[-1], u[:, 0], C, cfg.avg_num_neighbors)
+            A = pos.new_empty(n, nz, 16, 64)
+            for (i0, i1, e0, e1) in _chunks(csr, n, 4 * 64):
+                ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, False)
+                h3 = _hidden(ws, ef, False)
+                ops.mace_l0_moments(h3, pos, cell, b32, csr.eptr, csr.esend, csr.eS, row_map, i0, i1 - i0, e0, rmax, A)
+                del ef, h3
+            msg = pos.new_empty(n, 16, C)
+            for l in range(lmax + 1):
+                for lm in range(l * l, (l + 1) * (l + 1)):
+                    gemm.matmul(A[:, 0, lm], l0w[l][0], out=msg[:, lm])
+                    for s_ in range(1, nz):
+                        msg[:, lm] += gemm.matmul(A[:, s_, lm], l0w[l][s_])
+            del A
+            wgs, mid = None, None
+        elif fused:
             err = _err_words.setdefault(dev, torch.zeros(1, dtype=torch.int32, device=dev))
             wgs = _group_weights(ip, ws[-1], C)
             mid = pos.new_zeros(n, ip.n_mid, C)
@@ -351,7 +391,8 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
                 ops.mace_conv_fwd(u, pos, cell, b32, csr.eptr, csr.esend, csr.eS, R, i0, i1 - i0, e0, rmax, mid, hr, hw,
                                   u_ptrs)
                 del ef, R
-        msg = _linear_mid(ip, mid, cfg.avg_num_neighbors, lmax)
+        if l0w is None:
+            msg = _linear_mid(ip, mid, cfg.avg_num_neighbors, lmax)
         del mid
         w0, w1 = _sym_weights(ip, cfg.correlation)
         B = ops.mace_symcon_fwd(msg, sp32, w0, w1, max(ip.l_out), cfg.correlation)
@@ -367,7 +408,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
             node_e += s @ (ip.readout_w1 / math.sqrt(C))
             ro = (None, None)
         saved.append((ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs if not (pull and row_map is None) else pull_ptrs[1], wgs,
-                      row_map))
+                      row_map, l0w))
         h = h_new
         del B, sc
     scale, shift = model.scale.to(pos.dtype), model.shift.to(pos.dtype)
@@ -385,7 +426,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
     strain_grad = torch.zeros(num_graphs, 9, dtype=torch.float64, device=dev) if compute_stress else None
     dh: torch.Tensor | None = None
     for li in range(len(saved) - 1, -1, -1):
-        ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs, wgs, row_map = saved[li]
+        ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs, wgs, row_map, l0w = saved[li]
         k_du_ptrs = None if pull else du_ptrs  # pointer table handed to the kernels (none: local rows only)
         n_out = sum(2 * l + 1 for l in ip.l_out)
         dh_tot = pos.new_zeros(n, n_out, C) if dh is None else dh
@@ -397,12 +438,24 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         dB = _per_l_linear(dh_tot, ip.product_linear, ip.l_out, transpose=True).contiguous()
         dmsg = ops.mace_symcon_bwd(msg, sp32, w0, w1, max(ip.l_out), cfg.correlation, dB)
         del dB
-        dmid = _linear_mid_bwd(ip, dmsg, cfg.avg_num_neighbors, lmax)
-        del dmsg
+        dmid = _linear_mid_bwd(ip, dmsg, cfg.avg_num_neighbors, lmax) if l0w is None else None
         P = len(ip.paths)
         if dd is None:
             du = torch.zeros_like(u) if li > 0 else None
-        if wgs is not None:
+        if l0w is not None:
+            Q = pos.new_empty(n, nz, 16, 64)
+            for l in range(lmax + 1):
+                for lm in range(l * l, (l + 1) * (l + 1)):
+                    for s_ in range(nz):
+                        gemm.matmul(dmsg[:, lm], l0w[l][s_].t(), out=Q[:, s_, lm])
+            for (i0, i1, e0, e1) in _chunks(csr, n, 8 * 64):
+                ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, True)
+                h3 = _hidden(ws, ef, True)
+                ops.mace_l0_force(h3, Q, pos, cell, b32, csr.eptr, csr.esend, csr.eS, row_map, i0, i1 - i0, e0, rmax,
+                                  grad_pos, strain_grad)
+                del ef, h3
+            del Q
+        elif wgs is not None:
             err = _err_words[dev]
             for (i0, i1, e0, e1) in _chunks(csr, n, 8 * 64):
                 ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, True)
@@ -419,7 +472,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
                 ops.mace_conv_bwd(u, dmid, pos, cell, b32, csr.eptr, csr.esend, csr.eS, RD, i0, i1 - i0, e0, rmax, du,
                                   grad_pos, strain_grad, hr, hw, u_ptrs, k_du_ptrs, gp_ptrs)
                 del ef, RD
-        del dmid
+        del dmid, dmsg
         if pull:
             # return what was accumulated on ghost rows to the owners, once per row
             dd.barrier()  # owners finished their own accumulation
