@@ -72,18 +72,29 @@ __global__ void __launch_bounds__(32 * L0_WARPS) l0_moments_kernel(
         const unsigned okmask = __ballot_sync(0xffffffffu, ok);
         __syncwarp();
         const int cnt = min(32, e1 - eb);
-        for (int n = 0; n < cnt; ++n) {
-          if (!((okmask >> n) & 1u)) continue;  // uniform
-          const float* hp = h3 + ((int64_t)(eb + n) - e_chunk0) * NK;
-          const float ha = __ldg(hp + lane), hb = __ldg(hp + 32 + lane);
-          const float4* yp = reinterpret_cast<const float4*>(Ys[warp][n]);
+        if (okmask == 0u) continue;
+        // masked edges have Y = 0, so every edge of the batch is processed: four rows of h3 are in flight at a time
+        const float* hrow = h3 + ((int64_t)eb - e_chunk0) * NK + lane;
+        for (int n4 = 0; n4 < cnt; n4 += 4) {
+          float ha[4], hb[4];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float4 y = yp[q];
-            acc0[4 * q] = fmaf(y.x, ha, acc0[4 * q]); acc1[4 * q] = fmaf(y.x, hb, acc1[4 * q]);
-            acc0[4 * q + 1] = fmaf(y.y, ha, acc0[4 * q + 1]); acc1[4 * q + 1] = fmaf(y.y, hb, acc1[4 * q + 1]);
-            acc0[4 * q + 2] = fmaf(y.z, ha, acc0[4 * q + 2]); acc1[4 * q + 2] = fmaf(y.z, hb, acc1[4 * q + 2]);
-            acc0[4 * q + 3] = fmaf(y.w, ha, acc0[4 * q + 3]); acc1[4 * q + 3] = fmaf(y.w, hb, acc1[4 * q + 3]);
+          for (int u = 0; u < 4; ++u) {
+            const int n = min(n4 + u, cnt - 1);
+            ha[u] = __ldg(hrow + n * NK);
+            hb[u] = __ldg(hrow + n * NK + 32);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (n4 + u >= cnt) break;
+            const float4* yp = reinterpret_cast<const float4*>(Ys[warp][n4 + u]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 y = yp[q];
+              acc0[4 * q] = fmaf(y.x, ha[u], acc0[4 * q]); acc1[4 * q] = fmaf(y.x, hb[u], acc1[4 * q]);
+              acc0[4 * q + 1] = fmaf(y.y, ha[u], acc0[4 * q + 1]); acc1[4 * q + 1] = fmaf(y.y, hb[u], acc1[4 * q + 1]);
+              acc0[4 * q + 2] = fmaf(y.z, ha[u], acc0[4 * q + 2]); acc1[4 * q + 2] = fmaf(y.z, hb[u], acc1[4 * q + 2]);
+              acc0[4 * q + 3] = fmaf(y.w, ha[u], acc0[4 * q + 3]); acc1[4 * q + 3] = fmaf(y.w, hb[u], acc1[4 * q + 3]);
+            }
           }
         }
       }
@@ -134,20 +145,25 @@ __global__ void __launch_bounds__(32 * L0_WARPS) l0_force_kernel(
         const unsigned okmask = __ballot_sync(0xffffffffu, ok);
         // ---- lane = (lm, half): contraction of Q with the two h3 rows of every live edge
         const int cnt = min(32, e1 - eb);
-        for (int n = 0; n < cnt; ++n) {
-          if (!((okmask >> n) & 1u)) continue;  // uniform
-          const float4* hv = reinterpret_cast<const float4*>(h3 + (2 * ((int64_t)(eb + n) - e_chunk0)) * NK + 32 * half);
-          const float4* hd = hv + NK / 4;
-          float p = 0.f, pd = 0.f;
+        if (okmask != 0u) {
+          // every edge of the batch is contracted (results of masked edges are not used); the 16 vector loads of an
+          // edge are issued before its multiply-adds, and two independent accumulators per sum shorten the chains
+          for (int n = 0; n < cnt; ++n) {
+            const float4* hv = reinterpret_cast<const float4*>(h3 + (2 * ((int64_t)(eb + n) - e_chunk0)) * NK + 32 * half);
+            float4 a[8], d[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const float4 a = __ldg(hv + k), d = __ldg(hd + k);
-            p = fmaf(q[k].x, a.x, p); p = fmaf(q[k].y, a.y, p); p = fmaf(q[k].z, a.z, p); p = fmaf(q[k].w, a.w, p);
-            pd = fmaf(q[k].x, d.x, pd); pd = fmaf(q[k].y, d.y, pd); pd = fmaf(q[k].z, d.z, pd); pd = fmaf(q[k].w, d.w, pd);
+            for (int k = 0; k < 8; ++k) { a[k] = __ldg(hv + k); d[k] = __ldg(hv + NK / 4 + k); }
+            float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              p0 = fmaf(q[k].x, a[k].x, p0); p1 = fmaf(q[k].y, a[k].y, p1); p0 = fmaf(q[k].z, a[k].z, p0); p1 = fmaf(q[k].w, a[k].w, p1);
+              d0 = fmaf(q[k].x, d[k].x, d0); d1 = fmaf(q[k].y, d[k].y, d1); d0 = fmaf(q[k].z, d[k].z, d0); d1 = fmaf(q[k].w, d[k].w, d1);
+            }
+            float p = p0 + p1, pd = d0 + d1;
+            p += __shfl_xor_sync(0xffffffffu, p, 16);
+            pd += __shfl_xor_sync(0xffffffffu, pd, 16);
+            if (half == 0) { P[warp][n][lm] = p; P[warp][n][16 + lm] = pd; }
           }
-          p += __shfl_xor_sync(0xffffffffu, p, 16);
-          pd += __shfl_xor_sync(0xffffffffu, pd, 16);
-          if (half == 0) { P[warp][n][lm] = p; P[warp][n][16 + lm] = pd; }
         }
         __syncwarp();
         // ---- lane = edge: force along the edge
