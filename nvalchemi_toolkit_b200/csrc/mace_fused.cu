@@ -6,8 +6,8 @@
 //   mid[i, :, c] = sum_{e -> i} TP(u[sender(e), :, c], Y(e), R[e, :, c])   (CUDA cores, thread = channel)
 //
 // One persistent CTA per SM.  The A operand of the MMA is W4^T restricted to a group of at most five paths
-// ([paths*128, 64] fp32 = 160 KB, loaded once by TMA and kept resident); the B operand is a tile of 16 edges of the
-// hidden activations h3 (backward: 16 edges x (value, d/dr) = 32 rows), streamed by TMA through a two-slot ring.
+// ([paths*128, 64] fp32 = 160 KB, loaded once by TMA and kept resident); the B operand is a tile of FT edges of the
+// hidden activations h3 (backward: FT edges x (value, d/dr) = 2 FT rows), streamed by TMA through a two-slot ring.
 // D = [128 channels x (paths * rows)] lives in TMEM, double-buffered, so the tensor-core work of tile t+1 overlaps the
 // tensor-product arithmetic of tile t.  Thread c of the four compute warps owns TMEM lane c = channel c and reads its
 // radial weights with tcgen05.ld (one or two columns per edge and path).  Warp 4 allocates TMEM, issues TMA and MMA.
