@@ -183,11 +183,22 @@ __global__ void __launch_bounds__(128) radial_mlp_kernel(const __grid_constant__
     if (!(ok = layer(sW2, 2, v))) break;
     store_act(v);
     if (!(ok = layer(sW3, 2, v))) break;
-    if (row < rows) {
-      float4* o = reinterpret_cast<float4*>(out + row * 64);
-#pragma unroll
-      for (int j = 0; j < 16; ++j) o[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    // Output through the (now free) activation tile: a thread holds one 256-byte row, so direct stores would touch 32
+    // different rows per instruction; staged, a warp writes 512 contiguous bytes per instruction.
+    if (TANGENT) __syncthreads();  // partners finished reading the derivative factors left in the tile
+    store_act(v);
+    __syncthreads();
+#pragma unroll 4
+    for (int it = 0; it < 16; ++it) {
+      const int idx = it * 128 + t;
+      const int g = idx >> 4, ch = idx & 15;                       // row of the tile in global order, 16-byte chunk
+      const int r = TANGENT ? (g >> 1) + 64 * (g & 1) : g;         // the thread (= tile row) that produced it
+      const int64_t grow = tile * 128 + g;
+      if (grow < rows)
+        *reinterpret_cast<float4*>(out + grow * 64 + ch * 4) =
+            *reinterpret_cast<const float4*>(act + (ch >> 3) * ACT_KB + sw128_off(r, ch & 7));
     }
+    __syncthreads();  // the next tile's basis functions overwrite the tile
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
