@@ -42,3 +42,15 @@ def init_from_env(backend: str | None = None) -> tuple[int, int]:
             torch.cuda.set_device(resolve_local_rank())
         dist.init_process_group(backend)
     return resolve_global_rank(), resolve_world_size()
+
+
+def mesh_group(mesh: Any, dim: str | int | None = None) -> Any:
+    """Process group of one dimension of a ``DeviceMesh`` (``None``: the default group; a process group is returned as
+    is).  Reference: ``nvalchemi/distributed/_core/collectives.py`` (``mesh_group``)."""
+    if mesh is None:
+        return None
+    if isinstance(mesh, dist.ProcessGroup):
+        return mesh
+    if dim is None:
+        return mesh.get_group()
+    return mesh.get_group(dim)

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import itertools
 import math
+import os
 from typing import Any
 
 import torch
@@ -26,11 +27,47 @@ def _world(group: Any) -> tuple[int, int]:
     return dist.get_rank(group), dist.get_world_size(group)
 
 
+#: how variable-size row exchanges travel: ``"all_to_all"`` (one ``all_to_all_single`` over the whole group) or ``"p2p"``
+#: (``batch_isend_irecv`` with the ranks that actually exchange rows: at most 26 neighbours under a spatial
+#: decomposition, however large the group is).  Reference: ``nvalchemi/distributed/_core/collectives.py`` (funcol
+#: all-to-all, neighbour-only P2P, gloo isend/irecv fallback).
+TRANSPORT = os.environ.get("NVA_HALO_TRANSPORT", "all_to_all")
+
+
+def neighbor_exchange_rows(rows: torch.Tensor, in_splits: list[int], out_splits: list[int], group: Any = None) -> torch.Tensor:
+    """The same result as :func:`all_to_all_rows`, moved with point-to-point messages between the ranks whose split is
+    non-empty.  Every rank of the group must call it (peers post the matching receives)."""
+    rank, world = _world(group)
+    if world == 1:
+        return rows
+    rows = rows.contiguous()
+    out = rows.new_empty((sum(out_splits),) + tuple(rows.shape[1:]))
+    ops, so, ro = [], 0, 0
+    for peer in range(world):
+        ns, nr = in_splits[peer], out_splits[peer]
+        if peer == rank:
+            if ns:
+                out[ro: ro + nr] = rows[so: so + ns]
+        else:
+            g = dist.get_global_rank(group, peer) if group is not None else peer
+            if ns:
+                ops.append(dist.P2POp(dist.isend, rows[so: so + ns], g, group))
+            if nr:
+                ops.append(dist.P2POp(dist.irecv, out[ro: ro + nr], g, group))
+        so, ro = so + ns, ro + nr
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    return out
+
+
 def all_to_all_rows(rows: torch.Tensor, in_splits: list[int], out_splits: list[int], group: Any = None) -> torch.Tensor:
     """Variable-size all-to-all along dim 0 (identity for a single rank)."""
     _, world = _world(group)
     if world == 1:
         return rows
+    if TRANSPORT == "p2p":
+        return neighbor_exchange_rows(rows, in_splits, out_splits, group)
     out = rows.new_empty((sum(out_splits),) + tuple(rows.shape[1:]))
     dist.all_to_all_single(out, rows.contiguous(), out_splits, in_splits, group=group)
     return out

@@ -206,3 +206,53 @@ def test_unmodified_model_with_one_cutoff_halo_matches_single_process(which, por
         assert abs(energy[0] - float(ref["energy"].detach().reshape(-1)[0])) < 1e-8
         assert 0 < n_ghost < n_ghost_deep           # one cutoff of ghosts instead of one per message pass
         assert stats["refreshes"] >= 1              # ghost feature rows were exchanged between the layers
+
+
+def _p2p_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nvalchemi_toolkit_b200.distributed import halo as halo_mod
+        from nvalchemi_toolkit_b200.distributed._runtime import mesh_group
+
+        torch.set_num_threads(1)
+        # rank r sends r + p + 1 rows to peer p, except nothing to its right neighbour (an empty split)
+        send = [0 if p == (rank + 1) % world else rank + p + 1 for p in range(world)]
+        recv = halo_mod.exchange_counts(send, torch.device("cpu"))
+        rows = torch.arange(sum(send), dtype=torch.float64)[:, None] + 100.0 * rank
+        a = halo_mod.all_to_all_rows(rows, send, recv)
+        b = halo_mod.neighbor_exchange_rows(rows, send, recv)
+        same = torch.equal(a, b)
+        halo_mod.TRANSPORT = "p2p"   # the whole distributed evaluation over point-to-point messages
+        batch = Batch.from_data_list([fcc_supercell(4, a=3.61, z=29, noise=0.08, seed=3, dtype=torch.float64)])
+        cfg = DomainConfig(cutoff=3.0, skin=0.0)
+        model = _mpnn_wrapper()
+        spec = model.distribution_spec()
+        sh = ShardedBatch.from_batch(batch, cfg, spec)
+        out = DistributedModel(model, cfg, spec=spec)(sh)
+        forces = ShardTensor(out["forces"], sh).full_tensor()
+        q.put((rank, same, forces.tolist(), mesh_group(None) is None, mesh_group(dist.group.WORLD) is dist.group.WORLD))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_neighbor_only_p2p_transport_matches_all_to_all():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_p2p_worker, args=(r, 3, 29677, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(3):
+        item = q.get(timeout=240)
+        res[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=30)
+    batch = Batch.from_data_list([fcc_supercell(4, a=3.61, z=29, noise=0.08, seed=3, dtype=torch.float64)])
+    ref = _reference(_mpnn_wrapper(), batch)
+    for r in range(3):
+        same, forces, g0, g1 = res[r]
+        assert same and g0 and g1
+        assert torch.allclose(torch.tensor(forces, dtype=torch.float64), ref["forces"], atol=1e-8)
