@@ -143,3 +143,83 @@ def trace_and_validate(model_factory: Callable, batch_factory: Callable, world_s
                 suggestion = label
                 break
     return ValidationReport(ok, d, world_size, base.name, suggestion, attempts)
+
+
+# ---- layer-by-layer comparison (reference ``nvalchemi/distributed/validate/layer_diagnostics.py``) ---------------
+def _capture_node_outputs(model: Any, n_rows: int) -> tuple[dict[str, torch.Tensor], list]:
+    """Forward hooks that keep, per named sub-module, its first tensor output with ``n_rows`` rows."""
+    store: dict[str, torch.Tensor] = {}
+    handles = []
+
+    def make(name: str) -> Callable:
+        def hook(_m: Any, _inp: Any, out: Any) -> None:
+            t = out if isinstance(out, torch.Tensor) else next((o for o in out if isinstance(o, torch.Tensor)), None) \
+                if isinstance(out, (tuple, list)) else None
+            if isinstance(t, torch.Tensor) and t.dim() >= 1 and t.shape[0] == n_rows and name not in store:
+                store[name] = t.detach().clone()
+        return hook
+
+    for name, mod in model.named_modules():
+        if name:
+            handles.append(mod.register_forward_hook(make(name)))
+    return store, handles
+
+
+def _layer_worker(rank: int, world: int, port: int, q: Any, model_factory: Callable, batch_factory: Callable,
+                  cfg_kwargs: dict, spec: Any) -> None:
+    from nvalchemi_toolkit_b200.distributed import DistributedModel, DomainConfig, ShardedBatch, ShardTensor
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        model, batch = model_factory(), batch_factory()
+        cfg = DomainConfig(**cfg_kwargs)
+        use = spec if spec is not None else model.distribution_spec()
+        sh = ShardedBatch.from_batch(batch, cfg, use)
+        store, handles = _capture_node_outputs(model, sh.n_owned + sh.n_ghost)
+        DistributedModel(model, cfg, use)(sh)
+        for h in handles:
+            h.remove()
+        names = sorted(store)  # the same modules fire on every rank: the gathers below stay aligned
+        full = {k: ShardTensor(store[k][: sh.n_owned].contiguous(), sh).full_tensor().tolist() for k in names}
+        q.put((full if rank == 0 else None, 0))
+    finally:
+        dist.destroy_process_group()
+
+
+def layer_diff(model_factory: Callable, batch_factory: Callable, world_size: int = 2, *, cutoff: float, skin: float = 0.0,
+               spec: Any = None, atol: float = 1e-6, port: int = 29761) -> list[dict]:
+    """Per sub-module, the largest difference between its per-atom output in a single-process evaluation and in the
+    decomposed one (owned rows, gathered in global order), in execution order of the single-process run.  The first
+    entry with ``ok = False`` is where the decomposition starts to deviate (a layer that needs refreshed ghost rows, a
+    reduction that counts ghosts, ...).  Factories must be importable top-level callables."""
+    import torch.multiprocessing as mp
+
+    model, batch = model_factory(), batch_factory()
+    for h in model.make_neighbor_hooks():
+        h(SimpleNamespace(batch=batch), None)
+    store, handles = _capture_node_outputs(model, batch.num_nodes)
+    model(batch)
+    for h in handles:
+        h.remove()
+    order = list(store)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_layer_worker, args=(r, world_size, port, q, model_factory, batch_factory,
+                                                     {"cutoff": cutoff, "skin": skin}, spec)) for r in range(world_size)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in range(world_size)]
+    for p in procs:
+        p.join(timeout=30)
+    res = next(r for r, _ in got if r is not None)
+    report = []
+    for name in order:
+        if name not in res:
+            report.append({"module": name, "ok": False, "max_abs_diff": float("inf"), "note": "not captured under decomposition"})
+            continue
+        a, b = store[name].double(), torch.tensor(res[name], dtype=torch.float64)
+        d = float((a - b).abs().max()) if a.shape == b.shape else float("inf")
+        report.append({"module": name, "ok": d <= atol, "max_abs_diff": d})
+    return report

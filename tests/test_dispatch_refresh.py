@@ -256,3 +256,26 @@ def test_neighbor_only_p2p_transport_matches_all_to_all():
         same, forces, g0, g1 = res[r]
         assert same and g0 and g1
         assert torch.allclose(torch.tensor(forces, dtype=torch.float64), ref["forces"], atol=1e-8)
+
+
+def _batch_factory():
+    return Batch.from_data_list([fcc_supercell(4, a=3.61, z=29, noise=0.08, seed=3, dtype=torch.float64)])
+
+
+def _shallow_spec_mpnn():
+    """The three-layer network declared with a ONE-hop halo and no per-layer refresh: wrong from the second layer on."""
+    m = _mpnn_wrapper()
+    spec = m.distribution_spec().with_(refresh_per_layer=False, message_passes=1)
+    m.distribution_spec = lambda strategy=None: spec
+    return m
+
+
+def test_layer_diff_locates_the_first_deviating_layer():
+    from nvalchemi_toolkit_b200.distributed.validate import layer_diff
+
+    good = layer_diff(_mpnn_wrapper, _batch_factory, 2, cutoff=3.0, port=29681)
+    assert good and all(r["ok"] for r in good)
+    bad = layer_diff(_shallow_spec_mpnn, _batch_factory, 2, cutoff=3.0, port=29683)
+    by_name = {r["module"]: r["ok"] for r in bad}
+    assert by_name["net.emb"] and by_name["net.mix.0"]        # inputs of the first aggregation are still exact
+    assert not by_name["net.mix.2"] and not by_name["net.out"]  # stale ghost rows have reached the owned atoms
