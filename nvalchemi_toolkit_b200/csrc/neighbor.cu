@@ -275,8 +275,44 @@ void neighbor_matrix_build(const Tensor& pos, const Tensor& cell, const Tensor& 
   });
 }
 
+// Neighbour matrix -> receiver-major CSR edge arrays in one pass: thread (i, slot) copies its sender and image shift to
+// position eptr[i] + slot (eptr = exclusive prefix sum of the clamped counts, computed by the caller).
+__global__ void csr_fill_kernel(const int* __restrict__ nm, const int* __restrict__ shifts, const int* __restrict__ eptr,
+                                int64_t n, int K, int* __restrict__ esend, int* __restrict__ erecv, int* __restrict__ eS) {
+  const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (idx >= n * K) return;
+  const int64_t i = idx / K;
+  const int slot = (int)(idx - i * K);
+  const int e0 = eptr[i], cnt = eptr[i + 1] - e0;
+  if (slot >= cnt) return;
+  const int64_t e = (int64_t)e0 + slot;
+  esend[e] = nm[idx];
+  erecv[e] = (int)i;
+  if (shifts != nullptr) {
+    eS[3 * e] = shifts[3 * idx]; eS[3 * e + 1] = shifts[3 * idx + 1]; eS[3 * e + 2] = shifts[3 * idx + 2];
+  } else {
+    eS[3 * e] = 0; eS[3 * e + 1] = 0; eS[3 * e + 2] = 0;
+  }
+}
+
+void csr_fill(const Tensor& nm, const c10::optional<Tensor>& shifts, const Tensor& eptr, Tensor esend, Tensor erecv, Tensor eS) {
+  c10::cuda::CUDAGuard guard(nm.device());
+  NVA_CHECK_CONTIG(nm); NVA_CHECK_CONTIG(eptr); NVA_CHECK_CONTIG(esend); NVA_CHECK_CONTIG(erecv); NVA_CHECK_CONTIG(eS);
+  TORCH_CHECK(nm.scalar_type() == at::kInt && eptr.scalar_type() == at::kInt, "csr_fill: int32 inputs");
+  if (shifts.has_value()) { NVA_CHECK_CONTIG(*shifts); TORCH_CHECK(shifts->scalar_type() == at::kInt, "csr_fill: int32 shifts"); }
+  const int64_t n = nm.size(0), K = nm.size(1);
+  if (n * K == 0) return;
+  const int threads = 256;
+  const int64_t blocks = (n * K + threads - 1) / threads;
+  csr_fill_kernel<<<(unsigned)blocks, threads, 0, at::cuda::getCurrentCUDAStream()>>>(
+      nm.data_ptr<int>(), shifts.has_value() ? shifts->data_ptr<int>() : nullptr, eptr.data_ptr<int>(), n, (int)K,
+      esend.data_ptr<int>(), erecv.data_ptr<int>(), eS.data_ptr<int>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 }  // namespace nva
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
+  m.def("csr_fill(Tensor nm, Tensor? shifts, Tensor eptr, Tensor(a!) esend, Tensor(b!) erecv, Tensor(c!) eS) -> ()", &nva::csr_fill);
   m.def("neighbor_matrix_build(Tensor positions, Tensor cell, Tensor pbc, Tensor batch_idx, Tensor batch_ptr, float cutoff, bool half_list, Tensor(a!) out_matrix, Tensor(b!) out_num, Tensor(c!) out_shifts, Tensor? rebuild_flags=None) -> ()", &nva::neighbor_matrix_build);
 }

@@ -43,6 +43,18 @@ class EdgeCSR:
 def build_csr(nm: torch.Tensor, num: torch.Tensor, shifts: torch.Tensor | None) -> EdgeCSR:
     n, k = nm.shape
     cnt = num.clamp_max(k).to(torch.int32)
+    if (nm.is_cuda and nm.dtype == torch.int32 and nm.is_contiguous() and _native.available()
+            and (shifts is None or (shifts.dtype == torch.int32 and shifts.is_contiguous()))):
+        # one pass over the matrix instead of boolean-mask gathers (each of which is a select + gather over N x K)
+        eptr = torch.zeros(n + 1, dtype=torch.int32, device=nm.device)
+        torch.cumsum(cnt, 0, out=eptr[1:])
+        stats = torch.stack([eptr[-1], num.max().to(torch.int32) if n else eptr[-1]]).tolist()  # one host read
+        e, mx = int(stats[0]), (int(stats[1]) if n else 0)
+        esend = torch.empty(e, dtype=torch.int32, device=nm.device)
+        erecv = torch.empty(e, dtype=torch.int32, device=nm.device)
+        eS = torch.empty(e, 3, dtype=torch.int32, device=nm.device)
+        ops.csr_fill(nm, shifts, eptr, esend, erecv, eS)
+        return EdgeCSR(eptr, esend, erecv, eS, None, e, mx)
     valid = torch.arange(k, device=nm.device, dtype=torch.int32)[None, :] < cnt[:, None]
     esend = nm[valid].to(torch.int32).contiguous()
     e = esend.numel()

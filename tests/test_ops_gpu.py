@@ -129,3 +129,22 @@ def test_halo_pull_and_push_add_rows_single_device():
     b0[7] += src[4] + src[7]
     b0[0] += src[6]
     assert torch.allclose(a, a0, atol=1e-6) and torch.allclose(b, b0, atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_csr_fill_kernel_matches_mask_gathers():
+    """Neighbour matrix -> CSR edge arrays: the one-pass kernel against the boolean-mask formulation."""
+    from nvalchemi_toolkit_b200.models.mace import native
+
+    torch.manual_seed(0)
+    n, k = 1000, 24
+    num = torch.randint(0, k + 5, (n,), dtype=torch.int32, device="cuda")   # some counts overflow the matrix width
+    nm = torch.randint(0, n, (n, k), dtype=torch.int32, device="cuda")
+    sh = torch.randint(-1, 2, (n, k, 3), dtype=torch.int32, device="cuda")
+    got = native.build_csr(nm, num, sh)
+    ref = native.build_csr(nm.long(), num, sh)                               # int64 matrix takes the torch path
+    assert got.num_edges == ref.num_edges and got.max_count == ref.max_count
+    assert torch.equal(got.eptr, ref.eptr) and torch.equal(got.esend, ref.esend)
+    assert torch.equal(got.erecv, ref.erecv) and torch.equal(got.eS, ref.eS)
+    none = native.build_csr(nm, num, None)
+    assert torch.equal(none.esend, ref.esend) and int(none.eS.abs().sum()) == 0
