@@ -503,7 +503,7 @@ static void launch_fused(const float* wg, int64_t wrows, const float* h3, int64_
   CUtensorMap mw = fused_map(wg, wrows, 128);
   CUtensorMap mh = fused_map(h3, hrows, NROW);
   size_t smem = (size_t)G::NP * 2 * 128 * 128 + 2 * (2 * NROW * 128) + 256 + GR * FT * 336 + 64 + 1024 + 256;
-  constexpr int NG = 4;  // 16 compute warps; the backward fits the 96-register budget of 576 threads without spills
+  constexpr int NG = BWD ? 4 : 5;  // compute warp-groups: both fit their register budgets (96 / 80) without spills
   auto kern = conv_fused_kernel<LAYER, GROUP, BWD, NEED_DU, NG, FT>;
   static bool configured = false;
   if (!configured) {
