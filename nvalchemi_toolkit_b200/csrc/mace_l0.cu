@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(32 * L0_WARPS) l0_moments_kernel(
     const float* __restrict__ h3, int64_t e_chunk0, const float* __restrict__ pos, const float* __restrict__ cell,
     const int* __restrict__ batch_idx, const int* __restrict__ eptr, const int* __restrict__ esend,
     const int* __restrict__ eS, const int* __restrict__ species, int nz, int i0, int ni, float rmax,
-    float* __restrict__ A) {
+    float* __restrict__ A, int hstride) {
   __shared__ __align__(16) float Ys[L0_WARPS][32][NLM];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gw = blockIdx.x * L0_WARPS + warp, nw = gridDim.x * L0_WARPS;
@@ -74,14 +74,14 @@ __global__ void __launch_bounds__(32 * L0_WARPS) l0_moments_kernel(
         const int cnt = min(32, e1 - eb);
         if (okmask == 0u) continue;
         // masked edges have Y = 0, so every edge of the batch is processed: four rows of h3 are in flight at a time
-        const float* hrow = h3 + ((int64_t)eb - e_chunk0) * NK + lane;
+        const float* hrow = h3 + ((int64_t)eb - e_chunk0) * hstride + lane;
         for (int n4 = 0; n4 < cnt; n4 += 4) {
           float ha[4], hb[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int n = min(n4 + u, cnt - 1);
-            ha[u] = __ldg(hrow + n * NK);
-            hb[u] = __ldg(hrow + n * NK + 32);
+            ha[u] = __ldg(hrow + (int64_t)n * hstride);
+            hb[u] = __ldg(hrow + (int64_t)n * hstride + 32);
           }
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
@@ -236,13 +236,14 @@ void mace_l0_moments(const Tensor& h3, const Tensor& pos, const Tensor& cell, co
                      const Tensor& esend, const Tensor& eS, const Tensor& species, int64_t i0, int64_t ni, int64_t e_chunk0,
                      double rmax, Tensor A) {
   c10::cuda::CUDAGuard guard(pos.device());
-  NVA_CHECK_CONTIG(h3); NVA_CHECK_CONTIG(A); NVA_CHECK_CONTIG(pos);
+  NVA_CHECK_CONTIG(A); NVA_CHECK_CONTIG(pos);
+  TORCH_CHECK(h3.dim() == 2 && h3.stride(1) == 1, "mace_l0_moments: h3 is [E, 64] (rows may be strided)");
   TORCH_CHECK(A.dim() == 4 && A.size(2) == NLM && A.size(3) == NK && h3.size(-1) == NK, "mace_l0_moments: bad shapes");
   if (ni == 0) return;
   l0_moments_kernel<<<l0_grid((int)ni), 32 * L0_WARPS, 0, at::cuda::getCurrentCUDAStream()>>>(
       h3.data_ptr<float>(), e_chunk0, pos.data_ptr<float>(), cell.data_ptr<float>(), batch_idx.data_ptr<int>(),
       eptr.data_ptr<int>(), esend.data_ptr<int>(), eS.data_ptr<int>(), species.data_ptr<int>(), (int)A.size(1), (int)i0,
-      (int)ni, (float)rmax, A.data_ptr<float>());
+      (int)ni, (float)rmax, A.data_ptr<float>(), (int)h3.stride(0));
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

@@ -199,6 +199,17 @@ def _group_weights(ip: Any, w_last: torch.Tensor, c: int) -> list[torch.Tensor]:
 #: activation) per sender species, then one K = 64 GEMM; used while the number of species keeps the moments small
 L0_MOMENTS = os.environ.get("NVA_L0_MOMENTS", "1") != "0"
 L0_MOMENTS_MAX_SPECIES = 4
+#: when forces are requested, the forward pass evaluates the radial network with its tangent rows and keeps the result
+#: ([E, 2, 64] per interaction) for the adjoint instead of running the network twice; used only while it fits easily
+RADIAL_CACHE = os.environ.get("NVA_RADIAL_CACHE", "1") != "0"
+
+
+def _radial_cache_fits(dev: torch.device, num_edges: int, layers: int) -> bool:
+    if not RADIAL_CACHE or dev.type != "cuda":
+        return False
+    free, _total = torch.cuda.mem_get_info(dev)
+    free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+    return num_edges * 512 * layers < 0.3 * free
 
 
 def _l0_weights(ip: Any, w_last: torch.Tensor, table: torch.Tensor, c: int, avg: float) -> list[torch.Tensor]:
@@ -338,6 +349,19 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
     h = (model.node_embedding / math.sqrt(nz))[species].unsqueeze(1).contiguous()
     node_e = pos.new_zeros(n)
     saved = []
+    keep_h3 = (compute_force or compute_stress) and _radial_cache_fits(dev, csr.num_edges, len(model.interactions))
+
+    def radial_chunks(ws_: list, store: list | None) -> Any:
+        """Chunks ``(i0, i1, e0, e1, h3 value rows)``; with ``store`` the tangent rows are computed too and kept."""
+        for (i0_, i1_, e0_, e1_) in _chunks(csr, n, (8 if store is not None else 4) * 64):
+            ef_ = ops.mace_edge_radial(*geom, e0_, e1_ - e0_, rmax, nb, pc, store is not None)
+            h3_ = _hidden(ws_, ef_, store is not None)
+            del ef_
+            if store is not None:
+                store.append((i0_, i1_, e0_, e1_, h3_))
+                yield i0_, i1_, e0_, e1_, h3_[:, 0]
+            else:
+                yield i0_, i1_, e0_, e1_, h3_
     for li, ip in enumerate(model.interactions):
         ws = [w / math.sqrt(w.shape[0]) for w in ip.radial]
         P = len(ip.paths)
@@ -369,11 +393,10 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         if row_map is not None and L0_MOMENTS and nz <= L0_MOMENTS_MAX_SPECIES and lmax == 3 and ws[-1].shape[0] == 64:
             l0w = _l0_weights(ip, ws[-1], u[:, 0], C, cfg.avg_num_neighbors)
             A = pos.new_empty(n, nz, 16, 64)
-            for (i0, i1, e0, e1) in _chunks(csr, n, 4 * 64):
-                ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, False)
-                h3 = _hidden(ws, ef, False)
+            h3c = [] if keep_h3 else None
+            for (i0, i1, e0, e1, h3) in radial_chunks(ws, h3c):
                 ops.mace_l0_moments(h3, pos, cell, b32, csr.eptr, csr.esend, csr.eS, row_map, i0, i1 - i0, e0, rmax, A)
-                del ef, h3
+                del h3
             msg = pos.new_empty(n, 16, C)
             for l in range(lmax + 1):
                 for lm in range(l * l, (l + 1) * (l + 1)):
@@ -386,16 +409,15 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
             err = _err_words.setdefault(dev, torch.zeros(1, dtype=torch.int32, device=dev))
             wgs = _group_weights(ip, ws[-1], C)
             mid = pos.new_zeros(n, ip.n_mid, C)
-            for (i0, i1, e0, e1) in _chunks(csr, n, 4 * 64):
-                ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, False)
-                h3 = _hidden(ws, ef, False)
+            h3c = [] if keep_h3 else None
+            for (i0, i1, e0, e1, h3) in radial_chunks(ws, h3c):
                 for g, wg in enumerate(wgs):
                     ops.mace_conv_fused(0 if ip.l_in == [0] else 1, g, False, wg, h3, u, pos, cell, b32, csr.eptr, csr.esend,
                                         csr.eS, i0, i1 - i0, e0, rmax, mid, None, None, None, hr, hw, u_ptrs, None, None,
                                         err, row_map)
-                del ef, h3
+                del h3
         else:
-            wgs = None
+            wgs, h3c = None, None
             mid = pos.new_empty(n, ip.n_mid, C)
             for (i0, i1, e0, e1) in _chunks(csr, n, 4 * P * C):
                 ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, False)
@@ -420,7 +442,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
             node_e += s @ (ip.readout_w1 / math.sqrt(C))
             ro = (None, None)
         saved.append((ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs if not (pull and row_map is None) else pull_ptrs[1], wgs,
-                      row_map, l0w))
+                      row_map, l0w, h3c))
         h = h_new
         del B, sc
     scale, shift = model.scale.to(pos.dtype), model.shift.to(pos.dtype)
@@ -434,11 +456,23 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         return out
 
     grad_pos = dd.gpos if dd is not None else torch.zeros_like(pos)
+
+    def tangent_chunks(ws_: list, kept: list | None) -> Any:
+        """``(i0, i1, e0, e1, h3 [E, 2, 64])``: what the forward pass kept, else recomputed chunk by chunk."""
+        if kept is not None:
+            while kept:
+                yield kept.pop(0)
+            return
+        for (i0_, i1_, e0_, e1_) in _chunks(csr, n, 8 * 64):
+            ef_ = ops.mace_edge_radial(*geom, e0_, e1_ - e0_, rmax, nb, pc, True)
+            h3_ = _hidden(ws_, ef_, True)
+            del ef_
+            yield i0_, i1_, e0_, e1_, h3_
     gp_ptrs = dd.gpos_ptrs if dd is not None and not pull else None
     strain_grad = torch.zeros(num_graphs, 9, dtype=torch.float64, device=dev) if compute_stress else None
     dh: torch.Tensor | None = None
     for li in range(len(saved) - 1, -1, -1):
-        ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs, wgs, row_map, l0w = saved[li]
+        ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs, wgs, row_map, l0w, h3c = saved[li]
         k_du_ptrs = None if pull else du_ptrs  # pointer table handed to the kernels (none: local rows only)
         n_out = sum(2 * l + 1 for l in ip.l_out)
         dh_tot = pos.new_zeros(n, n_out, C) if dh is None else dh
@@ -460,23 +494,19 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
                 for lm in range(l * l, (l + 1) * (l + 1)):
                     for s_ in range(nz):
                         gemm.matmul(dmsg[:, lm], l0w[l][s_].t(), out=Q[:, s_, lm])
-            for (i0, i1, e0, e1) in _chunks(csr, n, 8 * 64):
-                ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, True)
-                h3 = _hidden(ws, ef, True)
+            for (i0, i1, e0, e1, h3) in tangent_chunks(ws, h3c):
                 ops.mace_l0_force(h3, Q, pos, cell, b32, csr.eptr, csr.esend, csr.eS, row_map, i0, i1 - i0, e0, rmax,
                                   grad_pos, strain_grad)
-                del ef, h3
+                del h3
             del Q
         elif wgs is not None:
             err = _err_words[dev]
-            for (i0, i1, e0, e1) in _chunks(csr, n, 8 * 64):
-                ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, True)
-                h3 = _hidden(ws, ef, True)
+            for (i0, i1, e0, e1, h3) in tangent_chunks(ws, h3c):
                 for g, wg in enumerate(wgs):
                     ops.mace_conv_fused(0 if ip.l_in == [0] else 1, g, True, wg, h3, u, pos, cell, b32, csr.eptr, csr.esend,
                                         csr.eS, i0, i1 - i0, e0, rmax, dmid, du, grad_pos, strain_grad, hr, hw, u_ptrs,
                                         k_du_ptrs, gp_ptrs, err, row_map)
-                del ef, h3
+                del h3
         else:
             for (i0, i1, e0, e1) in _chunks(csr, n, 8 * P * C):
                 ef = ops.mace_edge_radial(*geom, e0, e1 - e0, rmax, nb, pc, True)
