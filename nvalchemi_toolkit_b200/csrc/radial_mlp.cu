@@ -247,7 +247,7 @@ static void launch_radial(const CUtensorMap& m1, const CUtensorMap& m2, const CU
 // transposed, columns (W_hi, W_hi, W_lo, 0) with W_hi the tf32-representable part of the weight; w2t, w3t: [64, 64]
 // transposed layers.  Returns [rows, 64].
 Tensor mace_radial_hidden(const Tensor& ef, const Tensor& w1t, const Tensor& w2t, const Tensor& w3t, bool tangent,
-                          Tensor err) {
+                          Tensor err, const c10::optional<Tensor>& out_buf) {
   c10::cuda::CUDAGuard guard(ef.device());
   NVA_CHECK_CONTIG(ef); NVA_CHECK_CONTIG(w1t); NVA_CHECK_CONTIG(w2t); NVA_CHECK_CONTIG(w3t);
   TORCH_CHECK(ef.scalar_type() == at::kFloat && ef.size(-1) == 8, "basis rows must be float32 [rows, 8]");
@@ -255,7 +255,16 @@ Tensor mace_radial_hidden(const Tensor& ef, const Tensor& w1t, const Tensor& w2t
                   w3t.size(1) == 64, "fused radial MLP is specialised for 8 -> 64 -> 64 -> 64");
   int64_t rows = ef.numel() / 8;
   TORCH_CHECK(!tangent || rows % 2 == 0, "tangent mode needs interleaved (value, derivative) rows");
-  Tensor out = at::empty({rows, 64}, ef.options());
+  // `out_buf` (optional): caller-owned storage of at least rows * 64 floats, so that a result kept across kernels does
+  // not go through the allocator with a slightly different size every step
+  Tensor out;
+  if (out_buf.has_value()) {
+    TORCH_CHECK(out_buf->is_contiguous() && out_buf->scalar_type() == at::kFloat && out_buf->numel() >= rows * 64,
+                "mace_radial_hidden: output buffer too small");
+    out = out_buf->view({-1}).narrow(0, 0, rows * 64).view({rows, 64});
+  } else {
+    out = at::empty({rows, 64}, ef.options());
+  }
   if (rows == 0) return out;
   CUtensorMap m1 = weight_map(w1t.data_ptr<float>(), 32), m2 = weight_map(w2t.data_ptr<float>(), 64),
               m3 = weight_map(w3t.data_ptr<float>(), 64);
@@ -272,5 +281,5 @@ Tensor mace_radial_hidden(const Tensor& ef, const Tensor& w1t, const Tensor& w2t
 }  // namespace nva
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
-  m.def("mace_radial_hidden(Tensor ef, Tensor w1t, Tensor w2t, Tensor w3t, bool tangent, Tensor(a!) err) -> Tensor", &nva::mace_radial_hidden);
+  m.def("mace_radial_hidden(Tensor ef, Tensor w1t, Tensor w2t, Tensor w3t, bool tangent, Tensor(a!) err, Tensor(b!)? out_buf=None) -> Tensor", &nva::mace_radial_hidden);
 }

@@ -152,7 +152,28 @@ def _split_tf32(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return hi, w - hi
 
 
-def _hidden_fused(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool) -> torch.Tensor | None:
+#: storage of the radial activations kept between the forward pass and its adjoint, reused from step to step (the edge
+#: count changes a little every step; asking the allocator for a new ~10 GB block each time would stall it)
+_h3_pool: dict[tuple, torch.Tensor] = {}
+
+
+def _pooled(key: tuple, numel: int, like: torch.Tensor) -> torch.Tensor:
+    buf = _h3_pool.get(key)
+    if buf is None or buf.numel() < numel or buf.device != like.device:
+        buf = None
+        _h3_pool.pop(key, None)
+        cap = (int(numel * 1.03) + (1 << 22)) // (1 << 22) * (1 << 22)
+        buf = _h3_pool[key] = torch.empty(cap, dtype=torch.float32, device=like.device)
+    return buf
+
+
+def release_radial_cache() -> None:
+    """Frees the pooled storage of kept radial activations."""
+    _h3_pool.clear()
+
+
+def _hidden_fused(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool, out_buf: torch.Tensor | None = None
+                  ) -> torch.Tensor | None:
     if not (FUSED_RADIAL and ef.is_cuda and ef.dtype == torch.float32 and gemm.get_precision() == "tf32" and len(ws) == 4
             and tuple(ws[0].shape) == (8, 64) and tuple(ws[1].shape) == (64, 64) and tuple(ws[2].shape) == (64, 64)):
         return None
@@ -162,13 +183,13 @@ def _hidden_fused(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool) -> 
     err = _err_words.setdefault(ef.device, torch.zeros(1, dtype=torch.int32, device=ef.device))
     rows = ef if with_grad else ef[:, 0]
     out = ops.mace_radial_hidden(rows.reshape(-1, 8).contiguous(), w1t, ws[1].t().contiguous(), ws[2].t().contiguous(),
-                                 bool(with_grad), err)
+                                 bool(with_grad), err, out_buf)
     return out.reshape(ef.shape[0], 2, 64) if with_grad else out
 
 
-def _hidden(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool) -> torch.Tensor:
+def _hidden(ws: list[torch.Tensor], ef: torch.Tensor, with_grad: bool, out_buf: torch.Tensor | None = None) -> torch.Tensor:
     """Radial MLP up to its last hidden layer: ``[E, 64]`` or, with the tangent, ``[E, 2, 64]`` (rows interleaved)."""
-    fused = _hidden_fused(ws, ef, with_grad)
+    fused = _hidden_fused(ws, ef, with_grad, out_buf)
     if fused is not None:
         return fused
     e = ef.shape[0]
@@ -209,6 +230,7 @@ def _radial_cache_fits(dev: torch.device, num_edges: int, layers: int) -> bool:
         return False
     free, _total = torch.cuda.mem_get_info(dev)
     free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+    free += sum(b.numel() * 4 for b in _h3_pool.values() if b.device == dev)  # storage already set aside for this
     return num_edges * 512 * layers < 0.3 * free
 
 
@@ -351,11 +373,12 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
     saved = []
     keep_h3 = (compute_force or compute_stress) and _radial_cache_fits(dev, csr.num_edges, len(model.interactions))
 
-    def radial_chunks(ws_: list, store: list | None) -> Any:
+    def radial_chunks(ws_: list, store: list | None, layer: int) -> Any:
         """Chunks ``(i0, i1, e0, e1, h3 value rows)``; with ``store`` the tangent rows are computed too and kept."""
-        for (i0_, i1_, e0_, e1_) in _chunks(csr, n, (8 if store is not None else 4) * 64):
+        for ci, (i0_, i1_, e0_, e1_) in enumerate(_chunks(csr, n, (8 if store is not None else 4) * 64)):
             ef_ = ops.mace_edge_radial(*geom, e0_, e1_ - e0_, rmax, nb, pc, store is not None)
-            h3_ = _hidden(ws_, ef_, store is not None)
+            buf = _pooled((id(model), dev, layer, ci), (e1_ - e0_) * 128, pos) if store is not None else None
+            h3_ = _hidden(ws_, ef_, store is not None, buf)
             del ef_
             if store is not None:
                 store.append((i0_, i1_, e0_, e1_, h3_))
@@ -394,7 +417,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
             l0w = _l0_weights(ip, ws[-1], u[:, 0], C, cfg.avg_num_neighbors)
             A = pos.new_empty(n, nz, 16, 64)
             h3c = [] if keep_h3 else None
-            for (i0, i1, e0, e1, h3) in radial_chunks(ws, h3c):
+            for (i0, i1, e0, e1, h3) in radial_chunks(ws, h3c, li):
                 ops.mace_l0_moments(h3, pos, cell, b32, csr.eptr, csr.esend, csr.eS, row_map, i0, i1 - i0, e0, rmax, A)
                 del h3
             msg = pos.new_empty(n, 16, C)
@@ -410,7 +433,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
             wgs = _group_weights(ip, ws[-1], C)
             mid = pos.new_zeros(n, ip.n_mid, C)
             h3c = [] if keep_h3 else None
-            for (i0, i1, e0, e1, h3) in radial_chunks(ws, h3c):
+            for (i0, i1, e0, e1, h3) in radial_chunks(ws, h3c, li):
                 for g, wg in enumerate(wgs):
                     ops.mace_conv_fused(0 if ip.l_in == [0] else 1, g, False, wg, h3, u, pos, cell, b32, csr.eptr, csr.esend,
                                         csr.eS, i0, i1 - i0, e0, rmax, mid, None, None, None, hr, hw, u_ptrs, None, None,
