@@ -246,3 +246,16 @@ def test_neighbor_matrix_gpu_matches_cpu():
     mg = m.clone().cuda()
     compute_neighbors(mg, 4.0)
     assert torch.equal(mg.num_neighbors.cpu(), m.num_neighbors)
+
+
+def test_radial_cache_pool_reuses_and_releases_storage():
+    from nvalchemi_toolkit_b200.models.mace import native
+
+    like = torch.zeros(1)
+    a = native._pooled(("t", 0), 1000, like)
+    assert a.numel() >= 1000 and native._pooled(("t", 0), 900, like) is a     # smaller request: same storage
+    b = native._pooled(("t", 0), a.numel() + 1, like)
+    assert b is not a and b.numel() > a.numel()                                # grown, old buffer dropped
+    assert not native._radial_cache_fits(torch.device("cpu"), 10, 2)           # only used on CUDA devices
+    native.release_radial_cache()
+    assert not native._h3_pool
