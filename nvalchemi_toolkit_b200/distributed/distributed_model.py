@@ -59,6 +59,22 @@ def consolidate_outputs(out: dict, sharded: ShardedBatch, spec: MLIPSpec, halo: 
     return res
 
 
+def _keep_owned_senders(padded: Any, n_owned: int) -> None:
+    """Edge partition for folding policies: a rank keeps the edges whose SENDER it owns (the receiver may be a ghost, its
+    partial sum is folded into the owner afterwards), so every edge is evaluated exactly once over all ranks.  Rows of
+    the neighbour matrix are re-compacted in place (idempotent)."""
+    nm, num = padded.neighbor_matrix, padded.num_neighbors
+    k = nm.shape[1]
+    slot = torch.arange(k, device=nm.device)[None, :]
+    valid = (slot < num.long()[:, None]) & (nm.long() < n_owned)
+    order = torch.argsort((~valid).to(torch.int8), dim=1, stable=True)
+    nm.copy_(torch.gather(nm, 1, order))
+    sh = padded.neighbor_matrix_shifts
+    if sh is not None:
+        sh.copy_(torch.gather(sh, 1, order[..., None].expand(-1, -1, sh.shape[-1])))
+    num.copy_(valid.sum(1).to(num.dtype))
+
+
 class DistributedModel(nn.Module):
     def __init__(self, model: Any, config: DomainConfig, spec: MLIPSpec | None = None, group: Any = None,
                  max_neighbors: int | None = None, own_halo: bool = False) -> None:
@@ -89,6 +105,8 @@ class DistributedModel(nn.Module):
             self.neighbor_hook(SimpleNamespace(batch=padded), None)
             if spec.consolidation == Consolidation.DIRECT_MASKED or (spec.refresh_per_layer and not self._policy_folds()):
                 padded.num_neighbors[sharded.n_owned:] = 0  # ghost atoms send, they do not receive
+            elif spec.refresh_per_layer and halo.n_ghost > 0:
+                _keep_owned_senders(padded, sharded.n_owned)  # fold policy: every edge lives on its sender's owner
         if spec.refresh_per_layer and halo.n_ghost > 0:
             from nvalchemi_toolkit_b200.distributed.dispatch import HaloDispatchMode
 

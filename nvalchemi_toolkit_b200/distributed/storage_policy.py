@@ -96,6 +96,9 @@ class HaloStoragePolicy:
     ``gather_mode``: ``"halo_read"`` refreshes the ghost rows from their owners before a gather, ``"local"`` reads what
     is there.  ``scatter_mode``: ``"halo_correction"`` adds the partial sums accumulated on ghost rows into the owners'
     rows after a scatter (needed when edges whose receiver is a ghost are kept), ``"local"`` leaves them.
+
+    Folding is only right for an edge-partitioned graph (every edge evaluated on exactly one rank): with this policy
+    ``DistributedModel`` keeps, on each rank, the edges whose sender it owns (``_keep_owned_senders``).
     """
 
     scatter_mode: str = "halo_correction"

@@ -171,6 +171,8 @@ def _worker(rank, world, port, q, which):
         else:
             model = _mpnn_wrapper()
             spec = model.distribution_spec()
+            if which == "mpnn_fold":  # every edge on its sender's owner; partial sums of ghost receivers are folded
+                spec = spec.with_(storage_policy={"kind": "halo"})
             deep = ShardedBatch.from_batch(batch, cfg, spec.with_(refresh_per_layer=False)).n_ghost
         sh = ShardedBatch.from_batch(batch, cfg, spec)
         dm = DistributedModel(model, cfg, spec=spec)
@@ -181,7 +183,7 @@ def _worker(rank, world, port, q, which):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("which,port", [("mpnn", 29671), ("mace", 29673)])
+@pytest.mark.parametrize("which,port", [("mpnn", 29671), ("mace", 29673), ("mpnn_fold", 29675)])
 def test_unmodified_model_with_one_cutoff_halo_matches_single_process(which, port):
     import torch.multiprocessing as mp
 
@@ -206,6 +208,7 @@ def test_unmodified_model_with_one_cutoff_halo_matches_single_process(which, por
         assert abs(energy[0] - float(ref["energy"].detach().reshape(-1)[0])) < 1e-8
         assert 0 < n_ghost < n_ghost_deep           # one cutoff of ghosts instead of one per message pass
         assert stats["refreshes"] >= 1              # ghost feature rows were exchanged between the layers
+        assert (stats["folds"] >= 3) == (which == "mpnn_fold")
 
 
 def _p2p_worker(rank, world, port, q):
