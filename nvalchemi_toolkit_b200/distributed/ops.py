@@ -144,3 +144,21 @@ class ShardTensor:
         rows, _ = all_gather_rows(self.local.detach().contiguous(), self.sharded.group)
         ids, _ = all_gather_rows(self.sharded.global_ids, self.sharded.group)
         return rows[torch.argsort(ids)]
+
+
+# The "mechanism" namespace (reference ``nvalchemi/distributed/ops.py``): everything a hand-written distributed forward
+# needs, importable from one place.
+from nvalchemi_toolkit_b200.distributed._runtime import mesh_group  # noqa: E402
+from nvalchemi_toolkit_b200.distributed.collectives import (distributed_index_select, distributed_scatter_add,  # noqa: E402
+                                                            gather_to_replicate)
+from nvalchemi_toolkit_b200.distributed.context import (NOT_DISTRIBUTED, DistributedContext, ShardRouting,  # noqa: E402
+                                                        activate_dd_context, current_dd_context)
+from nvalchemi_toolkit_b200.distributed.halo import all_gather_rows, all_to_all_rows, neighbor_exchange_rows  # noqa: E402
+from nvalchemi_toolkit_b200.distributed.storage_policy import (GraphParallelPolicy, HaloStoragePolicy, PlainShard,  # noqa: E402
+                                                               RefreshOnlyHaloPolicy, StoragePolicy)
+
+__all__ = ["halo_forward", "halo_scatter_correct", "gather_replicate", "per_system_reduce", "distributed_all_reduce",
+           "ShardTensor", "mesh_group", "distributed_index_select", "distributed_scatter_add", "gather_to_replicate",
+           "DistributedContext", "NOT_DISTRIBUTED", "ShardRouting", "activate_dd_context", "current_dd_context",
+           "all_gather_rows", "all_to_all_rows", "neighbor_exchange_rows", "StoragePolicy", "PlainShard",
+           "HaloStoragePolicy", "RefreshOnlyHaloPolicy", "GraphParallelPolicy"]
