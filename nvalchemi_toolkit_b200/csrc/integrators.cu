@@ -157,17 +157,37 @@ void fire_step(Tensor pos, Tensor vel, const Tensor& force, const Tensor& mass, 
                const Tensor& alpha_start, const Tensor& f_alpha, const Tensor& dt_min, const Tensor& dt_max,
                const Tensor& maxstep, Tensor n_pos, const Tensor& n_min, const Tensor& f_dec,
                const Tensor& f_inc, const Tensor& uphill, Tensor vf, Tensor vv, Tensor ff,
-               const Tensor& batch_idx, bool compute_reductions) {
+               const Tensor& batch_idx, bool compute_reductions, const c10::optional<Tensor>& max_dr,
+               int64_t phase) {
+  // phase 0: the whole iteration.  phase 1: controller + velocity update only, the per-system largest displacement is
+  // left in `max_dr` (float32 [M]); phase 2: position update only, from a `max_dr` the caller has reduced (MAX) over
+  // the ranks of a domain decomposition in between, so that every rank applies the same step-length cap.
   NVA_CHECK_CONTIG(pos); NVA_CHECK_CONTIG(vel); NVA_CHECK_CONTIG(force);
   c10::cuda::OptionalCUDAGuard guard(pos.is_cuda() ? c10::make_optional(pos.device()) : c10::nullopt);
   bool cuda = pos.is_cuda();
   int64_t n = pos.size(0), M = alpha.size(0);
   const int* b = batch_idx.data_ptr<int>();
+  TORCH_CHECK(phase == 0 || (max_dr.has_value() && max_dr->scalar_type() == at::kFloat && max_dr->numel() == M),
+              "fire_step: phases 1 and 2 need a float32 max_dr of one entry per system");
   AT_DISPATCH_FLOATING_TYPES(pos.scalar_type(), "fire_step", [&] {
     scalar_t* r = pos.data_ptr<scalar_t>();
     scalar_t* v = vel.data_ptr<scalar_t>();
     const scalar_t* f = force.data_ptr<scalar_t>();
     const scalar_t* m = mass.data_ptr<scalar_t>();
+    Tensor maxdr = max_dr.has_value() ? *max_dr : at::empty({M}, pos.options().dtype(at::kFloat));
+    float* md = maxdr.data_ptr<float>();
+    const scalar_t* ms = maxstep.data_ptr<scalar_t>();
+    scalar_t* d = dt.data_ptr<scalar_t>();
+    if (phase == 2) {
+      for_each(cuda, n, [=] NVA_LAMBDA(int64_t i) {
+        int s = b[i];
+        scalar_t h = d[s];
+        scalar_t scale = md[s] > (float)ms[s] ? ms[s] / (scalar_t)md[s] : scalar_t(1);
+        for (int c = 0; c < 3; ++c) r[3 * i + c] += scale * h * v[3 * i + c];
+      });
+      return;
+    }
+    maxdr.zero_();
     if (compute_reductions) {
       Tensor red = at::zeros({M, 3}, pos.options().dtype(at::kDouble));
       seg_reduce<scalar_t>(cuda, n, b, red.data_ptr<double>(), 3, [=] NVA_LAMBDA(int64_t i, double* o) {
@@ -183,7 +203,6 @@ void fire_step(Tensor pos, Tensor vel, const Tensor& force, const Tensor& mass, 
     Tensor coef = at::empty({M, 3}, pos.options());
     scalar_t* cf = coef.data_ptr<scalar_t>();
     scalar_t* al = alpha.data_ptr<scalar_t>();
-    scalar_t* d = dt.data_ptr<scalar_t>();
     int* np_ = n_pos.data_ptr<int>();
     const scalar_t *as = alpha_start.data_ptr<scalar_t>(), *fa = f_alpha.data_ptr<scalar_t>(),
                    *dmin = dt_min.data_ptr<scalar_t>(), *dmax = dt_max.data_ptr<scalar_t>(),
@@ -210,8 +229,6 @@ void fire_step(Tensor pos, Tensor vel, const Tensor& force, const Tensor& mass, 
       cf[3 * s] = keep; cf[3 * s + 1] = mix; cf[3 * s + 2] = d[s];
     });
     // velocity mixing + kick; per-system max displacement (double accumulators via atomic max on bits)
-    Tensor maxdr = at::zeros({M}, pos.options().dtype(at::kFloat));
-    float* md = maxdr.data_ptr<float>();
     for_each(cuda, n, [=] NVA_LAMBDA(int64_t i) {
       int s = b[i];
       scalar_t keep = cf[3 * s], mix = cf[3 * s + 1], h = cf[3 * s + 2], im = scalar_t(1) / m[i];
@@ -228,7 +245,7 @@ void fire_step(Tensor pos, Tensor vel, const Tensor& force, const Tensor& mass, 
       if (dn > md[s]) md[s] = dn;
 #endif
     });
-    const scalar_t* ms = maxstep.data_ptr<scalar_t>();
+    if (phase == 1) return;
     for_each(cuda, n, [=] NVA_LAMBDA(int64_t i) {
       int s = b[i];
       scalar_t h = cf[3 * s + 2];
@@ -373,7 +390,7 @@ TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("langevin_half_step(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor masses, Tensor dt, Tensor temperature, Tensor friction, int random_seed, Tensor batch_idx, Tensor? atom_ids=None) -> ()", &nva::langevin_half_step);
   m.def("langevin_finalize(Tensor(a!) velocities, Tensor forces_new, Tensor masses, Tensor dt, Tensor batch_idx) -> ()", &nva::vv_velocity_finalize);
   m.def("compute_kinetic_energy(Tensor velocities, Tensor masses, Tensor batch_idx, int num_systems) -> Tensor", &nva::compute_kinetic_energy);
-  m.def("_fire_step_op(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor masses, Tensor(c!) alpha, Tensor(d!) dt, Tensor alpha_start, Tensor f_alpha, Tensor dt_min, Tensor dt_max, Tensor maxstep, Tensor(e!) n_steps_positive, Tensor n_min, Tensor f_dec, Tensor f_inc, Tensor uphill_flag, Tensor(f!) vf, Tensor(g!) vv, Tensor(h!) ff, Tensor batch_idx, bool compute_reductions) -> ()", &nva::fire_step);
+  m.def("_fire_step_op(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor masses, Tensor(c!) alpha, Tensor(d!) dt, Tensor alpha_start, Tensor f_alpha, Tensor dt_min, Tensor dt_max, Tensor maxstep, Tensor(e!) n_steps_positive, Tensor n_min, Tensor f_dec, Tensor f_inc, Tensor uphill_flag, Tensor(f!) vf, Tensor(g!) vv, Tensor(h!) ff, Tensor batch_idx, bool compute_reductions, Tensor? max_dr=None, int phase=0) -> ()", &nva::fire_step);
   m.def("maxwell_boltzmann(Tensor(a!) velocities, Tensor masses, Tensor kT, Tensor batch_idx, int seed, Tensor? atom_ids=None) -> ()", &nva::maxwell_boltzmann);
   m.def("momentum_sums(Tensor velocities, Tensor masses, Tensor batch_idx, int num_systems) -> Tensor", &nva::momentum_sums);
   m.def("velocity_shift_scale(Tensor(a!) velocities, Tensor shift, Tensor scale, Tensor batch_idx) -> ()", &nva::velocity_shift_scale);

@@ -54,11 +54,12 @@ __global__ void search_kernel(int64_t n, const T* __restrict__ pos, const T* __r
                               const int64_t* __restrict__ bin_id, const int* __restrict__ wrap,
                               const int64_t* __restrict__ order, const int64_t* __restrict__ bin_ptr,
                               const bool* __restrict__ rebuild, T cutoff2, int K, bool half_list,
-                              int* __restrict__ nm, int* __restrict__ num, int* __restrict__ shifts) {
+                              int* __restrict__ nm, int* __restrict__ num, int* __restrict__ shifts, int64_t n_rows) {
   int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (t >= n) return;
   // threads walk atoms in bin order so a warp shares its candidate bins
   int64_t i = order[t];
+  if (i >= n_rows) return;  // rows beyond n_rows are candidates only (ghost atoms send, they do not receive)
   int s = batch_idx[i];
   if (rebuild != nullptr && !rebuild[s]) return;
   const int* I = fi + 8 * s;
@@ -119,10 +120,11 @@ __global__ void search_kernel(int64_t n, const T* __restrict__ pos, const T* __r
 template <typename T>
 void search_cpu(int64_t n, const T* pos, const T* cell, const int* batch_idx, const int* fi, const int64_t* bin_id,
                 const int* wrap, const int64_t* order, const int64_t* bin_ptr, const bool* rebuild, T cutoff2,
-                int K, bool half_list, int* nm, int* num, int* shifts) {
+                int K, bool half_list, int* nm, int* num, int* shifts, int64_t n_rows) {
 #pragma omp parallel for schedule(dynamic, 64)
   for (int64_t t = 0; t < n; ++t) {
     int64_t i = order[t];
+    if (i >= n_rows) continue;
     int s = batch_idx[i];
     if (rebuild != nullptr && !rebuild[s]) continue;
     const int* I = fi + 8 * s;
@@ -181,11 +183,15 @@ void search_cpu(int64_t n, const T* pos, const T* cell, const int* batch_idx, co
 // out_* are updated in place (rows of systems whose rebuild flag is false are left untouched).
 void neighbor_matrix_build(const Tensor& pos, const Tensor& cell, const Tensor& pbc, const Tensor& batch_idx,
                            const Tensor& batch_ptr, double cutoff, bool half_list, Tensor out_matrix,
-                           Tensor out_num, Tensor out_shifts, const c10::optional<Tensor>& rebuild_flags) {
+                           Tensor out_num, Tensor out_shifts, const c10::optional<Tensor>& rebuild_flags,
+                           int64_t num_rows) {
   c10::cuda::OptionalCUDAGuard guard(pos.is_cuda() ? c10::make_optional(pos.device()) : c10::nullopt);
   NVA_CHECK_CONTIG(pos); NVA_CHECK_CONTIG(cell); NVA_CHECK_CONTIG(out_matrix); NVA_CHECK_CONTIG(out_shifts);
   int64_t n = pos.size(0), B = cell.size(0), K = out_matrix.size(1);
   if (n == 0) return;
+  const int64_t n_rows = num_rows < 0 ? n : std::min<int64_t>(num_rows, n);
+  TORCH_CHECK(out_matrix.size(0) >= n_rows && out_num.size(0) >= n_rows && out_shifts.size(0) >= n_rows,
+              "neighbor_matrix_build: output has fewer rows than requested");
   auto fopt = pos.options().dtype(at::kDouble);
   Tensor celld = cell.to(at::kDouble);
   Tensor inv = at::linalg_inv(celld);                                    // [B,3,3]
@@ -264,13 +270,13 @@ void neighbor_matrix_build(const Tensor& pos, const Tensor& cell, const Tensor& 
           n, pos.data_ptr<scalar_t>(), cell_t.data_ptr<scalar_t>(), batch_idx.data_ptr<int>(), fi.data_ptr<int>(),
           bin_id.data_ptr<int64_t>(), wrap.data_ptr<int>(), order.data_ptr<int64_t>(), bin_ptr.data_ptr<int64_t>(),
           rb, c2, (int)K, half_list, out_matrix.data_ptr<int>(), out_num.data_ptr<int>(),
-          out_shifts.data_ptr<int>());
+          out_shifts.data_ptr<int>(), n_rows);
       C10_CUDA_KERNEL_LAUNCH_CHECK();
     } else {
       search_cpu<scalar_t>(n, pos.data_ptr<scalar_t>(), cell_t.data_ptr<scalar_t>(), batch_idx.data_ptr<int>(),
                            fi.data_ptr<int>(), bin_id.data_ptr<int64_t>(), wrap.data_ptr<int>(),
                            order.data_ptr<int64_t>(), bin_ptr.data_ptr<int64_t>(), rb, c2, (int)K, half_list,
-                           out_matrix.data_ptr<int>(), out_num.data_ptr<int>(), out_shifts.data_ptr<int>());
+                           out_matrix.data_ptr<int>(), out_num.data_ptr<int>(), out_shifts.data_ptr<int>(), n_rows);
     }
   });
 }
@@ -314,5 +320,5 @@ void csr_fill(const Tensor& nm, const c10::optional<Tensor>& shifts, const Tenso
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("csr_fill(Tensor nm, Tensor? shifts, Tensor eptr, Tensor(a!) esend, Tensor(b!) erecv, Tensor(c!) eS) -> ()", &nva::csr_fill);
-  m.def("neighbor_matrix_build(Tensor positions, Tensor cell, Tensor pbc, Tensor batch_idx, Tensor batch_ptr, float cutoff, bool half_list, Tensor(a!) out_matrix, Tensor(b!) out_num, Tensor(c!) out_shifts, Tensor? rebuild_flags=None) -> ()", &nva::neighbor_matrix_build);
+  m.def("neighbor_matrix_build(Tensor positions, Tensor cell, Tensor pbc, Tensor batch_idx, Tensor batch_ptr, float cutoff, bool half_list, Tensor(a!) out_matrix, Tensor(b!) out_num, Tensor(c!) out_shifts, Tensor? rebuild_flags=None, int num_rows=-1) -> ()", &nva::neighbor_matrix_build);
 }

@@ -116,36 +116,95 @@ TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
 
 namespace nva {
 // Ghost refresh by pull: dst[row0 + g, :] = src_{home_rank[g]}[home_row[g], :] (+ shift[g, :]).  The consumer reads
-// the owners' rows over NVLink; no send lists or counts have to be negotiated.
-__global__ void halo_pull_kernel(int64_t n_ghost, int D, float* __restrict__ dst, int64_t row0,
-                                 const int* __restrict__ home_rank, const int* __restrict__ home_row,
-                                 const float* __restrict__ shift, const int64_t* __restrict__ src_ptrs) {
-  int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (t >= n_ghost * D) return;
-  int64_t g = t / D;
-  int d = (int)(t - g * D);
-  const float* src = reinterpret_cast<const float*>(src_ptrs[home_rank[g]]);
-  float v = src[(int64_t)home_row[g] * D + d];
-  if (shift != nullptr) v += shift[g * D + d];
-  dst[(row0 + g) * D + d] = v;
+// the owners' rows over NVLink; no send lists or counts have to be negotiated.  Rows whose width is a multiple of four
+// floats move as 16-byte vectors, one warp per row with all of a lane's loads issued before its stores (a 512-float
+// row keeps 2 KB in flight per warp); narrow rows (positions: three floats) take one thread per row.  `used` (optional,
+// one byte per ghost) skips rows that no local edge references.
+template <int UNROLL>
+__global__ void halo_pull_vec_kernel(int64_t n_ghost, int D4, float4* __restrict__ dst, int64_t row0,
+                                     const int* __restrict__ home_rank, const int* __restrict__ home_row,
+                                     const int64_t* __restrict__ src_ptrs, const uint8_t* __restrict__ used) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t g = warp; g < n_ghost; g += nwarps) {
+    if (used != nullptr && used[g] == 0) continue;
+    const float4* src = reinterpret_cast<const float4*>(src_ptrs[home_rank[g]]) + (int64_t)home_row[g] * D4;
+    float4* out = dst + (row0 + g) * D4;
+    for (int c0 = 0; c0 < D4; c0 += 32 * UNROLL) {
+      float4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < D4) v[u] = src[c];
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < D4) out[c] = v[u];
+      }
+    }
+  }
+}
+
+__global__ void halo_pull_narrow_kernel(int64_t n_ghost, int D, float* __restrict__ dst, int64_t row0,
+                                        const int* __restrict__ home_rank, const int* __restrict__ home_row,
+                                        const float* __restrict__ shift, const int64_t* __restrict__ src_ptrs,
+                                        const uint8_t* __restrict__ used) {
+  const int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (g >= n_ghost || (used != nullptr && used[g] == 0)) return;
+  const float* src = reinterpret_cast<const float*>(src_ptrs[home_rank[g]]) + (int64_t)home_row[g] * D;
+  float* out = dst + (row0 + g) * D;
+  for (int d = 0; d < D; ++d) out[d] = src[d] + (shift != nullptr ? shift[g * D + d] : 0.f);
 }
 
 void halo_pull_rows(at::Tensor dst, int64_t row0, const at::Tensor& home_rank, const at::Tensor& home_row,
-                    const c10::optional<at::Tensor>& shift, const at::Tensor& src_ptrs) {
+                    const c10::optional<at::Tensor>& shift, const at::Tensor& src_ptrs,
+                    const c10::optional<at::Tensor>& used) {
   c10::cuda::CUDAGuard guard(dst.device());
+  NVA_CHECK_CONTIG(dst);
   int64_t n = home_rank.size(0);
   if (n == 0) return;
+  TORCH_CHECK(row0 + n <= dst.size(0), "halo_pull_rows: ghost rows exceed the destination");
   int D = (int)(dst.numel() / dst.size(0));
-  int64_t total = n * D;
-  halo_pull_kernel<<<(unsigned)((total + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
-      n, D, dst.data_ptr<float>(), row0, home_rank.data_ptr<int>(), home_row.data_ptr<int>(),
-      shift.has_value() ? shift->data_ptr<float>() : nullptr, src_ptrs.data_ptr<int64_t>());
+  const uint8_t* um = used.has_value() ? used->data_ptr<uint8_t>() : nullptr;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (D % 4 == 0 && !shift.has_value() && (reinterpret_cast<uintptr_t>(dst.data_ptr()) & 15) == 0) {
+    int64_t blocks = std::min<int64_t>((n + 7) / 8, 148 * 16);
+    halo_pull_vec_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(
+        n, D / 4, reinterpret_cast<float4*>(dst.data_ptr<float>()), row0, home_rank.data_ptr<int>(), home_row.data_ptr<int>(),
+        src_ptrs.data_ptr<int64_t>(), um);
+  } else {
+    halo_pull_narrow_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+        n, D, dst.data_ptr<float>(), row0, home_rank.data_ptr<int>(), home_row.data_ptr<int>(),
+        shift.has_value() ? shift->data_ptr<float>() : nullptr, src_ptrs.data_ptr<int64_t>(), um);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// used[g] = 1 for every ghost row (local row >= n_owned) that appears as a sender in the edge list.
+__global__ void mark_used_senders_kernel(int64_t n_edges, const int* __restrict__ esend, int n_owned, int n_local,
+                                         uint8_t* __restrict__ used) {
+  const int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (e >= n_edges) return;
+  const int j = esend[e];
+  if (j >= n_owned && j < n_local) used[j - n_owned] = 1;
+}
+
+void mark_used_senders(const at::Tensor& esend, int64_t n_edges, int64_t n_owned, at::Tensor used) {
+  c10::cuda::CUDAGuard guard(esend.device());
+  TORCH_CHECK(esend.scalar_type() == at::kInt && used.scalar_type() == at::kByte, "mark_used_senders: int32 senders, uint8 marks");
+  TORCH_CHECK(n_edges <= esend.numel(), "mark_used_senders: edge count exceeds the sender array");
+  if (n_edges == 0) return;
+  mark_used_senders_kernel<<<(unsigned)((n_edges + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      n_edges, esend.data_ptr<int>(), (int)n_owned, (int)(n_owned + used.numel()), used.data_ptr<uint8_t>());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 }  // namespace nva
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
-  m.def("halo_pull_rows(Tensor(a!) dst, int row0, Tensor home_rank, Tensor home_row, Tensor? shift, Tensor src_ptrs) -> ()", &nva::halo_pull_rows);
+  m.def("halo_pull_rows(Tensor(a!) dst, int row0, Tensor home_rank, Tensor home_row, Tensor? shift, Tensor src_ptrs, Tensor? used=None) -> ()", &nva::halo_pull_rows);
+  m.def("mark_used_senders(Tensor esend, int n_edges, int n_owned, Tensor(a!) used) -> ()", &nva::mark_used_senders);
 }
 
 namespace nva {
@@ -191,33 +250,62 @@ TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
 namespace nva {
 // Reverse halo: dst_{home_rank[g]}[home_row[g], :] += src[row0 + g, :].  Gradients that the local kernels accumulated on
 // ghost rows travel to the owners once per row (instead of one NVLink reduction per edge from inside the convolution).
-__global__ void halo_push_add_kernel(int64_t n_ghost, int D, const float* __restrict__ src, int64_t row0,
-                                     const int* __restrict__ home_rank, const int* __restrict__ home_row,
-                                     const int64_t* __restrict__ dst_ptrs) {
-  int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (t >= n_ghost * D) return;
-  int64_t g = t / D;
-  int d = (int)(t - g * D);
-  float v = src[(row0 + g) * D + d];
-  if (v == 0.f) return;
-  float* dst = reinterpret_cast<float*>(dst_ptrs[home_rank[g]]);
-  atomicAdd(dst + (int64_t)home_row[g] * D + d, v);
+// Wide rows leave as 16-byte vector reductions (one warp per row, all-zero vectors skipped), narrow rows as scalar
+// reductions from one thread per row.
+__global__ void halo_push_add_vec_kernel(int64_t n_ghost, int D4, const float4* __restrict__ src, int64_t row0,
+                                         const int* __restrict__ home_rank, const int* __restrict__ home_row,
+                                         const int64_t* __restrict__ dst_ptrs, const uint8_t* __restrict__ used) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t g = warp; g < n_ghost; g += nwarps) {
+    if (used != nullptr && used[g] == 0) continue;
+    float4* dst = reinterpret_cast<float4*>(dst_ptrs[home_rank[g]]) + (int64_t)home_row[g] * D4;
+    const float4* in = src + (row0 + g) * D4;
+    for (int c = lane; c < D4; c += 32) {
+      const float4 v = in[c];
+      if (v.x != 0.f || v.y != 0.f || v.z != 0.f || v.w != 0.f) atomicAdd(dst + c, v);
+    }
+  }
+}
+
+__global__ void halo_push_add_narrow_kernel(int64_t n_ghost, int D, const float* __restrict__ src, int64_t row0,
+                                            const int* __restrict__ home_rank, const int* __restrict__ home_row,
+                                            const int64_t* __restrict__ dst_ptrs, const uint8_t* __restrict__ used) {
+  const int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (g >= n_ghost || (used != nullptr && used[g] == 0)) return;
+  float* dst = reinterpret_cast<float*>(dst_ptrs[home_rank[g]]) + (int64_t)home_row[g] * D;
+  const float* in = src + (row0 + g) * D;
+  for (int d = 0; d < D; ++d) {
+    const float v = in[d];
+    if (v != 0.f) atomicAdd(dst + d, v);
+  }
 }
 
 void halo_push_add_rows(const at::Tensor& src, int64_t row0, const at::Tensor& home_rank, const at::Tensor& home_row,
-                        const at::Tensor& dst_ptrs) {
+                        const at::Tensor& dst_ptrs, const c10::optional<at::Tensor>& used) {
   c10::cuda::CUDAGuard guard(src.device());
   NVA_CHECK_CONTIG(src);
   int64_t n = home_rank.size(0);
   if (n == 0) return;
+  TORCH_CHECK(row0 + n <= src.size(0), "halo_push_add_rows: ghost rows exceed the source");
   int D = (int)(src.numel() / src.size(0));
-  int64_t total = n * D;
-  halo_push_add_kernel<<<(unsigned)((total + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
-      n, D, src.data_ptr<float>(), row0, home_rank.data_ptr<int>(), home_row.data_ptr<int>(), dst_ptrs.data_ptr<int64_t>());
+  const uint8_t* um = used.has_value() ? used->data_ptr<uint8_t>() : nullptr;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (D % 4 == 0 && (reinterpret_cast<uintptr_t>(src.data_ptr()) & 15) == 0) {
+    int64_t blocks = std::min<int64_t>((n + 7) / 8, 148 * 16);
+    halo_push_add_vec_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+        n, D / 4, reinterpret_cast<const float4*>(src.data_ptr<float>()), row0, home_rank.data_ptr<int>(),
+        home_row.data_ptr<int>(), dst_ptrs.data_ptr<int64_t>(), um);
+  } else {
+    halo_push_add_narrow_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+        n, D, src.data_ptr<float>(), row0, home_rank.data_ptr<int>(), home_row.data_ptr<int>(),
+        dst_ptrs.data_ptr<int64_t>(), um);
+  }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 }  // namespace nva
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
-  m.def("halo_push_add_rows(Tensor src, int row0, Tensor home_rank, Tensor home_row, Tensor dst_ptrs) -> ()", &nva::halo_push_add_rows);
+  m.def("halo_push_add_rows(Tensor src, int row0, Tensor home_rank, Tensor home_row, Tensor dst_ptrs, Tensor? used=None) -> ()", &nva::halo_push_add_rows);
 }

@@ -1,9 +1,10 @@
 # SPDX-License-Identifier: Apache-2.0
 """Domain decomposition: one large system over many GPUs.
 
-Two layers: a generic, backend-agnostic API (``DomainParallel`` / ``ShardedBatch`` / ``DistributedModel`` / ``MLIPSpec``;
-any model wrapper, NCCL or gloo) and the single-node peer-memory engine for the native MACE path
-(``slab_md.SlabDomainMD``: ghost features read from the owner GPU inside the convolution kernels).
+One API (``DomainParallel`` / ``ShardedBatch`` / ``DistributedModel`` / ``MLIPSpec``) with two transports behind it:
+``torch.distributed`` collectives for any model wrapper on NCCL or gloo, and, for the native MACE on the GPUs of one
+node, the peer-memory engine (``peer_halo.PeerHaloEngine``: ghost rows pulled from and returned to their owners by
+NVLink kernels over symmetric buffers; selected automatically, ``DomainConfig(peer_memory=False)`` switches it off).
 
 The generic layer evaluates a model either on a ghost layer as deep as its receptive field (nothing inside the model is
 touched) or, with ``MLIPSpec(refresh_per_layer=True)``, on a ghost layer one cutoff deep whose feature rows are
@@ -33,6 +34,7 @@ from nvalchemi_toolkit_b200.distributed.graph_padder import (COOPadder, DenseBat
                                                              cap_agreement_group, resolve_cap)
 from nvalchemi_toolkit_b200.distributed import helpers
 from nvalchemi_toolkit_b200.distributed.pipeline2d import DomainPipeline
+from nvalchemi_toolkit_b200.distributed.peer_halo import PeerFailure, PeerHaloEngine, build_pull_tables, peer_memory_available
 
 __all__ = ["DomainConfig", "HookScope", "StrategyKind", "SpatialPartitioner", "IndexPartitioner", "factor_grid", "MLIPSpec",
            "Consolidation", "get_spec", "register_spec", "HaloExchange", "ShardedBatch", "DistributedModel", "DistributedPipelineModel",
@@ -43,4 +45,5 @@ __all__ = ["DomainConfig", "HookScope", "StrategyKind", "SpatialPartitioner", "I
            "gather_replicate", "per_system_reduce", "StoragePolicy", "PlainShard", "HaloStoragePolicy",
            "RefreshOnlyHaloPolicy", "GraphParallelPolicy", "policy_to_dict", "policy_from_dict", "HaloDispatchMode",
            "current_dispatch", "OpAdapter", "FunctionAdapter", "MethodAdapter", "ModuleForwardAdapter", "AdapterRegistry",
-           "GraphPadder", "COOPadder", "DensePadder", "DenseBatchPadder", "resolve_cap", "cap_agreement_group"]
+           "GraphPadder", "COOPadder", "DensePadder", "DenseBatchPadder", "resolve_cap", "cap_agreement_group",
+           "PeerHaloEngine", "PeerFailure", "build_pull_tables", "peer_memory_available"]

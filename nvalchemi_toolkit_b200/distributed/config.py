@@ -35,6 +35,13 @@ class DomainConfig(BaseModel):
     grid_dims: tuple[int, int, int] | None = None
     scripted_marshal: bool = False
     migration_hysteresis: float | None = None  # None -> skin / 2; must stay below skin
+    #: Verlet skin of the neighbour list built over owned + ghost rows (None -> ``skin``).  ``skin`` sizes the ghost
+    #: layer and decides when ownership and ghost lists are rebuilt; a dense system can afford a list rebuilt every step
+    #: (0.0) while keeping a ghost layer that lasts many steps.
+    neighbor_skin: float | None = None
+    #: ghost rows through peer-mapped memory and this package's NVLink kernels (True), through ``torch.distributed``
+    #: collectives only (False), or peer memory whenever the model, device and process group allow it (None)
+    peer_memory: bool | None = None
 
     @model_validator(mode="after")
     def _defaults(self) -> "DomainConfig":
@@ -44,6 +51,10 @@ class DomainConfig(BaseModel):
             self.__dict__["ghost_width"] = self.cutoff + self.skin
         if self.migration_hysteresis is None:
             self.__dict__["migration_hysteresis"] = 0.5 * self.skin
+        if self.neighbor_skin is None:
+            self.__dict__["neighbor_skin"] = self.skin
+        if self.neighbor_skin > self.skin:
+            raise ValueError("neighbor_skin cannot exceed skin (the ghost layer must outlast the neighbour list)")
         if self.skin > 0 and not self.migration_hysteresis < self.skin:
             raise ValueError("migration_hysteresis must be smaller than skin")
         return self

@@ -83,16 +83,35 @@ class DistributedModel(nn.Module):
         self.spec = spec if spec is not None else model.distribution_spec(config.strategy)
         if self.spec is None:
             raise ValueError(f"{type(model).__name__} declares no distribution spec; pass spec=MLIPSpec(...)")
+        self.engine: Any = None
+        if spec is None and not own_halo and config.peer_memory is not False:
+            from nvalchemi_toolkit_b200.distributed.peer_halo import PeerHaloEngine, peer_memory_available
+
+            params = list(model.parameters()) if isinstance(model, nn.Module) else []
+            device = params[0].device if params else torch.device("cpu")
+            if peer_memory_available(model, device, group):
+                # ghost layer one cutoff (+ skin) deep, feature rows refreshed from the owners before every interaction
+                self.spec = self.spec.with_(name=self.spec.name + "_peer", refresh_per_layer=True)
+                self.engine = PeerHaloEngine(model, config, group, max_neighbors=max_neighbors)
+            elif config.peer_memory:
+                raise RuntimeError("peer_memory=True needs a float32 native MACE on CUDA under an NCCL group of >= 2 ranks")
         self.model_config = model.model_config
         nc = self.model_config.neighbor_config
-        self.neighbor_hook = NeighborListHook(nc, skin=config.skin, max_neighbors=max_neighbors) if nc is not None else None
+        self.neighbor_hook = NeighborListHook(nc, skin=config.neighbor_skin, max_neighbors=max_neighbors) if nc is not None else None
         if nc is not None and self.spec.requires_full_list and nc.half_list:
             raise ValueError("domain decomposition needs a full neighbour list (each owned row must be complete)")
         self._halo_builds = -1
         self.last_dispatch_stats: dict = {}
 
+    @property
+    def wants_local_periodic(self) -> bool:
+        """The peer-memory engine keeps uncut periodic dimensions periodic in the local cluster."""
+        return self.engine is not None
+
     def forward(self, sharded: ShardedBatch, **kwargs: Any) -> dict:
         spec = self.spec
+        if self.engine is not None:
+            return self.engine.forward(sharded, set(self.model_config.active_outputs))
         if spec.consolidation == Consolidation.REPLICATED:
             out = self.model(sharded.owned, **kwargs)
             return consolidate_outputs(dict(out), sharded, spec)

@@ -61,14 +61,22 @@ class DynamicsCoordinator:
         sums = torch.stack([(v * f).sum(), (v * v).sum(), (f * f).sum()])
         dist.all_reduce(sums, group=self.group)
         for key, val in zip(("vf", "vv", "ff"), sums):
-            s[key].fill_(float(val))
+            s[key].copy_(val.to(s[key].dtype).expand_as(s[key]))  # stays on the device: no host read
 
 
 class DomainParallel:
+    """Runs ``dynamics`` on one system split over the ranks of ``group``.
+
+    Usable as a context manager (``with DomainParallel(...) as dp:``); leaving the block releases the peer-mapped
+    buffers collectively.  ``async_migration`` (default) decides ghost-list rebuilds and atom migration from a flag that
+    was reduced during the previous step, so that no step waits for its own reduction
+    (reference ``nvalchemi/distributed/domain_parallel.py:259,313-315,500-524``)."""
+
     def __init__(self, dynamics: Any, config: DomainConfig, spec: MLIPSpec | None = None, group: Any = None,
-                 max_neighbors: int | None = None) -> None:
+                 max_neighbors: int | None = None, async_migration: bool = True) -> None:
         self.dynamics, self.config, self.group = dynamics, config, group
         self.rank, self.world = _world(group)
+        self.async_migration = bool(async_migration)
         from nvalchemi_toolkit_b200.models.pipeline import PipelineModelWrapper
 
         if isinstance(dynamics.model, PipelineModelWrapper):
@@ -83,10 +91,27 @@ class DomainParallel:
         self.sharded: ShardedBatch | None = None
         self._scoped: list[tuple[Any, DynamicsStage, HookScope]] = []
         self.num_rebuilds = 0
+        self.converged = False
+        self.health_check_every = 64  # steps between reads of the device-side rendezvous status word
+
+    def __enter__(self) -> "DomainParallel":
+        return self
+
+    def __exit__(self, *exc: Any) -> None:
+        self.close()
+
+    def close(self) -> None:
+        engine = getattr(self.model, "engine", None)
+        if engine is not None and engine.p2p is not None:
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            engine.p2p = None
+            engine._bound = None
 
     # ---- set-up ---------------------------------------------------------------
     def partition(self, batch: Batch) -> ShardedBatch:
-        self.sharded = ShardedBatch.from_batch(batch, self.config, self.spec, self.group)
+        self.sharded = ShardedBatch.from_batch(batch, self.config, self.spec, self.group,
+                                               local_periodic=getattr(self.model, "wants_local_periodic", False))
         self._sync_atom_ids()
         return self.sharded
 
@@ -116,13 +141,19 @@ class DomainParallel:
                 hook(ctx, stage)
 
     # ---- stepping -------------------------------------------------------------
-    def compute(self) -> dict:
+    def _rebuild(self) -> None:
+        self.sharded.rebuild()
+        self.num_rebuilds += 1
+        self._sync_atom_ids()
+        state = getattr(self.dynamics, "_state", None)
+        if state is not None and hasattr(self.dynamics, "_on_atoms_migrated"):
+            self.dynamics._on_atoms_migrated(self.sharded.owned)
+
+    def compute(self, check_rebuild: bool = True) -> dict:
         """Distributed forward; results are written into the owned batch like ``BaseDynamics.compute`` does."""
         sh, dyn = self.sharded, self.dynamics
-        if sh.needs_rebuild():
-            sh.rebuild()
-            self.num_rebuilds += 1
-            self._sync_atom_ids()
+        if check_rebuild and sh.needs_rebuild():
+            self._rebuild()
         out = self.model(sh)
         dyn._validate_model_outputs(out)
         owned = sh.owned
@@ -132,14 +163,30 @@ class DomainParallel:
                 continue
             if attr == "energy" and value.dim() == 1:
                 value = value.unsqueeze(-1)
-            owned[attr] = value
+            target = getattr(owned, attr, None)
+            if target is not None and target.shape == value.shape and target.dtype == value.dtype:
+                target.copy_(value)
+            else:
+                owned[attr] = value
         dyn._last_outputs = out
         return out
+
+    def _global_convergence(self, owned: Batch) -> bool:
+        """Every criterion must hold on every rank's atoms (one small MIN reduction and one host read per check)."""
+        hook = self.dynamics.convergence_hook
+        if hook is None or self.dynamics.step_count % max(1, hook.frequency) != 0:
+            return False
+        ok = hook.converged_mask(owned).all().to(torch.int32).reshape(1)
+        if self.world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        return bool(int(ok))
 
     def step(self) -> ShardedBatch:
         sh, dyn = self.sharded, self.dynamics
         if sh is None:
             raise RuntimeError("call partition(batch) first")
+        if self.async_migration and sh.consume_rebuild_check():
+            self._rebuild()  # may replace sh.owned (migration)
         dyn._ensure_state_initialized(sh.owned)
         for stage, fn in ((DynamicsStage.BEFORE_STEP, None), (DynamicsStage.BEFORE_PRE_UPDATE, "pre"),
                           (DynamicsStage.AFTER_PRE_UPDATE, None), (DynamicsStage.BEFORE_COMPUTE, "compute"),
@@ -150,11 +197,20 @@ class DomainParallel:
             if fn == "pre":
                 self.coordinator.before_pre_update(sh.owned)
                 dyn.pre_update(sh.owned)
+                if self.async_migration:
+                    sh.dispatch_rebuild_check()  # positions are final for this step; the flag is read at the next one
             elif fn == "compute":
-                self.compute()  # may replace sh.owned (migration); later stages see the new batch
+                self.compute(check_rebuild=not self.async_migration)
             elif fn == "post":
                 dyn.post_update(sh.owned)
+        self.converged = self._global_convergence(sh.owned)
+        if self.converged:
+            dyn._call_hooks(DynamicsStage.ON_CONVERGE, sh.owned)
+            self._call_scoped(DynamicsStage.ON_CONVERGE)
         dyn.step_count += 1
+        engine = getattr(self.model, "engine", None)
+        if engine is not None and dyn.step_count % self.health_check_every == 0:
+            engine.check()
         return sh
 
     def run(self, batch: Batch | ShardedBatch | None = None, n_steps: int | None = None) -> ShardedBatch:
@@ -172,6 +228,8 @@ class DomainParallel:
         try:
             for _ in range(n):
                 self.step()
+                if self.converged:
+                    break
         finally:
             self.dynamics._close_hooks()
         return self.sharded

@@ -5,8 +5,8 @@ Reference: ``nvalchemi/distributed/_core/halo_index.py``, ``_core/gather.py``, `
 ``ops.py:110-540`` (halo forward, backward fold, scatter correction).  Design here: a *plan* is rebuilt rarely (when
 the neighbour skin is exhausted) and records, per destination rank, which owned rows are sent and with which integer
 lattice shift; between rebuilds a refresh is one variable-size all-to-all of positions, and the reverse exchange adds
-ghost-row gradients into their owners.  The single-node fast path for the headline MD benchmark does not go through
-this module: it uses peer loads and NVLink reductions from kernels (``distributed/slab_md.py``).
+ghost-row gradients into their owners.  The peer-memory engine (``distributed/peer_halo.py``) derives its pull tables
+from the same plan and then moves rows with NVLink kernels instead of collectives.
 """
 from __future__ import annotations
 
@@ -108,9 +108,13 @@ class HaloExchange:
     describe them.  ``wrap_shift`` (integer lattice vector per owned atom) maps owned positions into the primary cell
     so that owned and ghost rows live in one consistent frame."""
 
-    def __init__(self, partitioner: SpatialPartitioner, ghost_width: float, group: Any = None) -> None:
+    def __init__(self, partitioner: SpatialPartitioner, ghost_width: float, group: Any = None,
+                 local_periodic: bool = False) -> None:
         self.part, self.width, self.group = partitioner, float(ghost_width), group
         self.rank, self.world = _world(group)
+        #: periodic dimensions that the rank grid does not cut keep their periodicity in the local cluster (the
+        #: neighbour search applies the images) instead of being unrolled into explicit ghost rows
+        self.local_periodic = bool(local_periodic)
         self.send_index: torch.Tensor | None = None
         self.send_shift: torch.Tensor | None = None
         self.send_splits: list[int] = []
@@ -123,6 +127,12 @@ class HaloExchange:
     @property
     def n_ghost(self) -> int:
         return sum(self.recv_splits)
+
+    @property
+    def local_pbc(self) -> torch.Tensor:
+        """``bool[3]``: dimensions in which the owned + ghost cluster is still periodic."""
+        part = self.part
+        return torch.tensor([self.local_periodic and bool(part.pbc[d]) and part.grid[d] == 1 for d in range(3)])
 
     def build(self, positions: torch.Tensor, global_ids: torch.Tensor) -> None:
         part, dev = self.part, positions.device
@@ -137,8 +147,9 @@ class HaloExchange:
         self.wrap_shift = wrap.to(torch.int32)
         w = [self.width / part.face[d] for d in range(3)]
         rng = []
+        keep = self.local_pbc
         for d in range(3):
-            if not bool(part.pbc[d]) or f.shape[0] == 0:
+            if not bool(part.pbc[d]) or f.shape[0] == 0 or bool(keep[d]):
                 rng.append(range(0, 1))
                 continue
             fmin, fmax = float(f[:, d].min()), float(f[:, d].max())
@@ -189,6 +200,10 @@ class HaloExchange:
     def forward(self, owned_rows: torch.Tensor) -> torch.Tensor:
         """Ghost rows of a node-level tensor (owners send ``owned_rows[send_index]``)."""
         return all_to_all_rows(owned_rows[self.send_index], self.send_splits, self.recv_splits, self.group)
+
+    def forward_packed(self, send_rows: torch.Tensor) -> torch.Tensor:
+        """Ghost rows from rows that are already in send order (one per entry of ``send_index``)."""
+        return all_to_all_rows(send_rows, self.send_splits, self.recv_splits, self.group)
 
     def forward_positions(self, positions: torch.Tensor, cell: torch.Tensor) -> torch.Tensor:
         """Ghost positions: owner positions plus the recorded lattice shift."""

@@ -1,0 +1,239 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Peer-memory halo engine: the native MACE evaluated on one rank's owned + ghost rows, with every ghost exchange done
+by this package's NVLink kernels over symmetric (peer-mapped) buffers.
+
+It is the fast backend of :class:`DistributedModel` for a :class:`ShardedBatch` decomposed by
+:class:`SpatialPartitioner` (any 3-D rank grid).  What the reference does with ``HaloStrategy`` + ShardTensor dispatch
+(``nvalchemi/distributed/strategy.py:680-911``, ``distributed/_core/particle_halo.py:279-368,557-638``,
+``distributed/output_consolidation.py:316-340``) becomes:
+
+* **plan** (rebuilt with the ghost lists, i.e. when the skin is exhausted): the send/receive plan of
+  :class:`HaloExchange` is turned into *pull tables*: for every ghost row its owner rank, its row on the owner and
+  its integer lattice shift.  Only the ranks that share ghosts exchange anything (row indices, 4 bytes per ghost);
+* **per step**: owned positions are written into the symmetric position buffer, a flag barrier orders them, the ghost
+  positions are pulled from the owners (P2P loads + shift), the neighbour list is built over owned + ghost rows with
+  rows for owned atoms only, and the network runs on the owned atoms.  Before each interaction the ghost rows of the
+  sender features are pulled from their owners (16-byte loads, one warp per row, only rows some local edge uses); in the
+  adjoint the gradients accumulated on ghost rows are returned with vector reductions.  Each edge is evaluated once (at
+  the owner of its receiver) and energies are sums over owned atoms, so no ``/ world_size`` bookkeeping exists;
+* **sums**: the energy (and the virial when stress is requested) is all-reduced in float64.
+
+No TMA is involved in any peer access; the buffers are touched with plain loads, stores and reductions only.
+"""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from nvalchemi_toolkit_b200 import neighbors as _nb
+from nvalchemi_toolkit_b200.distributed.graph_padder import cap_agreement_group, resolve_cap
+from nvalchemi_toolkit_b200.ops._native_counter import ops as _nops
+
+
+class PeerFailure(RuntimeError):
+    """A peer did not reach a device-side rendezvous within the bounded wait."""
+
+
+def peer_memory_available(wrapper: Any, device: torch.device, group: Any) -> bool:
+    """Can this (model, device, process group) use the peer-memory engine?"""
+    from nvalchemi_toolkit_b200.models.mace.wrapper import MACEWrapper
+    from nvalchemi_toolkit_b200.ops import _native
+
+    if not (dist.is_available() and dist.is_initialized()) or device.type != "cuda":
+        return False
+    if dist.get_world_size(group) < 2 or dist.get_backend(group) != "nccl":
+        return False
+    if not isinstance(wrapper, MACEWrapper) or wrapper.model.backend == "torch" or wrapper.training:
+        return False
+    if next(wrapper.model.parameters()).dtype != torch.float32:
+        return False
+    return _native.available()
+
+
+def build_pull_tables(sharded: Any) -> dict[str, torch.Tensor]:
+    """Pull tables of a sharded batch's ghost plan (pure ``torch`` + the plan's own exchanges; any backend).
+
+    ``home_rank [G] int32`` / ``home_row [G] int32``: owner rank of every ghost row and its row among the owner's atoms;
+    ``ghost_image [G, 3]``: lattice image to add (times the cell) to the owner's row *as the owner stores it*, i.e. in
+    the owner's frame ``positions + wrap_image @ cell``; ``wrap_image [N_owned, 3]``: this rank's own frame."""
+    halo = sharded.halo
+    n = sharded.n_owned
+    dev = sharded.owned.positions.device
+    image = halo.send_shift - halo.wrap_shift[halo.send_index]  # image relative to the owner's own frame
+    return {
+        "home_rank": halo.ghost_owner_rank.to(torch.int32).contiguous(),
+        "home_row": halo.forward(torch.arange(n, dtype=torch.int32, device=dev)).contiguous(),
+        "ghost_image": halo.forward_packed(image.to(torch.float32).contiguous()).contiguous(),
+        "wrap_image": halo.wrap_shift.to(torch.float32).contiguous(),
+    }
+
+
+class PeerHaloEngine:
+    """Symmetric arena, pull tables and the per-step evaluation for one ``ShardedBatch``."""
+
+    #: rows are pulled / returned in bulk once per layer (the convolution kernels then work on local memory)
+    prefetch = True
+
+    def __init__(self, wrapper: Any, config: Any, group: Any = None, max_neighbors: int | None = None) -> None:
+        self.wrapper, self.model, self.config = wrapper, wrapper.model, config
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.cutoff = float(self.model.r_max)
+        self.neighbor_skin = float(config.neighbor_skin)
+        self.max_neighbors = max_neighbors or _nb.estimate_max_neighbors(self.cutoff + self.neighbor_skin)
+        self.p2p: Any = None
+        self.cap_rows = 0
+        self._caps: dict[str, int] = {}
+        self._bound: tuple[int, int] | None = None
+        self.n_owned = self.n_ghost = 0
+        self._nl: tuple | None = None
+        self._nl_ref: torch.Tensor | None = None
+        self._csr: Any = None
+        self.num_list_builds = 0
+        self.last_stats: dict[str, int] = {}
+
+    # ------------------------------------------------------------------ dd view consumed by ``native.forward``
+    @property
+    def n_local(self) -> int:
+        return self.n_owned + self.n_ghost
+
+    @property
+    def gpos(self) -> torch.Tensor:
+        return self.gpos_buf
+
+    def feature_buffer(self, key: str, shape: tuple[int, ...]) -> tuple[torch.Tensor, torch.Tensor]:
+        buf, ptrs = self.feat[key]
+        return buf[: shape[0]], ptrs
+
+    def barrier(self) -> None:
+        self.p2p.barrier()
+
+    # ------------------------------------------------------------------ capacity / plan
+    def _ensure_capacity(self, device: torch.device) -> None:
+        """Row capacity agreed over the ranks (grow-only, bucketed); a new arena is a collective allocation."""
+        from nvalchemi_toolkit_b200.parallel.symmetric import P2PContext
+
+        with cap_agreement_group(self.group, device):
+            cap = resolve_cap(self._caps, "rows", self.n_owned + self.n_ghost, initial_factor=1.2, stride=1024)
+        if self.p2p is not None and cap <= self.cap_rows:
+            return
+        self.cap_rows = cap
+        cfg = self.model.config
+        C = cfg.channels
+        widths = [sum(2 * l + 1 for l in ip.l_in) for ip in self.model.interactions]
+        floats = cap * (3 + 3 + sum(w * C for w in widths) + sum(w * C for w in widths[1:]))
+        self.p2p = None  # release the previous arena before asking for a larger one
+        self.p2p = P2PContext(4 * floats + 256 * (4 + 2 * len(widths)) + (1 << 16), device, self.group)
+        a = self.p2p.arena
+        self.pos_buf, self.pos_ptrs = a.alloc((cap, 3))
+        self.gpos_buf, self.gpos_ptrs = a.alloc((cap, 3))
+        self.feat = {}
+        for li, w in enumerate(widths):
+            self.feat[f"u{li}"] = a.alloc((cap, w, C))
+            if li > 0:
+                self.feat[f"du{li}"] = a.alloc((cap, w, C))
+
+    def _bind(self, sharded: Any) -> None:
+        halo = sharded.halo
+        key = (id(sharded), halo.num_builds)
+        if key == self._bound:
+            return
+        owned = sharded.owned
+        dev = owned.positions.device
+        self.n_owned, self.n_ghost = sharded.n_owned, halo.n_ghost
+        self._ensure_capacity(dev)
+        n, ng = self.n_owned, self.n_ghost
+        tables = build_pull_tables(sharded)
+        self.ghost_home_rank, self.ghost_home_row = tables["home_rank"], tables["home_row"]
+        self.ghost_image, self.wrap_image = tables["ghost_image"], tables["wrap_image"]
+        self.ghost_shift = torch.empty(ng, 3, dtype=torch.float32, device=dev)
+        z_owned = owned.atomic_numbers
+        z_ghost = sharded._ghost_static[id(halo)]["atomic_numbers"]
+        self.species = self.model.species_index(z_owned)
+        self.species_local = torch.cat([self.species, self.model.species_index(z_ghost)]).contiguous()
+        self.batch_idx = torch.zeros(n + ng, dtype=torch.int32, device=dev)
+        self.batch_ptr = torch.tensor([0, n + ng], dtype=torch.int32, device=dev)
+        self.batch_long = torch.zeros(n + ng, dtype=torch.long, device=dev)
+        self.pbc = halo.local_pbc.reshape(1, 3).to(dev)
+        self.ghost_used = torch.zeros(ng, dtype=torch.uint8, device=dev)
+        self._nl = self._nl_ref = self._csr = None
+        self._sums = torch.zeros(10, dtype=torch.float64, device=dev)
+        self._bound = key
+
+    # ------------------------------------------------------------------ neighbour list over owned + ghost rows
+    def _neighbors(self, pos_local: torch.Tensor, cell: torch.Tensor) -> Any:
+        from nvalchemi_toolkit_b200.models.mace import native
+
+        n, n_local = self.n_owned, pos_local.shape[0]
+        skin = self.neighbor_skin
+        if self._csr is not None and skin > 0.0:
+            moved = (pos_local - self._nl_ref).pow(2).sum(-1).max() > (0.5 * skin) ** 2
+            if not bool(moved):  # one host read per step: the price of a list that is reused
+                return self._csr
+        k = self.max_neighbors
+        while True:
+            if self._nl is None or self._nl[0].shape != (n, k):
+                self._nl = (torch.empty(n, k, dtype=torch.int32, device=pos_local.device),
+                            torch.empty(n, dtype=torch.int32, device=pos_local.device),
+                            torch.empty(n, k, 3, dtype=torch.int32, device=pos_local.device))
+            nm, num, sh = _nb.neighbor_matrix(pos_local, cell, self.pbc, self.batch_idx, self.batch_ptr, self.cutoff + skin, k,
+                                              False, out=self._nl, num_rows=n)
+            csr = native.build_csr(nm, num, sh)
+            if csr.max_count <= k:
+                break
+            k = self.max_neighbors = ((int(csr.max_count * 1.25) + 15) // 16) * 16
+        self.ghost_used.zero_()
+        _nops.mark_used_senders(csr.esend, csr.num_edges, n, self.ghost_used)
+        self._csr = csr
+        self._nl_ref = pos_local.clone() if skin > 0.0 else None
+        self.num_list_builds += 1
+        return csr
+
+    # ------------------------------------------------------------------ one evaluation
+    def forward(self, sharded: Any, active: set[str]) -> dict[str, torch.Tensor | None]:
+        from nvalchemi_toolkit_b200.models.mace import native
+
+        self._bind(sharded)
+        owned = sharded.owned
+        n, ng = self.n_owned, self.n_ghost
+        cell = owned.cell.reshape(3, 3).to(torch.float32)
+        # owned positions in this rank's frame; ghost images relative to the owners' frames
+        torch.addmm(owned.positions.detach(), self.wrap_image, cell, out=self.pos_buf[:n])
+        if ng:
+            torch.matmul(self.ghost_image, cell, out=self.ghost_shift)
+        self.p2p.barrier()  # every rank's owned rows are in place (and last step's readers are done)
+        _nops.halo_pull_rows(self.pos_buf, n, self.ghost_home_rank, self.ghost_home_row, self.ghost_shift, self.pos_ptrs)
+        pos_local = self.pos_buf[: n + ng]
+        cell3 = cell.reshape(1, 3, 3).contiguous()
+        csr = self._neighbors(pos_local, cell3)
+        want_f, want_s = "forces" in active, "stress" in active
+        out = native.forward(self.model, {"positions": pos_local, "cell": cell3, "_csr": csr}, self.species,
+                             self.batch_long, 1, want_f or want_s, want_s, dd=self)
+        sums = self._sums
+        sums.zero_()
+        sums[0:1] = out["energy"].double()
+        if want_s:
+            sums[1:10] = out["virial"].double().reshape(9)
+        dist.all_reduce(sums, group=self.group)
+        res: dict[str, torch.Tensor | None] = {"energy": sums[0:1].to(torch.float32).reshape(1, 1).clone(),
+                                                "atomic_energies": out["node_energy"]}
+        if want_f:
+            res["forces"] = out["forces"].clone()
+        if want_s:
+            vol = torch.linalg.det(cell.double()).abs()
+            virial = sums[1:10].reshape(1, 3, 3)
+            res["virial"] = virial.to(torch.float32)
+            res["stress"] = (-virial / vol).to(torch.float32)
+        self.last_stats = {"n_owned": n, "n_ghost": ng, "n_edges": csr.num_edges}
+        return res
+
+    def status(self) -> int:
+        """0 while every device-side rendezvous completed within its bounded wait (one host read)."""
+        return 0 if self.p2p is None else self.p2p.status()
+
+    def check(self) -> None:
+        code = self.status()
+        if code:
+            raise PeerFailure(f"rank {self.rank}: peer {code - 100} missed a device-side rendezvous")

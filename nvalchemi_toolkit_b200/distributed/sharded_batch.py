@@ -44,7 +44,8 @@ def _make_batch(node: dict[str, torch.Tensor], system: dict[str, torch.Tensor], 
 
 class ShardedBatch:
     def __init__(self, owned: Batch, global_ids: torch.Tensor, n_global: int, partitioner: SpatialPartitioner,
-                 config: DomainConfig, spec: MLIPSpec | None = None, group: Any = None) -> None:
+                 config: DomainConfig, spec: MLIPSpec | None = None, group: Any = None,
+                 local_periodic: bool = False) -> None:
         if owned.num_graphs != 1:
             raise ValueError("domain decomposition shards ONE system; batch many small systems instead of sharding them")
         self.owned, self.global_ids, self.n_global = owned, global_ids, int(n_global)
@@ -55,17 +56,21 @@ class ShardedBatch:
             width = max(width, spec.ghost_width(config.cutoff, config.skin)) if spec.message_passes > 0 else 0.0
         if width > 0.0 and self.world > 1:
             width += config.migration_hysteresis  # owned atoms may sit this far outside their owner's box
-        self.halo = HaloExchange(partitioner, width, group)
+        self.local_periodic = bool(local_periodic)
+        self.halo = HaloExchange(partitioner, width, group, local_periodic=self.local_periodic)
         self._extra_halos: dict[float, HaloExchange] = {}
         self._ref_positions: torch.Tensor | None = None
         self._ghost_static: dict[int, dict[str, torch.Tensor]] = {}
         self.num_migrated = 0
+        self._flag_host: torch.Tensor | None = None
+        self._flag_event: Any = None
+        self._flag_pending = False
         self.rebuild(migrate=False)
 
     # ---- construction --------------------------------------------------------
     @classmethod
-    def from_batch(cls, batch: Batch, config: DomainConfig, spec: MLIPSpec | None = None, group: Any = None
-                   ) -> "ShardedBatch":
+    def from_batch(cls, batch: Batch, config: DomainConfig, spec: MLIPSpec | None = None, group: Any = None,
+                   local_periodic: bool = False) -> "ShardedBatch":
         """Every rank passes the same (replicated) single-system batch and keeps the atoms inside its sub-domain."""
         rank, world = _world(group)
         cell = batch.cell.reshape(3, 3)
@@ -78,7 +83,7 @@ class ShardedBatch:
             raise RuntimeError(f"rank {rank} owns no atoms; use fewer ranks or set require_nondegenerate=False")
         node = {k: v[mine] for k, v in _node_fields(batch).items()}
         owned = _make_batch(node, _system_fields(batch), batch)
-        return cls(owned, mine.to(torch.int64), batch.num_nodes, part, config, spec, group)
+        return cls(owned, mine.to(torch.int64), batch.num_nodes, part, config, spec, group, local_periodic=local_periodic)
 
     # ---- views ---------------------------------------------------------------
     @property
@@ -114,7 +119,7 @@ class ShardedBatch:
             raise ValueError("a member halo cannot be wider than the sharded batch's own halo")
         key = round(width, 9)
         if key not in self._extra_halos:
-            halo = HaloExchange(self.partitioner, width, self.group)
+            halo = HaloExchange(self.partitioner, width, self.group, local_periodic=self.local_periodic)
             halo.build(self.owned.positions.detach(), self.global_ids)
             self._extra_halos[key] = halo
             self._ghost_static[id(halo)] = self._static_for(halo)
@@ -133,7 +138,7 @@ class ShardedBatch:
         for k, ghost in self._ghost_static[id(halo)].items():
             node[k] = torch.cat([getattr(self.owned, k), ghost])
         system = {k: v for k, v in _system_fields(self.owned).items() if k in ("cell", "total_charge", "spin")}
-        system["pbc"] = torch.zeros(1, 3, dtype=torch.bool, device=pos.device)
+        system["pbc"] = halo.local_pbc.reshape(1, 3).to(pos.device)
         weights = torch.zeros(allpos.shape[0], dtype=pos.dtype, device=pos.device)
         weights[: self.n_owned] = 1.0
         node["energy_weights"] = weights
@@ -156,6 +161,44 @@ class ShardedBatch:
             moved = moved.to(torch.float32)
             dist.all_reduce(moved, op=dist.ReduceOp.MAX, group=self.group)
         return bool(moved > 0)
+
+    # ---- asynchronous consensus (no step waits for the flag it raises) ---------
+    def dispatch_rebuild_check(self) -> None:
+        """Start the "has any atom anywhere moved more than skin / 2" reduction for the CURRENT positions; the answer
+        is read by :meth:`consume_rebuild_check` at the next step.  Reference:
+        ``nvalchemi/distributed/strategy.py:320-344`` (asynchronous all-reduce consumed one step later).
+
+        The flag trails the positions by one step: the forces of the step that raised it were evaluated with the old
+        ghost lists.  That is exact as long as two consecutive steps move no atom further than the remaining half of the
+        skin; keep ``skin`` above four times the largest per-step displacement."""
+        pos = self.owned.positions.detach()
+        if self._ref_positions is None or self._ref_positions.shape != pos.shape or self.config.skin <= 0.0:
+            flag = torch.ones(1, dtype=torch.int32, device=pos.device)
+        else:
+            d2 = (pos - self._ref_positions).pow(2).sum(-1)
+            lim = (0.5 * self.config.skin) ** 2
+            flag = (d2.max() > lim).to(torch.int32).reshape(1) if d2.numel() else torch.zeros(1, dtype=torch.int32, device=pos.device)
+        if self.world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+        if pos.is_cuda:
+            if self._flag_host is None:
+                self._flag_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._flag_host.copy_(flag, non_blocking=True)
+            self._flag_event = torch.cuda.Event()
+            self._flag_event.record()
+        else:
+            self._flag_host = flag.clone()
+            self._flag_event = None
+        self._flag_pending = True
+
+    def consume_rebuild_check(self) -> bool:
+        """Result of the last :meth:`dispatch_rebuild_check` (False when none is pending)."""
+        if not self._flag_pending:
+            return False
+        self._flag_pending = False
+        if self._flag_event is not None:
+            self._flag_event.synchronize()
+        return bool(int(self._flag_host[0]))
 
     def rebuild(self, migrate: bool = True) -> None:
         """Re-derive ownership (with hysteresis), move rows that changed owner, and rebuild the ghost plan."""
@@ -181,6 +224,7 @@ class ShardedBatch:
             halo.build(self.owned.positions.detach(), self.global_ids)
             self._ghost_static[id(halo)] = self._static_for(halo)
         self._ref_positions = self.owned.positions.detach().clone()
+        self._flag_pending = False
 
     # ---- gathering -----------------------------------------------------------
     def gather(self, dst: int | None = None) -> Batch | None:

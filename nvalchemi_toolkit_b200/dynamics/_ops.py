@@ -172,12 +172,14 @@ def _remove_rotations(velocities, positions, masses, batch_idx, m: int) -> None:
 # ------------------------------------------------------------------------ FIRE
 def fire_step(positions, velocities, forces, masses, alpha, dt, n_steps_positive, alpha_start, f_alpha, dt_min, dt_max,
               maxstep, n_min, f_dec, f_inc, uphill_flag, *, vf=None, vv=None, ff=None, batch_idx=None,
-              compute_reductions: bool = True) -> None:
+              compute_reductions: bool = True, reduce_max=None) -> None:
     """One FIRE iteration (power test, velocity mixing, adaptive ``dt``/``alpha``, kick, capped drift).
 
     With ``compute_reductions=False`` the caller supplies ``vf, vv, ff`` already summed (for example
     across ranks of a domain decomposition), mirroring the reference seam
-    (``nvalchemi/dynamics/_ops/fire.py:245-363``)."""
+    (``nvalchemi/dynamics/_ops/fire.py:245-363``).  ``reduce_max`` (a callable ``Tensor -> Tensor``) is applied to the
+    per-system largest displacement before the step-length cap, so that all ranks holding parts of one system scale
+    their drift alike."""
     m = alpha.shape[0]
     dev, dtype = positions.device, positions.dtype
     if batch_idx is None:
@@ -186,9 +188,15 @@ def fire_step(positions, velocities, forces, masses, alpha, dt, n_steps_positive
     vv = vv if vv is not None else torch.zeros(m, dtype=dtype, device=dev)
     ff = ff if ff is not None else torch.zeros(m, dtype=dtype, device=dev)
     if _nat(positions):
-        _nops._fire_step_op(positions, velocities, forces.contiguous(), masses, alpha, dt, alpha_start,
-                                          f_alpha, dt_min, dt_max, maxstep, n_steps_positive, n_min, f_dec, f_inc,
-                                          uphill_flag, vf, vv, ff, _i32(batch_idx), compute_reductions)
+        args = (positions, velocities, forces.contiguous(), masses, alpha, dt, alpha_start, f_alpha, dt_min, dt_max, maxstep,
+                n_steps_positive, n_min, f_dec, f_inc, uphill_flag, vf, vv, ff, _i32(batch_idx), compute_reductions)
+        if reduce_max is None:
+            _nops._fire_step_op(*args)
+        else:
+            mx = torch.zeros(m, dtype=torch.float32, device=dev)
+            _nops._fire_step_op(*args, mx, 1)
+            mx.copy_(reduce_max(mx))
+            _nops._fire_step_op(*args, mx, 2)
         return
     b = batch_idx.long()
     if compute_reductions:
@@ -208,6 +216,8 @@ def fire_step(positions, velocities, forces, masses, alpha, dt, n_steps_positive
     dr = h * velocities
     dn = dr.norm(dim=-1)
     mx = torch.zeros(m, dtype=dn.dtype, device=dev).scatter_reduce(0, b, dn, "amax", include_self=True)
+    if reduce_max is not None:
+        mx = reduce_max(mx)
     scale = torch.where(mx > maxstep, maxstep / mx.clamp_min(1e-30), torch.ones_like(mx))
     positions.add_(scale[b].unsqueeze(-1) * dr)
 

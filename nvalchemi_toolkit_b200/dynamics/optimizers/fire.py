@@ -33,6 +33,7 @@ class FIRE(BaseDynamics):
         self.alpha_start, self.f_alpha = alpha_start, f_alpha
         self._uphill_init = uphill
         self.compute_reductions = True  # a domain-decomposition coordinator supplies global sums instead
+        self.reduce_max = None          # ... and the cross-rank maximum for the step-length cap
 
     def _make_new_state(self, n: int, template_batch: Batch) -> dict[str, torch.Tensor]:
         dev, dtype = template_batch.device, template_batch.positions.dtype
@@ -59,7 +60,7 @@ class FIRE(BaseDynamics):
         _ops.fire_step(batch.positions, batch.velocities, batch.forces, batch.atomic_masses, s["alpha"], s["dt"],
                        s["n_steps_positive"], s["alpha_start"], s["f_alpha"], s["dt_min"], s["dt_max"], s["maxstep"],
                        s["n_min"], s["f_dec"], s["f_inc"], s["uphill_flag"], vf=s["vf"], vv=s["vv"], ff=s["ff"],
-                       batch_idx=batch.batch_idx, compute_reductions=self.compute_reductions)
+                       batch_idx=batch.batch_idx, compute_reductions=self.compute_reductions, reduce_max=self.reduce_max)
 
     def post_update(self, batch: Batch) -> None:
         pass

@@ -365,6 +365,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
     hr = dd.home_rank if dd is not None and not pull else None
     hw = dd.home_row if dd is not None and not pull else None
     n_rows = dd.n_local if pull else n  # rows of the feature / gradient buffers the kernels see
+    used = getattr(dd, "ghost_used", None) if pull else None  # ghost rows that some local edge references
     if dd is not None:
         dd.gpos.zero_()
 
@@ -406,7 +407,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
                 du.zero_()
             dd.barrier()  # every rank's u (and zeroed du / gradient buffers) is in place before peers touch it
             if pull:
-                ops.halo_pull_rows(u, n, dd.ghost_home_rank, dd.ghost_home_row, None, u_ptrs)
+                ops.halo_pull_rows(u, n, dd.ghost_home_rank, dd.ghost_home_row, None, u_ptrs, used)
                 pull_ptrs = (u_ptrs, du_ptrs)
                 u_ptrs = du_ptrs = None  # the convolution kernels read and write local rows only
         else:
@@ -542,9 +543,9 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
             # return what was accumulated on ghost rows to the owners, once per row
             dd.barrier()  # owners finished their own accumulation
             if li > 0:
-                ops.halo_push_add_rows(du, n, dd.ghost_home_rank, dd.ghost_home_row, du_ptrs)
+                ops.halo_push_add_rows(du, n, dd.ghost_home_rank, dd.ghost_home_row, du_ptrs, used)
             if li == 0:
-                ops.halo_push_add_rows(grad_pos[:dd.n_local], n, dd.ghost_home_rank, dd.ghost_home_row, dd.gpos_ptrs)
+                ops.halo_push_add_rows(grad_pos[:dd.n_local], n, dd.ghost_home_rank, dd.ghost_home_row, dd.gpos_ptrs, used)
         if dd is not None:
             dd.barrier()  # feature / position gradients pushed by peers have landed
         if li > 0 and dd is not None:

@@ -46,8 +46,12 @@ def cell_and_pbc(batch: Batch) -> tuple[torch.Tensor, torch.Tensor]:
 def neighbor_matrix(positions: torch.Tensor, cell: torch.Tensor, pbc: torch.Tensor, batch_idx: torch.Tensor,
                     batch_ptr: torch.Tensor, cutoff: float, max_neighbors: int, half_list: bool = False,
                     out: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
-                    rebuild_flags: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Dense neighbour search.  Returns ``(matrix [N,K] int32 padded with N, counts [N] int32, shifts [N,K,3] int32)``."""
+                    rebuild_flags: torch.Tensor | None = None, num_rows: int | None = None
+                    ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Dense neighbour search.  Returns ``(matrix [N,K] int32 padded with N, counts [N] int32, shifts [N,K,3] int32)``.
+
+    With ``num_rows`` only the first ``num_rows`` atoms get a neighbour row (all atoms remain candidates): under domain
+    decomposition ghost atoms send but do not receive, so their rows are never read."""
     n = positions.shape[0]
     dev = positions.device
     if out is None:
@@ -61,7 +65,13 @@ def neighbor_matrix(positions: torch.Tensor, cell: torch.Tensor, pbc: torch.Tens
     if _native.require(positions):
         _nops.neighbor_matrix_build(positions.detach().contiguous(), cell, pbc, batch_idx.to(torch.int32),
                                                   batch_ptr.to(torch.int32), float(cutoff), bool(half_list), nm, num, sh,
-                                                  rebuild_flags)
+                                                  rebuild_flags, -1 if num_rows is None else int(num_rows))
+        return nm, num, sh
+    if num_rows is not None and num_rows < n:
+        full = _neighbor_matrix_torch(positions.detach(), cell, pbc, batch_idx, cutoff, torch.full((n, nm.shape[1]), n, dtype=torch.int32, device=dev),
+                                      torch.zeros(n, dtype=torch.int32, device=dev),
+                                      torch.zeros(n, nm.shape[1], 3, dtype=torch.int32, device=dev), half_list)
+        nm[:num_rows], num[:num_rows], sh[:num_rows] = full[0][:num_rows], full[1][:num_rows], full[2][:num_rows]
         return nm, num, sh
     return _neighbor_matrix_torch(positions.detach(), cell, pbc, batch_idx, cutoff, nm, num, sh, half_list)
 
