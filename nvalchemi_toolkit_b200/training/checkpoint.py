@@ -1,22 +1,27 @@
 # SPDX-License-Identifier: Apache-2.0
-"""Manifest-based training checkpoints without pickle-dependent structure.
+"""Manifest-based training checkpoints without pickle-dependent structure, in the reference's on-disk layout
+(``nvalchemi/training/_checkpoint.py:21-51,175-193,495-532,915-933``)::
 
-Directory layout (same as the reference, ``nvalchemi/training/_checkpoint.py:21-51``)::
+    <dir>/manifest.json                          schema_version, checkpoint_index, component name lists, associations
+    <dir>/models/<name>/spec.json                {"cls_path", "timestamp", constructor kwargs...}
+    <dir>/models/<name>/checkpoints/<N>.pt       state_dict only
+    <dir>/optimizers/<model>_optimizer[_i]/spec.json, checkpoints/<N>.pt
+    <dir>/schedulers/<model>_scheduler[_i]/spec.json, checkpoints/<N>.pt
+    <dir>/hooks/checkpoints/<N>.pt               {"<module>.<QualName>:<occurrence>": state} of checkpointable hooks
+    <dir>/strategy.json                          latest strategy metadata (recipe + the five restart counters)
+    <dir>/strategy/checkpoints/<N>.json          the same per checkpoint index
 
-    <dir>/manifest.json
-    <dir>/models/<name>/spec.json              constructor spec (class path + JSON kwargs)
-    <dir>/models/<name>/checkpoints/<step>.pt  state_dict only
-    <dir>/optimizers/<i>/spec.json, checkpoints/<step>.pt
-    <dir>/schedulers/<i>/...
-    <dir>/hooks/<name>/<step>.pt               states of CheckpointableHook hooks
-    <dir>/strategy/<step>.json                 counters and the strategy spec
-
-``manifest.json`` lists components, the available steps and ``latest``.  Wrapped modules (FSDP) are rejected: only
-plain / DDP modules are supported, as in the reference (``_checkpoint.py:127-157``)."""
+``N`` is the checkpoint index (auto-incremented from the manifest).  ``associations`` maps a model name to its
+``optimizers`` / ``schedulers`` component names, the ``scheduler_optimizers`` edges and the ``optimizer_parameter_names``
+each optimizer holds.  Every ``.pt`` file is read with ``weights_only=True``: hook states must consist of tensors and
+plain containers.  Wrapped modules (FSDP) are rejected: only plain / DDP modules are supported, as in the reference
+(``_checkpoint.py:127-157``).  Directories written by the earlier layout of this package (``latest`` / ``steps`` in the
+manifest) are still readable."""
 from __future__ import annotations
 
 import json
 import os
+from datetime import datetime, timezone
 from pathlib import Path
 from typing import Any
 
@@ -25,6 +30,10 @@ import torch
 from nvalchemi_toolkit_b200._serialization import to_jsonable, type_to_path
 
 SCHEMA_VERSION = 1
+HOOK_DIR = Path("hooks") / "checkpoints"
+STRATEGY_FILE = "strategy.json"
+STRATEGY_DIR = Path("strategy") / "checkpoints"
+_COUNTERS = ("step_count", "global_step_count", "batch_count", "epoch_count", "epoch_step_count")
 
 
 def _unwrap(module: torch.nn.Module) -> torch.nn.Module:
@@ -34,93 +43,288 @@ def _unwrap(module: torch.nn.Module) -> torch.nn.Module:
     return module.module if isinstance(module, torch.nn.parallel.DistributedDataParallel) else module
 
 
+def _now() -> str:
+    return datetime.now(timezone.utc).isoformat()
+
+
 def model_spec(module: torch.nn.Module) -> dict[str, Any]:
+    """Constructor spec of a model: ``cls_path`` + ``timestamp`` + JSON-able keyword arguments."""
     m = _unwrap(module)
     if hasattr(m, "checkpoint_spec"):
-        return m.checkpoint_spec()
-    return {"cls": type_to_path(type(m)), "kwargs": to_jsonable(getattr(m, "_init_kwargs", {}))}
+        raw = m.checkpoint_spec()
+        kwargs = raw.get("config", raw.get("kwargs", {}))
+        return {"cls_path": raw.get("cls_path", raw.get("cls")), "timestamp": _now(), **to_jsonable(kwargs)}
+    return {"cls_path": type_to_path(type(m)), "timestamp": _now(), **to_jsonable(getattr(m, "_init_kwargs", {}))}
+
+
+def _optimizer_spec(obj: Any) -> dict[str, Any]:
+    spec: dict[str, Any] = {"cls_path": type_to_path(type(obj)), "timestamp": _now()}
+    defaults = getattr(obj, "defaults", None)
+    if isinstance(defaults, dict):
+        spec.update({k: v for k, v in to_jsonable(defaults).items()
+                     if isinstance(v, (int, float, bool, str, list, type(None)))})
+    return spec
+
+
+def component_names(model_keys: list[str], kind: str) -> list[str]:
+    """``<model>_<kind>`` (``<model>_<kind>_<i>`` when a model has several), in the order of ``model_keys``."""
+    total: dict[str, int] = {}
+    for k in model_keys:
+        total[k] = total.get(k, 0) + 1
+    seen: dict[str, int] = {}
+    out = []
+    for k in model_keys:
+        i = seen.get(k, 0)
+        seen[k] = i + 1
+        out.append(f"{k}_{kind}" if total[k] == 1 else f"{k}_{kind}_{i}")
+    return out
+
+
+def hook_state_key(hook: object, occurrence: int) -> str:
+    return f"{type(hook).__module__}.{type(hook).__qualname__}:{occurrence}"
+
+
+def _checkpointable(hooks: Any):
+    for h in hooks or []:
+        children = getattr(h, "_hooks", None)
+        if isinstance(children, (list, tuple)):
+            yield from _checkpointable(children)
+        if callable(getattr(h, "state_dict", None)) and callable(getattr(h, "load_state_dict", None)):
+            yield h
+
+
+def _keyed_hooks(hooks: Any):
+    occ: dict[str, int] = {}
+    for h in _checkpointable(hooks):
+        cls = f"{type(h).__module__}.{type(h).__qualname__}"
+        i = occ.get(cls, 0)
+        occ[cls] = i + 1
+        yield hook_state_key(h, i), h
+
+
+def _plain(value: Any) -> Any:
+    """Hook state reduced to what ``weights_only=True`` can read back: tensors, numbers, strings, dicts, lists."""
+    if isinstance(value, torch.Tensor):
+        return value.detach().cpu().clone()
+    if isinstance(value, dict):
+        return {str(k): _plain(v) for k, v in value.items()}
+    if isinstance(value, (list, tuple)):
+        return [_plain(v) for v in value]
+    if value is None or isinstance(value, (bool, int, float, str)):
+        return value
+    raise TypeError(f"hook state holds a {type(value).__name__}; only tensors and plain containers can be checkpointed")
 
 
 class CheckpointManifest:
+    """``manifest.json``: reads the reference schema (and this package's earlier one), writes the reference schema."""
+
     def __init__(self, root: str | Path) -> None:
         self.root = Path(root)
         self.path = self.root / "manifest.json"
-        self.data: dict[str, Any] = {"schema_version": SCHEMA_VERSION, "models": [], "optimizers": [], "schedulers": [],
-                                     "hooks": [], "steps": [], "latest": None}
+        self.data: dict[str, Any] = {"schema_version": SCHEMA_VERSION, "checkpoint_index": -1, "models": [],
+                                     "optimizers": [], "schedulers": [], "associations": {}}
+        self.legacy = False
         if self.path.exists():
-            self.data = json.loads(self.path.read_text())
-            if self.data.get("schema_version", 0) > SCHEMA_VERSION:
-                raise ValueError("checkpoint written by a newer schema version")
+            raw = json.loads(self.path.read_text())
+            if raw.get("schema_version", 0) > SCHEMA_VERSION:
+                raise ValueError(f"checkpoint schema version {raw['schema_version']} is newer than supported ({SCHEMA_VERSION})")
+            if "checkpoint_index" not in raw and "latest" in raw:  # earlier layout of this package
+                self.legacy = True
+                raw["checkpoint_index"] = -1 if raw["latest"] is None else raw["latest"]
+            for key in ("models", "checkpoint_index"):
+                if key not in raw:
+                    raise ValueError(f"manifest.json lacks the required field '{key}'")
+            self.data.update(raw)
+            self.data["schema_version"] = SCHEMA_VERSION
+
+    @property
+    def checkpoint_index(self) -> int:
+        return int(self.data["checkpoint_index"])
+
+    def indices(self) -> list[int]:
+        """Checkpoint indices present on disk for the first model component."""
+        if self.legacy:
+            return sorted(int(s) for s in self.data.get("steps", []))
+        names = self.data["models"]
+        if not names:
+            return []
+        d = self.root / "models" / names[0] / "checkpoints"
+        return sorted(int(f.stem) for f in d.glob("*.pt")) if d.is_dir() else []
 
     def write(self) -> None:
         self.root.mkdir(parents=True, exist_ok=True)
+        out = {k: self.data[k] for k in ("schema_version", "checkpoint_index", "models", "optimizers", "schedulers",
+                                         "associations")}
+        for k in ("models", "optimizers", "schedulers"):
+            out[k] = sorted(out[k])
         tmp = self.path.with_suffix(".tmp")
-        tmp.write_text(json.dumps(self.data, indent=1))
+        tmp.write_text(json.dumps(out, indent=2))
         os.replace(tmp, self.path)  # atomic: a crash never leaves a half-written manifest
 
 
-def save_checkpoint(root: str | Path, step: int, models: dict[str, torch.nn.Module], optimizers: list, schedulers: list,
-                    hooks: list, strategy_meta: dict[str, Any]) -> Path:
+def infer_associations(models: dict[str, torch.nn.Module], optimizers: dict[str, Any], schedulers: dict[str, Any]
+                       ) -> dict[str, dict[str, Any]]:
+    """Model-centric linkage from object identity: an optimizer belongs to every model that owns one of its
+    parameters, a scheduler to the models of the optimizer it drives (reference ``_checkpoint.py:728-795``)."""
+    assoc: dict[str, dict[str, Any]] = {}
+    opt_models: dict[str, list[str]] = {}
+    for oname, opt in optimizers.items():
+        ids = {id(p) for g in opt.param_groups for p in g["params"]}
+        for mname, m in models.items():
+            named = [(n, p) for n, p in _unwrap(m).named_parameters() if id(p) in ids]
+            if not named:
+                continue
+            a = assoc.setdefault(mname, {"optimizers": [], "schedulers": []})
+            a["optimizers"].append(oname)
+            a.setdefault("optimizer_parameter_names", {})[oname] = [f"{mname}.{n}" for n, _ in named]
+            opt_models.setdefault(oname, []).append(mname)
+    for sname, sched in schedulers.items():
+        target = getattr(sched, "optimizer", None)
+        for oname, opt in optimizers.items():
+            if opt is target:
+                for mname in opt_models.get(oname, []):
+                    a = assoc.setdefault(mname, {"optimizers": [], "schedulers": []})
+                    a["schedulers"].append(sname)
+                    a.setdefault("scheduler_optimizers", {})[sname] = oname
+    return assoc
+
+
+def validate_checkpoint(root: str | Path, checkpoint_index: int | None = None) -> list[str]:
+    """Problems found in a checkpoint directory (empty list: consistent): missing specs or state files, associations
+    that name unknown components."""
     root = Path(root)
     man = CheckpointManifest(root)
+    idx = man.checkpoint_index if checkpoint_index is None else checkpoint_index
+    problems = []
+    for kind in ("models", "optimizers", "schedulers"):
+        for name in man.data[kind]:
+            d = root / kind / name
+            if not man.legacy and not (d / "spec.json").exists():
+                problems.append(f"{kind}/{name}: spec.json missing")
+            if not (d / "checkpoints" / f"{idx}.pt").exists():
+                problems.append(f"{kind}/{name}: checkpoints/{idx}.pt missing")
+    for mname, a in man.data.get("associations", {}).items():
+        if mname not in man.data["models"]:
+            problems.append(f"associations name an unknown model '{mname}'")
+        for kind in ("optimizers", "schedulers"):
+            for comp in a.get(kind, []):
+                if comp not in man.data[kind]:
+                    problems.append(f"associations of '{mname}' name an unknown {kind[:-1]} '{comp}'")
+    return problems
 
-    def put(kind: str, name: str, state: Any, spec: dict | None) -> None:
+
+def save_checkpoint(root: str | Path, step: int, models: dict[str, torch.nn.Module], optimizers: list, schedulers: list,
+                    hooks: list, strategy_meta: dict[str, Any], optimizer_keys: list[str] | None = None,
+                    checkpoint_index: int = -1) -> Path:
+    """Write one checkpoint.  ``optimizers`` / ``schedulers`` are the strategy's flat lists; ``optimizer_keys`` names
+    the model each optimizer belongs to (default: the first model).  ``checkpoint_index = -1`` auto-increments."""
+    root = Path(root)
+    man = CheckpointManifest(root)
+    if man.legacy:
+        raise ValueError(f"{root} holds a checkpoint in this package's earlier layout; save into a fresh directory")
+    index = man.checkpoint_index + 1 if checkpoint_index == -1 else int(checkpoint_index)
+    keys = list(optimizer_keys) if optimizer_keys is not None else [next(iter(models))] * len(optimizers)
+    opt_names = component_names(keys, "optimizer")
+    sched_names = component_names(keys, "scheduler")
+    opts = dict(zip(opt_names, optimizers))
+    scheds = {n: s for n, s in zip(sched_names, schedulers) if s is not None}
+
+    def put(kind: str, name: str, state: Any, spec: dict) -> None:
         d = root / kind / name
         (d / "checkpoints").mkdir(parents=True, exist_ok=True)
-        if spec is not None:
-            (d / "spec.json").write_text(json.dumps(spec, indent=1))
-        torch.save(state, d / "checkpoints" / f"{step}.pt")
+        spec_path = d / "spec.json"
+        if spec_path.exists():
+            old = json.loads(spec_path.read_text())
+            if {k: v for k, v in old.items() if k != "timestamp"} != {k: v for k, v in spec.items() if k != "timestamp"}:
+                raise ValueError(f"{kind}/{name}/spec.json disagrees with the component being saved")
+        else:
+            spec_path.write_text(json.dumps(spec, indent=2))
+        torch.save(state, d / "checkpoints" / f"{index}.pt")
         if name not in man.data[kind]:
             man.data[kind].append(name)
 
+    specs = {}
     for name, m in models.items():
-        put("models", name, _unwrap(m).state_dict(), model_spec(m))
-    for i, o in enumerate(optimizers):
-        put("optimizers", str(i), o.state_dict(), {"cls": type_to_path(type(o))})
-    for i, s in enumerate(schedulers):
-        if s is not None:
-            put("schedulers", str(i), s.state_dict(), {"cls": type_to_path(type(s))})
-    for h in hooks:
-        if hasattr(h, "state_dict") and hasattr(h, "load_state_dict"):
-            name = getattr(h, "checkpoint_name", type(h).__name__)
-            d = root / "hooks" / name
-            d.mkdir(parents=True, exist_ok=True)
-            torch.save(dict(h.state_dict()), d / f"{step}.pt")
-            if name not in man.data["hooks"]:
-                man.data["hooks"].append(name)
-    (root / "strategy").mkdir(parents=True, exist_ok=True)
-    (root / "strategy" / f"{step}.json").write_text(json.dumps(to_jsonable(strategy_meta), indent=1))
-    if step not in man.data["steps"]:
-        man.data["steps"].append(step)
-    man.data["latest"] = step
+        specs[name] = model_spec(m)
+        put("models", name, _unwrap(m).state_dict(), specs[name])
+    for name, o in opts.items():
+        put("optimizers", name, o.state_dict(), _optimizer_spec(o))
+    for name, s in scheds.items():
+        put("schedulers", name, s.state_dict(), {"cls_path": type_to_path(type(s)), "timestamp": _now()})
+    states = {key: _plain(dict(h.state_dict())) for key, h in _keyed_hooks(hooks)}
+    if states:
+        (root / HOOK_DIR).mkdir(parents=True, exist_ok=True)
+        torch.save(states, root / HOOK_DIR / f"{index}.pt")
+    meta = dict(to_jsonable(strategy_meta))
+    meta.setdefault("model_specs", specs)
+    payload = json.dumps(meta, indent=2)
+    (root / STRATEGY_FILE).write_text(payload)
+    (root / STRATEGY_DIR).mkdir(parents=True, exist_ok=True)
+    (root / STRATEGY_DIR / f"{index}.json").write_text(payload)
+    man.data["checkpoint_index"] = index
+    man.data["associations"] = infer_associations({k: m for k, m in models.items()}, opts, scheds)
     man.write()
     return root
 
 
-def load_checkpoint(root: str | Path, models: dict[str, torch.nn.Module], optimizers: list | None = None,
-                    schedulers: list | None = None, hooks: list | None = None, step: int | None = None,
-                    map_location: Any = "cpu", strict: bool = True) -> dict[str, Any]:
-    """Restores states in place and returns the strategy metadata (counters) of the chosen step."""
+def read_strategy_metadata(root: str | Path, checkpoint_index: int | None = None) -> dict[str, Any]:
     root = Path(root)
     man = CheckpointManifest(root)
-    step = man.data["latest"] if step is None else step
-    if step is None or step not in man.data["steps"]:
-        raise FileNotFoundError(f"no checkpoint for step {step} under {root}")
+    idx = man.checkpoint_index if checkpoint_index is None else checkpoint_index
+    if man.legacy:
+        return json.loads((root / "strategy" / f"{idx}.json").read_text())
+    f = root / STRATEGY_DIR / f"{idx}.json"
+    if not f.exists():
+        f = root / STRATEGY_FILE
+    return json.loads(f.read_text()) if f.exists() else {}
+
+
+def load_checkpoint(root: str | Path, models: dict[str, torch.nn.Module], optimizers: list | None = None,
+                    schedulers: list | None = None, hooks: list | None = None, step: int | None = None,
+                    map_location: Any = "cpu", strict: bool = True, optimizer_keys: list[str] | None = None
+                    ) -> dict[str, Any]:
+    """Restores states in place and returns the strategy metadata (counters) of the chosen checkpoint index
+    (``step``; default: the manifest's latest)."""
+    root = Path(root)
+    man = CheckpointManifest(root)
+    idx = man.checkpoint_index if step is None else int(step)
+    if idx < 0 or (man.indices() and idx not in man.indices()):
+        raise FileNotFoundError(f"no checkpoint with index {idx} under {root}")
+
+    def read(f: Path) -> Any:
+        return torch.load(f, map_location=map_location, weights_only=True)
+
     for name, m in models.items():
-        f = root / "models" / name / "checkpoints" / f"{step}.pt"
+        f = root / "models" / name / "checkpoints" / f"{idx}.pt"
         if f.exists():
-            _unwrap(m).load_state_dict(torch.load(f, map_location=map_location, weights_only=True), strict=strict)
-    for i, o in enumerate(optimizers or []):
-        f = root / "optimizers" / str(i) / "checkpoints" / f"{step}.pt"
+            _unwrap(m).load_state_dict(read(f), strict=strict)
+    optimizers, schedulers = list(optimizers or []), list(schedulers or [])
+    if man.legacy:
+        opt_names = [str(i) for i in range(len(optimizers))]
+        sched_names = [str(i) for i in range(len(schedulers))]
+    else:
+        keys = list(optimizer_keys) if optimizer_keys is not None else [next(iter(models))] * len(optimizers)
+        opt_names = component_names(keys, "optimizer")
+        sched_names = component_names(keys, "scheduler")  # the scheduler list is aligned with the optimizer list
+    for name, o in zip(opt_names, optimizers):
+        f = root / "optimizers" / name / "checkpoints" / f"{idx}.pt"
         if f.exists():
-            o.load_state_dict(torch.load(f, map_location=map_location, weights_only=True))
-    for i, s in enumerate(schedulers or []):
-        f = root / "schedulers" / str(i) / "checkpoints" / f"{step}.pt"
+            o.load_state_dict(read(f))
+    for name, s in zip(sched_names, schedulers):
+        f = root / "schedulers" / name / "checkpoints" / f"{idx}.pt"
         if s is not None and f.exists():
-            s.load_state_dict(torch.load(f, map_location=map_location, weights_only=True))
-    for h in hooks or []:
-        if hasattr(h, "load_state_dict"):
-            f = root / "hooks" / getattr(h, "checkpoint_name", type(h).__name__) / f"{step}.pt"
-            if f.exists():
-                h.load_state_dict(torch.load(f, map_location=map_location, weights_only=False))
-    return json.loads((root / "strategy" / f"{step}.json").read_text())
+            s.load_state_dict(read(f))
+    if man.legacy:
+        for h in hooks or []:
+            if hasattr(h, "load_state_dict"):
+                f = root / "hooks" / getattr(h, "checkpoint_name", type(h).__name__) / f"{idx}.pt"
+                if f.exists():
+                    h.load_state_dict(read(f))
+    else:
+        f = root / HOOK_DIR / f"{idx}.pt"
+        if f.exists():
+            saved = read(f)
+            for key, h in _keyed_hooks(hooks):
+                if key in saved:
+                    h.load_state_dict(saved[key])
+    return read_strategy_metadata(root, idx)

@@ -122,13 +122,13 @@ class TrainingStrategy(HookRegistryMixin):
         self.active_dataloader = dataloader
         self._run_hooks(TrainingStage.SETUP, None)
         dataloader = self.active_dataloader
-        self._optimizers, self._lr_schedulers, keys = setup_optimizers(self.models, self.optimizer_configs,
-                                                                       self.optimizer_parameter_filter)
+        self._optimizers, self._lr_schedulers, self._opt_keys = setup_optimizers(self.models, self.optimizer_configs,
+                                                                                 self.optimizer_parameter_filter)
         self._opt_cfgs = [c for k in self.optimizer_configs for c in self.optimizer_configs[k]]
         pending = getattr(self, "_pending_restore", None)
         if pending is not None:
             meta = ckpt.load_checkpoint(pending[0], self.models, self._optimizers, self._lr_schedulers, self.hooks,
-                                        step=pending[1], map_location=dev)
+                                        step=pending[1], map_location=dev, optimizer_keys=self._opt_keys)
             self._apply_meta(meta)
             self._pending_restore = None
         for k, m in self.models.items():
@@ -294,20 +294,16 @@ class TrainingStrategy(HookRegistryMixin):
         if get_rank(self.distributed_manager) != 0:
             return Path(directory)
         return ckpt.save_checkpoint(directory, self.step_count, self.models, self._optimizers, self._lr_schedulers,
-                                    self.hooks, self._meta())
+                                    self.hooks, self._meta(), optimizer_keys=getattr(self, "_opt_keys", None))
 
     def load_checkpoint(self, directory: str | Path, step: int | None = None) -> None:
         """Restore models, optimisers, schedulers, hook states and counters (optimisers are built on demand)."""
         if not self._setup_done:
             self._pending_restore = (directory, step)
-            man = ckpt.CheckpointManifest(directory)
-            s = man.data["latest"] if step is None else step
-            import json
-
-            self._apply_meta(json.loads((Path(directory) / "strategy" / f"{s}.json").read_text()))
+            self._apply_meta(ckpt.read_strategy_metadata(directory, step))
             return
         meta = ckpt.load_checkpoint(directory, self.models, self._optimizers, self._lr_schedulers, self.hooks, step=step,
-                                    map_location=self.devices[0])
+                                    map_location=self.devices[0], optimizer_keys=getattr(self, "_opt_keys", None))
         self._apply_meta(meta)
 
     restore_checkpoint = load_checkpoint

@@ -147,3 +147,58 @@ def test_fused_gradient_allreduce_matches_single_process():
         st.train_batch(Batch.from_data_list(data[4 * (step % 2): 4 * (step % 2) + 4]))
     for a, b in zip(res[0], st.models["main"].parameters()):
         assert torch.allclose(torch.tensor(a), b.detach().reshape(-1), atol=5e-3)  # Adam amplifies rounding of tiny gradients
+
+
+def test_checkpoint_layout_matches_reference_and_reads_a_reference_fixture(tmp_path):
+    """Field names and paths of the reference's layout: ``checkpoint_index`` / ``associations`` in the manifest, named
+    optimizer / scheduler components, ``hooks/checkpoints/N.pt``, ``strategy.json`` + ``strategy/checkpoints/N.json``."""
+    import json
+
+    from nvalchemi_toolkit_b200.training import checkpoint as ckpt
+
+    a = _strategy(num_epochs=1, hooks=[EMAHook(decay=0.9), CheckpointHook(tmp_path / "ck", every_n_epochs=1)])
+    a.run(_loader(_dataset()))
+    root = tmp_path / "ck"
+    man = json.loads((root / "manifest.json").read_text())
+    assert set(man) == {"schema_version", "checkpoint_index", "models", "optimizers", "schedulers", "associations"}
+    assert man["checkpoint_index"] == 0 and man["models"] == ["main"] and man["optimizers"] == ["main_optimizer"]
+    assoc = man["associations"]["main"]
+    assert assoc["optimizers"] == ["main_optimizer"] and assoc["optimizer_parameter_names"]["main_optimizer"]
+    spec = json.loads((root / "models" / "main" / "spec.json").read_text())
+    assert "cls_path" in spec and "timestamp" in spec
+    assert (root / "optimizers" / "main_optimizer" / "checkpoints" / "0.pt").exists()
+    assert (root / "hooks" / "checkpoints" / "0.pt").exists()
+    assert (root / "strategy.json").exists() and (root / "strategy" / "checkpoints" / "0.json").exists()
+    hook_states = torch.load(root / "hooks" / "checkpoints" / "0.pt", weights_only=True)  # no pickle-dependent objects
+    assert list(hook_states) == [f"{EMAHook.__module__}.EMAHook:0"]
+    assert ckpt.validate_checkpoint(root) == []
+
+    # a directory written by hand exactly as the reference lays it out
+    fix = tmp_path / "ref"
+    model = a.models["main"]
+    opt = a._optimizers[0]
+    for kind, name, state in (("models", "main", model.state_dict()), ("optimizers", "main_optimizer", opt.state_dict())):
+        d = fix / kind / name / "checkpoints"
+        d.mkdir(parents=True)
+        (fix / kind / name / "spec.json").write_text(json.dumps({"cls_path": "torch.nn.Linear", "timestamp": "2026-01-01T00:00:00+00:00"}))
+        torch.save(state, d / "3.pt")
+    (fix / "hooks" / "checkpoints").mkdir(parents=True)
+    torch.save({f"{EMAHook.__module__}.EMAHook:0": {"num_updates": 5, "ema": None}}, fix / "hooks" / "checkpoints" / "3.pt")
+    meta = {"step_count": 7, "global_step_count": 7, "batch_count": 7, "epoch_count": 2, "epoch_step_count": 1}
+    (fix / "strategy.json").write_text(json.dumps(meta))
+    (fix / "strategy" / "checkpoints").mkdir(parents=True)
+    (fix / "strategy" / "checkpoints" / "3.json").write_text(json.dumps(meta))
+    (fix / "manifest.json").write_text(json.dumps({
+        "schema_version": 1, "checkpoint_index": 3, "models": ["main"], "optimizers": ["main_optimizer"], "schedulers": [],
+        "associations": {"main": {"optimizers": ["main_optimizer"], "schedulers": []}}}))
+    b = _strategy(num_epochs=3, hooks=[EMAHook(decay=0.9)])
+    b.load_checkpoint(fix)
+    assert (b.step_count, b.epoch_count, b.epoch_step_count) == (7, 2, 1)
+    b._setup(_loader(_dataset()))
+    for p, q in zip(model.parameters(), b.models["main"].parameters()):
+        assert torch.equal(p.detach().cpu(), q.detach().cpu())
+    assert b.hooks[0].num_updates == 5 or any(getattr(h, "num_updates", None) == 5 for h in b.hooks)
+    assert ckpt.validate_checkpoint(fix) == []
+    (fix / "manifest.json").write_text(json.dumps({"schema_version": 1, "models": ["main"]}))
+    with pytest.raises(ValueError):
+        ckpt.CheckpointManifest(fix)
