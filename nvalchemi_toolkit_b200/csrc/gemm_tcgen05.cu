@@ -28,11 +28,22 @@ constexpr int BK = 32;      // 32 tf32 = 128 bytes = one swizzle row
 
 constexpr float kSiluNorm = 1.6790176868438721f;
 
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(192) gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                        const __grid_constant__ CUtensorMap tmB,
-                                                        float* __restrict__ C, int M, int N, int K, int64_t ldc,
-                                                        float alpha, int act, int* __restrict__ err) {
+// Grouped form: one launch runs G independent products that share M, N and the leading dimensions,
+//   C[:, c_col[g] : c_col[g] + N] (+)= act(alpha * A[:, a_col[g] : a_col[g] + k[g]] @ Bt[b_row[g] : b_row[g] + N, : k[g]]^T),
+// i.e. column slices of one wide A matrix times row blocks of one packed weight matrix (the per-irrep channel mixes of
+// an equivariant layer: one slice per (l, m) component, one weight block per l).  Tiles are scheduled m-tile major so that
+// the groups reading the same rows of A run together.
+constexpr int kMaxGroups = 64;
+struct GemmGroups {
+  int n_groups;
+  int accumulate;  // 1: add to what C holds
+  int a_col[kMaxGroups], k[kMaxGroups], b_row[kMaxGroups], c_col[kMaxGroups];
+};
+
+template <int BN, int STAGES, bool GROUPED>
+__device__ __forceinline__ void gemm_tf32_body(const CUtensorMap& tmA, const CUtensorMap& tmB, float* __restrict__ C, int M,
+                                               int N, int K, int64_t ldc, float alpha, int act, int* __restrict__ err,
+                                               const GemmGroups* gt) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4, STAGE_BYTES = A_BYTES + B_BYTES;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -44,7 +55,19 @@ __global__ void __launch_bounds__(192) gemm_tf32_kernel(const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // 1D grid, N-tiles fastest: the CTAs that share an A row-block run together and hit it in L2
   const int n_tiles = (N + BN - 1) / BN;
-  const int m0 = (int)(blockIdx.x / n_tiles) * BM, n0 = (int)(blockIdx.x % n_tiles) * BN;
+  int m0, n0, a_col = 0, b_row = 0;
+  bool accumulate = false;
+  if constexpr (GROUPED) {
+    const int G = gt->n_groups;
+    const int g = (int)((blockIdx.x / n_tiles) % G);
+    m0 = (int)(blockIdx.x / (n_tiles * G)) * BM;
+    n0 = (int)(blockIdx.x % n_tiles) * BN;
+    a_col = gt->a_col[g]; b_row = gt->b_row[g]; K = gt->k[g];
+    C += gt->c_col[g];
+    accumulate = gt->accumulate != 0;
+  } else {
+    m0 = (int)(blockIdx.x / n_tiles) * BM; n0 = (int)(blockIdx.x % n_tiles) * BN;
+  }
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -71,8 +94,8 @@ __global__ void __launch_bounds__(192) gemm_tf32_kernel(const __grid_constant__ 
         if (!mbar_wait(empty_bar(s), ((kb / STAGES) & 1) ^ 1, err, 1)) break;
         mbar_expect_tx(full_bar(s), STAGE_BYTES);
         uint32_t sa = base + s * STAGE_BYTES;
-        tma_load_2d(sa, &tmA, kb * BK, m0, full_bar(s));
-        tma_load_2d(sa + A_BYTES, &tmB, kb * BK, n0, full_bar(s));
+        tma_load_2d(sa, &tmA, a_col + kb * BK, m0, full_bar(s));
+        tma_load_2d(sa + A_BYTES, &tmB, kb * BK, b_row + n0, full_bar(s));
       }
     }
   } else if (warp == 1) {
@@ -139,12 +162,16 @@ __global__ void __launch_bounds__(192) gemm_tf32_kernel(const __grid_constant__ 
           float4 val = stage[r * SPR + (slot ^ (r & 7))];
           float* dst = C + (int64_t)row * ldc + col;
           if (vec_ok && col + 4 <= N) {
+            if (accumulate) {
+              const float4 old = *reinterpret_cast<const float4*>(dst);
+              val.x += old.x; val.y += old.y; val.z += old.z; val.w += old.w;
+            }
             *reinterpret_cast<float4*>(dst) = val;
           } else {
-            dst[0] = val.x;
-            if (col + 1 < N) dst[1] = val.y;
-            if (col + 2 < N) dst[2] = val.z;
-            if (col + 3 < N) dst[3] = val.w;
+            dst[0] = val.x + (accumulate ? dst[0] : 0.f);
+            if (col + 1 < N) dst[1] = val.y + (accumulate ? dst[1] : 0.f);
+            if (col + 2 < N) dst[2] = val.z + (accumulate ? dst[2] : 0.f);
+            if (col + 3 < N) dst[3] = val.w + (accumulate ? dst[3] : 0.f);
           }
         }
       }
@@ -155,6 +182,23 @@ __global__ void __launch_bounds__(192) gemm_tf32_kernel(const __grid_constant__ 
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
   }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192) gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                        const __grid_constant__ CUtensorMap tmB,
+                                                        float* __restrict__ C, int M, int N, int K, int64_t ldc,
+                                                        float alpha, int act, int* __restrict__ err) {
+  gemm_tf32_body<BN, STAGES, false>(tmA, tmB, C, M, N, K, ldc, alpha, act, err, nullptr);
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192) gemm_tf32_grouped_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                const __grid_constant__ CUtensorMap tmB,
+                                                                const __grid_constant__ GemmGroups groups,
+                                                                float* __restrict__ C, int M, int N, int64_t ldc,
+                                                                float alpha, int act, int* __restrict__ err) {
+  gemm_tf32_body<BN, STAGES, true>(tmA, tmB, C, M, N, 0, ldc, alpha, act, err, &groups);
 }
 
 // ---- host side -------------------------------------------------------------------------------------
@@ -246,6 +290,68 @@ void gemm_tf32_out(const Tensor& a, const Tensor& bt, double alpha, int64_t act,
   gemm_tf32_impl(a, bt, alpha, act, out);
 }
 
+// Grouped product (see GemmGroups).  a [M, Wa] (row stride lda), bt [R, Kmax] packed weight blocks (K-major), c [M, Wc]
+// (row stride ldc); tables are int lists of one entry per group; every k[g] is a multiple of 32.
+void gemm_tf32_grouped(const Tensor& a, const Tensor& bt, Tensor c, int64_t n_cols, std::vector<int64_t> a_col,
+                       std::vector<int64_t> k, std::vector<int64_t> b_row, std::vector<int64_t> c_col, double alpha,
+                       int64_t act, bool accumulate) {
+  TORCH_CHECK(a.is_cuda() && bt.is_cuda() && c.is_cuda() && a.scalar_type() == at::kFloat && bt.scalar_type() == at::kFloat &&
+                  c.scalar_type() == at::kFloat, "gemm_tf32_grouped expects float32 CUDA tensors");
+  TORCH_CHECK(a.dim() == 2 && bt.dim() == 2 && c.dim() == 2 && a.stride(1) == 1 && bt.stride(1) == 1 && c.stride(1) == 1,
+              "gemm_tf32_grouped: 2-D operands with unit inner stride");
+  const int64_t G = (int64_t)a_col.size();
+  TORCH_CHECK(G >= 1 && G <= kMaxGroups && (int64_t)k.size() == G && (int64_t)b_row.size() == G && (int64_t)c_col.size() == G,
+              "gemm_tf32_grouped: 1..", kMaxGroups, " groups with one table entry each");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a.size(0), N = n_cols;
+  TORCH_CHECK(c.size(0) == M, "gemm_tf32_grouped: row counts differ");
+  const int64_t lda = a.stride(0), ldb = bt.stride(0);
+  TORCH_CHECK(lda % 4 == 0 && ldb % 4 == 0, "gemm_tf32_grouped: row strides must be multiples of 4");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(bt.data_ptr()) & 15) == 0,
+              "gemm_tf32_grouped: operands must be 16-byte aligned");
+  if (M == 0 || N == 0) return;
+  GemmGroups gt;
+  gt.n_groups = (int)G;
+  gt.accumulate = accumulate ? 1 : 0;
+  for (int64_t g = 0; g < G; ++g) {
+    TORCH_CHECK(k[g] > 0 && k[g] % BK == 0, "gemm_tf32_grouped: every k must be a positive multiple of ", BK);
+    TORCH_CHECK(a_col[g] >= 0 && a_col[g] % 4 == 0 && a_col[g] + k[g] <= a.size(1), "gemm_tf32_grouped: A slice out of range");
+    TORCH_CHECK(b_row[g] >= 0 && b_row[g] + N <= bt.size(0) && k[g] <= bt.size(1), "gemm_tf32_grouped: weight block out of range");
+    TORCH_CHECK(c_col[g] >= 0 && c_col[g] + N <= c.size(1), "gemm_tf32_grouped: C slice out of range");
+    gt.a_col[g] = (int)a_col[g]; gt.k[g] = (int)k[g]; gt.b_row[g] = (int)b_row[g]; gt.c_col[g] = (int)c_col[g];
+  }
+  const int bn = N <= 64 ? 64 : 128;
+  CUtensorMap ma = make_map(a.data_ptr<float>(), M, a.size(1), lda, BM);
+  CUtensorMap mb = make_map(bt.data_ptr<float>(), bt.size(0), bt.size(1), ldb, bn);
+  const int64_t tiles = ((N + bn - 1) / bn) * ((M + BM - 1) / BM) * G;
+  TORCH_CHECK(tiles < (int64_t)2147483647, "gemm_tf32_grouped: too many tiles");
+  dim3 grid((unsigned)tiles);
+  int* err = error_word(a.device()).data_ptr<int>();
+  auto st = at::cuda::getCurrentCUDAStream();
+  int64_t kmax = 0;
+  for (auto v : k) kmax = std::max(kmax, v);
+  const bool short_k = kmax <= 2 * BK;
+#define NVA_LAUNCH_G(BN_, ST_)                                                                                      \
+  do {                                                                                                              \
+    size_t smem = (size_t)ST_ * (BM * BK * 4 + BN_ * BK * 4) + 1024 + 256;                                          \
+    static bool configured = false;                                                                                 \
+    if (!configured) {                                                                                              \
+      C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_tf32_grouped_kernel<BN_, ST_>,                                       \
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                 \
+      configured = true;                                                                                            \
+    }                                                                                                               \
+    gemm_tf32_grouped_kernel<BN_, ST_><<<grid, 192, smem, st>>>(ma, mb, gt, c.data_ptr<float>(), (int)M, (int)N,    \
+                                                                c.stride(0), (float)alpha, (int)act, err);          \
+  } while (0)
+  if (bn == 64) {
+    if (short_k) NVA_LAUNCH_G(64, 2); else NVA_LAUNCH_G(64, 4);
+  } else {
+    if (short_k) NVA_LAUNCH_G(128, 2); else NVA_LAUNCH_G(128, 3);
+  }
+#undef NVA_LAUNCH_G
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 // Reads (and clears) the error word: 0 = no bounded wait expired since the last call.
 int64_t gemm_error_status(const Tensor& like) {
   Tensor& w = error_word(like.device());
@@ -260,4 +366,5 @@ TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("gemm_tf32(Tensor a, Tensor bt, float alpha=1.0, int act=0) -> Tensor", &nva::gemm_tf32);
   m.def("gemm_tf32_out(Tensor a, Tensor bt, float alpha, int act, Tensor(a!) out) -> ()", &nva::gemm_tf32_out);
   m.def("gemm_error_status(Tensor like) -> int", &nva::gemm_error_status);
+  m.def("gemm_tf32_grouped(Tensor a, Tensor bt, Tensor(a!) c, int n_cols, int[] a_col, int[] k, int[] b_row, int[] c_col, float alpha=1.0, int act=0, bool accumulate=False) -> ()", &nva::gemm_tf32_grouped);
 }

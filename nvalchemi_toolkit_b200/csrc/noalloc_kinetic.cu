@@ -15,8 +15,8 @@ static __device__ __align__(256) double nva_noalloc_ke_scratch[NVA_NOALLOC_MAX_S
 
 constexpr int kMaxDevices = 64;
 double* g_scratch_ptr[kMaxDevices] = {nullptr};
-std::mutex g_mutex;
-char g_error[256] = "";
+std::mutex g_mutex;                 // guards g_scratch_ptr only
+thread_local char g_error[256] = "";  // every thread reads back the text of ITS last failure: no sharing, no lock
 
 __global__ void ke_clear_kernel(double* scratch, int m) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -24,14 +24,18 @@ __global__ void ke_clear_kernel(double* scratch, int m) {
 }
 
 __global__ void ke_accumulate_kernel(const float* __restrict__ v, const float* __restrict__ mass,
-                                     const int* __restrict__ seg, int64_t n, double* __restrict__ scratch) {
+                                     const int* __restrict__ seg, int64_t n, int num_systems,
+                                     double* __restrict__ scratch) {
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   int s = -1;
   double ke = 0.0;
   if (i < n) {
     s = seg[i];
+    // an index outside [0, num_systems) is skipped: it must neither pollute slots that this call did not clear nor
+    // reach beyond the fixed array
+    if (s < 0 || s >= num_systems) s = -1;
     double x = v[3 * i], y = v[3 * i + 1], z = v[3 * i + 2];
-    ke = 0.5 * (double)mass[i] * (x * x + y * y + z * z);
+    ke = s >= 0 ? 0.5 * (double)mass[i] * (x * x + y * y + z * z) : 0.0;
   }
   // all 32 lanes take part; a warp whose lanes share one system issues a single atomic
   unsigned peers = __match_any_sync(0xffffffffu, s);
@@ -49,7 +53,6 @@ __global__ void ke_store_kernel(const double* scratch, int m, float* out) {
 }
 
 int fail(int code, const char* what, cudaError_t err) {
-  std::lock_guard<std::mutex> lock(g_mutex);
   if (err != cudaSuccess) snprintf(g_error, sizeof(g_error), "%s: %s", what, cudaGetErrorString(err));
   else snprintf(g_error, sizeof(g_error), "%s", what);
   return code;
@@ -82,20 +85,22 @@ extern "C" int nva_kinetic_energy_noalloc(const float* velocities, const float* 
     if (g_scratch_ptr[dev] == nullptr) {
       void* p = nullptr;
       err = cudaGetSymbolAddress(&p, nva_noalloc_ke_scratch);
-      if (err != cudaSuccess || p == nullptr) {
-        snprintf(g_error, sizeof(g_error), "cudaGetSymbolAddress: %s", cudaGetErrorString(err));
-        return NVA_NOALLOC_E_CUDA;
-      }
+      if (err != cudaSuccess || p == nullptr) return fail(NVA_NOALLOC_E_CUDA, "cudaGetSymbolAddress", err);
       g_scratch_ptr[dev] = static_cast<double*>(p);
     }
     scratch = g_scratch_ptr[dev];
   }
+  // an error left behind by an earlier, unrelated launch of this thread is not this call's failure: if one is pending,
+  // report it as such and launch nothing (cudaPeekAtLastError does not clear it for its owner)
+  err = cudaPeekAtLastError();
+  if (err != cudaSuccess) return fail(NVA_NOALLOC_E_CUDA, "an earlier CUDA error is pending on this thread", err);
   const int threads = 256;
   int mblocks = (num_systems + threads - 1) / threads;
   ke_clear_kernel<<<mblocks, threads, 0, stream>>>(scratch, num_systems);  // the array keeps the previous call's sums
   if (n_atoms > 0) {
     int64_t blocks = (n_atoms + threads - 1) / threads;
-    ke_accumulate_kernel<<<(unsigned)blocks, threads, 0, stream>>>(velocities, masses, batch_idx, n_atoms, scratch);
+    ke_accumulate_kernel<<<(unsigned)blocks, threads, 0, stream>>>(velocities, masses, batch_idx, n_atoms, num_systems,
+                                                                   scratch);
   }
   ke_store_kernel<<<mblocks, threads, 0, stream>>>(scratch, num_systems, out);
   err = cudaGetLastError();

@@ -10,7 +10,10 @@
 //
 // Contract
 //   * float32 inputs, contiguous: velocities [n_atoms,3], masses [n_atoms], batch_idx [n_atoms] (int32, values in
-//     [0, num_systems)), output out [num_systems] (float32, written, not accumulated).
+//     [0, num_systems); an atom whose index lies outside that range is ignored), output out [num_systems] (float32,
+//     written, not accumulated).
+//   * The call works on the CURRENT device: all pointers must be device memory of it and `stream` must be a stream of it
+//     (or 0).
 //   * num_systems <= NVA_NOALLOC_MAX_SYSTEMS, otherwise the call fails with NVA_NOALLOC_E_TOO_LARGE and touches nothing.
 //   * The accumulator array (NVA_NOALLOC_MAX_SYSTEMS doubles = 512 KiB) exists once per GPU that loads the library and
 //     stays resident until the process exits.  Every call on a device shares it: the part that is used is cleared at
@@ -35,7 +38,8 @@
 extern "C" {
 #endif
 
-// Returns NVA_NOALLOC_OK or an error code; `nva_noalloc_last_error()` gives the text of the last failure.
+// Returns NVA_NOALLOC_OK or an error code; `nva_noalloc_last_error()` gives the text of the calling thread's last
+// failure (the buffer is per thread).
 int nva_kinetic_energy_noalloc(const float* velocities, const float* masses, const int* batch_idx, int64_t n_atoms,
                                int num_systems, float* out, cudaStream_t stream);
 const char* nva_noalloc_last_error(void);

@@ -32,8 +32,7 @@ from nvalchemi_toolkit_b200.distributed.graph_padder import cap_agreement_group,
 from nvalchemi_toolkit_b200.ops._native_counter import ops as _nops
 
 
-class PeerFailure(RuntimeError):
-    """A peer did not reach a device-side rendezvous within the bounded wait."""
+from nvalchemi_toolkit_b200.distributed.failure import PeerFailure  # noqa: E402  (re-exported)
 
 
 def peer_memory_available(wrapper: Any, device: torch.device, group: Any) -> bool:
@@ -234,6 +233,6 @@ class PeerHaloEngine:
         return 0 if self.p2p is None else self.p2p.status()
 
     def check(self) -> None:
-        code = self.status()
-        if code:
-            raise PeerFailure(f"rank {self.rank}: peer {code - 100} missed a device-side rendezvous")
+        """Raise ``PeerFailure`` if a peer missed a device-side rendezvous (one host read)."""
+        if self.p2p is not None:
+            self.p2p.check(wait=True)

@@ -250,73 +250,120 @@ def _l0_weights(ip: Any, w_last: torch.Tensor, table: torch.Tensor, c: int, avg:
     return out
 
 
+def _cached(owner: Any, tag: str, params: list[torch.Tensor], build: Any) -> Any:
+    """Constants derived from parameters (packed / scaled weight copies, host floats), kept ON the module that owns the
+    parameters and rebuilt only when one of them changes (in MD they never do).  The cache lives and dies with its
+    module, so two models can never see each other's entries."""
+    store = owner.__dict__.setdefault("_nva_derived", {})
+    stamp = tuple((p.data_ptr(), p._version, p.device, tuple(p.shape)) for p in params)
+    hit = store.get(tag)
+    if hit is None or hit[0] != stamp:
+        hit = store[tag] = (stamp, build())
+    return hit[1]
+
+
+def _packed(owner: Any, tag: str, params: list[torch.Tensor], build: Any) -> tuple[torch.Tensor, list[int]]:
+    """Packed weight matrix (+ first rows of its blocks) of a grouped channel mix, cached on ``owner``."""
+    return _cached(owner, "pack:" + tag, params, lambda: gemm.pack_weights([b.detach().contiguous() for b in build()]))
+
+
+def _rows2d(x: torch.Tensor) -> torch.Tensor:
+    """``[N, a, b]`` (rows possibly a slice of a larger buffer) as ``[N, a * b]`` without a copy."""
+    return x.reshape(x.shape[0], -1) if x.is_contiguous() else x.contiguous().reshape(x.shape[0], -1)
+
+
 def _per_l_linear(x: torch.Tensor, w: torch.Tensor, ls: list[int], transpose: bool = False,
-                  out: torch.Tensor | None = None) -> torch.Tensor:
-    """Per-irrep channel mix on ``[N, n_lm, C]``: one GEMM per ``lm`` row, reading and writing the strided slices in
-    place (no gather / scatter copies)."""
+                  out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """Per-irrep channel mix on ``[N, n_lm, C]``: one grouped GEMM launch, one group per ``lm`` row (reading and writing
+    the strided slices in place, no gather / scatter copies), one weight block per ``l``."""
     c = x.shape[-1]
     out = torch.empty_like(x) if out is None else out
-    off = 0
+    packed, rows = _packed(w, "per_l_t" if transpose else "per_l", [w],  # cached on the parameter object itself
+                           lambda: [w[i].t() if transpose else w[i] for i in range(len(ls))])
+    groups, off = [], 0
     for i, l in enumerate(ls):
-        wi = w[i] / math.sqrt(c)
-        wi = wi.t() if transpose else wi
         for m in range(2 * l + 1):
-            gemm.matmul(x[:, off + m], wi, out=out[:, off + m])
+            groups.append(((off + m) * c, c, rows[i], (off + m) * c))
         off += 2 * l + 1
+    gemm.grouped(_rows2d(x), packed, out.view(out.shape[0], -1), c, groups, alpha=1.0 / math.sqrt(c), accumulate=accumulate)
     return out
 
 
-def _skip(ip: Any, h: torch.Tensor, species: torch.Tensor, nz: int, transpose: bool = False) -> torch.Tensor:
-    """Element-dependent channel mix ``sc[:, l] = h[:, l] @ W[l, z]`` (or its adjoint)."""
+def _skip(ip: Any, h: torch.Tensor, species: torch.Tensor, nz: int, transpose: bool = False,
+          accumulate_into: torch.Tensor | None = None) -> torch.Tensor:
+    """Element-dependent channel mix ``sc[:, l] = h[:, l] @ W[l, z]`` (or its adjoint).  With ``accumulate_into`` the
+    result is added to that tensor (same shape as the result) instead of being returned in a new one."""
     c = h.shape[-1]
     src_ls, dst_ls = (ip.l_out, ip.l_in) if transpose else (ip.l_in, ip.l_out)
     n_dst = sum(2 * l + 1 for l in dst_ls)
+    shared = [(i, l) for i, l in enumerate(ip.l_out) if l in ip.l_in]
+    if nz == 1:
+        full = len(shared) == len(dst_ls)  # every destination irrep is written: no need to clear first
+        out = accumulate_into if accumulate_into is not None else \
+            (h.new_empty(h.shape[0], n_dst, c) if full else h.new_zeros(h.shape[0], n_dst, c))
+        packed, rows = _packed(ip, "skip_t" if transpose else "skip", [ip.skip],
+                               lambda: [ip.skip[i, 0].t() if transpose else ip.skip[i, 0] for i, _ in shared])
+        groups = []
+        for b, (i, l) in enumerate(shared):
+            so = sum(2 * k + 1 for k in src_ls[: src_ls.index(l)])
+            do = sum(2 * k + 1 for k in dst_ls[: dst_ls.index(l)])
+            groups += [((so + m) * c, c, rows[b], (do + m) * c) for m in range(2 * l + 1)]
+        if groups:
+            gemm.grouped(_rows2d(h), packed, out.view(out.shape[0], -1), c, groups, alpha=1.0 / math.sqrt(c * nz),
+                         accumulate=accumulate_into is not None)
+        return out
     out = h.new_zeros(h.shape[0], n_dst, c)
     for z in range(nz):
-        rows = None if nz == 1 else torch.nonzero(species == z).squeeze(1)
-        if rows is not None and rows.numel() == 0:
+        rows = torch.nonzero(species == z).squeeze(1)
+        if rows.numel() == 0:
             continue
-        hz = h if rows is None else h[rows]
-        oz = out if rows is None else h.new_zeros(rows.numel(), n_dst, c)
-        for i, l in enumerate(ip.l_out):
-            if l not in ip.l_in:
-                continue
+        hz = h[rows]
+        oz = h.new_zeros(rows.numel(), n_dst, c)
+        for i, l in shared:
             so = sum(2 * k + 1 for k in src_ls[: src_ls.index(l)])
             do = sum(2 * k + 1 for k in dst_ls[: dst_ls.index(l)])
             w = ip.skip[i, z] / math.sqrt(c * nz)
             w = w.t() if transpose else w
             for m in range(2 * l + 1):
                 gemm.matmul(hz[:, so + m], w, out=oz[:, do + m])
-        if rows is not None:
-            out[rows] = oz
+        out[rows] = oz
+    if accumulate_into is not None:
+        accumulate_into += out
+        return accumulate_into
     return out
 
 
 def _linear_mid(ip: Any, mid: torch.Tensor, avg: float, lmax: int) -> torch.Tensor:
-    """``mid [N, n_mid, C]`` (components ordered ``(l, m, path)``) → ``msg [N, 16, C]``: for every ``lm`` one GEMM with
-    ``K = paths(l) * C`` straight from the strided slice of ``mid``."""
+    """``mid [N, n_mid, C]`` (components ordered ``(l, m, path)``) → ``msg [N, 16, C]``: one grouped launch, for every
+    ``lm`` a product with ``K = paths(l) * C`` straight from the strided slice of ``mid``."""
     n, _, c = mid.shape
     out = mid.new_empty(n, (lmax + 1) ** 2, c)
-    flat = mid.reshape(n, -1)
+    packed, rows = _packed(ip, f"mid{avg}", list(ip.linear),
+                           lambda: [ip.linear[l] / (math.sqrt(ip.paths_per_l[l] * c) * avg) for l in range(lmax + 1)])
+    groups = []
     for l in range(lmax + 1):
         npl = ip.paths_per_l[l]
-        w = ip.linear[l] / (math.sqrt(npl * c) * avg)
-        for m in range(2 * l + 1):
-            o = (ip.mid_off[l] + m * npl) * c
-            gemm.matmul(flat[:, o: o + npl * c], w, out=out[:, l * l + m])
+        groups += [((ip.mid_off[l] + m * npl) * c, npl * c, rows[l], (l * l + m) * c) for m in range(2 * l + 1)]
+    gemm.grouped(_rows2d(mid), packed, out.view(n, -1), c, groups)
     return out
 
 
 def _linear_mid_bwd(ip: Any, dmsg: torch.Tensor, avg: float, lmax: int) -> torch.Tensor:
     n, _, c = dmsg.shape
     dmid = dmsg.new_empty(n, ip.n_mid, c)
-    flat = dmid.reshape(n, -1)
+    # out[:, o + j*C : o + (j+1)*C] = dmsg[:, lm] @ W_l[j*C:(j+1)*C, :]^T: one weight block of C rows per (l, path slot)
+    blocks = [(l, j) for l in range(lmax + 1) for j in range(ip.paths_per_l[l])]
+    packed, rows = _packed(ip, f"mid_t{avg}", list(ip.linear),
+                           lambda: [(ip.linear[l][j * c: (j + 1) * c] / (math.sqrt(ip.paths_per_l[l] * c) * avg)).t()
+                                    for l, j in blocks])
+    row_of = {b: r for b, r in zip(blocks, rows)}
+    groups = []
     for l in range(lmax + 1):
         npl = ip.paths_per_l[l]
-        wt = (ip.linear[l] / (math.sqrt(npl * c) * avg)).t()
         for m in range(2 * l + 1):
             o = (ip.mid_off[l] + m * npl) * c
-            gemm.matmul(dmsg[:, l * l + m], wt, out=flat[:, o: o + npl * c])
+            groups += [((l * l + m) * c, c, row_of[(l, j)], o + j * c) for j in range(npl)]
+    gemm.grouped(_rows2d(dmsg), packed, dmid.view(n, -1), c, groups)
     return dmid
 
 
@@ -415,18 +462,20 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         fused = _fused_ok(model, ip)
         l0w = None
         if row_map is not None and L0_MOMENTS and nz <= L0_MOMENTS_MAX_SPECIES and lmax == 3 and ws[-1].shape[0] == 64:
-            l0w = _l0_weights(ip, ws[-1], u[:, 0], C, cfg.avg_num_neighbors)
+            l0_params = [ip.radial[-1], model.node_embedding, ip.linear_up] + list(ip.linear)  # what the folded weights depend on
+            l0w = True
             A = pos.new_empty(n, nz, 16, 64)
             h3c = [] if keep_h3 else None
             for (i0, i1, e0, e1, h3) in radial_chunks(ws, h3c, li):
                 ops.mace_l0_moments(h3, pos, cell, b32, csr.eptr, csr.esend, csr.eS, row_map, i0, i1 - i0, e0, rmax, A)
                 del h3
             msg = pos.new_empty(n, 16, C)
-            for l in range(lmax + 1):
-                for lm in range(l * l, (l + 1) * (l + 1)):
-                    gemm.matmul(A[:, 0, lm], l0w[l][0], out=msg[:, lm])
-                    for s_ in range(1, nz):
-                        msg[:, lm] += gemm.matmul(A[:, s_, lm], l0w[l][s_])
+            for s_ in range(nz):  # one grouped launch per sender species (16 products each)
+                pk, rws = _packed(ip, f"l0w{s_}", l0_params, lambda s_=s_, ip=ip, ws=ws, u=u: [
+                    w_[s_] for w_ in _l0_weights(ip, ws[-1], u[:, 0], C, cfg.avg_num_neighbors)])
+                gemm.grouped(A.view(n, -1), pk, msg.view(n, -1), C,
+                             [((s_ * 16 + lm) * 64, 64, rws[l], lm * C) for l in range(lmax + 1)
+                              for lm in range(l * l, (l + 1) * (l + 1))], accumulate=s_ > 0)
             del A
             wgs, mid = None, None
         elif fused:
@@ -454,22 +503,19 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         del mid
         w0, w1 = _sym_weights(ip, cfg.correlation)
         B = ops.mace_symcon_fwd(msg, sp32, w0, w1, max(ip.l_out), cfg.correlation)
-        h_new = _per_l_linear(B, ip.product_linear, ip.l_out) + sc
-        s = h_new[:, 0]
-        if ip.last:
-            a = gemm.matmul(s, ip.readout_w1 / math.sqrt(C))
-            y, gy = _silu_and_grad(a)
-            w2 = ip.readout_w2 / math.sqrt(ip.readout_w2.shape[0])
-            node_e += y @ w2
-            ro = (gy * w2, None)
-        else:
-            node_e += s @ (ip.readout_w1 / math.sqrt(C))
-            ro = (None, None)
+        h_new = _per_l_linear(B, ip.product_linear, ip.l_out, out=sc, accumulate=True)  # skip connection + product mix
+        # readout: e_i += w2 . silu(s_i W1) (last layer) or s_i . w1, fused with what the adjoint needs (one kernel)
+        rw1 = _cached(ip, "ro_w1", [ip.readout_w1], lambda ip=ip: (ip.readout_w1.detach() / math.sqrt(C)).contiguous())
+        rw2 = _cached(ip, "ro_w2", [ip.readout_w2], lambda ip=ip: (ip.readout_w2.detach() / math.sqrt(ip.readout_w2.shape[0]))
+                      .contiguous()) if ip.last else None
+        gy = ops.mace_readout_fwd(h_new, rw1, rw2, node_e)
+        ro = (gy if ip.last else None, rw1)
         saved.append((ip, u, msg, ws, w0, w1, ro, u_ptrs, du, du_ptrs if not (pull and row_map is None) else pull_ptrs[1], wgs,
                       row_map, l0w, h3c))
         h = h_new
         del B, sc
     scale, shift = model.scale.to(pos.dtype), model.shift.to(pos.dtype)
+    scale_f = _cached(model, "scale", [model.scale], lambda: float(model.scale))  # host copy for kernel arguments (read once)
     node_e = model.atomic_energies.to(pos.dtype)[species] + node_e * scale + shift
     ew = None if energy_weights is None else energy_weights[:n].to(pos.dtype)
     e_sum = node_e if ew is None else node_e * ew
@@ -500,11 +546,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         k_du_ptrs = None if pull else du_ptrs  # pointer table handed to the kernels (none: local rows only)
         n_out = sum(2 * l + 1 for l in ip.l_out)
         dh_tot = pos.new_zeros(n, n_out, C) if dh is None else dh
-        if ip.last:
-            seed = gemm.matmul(ro[0], (ip.readout_w1 / math.sqrt(C)).t()) * scale
-        else:
-            seed = ((ip.readout_w1 / math.sqrt(C)) * scale).expand(n, C)
-        dh_tot[:, 0] += seed if ew is None else seed * ew[:, None]
+        ops.mace_readout_bwd(ro[0], ro[1], scale_f, None if ew is None else ew.contiguous(), dh_tot)
         dB = _per_l_linear(dh_tot, ip.product_linear, ip.l_out, transpose=True).contiguous()
         dmsg = ops.mace_symcon_bwd(msg, sp32, w0, w1, max(ip.l_out), cfg.correlation, dB)
         del dB
@@ -514,10 +556,12 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
             du = torch.zeros_like(u) if li > 0 else None
         if l0w is not None:
             Q = pos.new_empty(n, nz, 16, 64)
-            for l in range(lmax + 1):
-                for lm in range(l * l, (l + 1) * (l + 1)):
-                    for s_ in range(nz):
-                        gemm.matmul(dmsg[:, lm], l0w[l][s_].t(), out=Q[:, s_, lm])
+            l0_params = [ip.radial[-1], model.node_embedding, ip.linear_up] + list(ip.linear)
+            pk, rws = _packed(ip, "l0w_t", l0_params, lambda ip=ip, ws=ws, u=u: [
+                w_[s_].t() for s_ in range(nz) for w_ in _l0_weights(ip, ws[-1], u[:, 0], C, cfg.avg_num_neighbors)])
+            gemm.grouped(_rows2d(dmsg), pk, Q.view(n, -1), 64,
+                         [(lm * C, C, rws[s_ * (lmax + 1) + l], (s_ * 16 + lm) * 64) for s_ in range(nz)
+                          for l in range(lmax + 1) for lm in range(l * l, (l + 1) * (l + 1))])
             for (i0, i1, e0, e1, h3) in tangent_chunks(ws, h3c):
                 ops.mace_l0_force(h3, Q, pos, cell, b32, csr.eptr, csr.esend, csr.eS, row_map, i0, i1 - i0, e0, rmax,
                                   grad_pos, strain_grad)
@@ -554,7 +598,8 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
             # the fused kernel accumulates the feature gradient as [row, channel, component] (vector reductions)
             du = du.view(du.shape[0], C, du.shape[1]).transpose(1, 2).contiguous()
         if li > 0:
-            dh = _per_l_linear(du, ip.linear_up, ip.l_in, transpose=True) + _skip(ip, dh_tot, species, nz, transpose=True)
+            dh = _per_l_linear(du, ip.linear_up, ip.l_in, transpose=True)
+            _skip(ip, dh_tot, species, nz, transpose=True, accumulate_into=dh)
         saved[li] = None
     out["forces"] = -grad_pos[:n]
     if compute_stress:

@@ -81,6 +81,53 @@ def matmul(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0, act: int = 0, o
     return res
 
 
+def pack_weights(blocks: list[torch.Tensor]) -> tuple[torch.Tensor, list[int]]:
+    """Stack weight blocks ``w_i [K_i, N]`` as K-major rows ``[sum N, K_max]`` (zero padded); returns the packed matrix
+    and the first row of every block.  The result is what :func:`grouped` takes as ``packed``."""
+    n = blocks[0].shape[1]
+    kmax = max(int(b.shape[0]) for b in blocks)
+    out = blocks[0].new_zeros(len(blocks) * n, kmax)
+    rows = []
+    for i, b in enumerate(blocks):
+        out[i * n: (i + 1) * n, : b.shape[0]] = b.t()
+        rows.append(i * n)
+    return out, rows
+
+
+def grouped(a: torch.Tensor, packed: torch.Tensor, out: torch.Tensor, n_cols: int, groups: list[tuple[int, int, int, int]],
+            alpha: float = 1.0, act: int = 0, accumulate: bool = False) -> torch.Tensor:
+    """Many slice products in one launch: for every ``(a_col, k, b_row, c_col)`` of ``groups``
+
+        ``out[:, c_col : c_col + n_cols] (+)= act(alpha * a[:, a_col : a_col + k] @ packed[b_row : b_row + n_cols, :k].T)``
+
+    ``a`` and ``out`` are 2-D (unit inner stride); ``packed`` comes from :func:`pack_weights`.  CUDA float32 inputs in
+    TF32 mode run as ONE tcgen05 kernel whose tile scheduler walks (row tile, group, column tile); anything else runs the
+    same products one by one through ``torch.matmul``."""
+    if (_precision == "tf32" and a.is_cuda and a.dtype == torch.float32 and a.shape[0] > 0 and _native.available()
+            and _tma_ok(a) and out.stride(1) == 1 and all(g[1] % 32 == 0 and g[0] % 4 == 0 for g in groups)):
+        for i in range(0, len(groups), 64):
+            part = groups[i: i + 64]
+            _counters["tcgen05"] += 1
+            _nops.gemm_tf32_grouped(a, packed, out, int(n_cols), [g[0] for g in part], [g[1] for g in part],
+                                    [g[2] for g in part], [g[3] for g in part], float(alpha), int(act), bool(accumulate))
+        return out
+    for a_col, k, b_row, c_col in groups:
+        _counters["library"] += 1
+        res = a[:, a_col: a_col + k] @ packed[b_row: b_row + n_cols, :k].t()
+        if alpha != 1.0:
+            res = res * alpha
+        if act == 1:
+            res = torch.nn.functional.silu(res) * 1.6790176868438721
+        elif act != 0:
+            raise ValueError("grouped: only act 0 and 1 are supported")
+        dst = out[:, c_col: c_col + n_cols]
+        if accumulate:
+            dst += res
+        else:
+            dst.copy_(res)
+    return out
+
+
 def check_errors(like: torch.Tensor) -> int:
     """Status word of the GEMM kernels on ``like``'s device (0 = fine; non-zero = a bounded wait expired)."""
     if like.is_cuda and _native.available():

@@ -58,18 +58,71 @@ class SymmetricArena:
         self.offset = 0
 
 
-class P2PContext:
-    """Arena + flag-based barrier with a bounded wait and a status word."""
+class _LocalArena:
+    """Stand-in for :class:`SymmetricArena` inside ONE process: ``world`` plain device buffers play the ranks' arenas.
+    Nothing ever writes the other "ranks'" flags, so every rendezvous runs into its bounded wait: this is how the
+    time-out path is exercised on a single GPU without any peer."""
 
-    def __init__(self, arena_bytes: int, device: torch.device, group: dist.ProcessGroup | None = None) -> None:
-        self.arena = SymmetricArena(arena_bytes + 4096, device, group)
+    def __init__(self, nbytes: int, device: torch.device, world: int) -> None:
+        self.world, self.rank, self.device, self.group = world, 0, device, None
+        self.nbytes = int((nbytes + 255) // 256 * 256)
+        self._bufs = [torch.zeros(self.nbytes, dtype=torch.uint8, device=device) for _ in range(world)]
+        self.buf = self._bufs[0]
+        self.base_ptrs = [int(b.data_ptr()) for b in self._bufs]
+        self.multicast_ptr = 0
+        self.offset = 0
+
+    alloc = SymmetricArena.alloc
+    offset_of = SymmetricArena.offset_of
+    reset = SymmetricArena.reset
+
+
+class P2PContext:
+    """Arena + flag-based barrier with a bounded wait and a status word.
+
+    The status word lives on the device; :meth:`post_status` mirrors it into pinned host memory without blocking and
+    :meth:`check` raises :class:`~nvalchemi_toolkit_b200.distributed.failure.PeerFailure` once a mirrored value is
+    non-zero, so that a peer that missed a rendezvous stops the run instead of letting later kernels work on incomplete
+    buffers."""
+
+    def __init__(self, arena_bytes: int, device: torch.device, group: dist.ProcessGroup | None = None,
+                 _arena: object | None = None) -> None:
+        self.arena = _arena if _arena is not None else SymmetricArena(arena_bytes + 4096, device, group)
         self.world, self.rank, self.device = self.arena.world, self.arena.rank, device
         self.flags, self.flag_ptrs = self.arena.alloc((64,), torch.int32)
         self.err = torch.zeros(1, dtype=torch.int32, device=device)
+        self._err_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._err_event: torch.cuda.Event | None = None
         self.epoch = 0
         self.persistent_offset = self.arena.offset
         torch.cuda.synchronize(device)
-        dist.barrier(self.arena.group)
+        if _arena is None:
+            dist.barrier(self.arena.group)
+
+    @classmethod
+    def single_process(cls, arena_bytes: int, device: torch.device, world: int = 2) -> "P2PContext":
+        """A context whose peers are plain buffers of this process and never arrive at a barrier (time-out tests)."""
+        return cls(arena_bytes, device, _arena=_LocalArena(arena_bytes + 4096, device, world))
+
+    def post_status(self) -> None:
+        """Start a non-blocking copy of the status word to the host (read later by :meth:`check`)."""
+        self._err_host.copy_(self.err, non_blocking=True)
+        self._err_event = torch.cuda.Event()
+        self._err_event.record()
+
+    def check(self, wait: bool = False) -> None:
+        """Raise ``PeerFailure`` if the last posted status word reports an expired wait.  ``wait=False`` looks only at a
+        copy that has already arrived (no host synchronisation); ``wait=True`` posts a fresh copy and waits for it."""
+        from nvalchemi_toolkit_b200.distributed.failure import PeerFailure
+
+        if wait:
+            self.post_status()
+        if self._err_event is None or (not wait and not self._err_event.query()):
+            return
+        self._err_event.synchronize()
+        code = int(self._err_host[0])
+        if code:
+            raise PeerFailure([code - 100], f"did not reach a device-side rendezvous of rank {self.rank} within its bounded wait")
 
     def barrier(self) -> None:
         """Device-side rendezvous on the current stream: orders this rank's earlier peer writes before the peers'
@@ -81,14 +134,21 @@ class P2PContext:
         return int(self.err.item())
 
     def allreduce_(self, view: torch.Tensor, scale: float = 1.0, out: torch.Tensor | None = None,
-                   use_multimem: bool | None = None) -> torch.Tensor:
+                   use_multimem: bool | None = None, check: str | None = "lazy") -> torch.Tensor:
         """Sum a symmetric sub-buffer over all ranks (times ``scale``).
 
         With an NVLS multicast mapping the reduction runs in the switch (``multimem.ld_reduce`` / ``multimem.st``, each
         rank reducing one slice) and the result is left IN PLACE in every rank's buffer; otherwise every rank reads all
-        peers' buffers and writes ``out``.  Both are bracketed by flag barriers with bounded waits."""
+        peers' buffers and writes ``out``.  Both are bracketed by flag barriers with bounded waits.
+
+        ``check``: ``"sync"`` reads the status word after the closing barrier (one host synchronisation) and raises
+        ``PeerFailure`` before the result can be used; ``"lazy"`` (default) raises at the NEXT call for a wait that
+        expired in this one (no synchronisation: the status travels through pinned memory), i.e. one reduction may be
+        consumed before the failure surfaces; ``None`` leaves the status to the caller."""
         import os
 
+        if check == "lazy":
+            self.check(wait=False)
         n = view.numel()
         if use_multimem is None:
             use_multimem = self.arena.multicast_ptr != 0 and n % 4 == 0 and os.environ.get("NVA_MULTIMEM", "1") != "0"
@@ -103,6 +163,10 @@ class P2PContext:
             result = out if out is not None else torch.empty_like(view)
             _nops.p2p_allreduce(ptrs, self.world, float(scale), result)
         self.barrier()
+        if check == "sync":
+            self.check(wait=True)
+        elif check == "lazy":
+            self.post_status()
         return result
 
     def release_transient(self) -> None:

@@ -92,8 +92,12 @@ class FusedGradAllReduceHook(_Base):
     stage = S.AFTER_BACKWARD
     priority = 5
 
-    def __init__(self, model_keys: list[str] | None = None, loss_scale: float = 1.0, frequency: int = 1) -> None:
+    def __init__(self, model_keys: list[str] | None = None, loss_scale: float = 1.0, frequency: int = 1,
+                 status_check: str | None = "lazy") -> None:
         self.model_keys, self.loss_scale, self.frequency = model_keys, loss_scale, frequency
+        #: how a peer that missed the device-side rendezvous surfaces: "sync" (host read every step, raises before the
+        #: gradients are used), "lazy" (raises at the next step, no host synchronisation) or None
+        self.status_check = status_check
         self._p2p = None
         self._flat = self._ptrs = self._out = None
         self._params: list[torch.nn.Parameter] = []
@@ -139,15 +143,18 @@ class FusedGradAllReduceHook(_Base):
             from nvalchemi_toolkit_b200.ops._native_counter import ops
 
             # barrier - reduce (in the NVSwitch when a multicast mapping exists, else by peer loads) - barrier
-            result = self._p2p.allreduce_(self._flat, scale, out=self._out)
+            result = self._p2p.allreduce_(self._flat, scale, out=self._out, check=self.status_check)
         else:
             dist.all_reduce(self._flat)
             result = self._flat.mul_(scale)
         off = 0
         for p in self._params:
             n = p.numel()
-            if p.grad is not None:
-                p.grad.copy_(result[off: off + n].reshape(p.shape))
+            if p.grad is None:
+                # a parameter unused on this rank still receives the peers' contribution: every rank must apply the
+                # same reduced gradient or the replicas drift apart
+                p.grad = torch.empty_like(p)
+            p.grad.copy_(result[off: off + n].reshape(p.shape))
             off += n
 
 

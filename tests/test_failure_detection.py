@@ -97,3 +97,28 @@ def test_device_barrier_wait_is_bounded_and_reports_status():
     assert int(err) == 101  # 100 + the rank that did not arrive
     x = torch.ones(8, device=dev) * 2
     assert float(x.sum()) == 16.0  # the context is alive
+
+
+@pytest.mark.gpu
+def test_allreduce_reports_a_peer_that_never_arrives():
+    """``P2PContext.allreduce_`` over a context whose second "rank" is a plain buffer nothing drives: both rendezvous
+    run into their bounded wait, the call returns, and the status check raises instead of handing out a sum of
+    incomplete buffers (immediately with ``check="sync"``, at the following call with ``check="lazy"``)."""
+    from nvalchemi_toolkit_b200.distributed.failure import PeerFailure
+    from nvalchemi_toolkit_b200.parallel.symmetric import P2PContext
+
+    dev = torch.device("cuda", 0)
+    ctx = P2PContext.single_process(4096, dev, world=2)
+    view, _ = ctx.arena.alloc((256,), torch.float32)
+    view.fill_(1.0)
+    out = torch.empty_like(view)
+    with pytest.raises(PeerFailure) as info:
+        ctx.allreduce_(view, 0.5, out=out, use_multimem=False, check="sync")
+    assert info.value.ranks == [1]
+    lazy = P2PContext.single_process(4096, dev, world=2)
+    v2, _ = lazy.arena.alloc((256,), torch.float32)
+    lazy.allreduce_(v2, 1.0, out=out, use_multimem=False, check="lazy")  # returns: the failure is only posted
+    torch.cuda.synchronize()
+    with pytest.raises(PeerFailure):
+        lazy.allreduce_(v2, 1.0, out=out, use_multimem=False, check="lazy")
+    assert float((torch.ones(4, device=dev) * 3).sum()) == 12.0  # the context is alive

@@ -207,10 +207,10 @@ def test_fused_backward_feature_gradient_matches_unfused_elementwise():
     seen = {}
     orig = native._per_l_linear
 
-    def spy(x, wt, ls, transpose=False, out=None):
+    def spy(x, wt, ls, transpose=False, **kw):
         if transpose and x.dim() == 3 and x.shape[1] == 4:  # the feature gradient of layer 2 enters here
             seen.setdefault(native.FUSED, []).append(x.detach().clone())
-        return orig(x, wt, ls, transpose=transpose, out=out)
+        return orig(x, wt, ls, transpose=transpose, **kw)
 
     native._per_l_linear = spy
     try:

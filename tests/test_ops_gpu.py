@@ -148,3 +148,39 @@ def test_csr_fill_kernel_matches_mask_gathers():
     assert torch.equal(got.erecv, ref.erecv) and torch.equal(got.eS, ref.eS)
     none = native.build_csr(nm, num, None)
     assert torch.equal(none.esend, ref.esend) and int(none.eS.abs().sum()) == 0
+
+
+@pytest.mark.gpu
+def test_grouped_gemm_matches_fp32_reference():
+    """One grouped tcgen05 launch (column slices of a wide matrix times packed weight blocks, different K per group,
+    optional accumulation) against the same products in float32 PyTorch."""
+    from nvalchemi_toolkit_b200.ops import gemm
+
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    m, c = 1000, 128
+    a = torch.randn(m, 9 * c, device=dev, generator=g)
+    w_small = [torch.randn(c, c, device=dev, generator=g) for _ in range(2)]
+    w_big = torch.randn(3 * c, c, device=dev, generator=g)
+    packed, rows = gemm.pack_weights(w_small + [w_big])
+    groups = [(0, c, rows[0], 0), (c, c, rows[1], c), (2 * c, c, rows[1], 2 * c), (3 * c, 3 * c, rows[2], 3 * c),
+              (6 * c, 3 * c, rows[2], 4 * c)]
+    out = torch.full((m, 5 * c), float("nan"), device=dev)
+    gemm.grouped(a, packed, out, c, groups, alpha=0.5)
+    ws = [w_small[0], w_small[1], w_small[1], w_big, w_big]
+    ref = torch.cat([0.5 * (a[:, ac: ac + k].double() @ w.double()) for (ac, k, _, _), w in zip(groups, ws)], dim=1)
+    scale = float(ref.abs().max())
+    assert float((out.double() - ref).abs().max()) < 2e-3 * scale  # tf32 operands
+    base = torch.randn(m, 5 * c, device=dev, generator=g)
+    acc = base.clone()
+    gemm.grouped(a, packed, acc, c, groups, alpha=0.5, accumulate=True)
+    assert float((acc.double() - base.double() - ref).abs().max()) < 2e-3 * scale
+    # narrow outputs (N = 64) and a strided destination
+    w64 = [torch.randn(c, 64, device=dev, generator=g) for _ in range(3)]
+    p64, r64 = gemm.pack_weights(w64)
+    wide = torch.zeros(m, 4 * 64 + 8, device=dev)
+    gemm.grouped(a, p64, wide[:, :4 * 64], 64, [(i * c, c, r64[i % 3], i * 64) for i in range(4)])
+    ref64 = torch.cat([a[:, i * c: (i + 1) * c].double() @ w64[i % 3].double() for i in range(4)], dim=1)
+    assert float((wide[:, :256].double() - ref64).abs().max()) < 2e-3 * float(ref64.abs().max())
+    assert float(wide[:, 256:].abs().max()) == 0.0
+    assert gemm.check_errors(a) == 0

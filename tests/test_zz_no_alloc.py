@@ -45,6 +45,21 @@ def test_noalloc_kinetic_energy_matches_operator_twice():
         torch.cuda.synchronize()
         assert rc == 0, lib.nva_noalloc_last_error()
         assert torch.allclose(out, ref, rtol=1e-5, atol=1e-6)
+        # independent statement of the same sum in float64 PyTorch
+        ke64 = 0.5 * mass.double() * vel.double().pow(2).sum(-1)
+        ref64 = torch.zeros(m, dtype=torch.float64, device=dev).index_add_(0, bidx.long(), ke64)
+        assert torch.allclose(out.double(), ref64, rtol=1e-5, atol=1e-6)
+    # atoms labelled with a system outside [0, m) are ignored (nothing is written outside the slots of this call)
+    bad = bidx.clone()
+    bad[::7] = m + 3
+    bad[1::11] = 70000
+    bad[2::13] = -5
+    keep = (bad >= 0) & (bad < m)
+    rc, out = _call(lib, vel, mass, bad, m)
+    torch.cuda.synchronize()
+    assert rc == 0, lib.nva_noalloc_last_error()
+    ref64 = torch.zeros(m, dtype=torch.float64, device=dev).index_add_(0, bad[keep].long(), ke64[keep])
+    assert torch.allclose(out.double(), ref64, rtol=1e-5, atol=1e-6)
     # sizes beyond the fixed accumulator are refused with a message and leave the output untouched
     rc, out = _call(lib, vel, mass, bidx, 65537)
     assert rc == 1 and b"NVA_NOALLOC_MAX_SYSTEMS" in lib.nva_noalloc_last_error()
