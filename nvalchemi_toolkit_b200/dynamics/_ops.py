@@ -339,3 +339,107 @@ def batch_neighbor_list_rebuild_inplace(reference_positions, current_positions, 
     if update_reference_positions:
         sel = rebuild_flags[bi]
         reference_positions[sel] = current_positions[sel]
+
+
+# ------------------------------------------------------------------------ Nose-Hoover chains, barostat pieces
+_YS_W = {1: [1.0], 3: [1.0 / (2.0 - 2.0 ** (1.0 / 3.0))] * 2, 5: [1.0 / (4.0 - 4.0 ** (1.0 / 3.0))] * 4}
+_YS_W[3] = [_YS_W[3][0], 1.0 - 2.0 * _YS_W[3][0], _YS_W[3][0]]
+_YS_W[5] = [_YS_W[5][0]] * 2 + [1.0 - 4.0 * _YS_W[5][0]] + [_YS_W[5][0]] * 2
+
+
+def nhc_compute_masses(ndof: torch.Tensor, temperature: torch.Tensor, thermostat_time: torch.Tensor, chain_length: int
+                       ) -> torch.Tensor:
+    """``Q [M, C]``: ``Q_1 = N_f kT tau^2``, ``Q_k = kT tau^2`` (reference ``_ops/nose_hoover.py:65-127``)."""
+    q = (temperature * thermostat_time ** 2).unsqueeze(1).repeat(1, chain_length)
+    q[:, 0] = q[:, 0] * ndof
+    return q.contiguous()
+
+
+def _nhc_chain_torch(ke2, eta, eta_dot, Q, kT, ndof, dt, yoshida_order):
+    c = eta.shape[1]
+    scale = torch.ones_like(ke2)
+    for w in _YS_W[yoshida_order]:
+        h = w * dt
+        for sweep in (range(c - 1, -1, -1), None, range(c)):
+            if sweep is None:
+                s = torch.exp(-0.5 * h * eta_dot[:, 0])
+                scale = scale * s
+                ke2.mul_(s * s)
+                eta.add_(0.5 * h.unsqueeze(1) * eta_dot)
+                continue
+            for k in sweep:
+                g = ((ke2 - ndof * kT) if k == 0 else (Q[:, k - 1] * eta_dot[:, k - 1] ** 2 - kT)) / Q[:, k]
+                if k == c - 1:
+                    eta_dot[:, k] += 0.25 * h * g
+                else:
+                    f = torch.exp(-0.125 * h * eta_dot[:, k + 1])
+                    eta_dot[:, k] = (eta_dot[:, k] * f + 0.25 * h * g) * f
+    return scale
+
+
+def nhc_chain_scalar(ke2, eta, eta_dot, Q, temperature, ndof, dt, yoshida_order: int = 3) -> torch.Tensor:
+    """Half-step propagation of one chain per system driven by ``ke2 = 2 KE`` (updated in place); returns the scale factor
+    of the thermostatted velocities.  One kernel (thread = system) instead of ~150 tiny tensor operations."""
+    if _nat(ke2) and eta.is_contiguous() and eta_dot.is_contiguous():
+        return _nops.nhc_chain_scalar(ke2, eta, eta_dot, Q.contiguous(), temperature.contiguous(), ndof.contiguous(),
+                                      dt.contiguous(), int(yoshida_order))
+    return _nhc_chain_torch(ke2, eta, eta_dot, Q, temperature, ndof, dt, yoshida_order)
+
+
+def nhc_chain_update(velocities, masses, eta, eta_dot, Q, temperature, dt, ndof, ke2, total_scale, step_scale=None,
+                     dt_chain=None, batch_idx=None, compute_ke: bool = True, yoshida_order: int = 3) -> None:
+    """Chain half step + velocity rescale (reference op ``nvalchemi::nhc_chain_update``).  ``compute_ke=False`` takes
+    ``ke2`` as given (already summed over the ranks of a domain decomposition)."""
+    m = eta.shape[0]
+    if batch_idx is None:
+        batch_idx = torch.zeros(velocities.shape[0], dtype=torch.int32, device=velocities.device)
+    if _nat(velocities):
+        empty = velocities.new_empty(0)
+        _nops.nhc_chain_update(velocities, masses, eta, eta_dot, Q.contiguous(), temperature.contiguous(), dt.contiguous(),
+                               ndof.contiguous(), ke2, total_scale, step_scale if step_scale is not None else empty,
+                               dt_chain if dt_chain is not None else empty, _i32(batch_idx), bool(compute_ke),
+                               int(yoshida_order))
+        return
+    if compute_ke:
+        ke2.copy_(2.0 * compute_kinetic_energy(velocities, masses, batch_idx, m))
+    total_scale.copy_(_nhc_chain_torch(ke2, eta, eta_dot, Q, temperature, ndof, dt, yoshida_order))
+    velocities.mul_(total_scale[batch_idx.long()].unsqueeze(-1))
+
+
+def nhc_velocity_half_step(velocities, forces, masses, dt, batch_idx) -> None:
+    vv_velocity_finalize(velocities, forces, masses, dt, batch_idx)
+
+
+def nhc_position_update(positions, velocities, dt, batch_idx) -> None:
+    if _nat(positions):
+        _nops.nhc_position_update(positions, velocities.contiguous(), dt, _i32(batch_idx))
+        return
+    positions.add_(velocities * dt[batch_idx.long()].unsqueeze(-1))
+
+
+def compute_kinetic_tensor(velocities, masses, batch_idx, num_systems: int) -> torch.Tensor:
+    """``sum_i m_i v_i (x) v_i`` per system, ``[M, 3, 3]`` (float64 accumulation)."""
+    out = velocities.new_zeros(num_systems, 9)
+    if _nat(velocities):
+        _nops.compute_kinetic_tensor(velocities.contiguous(), masses, out, _i32(batch_idx))
+    else:
+        kt = (masses[:, None, None] * velocities[:, :, None] * velocities[:, None, :]).reshape(-1, 9).double()
+        out.copy_(torch.zeros(num_systems, 9, dtype=torch.float64, device=out.device).index_add_(0, batch_idx.long(), kt))
+    return out.reshape(num_systems, 3, 3)
+
+
+def affine_rows_(x, A, batch_idx, y=None, C=None, forces=None, masses=None, kick=None, kick_first: bool = False) -> None:
+    """``x_i <- x_i A_s + y_i C_s`` with an optional kick ``kick_s f_i / m_i`` added before (``kick_first``) or after the
+    map; ``A, C [M, 3, 3]``, row-vector convention.  The per-atom primitive of the MTK barostat."""
+    if _nat(x):
+        _nops.affine_rows_(x, A.contiguous(), y, C, forces, masses, kick, _i32(batch_idx), bool(kick_first))
+        return
+    b = batch_idx.long()
+    k = (kick[b] / masses).unsqueeze(-1) * forces if forces is not None else None
+    v = x + k if (k is not None and kick_first) else x
+    out = torch.einsum("ip,ipq->iq", v, A[b])
+    if y is not None:
+        out = out + torch.einsum("ip,ipq->iq", y, C[b])
+    if k is not None and not kick_first:
+        out = out + k
+    x.copy_(out)

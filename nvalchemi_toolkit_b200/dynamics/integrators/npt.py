@@ -2,10 +2,12 @@
 """Isothermal-isobaric (NPT) and isoenthalpic (NPH) dynamics, Martyna-Tobias-Klein equations.
 
 Reference: ``nvalchemi/dynamics/integrators/npt.py`` / ``nph.py`` and the ``npt_*`` / ``nph_*`` ops
-(``dynamics/_ops/npt_nph.py:59-911``).  The cell has one strain-rate degree of freedom per system (``isotropic``) or one
-per axis (``anisotropic``); ``triclinic`` is accepted and treated per axis after cell alignment.  Particles and barostat
-carry separate Nose-Hoover chains in NPT; NPH drops both chains.  The model must provide ``stress`` (tensile positive).
-Pressure is given in eV/A^3."""
+(``dynamics/_ops/npt_nph.py:59-911``).  The cell strain rate is a 3 x 3 matrix ``v_g`` per system: a multiple of the identity
+(``isotropic``), diagonal (``anisotropic``) or a full symmetric matrix (``triclinic``: shear components of the pressure
+tensor drive the cell angles; the symmetric form keeps the cell from rotating).  Particle velocities and positions are
+advanced with the matrix exponentials of ``v_g`` (one fused per-atom kernel each, ``_ops.affine_rows_``).  Particles and
+barostat carry separate Nose-Hoover chains in NPT; NPH drops both chains.  The model must provide ``stress`` (tensile
+positive).  Pressure is given in eV/A^3."""
 from __future__ import annotations
 
 from typing import Any
@@ -21,8 +23,7 @@ from nvalchemi_toolkit_b200.dynamics.integrators.nvt_nose_hoover import nhc_chai
 
 def compute_kinetic_tensor(velocities: torch.Tensor, masses: torch.Tensor, batch_idx: torch.Tensor, m: int) -> torch.Tensor:
     """``sum_i m_i v_i (x) v_i`` per system, ``[M,3,3]``."""
-    kt = (masses[:, None, None] * velocities[:, :, None] * velocities[:, None, :]).reshape(-1, 9)
-    return _ops.segmented_sum(kt, batch_idx, m).reshape(m, 3, 3)
+    return _ops.compute_kinetic_tensor(velocities, masses, batch_idx, m)
 
 
 def compute_pressure_tensor(kinetic_tensor: torch.Tensor, stress: torch.Tensor, volume: torch.Tensor) -> torch.Tensor:
@@ -60,7 +61,7 @@ class NPT(BaseDynamics):
                 "tau_t": _ops._to_per_system(self._tau_t, n, dev, dtype),
                 "tau_b": _ops._to_per_system(self._tau_b, n, dev, dtype),
                 "eta": z.clone(), "eta_dot": z.clone(), "xi": z.clone(), "xi_dot": z.clone(),
-                "v_eps": torch.zeros(n, 3, dtype=dtype, device=dev)}
+                "v_g": torch.zeros(n, 3, 3, dtype=dtype, device=dev)}
 
     def _init_state(self, batch: Batch) -> None:
         self._state = self._make_new_state(batch.num_graphs, batch)
@@ -74,6 +75,15 @@ class NPT(BaseDynamics):
         s = self._state
         return (self._ndof(batch) + 3.0) * s["kT"] * s["tau_b"] ** 2
 
+    def _project(self, g: torch.Tensor) -> torch.Tensor:
+        """Restrict a 3 x 3 generalised force to the degrees of freedom of the coupling mode."""
+        if self.pressure_coupling == "triclinic":
+            return 0.5 * (g + g.transpose(-1, -2))
+        d = torch.diagonal(g, dim1=1, dim2=2)
+        if self.pressure_coupling == "isotropic":
+            d = d.mean(-1, keepdim=True).expand(-1, 3)
+        return torch.diag_embed(d)
+
     def _thermostat_half(self, batch: Batch) -> None:
         if not self._thermostat:
             return
@@ -86,11 +96,12 @@ class NPT(BaseDynamics):
         scale = nhc_chain_update(ke2, s["eta"], s["eta_dot"], Q, s["kT"], ndof, s["dt"])
         _ops.velocity_rescale(batch.velocities, scale, batch.batch_idx)
         W = self._barostat_mass(batch)
-        nb = torch.full_like(ndof, 1.0 if self.pressure_coupling == "isotropic" else 3.0)
-        kb2 = W * (s["v_eps"] ** 2).sum(-1) * (1.0 if self.pressure_coupling != "isotropic" else 1.0 / 3.0)
+        n_b = {"isotropic": 1.0, "anisotropic": 3.0, "triclinic": 6.0}[self.pressure_coupling]
+        nb = torch.full_like(ndof, n_b)
+        kb2 = W * (s["v_g"] ** 2).sum((-1, -2)) * (1.0 / 3.0 if self.pressure_coupling == "isotropic" else 1.0)
         Qb = nhc_compute_masses(nb, s["kT"], s["tau_b"], self.chain_length)
         sb = nhc_chain_update(kb2, s["xi"], s["xi_dot"], Qb, s["kT"], nb, s["dt"])
-        s["v_eps"].mul_(sb.unsqueeze(-1))
+        s["v_g"].mul_(sb.reshape(-1, 1, 1))
 
     def _barostat_half(self, batch: Batch) -> None:
         s, m = self._state, batch.num_graphs
@@ -105,41 +116,38 @@ class NPT(BaseDynamics):
         ke2 = torch.diagonal(K, dim1=1, dim2=2).sum(-1)
         ndof = self._ndof(batch)
         W = self._barostat_mass(batch)
-        pdiag = torch.diagonal(P, dim1=1, dim2=2)
-        if self.pressure_coupling == "isotropic":
-            pdiag = pdiag.mean(-1, keepdim=True).expand(m, 3)
-        g = (vol.unsqueeze(-1) * (pdiag - s["p_ext"].unsqueeze(-1)) + (ke2 / ndof).unsqueeze(-1)) / W.unsqueeze(-1)
-        s["v_eps"].add_(0.5 * s["dt"].unsqueeze(-1) * g)
+        eye = torch.eye(3, dtype=P.dtype, device=P.device)
+        g = (vol.reshape(-1, 1, 1) * (P - s["p_ext"].reshape(-1, 1, 1) * eye) + (ke2 / ndof).reshape(-1, 1, 1) * eye)
+        s["v_g"].add_(0.5 * s["dt"].reshape(-1, 1, 1) * self._project(g) / W.reshape(-1, 1, 1))
+
+    def _damping(self, batch: Batch) -> torch.Tensor:
+        """``exp(-dt/2 (v_g + tr(v_g) / N_f))`` per system."""
+        s = self._state
+        tr = torch.diagonal(s["v_g"], dim1=1, dim2=2).sum(-1) / self._ndof(batch)
+        eye = torch.eye(3, dtype=tr.dtype, device=tr.device)
+        return torch.linalg.matrix_exp(-0.5 * s["dt"].reshape(-1, 1, 1) * (s["v_g"] + tr.reshape(-1, 1, 1) * eye))
 
     def _velocity_half(self, batch: Batch) -> None:
+        """Damp by the cell motion, then half kick (one fused per-atom kernel)."""
         s = self._state
-        b = batch.batch_idx.long()
-        ndof = self._ndof(batch)
-        alpha = 1.0 + 3.0 / ndof
-        tr = s["v_eps"].sum(-1) / 3.0
-        damp = torch.exp(-0.5 * s["dt"].unsqueeze(-1) * (s["v_eps"] + ((alpha - 1.0) * tr).unsqueeze(-1)))
-        batch.velocities.mul_(damp[b])
-        _ops.vv_velocity_finalize(batch.velocities, batch.forces, batch.atomic_masses, s["dt"], batch.batch_idx)
+        _ops.affine_rows_(batch.velocities, self._damping(batch), batch.batch_idx, forces=batch.forces,
+                          masses=batch.atomic_masses, kick=0.5 * s["dt"], kick_first=False)
 
     def _velocity_half_reverse(self, batch: Batch) -> None:
+        """Half kick, then damp (the mirror image of :meth:`_velocity_half`)."""
         s = self._state
-        b = batch.batch_idx.long()
-        ndof = self._ndof(batch)
-        alpha = 1.0 + 3.0 / ndof
-        tr = s["v_eps"].sum(-1) / 3.0
-        _ops.vv_velocity_finalize(batch.velocities, batch.forces, batch.atomic_masses, s["dt"], batch.batch_idx)
-        damp = torch.exp(-0.5 * s["dt"].unsqueeze(-1) * (s["v_eps"] + ((alpha - 1.0) * tr).unsqueeze(-1)))
-        batch.velocities.mul_(damp[b])
+        _ops.affine_rows_(batch.velocities, self._damping(batch), batch.batch_idx, forces=batch.forces,
+                          masses=batch.atomic_masses, kick=0.5 * s["dt"], kick_first=True)
 
     def _drift(self, batch: Batch) -> None:
+        """``r <- r exp(dt v_g) + dt v exp(dt v_g / 2)``; the lattice vectors (cell rows) follow ``exp(dt v_g)``."""
         s, m = self._state, batch.num_graphs
-        b = batch.batch_idx.long()
-        dt = s["dt"].unsqueeze(-1)
-        grow = torch.exp(dt * s["v_eps"])
-        half = torch.exp(0.5 * dt * s["v_eps"])
-        batch.positions.mul_(grow[b]).add_(batch.velocities * (dt * half)[b])
+        dt = s["dt"].reshape(-1, 1, 1)
+        grow = torch.linalg.matrix_exp(dt * s["v_g"])
+        half = dt * torch.linalg.matrix_exp(0.5 * dt * s["v_g"])
+        _ops.affine_rows_(batch.positions, grow, batch.batch_idx, y=batch.velocities, C=half)
         cell = batch.cell.reshape(m, 3, 3)
-        cell.mul_(grow.unsqueeze(1))  # column d of every lattice vector scales with axis d
+        cell.copy_(cell @ grow)
 
     # -- step ------------------------------------------------------------------------
     def pre_update(self, batch: Batch) -> None:

@@ -15,44 +15,14 @@ from nvalchemi_toolkit_b200.dynamics import _ops
 from nvalchemi_toolkit_b200.dynamics._units import KB_EV, fs_to_internal_time
 from nvalchemi_toolkit_b200.dynamics.base import BaseDynamics
 
-_YS = {1: [1.0], 3: [1.0 / (2.0 - 2.0 ** (1.0 / 3.0))] * 2, 5: [1.0 / (4.0 - 4.0 ** (1.0 / 3.0))] * 4}
-_YS[3] = [_YS[3][0], 1.0 - 2.0 * _YS[3][0], _YS[3][0]]
-_YS[5] = [_YS[5][0]] * 2 + [1.0 - 4.0 * _YS[5][0]] + [_YS[5][0]] * 2
-
-
-def nhc_compute_masses(ndof: torch.Tensor, kT: torch.Tensor, thermostat_time: torch.Tensor, chain_length: int
-                       ) -> torch.Tensor:
-    q = (kT * thermostat_time ** 2).unsqueeze(1).repeat(1, chain_length)
-    q[:, 0] = q[:, 0] * ndof
-    return q
+_YS = _ops._YS_W
+nhc_compute_masses = _ops.nhc_compute_masses
 
 
 def nhc_chain_update(ke2: torch.Tensor, eta: torch.Tensor, eta_dot: torch.Tensor, Q: torch.Tensor, kT: torch.Tensor,
                      ndof: torch.Tensor, dt: torch.Tensor, yoshida_order: int = 3) -> torch.Tensor:
     """Half-step propagation of the chains.  ``ke2 = 2 KE`` per system (updated in place); returns the velocity scale."""
-    m, c = eta.shape
-    scale = torch.ones_like(ke2)
-    for w in _YS[yoshida_order]:
-        h = w * dt
-        for k in range(c - 1, -1, -1):
-            g = ((ke2 - ndof * kT) if k == 0 else (Q[:, k - 1] * eta_dot[:, k - 1] ** 2 - kT)) / Q[:, k]
-            if k == c - 1:
-                eta_dot[:, k] += 0.25 * h * g
-            else:
-                f = torch.exp(-0.125 * h * eta_dot[:, k + 1])
-                eta_dot[:, k] = (eta_dot[:, k] * f + 0.25 * h * g) * f
-        s = torch.exp(-0.5 * h * eta_dot[:, 0])
-        scale = scale * s
-        ke2.mul_(s * s)
-        eta.add_(0.5 * h.unsqueeze(1) * eta_dot)
-        for k in range(c):
-            g = ((ke2 - ndof * kT) if k == 0 else (Q[:, k - 1] * eta_dot[:, k - 1] ** 2 - kT)) / Q[:, k]
-            if k == c - 1:
-                eta_dot[:, k] += 0.25 * h * g
-            else:
-                f = torch.exp(-0.125 * h * eta_dot[:, k + 1])
-                eta_dot[:, k] = (eta_dot[:, k] * f + 0.25 * h * g) * f
-    return scale
+    return _ops.nhc_chain_scalar(ke2, eta, eta_dot, Q, kT, ndof, dt, yoshida_order)
 
 
 class NVTNoseHoover(BaseDynamics):

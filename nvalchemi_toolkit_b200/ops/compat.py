@@ -41,13 +41,6 @@ def _lj_energy_forces_batch(positions, cells, neighbor_matrix, neighbor_matrix_s
     return e, f
 
 
-def _kinetic_tensor(velocities, masses, kinetic_tensors, batch_idx):
-    from nvalchemi_toolkit_b200.dynamics.integrators.npt import compute_kinetic_tensor
-
-    m = kinetic_tensors.shape[0]
-    kinetic_tensors.copy_(compute_kinetic_tensor(velocities, masses, batch_idx, m).reshape(kinetic_tensors.shape))
-
-
 def _per_system_reduce(local_vals, system_index, n_systems):
     import torch.distributed as dist
 
@@ -71,8 +64,6 @@ _define(_lib, "_batch_neighbor_list_rebuild_inplace(Tensor(a!) reference_positio
         lambda r, c, b, f, t, u, cell, inv, pbc: _ops.batch_neighbor_list_rebuild_inplace(r, c, b, f, t, u, cell, inv, pbc))
 _define(_lib, "lj_energy_forces_batch(Tensor positions, Tensor cells, Tensor neighbor_matrix, Tensor neighbor_matrix_shifts, Tensor num_neighbors, Tensor batch_idx, int fill_value, float epsilon, float sigma, float cutoff, float switch_width, bool half_list, int num_systems) -> (Tensor, Tensor)",
         _lj_energy_forces_batch)
-_define(_lib, "compute_kinetic_tensor(Tensor velocities, Tensor masses, Tensor(a!) kinetic_tensors, Tensor batch_idx) -> ()",
-        _kinetic_tensor)
 _define(_lib, "per_system_reduce(Tensor local_vals, Tensor system_index, int n_systems) -> Tensor", _per_system_reduce)
 for _mode in ("sum", "max", "min", "mean"):
     _define(_hooks, f"segmented_{_mode}(Tensor values, Tensor idx, int num_segments) -> Tensor",

@@ -96,3 +96,83 @@ def test_fire2_and_variable_cell_relaxation():
     vc.run(b2, 60)
     p1 = -torch.diagonal(b2.stress, dim1=1, dim2=2).mean(-1)
     assert (p1.abs() < 0.5 * p0.abs()).all()
+
+
+def test_triclinic_npt_relaxes_shear_without_rotating_the_cell():
+    """Full 3 x 3 cell coupling: a sheared argon crystal under NPT(triclinic) loses its shear stress (the isotropic and
+    per-axis modes cannot: their strain rate has no off-diagonal part), and the symmetric strain rate adds no rotation."""
+    from nvalchemi_toolkit_b200.dynamics.integrators.npt import NPT
+
+    def sheared():
+        b = _lj_batch(dtype=torch.float64, a=5.3)
+        shear = torch.eye(3, dtype=torch.float64)
+        shear[0, 1] = shear[1, 0] = 0.03  # symmetric (pure) shear strain
+        b["positions"] = b.positions @ shear
+        cell = b.cell.reshape(-1, 3, 3)
+        cell.copy_(cell @ shear)
+        _ops.initialize_velocities(b.velocities, b.atomic_masses, 20.0, b.batch_idx, random_seed=5)
+        return b
+
+    model = LennardJonesModelWrapper(epsilon=0.0104, sigma=3.4, cutoff=8.0, switch_width=1.0)
+    res = {}
+    for mode in ("triclinic", "anisotropic"):
+        b = sheared()
+        cell0 = b.cell.reshape(-1, 3, 3).clone()
+        dyn = NPT(model, dt=2.0, temperature=20.0, pressure=0.0, barostat_time=150.0, thermostat_time=50.0,
+                  pressure_coupling=mode, hooks=model.make_neighbor_hooks())
+        _prime(dyn, b)
+        s0 = b.stress.reshape(-1, 3, 3)[:, 0, 1].abs().clone()
+        dyn.run(b, 150)
+        cell1 = b.cell.reshape(-1, 3, 3)
+        F = torch.linalg.solve(cell0, cell1)  # deformation gradient of the lattice (row convention)
+        res[mode] = (s0, b.stress.reshape(-1, 3, 3)[:, 0, 1].abs(), (F - F.transpose(-1, -2)).abs().max(),
+                     (cell1[:, 0] * cell1[:, 1]).sum(-1).abs())
+        assert torch.isfinite(b.positions).all() and torch.isfinite(cell1).all()
+    s0, s1, rot, _ = res["triclinic"]
+    assert (s1 < 0.5 * s0).all(), (s0, s1)
+    assert float(rot) < 5e-3          # symmetric strain rates: only the commutator of successive strains can rotate
+    s0a, s1a, _, _ = res["anisotropic"]
+    assert (s1a > 0.5 * s0a).all()    # the per-axis barostat cannot remove the shear
+
+
+def test_nhc_and_barostat_kernels_match_torch_statements(device):
+    """The chain kernel, the kinetic tensor and the per-system affine map against independent PyTorch expressions."""
+    from nvalchemi_toolkit_b200.ops import _native
+
+    if not _native.available():
+        pytest.skip("native library not built")
+    g = torch.Generator().manual_seed(0)
+    m, c, n = 5, 3, 400
+    b = torch.sort(torch.randint(0, m, (n,), generator=g)).values.to(torch.int32).to(device)
+    v = torch.randn(n, 3, generator=g, dtype=torch.float64).to(device)
+    f = torch.randn(n, 3, generator=g, dtype=torch.float64).to(device)
+    mass = (torch.rand(n, generator=g, dtype=torch.float64) * 30 + 1).to(device)
+    kt = _ops.compute_kinetic_tensor(v, mass, b, m)
+    want = torch.zeros(m, 3, 3, dtype=torch.float64, device=device).index_add_(
+        0, b.long(), mass[:, None, None] * v[:, :, None] * v[:, None, :])
+    assert torch.allclose(kt, want, rtol=1e-12, atol=1e-12)
+    # chain: kernel against the tensor-op statement, all Yoshida orders
+    for order in (1, 3, 5):
+        st = lambda: (torch.rand(m, generator=torch.Generator().manual_seed(order), dtype=torch.float64) * 4 + 1).to(device)  # noqa: E731
+        ke2a, ke2b = st(), st()
+        eta = [torch.zeros(m, c, dtype=torch.float64, device=device) for _ in range(2)]
+        etd = [(torch.ones(m, c, dtype=torch.float64, device=device) * 0.01) for _ in range(2)]
+        ndof = torch.full((m,), 30.0, dtype=torch.float64, device=device)
+        kT = torch.full((m,), 0.02, dtype=torch.float64, device=device)
+        dt = torch.full((m,), 0.3, dtype=torch.float64, device=device)
+        Q = _ops.nhc_compute_masses(ndof, kT, torch.full_like(kT, 5.0), c)
+        s_kernel = _ops.nhc_chain_scalar(ke2a, eta[0], etd[0], Q, kT, ndof, dt, order)
+        s_torch = _ops._nhc_chain_torch(ke2b, eta[1], etd[1], Q, kT, ndof, dt, order)
+        assert torch.allclose(s_kernel, s_torch, rtol=1e-12) and torch.allclose(ke2a, ke2b, rtol=1e-12)
+        assert torch.allclose(eta[0], eta[1], rtol=1e-12, atol=1e-15) and torch.allclose(etd[0], etd[1], rtol=1e-12)
+    # affine map with a kick before / after
+    A = torch.randn(m, 3, 3, generator=g, dtype=torch.float64).to(device)
+    C = torch.randn(m, 3, 3, generator=g, dtype=torch.float64).to(device)
+    kick = (torch.rand(m, generator=g, dtype=torch.float64) + 0.1).to(device)
+    for first in (False, True):
+        x = v.clone()
+        _ops.affine_rows_(x, A, b, y=f, C=C, forces=f, masses=mass, kick=kick, kick_first=first)
+        k = (kick[b.long()] / mass).unsqueeze(-1) * f
+        base = (v + k) if first else v
+        want = torch.einsum("ip,ipq->iq", base, A[b.long()]) + torch.einsum("ip,ipq->iq", f, C[b.long()]) + (0 if first else k)
+        assert torch.allclose(x, want, rtol=1e-12, atol=1e-12)
