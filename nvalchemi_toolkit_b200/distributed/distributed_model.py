@@ -83,8 +83,14 @@ class DistributedModel(nn.Module):
         self.spec = spec if spec is not None else model.distribution_spec(config.strategy)
         if self.spec is None:
             raise ValueError(f"{type(model).__name__} declares no distribution spec; pass spec=MLIPSpec(...)")
+        from nvalchemi_toolkit_b200.distributed.config import StrategyKind
+
+        graph = StrategyKind(config.strategy) == StrategyKind.GRAPH_PARTITION
+        if graph and self.spec.message_passes > 1 and not self.spec.refresh_per_layer:
+            # index blocks keep one hop of senders; deeper models refresh those rows before every layer
+            self.spec = self.spec.with_(refresh_per_layer=True)
         self.engine: Any = None
-        if spec is None and not own_halo and config.peer_memory is not False:
+        if spec is None and not own_halo and config.peer_memory is not False and not graph:
             from nvalchemi_toolkit_b200.distributed.peer_halo import PeerHaloEngine, peer_memory_available
 
             params = list(model.parameters()) if isinstance(model, nn.Module) else []

@@ -110,8 +110,15 @@ class DomainParallel:
 
     # ---- set-up ---------------------------------------------------------------
     def partition(self, batch: Batch) -> ShardedBatch:
-        self.sharded = ShardedBatch.from_batch(batch, self.config, self.spec, self.group,
-                                               local_periodic=getattr(self.model, "wants_local_periodic", False))
+        from nvalchemi_toolkit_b200.distributed.config import StrategyKind
+
+        if StrategyKind(self.config.strategy) == StrategyKind.GRAPH_PARTITION:
+            from nvalchemi_toolkit_b200.distributed.graph_partition import GraphShardedBatch
+
+            self.sharded = GraphShardedBatch.from_batch(batch, self.config, self.spec, self.group)
+        else:
+            self.sharded = ShardedBatch.from_batch(batch, self.config, self.spec, self.group,
+                                                   local_periodic=getattr(self.model, "wants_local_periodic", False))
         self._sync_atom_ids()
         return self.sharded
 

@@ -60,58 +60,45 @@ class HaloStrategy(ParallelizationStrategy):
 
 
 class GraphPartitionStrategy(ParallelizationStrategy):
+    """Node partition by index blocks (``distributed/graph_partition.py``): a rank evaluates only the edges whose
+    receiver lies in its block, exchanges the one-hop sender rows before every layer, and the per-atom results of all
+    blocks are concatenated at the end (forces of foreign senders travel back by the reverse exchange first)."""
+
     kind = StrategyKind.GRAPH_PARTITION
 
     def __init__(self, config: DomainConfig, group: Any = None) -> None:
         super().__init__(config, group)
-        self._hook: Any = None
+        self._dm: Any = None
+        self._sharded: Any = None
+        self.last_edges_owned = 0
 
     def run_forward(self, model: Any, batch: Any, spec: MLIPSpec, **kwargs: Any) -> dict:
-        """``batch`` is the full (replicated) batch; every rank returns the full, summed outputs."""
-        from nvalchemi_toolkit_b200.hooks.neighbor_list import NeighborListHook
+        """``batch`` is the full (replicated) batch; every rank returns the full outputs (per-atom rows of all blocks
+        gathered, system sums reduced)."""
+        from nvalchemi_toolkit_b200.distributed.distributed_model import DistributedModel
+        from nvalchemi_toolkit_b200.distributed.graph_partition import GraphShardedBatch
+        from nvalchemi_toolkit_b200.distributed.halo import all_gather_rows
 
-        n = batch.num_nodes
-        lo, hi = IndexPartitioner(n, self.world).block(self.rank)
-        nc = model.model_config.neighbor_config
-        if nc is not None:
-            if self._hook is None:
-                self._hook = NeighborListHook(nc, skin=self.config.skin)
-            self._hook(SimpleNamespace(batch=batch), None)
-        weights = torch.zeros(n, dtype=batch.positions.dtype, device=batch.device)
-        weights[lo:hi] = 1.0
-        if spec.consolidation == Consolidation.DIRECT_MASKED and nc is not None:
-            saved = batch.num_neighbors.clone()
-            batch.num_neighbors[:lo] = 0
-            batch.num_neighbors[hi:] = 0
+        cfg = self.config if StrategyKind(self.config.strategy) == StrategyKind.GRAPH_PARTITION else \
+            self.config.model_copy(update={"strategy": StrategyKind.GRAPH_PARTITION})
+        if self._dm is None or self._dm.model is not model:
+            self._dm = DistributedModel(model, cfg, spec, self.group)
+        sh = self._sharded
+        if sh is None or sh.n_global != batch.num_nodes:
+            sh = self._sharded = GraphShardedBatch.from_batch(batch, cfg, self._dm.spec, self.group)
         else:
-            saved = None
-            try:
-                batch["energy_weights"] = weights
-            except KeyError:
-                batch.add_key("energy_weights", weights, level="node", overwrite=True)
-        ctx = DistributedContext(self.rank, self.world, hi - lo, n, is_halo=False, is_sharded=True, group=self.group)
-        try:
-            with activate_dd_context(ctx):
-                out = dict(model(batch, **kwargs))
-        finally:
-            if saved is not None:
-                batch.num_neighbors.copy_(saved)
+            lo, hi = sh.partitioner.block(self.rank)
+            sh.owned["positions"] = batch.positions[lo:hi]
+            if sh.needs_rebuild():
+                sh.rebuild()
+        self.last_edges_owned = sh.halo.edges_owned
+        out = self._dm(sh, **kwargs)
         res: dict[str, Any] = {}
         for key, value in out.items():
-            if not isinstance(value, torch.Tensor):
+            if isinstance(value, torch.Tensor) and value.dim() >= 1 and value.shape[0] == sh.n_owned and sh.n_owned != 1:
+                res[key], _ = all_gather_rows(value.contiguous(), self.group)
+            else:
                 res[key] = value
-                continue
-            v = value.detach().clone()
-            if key in spec.extensive_outputs or key == "forces":
-                if key == "forces" and spec.consolidation == Consolidation.DIRECT_MASKED:
-                    v[:lo] = 0
-                    v[hi:] = 0
-                v = self.reduce_system(v)
-            elif v.dim() >= 1 and v.shape[0] == n:  # other per-atom outputs: each rank contributes its block
-                block = torch.zeros_like(v)
-                block[lo:hi] = v[lo:hi]
-                v = self.reduce_system(block)
-            res[key] = v
         return res
 
 

@@ -84,7 +84,7 @@ class MACEWrapper(nn.Module, BaseModelMixin):
         active = set(self.model_config.active_outputs)
         inputs = self.adapt_input(data)
         res = self.model(inputs, compute_force="forces" in active, compute_stress="stress" in active,
-                         compute_hessian="hessian" in active and "hessian" in kwargs.get("extra", ("hessian",)) and False,
+                         compute_hessian="hessian" in active,  # second derivatives run on the differentiable PyTorch path
                          training=self.training)
         res["atomic_energies"] = res.get("node_energy")
         return self.adapt_output(res, data)

@@ -323,6 +323,17 @@ def _gp_worker(rank, world, port, q):
             strat = get_strategy(DomainConfig(cutoff=6.0, strategy=StrategyKind.GRAPH_PARTITION))
             res = strat.run_forward(model, batch, model.distribution_spec())
             out[name] = {k: res[k].tolist() for k in ("energy", "forces")}
+            out[name]["edges_owned"] = strat.last_edges_owned
+            out[name]["n_owned"], out[name]["n_ghost"] = strat._sharded.n_owned, strat._sharded.n_ghost
+        # the same partition under the dynamics wrapper
+        from nvalchemi_toolkit_b200.distributed import DomainParallel
+        from nvalchemi_toolkit_b200.dynamics import NVE
+
+        dp = DomainParallel(NVE(_lj(), dt=1.0), DomainConfig(cutoff=6.0, skin=0.5, strategy=StrategyKind.GRAPH_PARTITION))
+        dp.run(_lj_batch(3), n_steps=3)
+        full = dp.gather()
+        out["nve_positions"] = full.positions.tolist()
+        out["dp_sharded"] = type(dp.sharded).__name__
         q.put((rank, out))
     finally:
         dist.destroy_process_group()
@@ -346,6 +357,23 @@ def test_graph_partition_strategy_matches_single_process():
         for r in range(2):
             assert torch.allclose(torch.tensor(res[r][name]["forces"], dtype=torch.float64), ref["forces"].detach(), atol=1e-8)
             assert torch.allclose(torch.tensor(res[r][name]["energy"], dtype=torch.float64), ref["energy"].detach(), atol=1e-8)
+        # the work is split: each rank holds about half of the atoms and evaluates about half of the edges
+        e0, e1 = res[0][name]["edges_owned"], res[1][name]["edges_owned"]
+        assert e0 > 0 and e1 > 0 and 0.4 < e0 / (e0 + e1) < 0.6
+        n_total = res[0][name]["n_owned"] + res[1][name]["n_owned"]
+        assert abs(res[0][name]["n_owned"] - res[1][name]["n_owned"]) <= 1 and n_total == ref["forces"].shape[0]
+    # NVE through DomainParallel(strategy=graph_partition) against the single-process trajectory
+    from nvalchemi_toolkit_b200.dynamics import NVE, DynamicsStage
+
+    model = _lj()
+    b = _lj_batch(3)
+    dyn = NVE(model, dt=1.0, hooks=model.make_neighbor_hooks())
+    dyn._call_hooks(DynamicsStage.BEFORE_COMPUTE, b)
+    dyn.compute(b)
+    dyn.run(b, 3)
+    for r in range(2):
+        assert res[r]["dp_sharded"] == "GraphShardedBatch"
+        assert torch.allclose(torch.tensor(res[r]["nve_positions"], dtype=torch.float64), b.positions, atol=1e-9)
 
 
 def test_shard_routing_tables():

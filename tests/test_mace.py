@@ -259,3 +259,31 @@ def test_radial_cache_pool_reuses_and_releases_storage():
     assert not native._radial_cache_fits(torch.device("cpu"), 10, 2)           # only used on CUDA devices
     native.release_radial_cache()
     assert not native._h3_pool
+
+
+def test_hessian_output_matches_finite_differences_of_forces():
+    """``hessian`` (d2E / dr dr, ``[3N, 3N]``) from the wrapper against central differences of the forces."""
+    torch.manual_seed(3)
+    cfg = MACEConfig(atomic_numbers=[29], channels=8, avg_num_neighbors=10.0, r_max=4.0)
+    w = MACEWrapper(MACE(cfg, backend="torch").double()).eval()
+    d = fcc_supercell(1, a=3.7, noise=0.15, dtype=torch.float64)
+    w.model_config.active_outputs = {"energy", "forces", "hessian"}
+    b = Batch.from_data_list([d])
+    compute_neighbors(b, config=w.model_config.neighbor_config)
+    out = w(b)
+    n = b.num_nodes
+    H = out["hessian"].detach()
+    assert H.shape == (3 * n, 3 * n) and torch.allclose(H, H.t(), atol=1e-9)
+    w.model_config.active_outputs = {"energy", "forces"}
+    eps = 1e-5
+    for col in (0, 4, 3 * n - 1):
+        f = []
+        for sgn in (1.0, -1.0):
+            bb = Batch.from_data_list([d])
+            pos = bb.positions.clone().reshape(-1)
+            pos[col] += sgn * eps
+            bb["positions"] = pos.reshape(-1, 3)
+            compute_neighbors(bb, config=w.model_config.neighbor_config)
+            f.append(w(bb)["forces"].detach().reshape(-1))
+        fd = -(f[0] - f[1]) / (2 * eps)
+        assert torch.allclose(H[:, col], fd, atol=1e-6), float((H[:, col] - fd).abs().max())
