@@ -11,10 +11,12 @@ On-disk layout (the reference's, ``nvalchemi/data/datapipes/backends/zarr.py:433
     <store>/core/<field>              concatenated over samples along axis 0 (system fields: one row per sample)
     <store>/custom/<key>              user arrays added later
 
-Arrays are regular-chunked along axis 0 with the ``bytes`` codec (little endian), optionally followed by ``gzip``
-(standard library) or ``zstd`` (when ``zstandard`` is importable); each array directory holds ``zarr.json`` and chunk
-files ``c/<i>/0/...``.  Stores written here are plain Zarr v3 and can be opened by ``zarr>=3``; stores written by the
-reference can be read when their codecs are among the three above (sharded stores are not supported).
+Arrays are regular-chunked along axis 0 with the ``bytes`` codec (little endian), optionally followed by ``gzip`` or
+``zstd`` and optionally wrapped in ``sharding_indexed`` (``ZarrArrayConfig.shard_rows``: many chunks and their offset
+index in one file); each array directory holds ``zarr.json`` and chunk files ``c/<i>/0/...``.  Stores written here are
+plain Zarr v3 and can be opened by ``zarr>=3``; stores written by the reference are readable with the codecs of
+``data/zarr_codecs.py`` (``bytes, gzip, zstd, crc32c, blosc`` with LZ4 / Zstd / zlib and byte shuffle, ``transpose``,
+``sharding_indexed``).
 """
 from __future__ import annotations
 
@@ -27,6 +29,8 @@ from typing import Any, Sequence
 import numpy as np
 import torch
 from pydantic import BaseModel
+
+from nvalchemi_toolkit_b200.data import zarr_codecs as _codecs
 
 from nvalchemi_toolkit_b200.data.level_storage import LevelSchema
 
@@ -41,6 +45,9 @@ class ZarrArrayConfig(BaseModel):
     chunk_rows: int = 65536
     compressor: str | None = None  # None | "gzip" | "zstd"
     level: int = 3
+    #: rows per shard file (a multiple of ``chunk_rows``): many chunks + an offset index in ONE file (Zarr v3
+    #: ``sharding_indexed``), which keeps the file count of large datasets small.  None: one file per chunk.
+    shard_rows: int | None = None
 
 
 class ZarrWriteConfig(BaseModel):
@@ -72,9 +79,7 @@ class ZarrArray:
         self.dtype = np.dtype(_DTYPES[self.meta["data_type"]])
         self.chunk = tuple(self.meta["chunk_grid"]["configuration"]["chunk_shape"])
         self.codecs = [c["name"] for c in self.meta["codecs"]]
-        for c in self.codecs:
-            if c not in ("bytes", "gzip", "zstd"):
-                raise NotImplementedError(f"Zarr codec '{c}' is not supported by this reader")
+        _codecs.check_supported(self.meta["codecs"])
         enc = self.meta.get("chunk_key_encoding", {"name": "default", "configuration": {"separator": "/"}})
         self.sep = enc.get("configuration", {}).get("separator", "/")
         self.prefix = "c" if enc["name"] == "default" else ""
@@ -88,12 +93,19 @@ class ZarrArray:
         if cfg.compressor == "gzip":
             codecs.append({"name": "gzip", "configuration": {"level": cfg.level}})
         elif cfg.compressor == "zstd":
-            import zstandard  # noqa: F401  (fails loudly when unavailable)
-
+            if not _codecs.zstd_available():
+                raise ImportError("zstd compression needs the 'zstandard' package or pyarrow's Zstandard codec")
             codecs.append({"name": "zstd", "configuration": {"level": cfg.level, "checksum": False}})
         elif cfg.compressor is not None:
             raise ValueError(f"unknown compressor {cfg.compressor!r}")
         chunk = [max(1, int(cfg.chunk_rows))] + [max(1, int(s)) for s in shape[1:]]
+        if cfg.shard_rows is not None:
+            if cfg.shard_rows % chunk[0] != 0:
+                raise ValueError(f"shard_rows ({cfg.shard_rows}) must be a multiple of chunk_rows ({chunk[0]})")
+            codecs = [{"name": "sharding_indexed", "configuration": {
+                "chunk_shape": list(chunk), "codecs": codecs, "index_location": "end",
+                "index_codecs": [{"name": "bytes", "configuration": {"endian": "little"}}, {"name": "crc32c"}]}}]
+            chunk = [int(cfg.shard_rows)] + chunk[1:]
         _write_json(path / "zarr.json", {
             "zarr_format": 3, "node_type": "array", "shape": [int(s) for s in shape], "data_type": name,
             "chunk_grid": {"name": "regular", "configuration": {"chunk_shape": chunk}},
@@ -111,27 +123,10 @@ class ZarrArray:
         return self.path / key
 
     def _decode(self, raw: bytes) -> np.ndarray:
-        for c in reversed(self.codecs[1:]):
-            if c == "gzip":
-                raw = zlib.decompress(raw, 16 + zlib.MAX_WBITS)
-            else:
-                import zstandard
-
-                raw = zstandard.ZstdDecompressor().decompress(raw)
-        return np.frombuffer(raw, dtype=self.dtype).reshape(self.chunk)
+        return _codecs.decode(raw, self.meta["codecs"], self.dtype, self.chunk)
 
     def _encode(self, arr: np.ndarray) -> bytes:
-        raw = np.ascontiguousarray(arr, dtype=self.dtype).tobytes()
-        for c, spec in zip(self.codecs[1:], self.meta["codecs"][1:]):
-            lvl = spec.get("configuration", {}).get("level", 3)
-            if c == "gzip":
-                co = zlib.compressobj(lvl, zlib.DEFLATED, 16 + zlib.MAX_WBITS)
-                raw = co.compress(raw) + co.flush()
-            else:
-                import zstandard
-
-                raw = zstandard.ZstdCompressor(level=lvl).compress(raw)
-        return raw
+        return _codecs.encode(arr, self.meta["codecs"], self.dtype)
 
     def _read_chunk(self, i: int) -> np.ndarray:
         p = self._chunk_path(i)

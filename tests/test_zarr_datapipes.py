@@ -109,3 +109,90 @@ def test_zarr_sink_and_cli(tmp_path):
     assert res["roundtrip_ok"] and res["compression_ratio"] > 1.0
     res2 = io_test.main(["read", res["store"]])
     assert res2["samples"] == 400
+
+
+def test_sharded_and_compressed_arrays_round_trip(tmp_path):
+    """``sharding_indexed`` (index at the end, crc32c-protected) around zstd / gzip inner chunks; partial last shard,
+    in-place row updates, and the file count a shard saves."""
+    import json
+
+    import numpy as np
+
+    from nvalchemi_toolkit_b200.data import zarr_codecs
+    from nvalchemi_toolkit_b200.data.zarr_store import ZarrArray, ZarrArrayConfig
+
+    rng = np.random.default_rng(0)
+    data = rng.standard_normal((1000, 3)).astype(np.float32)
+    for comp in (None, "gzip", "zstd"):
+        a = ZarrArray.create(tmp_path / f"sh_{comp}", data.shape, np.float32,
+                             ZarrArrayConfig(chunk_rows=64, shard_rows=256, compressor=comp))
+        a.write(0, data)
+        assert np.array_equal(ZarrArray(tmp_path / f"sh_{comp}").read(), data)
+        assert np.array_equal(a.read(100, 700), data[100:700])
+        patch = rng.standard_normal((50, 3)).astype(np.float32)
+        a.write(230, patch)  # straddles two shards
+        data2 = data.copy()
+        data2[230:280] = patch
+        assert np.array_equal(a.read(), data2)
+        files = [f for f in (tmp_path / f"sh_{comp}").rglob("*") if f.is_file() and f.name != "zarr.json"]
+        assert len(files) == 4  # 1000 rows / 256 per shard, instead of 16 chunk files
+        meta = json.loads((tmp_path / f"sh_{comp}" / "zarr.json").read_text())
+        assert meta["codecs"][0]["name"] == "sharding_indexed" and meta["chunk_grid"]["configuration"]["chunk_shape"] == [256, 3]
+    # the index of a shard written by hand per the specification: offsets / lengths, all-ones for a missing inner chunk
+    cfg = {"chunk_shape": [2, 3], "codecs": [{"name": "bytes", "configuration": {"endian": "little"}}], "index_location": "start"}
+    inner = np.arange(6, dtype="<f4").reshape(2, 3)
+    idx = np.full((2, 1, 2), zarr_codecs.MAX_U64, dtype="<u8")
+    idx[1, 0] = (32 + 4, inner.nbytes)
+    body = idx.tobytes()
+    raw = body + zarr_codecs.crc32c(body).to_bytes(4, "little") + inner.tobytes()
+    out = zarr_codecs.decode_shard(raw, cfg, np.dtype("float32"), [4, 3], fill=7)
+    assert np.array_equal(out[2:], inner) and (out[:2] == 7).all()
+    assert zarr_codecs.crc32c(b"123456789") == 0xE3069283  # published check value of CRC-32C
+
+
+def test_blosc_frames_decode(tmp_path):
+    """Blosc v1 frames assembled per the container layout (header, block offsets, split streams, byte shuffle) with LZ4 raw
+    blocks, Zstandard and stored blocks."""
+    import struct
+
+    import numpy as np
+    import pyarrow as pa
+
+    from nvalchemi_toolkit_b200.data import zarr_codecs
+
+    x = (np.arange(4096, dtype=np.float32) * 0.5).astype("<f4")
+    raw = x.tobytes()
+    typesize, blocksize = 4, 8192
+
+    def frame(comp_code, compress, shuffle):
+        blocks, nblocks = [], len(raw) // blocksize
+        for b in range(nblocks):
+            blk = raw[b * blocksize: (b + 1) * blocksize]
+            if shuffle:
+                blk = np.frombuffer(blk, np.uint8).reshape(-1, typesize).T.tobytes()
+            streams = b""
+            ne = blocksize // typesize
+            for s in range(typesize):  # split: one stream per byte of the type
+                part = blk[s * ne: (s + 1) * ne]
+                c = compress(part)
+                c = part if len(c) >= len(part) else c
+                streams += struct.pack("<i", len(c)) + c
+            blocks.append(streams)
+        header_len = 16 + 4 * nblocks
+        starts, pos = [], header_len
+        for blk in blocks:
+            starts.append(pos)
+            pos += len(blk)
+        flags = (comp_code << 5) | (1 if shuffle else 0)
+        head = bytes([2, 1, flags, typesize]) + struct.pack("<III", len(raw), blocksize, pos)
+        return head + struct.pack(f"<{nblocks}i", *starts) + b"".join(blocks)
+
+    lz4 = lambda p: pa.Codec("lz4_raw").compress(p, asbytes=True)  # noqa: E731
+    zst = lambda p: zarr_codecs.zstd_compress(p, 3)  # noqa: E731
+    for code, fn in ((1, lz4), (4, zst)):
+        for shuffle in (False, True):
+            assert zarr_codecs.blosc_decompress(frame(code, fn, shuffle)) == raw
+    stored = bytes([2, 1, 0x2, typesize]) + struct.pack("<III", len(raw), blocksize, 16 + len(raw)) + raw
+    assert zarr_codecs.blosc_decompress(stored) == raw
+    codecs = [{"name": "bytes", "configuration": {"endian": "little"}}, {"name": "blosc", "configuration": {}}]
+    assert np.array_equal(zarr_codecs.decode(frame(1, lz4, True), codecs, np.dtype("float32"), [4096]), x)
