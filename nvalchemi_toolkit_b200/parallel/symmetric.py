@@ -134,7 +134,8 @@ class P2PContext:
         return int(self.err.item())
 
     def allreduce_(self, view: torch.Tensor, scale: float = 1.0, out: torch.Tensor | None = None,
-                   use_multimem: bool | None = None, check: str | None = "lazy") -> torch.Tensor:
+                   use_multimem: bool | None = None, check: str | None = "lazy", ptrs: torch.Tensor | None = None
+                   ) -> torch.Tensor:
         """Sum a symmetric sub-buffer over all ranks (times ``scale``).
 
         With an NVLS multicast mapping the reduction runs in the switch (``multimem.ld_reduce`` / ``multimem.st``, each
@@ -158,8 +159,9 @@ class P2PContext:
                                      float(scale), view)
             result = view
         else:
-            ptrs = torch.tensor([b + self.arena.offset_of(view) for b in self.arena.base_ptrs], dtype=torch.int64,
-                                device=self.device)
+            if ptrs is None:  # callers on a hot path pass the table of peer addresses they built once
+                ptrs = torch.tensor([b + self.arena.offset_of(view) for b in self.arena.base_ptrs], dtype=torch.int64,
+                                    device=self.device)
             result = out if out is not None else torch.empty_like(view)
             _nops.p2p_allreduce(ptrs, self.world, float(scale), result)
         self.barrier()

@@ -82,25 +82,42 @@ class DDPHook(_Base):
 
 
 class FusedGradAllReduceHook(_Base):
-    """Gradient all-reduce over peer memory fused with the ``1/world`` and loss-scale factors (runs at AFTER_BACKWARD).
+    """Gradient all-reduce over peer memory, bucketed and overlapped with the backward pass, with the ``1/world`` and
+    loss-scale factors applied inside the reduction kernel.
 
-    Gradients are packed into one flat buffer that lives in a symmetric (peer-mapped) arena; after a device-side flag
-    barrier every rank reads all peers' buffers, sums them and scales in a single kernel (``p2p_allreduce``), then the
-    result is unpacked.  Without CUDA peer memory (CPU / gloo) a ``torch.distributed`` all-reduce of the same flat buffer
-    is used, so the hook is testable on CPU ranks."""
+    Parameters are packed (in reverse registration order, the order in which backward produces their gradients) into
+    buckets of about ``bucket_mb`` MiB that live in a symmetric (peer-mapped) arena.  A
+    ``register_post_accumulate_grad_hook`` on every parameter copies its finished gradient into its bucket; as soon as a
+    bucket is complete (and all earlier buckets have been launched, so every rank issues the same sequence) its
+    reduction is enqueued on a side stream: flag barrier, then one kernel that sums the peers' buckets (in the NVSwitch
+    with ``multimem.ld_reduce`` when a multicast mapping exists, by peer loads otherwise) and scales, then a second
+    barrier, while the main stream continues with the rest of backward.  ``AFTER_BACKWARD`` flushes what is left
+    (parameters without a gradient contribute zeros and still receive the peers' sum), joins the side stream and
+    writes the reduced values back into ``p.grad``.  Replaces PyTorch DDP's bucketed NCCL all-reduce
+    (reference ``nvalchemi/training/hooks/ddp.py:250-301``).  Without CUDA peer memory (CPU / gloo) one
+    ``torch.distributed`` all-reduce of the flat buffer is used, so the hook is testable on CPU ranks."""
 
     stage = S.AFTER_BACKWARD
     priority = 5
 
     def __init__(self, model_keys: list[str] | None = None, loss_scale: float = 1.0, frequency: int = 1,
-                 status_check: str | None = "lazy") -> None:
+                 status_check: str | None = "lazy", bucket_mb: float = 4.0, overlap: bool = True) -> None:
         self.model_keys, self.loss_scale, self.frequency = model_keys, loss_scale, frequency
         #: how a peer that missed the device-side rendezvous surfaces: "sync" (host read every step, raises before the
         #: gradients are used), "lazy" (raises at the next step, no host synchronisation) or None
         self.status_check = status_check
+        self.bucket_mb, self.overlap = float(bucket_mb), bool(overlap)
         self._p2p = None
-        self._flat = self._ptrs = self._out = None
+        self._flat = self._out = None
         self._params: list[torch.nn.Parameter] = []
+        self._slots: dict[int, tuple[int, int, int]] = {}   # id(param) -> (bucket, offset, numel)
+        self._buckets: list[dict] = []
+        self._armed = False
+        self._comm_stream: Any = None
+        self.num_overlapped = 0  # buckets launched from inside backward during the last step
+
+    def _runs_on_stage(self, stage: Enum) -> bool:
+        return stage in (S.BEFORE_BACKWARD, S.AFTER_BACKWARD)
 
     def prepare_strategy(self, strategy: Any) -> None:
         if not dist.is_initialized():
@@ -109,53 +126,134 @@ class FusedGradAllReduceHook(_Base):
     def _setup(self, strategy: Any) -> None:
         keys = self.model_keys or [k for k in strategy.models if k in strategy.optimizer_configs]
         self._params = [p for k in keys for p in strategy.models[k].parameters() if p.requires_grad]
-        n = sum(p.numel() for p in self._params)
         dev = strategy.devices[0]
         for p in self._params:  # identical initial weights on every rank
             dist.broadcast(p.data, src=0)
-        if dev.type == "cuda" and dist.get_backend() == "nccl":
+        limit = max(1, int(self.bucket_mb * (1 << 20) / 4))
+        off, cur = 0, {"start": 0, "numel": 0, "params": []}
+        for p in reversed(self._params):
+            if cur["params"] and cur["numel"] + p.numel() > limit:
+                cur["numel"] = (cur["numel"] + 3) // 4 * 4  # 16-byte groups for the vector / multimem paths
+                self._buckets.append(cur)
+                off = cur["start"] + cur["numel"]
+                cur = {"start": off, "numel": 0, "params": []}
+            self._slots[id(p)] = (len(self._buckets), cur["start"] + cur["numel"], p.numel())
+            cur["params"].append(p)
+            cur["numel"] += p.numel()
+        cur["numel"] = (cur["numel"] + 3) // 4 * 4
+        self._buckets.append(cur)
+        n = cur["start"] + cur["numel"]
+        peer = dev.type == "cuda" and dist.get_backend() == "nccl"
+        if peer:
             from nvalchemi_toolkit_b200.parallel.symmetric import P2PContext
 
-            n_pad = (n + 3) // 4 * 4  # float4 groups for the multimem path
-            self._p2p = P2PContext(4 * n_pad + 4096, dev)
-            self._flat, self._ptrs = self._p2p.arena.alloc((n_pad,), torch.float32)
-            n = n_pad
+            self._p2p = P2PContext(4 * n + 4096, dev)
+            self._flat, _ = self._p2p.arena.alloc((n,), torch.float32)
             self._out = torch.empty(n, dtype=torch.float32, device=dev)
+            self._comm_stream = torch.cuda.Stream(device=dev)
+            base = self._p2p.arena.offset_of(self._flat)
+            for b in self._buckets:
+                b["ptrs"] = torch.tensor([a + base + 4 * b["start"] for a in self._p2p.arena.base_ptrs], dtype=torch.int64,
+                                         device=dev)
         else:
             self._flat = torch.zeros(n, dtype=torch.float32, device=dev)
+        for b in self._buckets:
+            b["ready"], b["launched"] = 0, False
+        if peer and self.overlap:
+            for p in self._params:
+                p.register_post_accumulate_grad_hook(self._on_grad)
+
+    # ---- overlap with backward ------------------------------------------------------------------------------------
+    def _on_grad(self, p: torch.nn.Parameter) -> None:
+        if not self._armed:
+            return
+        bi, off, n = self._slots[id(p)]
+        self._flat[off: off + n].copy_(p.grad.reshape(-1))
+        b = self._buckets[bi]
+        b["ready"] += 1
+        self._launch_ready(count=True)
+
+    def _launch_ready(self, count: bool = False) -> None:
+        """Enqueue, in bucket order, every bucket whose gradients are all in place."""
+        for b in self._buckets:
+            if b["launched"]:
+                continue
+            if b["ready"] < len(b["params"]):
+                break
+            self._launch(b)
+            if count:
+                self.num_overlapped += 1
+
+    def _launch(self, b: dict) -> None:
+        world = dist.get_world_size()
+        scale = 1.0 / (world * self.loss_scale)
+        view = self._flat[b["start"]: b["start"] + b["numel"]]
+        out = self._out[b["start"]: b["start"] + b["numel"]]
+        done = torch.cuda.Event()
+        done.record()  # the copies into this bucket (current stream) precede the reduction
+        self._comm_stream.wait_event(done)
+        with torch.cuda.stream(self._comm_stream):
+            b["result"] = self._p2p.allreduce_(view, scale, out=out, check=None, ptrs=b["ptrs"])
+        b["launched"] = True
 
     def __call__(self, ctx: Any, stage: Enum) -> None:
         if not dist.is_initialized() or dist.get_world_size() == 1:
             return
         if self._flat is None:
             self._setup(ctx.workflow)
+        if stage == S.BEFORE_BACKWARD:
+            self._armed = self._p2p is not None and self.overlap and not getattr(ctx, "accumulating", False)
+            self.num_overlapped = 0
+            for b in self._buckets:
+                b["ready"], b["launched"] = 0, False
+            if self._p2p is not None and self.status_check == "lazy":
+                self._p2p.check(wait=False)  # a rendezvous missed in the previous step surfaces here
+            return
+        if getattr(ctx, "accumulating", False):
+            return  # gradients keep accumulating locally; the reduction happens with the last micro-batch
         world = dist.get_world_size()
-        off = 0
-        for p in self._params:
-            n = p.numel()
-            if p.grad is None:
-                self._flat[off: off + n].zero_()
-            else:
-                self._flat[off: off + n].copy_(p.grad.reshape(-1))
-            off += n
-        scale = 1.0 / (world * self.loss_scale)
+        armed, self._armed = self._armed, False
         if self._p2p is not None:
-            from nvalchemi_toolkit_b200.ops._native_counter import ops
-
-            # barrier - reduce (in the NVSwitch when a multicast mapping exists, else by peer loads) - barrier
-            result = self._p2p.allreduce_(self._flat, scale, out=self._out, check=self.status_check)
+            for p in self._params:
+                bi, off, n = self._slots[id(p)]
+                b = self._buckets[bi]
+                if armed and b["launched"]:
+                    continue
+                if p.grad is None:
+                    self._flat[off: off + n].zero_()
+                elif not armed or b["ready"] < len(b["params"]):
+                    self._flat[off: off + n].copy_(p.grad.reshape(-1))
+            for b in self._buckets:
+                if not b["launched"]:
+                    b["ready"] = len(b["params"])
+            self._launch_ready()
+            torch.cuda.current_stream().wait_stream(self._comm_stream)
+            if self.status_check == "sync":
+                self._p2p.check(wait=True)
+            elif self.status_check == "lazy":
+                self._p2p.post_status()
+            result = None
         else:
+            for p in self._params:
+                _, off, n = self._slots[id(p)]
+                if p.grad is None:
+                    self._flat[off: off + n].zero_()
+                else:
+                    self._flat[off: off + n].copy_(p.grad.reshape(-1))
             dist.all_reduce(self._flat)
-            result = self._flat.mul_(scale)
-        off = 0
+            result = self._flat.mul_(1.0 / (world * self.loss_scale))
         for p in self._params:
-            n = p.numel()
+            bi, off, n = self._slots[id(p)]
+            if result is not None:
+                src = result[off: off + n]
+            else:
+                b = self._buckets[bi]
+                src = b["result"][off - b["start"]: off - b["start"] + n]
             if p.grad is None:
                 # a parameter unused on this rank still receives the peers' contribution: every rank must apply the
                 # same reduced gradient or the replicas drift apart
                 p.grad = torch.empty_like(p)
-            p.grad.copy_(result[off: off + n].reshape(p.shape))
-            off += n
+            p.grad.copy_(src.reshape(p.shape))
 
 
 # ------------------------------------------------------------------ update policies

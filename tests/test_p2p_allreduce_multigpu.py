@@ -87,3 +87,64 @@ def test_peer_allreduce_matches_nccl():
             assert res["multimem"] < 1e-4
     print("\nall-reduce of 4 MiB on", world, "GPUs:", {k: round(v, 1) for k, v in results[0].items() if k.endswith("_us")},
           "multicast:", results[0]["multicast"])
+
+
+def _hook_worker(rank: int, world: int, port: int, q) -> None:
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                          NCCL_NVLS_ENABLE="0")
+        import torch.distributed as dist
+
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from nvalchemi_toolkit_b200 import Batch
+        from nvalchemi_toolkit_b200.training.hooks import FusedGradAllReduceHook
+        from tests.test_training import _dataset, _strategy
+
+        data = _dataset(8)
+        hook = FusedGradAllReduceHook(bucket_mb=0.002, status_check="sync")  # ~500 floats per bucket: several buckets
+        st = _strategy(num_steps=3, hooks=[hook], devices=[str(dev)])
+        for step in range(3):
+            lo = 4 * (step % 2) + 2 * rank
+            st.train_batch(Batch.from_data_list(data[lo: lo + 2], device=dev))
+        torch.cuda.synchronize()
+        q.put((rank, {"params": [p.detach().reshape(-1).cpu().tolist() for p in st.models["main"].parameters()],
+                      "buckets": len(hook._buckets), "overlapped": hook.num_overlapped, "status": hook._p2p.status()}))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as exc:  # pragma: no cover
+        import traceback
+
+        q.put((rank, {"error": f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"}))
+
+
+def test_bucketed_gradient_allreduce_overlaps_backward_and_matches_single_process():
+    """The training hook on 2 GPUs: several buckets, reductions launched from inside backward, parameters identical on
+    both ranks and equal to a single-process run on the union of the two ranks' batches."""
+    import torch.multiprocessing as mp
+
+    from nvalchemi_toolkit_b200 import Batch
+    from tests.test_training import _dataset, _strategy
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_hook_worker, args=(r, 2, 29571, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=600) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        if p.is_alive():
+            p.terminate()
+    for r in res.values():
+        assert "error" not in r, r["error"]
+        assert r["status"] == 0 and r["buckets"] > 1 and r["overlapped"] >= 1
+    for a, b in zip(res[0]["params"], res[1]["params"]):
+        assert torch.allclose(torch.tensor(a), torch.tensor(b), atol=1e-7)
+    data = _dataset(8)
+    st = _strategy(num_steps=3)
+    for step in range(3):
+        st.train_batch(Batch.from_data_list(data[4 * (step % 2): 4 * (step % 2) + 4]))
+    for a, b in zip(res[0]["params"], st.models["main"].parameters()):
+        assert torch.allclose(torch.tensor(a), b.detach().reshape(-1), atol=5e-3)

@@ -38,7 +38,8 @@ def _strategy(**kw):
     loss = EnergyMSELoss() + 10.0 * ForceMSELoss()
     if "num_steps" not in kw:
         kw.setdefault("num_epochs", 2)
-    return TrainingStrategy(DemoModelWrapper(), OptimizerConfig(kwargs={"lr": 3e-3}), loss, devices=["cpu"], **kw)
+    kw.setdefault("devices", ["cpu"])
+    return TrainingStrategy(DemoModelWrapper(), OptimizerConfig(kwargs={"lr": 3e-3}), loss, **kw)
 
 
 class Recorder:
