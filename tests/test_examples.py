@@ -11,7 +11,11 @@ ROOT = Path(__file__).resolve().parents[1]
 FAST = ["basic/01_atomic_data_and_batch.py", "basic/02_neighbor_lists.py", "basic/04_batched_fire_relaxation.py",
         "intermediate/06_inflight_batching.py", "intermediate/07_zarr_and_dataloader.py",
         "intermediate/08_train_a_model.py", "advanced/10_ewald_vs_pme.py", "advanced/11_variable_cell_relaxation.py",
-        "distributed/12_domain_parallel_md.py", "distributed/14_bring_your_own_mpnn.py"]
+        "distributed/12_domain_parallel_md.py", "distributed/14_bring_your_own_mpnn.py",
+        "advanced/15_biased_potential.py", "advanced/16_custom_hook_and_convergence.py", "advanced/17_custom_integrator.py",
+        "intermediate/18_npt_triclinic.py", "intermediate/19_safety_and_monitoring.py",
+        "intermediate/20_sharded_zarr_store.py", "distributed/21_graph_partition.py",
+        "distributed/22_relax_then_md_domain_parallel.py", "intermediate/23_data_parallel_training.py"]
 
 
 @pytest.mark.parametrize("script", FAST)
