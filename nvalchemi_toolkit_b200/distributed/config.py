@@ -28,7 +28,7 @@ class DomainConfig(BaseModel):
     skin: float = 0.0
     ghost_width: float | None = None          # None -> cutoff + skin (times the model's number of message passes)
     strategy: StrategyKind = StrategyKind.HALO
-    compile: bool = False                      # accepted for API parity; kernels are hand-written, nothing is traced
+    compile: bool = False                      # API parity only: True warns (kernels are hand-written, nothing is traced)
     require_nondegenerate: bool = True
     mesh: Any = None
     mesh_dim: str = "domain"
@@ -51,6 +51,11 @@ class DomainConfig(BaseModel):
             self.__dict__["ghost_width"] = self.cutoff + self.skin
         if self.migration_hysteresis is None:
             self.__dict__["migration_hysteresis"] = 0.5 * self.skin
+        if self.compile or self.scripted_marshal:
+            import warnings
+
+            warnings.warn("DomainConfig.compile / scripted_marshal have no effect in this package: the distributed "
+                          "forward runs precompiled kernels and is never traced", UserWarning, stacklevel=2)
         if self.neighbor_skin is None:
             self.__dict__["neighbor_skin"] = self.skin
         if self.neighbor_skin > self.skin:

@@ -74,6 +74,8 @@ class DomainParallel:
 
     def __init__(self, dynamics: Any, config: DomainConfig, spec: MLIPSpec | None = None, group: Any = None,
                  max_neighbors: int | None = None, async_migration: bool = True) -> None:
+        if group is None and config.mesh is not None:
+            group = config.mesh.get_group(config.mesh_dim)  # the ranks of the mesh's domain dimension share the system
         self.dynamics, self.config, self.group = dynamics, config, group
         self.rank, self.world = _world(group)
         self.async_migration = bool(async_migration)

@@ -585,7 +585,12 @@ class FusedStage(BaseDynamics):
                     f"n_steps_counter_{code}", lambda n, dev: torch.zeros(n, 1, dtype=torch.long, device=dev))
 
     def compile(self, **kwargs: Any) -> "FusedStage":
-        """Kept for API compatibility: the step already runs hand-written kernels, there is no tracing compiler."""
+        """Accepted for API compatibility and reported as a no-op: the step already runs precompiled hand-written
+        kernels and nothing here goes through a tracing compiler."""
+        import warnings
+
+        warnings.warn("FusedStage.compile() has no effect in this package: the fused step runs precompiled kernels",
+                      UserWarning, stacklevel=2)
         return self
 
     def register_fused_hook(self, hook: Any) -> None:

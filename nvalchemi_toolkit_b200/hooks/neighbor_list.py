@@ -25,7 +25,14 @@ class NeighborListHook:
         self.config = config
         self.skin = float(skin)
         self.stage = stage
-        self.method = method  # accepted for API parity; the cell list handles every size
+        if method not in (None, "auto", "cell_list", "naive"):
+            raise ValueError(f"unknown neighbour-list method {method!r}; expected 'auto', 'cell_list' or 'naive'")
+        #: "cell_list" (binned search kernel, any size), "naive" (all pairs with periodic images, plain tensor
+        #: expressions: only sensible for systems of a few hundred atoms) or "auto" / None (cell list)
+        self.method = method
+        #: shrink the matrix width again when the largest count has stayed below half of it for this many rebuilds
+        self.shrink_after = 8
+        self._low_use = 0
         self.frequency = 1
         self._max_neighbors = max_neighbors
         self._ref_positions: torch.Tensor | None = None
@@ -45,14 +52,27 @@ class NeighborListHook:
         cutoff = self.config.cutoff + self.skin
         k = self._bufs[0].shape[1]
         while True:
-            _nb.neighbor_matrix(batch.positions, cell, pbc, batch.batch_idx, batch.batch_ptr, cutoff, k,
-                                self.config.half_list, out=self._bufs, rebuild_flags=flags)
+            if self.method == "naive":
+                _nb._neighbor_matrix_torch(batch.positions.detach(), cell, pbc, batch.batch_idx, cutoff, *self._bufs,
+                                           self.config.half_list)
+            else:
+                _nb.neighbor_matrix(batch.positions, cell, pbc, batch.batch_idx, batch.batch_ptr, cutoff, k,
+                                    self.config.half_list, out=self._bufs, rebuild_flags=flags)
             actual = int(self._bufs[1].max())
             if actual <= k:
                 break
             k = ((int(actual * 1.5) + 1) + 15) // 16 * 16
             self._alloc(batch, k)
             flags = None  # a wider matrix needs every row rebuilt
+        # adaptive shrink: a width that has been more than twice the need for a while costs memory and bandwidth
+        self._low_use = self._low_use + 1 if (self._max_neighbors is None and actual * 2 < k and k > 16) else 0
+        if self._low_use >= self.shrink_after:
+            k_new = max(16, ((int(actual * 1.25) + 1) + 15) // 16 * 16)
+            if k_new < k:
+                self._alloc(batch, k_new)
+                _nb.neighbor_matrix(batch.positions, cell, pbc, batch.batch_idx, batch.batch_ptr, cutoff, k_new,
+                                    self.config.half_list, out=self._bufs)
+            self._low_use = 0
         self.num_rebuilds += 1
         self.version += 1
 

@@ -126,3 +126,43 @@ def test_reference_operator_names_are_callable():
     assert torch.equal(s, torch.full((m, 2), 4.0, dtype=torch.float64))
     assert torch.equal(torch.ops.nvalchemi.per_system_reduce(torch.ones(n, dtype=torch.float64), batch_idx, m),
                        torch.full((m,), 4.0, dtype=torch.float64))
+
+
+def test_neighbor_hook_methods_agree_and_width_shrinks():
+    """``method="naive"`` and the cell list give the same neighbour sets; a matrix much wider than needed shrinks after a
+    few rebuilds; unknown methods and the accepted-but-ineffective ``compile`` switches say so."""
+    import warnings
+    from types import SimpleNamespace
+
+    import pytest
+    import torch
+
+    from nvalchemi_toolkit_b200 import Batch
+    from nvalchemi_toolkit_b200.distributed import DomainConfig
+    from nvalchemi_toolkit_b200.hooks.neighbor_list import NeighborListHook
+    from nvalchemi_toolkit_b200.models.base import NeighborConfig, NeighborListFormat
+    from tests.helpers import fcc_supercell
+
+    cfg = NeighborConfig(cutoff=4.0, format=NeighborListFormat.MATRIX)
+    sets = {}
+    for method in ("cell_list", "naive"):
+        b = Batch.from_data_list([fcc_supercell(2, noise=0.05, seed=1, dtype=torch.float64)])
+        h = NeighborListHook(cfg, method=method)
+        h(SimpleNamespace(batch=b), None)
+        nm, num = b.neighbor_matrix, b.num_neighbors
+        sets[method] = [sorted(nm[i, : int(num[i])].tolist()) for i in range(b.num_nodes)]
+    assert sets["cell_list"] == sets["naive"]
+    with pytest.raises(ValueError):
+        NeighborListHook(cfg, method="octree")
+    b = Batch.from_data_list([fcc_supercell(2, noise=0.05, seed=1, dtype=torch.float64)])
+    h = NeighborListHook(cfg)
+    h.shrink_after = 2
+    h(SimpleNamespace(batch=b), None)
+    h._alloc(b, 512)  # pretend an earlier, denser state had widened the matrix
+    for _ in range(3):
+        h(SimpleNamespace(batch=b), None)
+    assert b.neighbor_matrix.shape[1] < 512 and int(b.num_neighbors.max()) <= b.neighbor_matrix.shape[1]
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        DomainConfig(cutoff=5.0, compile=True)
+    assert any("no effect" in str(x.message) for x in w)
