@@ -397,10 +397,10 @@ void defrag_segmented(Tensor source, Tensor source_batch_ptr, Tensor source_data
 }  // namespace nva
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
-  m.def("compute_put_fit_mask_per_system(Tensor source_mask, Tensor dest_mask, Tensor(a!) fit_mask) -> ()", &nva::compute_put_fit_mask_per_system);
-  m.def("put_masked_per_system(Tensor source, Tensor source_mask, Tensor(a!) dest, Tensor(b!) dest_mask, Tensor(c!) source_data_copied) -> ()", &nva::put_masked_per_system);
-  m.def("defrag_per_system(Tensor(a!) source, Tensor(b!) source_data_copied) -> ()", &nva::defrag_per_system);
-  m.def("compute_put_fit_mask_segmented(Tensor source_batch_ptr, Tensor source_mask, Tensor dest_batch_ptr, int num_dest_segments, int dest_capacity, Tensor(a!) fit_mask) -> ()", &nva::compute_put_fit_mask_segmented);
-  m.def("put_masked_segmented(Tensor source, Tensor source_batch_ptr, Tensor source_mask, Tensor(a!) dest, Tensor(b!) dest_batch_ptr, Tensor(c!) source_data_copied, Tensor(d!) new_num_dest, int num_dest_segments) -> ()", &nva::put_masked_segmented);
-  m.def("defrag_segmented(Tensor(a!) source, Tensor(b!) source_batch_ptr, Tensor(c!) source_data_copied, Tensor(d!) temp, Tensor(e!) num_kept) -> ()", &nva::defrag_segmented);
+  m.def("compute_put_fit_mask_per_system(Tensor source_mask, Tensor dest_mask, Tensor(a!) fit_mask) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::compute_put_fit_mask_per_system));
+  m.def("put_masked_per_system(Tensor source, Tensor source_mask, Tensor(a!) dest, Tensor(b!) dest_mask, Tensor(c!) source_data_copied) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::put_masked_per_system));
+  m.def("defrag_per_system(Tensor(a!) source, Tensor(b!) source_data_copied) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::defrag_per_system));
+  m.def("compute_put_fit_mask_segmented(Tensor source_batch_ptr, Tensor source_mask, Tensor dest_batch_ptr, int num_dest_segments, int dest_capacity, Tensor(a!) fit_mask) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::compute_put_fit_mask_segmented));
+  m.def("put_masked_segmented(Tensor source, Tensor source_batch_ptr, Tensor source_mask, Tensor(a!) dest, Tensor(b!) dest_batch_ptr, Tensor(c!) source_data_copied, Tensor(d!) new_num_dest, int num_dest_segments) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::put_masked_segmented));
+  m.def("defrag_segmented(Tensor(a!) source, Tensor(b!) source_batch_ptr, Tensor(c!) source_data_copied, Tensor(d!) temp, Tensor(e!) num_kept) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::defrag_segmented));
 }

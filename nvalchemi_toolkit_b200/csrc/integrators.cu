@@ -385,15 +385,15 @@ void neighbor_rebuild_check(Tensor ref_pos, const Tensor& pos, const Tensor& bat
 }  // namespace nva
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
-  m.def("vv_position_update(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor masses, Tensor dt, Tensor batch_idx) -> ()", &nva::vv_position_update);
-  m.def("vv_velocity_finalize(Tensor(a!) velocities, Tensor forces_new, Tensor masses, Tensor dt, Tensor batch_idx) -> ()", &nva::vv_velocity_finalize);
-  m.def("langevin_half_step(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor masses, Tensor dt, Tensor temperature, Tensor friction, int random_seed, Tensor batch_idx, Tensor? atom_ids=None) -> ()", &nva::langevin_half_step);
-  m.def("langevin_finalize(Tensor(a!) velocities, Tensor forces_new, Tensor masses, Tensor dt, Tensor batch_idx) -> ()", &nva::vv_velocity_finalize);
-  m.def("compute_kinetic_energy(Tensor velocities, Tensor masses, Tensor batch_idx, int num_systems) -> Tensor", &nva::compute_kinetic_energy);
-  m.def("_fire_step_op(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor masses, Tensor(c!) alpha, Tensor(d!) dt, Tensor alpha_start, Tensor f_alpha, Tensor dt_min, Tensor dt_max, Tensor maxstep, Tensor(e!) n_steps_positive, Tensor n_min, Tensor f_dec, Tensor f_inc, Tensor uphill_flag, Tensor(f!) vf, Tensor(g!) vv, Tensor(h!) ff, Tensor batch_idx, bool compute_reductions, Tensor? max_dr=None, int phase=0) -> ()", &nva::fire_step);
+  m.def("vv_position_update(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor masses, Tensor dt, Tensor batch_idx) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::vv_position_update));
+  m.def("vv_velocity_finalize(Tensor(a!) velocities, Tensor forces_new, Tensor masses, Tensor dt, Tensor batch_idx) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::vv_velocity_finalize));
+  m.def("langevin_half_step(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor masses, Tensor dt, Tensor temperature, Tensor friction, int random_seed, Tensor batch_idx, Tensor? atom_ids=None) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::langevin_half_step));
+  m.def("langevin_finalize(Tensor(a!) velocities, Tensor forces_new, Tensor masses, Tensor dt, Tensor batch_idx) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::vv_velocity_finalize));
+  m.def("compute_kinetic_energy(Tensor velocities, Tensor masses, Tensor batch_idx, int num_systems) -> Tensor", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::compute_kinetic_energy));
+  m.def("_fire_step_op(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor masses, Tensor(c!) alpha, Tensor(d!) dt, Tensor alpha_start, Tensor f_alpha, Tensor dt_min, Tensor dt_max, Tensor maxstep, Tensor(e!) n_steps_positive, Tensor n_min, Tensor f_dec, Tensor f_inc, Tensor uphill_flag, Tensor(f!) vf, Tensor(g!) vv, Tensor(h!) ff, Tensor batch_idx, bool compute_reductions, Tensor? max_dr=None, int phase=0) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::fire_step));
   m.def("maxwell_boltzmann(Tensor(a!) velocities, Tensor masses, Tensor kT, Tensor batch_idx, int seed, Tensor? atom_ids=None) -> ()", &nva::maxwell_boltzmann);
-  m.def("momentum_sums(Tensor velocities, Tensor masses, Tensor batch_idx, int num_systems) -> Tensor", &nva::momentum_sums);
-  m.def("velocity_shift_scale(Tensor(a!) velocities, Tensor shift, Tensor scale, Tensor batch_idx) -> ()", &nva::velocity_shift_scale);
-  m.def("wrap_positions(Tensor positions, Tensor cell, Tensor cell_inv, Tensor pbc, Tensor batch_idx) -> Tensor", &nva::wrap_positions);
+  m.def("momentum_sums(Tensor velocities, Tensor masses, Tensor batch_idx, int num_systems) -> Tensor", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::momentum_sums));
+  m.def("velocity_shift_scale(Tensor(a!) velocities, Tensor shift, Tensor scale, Tensor batch_idx) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::velocity_shift_scale));
+  m.def("wrap_positions(Tensor positions, Tensor cell, Tensor cell_inv, Tensor pbc, Tensor batch_idx) -> Tensor", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::wrap_positions));
   m.def("neighbor_rebuild_check(Tensor(a!) reference_positions, Tensor current_positions, Tensor batch_idx, Tensor(b!) rebuild_flags, float threshold, bool update_reference_positions, Tensor cell, Tensor cell_inv, Tensor pbc) -> ()", &nva::neighbor_rebuild_check);
 }

@@ -226,10 +226,10 @@ void affine_rows_(Tensor x, const Tensor& A, const c10::optional<Tensor>& y, con
 }  // namespace nva
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
-  m.def("nhc_chain_update(Tensor(a!) velocities, Tensor masses, Tensor(b!) eta, Tensor(c!) eta_dot, Tensor Q, Tensor temperature, Tensor dt, Tensor ndof, Tensor(d!) ke2, Tensor(e!) total_scale, Tensor(f!) step_scale, Tensor(g!) dt_chain, Tensor batch_idx, bool compute_ke, int yoshida_order=3) -> ()", &nva::nhc_chain_update);
-  m.def("nhc_chain_scalar(Tensor(a!) ke2, Tensor(b!) eta, Tensor(c!) eta_dot, Tensor Q, Tensor temperature, Tensor ndof, Tensor dt, int yoshida_order=3) -> Tensor", &nva::nhc_chain_scalar);
-  m.def("nhc_velocity_half_step(Tensor(a!) velocities, Tensor forces, Tensor masses, Tensor dt, Tensor batch_idx) -> ()", &nva::nhc_velocity_half_step);
-  m.def("nhc_position_update(Tensor(a!) positions, Tensor velocities, Tensor dt, Tensor batch_idx) -> ()", &nva::nhc_position_update);
-  m.def("compute_kinetic_tensor(Tensor velocities, Tensor masses, Tensor(a!) kinetic_tensors, Tensor batch_idx) -> ()", &nva::compute_kinetic_tensor);
-  m.def("affine_rows_(Tensor(a!) x, Tensor A, Tensor? y, Tensor? C, Tensor? forces, Tensor? masses, Tensor? kick, Tensor batch_idx, bool kick_first=False) -> ()", &nva::affine_rows_);
+  m.def("nhc_chain_update(Tensor(a!) velocities, Tensor masses, Tensor(b!) eta, Tensor(c!) eta_dot, Tensor Q, Tensor temperature, Tensor dt, Tensor ndof, Tensor(d!) ke2, Tensor(e!) total_scale, Tensor(f!) step_scale, Tensor(g!) dt_chain, Tensor batch_idx, bool compute_ke, int yoshida_order=3) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::nhc_chain_update));
+  m.def("nhc_chain_scalar(Tensor(a!) ke2, Tensor(b!) eta, Tensor(c!) eta_dot, Tensor Q, Tensor temperature, Tensor ndof, Tensor dt, int yoshida_order=3) -> Tensor", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::nhc_chain_scalar));
+  m.def("nhc_velocity_half_step(Tensor(a!) velocities, Tensor forces, Tensor masses, Tensor dt, Tensor batch_idx) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::nhc_velocity_half_step));
+  m.def("nhc_position_update(Tensor(a!) positions, Tensor velocities, Tensor dt, Tensor batch_idx) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::nhc_position_update));
+  m.def("compute_kinetic_tensor(Tensor velocities, Tensor masses, Tensor(a!) kinetic_tensors, Tensor batch_idx) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::compute_kinetic_tensor));
+  m.def("affine_rows_(Tensor(a!) x, Tensor A, Tensor? y, Tensor? C, Tensor? forces, Tensor? masses, Tensor? kick, Tensor batch_idx, bool kick_first=False) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::affine_rows_));
 }

@@ -64,7 +64,40 @@ def build(force: bool = False, verbose: bool = False) -> str:
     shutil.copyfile(built, LIB_PATH)
     global _loaded
     _loaded = True  # cpp_extension.load already registered the ops in this process
+    _register_fakes()
     return LIB_PATH
+
+
+_fakes_done = False
+
+
+def _register_fakes() -> None:
+    """``torch.library.register_fake`` for the operators dynamics code calls, so that a function using them can be traced
+    (``torch.compile(fullgraph=True)``, ``make_fx``) without entering the kernels: they become opaque graph nodes, as the
+    reference's custom ops are (``nvalchemi/dynamics/_ops/velocity_verlet.py:50-143``).  Runs once, after the library
+    has been loaded."""
+    global _fakes_done
+    if _fakes_done:
+        return
+    _fakes_done = True
+    nothing = [
+        "vv_position_update", "vv_velocity_finalize", "langevin_half_step", "langevin_finalize", "nhc_chain_update",
+        "nhc_velocity_half_step", "nhc_position_update", "compute_kinetic_tensor", "affine_rows_", "_fire_step_op",
+        "velocity_shift_scale", "compute_put_fit_mask_per_system", "put_masked_per_system", "defrag_per_system",
+        "compute_put_fit_mask_segmented", "put_masked_segmented", "defrag_segmented"]
+    shaped = {
+        "compute_kinetic_energy": lambda v, m, b, n: v.new_empty(n),
+        "nhc_chain_scalar": lambda ke2, *a, **k: torch.empty_like(ke2),
+        "momentum_sums": lambda v, m, b, n: v.new_empty(n, 4),
+        "wrap_positions": lambda p, *a, **k: torch.empty_like(p),
+    }
+    for name in nothing:
+        shaped[name] = lambda *a, **k: None
+    for name, fn in shaped.items():
+        try:
+            torch.library.register_fake(f"nvalchemi::{name}")(fn)
+        except (RuntimeError, ValueError):  # operator absent from an older build of the library
+            pass
 
 
 def available() -> bool:
@@ -74,6 +107,7 @@ def available() -> bool:
         if os.path.exists(LIB_PATH):
             torch.ops.load_library(LIB_PATH)
             _loaded = True
+            _register_fakes()
         else:
             _loaded = False
             if torch.cuda.is_available() and not os.environ.get("NVALCHEMI_B200_ALLOW_FALLBACK"):

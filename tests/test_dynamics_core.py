@@ -166,3 +166,31 @@ def test_neighbor_hook_methods_agree_and_width_shrinks():
         warnings.simplefilter("always")
         DomainConfig(cutoff=5.0, compile=True)
     assert any("no effect" in str(x.message) for x in w)
+
+
+def test_native_integrator_ops_trace_as_opaque_nodes():
+    """A velocity-Verlet step written with the native operators traces under ``torch.compile(fullgraph=True)`` (the
+    operators carry fake implementations) and gives the eager result."""
+    import pytest
+    import torch
+
+    from nvalchemi_toolkit_b200.ops import _native
+
+    if not _native.available():
+        pytest.skip("native library not built")
+    import nvalchemi_toolkit_b200.ops.compat  # noqa: F401  (registers the fake implementations)
+
+    def step(pos, vel, frc, mass, dt, b):
+        torch.ops.nvalchemi.vv_position_update(pos, vel, frc, mass, dt, b)
+        torch.ops.nvalchemi.vv_velocity_finalize(vel, frc, mass, dt, b)
+        return torch.ops.nvalchemi.compute_kinetic_energy(vel, mass, b, 2)
+
+    def state():
+        g = torch.Generator().manual_seed(0)
+        return (torch.randn(10, 3, generator=g), torch.randn(10, 3, generator=g), torch.randn(10, 3, generator=g),
+                torch.rand(10, generator=g) + 1.0, torch.tensor([0.5, 0.25]), torch.tensor([0] * 6 + [1] * 4, dtype=torch.int32))
+
+    a, b = state(), state()
+    ke_eager = step(*a)
+    ke_traced = torch.compile(step, fullgraph=True, backend="eager")(*b)
+    assert torch.allclose(ke_eager, ke_traced) and torch.allclose(a[0], b[0]) and torch.allclose(a[1], b[1])
