@@ -204,7 +204,9 @@ def main(argv: list[str] | None = None) -> int:
     r.add_argument("--max-steps", type=int, default=None)
     t = sub.add_parser("train")
     t.add_argument("--structures", type=int, default=1024, help="size of the synthetic training set (whole job)")
-    t.add_argument("--batch", type=int, default=64)
+    t.add_argument("--batch", type=int, default=8,
+                   help="structures per rank and step (the differentiable PyTorch path keeps every per-edge tensor for the "
+                        "double backward: 64 structures of this size need more than 180 GB)")
     t.add_argument("--steps", type=int, default=8)
     t.add_argument("--warmup", type=int, default=2)
     t.add_argument("--backend", default="torch", choices=["torch"], help="differentiable path used under autograd")

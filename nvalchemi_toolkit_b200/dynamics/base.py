@@ -690,6 +690,8 @@ class FusedStage(BaseDynamics):
             if self.sampler is None:
                 raise ValueError("No batch provided and no sampler configured.")
             batch = self.sampler.build_initial_batch()
+            if batch.device.type != self.device_type:  # datasets live on the host; the workflow runs on its device
+                batch = batch.to(self.device)
             if self.init_fn is not None:
                 self.init_fn(batch)
             self.active_batch = batch
