@@ -5,7 +5,8 @@ barrier, timed on the device with CUDA events and reported as the maximum over r
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m nvalchemi_toolkit_b200.benchmark.halo_bandwidth
 
 Every rank pulls ``--rows`` ghost rows from each of ``--peers`` other ranks (rows spread with a stride over the owner's
-buffer, as boundary atoms are) and returns as many gradient rows.  Row widths: 512 floats (sender features of a
+buffer, as boundary atoms are) and returns as many gradient rows, once by remote reductions issued by the holder
+(``push_add``) and once by the owner fetching its copies (``pull_add``, the path the MD engine uses).  Row widths: 512 floats (sender features of a
 ``128x0e+128x1o`` layer) and 3 floats (positions / forces).  The roofline is the bytes that cross NVLink divided by the
 per-direction link bandwidth (``--link-gbs``)."""
 from __future__ import annotations
@@ -77,6 +78,12 @@ def main() -> None:
         ms = _time(lambda: ops.halo_push_add_rows(buf, args.owned, home_rank, home_row, ptrs), args.iters)
         nbytes = g * width * 4
         res[f"push_add_{name}"] = {"ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "of_link": nbytes / ms / 1e6 / args.link_gbs}
+    # the same gradient rows fetched by their owners instead (plain peer loads + local reductions)
+    ghost_row = (args.owned + torch.arange(g, device=dev, dtype=torch.int32)).contiguous()
+    for name, buf, ptrs, width in (("features_512", grad, grad_ptrs, 512), ("positions_3", gpos, gpos_ptrs, 3)):
+        ms = _time(lambda: ops.halo_pull_add_rows(buf, home_row, home_rank, ghost_row, ptrs), args.iters)
+        nbytes = g * width * 4
+        res[f"pull_add_{name}"] = {"ms": ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "of_link": nbytes / ms / 1e6 / args.link_gbs}
     res["barrier_us"] = 1e3 * _time(p2p.barrier, 200)
     res["status"] = p2p.status()
     if rank == 0:

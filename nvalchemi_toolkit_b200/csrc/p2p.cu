@@ -309,3 +309,85 @@ void halo_push_add_rows(const at::Tensor& src, int64_t row0, const at::Tensor& h
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("halo_push_add_rows(Tensor src, int row0, Tensor home_rank, Tensor home_row, Tensor dst_ptrs, Tensor? used=None) -> ()", &nva::halo_push_add_rows);
 }
+
+namespace nva {
+// Reverse halo by pull: the OWNER collects what the other ranks accumulated on their ghost copies of its rows,
+//   buf[dst_row[k], :] += buf_{peer[k]}[peer_row[k], :]      (same symmetric buffer on both sides),
+// with plain 16-byte peer loads (the fast direction of the link) and reductions into local memory; several entries may
+// name the same owned row (one per rank / periodic image that holds a copy), hence the local atomics.  `peer_used`
+// (optional): table of the peers' per-ghost "some edge used this row" bytes, indexed [peer] -> uint8*, with
+// `peer_used_index[k]` the ghost's position in that array; unused copies hold zeros and are skipped without reading them.
+__global__ void halo_pull_add_vec_kernel(int64_t n, int D4, float4* __restrict__ buf, const int* __restrict__ dst_row,
+                                         const int* __restrict__ peer, const int* __restrict__ peer_row,
+                                         const int64_t* __restrict__ ptrs, const int64_t* __restrict__ used_ptrs,
+                                         const int* __restrict__ used_index) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t k = warp; k < n; k += nwarps) {
+    const int p = peer[k];
+    if (used_ptrs != nullptr && reinterpret_cast<const uint8_t*>(used_ptrs[p])[used_index[k]] == 0) continue;
+    const float4* src = reinterpret_cast<const float4*>(ptrs[p]) + (int64_t)peer_row[k] * D4;
+    float4* out = buf + (int64_t)dst_row[k] * D4;
+    for (int c0 = 0; c0 < D4; c0 += 128) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < D4) v[u] = src[c];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < D4 && (v[u].x != 0.f || v[u].y != 0.f || v[u].z != 0.f || v[u].w != 0.f)) atomicAdd(out + c, v[u]);
+      }
+    }
+  }
+}
+
+__global__ void halo_pull_add_narrow_kernel(int64_t n, int D, float* __restrict__ buf, const int* __restrict__ dst_row,
+                                            const int* __restrict__ peer, const int* __restrict__ peer_row,
+                                            const int64_t* __restrict__ ptrs, const int64_t* __restrict__ used_ptrs,
+                                            const int* __restrict__ used_index) {
+  const int64_t k = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (k >= n) return;
+  const int p = peer[k];
+  if (used_ptrs != nullptr && reinterpret_cast<const uint8_t*>(used_ptrs[p])[used_index[k]] == 0) return;
+  const float* src = reinterpret_cast<const float*>(ptrs[p]) + (int64_t)peer_row[k] * D;
+  float* out = buf + (int64_t)dst_row[k] * D;
+  for (int d = 0; d < D; ++d) {
+    const float v = src[d];
+    if (v != 0.f) atomicAdd(out + d, v);
+  }
+}
+
+void halo_pull_add_rows(at::Tensor buf, const at::Tensor& dst_row, const at::Tensor& peer, const at::Tensor& peer_row,
+                        const at::Tensor& ptrs, const c10::optional<at::Tensor>& used_ptrs,
+                        const c10::optional<at::Tensor>& used_index) {
+  c10::cuda::CUDAGuard guard(buf.device());
+  NVA_CHECK_CONTIG(buf);
+  const int64_t n = dst_row.size(0);
+  if (n == 0) return;
+  TORCH_CHECK(peer.size(0) == n && peer_row.size(0) == n, "halo_pull_add_rows: tables of different lengths");
+  TORCH_CHECK(used_ptrs.has_value() == used_index.has_value(), "halo_pull_add_rows: used_ptrs and used_index come together");
+  const int D = (int)(buf.numel() / buf.size(0));
+  const int64_t* up = used_ptrs.has_value() ? used_ptrs->data_ptr<int64_t>() : nullptr;
+  const int* ui = used_index.has_value() ? used_index->data_ptr<int>() : nullptr;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (D % 4 == 0 && (reinterpret_cast<uintptr_t>(buf.data_ptr()) & 15) == 0) {
+    const int64_t blocks = std::min<int64_t>((n + 7) / 8, 148 * 16);
+    halo_pull_add_vec_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+        n, D / 4, reinterpret_cast<float4*>(buf.data_ptr<float>()), dst_row.data_ptr<int>(), peer.data_ptr<int>(),
+        peer_row.data_ptr<int>(), ptrs.data_ptr<int64_t>(), up, ui);
+  } else {
+    halo_pull_add_narrow_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+        n, D, buf.data_ptr<float>(), dst_row.data_ptr<int>(), peer.data_ptr<int>(), peer_row.data_ptr<int>(),
+        ptrs.data_ptr<int64_t>(), up, ui);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+}  // namespace nva
+
+TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
+  m.def("halo_pull_add_rows(Tensor(a!) buf, Tensor dst_row, Tensor peer, Tensor peer_row, Tensor ptrs, Tensor? used_ptrs=None, Tensor? used_index=None) -> ()", &nva::halo_pull_add_rows);
+}

@@ -205,6 +205,11 @@ class HaloExchange:
         """Ghost rows from rows that are already in send order (one per entry of ``send_index``)."""
         return all_to_all_rows(send_rows, self.send_splits, self.recv_splits, self.group)
 
+    def reverse_packed(self, ghost_rows: torch.Tensor) -> torch.Tensor:
+        """One row per ghost travels back to the rank that sent it; the result is in send order (one row per entry of
+        ``send_index``).  No accumulation: use :meth:`reverse_add` for that."""
+        return all_to_all_rows(ghost_rows, self.recv_splits, self.send_splits, self.group)
+
     def forward_positions(self, positions: torch.Tensor, cell: torch.Tensor) -> torch.Tensor:
         """Ghost positions: owner positions plus the recorded lattice shift."""
         shifted = positions[self.send_index] + self.send_shift.to(positions.dtype) @ cell.reshape(3, 3).to(positions.dtype)

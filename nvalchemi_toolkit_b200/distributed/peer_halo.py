@@ -56,12 +56,23 @@ def build_pull_tables(sharded: Any) -> dict[str, torch.Tensor]:
 
     ``home_rank [G] int32`` / ``home_row [G] int32``: owner rank of every ghost row and its row among the owner's atoms;
     ``ghost_image [G, 3]``: lattice image to add (times the cell) to the owner's row *as the owner stores it*, i.e. in
-    the owner's frame ``positions + wrap_image @ cell``; ``wrap_image [N_owned, 3]``: this rank's own frame."""
+    the owner's frame ``positions + wrap_image @ cell``; ``wrap_image [N_owned, 3]``: this rank's own frame;
+    ``send_row / send_peer / send_peer_row / send_used_index [S]``: for every row this rank sends, its own row, the rank
+    that holds the copy, the copy's row in that rank's local numbering and its index among that rank's ghosts."""
     halo = sharded.halo
     n = sharded.n_owned
     dev = sharded.owned.positions.device
     image = halo.send_shift - halo.wrap_shift[halo.send_index]  # image relative to the owner's own frame
+    ng = halo.n_ghost
+    ghost_ids = torch.arange(ng, dtype=torch.int32, device=dev)
+    world = max(1, len(halo.send_splits))
     return {
+        # reverse path (owner pulls): for every row this rank sends, the rank holding the copy and the copy's row there
+        "send_row": halo.send_index.to(torch.int32).contiguous(),
+        "send_peer": torch.repeat_interleave(torch.arange(world, dtype=torch.int32, device=dev),
+                                             torch.tensor(halo.send_splits, device=dev)).contiguous(),
+        "send_used_index": halo.reverse_packed(ghost_ids).contiguous(),
+        "send_peer_row": halo.reverse_packed(ghost_ids + n).contiguous(),
         "home_rank": halo.ghost_owner_rank.to(torch.int32).contiguous(),
         "home_row": halo.forward(torch.arange(n, dtype=torch.int32, device=dev)).contiguous(),
         "ghost_image": halo.forward_packed(image.to(torch.float32).contiguous()).contiguous(),
@@ -74,6 +85,9 @@ class PeerHaloEngine:
 
     #: rows are pulled / returned in bulk once per layer (the convolution kernels then work on local memory)
     prefetch = True
+    #: gradients on ghost rows come home by the OWNER pulling them (plain peer loads + local reductions, the fast
+    #: direction of the link) instead of the holder pushing remote reductions
+    reverse_pull = True
 
     def __init__(self, wrapper: Any, config: Any, group: Any = None, max_neighbors: int | None = None) -> None:
         self.wrapper, self.model, self.config = wrapper, wrapper.model, config
@@ -124,10 +138,11 @@ class PeerHaloEngine:
         widths = [sum(2 * l + 1 for l in ip.l_in) for ip in self.model.interactions]
         floats = cap * (3 + 3 + sum(w * C for w in widths) + sum(w * C for w in widths[1:]))
         self.p2p = None  # release the previous arena before asking for a larger one
-        self.p2p = P2PContext(4 * floats + 256 * (4 + 2 * len(widths)) + (1 << 16), device, self.group)
+        self.p2p = P2PContext(4 * floats + cap + 256 * (5 + 2 * len(widths)) + (1 << 16), device, self.group)
         a = self.p2p.arena
         self.pos_buf, self.pos_ptrs = a.alloc((cap, 3))
         self.gpos_buf, self.gpos_ptrs = a.alloc((cap, 3))
+        self.used_buf, self.used_ptrs = a.alloc((cap,), torch.uint8)
         self.feat = {}
         for li, w in enumerate(widths):
             self.feat[f"u{li}"] = a.alloc((cap, w, C))
@@ -156,7 +171,10 @@ class PeerHaloEngine:
         self.batch_ptr = torch.tensor([0, n + ng], dtype=torch.int32, device=dev)
         self.batch_long = torch.zeros(n + ng, dtype=torch.long, device=dev)
         self.pbc = halo.local_pbc.reshape(1, 3).to(dev)
-        self.ghost_used = torch.zeros(ng, dtype=torch.uint8, device=dev)
+        self.ghost_used = self.used_buf[:ng]  # in the arena: owners read their copies' flags on the reverse path
+        self.ghost_used.zero_()
+        self.send_row, self.send_peer = tables["send_row"], tables["send_peer"]
+        self.send_used_index, self.send_peer_row = tables["send_used_index"], tables["send_peer_row"]
         self._nl = self._nl_ref = self._csr = None
         self._sums = torch.zeros(10, dtype=torch.float64, device=dev)
         self._bound = key

@@ -585,11 +585,18 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         del dmid, dmsg
         if pull:
             # return what was accumulated on ghost rows to the owners, once per row
-            dd.barrier()  # owners finished their own accumulation
-            if li > 0:
-                ops.halo_push_add_rows(du, n, dd.ghost_home_rank, dd.ghost_home_row, du_ptrs, used)
-            if li == 0:
-                ops.halo_push_add_rows(grad_pos[:dd.n_local], n, dd.ghost_home_rank, dd.ghost_home_row, dd.gpos_ptrs, used)
+            dd.barrier()  # owners finished their own accumulation, holders finished theirs on the ghost copies
+            if getattr(dd, "reverse_pull", False):
+                rev = (dd.send_row, dd.send_peer, dd.send_peer_row)
+                if li > 0:
+                    ops.halo_pull_add_rows(du, *rev, du_ptrs, dd.used_ptrs, dd.send_used_index)
+                if li == 0:
+                    ops.halo_pull_add_rows(grad_pos, *rev, dd.gpos_ptrs, dd.used_ptrs, dd.send_used_index)
+            else:
+                if li > 0:
+                    ops.halo_push_add_rows(du, n, dd.ghost_home_rank, dd.ghost_home_row, du_ptrs, used)
+                if li == 0:
+                    ops.halo_push_add_rows(grad_pos[:dd.n_local], n, dd.ghost_home_rank, dd.ghost_home_row, dd.gpos_ptrs, used)
         if dd is not None:
             dd.barrier()  # feature / position gradients pushed by peers have landed
         if li > 0 and dd is not None:

@@ -32,7 +32,19 @@ def _worker(rank: int, world: int, port: int, grid, q) -> None:
         rows_ok = bool((t["home_row"].long() < torch.tensor(counts)[t["home_rank"].long()]).all())
         ghost = allbuf[start[t["home_rank"].long()] + t["home_row"].long()] + t["ghost_image"] @ cell
         ref = sh.halo.forward_positions(sh.owned.positions, sh.cell)
+        # reverse path: every owner pulls what the holders accumulated on their copies of its rows
+        g = torch.Generator().manual_seed(10 + rank)
+        local = torch.randn(sh.n_owned + sh.n_ghost, 4, generator=g)
+        every, cnt = all_gather_rows(local)
+        base = torch.cumsum(torch.tensor([0] + cnt[:-1]), 0)
+        pulled = local[: sh.n_owned].clone()
+        pulled.index_add_(0, t["send_row"].long(), every[base[t["send_peer"].long()] + t["send_peer_row"].long()])
+        want = sh.halo.reverse_add(local[sh.n_owned:].clone(), local[: sh.n_owned].clone())
+        n_ghost_of = torch.tensor([c for c in cnt]) - torch.tensor(counts)
+        used_ok = bool((t["send_used_index"].long() < n_ghost_of[t["send_peer"].long()]).all()) and \
+            bool((t["send_peer_row"].long() - t["send_used_index"].long() == torch.tensor(counts)[t["send_peer"].long()]).all())
         q.put((rank, {"err": float((ghost - ref).abs().max()), "rows_ok": rows_ok, "ghost": sh.n_ghost,
+                      "rev_err": float((pulled - want).abs().max()), "used_ok": used_ok,
                       "local_pbc": sh.halo.local_pbc.tolist()}))
         dist.barrier()
         dist.destroy_process_group()
@@ -59,4 +71,5 @@ def test_pull_tables_reproduce_plan_positions(world, grid):
     for r, res in results.items():
         assert "error" not in res, res["error"]
         assert res["rows_ok"] and res["ghost"] > 0 and res["err"] < 1e-5
+        assert res["rev_err"] < 1e-5 and res["used_ok"]
         assert res["local_pbc"] == [g == 1 for g in grid]
