@@ -25,6 +25,9 @@ from nvalchemi_toolkit_b200.ops._native_counter import ops  # noqa: E402
 
 #: upper bound on the radial-weight scratch per chunk (bytes); [E_chunk, 2, P, C] floats in the backward
 CHUNK_BYTES = 2 << 30
+#: chunk bound while the radial activations are kept for the adjoint anyway (the buffers are pooled and resident, so
+#: small chunks would only multiply kernel launches: eleven chunks per layer at 1 M atoms with the bound above)
+CACHED_CHUNK_BYTES = 24 << 30
 
 
 @dataclass
@@ -81,9 +84,10 @@ def csr_from_edge_index(edge_index: torch.Tensor, unit_shifts: torch.Tensor | No
                    None, int(order.numel()))
 
 
-def _chunks(csr: EdgeCSR, n: int, bytes_per_edge: int) -> list[tuple[int, int, int, int]]:
-    """Receiver ranges ``(i0, i1, e0, e1)`` whose radial scratch stays below ``CHUNK_BYTES``."""
-    max_edges = max(CHUNK_BYTES // max(bytes_per_edge, 1), 1024)
+def _chunks(csr: EdgeCSR, n: int, bytes_per_edge: int, limit: int | None = None) -> list[tuple[int, int, int, int]]:
+    """Receiver ranges ``(i0, i1, e0, e1)`` whose radial scratch stays below ``limit`` (default ``CHUNK_BYTES``)."""
+    max_edges = max((limit or CHUNK_BYTES) // max(bytes_per_edge, 1), 1024)
+    max_edges = min(max_edges, (1 << 30) - 1)  # two rows per edge must stay addressable by 32-bit TMA coordinates
     if csr.num_edges <= max_edges:
         return [(0, n, 0, csr.num_edges)]
     if csr.eptr_host is None:
@@ -423,7 +427,8 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
 
     def radial_chunks(ws_: list, store: list | None, layer: int) -> Any:
         """Chunks ``(i0, i1, e0, e1, h3 value rows)``; with ``store`` the tangent rows are computed too and kept."""
-        for ci, (i0_, i1_, e0_, e1_) in enumerate(_chunks(csr, n, (8 if store is not None else 4) * 64)):
+        for ci, (i0_, i1_, e0_, e1_) in enumerate(_chunks(csr, n, (8 if store is not None else 4) * 64,
+                                                          CACHED_CHUNK_BYTES if store is not None else None)):
             ef_ = ops.mace_edge_radial(*geom, e0_, e1_ - e0_, rmax, nb, pc, store is not None)
             buf = _pooled((id(model), dev, layer, ci), (e1_ - e0_) * 128, pos) if store is not None else None
             h3_ = _hidden(ws_, ef_, store is not None, buf)
