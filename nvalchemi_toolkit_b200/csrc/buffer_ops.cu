@@ -394,6 +394,47 @@ void defrag_segmented(Tensor source, Tensor source_batch_ptr, Tensor source_data
   source.copy_(temp.view_as(source));
 }
 
+// ---- plan once, copy many ---------------------------------------------------------------------------------------
+// A buffer holds several arrays per level (positions, velocities, ...) that share one pointer array, so the container
+// plans a put / defrag ONCE and then moves every array with the same plan.  `count` is the device-resident number of live
+// segments of the destination (read and updated in place); no value returns to the host.
+// Returns plan[s] = first destination row of source segment s, or -1; `copied[s]` says whether segment s goes.  With
+// commit = false nothing is written but `copied` (the fit mask against the device-resident count).
+Tensor segmented_put_plan(const Tensor& source_batch_ptr, const Tensor& source_mask, Tensor dest_batch_ptr, Tensor count,
+                          int64_t dest_capacity, Tensor copied, bool commit) {
+  c10::cuda::OptionalCUDAGuard guard(source_mask.is_cuda() ? c10::make_optional(source_mask.device()) : c10::nullopt);
+  check_ptr(source_batch_ptr, "source_batch_ptr"); check_ptr(dest_batch_ptr, "dest_batch_ptr");
+  check_mask(source_mask, "source_mask"); check_mask(copied, "copied");
+  TORCH_CHECK(count.scalar_type() == at::kInt && count.numel() >= 1, "count must be an int32 tensor");
+  TORCH_CHECK(source_mask.numel() >= source_batch_ptr.numel() - 1 && copied.numel() >= source_batch_ptr.numel() - 1,
+              "masks are shorter than the number of source segments");
+  return run_segmented_plan(commit ? 1 : 0, source_batch_ptr, source_mask, dest_batch_ptr, -1, &count, dest_capacity,
+                            copied.data_ptr<bool>(), count.data_ptr<int>());
+}
+
+// Keeps the segments NOT flagged in `removed`; batch_ptr (the live prefix, n + 1 entries) is rebuilt in place and
+// count[0] receives the number kept.  Returns (plan, old batch_ptr) for segmented_copy_planned.
+std::tuple<Tensor, Tensor> segmented_defrag_plan(Tensor batch_ptr, const Tensor& removed, Tensor count) {
+  c10::cuda::OptionalCUDAGuard guard(removed.is_cuda() ? c10::make_optional(removed.device()) : c10::nullopt);
+  check_ptr(batch_ptr, "batch_ptr"); check_mask(removed, "removed");
+  TORCH_CHECK(count.scalar_type() == at::kInt && count.numel() >= 1, "count must be an int32 tensor");
+  TORCH_CHECK(removed.numel() >= batch_ptr.numel() - 1, "mask shorter than the number of segments");
+  Tensor old_ptr = batch_ptr.clone();
+  Tensor plan = run_segmented_plan(2, old_ptr, removed, batch_ptr, 0, nullptr, 0, nullptr, count.data_ptr<int>());
+  return std::make_tuple(plan, old_ptr);
+}
+
+// dest rows [plan[s], plan[s] + len(s)) <- source rows of segment s, for every s with plan[s] >= 0.  Source and
+// destination must not overlap (a defrag goes through a scratch array).
+void segmented_copy_planned(const Tensor& source, const Tensor& source_batch_ptr, const Tensor& plan, Tensor dest) {
+  c10::cuda::OptionalCUDAGuard guard(source.is_cuda() ? c10::make_optional(source.device()) : c10::nullopt);
+  check_ptr(source_batch_ptr, "source_batch_ptr");
+  NVA_CHECK_CONTIG(source); NVA_CHECK_CONTIG(dest);
+  TORCH_CHECK(source.scalar_type() == dest.scalar_type(), "segmented_copy_planned: dtype mismatch");
+  TORCH_CHECK(plan.scalar_type() == at::kInt && plan.numel() <= source_batch_ptr.numel() - 1, "plan does not match source_batch_ptr");
+  copy_segments(source, source_batch_ptr, plan, dest);
+}
+
 }  // namespace nva
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
@@ -403,4 +444,7 @@ TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("compute_put_fit_mask_segmented(Tensor source_batch_ptr, Tensor source_mask, Tensor dest_batch_ptr, int num_dest_segments, int dest_capacity, Tensor(a!) fit_mask) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::compute_put_fit_mask_segmented));
   m.def("put_masked_segmented(Tensor source, Tensor source_batch_ptr, Tensor source_mask, Tensor(a!) dest, Tensor(b!) dest_batch_ptr, Tensor(c!) source_data_copied, Tensor(d!) new_num_dest, int num_dest_segments) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::put_masked_segmented));
   m.def("defrag_segmented(Tensor(a!) source, Tensor(b!) source_batch_ptr, Tensor(c!) source_data_copied, Tensor(d!) temp, Tensor(e!) num_kept) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::defrag_segmented));
+  m.def("segmented_put_plan(Tensor source_batch_ptr, Tensor source_mask, Tensor(a!) dest_batch_ptr, Tensor(b!) count, int dest_capacity, Tensor(c!) copied, bool commit=True) -> Tensor", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::segmented_put_plan));
+  m.def("segmented_defrag_plan(Tensor(a!) batch_ptr, Tensor removed, Tensor(b!) count) -> (Tensor, Tensor)", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::segmented_defrag_plan));
+  m.def("segmented_copy_planned(Tensor source, Tensor source_batch_ptr, Tensor plan, Tensor(a!) dest) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::segmented_copy_planned));
 }

@@ -20,7 +20,7 @@ import torch.distributed as dist
 
 from nvalchemi_toolkit_b200.data.atomic_data import AtomicData, DataMixin
 from nvalchemi_toolkit_b200.data.level_storage import (
-    LevelSchema, MultiLevelStorage, SegmentedLevelStorage, UniformLevelStorage,
+    DeviceCounts, LevelSchema, MultiLevelStorage, SegmentedLevelStorage, UniformLevelStorage, _buffer_ops,
 )
 
 _INDEX_KEYS = frozenset({"neighbor_list"})
@@ -334,6 +334,10 @@ class Batch(DataMixin):
         receives the mask of graphs actually copied, for a following :meth:`defrag`.
         """
         mask = mask.to(self.device).bool().reshape(-1)[: src_batch.num_graphs]
+        ops = _buffer_ops()
+        if ops is not None and self._atoms_group is not None and src_batch._atoms_group is not None:
+            self._put_planned(ops, src_batch, mask.contiguous(), copied_mask)
+            return
         cand = torch.nonzero(mask).squeeze(1)
         na = src_batch.num_nodes_per_graph.long()[cand]
         fits = torch.arange(1, cand.numel() + 1, device=self.device) <= (self.system_capacity - self.num_graphs)
@@ -370,6 +374,81 @@ class Batch(DataMixin):
         else:
             object.__setattr__(src_batch, "_copied_mask", done)
 
+    # ---- device-planned put / defrag: masks in, masks out, counts stay on the device ---------------------------
+    def _put_planned(self, ops: Any, src: "Batch", mask: torch.Tensor, copied_mask: torch.Tensor | None) -> None:
+        """Masked put through the native planners (``segmented_put_plan`` / ``segmented_copy_planned``; the reference's
+        ``put_masked_segmented`` / ``put_masked_per_system`` chain, ``nvalchemi/data/level_storage.py``): the fit over
+        atoms, edges and systems, the slot assignment and every copy run on the device, and the new counts are read by
+        the host only when ``num_graphs`` / ``num_nodes`` / ``num_edges`` are next asked for."""
+        dev = self.device
+        n_src = src.num_graphs
+        a, e, sysg = self._atoms_group, self._edges_group, self._system_group
+        sa, se = src._atoms_group, src._edges_group
+        done = torch.zeros(max(n_src, 1), dtype=torch.bool, device=dev)[:n_src]
+        if n_src == 0:
+            self._publish_copied(src, done, copied_mask)
+            return
+        a_ptr = sa.batch_ptr
+        zero_ptr = torch.zeros(n_src + 1, dtype=torch.int32, device=dev)
+        e_ptr = se.batch_ptr if (e is not None and se is not None) else zero_ptr
+        fit = torch.empty_like(done)
+        a.put_masked(ops, a_ptr, mask, fit, {}, commit=False)              # fits the atom rows and the system slots
+        if e is not None:
+            fit_e = torch.empty_like(done)
+            e.put_masked(ops, e_ptr, fit, fit_e, {}, commit=False)        # ... and the edge rows
+            fit = fit_e  # a subset of a fitting set still fits the atoms: offsets only shrink
+        plan_a = a.put_masked(ops, a_ptr, fit, done, {k: v for k, v in sa.data.items()})
+        if e is not None:
+            src_edges: dict[str, torch.Tensor] = dict(se.data) if se is not None else {}
+            if "neighbor_list" in src_edges and "neighbor_list" in e.data and src.num_edges:
+                # re-base node indices: minus the graph's source offset, plus its destination offset
+                delta = (plan_a - a_ptr[:-1])[se.batch_idx.long()]
+                nl = src_edges["neighbor_list"][: src.num_edges]
+                src_edges["neighbor_list"] = nl + delta.to(nl.dtype)[:, None]
+            went_e = torch.empty_like(done)
+            e.put_masked(ops, e_ptr, fit, went_e, src_edges)
+        if sysg is not None:
+            sysg.put_masked(ops, src._system_group if src._system_group is not None else UniformLevelStorage({}, 0, 0), fit, n_src)
+        self._adopt_counts()
+        self._publish_copied(src, done, copied_mask)
+
+    def _adopt_counts(self) -> None:
+        a, e, sysg = self._atoms_group, self._edges_group, self._system_group
+        ptr_a, count_a = a.device_csr()
+        idx = count_a.long()
+        parts = [count_a, ptr_a[idx]]
+        if e is not None:
+            ptr_e, count_e = e.device_csr()
+            parts.append(ptr_e[count_e.long()])
+        counts = DeviceCounts(torch.cat([p.reshape(1) for p in parts]))
+        a._adopt_device_csr(counts, 0, 1)
+        if e is not None:
+            e._adopt_device_csr(counts, 0, 2)
+        if sysg is not None:
+            sysg.set_pending(counts, 0)
+
+    @staticmethod
+    def _publish_copied(src: "Batch", done: torch.Tensor, copied_mask: torch.Tensor | None) -> None:
+        if copied_mask is not None:
+            copied_mask[: done.numel()] = done
+        else:
+            object.__setattr__(src, "_copied_mask", done)
+
+    def _defrag_planned(self, ops: Any, removed: torch.Tensor, n: int) -> None:
+        a, e, sysg = self._atoms_group, self._edges_group, self._system_group
+        n_nodes, n_edges = self.num_nodes, self.num_edges
+        e_idx = e.batch_idx.long() if (e is not None and "neighbor_list" in e.data and n_edges) else None
+        plan_a, old_a = a.defrag_masked(ops, removed, n, n_nodes)
+        if e is not None:
+            if e_idx is not None:
+                delta = (plan_a - old_a[:-1])[e_idx]  # rows of dropped graphs get a meaningless shift and are dropped too
+                nl = e.data["neighbor_list"]
+                nl[:n_edges] += delta.to(nl.dtype)[:, None]
+            e.defrag_masked(ops, removed, n, n_edges)
+        if sysg is not None:
+            sysg.defrag_masked(ops, removed, n)
+        self._adopt_counts()
+
     def defrag(self, copied_mask: torch.Tensor | None = None) -> "Batch":
         """Remove the graphs flagged in ``copied_mask`` in place, keeping capacity."""
         if copied_mask is None:
@@ -377,6 +456,11 @@ class Batch(DataMixin):
             if copied_mask is None:
                 return self
         n = self.num_graphs
+        ops = _buffer_ops()
+        if ops is not None and self._atoms_group is not None:
+            self._defrag_planned(ops, copied_mask.to(self.device).bool().reshape(-1)[:n].contiguous(), n)
+            object.__setattr__(self, "_copied_mask", None)
+            return self
         keep = torch.nonzero(~copied_mask.to(self.device).bool()[:n]).squeeze(1)
         if keep.numel() == n:
             return self

@@ -110,6 +110,44 @@ class BaseLevelStorage:
         return None
 
 
+def _as(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    src = src if src.dtype == dst.dtype else src.to(dst.dtype)
+    return src if src.is_contiguous() else src.contiguous()
+
+
+def _compact_through_scratch(ops: Any, v: torch.Tensor, old_ptr: torch.Tensor, plan: torch.Tensor, n_rows: int) -> None:
+    """In-place compaction of the first ``n_rows`` rows of ``v``: kept segments go to a zeroed scratch copy and back, so
+    vacated rows end up zero and overlapping moves cannot clobber one another."""
+    if n_rows == 0:
+        return
+    head = v[:n_rows]
+    tmp = torch.zeros_like(head)
+    ops.segmented_copy_planned(head, old_ptr, plan, tmp)
+    head.copy_(tmp)
+
+
+class DeviceCounts:
+    """Row / segment counts that a device-side put or defrag produced, read back to the host only when someone asks.
+
+    ``tensor`` is a small int32 device vector; :meth:`host` copies it once (the only synchronisation of a masked put) and
+    caches the integers.  The storages of one batch share one instance, so the three levels resolve with one copy."""
+
+    def __init__(self, tensor: torch.Tensor) -> None:
+        self.tensor, self._host = tensor, None
+
+    def host(self) -> list[int]:
+        if self._host is None:
+            self._host = [int(x) for x in self.tensor.tolist()]
+        return self._host
+
+
+def _buffer_ops() -> Any:
+    """The native masked put / defrag operators, or ``None`` when the library is not built (pure-torch fallback)."""
+    from nvalchemi_toolkit_b200.ops import _native
+
+    return torch.ops.nvalchemi if _native.available() and hasattr(torch.ops.nvalchemi, "segmented_put_plan") else None
+
+
 class UniformLevelStorage(BaseLevelStorage):
     """Rows indexed by system; ``num_valid`` rows are live, the rest is spare capacity."""
 
@@ -118,7 +156,20 @@ class UniformLevelStorage(BaseLevelStorage):
         self.data = dict(data or {})
         cap = capacity if capacity is not None else (next(iter(self.data.values())).shape[0] if self.data else 0)
         self.capacity = int(cap)
+        self._pending: tuple[DeviceCounts, int] | None = None
+        self._count_dev: torch.Tensor | None = None
         self.num_valid = int(self.capacity if num_valid is None else num_valid)
+
+    @property
+    def num_valid(self) -> int:
+        if self._pending is not None:
+            counts, i = self._pending
+            self._n_valid, self._pending = counts.host()[i], None
+        return self._n_valid
+
+    @num_valid.setter
+    def num_valid(self, n: int) -> None:
+        self._n_valid, self._pending, self._count_dev = int(n), None, None
 
     def __getitem__(self, key: str) -> torch.Tensor:
         return self.data[key][: self.num_valid]
@@ -179,6 +230,39 @@ class UniformLevelStorage(BaseLevelStorage):
                 _buf.copy_rows(src.data[k], take, dst, dst_rows)
         self.num_valid += n
 
+    # ---- device-planned variants (no index lists, no counts on the host) ---------------------------------------
+    def _unit_ptr(self, n: int, device: torch.device) -> torch.Tensor:
+        """``[0, 1, ..., n]``: a uniform level is a segmented one whose segments all have one row."""
+        return torch.arange(n + 1, dtype=torch.int32, device=device)
+
+    def device_count(self, device: torch.device) -> torch.Tensor:
+        if self._count_dev is None:
+            self._count_dev = torch.tensor([self._n_valid], dtype=torch.int32).to(device, non_blocking=True)
+        return self._count_dev
+
+    def put_masked(self, ops: Any, src: "UniformLevelStorage", take: torch.Tensor, n_src: int) -> None:
+        """Append the rows of ``src`` flagged in ``take`` (bool, device) behind the live rows; the new row count stays on
+        the device until :attr:`num_valid` is read."""
+        dev = take.device
+        count = self.device_count(dev)
+        went = torch.empty(n_src, dtype=torch.bool, device=dev)
+        sp = self._unit_ptr(n_src, dev)
+        plan = ops.segmented_put_plan(sp, take, self._unit_ptr(self.capacity, dev), count, self.capacity, went, True)
+        for k, dst in self.data.items():
+            if k in src.data:
+                ops.segmented_copy_planned(_as(src.data[k], dst), sp, plan, dst)
+
+    def defrag_masked(self, ops: Any, removed: torch.Tensor, n_live: int) -> None:
+        dev = removed.device
+        count = self.device_count(dev)
+        ptr = self._unit_ptr(n_live, dev)
+        plan, old = ops.segmented_defrag_plan(ptr, removed, count)
+        for v in self.data.values():
+            _compact_through_scratch(ops, v, old, plan, n_live)
+
+    def set_pending(self, counts: DeviceCounts, index: int) -> None:
+        self._pending = (counts, index)  # the device counter stays valid: only the host copy is stale
+
     def defrag(self, keep: torch.Tensor) -> None:
         """Keep rows ``keep`` (sorted int64 indices of live rows); close the gaps in place."""
         n = int(keep.numel())
@@ -201,6 +285,8 @@ class SegmentedLevelStorage(BaseLevelStorage):
             lengths = torch.zeros(0, dtype=torch.int32, device=dev)
         self.lengths = lengths.to(torch.int32)  # [segment_capacity]; zero beyond num_segments
         self.segment_capacity = int(segment_capacity if segment_capacity is not None else self.lengths.numel())
+        self._pending: tuple[DeviceCounts, int, int] | None = None
+        self._csr_dev: tuple[torch.Tensor, torch.Tensor] | None = None
         self.num_segments = int(self.lengths.numel() if num_segments is None else num_segments)
         ecap = element_capacity
         if ecap is None:
@@ -211,10 +297,87 @@ class SegmentedLevelStorage(BaseLevelStorage):
         self._ptr: torch.Tensor | None = None
         self._idx: torch.Tensor | None = None
 
+    # ---- counts: host integers, or still on the device after a masked put / defrag --------------------------------
+    def _resolve(self) -> None:
+        if self._pending is not None:
+            counts, i_seg, i_elem = self._pending
+            host = counts.host()
+            self._n_seg, self._n_elem, self._pending = host[i_seg], host[i_elem], None
+
+    @property
+    def num_segments(self) -> int:
+        self._resolve()
+        return self._n_seg
+
+    @num_segments.setter
+    def num_segments(self, n: int) -> None:
+        self._resolve()
+        self._n_seg, self._csr_dev = int(n), None
+
+    @property
+    def num_elements(self) -> int:
+        self._resolve()
+        return self._n_elem
+
+    @num_elements.setter
+    def num_elements(self, n: int) -> None:
+        self._resolve()
+        self._n_elem, self._csr_dev = int(n), None
+
     # ---- lazily derived CSR views -------------------------------------------
     def _invalidate(self) -> None:
         self._ptr = None
         self._idx = None
+        self._csr_dev = None
+
+    def device_csr(self) -> tuple[torch.Tensor, torch.Tensor]:
+        """``(ptr, count)`` on the device: ``ptr`` has ``segment_capacity + 1`` entries whose first ``count + 1`` are the
+        row offsets of the live segments.  The masked put / defrag operators read and update both in place."""
+        if self._csr_dev is None:
+            dev = self.lengths.device
+            ptr = torch.zeros(self.segment_capacity + 1, dtype=torch.int32, device=dev)
+            n = min(int(self.lengths.numel()), self.segment_capacity)
+            if n:
+                torch.cumsum(self.lengths[:n], 0, out=ptr[1: n + 1])  # lengths are zero behind the live segments
+                if n < self.segment_capacity:
+                    ptr[n + 1:] = ptr[n]
+            count = torch.tensor([self._n_seg], dtype=torch.int32).to(dev, non_blocking=True)
+            self._csr_dev = (ptr, count)
+        return self._csr_dev
+
+    def _adopt_device_csr(self, counts: DeviceCounts, i_seg: int, i_elem: int) -> None:
+        """After a device-side update of ``(ptr, count)``: refresh ``lengths`` from them (on the device) and leave the host
+        counts pending."""
+        ptr, count = self._csr_dev
+        cap = self.segment_capacity
+        live = torch.arange(cap, device=ptr.device) < count
+        lengths = torch.where(live, ptr[1:] - ptr[:-1], torch.zeros((), dtype=torch.int32, device=ptr.device))
+        if self.lengths.numel() == cap:
+            self.lengths.copy_(lengths)
+        else:
+            self.lengths = lengths
+        self._ptr = self._idx = None
+        self._pending = (counts, i_seg, i_elem)
+
+    def put_masked(self, ops: Any, src_ptr: torch.Tensor, take: torch.Tensor, went: torch.Tensor, src_data: Mapping[str, torch.Tensor],
+                   commit: bool = True) -> torch.Tensor:
+        """Append the source segments flagged in ``take`` that fit (``went`` receives which); with ``commit=False`` only
+        the fit mask is computed.  Returns the plan (first destination row per source segment, or -1)."""
+        ptr, count = self.device_csr()
+        plan = ops.segmented_put_plan(src_ptr, take, ptr, count, self.element_capacity, went, commit)
+        if commit:
+            for k, dst in self.data.items():
+                if k in src_data:
+                    ops.segmented_copy_planned(_as(src_data[k], dst), src_ptr, plan, dst)
+        return plan
+
+    def defrag_masked(self, ops: Any, removed: torch.Tensor, n_live: int, n_rows: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """Drop the live segments flagged in ``removed``; returns ``(plan, old_ptr)``."""
+        ptr, count = self.device_csr()
+        plan, old = ops.segmented_defrag_plan(ptr[: n_live + 1], removed, count)
+        for v in self.data.values():
+            _compact_through_scratch(ops, v, old, plan, n_rows)
+        return plan, old
 
     @property
     def batch_ptr(self) -> torch.Tensor:

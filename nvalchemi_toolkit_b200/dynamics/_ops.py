@@ -313,7 +313,10 @@ def align_cell(positions, cell, batch_idx) -> None:
     q = q * sign.unsqueeze(-2)
     r = r * sign.unsqueeze(-1)
     new_cell = r.transpose(-1, -2)
-    positions.copy_(torch.einsum("ni,nij->nj", positions, q[batch_idx.long()]))
+    if _nat(positions) and positions.is_contiguous():
+        _nops.affine_rows_(positions, q.contiguous(), None, None, None, None, None, _i32(batch_idx), False)  # r <- r Q
+    else:
+        positions.copy_(torch.einsum("ni,nij->nj", positions, q[batch_idx.long()]))
     cell.copy_(new_cell)
 
 

@@ -107,3 +107,64 @@ def test_reference_package_name_alias():
         assert nvalchemi is real and A is real.AtomicData and N is NVE and L is LennardJonesModelWrapper
     finally:
         compat.remove_alias()
+
+
+def _fill_and_drain(device, planned: bool, monkeypatch):
+    """Three puts into a fixed buffer interleaved with a defrag; returns the observable state after every stage."""
+    import nvalchemi_toolkit_b200.data.batch as batch_mod
+
+    if not planned:
+        monkeypatch.setattr(batch_mod, "_buffer_ops", lambda: None)
+    src1 = random_batch([3, 5, 2, 4], n_edges=3, periodic=True, device=device, seed=1)
+    src2 = random_batch([2, 6, 1], n_edges=2, periodic=True, device=device, seed=2)
+    buf = Batch.empty(num_systems=5, num_nodes=14, num_edges=14, template=src1, device=device)
+    out = []
+
+    def snap(tag):
+        out.append((tag, buf.num_graphs, buf.num_nodes, buf.num_edges, buf.batch_ptr.cpu().clone(), buf.positions.cpu().clone(),
+                    buf.neighbor_list.cpu().clone(), buf.cell.cpu().clone()))
+
+    buf.put(src1, torch.tensor([True, False, True, True], device=device))  # 3 + 2 + 4 atoms, 9 edges
+    c1 = src1._copied_mask.cpu().clone()
+    buf.put(src2, torch.tensor([True, True, True], device=device))          # chained: counts not read in between
+    c2 = src2._copied_mask.cpu().clone()
+    snap("after puts")
+    buf.defrag(torch.tensor([False, True, False, True, False], device=device)[: buf.num_graphs])
+    snap("after defrag")
+    buf.put(src1, torch.tensor([False, True, False, False], device=device))
+    snap("after refill")
+    return out, c1, c2
+
+
+def test_planned_put_defrag_matches_index_path(device, monkeypatch):
+    """``Batch.put`` / ``defrag`` through the device planners leave the same buffer as the index-list fallback."""
+    from nvalchemi_toolkit_b200.data.level_storage import _buffer_ops
+
+    if _buffer_ops() is None:
+        pytest.skip("native library not built")
+    got, g1, g2 = _fill_and_drain(device, True, monkeypatch)
+    want, w1, w2 = _fill_and_drain(device, False, monkeypatch)
+    assert torch.equal(g1, w1) and torch.equal(g2, w2)
+    for a, b in zip(got, want):
+        assert a[:4] == b[:4], (a[:4], b[:4])
+        for x, y in zip(a[4:], b[4:]):
+            assert torch.equal(x, y), a[0]
+
+
+@pytest.mark.gpu
+def test_planned_put_makes_no_host_sync():
+    """On the GPU a masked put followed by a second one runs without a single host synchronisation; the counts are read
+    back once, when the host asks for them."""
+    src = random_batch([3, 5, 2, 4], n_edges=3, periodic=True, device="cuda", seed=1)
+    buf = Batch.empty(num_systems=8, num_nodes=64, num_edges=64, template=src, device="cuda")
+    m = torch.tensor([True, False, True, True], device="cuda")
+    src.batch_ptr, src.edge_ptr, src._edges_group.batch_idx  # derived CSR views of the source exist before the region
+    buf.put(src, m)  # first call builds the buffer's device-side CSR
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        buf.put(src, m)
+        buf.put(src, m)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    assert buf.num_graphs == 8 and buf.num_nodes == 9 * 2 + 3 + 2
