@@ -256,6 +256,106 @@ void fire_step(Tensor pos, Tensor vel, const Tensor& force, const Tensor& mass, 
   (void)uphill;
 }
 
+// ------------------------------------------------------------------ FIRE2
+// One FIRE2 iteration (Guenole et al. 2020; reference op family nvalchemi/dynamics/_ops/fire.py:467-648) on per-system
+// state (alpha, dt, nsteps_inc).  The iteration has three per-system reductions, so it is cut into four phases that a
+// domain decomposition can interleave with its cross-rank reductions; phase 0 runs all four back to back.
+//   1: sums[:,0] = sum v.f
+//   2: controller from sums[:,0] (P > 0 for more than `delaystep` steps grows dt and shrinks alpha; P <= 0 shrinks dt,
+//      resets alpha); uphill systems step back half a step and stop; v += dt f; sums[:,1] = sum v.v, sums[:,2] = sum f.f
+//   3: v <- (1 - alpha) v + alpha sqrt(vv / ff) f; max_dr[s] = max |dt v|
+//   4: r += min(1, maxstep / max_dr) dt v
+void fire2_step(Tensor pos, Tensor vel, const Tensor& force, const Tensor& batch_idx, Tensor alpha, Tensor dt,
+                Tensor nsteps_inc, Tensor sums, Tensor max_dr, int64_t delaystep, double dtgrow, double dtshrink,
+                double alphashrink, double alpha0, double tmax, double tmin, double maxstep, int64_t phase) {
+  NVA_CHECK_CONTIG(pos); NVA_CHECK_CONTIG(vel); NVA_CHECK_CONTIG(force); NVA_CHECK_CONTIG(sums);
+  c10::cuda::OptionalCUDAGuard guard(pos.is_cuda() ? c10::make_optional(pos.device()) : c10::nullopt);
+  const bool cuda = pos.is_cuda();
+  const int64_t n = pos.size(0), M = alpha.size(0);
+  TORCH_CHECK(sums.scalar_type() == at::kDouble && sums.numel() == 3 * M, "fire2_step: sums must be float64 [M, 3]");
+  TORCH_CHECK(max_dr.scalar_type() == at::kFloat && max_dr.numel() == M, "fire2_step: max_dr must be float32 [M]");
+  TORCH_CHECK(nsteps_inc.scalar_type() == at::kInt && batch_idx.scalar_type() == at::kInt, "fire2_step: int32 counters / batch_idx");
+  TORCH_CHECK(phase >= 0 && phase <= 4, "fire2_step: phase must be 0..4");
+  const int* b = batch_idx.data_ptr<int>();
+  double* sm = sums.data_ptr<double>();
+  float* md = max_dr.data_ptr<float>();
+  int* nsi = nsteps_inc.data_ptr<int>();
+  AT_DISPATCH_FLOATING_TYPES(pos.scalar_type(), "fire2_step", [&] {
+    scalar_t* r = pos.data_ptr<scalar_t>();
+    scalar_t* v = vel.data_ptr<scalar_t>();
+    const scalar_t* f = force.data_ptr<scalar_t>();
+    scalar_t* al = alpha.data_ptr<scalar_t>();
+    scalar_t* d = dt.data_ptr<scalar_t>();
+    if (phase == 0 || phase == 1) {
+      sums.zero_();
+      seg_reduce<scalar_t>(cuda, n, b, sm, 3, [=] NVA_LAMBDA(int64_t i, double* o) {
+        for (int c = 0; c < 3; ++c) o[0] += (double)v[3 * i + c] * (double)f[3 * i + c];
+      });
+    }
+    if (phase == 0 || phase == 2) {
+      // controller; the sign of P is kept in max_dr (1 = uphill) until phase 3 overwrites it with the displacements
+      for_each(cuda, M, [=] NVA_LAMBDA(int64_t s) {
+        const bool neg = !(sm[3 * s] > 0.0);
+        const int inc = neg ? 0 : nsi[s] + 1;
+        nsi[s] = inc;
+        if (neg) {
+          const scalar_t nd = d[s] * (scalar_t)dtshrink;
+          d[s] = nd > (scalar_t)tmin ? nd : (scalar_t)tmin;
+          al[s] = (scalar_t)alpha0;
+        } else if (inc > delaystep) {
+          const scalar_t nd = d[s] * (scalar_t)dtgrow;
+          d[s] = nd < (scalar_t)tmax ? nd : (scalar_t)tmax;
+          al[s] = al[s] * (scalar_t)alphashrink;
+        }
+        md[s] = neg ? 1.0f : 0.0f;
+        sm[3 * s + 1] = 0.0; sm[3 * s + 2] = 0.0;
+      });
+      seg_reduce<scalar_t>(cuda, n, b, sm, 3, [=] NVA_LAMBDA(int64_t i, double* o) {
+        const int s = b[i];
+        const scalar_t h = d[s];
+        const bool neg = md[s] != 0.0f;
+        for (int c = 0; c < 3; ++c) {
+          scalar_t vc = v[3 * i + c];
+          const scalar_t fc = f[3 * i + c];
+          if (neg) { r[3 * i + c] -= scalar_t(0.5) * h * vc; vc = scalar_t(0); }
+          vc += h * fc;
+          v[3 * i + c] = vc;
+          o[1] += (double)vc * (double)vc; o[2] += (double)fc * (double)fc;
+        }
+      });
+    }
+    if (phase == 0 || phase == 3) {
+      max_dr.zero_();
+      for_each(cuda, n, [=] NVA_LAMBDA(int64_t i) {
+        const int s = b[i];
+        const scalar_t a = al[s], h = d[s];
+        const double ffs = sm[3 * s + 2];
+        const scalar_t mix = a * (scalar_t)sqrt(sm[3 * s + 1] / (ffs > 1e-300 ? ffs : 1e-300));
+        scalar_t d2 = 0;
+        for (int c = 0; c < 3; ++c) {
+          const scalar_t vc = (scalar_t(1) - a) * v[3 * i + c] + mix * f[3 * i + c];
+          v[3 * i + c] = vc;
+          d2 += h * vc * h * vc;
+        }
+        const float dn = (float)sqrt((double)d2);
+#ifdef __CUDA_ARCH__
+        atomicMax((int*)md + s, __float_as_int(dn));  // non-negative floats order like ints
+#else
+        if (dn > md[s]) md[s] = dn;
+#endif
+      });
+    }
+    if (phase == 0 || phase == 4) {
+      for_each(cuda, n, [=] NVA_LAMBDA(int64_t i) {
+        const int s = b[i];
+        const scalar_t h = d[s];
+        const scalar_t scale = md[s] > (float)maxstep ? (scalar_t)(maxstep / (double)md[s]) : scalar_t(1);
+        for (int c = 0; c < 3; ++c) r[3 * i + c] += scale * h * v[3 * i + c];
+      });
+    }
+  });
+}
+
 // ------------------------------------------------------------------ velocities
 // Maxwell-Boltzmann draw: v = sqrt(kT/m) * N(0,1), kT in eV per system.
 void maxwell_boltzmann(Tensor vel, const Tensor& mass, const Tensor& kT, const Tensor& batch_idx, int64_t seed,
@@ -390,6 +490,7 @@ TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("langevin_half_step(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor masses, Tensor dt, Tensor temperature, Tensor friction, int random_seed, Tensor batch_idx, Tensor? atom_ids=None) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::langevin_half_step));
   m.def("langevin_finalize(Tensor(a!) velocities, Tensor forces_new, Tensor masses, Tensor dt, Tensor batch_idx) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::vv_velocity_finalize));
   m.def("compute_kinetic_energy(Tensor velocities, Tensor masses, Tensor batch_idx, int num_systems) -> Tensor", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::compute_kinetic_energy));
+  m.def("fire2_step(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor batch_idx, Tensor(c!) alpha, Tensor(d!) dt, Tensor(e!) nsteps_inc, Tensor(f!) sums, Tensor(g!) max_dr, int delaystep, float dtgrow, float dtshrink, float alphashrink, float alpha0, float tmax, float tmin, float maxstep, int phase=0) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::fire2_step));
   m.def("_fire_step_op(Tensor(a!) positions, Tensor(b!) velocities, Tensor forces, Tensor masses, Tensor(c!) alpha, Tensor(d!) dt, Tensor alpha_start, Tensor f_alpha, Tensor dt_min, Tensor dt_max, Tensor maxstep, Tensor(e!) n_steps_positive, Tensor n_min, Tensor f_dec, Tensor f_inc, Tensor uphill_flag, Tensor(f!) vf, Tensor(g!) vv, Tensor(h!) ff, Tensor batch_idx, bool compute_reductions, Tensor? max_dr=None, int phase=0) -> ()", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::fire_step));
   m.def("maxwell_boltzmann(Tensor(a!) velocities, Tensor masses, Tensor kT, Tensor batch_idx, int seed, Tensor? atom_ids=None) -> ()", &nva::maxwell_boltzmann);
   m.def("momentum_sums(Tensor velocities, Tensor masses, Tensor batch_idx, int num_systems) -> Tensor", torch::dispatch(c10::DispatchKey::CompositeExplicitAutograd, &nva::momentum_sums));

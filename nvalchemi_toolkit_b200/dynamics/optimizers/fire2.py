@@ -14,11 +14,35 @@ import torch
 from nvalchemi_toolkit_b200.data.batch import Batch
 from nvalchemi_toolkit_b200.dynamics import _ops
 from nvalchemi_toolkit_b200.dynamics.base import BaseDynamics
+from nvalchemi_toolkit_b200.ops import _native
 
 
 def fire2_step_coord(positions, velocities, forces, batch_idx, alpha, dt, nsteps_inc, *, delaystep, dtgrow, dtshrink,
                      alphashrink, alpha0, tmax, tmin, maxstep, reduce=None, reduce_max=None) -> None:
     m = alpha.shape[0]
+    if (_native.available() and hasattr(torch.ops.nvalchemi, "fire2_step") and positions.is_contiguous()
+            and velocities.is_contiguous() and forces.is_contiguous() and alpha.dtype == positions.dtype == dt.dtype
+            and nsteps_inc.dtype == torch.int32):
+        # four kernel phases; a domain decomposition reduces the per-system sums between them
+        op = torch.ops.nvalchemi.fire2_step
+        sums = torch.empty(m, 3, dtype=torch.float64, device=positions.device)
+        max_dr = torch.empty(m, dtype=torch.float32, device=positions.device)
+        args = (positions, velocities, forces, batch_idx.to(torch.int32), alpha, dt, nsteps_inc, sums, max_dr, int(delaystep),
+                float(dtgrow), float(dtshrink), float(alphashrink), float(alpha0), float(tmax), float(tmin), float(maxstep))
+        if reduce is None and reduce_max is None:
+            op(*args, 0)
+            return
+        op(*args, 1)
+        if reduce is not None:
+            sums[:, 0] = reduce(sums[:, 0].contiguous())
+        op(*args, 2)
+        if reduce is not None:
+            sums[:, 1], sums[:, 2] = reduce(sums[:, 1].contiguous()), reduce(sums[:, 2].contiguous())
+        op(*args, 3)
+        if reduce_max is not None:
+            max_dr.copy_(reduce_max(max_dr))
+        op(*args, 4)
+        return
     b = batch_idx.long()
     z = torch.zeros(m, dtype=torch.float64, device=positions.device)
     vf = z.clone().index_add_(0, b, (velocities.double() * forces.double()).sum(-1))

@@ -83,7 +83,7 @@ def _register_fakes() -> None:
     nothing = [
         "vv_position_update", "vv_velocity_finalize", "langevin_half_step", "langevin_finalize", "nhc_chain_update",
         "nhc_velocity_half_step", "nhc_position_update", "compute_kinetic_tensor", "affine_rows_", "_fire_step_op",
-        "velocity_shift_scale", "compute_put_fit_mask_per_system", "put_masked_per_system", "defrag_per_system",
+        "velocity_shift_scale", "fire2_step", "segmented_copy_planned", "compute_put_fit_mask_per_system", "put_masked_per_system", "defrag_per_system",
         "compute_put_fit_mask_segmented", "put_masked_segmented", "defrag_segmented"]
     shaped = {
         "compute_kinetic_energy": lambda v, m, b, n: v.new_empty(n),
