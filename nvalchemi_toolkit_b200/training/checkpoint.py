@@ -19,8 +19,10 @@ plain containers.  Wrapped modules (FSDP) are rejected: only plain / DDP modules
 manifest) are still readable."""
 from __future__ import annotations
 
+import copy
 import json
 import os
+import threading
 from datetime import datetime, timezone
 from pathlib import Path
 from typing import Any
@@ -213,58 +215,121 @@ def validate_checkpoint(root: str | Path, checkpoint_index: int | None = None) -
     return problems
 
 
+def host_snapshot(obj: Any) -> Any:
+    """Deep copy of a state-dict-like object with every tensor moved to host memory.  CUDA tensors go to pinned buffers
+    with non-blocking copies on the current stream; the caller records an event after the call and the writer waits on
+    it, so training continues while the copies drain and the files are written from the copies, never from live
+    parameters."""
+    if isinstance(obj, torch.Tensor):
+        if obj.is_cuda:
+            out = torch.empty(obj.shape, dtype=obj.dtype, device="cpu", pin_memory=True)
+            out.copy_(obj.detach(), non_blocking=True)
+            return out
+        return obj.detach().clone()
+    if isinstance(obj, dict):
+        return type(obj)((k, host_snapshot(v)) for k, v in obj.items())
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(host_snapshot(v) for v in obj)
+    return copy.deepcopy(obj)
+
+
+class PendingCheckpoint:
+    """Handle of a checkpoint whose files are being written by a background thread; :meth:`wait` joins it and re-raises
+    a failure of the writer."""
+
+    def __init__(self, root: Path, thread: threading.Thread, box: dict[str, Any]) -> None:
+        self.root, self._thread, self._box = root, thread, box
+
+    def done(self) -> bool:
+        return not self._thread.is_alive()
+
+    def wait(self) -> Path:
+        self._thread.join()
+        if "error" in self._box:
+            raise self._box["error"]
+        return self.root
+
+
 def save_checkpoint(root: str | Path, step: int, models: dict[str, torch.nn.Module], optimizers: list, schedulers: list,
                     hooks: list, strategy_meta: dict[str, Any], optimizer_keys: list[str] | None = None,
-                    checkpoint_index: int = -1) -> Path:
+                    checkpoint_index: int = -1, asynchronous: bool = False) -> "Path | PendingCheckpoint":
     """Write one checkpoint.  ``optimizers`` / ``schedulers`` are the strategy's flat lists; ``optimizer_keys`` names
-    the model each optimizer belongs to (default: the first model).  ``checkpoint_index = -1`` auto-increments."""
+    the model each optimizer belongs to (default: the first model).  ``checkpoint_index = -1`` auto-increments.
+
+    ``asynchronous=True`` snapshots every state to (pinned) host memory on the calling thread, returns a
+    :class:`PendingCheckpoint` at once and writes the files from a background thread (the reference's checkpoint hook has
+    the same switch, ``nvalchemi/training/hooks/checkpoint.py``); the manifest is written last, so a reader never sees an
+    index whose files are incomplete."""
     root = Path(root)
-    man = CheckpointManifest(root)
-    if man.legacy:
+    if CheckpointManifest(root).legacy:
         raise ValueError(f"{root} holds a checkpoint in this package's earlier layout; save into a fresh directory")
-    index = man.checkpoint_index + 1 if checkpoint_index == -1 else int(checkpoint_index)
+    grab = host_snapshot if asynchronous else (lambda x: x)
     keys = list(optimizer_keys) if optimizer_keys is not None else [next(iter(models))] * len(optimizers)
-    opt_names = component_names(keys, "optimizer")
-    sched_names = component_names(keys, "scheduler")
-    opts = dict(zip(opt_names, optimizers))
-    scheds = {n: s for n, s in zip(sched_names, schedulers) if s is not None}
-
-    def put(kind: str, name: str, state: Any, spec: dict) -> None:
-        d = root / kind / name
-        (d / "checkpoints").mkdir(parents=True, exist_ok=True)
-        spec_path = d / "spec.json"
-        if spec_path.exists():
-            old = json.loads(spec_path.read_text())
-            if {k: v for k, v in old.items() if k != "timestamp"} != {k: v for k, v in spec.items() if k != "timestamp"}:
-                raise ValueError(f"{kind}/{name}/spec.json disagrees with the component being saved")
-        else:
-            spec_path.write_text(json.dumps(spec, indent=2))
-        torch.save(state, d / "checkpoints" / f"{index}.pt")
-        if name not in man.data[kind]:
-            man.data[kind].append(name)
-
+    opts = dict(zip(component_names(keys, "optimizer"), optimizers))
+    scheds = {n: sc for n, sc in zip(component_names(keys, "scheduler"), schedulers) if sc is not None}
+    # ---- collect: everything that touches live objects happens here, on the caller's thread ----------------------
+    parts: list[tuple[str, str, Any, dict]] = []
     specs = {}
     for name, m in models.items():
         specs[name] = model_spec(m)
-        put("models", name, _unwrap(m).state_dict(), specs[name])
+        parts.append(("models", name, grab(_unwrap(m).state_dict()), specs[name]))
     for name, o in opts.items():
-        put("optimizers", name, o.state_dict(), _optimizer_spec(o))
-    for name, s in scheds.items():
-        put("schedulers", name, s.state_dict(), {"cls_path": type_to_path(type(s)), "timestamp": _now()})
-    states = {key: _plain(dict(h.state_dict())) for key, h in _keyed_hooks(hooks)}
-    if states:
-        (root / HOOK_DIR).mkdir(parents=True, exist_ok=True)
-        torch.save(states, root / HOOK_DIR / f"{index}.pt")
+        parts.append(("optimizers", name, grab(o.state_dict()), _optimizer_spec(o)))
+    for name, sc in scheds.items():
+        parts.append(("schedulers", name, grab(sc.state_dict()), {"cls_path": type_to_path(type(sc)), "timestamp": _now()}))
+    hook_states = {key: grab(_plain(dict(h.state_dict()))) for key, h in _keyed_hooks(hooks)}
     meta = dict(to_jsonable(strategy_meta))
     meta.setdefault("model_specs", specs)
-    payload = json.dumps(meta, indent=2)
-    (root / STRATEGY_FILE).write_text(payload)
-    (root / STRATEGY_DIR).mkdir(parents=True, exist_ok=True)
-    (root / STRATEGY_DIR / f"{index}.json").write_text(payload)
-    man.data["checkpoint_index"] = index
-    man.data["associations"] = infer_associations({k: m for k, m in models.items()}, opts, scheds)
-    man.write()
-    return root
+    associations = infer_associations(dict(models), opts, scheds)
+
+    # ---- commit: files only ---------------------------------------------------------------------------------------
+    def commit() -> Path:
+        man = CheckpointManifest(root)
+        index = man.checkpoint_index + 1 if checkpoint_index == -1 else int(checkpoint_index)
+        for kind, name, state, spec in parts:
+            d = root / kind / name
+            (d / "checkpoints").mkdir(parents=True, exist_ok=True)
+            spec_path = d / "spec.json"
+            if spec_path.exists():
+                old = json.loads(spec_path.read_text())
+                if {k: v for k, v in old.items() if k != "timestamp"} != {k: v for k, v in spec.items() if k != "timestamp"}:
+                    raise ValueError(f"{kind}/{name}/spec.json disagrees with the component being saved")
+            else:
+                spec_path.write_text(json.dumps(spec, indent=2))
+            torch.save(state, d / "checkpoints" / f"{index}.pt")
+            if name not in man.data[kind]:
+                man.data[kind].append(name)
+        if hook_states:
+            (root / HOOK_DIR).mkdir(parents=True, exist_ok=True)
+            torch.save(hook_states, root / HOOK_DIR / f"{index}.pt")
+        payload = json.dumps(meta, indent=2)
+        (root / STRATEGY_FILE).write_text(payload)
+        (root / STRATEGY_DIR).mkdir(parents=True, exist_ok=True)
+        (root / STRATEGY_DIR / f"{index}.json").write_text(payload)
+        man.data["checkpoint_index"] = index
+        man.data["associations"] = associations
+        man.write()
+        return root
+
+    if not asynchronous:
+        return commit()
+    event = None
+    if torch.cuda.is_available():
+        event = torch.cuda.Event()
+        event.record()
+    box: dict[str, Any] = {}
+
+    def work() -> None:
+        try:
+            if event is not None:
+                event.synchronize()  # the device-to-host copies of the snapshot have landed
+            commit()
+        except BaseException as exc:  # re-raised by PendingCheckpoint.wait()
+            box["error"] = exc
+
+    th = threading.Thread(target=work, name="checkpoint-writer", daemon=True)
+    th.start()
+    return PendingCheckpoint(root, th, box)
 
 
 def read_strategy_metadata(root: str | Path, checkpoint_index: int | None = None) -> dict[str, Any]:

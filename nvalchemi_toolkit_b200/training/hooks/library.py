@@ -445,7 +445,7 @@ class CheckpointHook(_Base):
                  asynchronous: bool = False, rank_zero_only: bool = True) -> None:
         self.directory, self.every_n_steps, self.every_n_epochs = Path(directory), every_n_steps, every_n_epochs
         self.asynchronous, self.rank_zero_only = asynchronous, rank_zero_only
-        self._thread: threading.Thread | None = None
+        self._pending: Any = None
         self._last_step = -1
 
     def _runs_on_stage(self, stage: Enum) -> bool:
@@ -460,14 +460,13 @@ class CheckpointHook(_Base):
         if not due or (self.rank_zero_only and get_rank(st.distributed_manager) != 0):
             return
         self._last_step = st.step_count
-        if self._thread is not None:
-            self._thread.join()
-            self._thread = None
+        if self._pending is not None:  # one writer at a time: the previous files are complete before the next index
+            self._pending.wait()
+            self._pending = None
         if self.asynchronous and stage != S.AFTER_TRAINING:
-            if torch.cuda.is_available():
-                torch.cuda.synchronize()
-            self._thread = threading.Thread(target=st.save_checkpoint, args=(self.directory,), daemon=True)
-            self._thread.start()
+            # states are snapshotted to pinned host memory here; the files are written while training goes on
+            out = st.save_checkpoint(self.directory, asynchronous=True)
+            self._pending = out if hasattr(out, "wait") else None
         else:
             st.save_checkpoint(self.directory)
 

@@ -290,11 +290,14 @@ class TrainingStrategy(HookRegistryMixin):
         kw.update(overrides)
         return cls(models, **kw)
 
-    def save_checkpoint(self, directory: str | Path) -> Path:
+    def save_checkpoint(self, directory: str | Path, asynchronous: bool = False) -> "Path | ckpt.PendingCheckpoint":
+        """Rank 0 writes the checkpoint; ``asynchronous=True`` snapshots to host memory and returns a handle whose
+        ``wait()`` joins the background writer."""
         if get_rank(self.distributed_manager) != 0:
             return Path(directory)
         return ckpt.save_checkpoint(directory, self.step_count, self.models, self._optimizers, self._lr_schedulers,
-                                    self.hooks, self._meta(), optimizer_keys=getattr(self, "_opt_keys", None))
+                                    self.hooks, self._meta(), optimizer_keys=getattr(self, "_opt_keys", None),
+                                    asynchronous=asynchronous)
 
     def load_checkpoint(self, directory: str | Path, step: int | None = None) -> None:
         """Restore models, optimisers, schedulers, hook states and counters (optimisers are built on demand)."""

@@ -203,3 +203,29 @@ def test_checkpoint_layout_matches_reference_and_reads_a_reference_fixture(tmp_p
     (fix / "manifest.json").write_text(json.dumps({"schema_version": 1, "models": ["main"]}))
     with pytest.raises(ValueError):
         ckpt.CheckpointManifest(fix)
+
+
+def test_asynchronous_checkpoint_holds_the_snapshot_not_the_live_weights(tmp_path):
+    """``save_checkpoint(asynchronous=True)`` returns before the files exist; what lands on disk is the state at the call,
+    even when the parameters change while the writer runs; the next index appears only after ``wait()``."""
+    from nvalchemi_toolkit_b200.training import checkpoint as ck
+
+    net = torch.nn.Linear(4, 3)
+    opt = torch.optim.SGD(net.parameters(), lr=0.1)
+    net(torch.randn(2, 4)).sum().backward()
+    opt.step()
+    want = {k: v.clone() for k, v in net.state_dict().items()}
+    handle = ck.save_checkpoint(tmp_path, 7, {"main": net}, [opt], [None], [], {"step_count": 7}, asynchronous=True)
+    with torch.no_grad():
+        for p in net.parameters():
+            p.add_(100.0)  # training goes on
+    assert handle.wait() == tmp_path and handle.done()
+    assert ck.CheckpointManifest(tmp_path).checkpoint_index == 0 and not ck.validate_checkpoint(tmp_path)
+    fresh = torch.nn.Linear(4, 3)
+    ck.load_checkpoint(tmp_path, {"main": fresh})
+    for k, v in fresh.state_dict().items():
+        assert torch.equal(v, want[k])
+    # a failing writer surfaces in wait()
+    bad = ck.save_checkpoint(tmp_path, 8, {"main": torch.nn.Embedding(5, 3)}, [], [], [], {}, asynchronous=True)
+    with pytest.raises(ValueError, match="spec.json disagrees"):
+        bad.wait()
