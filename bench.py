@@ -291,6 +291,13 @@ def run_ours(args, impl: str = "ours") -> dict:
     err = gemm.check_errors(torch.zeros(1, device=device))
     engine = getattr(job.dp.model, "engine", None) if job.dp is not None else None
     peer_status = engine.status() if engine is not None else 0
+    phases = None
+    if args.phase_times and engine is not None:  # separate, untimed steps: the event records are not in the headline
+        engine.phase_events = []
+        for _ in range(max(3, min(args.steps, 5))):
+            job.step()
+        phases = {k: round(v, 3) for k, v in engine.phase_times_ms().items()}
+        engine.phase_events = None
     rebuilds = job.dp.num_rebuilds if job.dp is not None else 0
     parallelism = job.parallelism
     value = n_atoms_total * args.steps / (ms * 1e-3)
@@ -314,6 +321,8 @@ def run_ours(args, impl: str = "ours") -> dict:
             extra["baseline_error"] = f"{type(exc).__name__}: {exc}".splitlines()[0][:300]
             if world > 1:
                 raise
+    if phases is not None:
+        extra["phase_ms_rank0"] = phases
     out = _result(locals())
     out.update(extra)
     if world > 1:
@@ -403,6 +412,8 @@ def main() -> None:
     ap.add_argument("--grid", type=int, nargs=3, default=None, help="rank grid (default: least cut surface)")
     ap.add_argument("--baseline-steps", type=int, default=3, help="timed steps of the stand-in baseline arm (0: skip)")
     ap.add_argument("--baseline-cells", type=int, default=14, help="cells per edge of the single-GPU eager-PyTorch arm")
+    ap.add_argument("--phase-times", action="store_true",
+                    help="multi-GPU: after the timed steps, CUDA-event times of the phases of a few extra steps (rank 0)")
     ap.add_argument("--atom-order", default="lattice", choices=["lattice", "morton"],
                     help="memory order of the synthetic atoms: x-major lattice order or a Z-curve over 4 A bins")
     args = ap.parse_args()

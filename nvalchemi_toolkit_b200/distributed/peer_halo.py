@@ -89,6 +89,8 @@ class PeerHaloEngine:
     #: direction of the link) instead of the holder pushing remote reductions
     reverse_pull = True
 
+    phase_events: list | None = None
+
     def __init__(self, wrapper: Any, config: Any, group: Any = None, max_neighbors: int | None = None) -> None:
         self.wrapper, self.model, self.config = wrapper, wrapper.model, config
         self.group = group if group is not None else dist.group.WORLD
@@ -215,6 +217,8 @@ class PeerHaloEngine:
         self._bind(sharded)
         owned = sharded.owned
         n, ng = self.n_owned, self.n_ghost
+        mark = self._mark
+        mark("bind")
         cell = owned.cell.reshape(3, 3).to(torch.float32)
         # owned positions in this rank's frame; ghost images relative to the owners' frames
         torch.addmm(owned.positions.detach(), self.wrap_image, cell, out=self.pos_buf[:n])
@@ -222,12 +226,15 @@ class PeerHaloEngine:
             torch.matmul(self.ghost_image, cell, out=self.ghost_shift)
         self.p2p.barrier()  # every rank's owned rows are in place (and last step's readers are done)
         _nops.halo_pull_rows(self.pos_buf, n, self.ghost_home_rank, self.ghost_home_row, self.ghost_shift, self.pos_ptrs)
+        mark("ghost_positions")
         pos_local = self.pos_buf[: n + ng]
         cell3 = cell.reshape(1, 3, 3).contiguous()
         csr = self._neighbors(pos_local, cell3)
+        mark("neighbor_list")
         want_f, want_s = "forces" in active, "stress" in active
         out = native.forward(self.model, {"positions": pos_local, "cell": cell3, "_csr": csr}, self.species,
                              self.batch_long, 1, want_f or want_s, want_s, dd=self)
+        mark("model")
         sums = self._sums
         sums.zero_()
         sums[0:1] = out["energy"].double()
@@ -244,7 +251,30 @@ class PeerHaloEngine:
             res["virial"] = virial.to(torch.float32)
             res["stress"] = (-virial / vol).to(torch.float32)
         self.last_stats = {"n_owned": n, "n_ghost": ng, "n_edges": csr.num_edges}
+        mark("reduce_outputs")
         return res
+
+    # ------------------------------------------------------------------ optional phase timing (CUDA events)
+    def _mark(self, name: str) -> None:
+        """With ``phase_events`` set to a list, records a CUDA event at the end of each phase of :meth:`forward`."""
+        ev = self.phase_events
+        if ev is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            ev.append((name, e))
+
+    def phase_times_ms(self) -> dict[str, float]:
+        """Device time per phase and evaluation (a phase that occurs several times per evaluation is summed), averaged over
+        the evaluations recorded since ``phase_events`` was set (synchronises)."""
+        ev = self.phase_events or []
+        torch.cuda.synchronize()
+        tot: dict[str, float] = {}
+        for (_, e0), (name, e1) in zip(ev[:-1], ev[1:]):
+            if name == "bind":
+                name = "outside_forward"  # from the end of one evaluation to the start of the next: integrator, hooks
+            tot[name] = tot.get(name, 0.0) + e0.elapsed_time(e1)
+        n_eval = max(1, sum(1 for name, _ in ev if name == "reduce_outputs"))
+        return {k: v / n_eval for k, v in tot.items()}
 
     def status(self) -> int:
         """0 while every device-side rendezvous completed within its bounded wait (one host read)."""

@@ -417,6 +417,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
     hw = dd.home_row if dd is not None and not pull else None
     n_rows = dd.n_local if pull else n  # rows of the feature / gradient buffers the kernels see
     used = getattr(dd, "ghost_used", None) if pull else None  # ghost rows that some local edge references
+    mark = getattr(dd, "_mark", None) or (lambda name: None)  # optional CUDA-event phase marks of the halo engine
     if dd is not None:
         dd.gpos.zero_()
 
@@ -457,9 +458,11 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
             if li > 0 and compute_force:
                 du, du_ptrs = dd.feature_buffer(f"du{li}", (n_rows, h.shape[1], C))
                 du.zero_()
+            mark("model")
             dd.barrier()  # every rank's u (and zeroed du / gradient buffers) is in place before peers touch it
             if pull:
                 ops.halo_pull_rows(u, n, dd.ghost_home_rank, dd.ghost_home_row, None, u_ptrs, used)
+                mark("halo_forward")
                 pull_ptrs = (u_ptrs, du_ptrs)
                 u_ptrs = du_ptrs = None  # the convolution kernels read and write local rows only
         else:
@@ -590,6 +593,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         del dmid, dmsg
         if pull:
             # return what was accumulated on ghost rows to the owners, once per row
+            mark("model")
             dd.barrier()  # owners finished their own accumulation, holders finished theirs on the ghost copies
             if getattr(dd, "reverse_pull", False):
                 rev = (dd.send_row, dd.send_peer, dd.send_peer_row)
@@ -604,6 +608,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
                     ops.halo_push_add_rows(grad_pos[:dd.n_local], n, dd.ghost_home_rank, dd.ghost_home_row, dd.gpos_ptrs, used)
         if dd is not None:
             dd.barrier()  # feature / position gradients pushed by peers have landed
+            mark("halo_reverse")
         if li > 0 and dd is not None:
             du = du[:n]
         if li > 0 and wgs is not None:

@@ -1,6 +1,7 @@
 # SPDX-License-Identifier: Apache-2.0
 """Counting proxy over ``torch.ops.nvalchemi``: every call of one of this package's native operators is tallied
-(benchmarks report the tally as the number of native operator launches in the timed region)."""
+(benchmarks report the tally as the number of native operator launches in the timed region).  With the bounds-checked
+debug mode on (``ops/debug_bounds.py``) every call validates its index arguments on the host first."""
 from __future__ import annotations
 
 import torch
@@ -14,7 +15,9 @@ class _Ops:
 
         if not _native.available():  # loads the in-tree library on first use
             raise RuntimeError("native extension is not built: run `python -m nvalchemi_toolkit_b200.ops.build`")
-        fn = getattr(torch.ops.nvalchemi, name)
+        from nvalchemi_toolkit_b200.ops import debug_bounds
+
+        fn = debug_bounds.wrap(name, getattr(torch.ops.nvalchemi, name))  # validates index arguments in debug mode
 
         def call(*a, **k):
             global _count
