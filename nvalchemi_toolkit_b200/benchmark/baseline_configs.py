@@ -6,6 +6,8 @@ shapes, random-initialised weights of the named MACE architecture, one JSON line
     python -m nvalchemi_toolkit_b200.benchmark.baseline_configs train --structures 512 --steps 8
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m \\
         nvalchemi_toolkit_b200.benchmark.baseline_configs train ...      (data parallel: fused gradient all-reduce)
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m \\
+        nvalchemi_toolkit_b200.benchmark.baseline_configs pipeline       (4 FIRE ranks | 4 NVT ranks, water + D3 + PME)
 
 ``relax``: FIRE to ``fmax`` with inflight batching (``SizeAwareSampler`` refills the slots of converged systems) over a
 stream of periodic fcc / bcc supercells of 32-256 atoms of Cu, Ni, Al, Fe with lattice constants 2.8-4.1 A and 0.1 A
@@ -190,6 +192,99 @@ def train(args: argparse.Namespace) -> dict:
             "gradient_allreduce": "fused peer-memory all-reduce" if world > 1 and device.type == "cuda" else "none"}
 
 
+class WaterStream:
+    """Dataset protocol of ``SizeAwareSampler`` over periodic water boxes of ``lo``-``hi`` molecules (3 atoms each)."""
+
+    def __init__(self, n: int, lo: int = 512, hi: int = 1024, seed: int = 0, offset: int = 0) -> None:
+        g = torch.Generator().manual_seed(seed)
+        self.molecules = torch.randint(lo, hi + 1, (n + offset,), generator=g)[offset:].tolist()
+        self.seed = seed + offset
+        self._cache: dict[int, Any] = {}
+
+    def __len__(self) -> int:
+        return len(self.molecules)
+
+    def get_metadata(self, i: int) -> tuple[int, int]:
+        return 3 * self.molecules[i], 0
+
+    def __getitem__(self, i: int) -> tuple[Any, dict]:
+        if i not in self._cache:
+            self._cache[i] = systems.water_box(self.molecules[i], seed=self.seed + i)
+        return self._cache[i], {}
+
+
+def _water_model(device: torch.device, channels: int) -> Any:
+    """MACE (2 layers, ``channels`` x (0e + 1o), lmax 3, correlation 3, 5 A) + DFT-D3(BJ) + PME (alpha 0.3 / A, 1 A mesh)."""
+    from nvalchemi_toolkit_b200.models.dftd3 import DFTD3ModelWrapper, DFTD3Parameters
+    from nvalchemi_toolkit_b200.models.ewald import PMEModelWrapper
+    from nvalchemi_toolkit_b200.models.mace import MACE, MACEConfig, MACEWrapper
+    from nvalchemi_toolkit_b200.models.pipeline import PipelineGroup, PipelineModelWrapper
+
+    torch.manual_seed(0)
+    cfg = MACEConfig(atomic_numbers=[1, 8], r_max=5.0, num_bessel=8, num_polynomial_cutoff=5, max_ell=3, num_interactions=2,
+                     channels=channels, hidden_lmax=1, correlation=3, avg_num_neighbors=50.0)
+    mace = MACEWrapper(MACE(cfg, backend="auto").to(device)).eval()
+    d3 = DFTD3ModelWrapper("pbe", parameters=DFTD3Parameters.synthetic(10), cutoff=10.0)  # synthetic reference tables
+    pme = PMEModelWrapper(cutoff=9.0, alpha=0.3, mesh_spacing=1.0, charge_key="charges")
+    model = PipelineModelWrapper([PipelineGroup([mace]), PipelineGroup([d3]), PipelineGroup([pme])])
+    model.model_config.active_outputs = {"energy", "forces"}
+    return model.to(device)
+
+
+def pipeline(args: argparse.Namespace) -> dict:
+    """Relaxation ranks feed MD ranks: ``world / 2`` lanes, lane ``l`` = FIRE on rank ``l`` handing each system after
+    ``--relax-steps`` iterations to NVT-Langevin on rank ``l + world / 2`` (``--md-steps`` steps), inflight batching on the
+    first stage, hand-off over ``torch.distributed`` point-to-point.  One rank runs both stages fused on its GPU."""
+    from nvalchemi_toolkit_b200.dynamics import FIRE, FusedStage, HostMemory, NVTLangevin, SizeAwareSampler
+    from nvalchemi_toolkit_b200.dynamics.pipeline import DistributedPipeline
+
+    rank, world, device = _dist()
+    if world > 1 and world % 2:
+        raise SystemExit("pipeline: the number of ranks must be 1 or even (half relax, half run MD)")
+    lanes = max(1, world // 2)
+    lane = rank % lanes
+    share = args.systems // lanes
+    model = _water_model(device, args.channels)
+    hooks = lambda: model.make_neighbor_hooks(max_neighbors=args.max_neighbors)  # noqa: E731
+    data = WaterStream(share, args.min_molecules, args.max_molecules, seed=2, offset=lane * share)
+    sampler = SizeAwareSampler(data, max_atoms=args.max_atoms, max_batch_size=args.max_batch)
+    sink = HostMemory(capacity=share)
+    fire = FIRE(model, dt=args.dt_relax, n_steps=args.relax_steps, hooks=hooks(), sampler=sampler, device_type=device.type,
+                max_batch_size=args.max_batch)
+    md = NVTLangevin(model, dt=args.dt_md, temperature=300.0, friction=0.01, random_seed=7, n_steps=args.md_steps,
+                     hooks=hooks(), sinks=[sink], device_type=device.type, max_batch_size=2 * args.max_batch)
+    if world == 1:
+        flow: Any = FusedStage(sub_stages=[(0, fire), (1, md)], sampler=sampler, sinks=[sink], refill_frequency=1,
+                               device_type=device.type)
+        run = lambda: flow.run(n_steps=args.max_iterations)  # noqa: E731
+    else:
+        groups = [dist.new_group([ln, ln + lanes]) for ln in range(lanes)]  # created by every rank, in the same order
+        flow = DistributedPipeline({lane: fire, lane + lanes: md}, group=groups[lane])
+        flow.setup()
+        run = lambda: flow.run(max_iterations=args.max_iterations)  # noqa: E731
+    if device.type == "cuda":
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    run()
+    if device.type == "cuda":
+        torch.cuda.synchronize()
+    seconds = _max_over_ranks(time.perf_counter() - t0, device, world)
+    done = sink.read()
+    n_done = torch.tensor([0 if done is None else done.num_graphs, 0 if done is None else done.num_nodes], device=device)
+    if world > 1:
+        dist.all_reduce(n_done)
+    steps_per_atom = args.relax_steps + args.md_steps
+    return {"metric": "two-stage pipeline (FIRE ranks | NVT-Langevin ranks), water boxes, MACE + DFT-D3(BJ) + PME",
+            "value": int(n_done[1]) * steps_per_atom / seconds, "unit": "atom-steps/s", "systems_per_s": int(n_done[0]) / seconds,
+            "n_gpus": world, "lanes": lanes, "systems_finished": int(n_done[0]), "systems_in_stream": share * lanes,
+            "atoms_finished": int(n_done[1]), "seconds": seconds, "data": "synthetic (water boxes, 1.0 g/cm^3)",
+            "config": {"relax_steps": args.relax_steps, "md_steps": args.md_steps, "molecules": [args.min_molecules, args.max_molecules],
+                       "max_atoms": args.max_atoms, "max_batch": args.max_batch, "channels": args.channels,
+                       "d3": "BJ damping, synthetic reference tables", "pme": "alpha 0.3 / A, 1 A mesh, order 5"}}
+
+
 def main(argv: list[str] | None = None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -210,8 +305,21 @@ def main(argv: list[str] | None = None) -> int:
     t.add_argument("--steps", type=int, default=8)
     t.add_argument("--warmup", type=int, default=2)
     t.add_argument("--backend", default="torch", choices=["torch"], help="differentiable path used under autograd")
+    pl = sub.add_parser("pipeline")
+    pl.add_argument("--systems", type=int, default=64, help="water boxes in the stream (whole job)")
+    pl.add_argument("--min-molecules", type=int, default=512)
+    pl.add_argument("--max-molecules", type=int, default=1024)
+    pl.add_argument("--relax-steps", type=int, default=20)
+    pl.add_argument("--md-steps", type=int, default=20)
+    pl.add_argument("--max-atoms", type=int, default=16384)
+    pl.add_argument("--max-batch", type=int, default=6)
+    pl.add_argument("--max-neighbors", type=int, default=512)
+    pl.add_argument("--channels", type=int, default=128)
+    pl.add_argument("--dt-relax", type=float, default=0.05)
+    pl.add_argument("--dt-md", type=float, default=0.5)
+    pl.add_argument("--max-iterations", type=int, default=None)
     args = ap.parse_args(argv)
-    out = relax(args) if args.cmd == "relax" else train(args)
+    out = {"relax": relax, "train": train, "pipeline": pipeline}[args.cmd](args)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(out))
     if dist.is_initialized():

@@ -3,6 +3,7 @@
 rock-salt NaCl, a beta-cristobalite-like SiO2 framework and a methane box, each scalable by repetition count."""
 from __future__ import annotations
 
+import math
 from typing import Any, Callable
 
 import torch
@@ -82,8 +83,39 @@ def methane_box(reps: int, spacing: float = 4.2, **kw: Any) -> AtomicData:
                     kw.get("dtype", torch.float32))
 
 
+def water_box(n_molecules: int, density: float = 1.0, seed: int = 0, dtype: torch.dtype = torch.float32, **kw: Any) -> AtomicData:
+    """Periodic box of ``n_molecules`` rigid-geometry water molecules at ``density`` g/cm^3: oxygens on a jittered simple
+    cubic lattice (the ``ceil(n^(1/3))^3`` sites are subsampled), O-H 0.96 A, H-O-H 104.5 degrees, uniformly random
+    orientations, partial charges O -0.82 / H +0.41 (the ``charges`` field)."""
+    g = torch.Generator().manual_seed(seed)
+    vol = n_molecules * 18.015 / (density * 0.602214)          # A^3: 18.015 g/mol over N_A * 1e-24 cm^3
+    box = vol ** (1.0 / 3.0)
+    m = int(math.ceil(n_molecules ** (1.0 / 3.0) - 1e-9))
+    sites = torch.stack(torch.meshgrid(*(torch.arange(m, dtype=torch.float64),) * 3, indexing="ij"), -1).reshape(-1, 3)
+    pick = torch.randperm(sites.shape[0], generator=g)[:n_molecules]
+    o = (sites[pick] + 0.5 + 0.15 * (torch.rand(n_molecules, 3, generator=g, dtype=torch.float64) - 0.5)) * (box / m)
+    # random rotations from normalised quaternions
+    q = torch.randn(n_molecules, 4, generator=g, dtype=torch.float64)
+    q = q / q.norm(dim=1, keepdim=True)
+    w, x, y, z = q.unbind(1)
+    rot = torch.stack([1 - 2 * (y * y + z * z), 2 * (x * y - z * w), 2 * (x * z + y * w),
+                       2 * (x * y + z * w), 1 - 2 * (x * x + z * z), 2 * (y * z - x * w),
+                       2 * (x * z - y * w), 2 * (y * z + x * w), 1 - 2 * (x * x + y * y)], 1).reshape(-1, 3, 3)
+    half = math.radians(104.5) / 2.0
+    h_local = 0.96 * torch.tensor([[math.sin(half), 0.0, math.cos(half)], [-math.sin(half), 0.0, math.cos(half)]], dtype=torch.float64)
+    h = o[:, None, :] + torch.einsum("nij,kj->nki", rot, h_local)
+    pos = torch.cat([o[:, None, :], h], 1).reshape(-1, 3)
+    n = pos.shape[0]
+    data = AtomicData(atomic_numbers=torch.tensor([8, 1, 1]).repeat(n_molecules), positions=pos.to(dtype),
+                      cell=(torch.eye(3, dtype=torch.float64) * box).to(dtype), pbc=torch.tensor([True, True, True]),
+                      forces=torch.zeros(n, 3, dtype=dtype), energy=torch.zeros(1, 1, dtype=dtype),
+                      velocities=torch.zeros(n, 3, dtype=dtype),
+                      charges=torch.tensor([-0.82, 0.41, 0.41]).repeat(n_molecules).to(dtype))
+    return data
+
+
 SYSTEMS: dict[str, Callable[..., AtomicData]] = {"fcc_cu": fcc, "bcc_fe": bcc_iron, "nacl": nacl, "sio2": silica,
-                                                 "ar_cluster": argon_cluster, "ch4": methane_box}
+                                                 "ar_cluster": argon_cluster, "ch4": methane_box, "water": water_box}
 
 
 def build(name: str, size: int, device: str | torch.device = "cpu", **kw: Any) -> Batch:

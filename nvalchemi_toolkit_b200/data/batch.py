@@ -588,9 +588,15 @@ class Batch(DataMixin):
                 out.extend((gname, k) for k in sorted(g.keys()))
         return out
 
-    def isend(self, dst: int, group: Any = None, tag: int = 0) -> "_BatchSendHandle":
-        """Non-blocking send.  An empty batch is still sent so the peer's ``irecv`` always completes."""
+    def isend(self, dst: int, group: Any = None, tag: int = 0, template: "Batch | None" = None) -> "_BatchSendHandle":
+        """Non-blocking send.  An empty batch is still sent so the peer's ``irecv`` always completes.
+
+        The receiver posts one message per field of ITS template; with ``template`` given the sender transmits exactly
+        that field set (fields this batch lacks go as zeros, fields the template lacks stay behind), so bookkeeping or
+        cache fields a stage added to its batch cannot desynchronise the two sides."""
         b = self._tight()
+        if template is not None:
+            b = b._conformed_to(template)
         header = torch.tensor([b.num_graphs, b.num_nodes, b.num_edges], dtype=torch.int64, device=self.device)
         handles, keep = [], [header]
         handles.append(dist.isend(header, dst, group=group, tag=tag))
@@ -607,6 +613,27 @@ class Batch(DataMixin):
                 keep.append(t)
                 handles.append(dist.isend(t, dst, group=group, tag=tag + 2 + i))
         return _BatchSendHandle(handles, keep)
+
+    def _conformed_to(self, template: "Batch") -> "Batch":
+        """Shallow copy of this (tight) batch holding exactly the fields of ``template``."""
+        rows = {"atoms": self.num_nodes, "edges": self.num_edges, "system": self.num_graphs}
+        same = all((self._storage.groups[g] is None) == (template._storage.groups[g] is None) and
+                   (self._storage.groups[g] is None or set(self._storage.groups[g].keys()) == set(template._storage.groups[g].keys()))
+                   for g in rows)
+        if same:
+            return self
+        out = self.index_select(torch.arange(self.num_graphs, device=self.device))
+        for gname, n in rows.items():
+            tg, og = template._storage.groups[gname], out._storage.groups[gname]
+            if tg is None or og is None:
+                continue
+            for k in list(og.keys()):
+                if k not in tg.data:
+                    del og[k]
+            for k, ref in tg.data.items():
+                if k not in og.data:
+                    og[k] = torch.zeros((n,) + tuple(ref.shape[1:]), dtype=ref.dtype, device=self.device)
+        return out
 
     @classmethod
     def irecv(cls, src: int, template: "Batch", device: torch.device | str | None = None, group: Any = None,

@@ -21,12 +21,17 @@ import torch.distributed as dist
 
 from nvalchemi_toolkit_b200.data.batch import Batch
 from nvalchemi_toolkit_b200.dynamics.base import BaseDynamics, BufferConfig, DynamicsStage, _flat_status
+from nvalchemi_toolkit_b200.dynamics.sinks import strip_neighbor_caches
 
 
 class DistributedPipeline:
     def __init__(self, stages: dict[int, BaseDynamics], synchronized: bool = False, debug_mode: bool = False,
-                 mesh: Any = None, **dist_kwargs: Any) -> None:
+                 mesh: Any = None, group: Any = None, **dist_kwargs: Any) -> None:
+        """``stages`` maps a (global) rank to its dynamics stage.  ``group``: process group that holds exactly the ranks
+        of this pipeline, for jobs that run several independent pipelines side by side (lanes); template broadcast and
+        the termination vote then stay inside the lane."""
         self.stages = dict(sorted(stages.items()))
+        self.group = group
         self.synchronized = synchronized
         self.debug_mode = debug_mode
         self.mesh = mesh
@@ -47,7 +52,7 @@ class DistributedPipeline:
                 stages[nxt + k] = st
         else:
             stages[nxt] = other
-        return DistributedPipeline(stages, self.synchronized, self.debug_mode, self.mesh, **self.dist_kwargs)
+        return DistributedPipeline(stages, self.synchronized, self.debug_mode, self.mesh, self.group, **self.dist_kwargs)
 
     # ---- lifecycle ---------------------------------------------------------------
     def init_distributed(self) -> None:
@@ -112,7 +117,7 @@ class DistributedPipeline:
                 pass
             payload = [st.active_batch.index_select(torch.zeros(0, dtype=torch.long)).to("cpu")]
         if dist.is_initialized() and dist.get_world_size() > 1:
-            dist.broadcast_object_list(payload, src=first)
+            dist.broadcast_object_list(payload, src=first, group=self.group)
         self._template = payload[0]
 
     # ---- one iteration -------------------------------------------------------------
@@ -160,7 +165,7 @@ class DistributedPipeline:
             batch, converged = st.step(batch)
             mask = self._graduated_mask(st, batch, converged)
             if bool(mask.any()):
-                graduated = batch.index_select(mask)
+                graduated = strip_neighbor_caches(batch.index_select(mask))  # messages carry the template's fields only
                 rest = batch.index_select(~mask) if not bool(mask.all()) else None
                 st._sync_state_to_batch(torch.nonzero(~mask).squeeze(1), 0, rest if rest is not None else batch)
                 batch = rest
@@ -177,7 +182,7 @@ class DistributedPipeline:
                     st._primed_for = None
         if st.next_rank is not None:
             out = graduated if graduated is not None else template
-            self._pending_send = out.isend(st.next_rank)
+            self._pending_send = out.isend(st.next_rank, template=template)
             self._keepalive = out
         elif graduated is not None and st.sinks:
             st._overflow_to_sinks(graduated)
@@ -246,7 +251,7 @@ class DistributedPipeline:
             # a stage may only finish one iteration after its predecessor: its last send is then already received
             self._done_flags[i] = int(self._stage_done(st, prior_done))
         if dist.is_initialized() and dist.get_world_size() > 1:
-            dist.all_reduce(self._done_flags, op=dist.ReduceOp.MAX)
+            dist.all_reduce(self._done_flags, op=dist.ReduceOp.MAX, group=self.group)
         return bool(self._done_flags.all())
 
     def run(self, max_iterations: int | None = None) -> None:
@@ -269,4 +274,4 @@ class DistributedPipeline:
             if st is not None:
                 st._close_hooks()
             if self.synchronized and dist.is_initialized():
-                dist.barrier()
+                dist.barrier(group=self.group)

@@ -53,12 +53,35 @@ class DataSink(abc.ABC):
         return head
 
 
+_TRANSIENT_PREFIXES = ("neighbor_matrix", "num_neighbors")
+
+
+def _without_transients(batch: Batch) -> Batch:
+    """Neighbour matrices are caches of the hooks that built them: their width follows the current neighbour capacity,
+    so two batches written at different times need not agree on it.  A sink stores the physical state only."""
+    drop = [k for k in batch._storage.keys() if k.startswith(_TRANSIENT_PREFIXES)]
+    if not drop:
+        return batch
+    out = batch.index_select(torch.arange(batch.num_graphs, device=batch.device)) if drop else batch
+    for k in drop:
+        del out[k]
+    return out
+
+
+def strip_neighbor_caches(batch: Batch) -> Batch:
+    """Remove the neighbour-matrix caches from ``batch`` IN PLACE (for a batch that is about to leave its stage: sinks,
+    hand-off messages whose field set is fixed by a template)."""
+    for k in [k for k in batch._storage.keys() if k.startswith(_TRANSIENT_PREFIXES)]:
+        del batch[k]
+    return batch
+
+
 def _masked(batch: Batch, mask: torch.Tensor | None) -> Batch | None:
     if mask is None:
-        return batch if batch.num_graphs else None
+        return _without_transients(batch) if batch.num_graphs else None
     if not bool(mask.any()):
         return None
-    return batch.index_select(mask)
+    return strip_neighbor_caches(batch.index_select(mask))
 
 
 class GPUBuffer(DataSink):

@@ -19,7 +19,7 @@ def test_system_builders():
     assert int((d < 1.8).sum()) >= 16
     c = build("ar_cluster", 150)
     assert c.num_nodes == 150 and not bool(c.pbc.any())
-    assert sorted(systems.SYSTEMS) == ["ar_cluster", "bcc_fe", "ch4", "fcc_cu", "nacl", "sio2"]
+    assert sorted(systems.SYSTEMS) == ["ar_cluster", "bcc_fe", "ch4", "fcc_cu", "nacl", "sio2", "water"]
 
 
 def test_runners_from_config(tmp_path):
@@ -44,3 +44,43 @@ cases:
     assert rows[1]["ms_per_step_median"] > 0 and rows[1]["mode"] == "nvt"
     shipped = runners.load_cases(str(__import__("pathlib").Path(runners.__file__).parent / "configs" / "mace_nvt.yaml"))
     assert shipped[0].model.endswith("MACEWrapper") and shipped[2].system == "sio2"
+
+
+def test_water_box_geometry_and_density():
+    import math
+
+    import torch
+
+    from nvalchemi_toolkit_b200.benchmark.systems import water_box
+
+    d = water_box(64, seed=3)
+    p = d.positions.double()
+    o, h1, h2 = p[0::3], p[1::3], p[2::3]
+    assert torch.allclose((h1 - o).norm(dim=1), torch.full((64,), 0.96, dtype=torch.float64), atol=1e-5)
+    cosang = ((h1 - o) * (h2 - o)).sum(1) / 0.96 ** 2
+    assert torch.allclose(torch.rad2deg(torch.acos(cosang)), torch.full((64,), 104.5, dtype=torch.float64), atol=1e-3)
+    vol = float(torch.linalg.det(d.cell.reshape(3, 3).double()))
+    assert abs(64 * 18.015 / 0.602214 / vol - 1.0) < 1e-6  # g / cm^3
+    assert abs(float(d.charges.sum())) < 1e-5 and d.atomic_numbers.tolist()[:3] == [8, 1, 1]
+    oo = torch.cdist(o, o) + 10 * torch.eye(64, dtype=torch.float64)
+    assert float(oo.min()) > 1.8 and math.isfinite(vol)
+
+
+def test_pipeline_benchmark_two_lanes_of_two_stages(tmp_path):
+    """Four gloo ranks = two independent lanes of FIRE -> NVT hand-off over water boxes with MACE + D3 + PME; every system
+    of the stream reaches the sinks of the MD ranks, lanes terminate independently."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr", "127.0.0.1",
+           "--master-port", "29671", "-m", "nvalchemi_toolkit_b200.benchmark.baseline_configs", "pipeline", "--systems", "6",
+           "--min-molecules", "5", "--max-molecules", "8", "--relax-steps", "2", "--md-steps", "2", "--channels", "4",
+           "--max-atoms", "48", "--max-batch", "2", "--max-neighbors", "48"]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    line = [ln for ln in res.stdout.splitlines() if ln.startswith("{")][-1]
+    out = json.loads(line)
+    assert out["lanes"] == 2 and out["systems_finished"] == 6 and out["unit"] == "atom-steps/s" and out["value"] > 0
