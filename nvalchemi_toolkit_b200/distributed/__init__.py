@@ -14,7 +14,7 @@ opaque fused operators the same treatment).  ``graph_padder`` keeps per-rank sha
 """
 from nvalchemi_toolkit_b200.distributed.config import DomainConfig, HookScope, StrategyKind
 from nvalchemi_toolkit_b200.distributed.partitioner import IndexPartitioner, SpatialPartitioner, factor_grid
-from nvalchemi_toolkit_b200.distributed.spec import (Consolidation, MLIPSpec, SPEC_AIMNET2_GRAPH_PARTITION,
+from nvalchemi_toolkit_b200.distributed.spec import (CompilePolicy, Consolidation, ForceStrategy, MLIPSpec, SPEC_AIMNET2_GRAPH_PARTITION,
                                                      SPEC_AIMNET2_HALO, SPEC_DEMO, SPEC_DFTD3_HALO,
                                                      SPEC_EWALD_REAL_HALO, SPEC_LJ_HALO, SPEC_MACE_CUEQ_HALO,
                                                      SPEC_MACE_GRAPH_PARTITION, SPEC_MACE_HALO, SPEC_PAIR_HALO, get_spec,
@@ -36,7 +36,7 @@ from nvalchemi_toolkit_b200.distributed import helpers
 from nvalchemi_toolkit_b200.distributed.pipeline2d import DomainPipeline
 from nvalchemi_toolkit_b200.distributed.peer_halo import PeerFailure, PeerHaloEngine, build_pull_tables, peer_memory_available
 
-__all__ = ["DomainConfig", "HookScope", "StrategyKind", "SpatialPartitioner", "IndexPartitioner", "factor_grid", "MLIPSpec",
+__all__ = ["CompilePolicy", "ForceStrategy", "DomainConfig", "HookScope", "StrategyKind", "SpatialPartitioner", "IndexPartitioner", "factor_grid", "MLIPSpec",
            "Consolidation", "get_spec", "register_spec", "HaloExchange", "ShardedBatch", "DistributedModel", "DistributedPipelineModel",
            "consolidate_outputs", "DomainParallel", "DomainPipeline", "DynamicsCoordinator", "ShardTensor", "halo_forward",
            "halo_scatter_correct", "helpers", "all_gather_rows", "all_to_all_rows", "SPEC_LJ_HALO", "SPEC_PAIR_HALO",

@@ -33,6 +33,49 @@ class Consolidation(str, Enum):
     REPLICATED = "replicated"       # the model needs no neighbours (per-atom terms only)
 
 
+class ForceStrategy(str, Enum):
+    """Who produces the forces of a distributed forward (reference ``distributed/spec.py:211-238``).
+
+    ``MODEL_INTERNAL``: the model returns forces itself (kernels with analytic forces); owned rows are complete because
+    ghost rows carry empty neighbour lists.  ``FRAMEWORK_FROM_NODE_ENERGY``: the model returns per-node energies, the
+    framework sums the owned ones, differentiates and returns ghost gradients to their owners.
+    ``FRAMEWORK_FROM_GLOBAL_ENERGY``: the model itself consolidates the per-system energy (it consumes the per-atom
+    ``energy_weights`` of the padded batch: 1 owned, 0 ghost) and the framework differentiates that energy as it is."""
+
+    MODEL_INTERNAL = "model_internal"
+    FRAMEWORK_FROM_NODE_ENERGY = "framework_from_node_energy"
+    FRAMEWORK_FROM_GLOBAL_ENERGY = "framework_from_global_energy"
+
+
+@dataclass(frozen=True)
+class CompilePolicy:
+    """Fixed-shape contract of a model under domain decomposition (reference ``distributed/spec.py:241-292``).
+
+    The reference uses it to keep a ``torch.compile``-d trajectory compiled; here nothing is traced, and the same
+    contract serves CUDA-graph replay and the peer-memory engine, whose buffers are sized once: ``static_shapes`` asks
+    for per-rank capacities agreed over the ranks (``graph_padder.resolve_cap``) instead of exact sizes, ``graph_padder``
+    names the padder (``None``: the COO edge-list padder), ``force_strategy`` declares who produces the forces and
+    ``stress_via_strain`` lets the framework obtain the virial by straining positions and cell (only sound for models
+    whose whole cell dependence is differentiable)."""
+
+    static_shapes: bool = True
+    graph_padder: object | None = None
+    force_strategy: ForceStrategy = ForceStrategy.MODEL_INTERNAL
+    stress_via_strain: bool = False
+
+    @property
+    def forces_via_autograd(self) -> bool:
+        return self.force_strategy is not ForceStrategy.MODEL_INTERNAL
+
+    @property
+    def consolidate_node_energy(self) -> bool:
+        return self.force_strategy is ForceStrategy.FRAMEWORK_FROM_NODE_ENERGY
+
+    @property
+    def energy_output(self) -> str:
+        return "atomic_energies" if self.force_strategy is ForceStrategy.FRAMEWORK_FROM_NODE_ENERGY else "energy"
+
+
 @dataclass(frozen=True)
 class MLIPSpec:
     name: str
@@ -52,6 +95,18 @@ class MLIPSpec:
     #: serialised storage policy of node features under ``refresh_per_layer`` (``None``: refresh only)
     storage_policy: dict | None = None
 
+    #: fixed-shape / force-production contract (``None``: derived from ``consolidation``)
+    compile: CompilePolicy | None = field(default=None, compare=False, hash=False)
+
+    @property
+    def force_strategy(self) -> ForceStrategy:
+        """The declared strategy, or the one the consolidation mode implies."""
+        if self.compile is not None:
+            return self.compile.force_strategy
+        if self.consolidation == Consolidation.WEIGHTED_ENERGY:
+            return ForceStrategy.FRAMEWORK_FROM_NODE_ENERGY
+        return ForceStrategy.MODEL_INTERNAL
+
     def ghost_width(self, cutoff: float, skin: float = 0.0) -> float:
         if self.refresh_per_layer:
             return cutoff + skin
@@ -66,6 +121,9 @@ class MLIPSpec:
         from dataclasses import asdict
 
         d = asdict(self)
+        d["compile"] = None if self.compile is None else {
+            "static_shapes": self.compile.static_shapes, "force_strategy": self.compile.force_strategy.value,
+            "stress_via_strain": self.compile.stress_via_strain}  # the padder object is not serialised
         d["strategy"], d["consolidation"] = self.strategy.value, self.consolidation.value
         d["node_outputs"], d["extensive_outputs"] = list(self.node_outputs), list(self.extensive_outputs)
         return d
@@ -75,6 +133,11 @@ class MLIPSpec:
         d = dict(d)
         d["strategy"], d["consolidation"] = StrategyKind(d["strategy"]), Consolidation(d["consolidation"])
         d["node_outputs"], d["extensive_outputs"] = tuple(d["node_outputs"]), tuple(d["extensive_outputs"])
+        c = d.pop("compile", None)
+        if c is not None:
+            d["compile"] = CompilePolicy(static_shapes=bool(c.get("static_shapes", True)),
+                                         force_strategy=ForceStrategy(c.get("force_strategy", "model_internal")),
+                                         stress_via_strain=bool(c.get("stress_via_strain", False)))
         return cls(**d)
 
     def save(self, path: str) -> None:

@@ -462,6 +462,10 @@ class BaseDynamics(HookRegistryMixin, _CommunicationMixin):
                              f"via `{type(self).__name__}(..., n_steps=N)`.")
         self._open_hooks()
         try:
+            if "forces" in getattr(self, "__needs_keys__", ()) and getattr(batch, "forces", None) is None:
+                # a batch that never saw the model (freshly built from raw coordinates): the first half-kick needs forces
+                self._call_hooks(DynamicsStage.BEFORE_COMPUTE, batch)
+                self.compute(batch)
             for _ in range(resolved):
                 batch, conv = self.step(batch)
                 if self.sampler is None and conv is not None and conv.numel() == batch.num_graphs:

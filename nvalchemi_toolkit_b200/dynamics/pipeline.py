@@ -110,6 +110,9 @@ class DistributedPipeline:
             st = self.stages[first]
             if st.active_batch is None and st.sampler is not None:
                 st.active_batch = st.sampler.build_initial_batch()
+                dev = self._device(st)
+                if st.active_batch.device != dev:  # datasets live on the host; the stage runs on its device
+                    st.active_batch = st.active_batch.to(dev)
             if st.active_batch is None:
                 raise RuntimeError("first pipeline stage needs a sampler or an active batch")
             st._ensure_bookkeeping_fields(st.active_batch)

@@ -616,3 +616,19 @@ def test_pipeline_of_domain_decomposed_stages():
             dyn.compute(batch)
             dyn.run(batch, n_steps=n)
         assert torch.allclose(torch.tensor(res[2][2][k], dtype=torch.float64), batch.positions, atol=1e-8)
+
+
+def test_force_strategy_and_compile_policy_round_trip(tmp_path):
+    from nvalchemi_toolkit_b200.distributed import CompilePolicy, ForceStrategy
+    from nvalchemi_toolkit_b200.distributed.spec import SPEC_LJ_HALO, SPEC_MACE_HALO
+
+    assert SPEC_LJ_HALO.force_strategy is ForceStrategy.MODEL_INTERNAL
+    assert SPEC_MACE_HALO.force_strategy is ForceStrategy.FRAMEWORK_FROM_NODE_ENERGY
+    pol = CompilePolicy(force_strategy=ForceStrategy.FRAMEWORK_FROM_GLOBAL_ENERGY, stress_via_strain=True)
+    assert pol.forces_via_autograd and not pol.consolidate_node_energy and pol.energy_output == "energy"
+    assert CompilePolicy(force_strategy=ForceStrategy.FRAMEWORK_FROM_NODE_ENERGY).energy_output == "atomic_energies"
+    spec = SPEC_MACE_HALO.with_(name="mace_global", compile=pol)
+    assert spec.force_strategy is ForceStrategy.FRAMEWORK_FROM_GLOBAL_ENERGY
+    spec.save(str(tmp_path / "spec.json"))
+    back = type(spec).load(str(tmp_path / "spec.json"))
+    assert back.compile == pol and back.name == "mace_global" and back.message_passes == 2

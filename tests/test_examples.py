@@ -15,7 +15,14 @@ FAST = ["basic/01_atomic_data_and_batch.py", "basic/02_neighbor_lists.py", "basi
         "advanced/15_biased_potential.py", "advanced/16_custom_hook_and_convergence.py", "advanced/17_custom_integrator.py",
         "intermediate/18_npt_triclinic.py", "intermediate/19_safety_and_monitoring.py",
         "intermediate/20_sharded_zarr_store.py", "distributed/21_graph_partition.py",
-        "distributed/22_relax_then_md_domain_parallel.py", "intermediate/23_data_parallel_training.py"]
+        "distributed/22_relax_then_md_domain_parallel.py", "intermediate/23_data_parallel_training.py",
+        "basic/24_nvt_langevin_thermostat.py", "basic/25_ase_interop.py", "advanced/26_mace_nvt.py",
+        "advanced/27_learned_charges_plus_ewald.py", "advanced/28_direct_force_model_nve.py",
+        "advanced/29_mace_energy_force_training.py", "distributed/30_bring_your_own_graph_transformer.py",
+        "distributed/31_npt_domain_parallel.py", "intermediate/32_three_stage_workflow.py",
+        "intermediate/33_training_with_live_reporting.py"]
+TWO_RANKS = ["distributed/13_stage_pipeline.py", "distributed/30_bring_your_own_graph_transformer.py",
+             "distributed/31_npt_domain_parallel.py", "distributed/34_pipeline_monitoring.py"]
 
 
 @pytest.mark.parametrize("script", FAST)
@@ -26,3 +33,17 @@ def test_example_runs(script):
                          timeout=300)
     assert res.returncode == 0, res.stderr[-2000:]
     assert res.stdout.strip()
+
+
+@pytest.mark.parametrize("script", TWO_RANKS)
+def test_example_runs_on_two_ranks(script):
+    """The distributed examples under ``torchrun`` with two gloo ranks."""
+    env = dict(os.environ, PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    port = 29700 + TWO_RANKS.index(script)
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                          "127.0.0.1", "--master-port", str(port), str(ROOT / "examples" / script)], env=env,
+                         capture_output=True, text=True, timeout=420)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "rank" in res.stdout
