@@ -51,6 +51,14 @@ class MACEConfig:
     atomic_energies: list[float] | None = None
     scale: float = 1.0
     shift: float = 0.0
+    #: ``"None"`` or ``"Agnesi"``: the radial basis then sees a species-pair dependent transform of the distance
+    #: (``mace.modules.radial.AgnesiTransform``, used by the MACE-MP foundation models); the PyTorch path implements it,
+    #: the native kernels evaluate the plain Bessel basis only, so a model with a transform runs the PyTorch path
+    distance_transform: str = "None"
+
+    def __post_init__(self) -> None:
+        if self.distance_transform not in ("None", "Agnesi"):
+            raise ValueError(f"distance_transform must be 'None' or 'Agnesi', got {self.distance_transform!r}")
 
     @classmethod
     def from_hidden_irreps(cls, hidden_irreps: str, **kw: Any) -> "MACEConfig":
@@ -64,6 +72,22 @@ class MACEConfig:
 def bessel_basis(r: torch.Tensor, r_max: float, n: int) -> torch.Tensor:
     k = torch.arange(1, n + 1, dtype=r.dtype, device=r.device) * (math.pi / r_max)
     return math.sqrt(2.0 / r_max) * torch.sin(k * r.unsqueeze(-1)) / r.unsqueeze(-1)
+
+
+# Covalent radii in Angstrom (Cordero et al., Dalton Trans. 2008; the table ASE ships), indexed by atomic number.
+COVALENT_RADII = (0.2, 0.31, 0.28, 1.28, 0.96, 0.84, 0.76, 0.71, 0.66, 0.57, 0.58, 1.66, 1.41, 1.21, 1.11, 1.07, 1.05, 1.02, 1.06,
+                  2.03, 1.76, 1.70, 1.60, 1.53, 1.39, 1.39, 1.32, 1.26, 1.24, 1.32, 1.22, 1.22, 1.20, 1.19, 1.20, 1.20, 1.16,
+                  2.20, 1.95, 1.90, 1.75, 1.64, 1.54, 1.47, 1.46, 1.42, 1.39, 1.45, 1.44, 1.42, 1.39, 1.39, 1.38, 1.39, 1.40,
+                  2.44, 2.15, 2.07, 2.04, 2.03, 2.01, 1.99, 1.98, 1.98, 1.96, 1.94, 1.92, 1.92, 1.89, 1.90, 1.87, 1.87,
+                  1.75, 1.70, 1.62, 1.51, 1.44, 1.41, 1.36, 1.36, 1.32, 1.45, 1.46, 1.48, 1.40, 1.50, 1.50)
+
+
+def agnesi_transform(r: torch.Tensor, r0: torch.Tensor, q: float = 0.9183, p: float = 4.5791, a: float = 1.0805) -> torch.Tensor:
+    """``1 / (1 + a x^q / (1 + x^(q - p)))`` with ``x = r / r0`` and ``r0`` the mean covalent radius of the pair: a smooth,
+    monotonically decreasing map of the distance onto (0, 1) that resolves the bonding region
+    (``mace/modules/radial.py`` ``AgnesiTransform``)."""
+    x = r / r0
+    return 1.0 / (1.0 + a * x.pow(q) / (1.0 + x.pow(q - p)))
 
 
 def polynomial_cutoff(r: torch.Tensor, r_max: float, p: int) -> torch.Tensor:
@@ -154,6 +178,10 @@ class MACE(nn.Module):
 
     def _use_native(self, positions: torch.Tensor, training: bool) -> bool:
         if self.backend == "torch":
+            return False
+        if self.config.distance_transform != "None":
+            if self.backend == "native":
+                raise RuntimeError("backend='native' evaluates the plain Bessel basis; distance_transform needs the PyTorch path")
             return False
         ok = positions.is_cuda and positions.dtype == torch.float32 and not training
         if self.backend == "native" and not ok:
@@ -254,7 +282,12 @@ class MACE(nn.Module):
         vec = positions[receiver] - positions[sender] + shifts
         r = vec.norm(dim=-1)
         Y = o3.spherical_harmonics(vec, cfg.max_ell, normalize=True)
-        ef = bessel_basis(r, cfg.r_max, cfg.num_bessel) * polynomial_cutoff(r, cfg.r_max, cfg.num_polynomial_cutoff).unsqueeze(-1)
+        r_basis = r
+        if cfg.distance_transform == "Agnesi":
+            rc = torch.tensor(COVALENT_RADII, dtype=r.dtype, device=r.device)[
+                torch.tensor(cfg.atomic_numbers, device=r.device)][species]
+            r_basis = agnesi_transform(r, 0.5 * (rc[sender] + rc[receiver]))
+        ef = bessel_basis(r_basis, cfg.r_max, cfg.num_bessel) * polynomial_cutoff(r, cfg.r_max, cfg.num_polynomial_cutoff).unsqueeze(-1)
         Z = len(cfg.atomic_numbers)
         h = (self.node_embedding / math.sqrt(Z))[species].unsqueeze(1)  # [N,1,C]
         total = positions.new_zeros(n)

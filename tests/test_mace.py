@@ -287,3 +287,37 @@ def test_hessian_output_matches_finite_differences_of_forces():
             f.append(w(bb)["forces"].detach().reshape(-1))
         fd = -(f[0] - f[1]) / (2 * eps)
         assert torch.allclose(H[:, col], fd, atol=1e-6), float((H[:, col] - fd).abs().max())
+
+
+def test_agnesi_distance_transform():
+    """The species-pair distance transform of the MACE foundation models: maps (0, inf) onto (1, 0) monotonically, equals
+    1 / (1 + a / 2) at the covalent distance, changes the energy, keeps forces consistent with finite differences."""
+    from nvalchemi_toolkit_b200.models.mace.model import COVALENT_RADII, agnesi_transform
+
+    r = torch.linspace(0.3, 6.0, 200, dtype=torch.float64)
+    t = agnesi_transform(r, torch.tensor(1.32, dtype=torch.float64))
+    assert bool((t[1:] < t[:-1]).all()) and 0.0 < float(t[-1]) < float(t[0]) < 1.0
+    at_r0 = agnesi_transform(torch.tensor(1.32, dtype=torch.float64), torch.tensor(1.32, dtype=torch.float64))
+    assert abs(float(at_r0) - 1.0 / (1.0 + 1.0805 / 2.0)) < 1e-12
+    assert COVALENT_RADII[1] == 0.31 and COVALENT_RADII[6] == 0.76 and COVALENT_RADII[29] == 1.32 and len(COVALENT_RADII) == 87
+    torch.manual_seed(0)
+    plain = MACE(MACEConfig(atomic_numbers=[29, 28], channels=8, avg_num_neighbors=20.0), backend="torch").double()
+    agn = MACE(MACEConfig(atomic_numbers=[29, 28], channels=8, avg_num_neighbors=20.0, distance_transform="Agnesi"), backend="torch").double()
+    agn.load_state_dict(plain.state_dict())
+    d = fcc_supercell(2, noise=0.1, dtype=torch.float64)
+    d.__dict__["atomic_numbers"] = torch.where(torch.arange(d.num_nodes) % 2 == 0, 29, 28)
+    b = Batch.from_data_list([d])
+    w0, w1 = MACEWrapper(plain), MACEWrapper(agn)
+    for w in (w0, w1):
+        w.model_config.active_outputs = {"energy", "forces"}
+    compute_neighbors(b, config=w0.model_config.neighbor_config)
+    e0, out = w0(b)["energy"], w1(b)
+    assert abs(float(e0 - out["energy"])) > 1e-6
+    i, eps = 3, 1e-5
+    bp, bm = b.clone(), b.clone()
+    bp.positions[i, 0] += eps
+    bm.positions[i, 0] -= eps
+    fd = -(float(w1(bp)["energy"]) - float(w1(bm)["energy"])) / (2 * eps)
+    assert abs(fd - float(out["forces"][i, 0])) < 1e-6 * max(1.0, abs(fd))
+    with pytest.raises(RuntimeError, match="distance_transform"):
+        MACE(MACEConfig(atomic_numbers=[29], channels=8, distance_transform="Agnesi"), backend="native")._use_native(b.positions, False)
