@@ -149,9 +149,13 @@ def train(args: argparse.Namespace) -> dict:
     from nvalchemi_toolkit_b200.dynamics.base import DynamicsStage  # noqa: F401  (neighbour hooks live on the wrapper)
     from nvalchemi_toolkit_b200.neighbors import compute_neighbors
     from nvalchemi_toolkit_b200.training import EnergyMSELoss, ForceMSELoss, OptimizerConfig, TrainingStrategy
-    from nvalchemi_toolkit_b200.training.hooks.library import FusedGradAllReduceHook
+    from nvalchemi_toolkit_b200.training.hooks.library import FusedGradAllReduceHook, GradientAccumulationHook
 
     rank, world, device = _dist()
+    micro = args.micro_batch or args.batch
+    if args.batch % micro:
+        raise SystemExit("train: --batch must be a multiple of --micro-batch")
+    accumulate = args.batch // micro
     per_rank = args.structures // world
     g = torch.Generator().manual_seed(7 + rank)
     reps = torch.randint(0, 3, (per_rank,), generator=g).tolist()
@@ -160,9 +164,9 @@ def train(args: argparse.Namespace) -> dict:
     wrapper.train()
     nc = wrapper.model_config.neighbor_config
     loader = []
-    for i in range(0, per_rank, args.batch):
+    for i in range(0, per_rank, micro):
         items = []
-        for k in range(i, min(i + args.batch, per_rank)):
+        for k in range(i, min(i + micro, per_rank)):
             rx, ry, rz = shapes[reps[k]]
             items.append(systems._crystal(torch.tensor([[0, 0, 0], [0.5, 0.5, 0], [0.5, 0, 0.5], [0, 0.5, 0.5]]),
                                           torch.full((4,), 29), 3.61, (rx, ry, rz), 0.15, 1000 * rank + k, torch.float32))
@@ -170,7 +174,7 @@ def train(args: argparse.Namespace) -> dict:
         _lj_labels(b)
         compute_neighbors(b, config=nc)  # the student's own (5 A) list replaces the teacher's
         loader.append(b)
-    hooks = [FusedGradAllReduceHook()] if world > 1 else []
+    hooks = ([GradientAccumulationHook(steps=accumulate)] if accumulate > 1 else []) + ([FusedGradAllReduceHook()] if world > 1 else [])
     loss = EnergyMSELoss(weight=1.0) + ForceMSELoss(weight=100.0)
     st = TrainingStrategy(wrapper, OptimizerConfig(kwargs={"lr": 1e-3}), loss_fn=loss, num_steps=args.warmup, devices=[str(device)],
                           hooks=hooks)
@@ -189,6 +193,7 @@ def train(args: argparse.Namespace) -> dict:
     return {"metric": "MLIP training structures/s (MACE 2x(128x0e+128x1o), Adam, energy + 100 x force MSE, batch %d / rank)" % args.batch,
             "value": n_struct / seconds, "unit": "structures/s", "n_gpus": world, "steps": args.steps, "seconds": seconds,
             "last_loss": float(st.last_losses["total_loss"]), "backend": args.backend, "data": "synthetic (LJ-labelled fcc Cu)",
+            "micro_batch": micro, "accumulation_steps": accumulate,
             "gradient_allreduce": "fused peer-memory all-reduce" if world > 1 and device.type == "cuda" else "none"}
 
 
@@ -302,7 +307,10 @@ def main(argv: list[str] | None = None) -> int:
     t.add_argument("--batch", type=int, default=8,
                    help="structures per rank and step (the differentiable PyTorch path keeps every per-edge tensor for the "
                         "double backward: 64 structures of this size need more than 180 GB)")
-    t.add_argument("--steps", type=int, default=8)
+    t.add_argument("--micro-batch", type=int, default=None,
+                   help="structures per forward / backward pass; gradients of batch / micro-batch passes are accumulated "
+                        "before the (single) reduction and optimiser step, e.g. --batch 64 --micro-batch 8")
+    t.add_argument("--steps", type=int, default=8, help="optimiser steps in the timed region")
     t.add_argument("--warmup", type=int, default=2)
     t.add_argument("--backend", default="torch", choices=["torch"], help="differentiable path used under autograd")
     pl = sub.add_parser("pipeline")

@@ -202,14 +202,14 @@ class FusedGradAllReduceHook(_Base):
         if self._flat is None:
             self._setup(ctx.workflow)
         if stage == S.BEFORE_BACKWARD:
-            self._armed = self._p2p is not None and self.overlap and not getattr(ctx, "accumulating", False)
+            self._armed = self._p2p is not None and self.overlap and getattr(ctx, "sync_gradients", True)
             self.num_overlapped = 0
             for b in self._buckets:
                 b["ready"], b["launched"] = 0, False
             if self._p2p is not None and self.status_check == "lazy":
                 self._p2p.check(wait=False)  # a rendezvous missed in the previous step surfaces here
             return
-        if getattr(ctx, "accumulating", False):
+        if not getattr(ctx, "sync_gradients", True):
             return  # gradients keep accumulating locally; the reduction happens with the last micro-batch
         world = dist.get_world_size()
         armed, self._armed = self._armed, False
@@ -271,7 +271,8 @@ class GradientAccumulationHook(_Base):
     def __call__(self, ctx: Any, stage: Enum) -> None:
         k = ctx.batch_count % self.steps
         if stage == S.BEFORE_BATCH:
-            ctx.accumulating = k != 0
+            ctx.accumulating = k != 0                     # keep the gradients of the previous micro-batches
+            ctx.sync_gradients = k == self.steps - 1      # the micro-batch that ends with the optimiser step
         elif stage == S.AFTER_LOSS and self.steps > 1:
             ctx.loss = ctx.loss / self.steps
         elif stage == S.BEFORE_OPTIMIZER_STEP and k != self.steps - 1:

@@ -129,6 +129,53 @@ def _dp_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+def _dp_accum_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+
+    from nvalchemi_toolkit_b200.training.hooks.library import GradientAccumulationHook
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        data = _dataset(8)
+        hook = FusedGradAllReduceHook()
+        calls = []
+        orig = dist.all_reduce
+
+        def spy(t, *a, **k):
+            calls.append(int(t.numel()))
+            return orig(t, *a, **k)
+
+        dist.all_reduce = spy
+        st = _strategy(num_steps=2, hooks=[GradientAccumulationHook(steps=2), hook])
+        for micro in range(4):  # optimiser step s = micro // 2 sees graphs [4 (s % 2), +4); rank r takes one per micro-batch
+            lo = 4 * ((micro // 2) % 2) + 2 * (micro % 2) + rank
+            st.train_batch(Batch.from_data_list(data[lo: lo + 1]))
+        dist.all_reduce = orig
+        big = [c for c in calls if c > 8]
+        q.put((rank, st.step_count, len(big), [p.detach().reshape(-1).tolist() for p in st.models["main"].parameters()]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gradient_accumulation_reduces_once_per_optimizer_step():
+    """With accumulation the cross-rank reduction runs with the LAST micro-batch of an optimiser step (once per step, on the
+    accumulated gradients), and the replicas stay in lock-step."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_dp_accum_worker, args=(r, 2, 29589, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {r[0]: r[1:] for r in (q.get(timeout=120) for _ in range(2))}
+    for p in procs:
+        p.join(timeout=30)
+    assert res[0][0] == res[1][0] == 2 and res[0][1] == res[1][1] == 2  # two optimiser steps, two gradient reductions
+    for a, b in zip(res[0][2], res[1][2]):
+        assert torch.allclose(torch.tensor(a), torch.tensor(b), atol=1e-7)
+
+
 def test_fused_gradient_allreduce_matches_single_process():
     import torch.multiprocessing as mp
 
