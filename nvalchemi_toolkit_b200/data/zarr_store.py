@@ -128,11 +128,29 @@ class ZarrArray:
     def _encode(self, arr: np.ndarray) -> bytes:
         return _codecs.encode(arr, self.meta["codecs"], self.dtype)
 
+    #: decoded chunks kept per array: random per-sample reads touch the same chunk (or shard) many times, and decoding a
+    #: compressed shard costs milliseconds.  Entries are validated against the file's size and modification time, so a
+    #: chunk rewritten by another writer object is decoded again.
+    CACHE_CHUNKS = 4
+
     def _read_chunk(self, i: int) -> np.ndarray:
         p = self._chunk_path(i)
-        if not p.exists():
+        try:
+            st = p.stat()
+        except FileNotFoundError:
             return np.full(self.chunk, self.meta.get("fill_value", 0), dtype=self.dtype)
-        return self._decode(p.read_bytes())
+        cache = self.__dict__.setdefault("_chunk_cache", {})
+        stamp = (st.st_size, st.st_mtime_ns)
+        hit = cache.get(i)
+        if hit is not None and hit[0] == stamp:
+            cache[i] = cache.pop(i)  # most recently used last
+            return hit[1]
+        arr = self._decode(p.read_bytes())
+        arr.setflags(write=False)  # shared with later readers of the same chunk
+        cache[i] = (stamp, arr)
+        while len(cache) > self.CACHE_CHUNKS:
+            cache.pop(next(iter(cache)))
+        return arr
 
     def read(self, start: int = 0, stop: int | None = None) -> np.ndarray:
         n = self.shape[0]
@@ -146,9 +164,10 @@ class ZarrArray:
             ch = self._read_chunk(ci)
             lo, hi = max(start, ci * cr) - ci * cr, min(stop, (ci + 1) * cr) - ci * cr
             parts.append(ch[lo:hi])
-        out = parts[0] if len(parts) == 1 else np.concatenate(parts, 0)
         tail = tuple(slice(0, s) for s in self.shape[1:])
-        return out[(slice(None),) + tail]
+        if len(parts) == 1:
+            return np.array(parts[0][(slice(None),) + tail])  # a copy: the chunk itself stays in the cache, read-only
+        return np.concatenate(parts, 0)[(slice(None),) + tail]
 
     def write(self, start: int, data: np.ndarray) -> None:
         """Overwrite rows ``[start, start + len(data))`` (the array must already be large enough)."""

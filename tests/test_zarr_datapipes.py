@@ -196,3 +196,49 @@ def test_blosc_frames_decode(tmp_path):
     assert zarr_codecs.blosc_decompress(stored) == raw
     codecs = [{"name": "bytes", "configuration": {"endian": "little"}}, {"name": "blosc", "configuration": {}}]
     assert np.array_equal(zarr_codecs.decode(frame(1, lz4, True), codecs, np.dtype("float32"), [4096]), x)
+
+
+def test_io_cli_sweep_edges_shards_and_read_orders(tmp_path, capsys):
+    """The IO benchmark command: two dataset sizes, edge arrays with their own shard size, every read mode and order; the
+    block shuffle keeps samples of a block together; options without a command mean ``roundtrip``."""
+    from nvalchemi_toolkit_b200.data import io_test
+
+    res = io_test.main(["-n", "60", "-n", "90", "--edges-per-atom", "4", "--compressor", "zstd", "--chunk-size", "512",
+                        "--shard-size", "2048", "--edge-shard-size", "4096", "--read-mode", "both", "--read-order", "all",
+                        "--read-block-size", "16", "--output-dir", str(tmp_path)])
+    assert [r["samples"] for r in res] == [60, 90]
+    for r in res:
+        assert r["roundtrip_ok"] and r["edges"] == 4 * r["atoms"] and r["compression_ratio"] > 1.0
+        assert {(p["mode"], p["order"]) for p in r["reads"]} == {(m, o) for m in io_test.READ_MODES for o in io_test.READ_ORDERS}
+        assert all(p["samples"] == r["samples"] and p["atoms"] == r["atoms"] for p in r["reads"])
+        assert abs(r["estimated_raw_bytes"] - r["raw_bytes"]) < 0.15 * r["raw_bytes"]
+    out = capsys.readouterr().out
+    assert "edge-shard=4096" in out and "block-shuffle" in out
+    idx = io_test.read_indices(50, "block-shuffle", seed=3, block=8)
+    assert sorted(idx) == list(range(50)) and idx != list(range(50))
+    assert all(idx[k + 1] == idx[k] + 1 for k in range(len(idx) - 1) if (idx[k] + 1) % 8 and idx[k] + 1 < 50)
+    assert io_test.fmt_bytes(1536) == "1.5 KiB" and io_test.fmt_bytes(12) == "12 B"
+
+
+def test_decoded_chunk_cache_sees_rewrites(tmp_path):
+    """Repeated reads of one chunk decode it once; a rewrite by ANOTHER array object is picked up (size / mtime stamp)."""
+    import numpy as np
+
+    from nvalchemi_toolkit_b200.data.zarr_store import ZarrArray, ZarrArrayConfig
+
+    a = ZarrArray.create(tmp_path / "x", (0, 3), np.float32, ZarrArrayConfig(chunk_rows=8, compressor="gzip"))
+    a.append(np.arange(48, dtype=np.float32).reshape(16, 3))
+    calls = []
+    orig = a._decode
+    a._decode = lambda raw: (calls.append(1), orig(raw))[1]
+    first = a.read(2, 5)
+    assert np.array_equal(a.read(2, 5), first) and len(calls) == 1
+    first[0, 0] = -1.0  # the caller owns what read() returns
+    assert a.read(2, 3)[0, 0] == 6.0
+    b = ZarrArray(tmp_path / "x")
+    b.write(2, np.full((1, 3), 99.0, dtype=np.float32))
+    import os
+    import time
+
+    os.utime(b._chunk_path(0), ns=(time.time_ns(), time.time_ns() + 1_000_000))
+    assert a.read(2, 3)[0, 0] == 99.0 and len(calls) == 2
