@@ -156,28 +156,48 @@ class DistributedModel(nn.Module):
 class DistributedPipelineModel(nn.Module):
     """Domain-decomposed ``PipelineModelWrapper``: every member of a direct group is evaluated with a halo of its own
     depth over the one owned partition, and the consolidated member outputs are summed like the pipeline does.
-    Reference: ``nvalchemi/distributed/distributed_pipeline.py:65-448``.  Groups that differentiate a summed energy
-    through wires are not decomposed here (evaluate such members in direct groups)."""
+    Reference: ``nvalchemi/distributed/distributed_pipeline.py:65-448``.
+
+    A group that differentiates its summed energy (``use_autograd``) or passes outputs along wires (predicted charges
+    into an electrostatics member) is decomposed AS ONE MODEL: the whole group runs on owned + ghost atoms with a ghost
+    layer as deep as the members' receptive fields chained together (a wired quantity on a ghost atom must itself be
+    exact before the next member reads it), every member sums its energy with the per-atom ``energy_weights`` of the
+    padded batch (1 owned, 0 ghost: MACE, DFT-D3, Ewald / PME and the pair potentials do), the group's autograd pass
+    yields gradients on all local rows and the ghost rows' share returns to the owners by the reverse halo."""
 
     def __init__(self, pipeline: Any, config: DomainConfig, group: Any = None, max_neighbors: int | None = None) -> None:
         super().__init__()
         from nvalchemi_toolkit_b200.models._utils import sum_outputs
+        from nvalchemi_toolkit_b200.models.pipeline import PipelineModelWrapper
 
         self.pipeline, self.config, self._sum = pipeline, config, sum_outputs
         self.model_config = pipeline.model_config
         self.members = nn.ModuleList()
+        active = set(pipeline.model_config.active_outputs)
+
+        def member_config(cutoff: float) -> DomainConfig:
+            d = {k: v for k, v in config.model_dump().items() if k != "ghost_width"}
+            d["cutoff"] = cutoff
+            return DomainConfig(**d)
+
         for g in pipeline.groups:
-            if g.use_autograd:
-                raise NotImplementedError("autograd groups are not domain-decomposed; use direct groups")
+            if g.use_autograd or any(s.wire for s in g.steps):
+                depth = 0.0
+                for s in g.steps:
+                    nc = s.model.model_config.neighbor_config
+                    spec = s.model.distribution_spec(config.strategy)
+                    passes = max(1, spec.message_passes) if spec is not None else 1
+                    depth += passes * ((nc.cutoff if nc is not None else 0.0) + config.skin)
+                sub = PipelineModelWrapper([g], additive_keys=set(pipeline.additive_keys))
+                sub.model_config.active_outputs = set(active) & set(sub.model_config.outputs)
+                group_spec = MLIPSpec("pipeline_group", message_passes=1, consolidation=Consolidation.WEIGHTED_ENERGY)
+                self.members.append(DistributedModel(sub, member_config(depth - config.skin), spec=group_spec, group=group,
+                                                     max_neighbors=max_neighbors, own_halo=True))
+                continue
             for s in g.steps:
-                if s.wire:
-                    raise NotImplementedError("wired members are not domain-decomposed")
                 nc = s.model.model_config.neighbor_config
-                member_cfg = config.model_copy(update={"cutoff": nc.cutoff if nc is not None else config.cutoff,
-                                                       "ghost_width": None})
-                member_cfg = DomainConfig(**{k: v for k, v in member_cfg.model_dump().items() if k != "ghost_width"})
-                self.members.append(DistributedModel(s.model, member_cfg, group=group, max_neighbors=max_neighbors,
-                                                     own_halo=True))
+                self.members.append(DistributedModel(s.model, member_config(nc.cutoff if nc is not None else config.cutoff),
+                                                     group=group, max_neighbors=max_neighbors, own_halo=True))
         deepest = max(m.spec.ghost_width(m.config.cutoff, m.config.skin) for m in self.members)
         self.spec = MLIPSpec("pipeline", message_passes=1, consolidation=Consolidation.WEIGHTED_ENERGY)
         self.required_ghost_width = deepest

@@ -28,8 +28,9 @@ class _CoulombEnergy(torch.autograd.Function):
     that makes ``dE/d(strain)`` of the affine strain construction equal ``-W``."""
 
     @staticmethod
-    def forward(ctx: Any, positions, charges, cells, batch_idx, energy, forces, virial, phi):
+    def forward(ctx: Any, positions, charges, cells, batch_idx, energy, forces, virial, phi, weights=None):
         ctx.save_for_backward(positions.detach(), cells.detach(), batch_idx, forces, virial, phi)
+        ctx.weights = weights
         return energy.clone()
 
     @staticmethod
@@ -39,10 +40,15 @@ class _CoulombEnergy(torch.autograd.Function):
         g = grad.reshape(-1)
         gp = -forces * g[b][:, None]
         gq = phi * g[b]
+        if ctx.weights is not None:
+            # one rank's share of a decomposed system: F_i and phi_i of an OWNED atom are already the derivatives of the
+            # whole system's energy; a ghost row's derivatives are accounted for on the rank that owns the atom
+            w = ctx.weights.to(gp.dtype)
+            gp, gq = gp * w[:, None], gq * w
         # dE/d(strain) = sum_i r_i (x) dE/dr_i + cell^T dE/dcell = -W  =>  dE/dcell = cell^-T (-W + sum_i r_i (x) F_i)
         rf = torch.zeros_like(virial).index_add_(0, b, positions[:, :, None] * forces[:, None, :])
         gc = torch.linalg.solve(cells.transpose(1, 2), (-virial + rf)) * g[:, None, None]
-        return gp, gq, gc, None, None, None, None, None
+        return gp, gq, gc, None, None, None, None, None, None
 
 
 class _CoulombBase(nn.Module, BaseModelMixin):
@@ -155,7 +161,8 @@ class _CoulombBase(nn.Module, BaseModelMixin):
             energy = _CoulombEnergy.apply(pos.double() if pos.dtype != torch.float64 else pos,
                                           q.double() if q.dtype != torch.float64 else q,
                                           cells.double() if cells.dtype != torch.float64 else cells,
-                                          r["batch_idx"], energy, r["forces"], r["virial"], r["phi"])
+                                          r["batch_idx"], energy, r["forces"], r["virial"], r["phi"],
+                                          getattr(data, "energy_weights", None))
         vol = torch.linalg.det(r["cells"].detach().double()).abs().clamp_min(1e-30)
         out = {"energy": energy.to(dtype).unsqueeze(-1), "forces": r["forces"].to(dtype),
                "virial": r["virial"].to(dtype), "stress": (-r["virial"] / vol[:, None, None]).to(dtype),

@@ -14,6 +14,7 @@ from nvalchemi_toolkit_b200.distributed import (DistributedModel, DomainConfig, 
                                                 halo_scatter_correct)
 from nvalchemi_toolkit_b200.dynamics import NVE
 from nvalchemi_toolkit_b200.hooks import NeighborListHook
+from nvalchemi_toolkit_b200.models.base import BaseModelMixin
 from nvalchemi_toolkit_b200.models.lj import LennardJonesModelWrapper
 from tests.helpers import fcc_supercell
 
@@ -711,3 +712,108 @@ def test_static_halo_matches_dynamic_exchange_on_two_ranks():
         p.join(timeout=30)
     assert all(r[1] is True for r in res), res
     assert all(r[2] > 0 for r in res)
+
+
+class _ChargeNet(torch.nn.Module, BaseModelMixin):
+    """Environment-dependent partial charges (no energy of its own): the upstream member of a wired group."""
+
+    def __init__(self, cutoff: float = 3.5) -> None:
+        super().__init__()
+        from nvalchemi_toolkit_b200.models.base import ModelConfig, NeighborConfig, NeighborListFormat
+
+        self.cutoff = cutoff
+        self.scale = torch.nn.Parameter(torch.tensor(0.4, dtype=torch.float64))
+        self.model_config = ModelConfig(outputs=frozenset({"energy", "charges"}), active_outputs={"energy", "charges"},
+                                        neighbor_config=NeighborConfig(cutoff=cutoff, format=NeighborListFormat.MATRIX))
+
+    def forward(self, data, **kw):
+        pos = data.positions
+        nm, num = data.neighbor_matrix.long(), data.num_neighbors.long()
+        n = pos.shape[0]
+        valid = torch.arange(nm.shape[1], device=nm.device)[None, :] < num[:, None]
+        j = torch.where(valid, nm, torch.zeros_like(nm))
+        cell = data.cell.reshape(-1, 3, 3)[data.batch_idx.long()].to(pos.dtype)
+        sh = torch.einsum("nki,nij->nkj", data.neighbor_matrix_shifts.to(pos.dtype), cell)
+        r = (pos[j] + sh - pos[:, None, :]).norm(dim=-1)
+        w = torch.where(valid & (r < self.cutoff), torch.exp(-r) * (1.0 - r / self.cutoff) ** 2, torch.zeros_like(r)).sum(-1)
+        sign = torch.where(data.atomic_numbers == 11, 1.0, -1.0).to(pos.dtype)
+        nb = data.cell.reshape(-1, 3, 3).shape[0]
+        return {"energy": pos.new_zeros(nb, 1) + 0.0 * w.sum(), "charges": sign * torch.tanh(self.scale * w)}
+
+    def distribution_spec(self, strategy=None):
+        from nvalchemi_toolkit_b200.distributed import Consolidation, MLIPSpec
+
+        return MLIPSpec("charge_net", message_passes=1, consolidation=Consolidation.WEIGHTED_ENERGY)
+
+
+def _wired_pipeline():
+    from nvalchemi_toolkit_b200.models.ewald import EwaldModelWrapper
+    from nvalchemi_toolkit_b200.models.pipeline import PipelineGroup, PipelineModelWrapper, PipelineStep
+
+    torch.manual_seed(0)
+    coulomb = EwaldModelWrapper(cutoff=5.0, accuracy=1e-6)
+    lj = LennardJonesModelWrapper(epsilon=0.01, sigma=2.6, cutoff=4.5, switch_width=0.5)
+    pipe = PipelineModelWrapper([PipelineGroup([PipelineStep(_ChargeNet(), wire={"charges": "node_charges"}), coulomb],
+                                               use_autograd=True), PipelineGroup([lj])])
+    pipe.model_config.active_outputs = {"energy", "forces"}
+    return pipe
+
+
+def _nacl_batch():
+    from nvalchemi_toolkit_b200.benchmark import build
+
+    return build("nacl", 2, dtype=torch.float64, noise=0.05)
+
+
+def _wired_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        from nvalchemi_toolkit_b200.distributed import DistributedPipelineModel, ShardTensor
+
+        pipe = _wired_pipeline()
+        cfg = DomainConfig(cutoff=5.0, skin=0.0)
+        dm = DistributedPipelineModel(pipe, cfg)
+        cfg = cfg.model_copy(update={"ghost_width": dm.required_ghost_width})
+        sh = ShardedBatch.from_batch(_nacl_batch(), cfg)
+        out = dm(sh)
+        forces = ShardTensor(out["forces"], sh).full_tensor()
+        q.put((rank, forces.tolist(), float(out["energy"].reshape(-1)[0]), dm.required_ghost_width, sh.n_owned))
+    except Exception as exc:
+        import traceback
+
+        q.put((rank, "".join(traceback.format_exception(exc))[-1500:], 0.0, 0.0, 0))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_wired_autograd_group_is_decomposed_as_one_model():
+    """Predicted charges wired into Ewald inside an autograd group, plus a direct pair-potential group, over two ranks:
+    energy and forces (including the response of the charges to the positions) match the single-process pipeline; the group's
+    ghost layer is as deep as both members' ranges chained."""
+    import torch.multiprocessing as mp
+
+    from nvalchemi_toolkit_b200.dynamics.base import DynamicsStage
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_wired_worker, args=(r, 2, 29796, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(2):
+        item = q.get(timeout=300)
+        res[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=30)
+    assert not isinstance(res[0][0], str), res[0][0]
+    pipe = _wired_pipeline()
+    batch = _nacl_batch()
+    dyn = NVE(pipe, dt=1.0, hooks=pipe.make_neighbor_hooks())
+    dyn._call_hooks(DynamicsStage.BEFORE_COMPUTE, batch)
+    ref = dyn.compute(batch)
+    for r in range(2):
+        assert abs(res[r][1] - float(ref["energy"].reshape(-1)[0])) < 1e-8
+        assert torch.allclose(torch.tensor(res[r][0], dtype=torch.float64), ref["forces"], atol=1e-8)
+        assert abs(res[r][2] - 8.5) < 1e-9 and 0 < res[r][3] < batch.num_nodes
