@@ -27,6 +27,17 @@ namespace {
 
 constexpr int L0_WARPS = 8;
 constexpr int NLM = 16, NK = 64;
+constexpr int L0_ROWS = 8;     // h3 rows a warp of the moments kernel keeps in flight
+constexpr int L0_SUB = 8;      // edges per staged sub-batch of the force kernel (8 x 512 B = 4 KB per warp and slot)
+
+// 16-byte asynchronous global -> shared copy (Ampere-style cp.async, bypassing L1) and its group fences.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Moments: lane owns hidden units k = lane and lane + 32 for all 16 harmonics.
 __global__ void __launch_bounds__(32 * L0_WARPS) l0_moments_kernel(
@@ -73,18 +84,18 @@ __global__ void __launch_bounds__(32 * L0_WARPS) l0_moments_kernel(
         __syncwarp();
         const int cnt = min(32, e1 - eb);
         if (okmask == 0u) continue;
-        // masked edges have Y = 0, so every edge of the batch is processed: four rows of h3 are in flight at a time
+        // masked edges have Y = 0, so every edge of the batch is processed: L0_ROWS rows of h3 are in flight at a time
         const float* hrow = h3 + ((int64_t)eb - e_chunk0) * hstride + lane;
-        for (int n4 = 0; n4 < cnt; n4 += 4) {
-          float ha[4], hb[4];
+        for (int n4 = 0; n4 < cnt; n4 += L0_ROWS) {
+          float ha[L0_ROWS], hb[L0_ROWS];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < L0_ROWS; ++u) {
             const int n = min(n4 + u, cnt - 1);
             ha[u] = __ldg(hrow + (int64_t)n * hstride);
             hb[u] = __ldg(hrow + (int64_t)n * hstride + 32);
           }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < L0_ROWS; ++u) {
             if (n4 + u >= cnt) break;
             const float4* yp = reinterpret_cast<const float4*>(Ys[warp][n4 + u]);
 #pragma unroll
@@ -114,6 +125,9 @@ __global__ void __launch_bounds__(32 * L0_WARPS) l0_force_kernel(
     const int* __restrict__ esend, const int* __restrict__ eS, const int* __restrict__ species, int nz, int i0, int ni,
     float rmax, float* __restrict__ grad_pos, double* __restrict__ virial) {
   __shared__ __align__(16) float P[L0_WARPS][32][32];  // [edge][lm | 16 + lm]: dE/dY and the radial factor per harmonic
+  // staged (value | derivative) rows, two slots per warp: 64 KB, above the static limit, hence dynamic shared memory
+  extern __shared__ __align__(16) float l0_stage[];
+  float (*H)[2][L0_SUB][2 * NK] = reinterpret_cast<float (*)[2][L0_SUB][2 * NK]>(l0_stage);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int lm = lane & 15, half = lane >> 4;
   const int gw = blockIdx.x * L0_WARPS + warp, nw = gridDim.x * L0_WARPS;
@@ -146,23 +160,39 @@ __global__ void __launch_bounds__(32 * L0_WARPS) l0_force_kernel(
         // ---- lane = (lm, half): contraction of Q with the two h3 rows of every live edge
         const int cnt = min(32, e1 - eb);
         if (okmask != 0u) {
-          // every edge of the batch is contracted (results of masked edges are not used); the 16 vector loads of an
-          // edge are issued before its multiply-adds, and two independent accumulators per sum shorten the chains
-          for (int n = 0; n < cnt; ++n) {
-            const float4* hv = reinterpret_cast<const float4*>(h3 + (2 * ((int64_t)(eb + n) - e_chunk0)) * NK + 32 * half);
-            float4 a[8], d[8];
+          // The value and derivative rows of consecutive edges are one contiguous block (512 B per edge).  The warp stages
+          // it in shared memory in sub-batches of L0_SUB edges with 16-byte asynchronous copies, two sub-batches in
+          // flight, so the loads of the next edges overlap the multiply-adds of the current ones (every edge of the
+          // batch is contracted; results of masked edges are not used).
+          const float* hblock = h3 + (2 * ((int64_t)eb - e_chunk0)) * NK;
+          const int nsub = (cnt + L0_SUB - 1) / L0_SUB;
+          auto stage = [&](int sb) {
+            float* dst = &H[warp][sb & 1][0][0];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) { a[k] = __ldg(hv + k); d[k] = __ldg(hv + NK / 4 + k); }
-            float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+            for (int u = 0; u < L0_SUB; ++u)
+              if (sb * L0_SUB + u < cnt) cp_async16(dst + u * 2 * NK + 4 * lane, hblock + ((int64_t)(sb * L0_SUB + u)) * 2 * NK + 4 * lane);
+            cp_async_commit();
+          };
+          stage(0);
+          for (int sb = 0; sb < nsub; ++sb) {
+            if (sb + 1 < nsub) { stage(sb + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+            __syncwarp();
+            const int m = min(L0_SUB, cnt - sb * L0_SUB);
+            for (int u = 0; u < m; ++u) {
+              const float4* hv = reinterpret_cast<const float4*>(&H[warp][sb & 1][u][32 * half]);
+              float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              p0 = fmaf(q[k].x, a[k].x, p0); p1 = fmaf(q[k].y, a[k].y, p1); p0 = fmaf(q[k].z, a[k].z, p0); p1 = fmaf(q[k].w, a[k].w, p1);
-              d0 = fmaf(q[k].x, d[k].x, d0); d1 = fmaf(q[k].y, d[k].y, d1); d0 = fmaf(q[k].z, d[k].z, d0); d1 = fmaf(q[k].w, d[k].w, d1);
+              for (int k = 0; k < 8; ++k) {
+                const float4 a = hv[k], d = hv[NK / 4 + k];
+                p0 = fmaf(q[k].x, a.x, p0); p1 = fmaf(q[k].y, a.y, p1); p0 = fmaf(q[k].z, a.z, p0); p1 = fmaf(q[k].w, a.w, p1);
+                d0 = fmaf(q[k].x, d.x, d0); d1 = fmaf(q[k].y, d.y, d1); d0 = fmaf(q[k].z, d.z, d0); d1 = fmaf(q[k].w, d.w, d1);
+              }
+              float p = p0 + p1, pd = d0 + d1;
+              p += __shfl_xor_sync(0xffffffffu, p, 16);
+              pd += __shfl_xor_sync(0xffffffffu, pd, 16);
+              if (half == 0) { P[warp][sb * L0_SUB + u][lm] = p; P[warp][sb * L0_SUB + u][16 + lm] = pd; }
             }
-            float p = p0 + p1, pd = d0 + d1;
-            p += __shfl_xor_sync(0xffffffffu, p, 16);
-            pd += __shfl_xor_sync(0xffffffffu, pd, 16);
-            if (half == 0) { P[warp][n][lm] = p; P[warp][n][16 + lm] = pd; }
+            __syncwarp();  // the slot is refilled two iterations later
           }
         }
         __syncwarp();
@@ -255,7 +285,10 @@ void mace_l0_force(const Tensor& h3, const Tensor& Q, const Tensor& pos, const T
   NVA_CHECK_CONTIG(h3); NVA_CHECK_CONTIG(Q); NVA_CHECK_CONTIG(pos); NVA_CHECK_CONTIG(grad_pos);
   TORCH_CHECK(Q.dim() == 4 && Q.size(2) == NLM && Q.size(3) == NK && h3.size(-1) == NK, "mace_l0_force: bad shapes");
   if (ni == 0) return;
-  l0_force_kernel<<<l0_grid((int)ni), 32 * L0_WARPS, 0, at::cuda::getCurrentCUDAStream()>>>(
+  constexpr int kStageBytes = L0_WARPS * 2 * L0_SUB * 2 * NK * (int)sizeof(float);
+  // above the 48 KB static limit: opt in (per device; a few microseconds per call)
+  C10_CUDA_CHECK(cudaFuncSetAttribute(l0_force_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes));
+  l0_force_kernel<<<l0_grid((int)ni), 32 * L0_WARPS, kStageBytes, at::cuda::getCurrentCUDAStream()>>>(
       h3.data_ptr<float>(), e_chunk0, Q.data_ptr<float>(), pos.data_ptr<float>(), cell.data_ptr<float>(),
       batch_idx.data_ptr<int>(), eptr.data_ptr<int>(), esend.data_ptr<int>(), eS.data_ptr<int>(), species.data_ptr<int>(),
       (int)Q.size(1), (int)i0, (int)ni, (float)rmax, grad_pos.data_ptr<float>(),

@@ -436,12 +436,28 @@ def write_header(path: str) -> None:
             for (e, M), tl in groups.items():
                 expr = " + ".join(f"{coef:.9e}f*" + "*".join(f"x[{i}]" for i in mono) for mono, coef in tl)
                 fwd.append(f"  out[{M}] = fmaf(W({e}), {expr}, out[{M}]);")
-                bwd.append(f"  {{ const float s_ = W({e})*g[{M}];")
+                # adjoint of one (basis element, output component) block: d/dx_a of every monomial, merged per target a
+                # and per remaining factor product, so that a term costs one fma on a product x_b*x_c that the compiler
+                # can share between blocks (the parenthesised product is the same expression everywhere)
+                bwd.append(f"  {{ const float s_ = W({e})*g[{M}]; float t_;")
+                per_target: dict[int, dict[tuple[int, ...], float]] = {}
                 for mono, coef in tl:
                     for q in range(len(mono)):
-                        rest = [f"x[{i}]" for k, i in enumerate(mono) if k != q]
-                        fac = "*".join([f"{coef:.9e}f"] + rest)
-                        bwd.append(f"    dx[{mono[q]}] = fmaf(s_, {fac}, dx[{mono[q]}]);")
+                        rest = tuple(sorted(i for k, i in enumerate(mono) if k != q))
+                        acc = per_target.setdefault(mono[q], {})
+                        acc[rest] = acc.get(rest, 0.0) + coef
+                for a_, rests in sorted(per_target.items()):
+                    items = [(r_, c_) for r_, c_ in sorted(rests.items()) if c_ != 0.0]
+                    if not items:
+                        continue
+                    if len(items[0][0]) == 0:      # nu = 1: the derivative is the coefficient itself
+                        bwd.append(f"    dx[{a_}] = fmaf(s_, {items[0][1]:.9e}f, dx[{a_}]);")
+                        continue
+                    prod = lambda r_: "(" + "*".join(f"x[{i}]" for i in r_) + ")"  # noqa: E731
+                    bwd.append(f"    t_ = {items[0][1]:.9e}f*{prod(items[0][0])};")
+                    for r_, c_ in items[1:]:
+                        bwd.append(f"    t_ = fmaf({c_:.9e}f, {prod(r_)}, t_);")
+                    bwd.append(f"    dx[{a_}] = fmaf(s_, t_, dx[{a_}]);")
                 bwd.append("  }")
             lines += [f"#define MACE_SYM_FWD_{nu}_{L}(x, out) do {{ \\"] + [t + " \\" for t in fwd] + ["} while (0)"]
             lines += [f"#define MACE_SYM_BWD_{nu}_{L}(x, g, dx) do {{ \\"] + [t + " \\" for t in bwd] + ["} while (0)", ""]

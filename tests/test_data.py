@@ -168,3 +168,30 @@ def test_planned_put_makes_no_host_sync():
     finally:
         torch.cuda.set_sync_debug_mode("default")
     assert buf.num_graphs == 8 and buf.num_nodes == 9 * 2 + 3 + 2
+
+
+def test_lazy_counts_after_planned_put(device):
+    """After a planned put the host counts are pending (still on the device) until first read; the derived CSR views and a
+    host-path modification afterwards see the resolved values."""
+    from nvalchemi_toolkit_b200.data.level_storage import _buffer_ops
+
+    if _buffer_ops() is None:
+        pytest.skip("native library not built")
+    src = random_batch([3, 5, 2], n_edges=2, periodic=True, device=device, seed=4)
+    buf = Batch.empty(num_systems=6, num_nodes=32, num_edges=32, template=src, device=device)
+    buf.put(src, torch.tensor([True, False, True], device=device))
+    atoms = buf._atoms_group
+    assert atoms._pending is not None and buf._system_group._pending is not None
+    ptr, count = atoms.device_csr()
+    assert int(count) == 2 and ptr[:3].tolist() == [0, 3, 5]
+    assert buf.num_graphs == 2 and atoms._pending is None            # resolved by the read
+    assert buf.num_nodes == 5 and buf.num_edges == 4
+    assert buf.batch_ptr.tolist() == [0, 3, 5] and buf.batch_idx.tolist() == [0, 0, 0, 1, 1]
+    assert atoms.lengths[:3].tolist() == [3, 2, 0]
+    buf.put(src, torch.tensor([False, True, False], device=device))   # counts pending again, then a host-path append
+    more = random_batch([4], n_edges=2, periodic=True, device=device, seed=9)
+    buf.put(more, torch.tensor([True], device=device))
+    assert buf.num_graphs == 4 and buf.num_nodes == 14 and buf.batch_ptr.tolist() == [0, 3, 5, 10, 14]
+    got = buf.get_data(2)
+    assert torch.equal(got.positions.cpu(), src.get_data(1).positions.cpu())
+    assert torch.equal(got.neighbor_list.cpu(), src.get_data(1).neighbor_list.cpu())
