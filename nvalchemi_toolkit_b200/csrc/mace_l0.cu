@@ -27,7 +27,7 @@ namespace {
 
 constexpr int L0_WARPS = 8;
 constexpr int NLM = 16, NK = 64;
-constexpr int L0_ROWS = 8;     // h3 rows a warp of the moments kernel keeps in flight
+constexpr int L0_MSUB = 16;    // edges per staged sub-batch of the moments kernel (16 x 256 B = 4 KB per warp and slot)
 constexpr int L0_SUB = 8;      // edges per staged sub-batch of the force kernel (8 x 512 B = 4 KB per warp and slot)
 
 // 16-byte asynchronous global -> shared copy (Ampere-style cp.async, bypassing L1) and its group fences.
@@ -46,6 +46,8 @@ __global__ void __launch_bounds__(32 * L0_WARPS) l0_moments_kernel(
     const int* __restrict__ eS, const int* __restrict__ species, int nz, int i0, int ni, float rmax,
     float* __restrict__ A, int hstride) {
   __shared__ __align__(16) float Ys[L0_WARPS][32][NLM];
+  extern __shared__ __align__(16) float l0_stage[];  // staged h3 rows, two slots per warp (64 KB: dynamic shared memory)
+  float (*Hs)[2][L0_MSUB][NK] = reinterpret_cast<float (*)[2][L0_MSUB][NK]>(l0_stage);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gw = blockIdx.x * L0_WARPS + warp, nw = gridDim.x * L0_WARPS;
   for (int r = gw; r < ni; r += nw) {
@@ -84,29 +86,39 @@ __global__ void __launch_bounds__(32 * L0_WARPS) l0_moments_kernel(
         __syncwarp();
         const int cnt = min(32, e1 - eb);
         if (okmask == 0u) continue;
-        // masked edges have Y = 0, so every edge of the batch is processed: L0_ROWS rows of h3 are in flight at a time
-        const float* hrow = h3 + ((int64_t)eb - e_chunk0) * hstride + lane;
-        for (int n4 = 0; n4 < cnt; n4 += L0_ROWS) {
-          float ha[L0_ROWS], hb[L0_ROWS];
+        // masked edges have Y = 0, so every edge of the batch is processed.  The value rows (256 B each, `hstride` floats
+        // apart) are staged in shared memory in sub-batches of L0_MSUB edges with 16-byte asynchronous copies, two
+        // sub-batches in flight: the loads of the next edges overlap the multiply-adds of the current ones.
+        const float* hbase = h3 + ((int64_t)eb - e_chunk0) * hstride;
+        const int nsub = (cnt + L0_MSUB - 1) / L0_MSUB;
+        auto stage = [&](int sb) {
+          float* dst = &Hs[warp][sb & 1][0][0];
 #pragma unroll
-          for (int u = 0; u < L0_ROWS; ++u) {
-            const int n = min(n4 + u, cnt - 1);
-            ha[u] = __ldg(hrow + (int64_t)n * hstride);
-            hb[u] = __ldg(hrow + (int64_t)n * hstride + 32);
+          for (int u = 0; u < L0_MSUB / 2; ++u) {
+            const int n = 2 * u + (lane >> 4), w = lane & 15;  // edge of the sub-batch, 16-byte piece of its row
+            if (sb * L0_MSUB + n < cnt) cp_async16(dst + n * NK + 4 * w, hbase + (int64_t)(sb * L0_MSUB + n) * hstride + 4 * w);
           }
-#pragma unroll
-          for (int u = 0; u < L0_ROWS; ++u) {
-            if (n4 + u >= cnt) break;
-            const float4* yp = reinterpret_cast<const float4*>(Ys[warp][n4 + u]);
+          cp_async_commit();
+        };
+        stage(0);
+        for (int sb = 0; sb < nsub; ++sb) {
+          if (sb + 1 < nsub) { stage(sb + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+          __syncwarp();
+          const int m = min(L0_MSUB, cnt - sb * L0_MSUB);
+#pragma unroll 2
+          for (int u = 0; u < m; ++u) {
+            const float ha = Hs[warp][sb & 1][u][lane], hb = Hs[warp][sb & 1][u][lane + 32];
+            const float4* yp = reinterpret_cast<const float4*>(Ys[warp][sb * L0_MSUB + u]);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const float4 y = yp[q];
-              acc0[4 * q] = fmaf(y.x, ha[u], acc0[4 * q]); acc1[4 * q] = fmaf(y.x, hb[u], acc1[4 * q]);
-              acc0[4 * q + 1] = fmaf(y.y, ha[u], acc0[4 * q + 1]); acc1[4 * q + 1] = fmaf(y.y, hb[u], acc1[4 * q + 1]);
-              acc0[4 * q + 2] = fmaf(y.z, ha[u], acc0[4 * q + 2]); acc1[4 * q + 2] = fmaf(y.z, hb[u], acc1[4 * q + 2]);
-              acc0[4 * q + 3] = fmaf(y.w, ha[u], acc0[4 * q + 3]); acc1[4 * q + 3] = fmaf(y.w, hb[u], acc1[4 * q + 3]);
+              acc0[4 * q] = fmaf(y.x, ha, acc0[4 * q]); acc1[4 * q] = fmaf(y.x, hb, acc1[4 * q]);
+              acc0[4 * q + 1] = fmaf(y.y, ha, acc0[4 * q + 1]); acc1[4 * q + 1] = fmaf(y.y, hb, acc1[4 * q + 1]);
+              acc0[4 * q + 2] = fmaf(y.z, ha, acc0[4 * q + 2]); acc1[4 * q + 2] = fmaf(y.z, hb, acc1[4 * q + 2]);
+              acc0[4 * q + 3] = fmaf(y.w, ha, acc0[4 * q + 3]); acc1[4 * q + 3] = fmaf(y.w, hb, acc1[4 * q + 3]);
             }
           }
+          __syncwarp();  // the slot is refilled two iterations later
         }
       }
       float* ap = A + (((int64_t)i * nz + s) * NLM) * NK + lane;
@@ -270,7 +282,11 @@ void mace_l0_moments(const Tensor& h3, const Tensor& pos, const Tensor& cell, co
   TORCH_CHECK(h3.dim() == 2 && h3.stride(1) == 1, "mace_l0_moments: h3 is [E, 64] (rows may be strided)");
   TORCH_CHECK(A.dim() == 4 && A.size(2) == NLM && A.size(3) == NK && h3.size(-1) == NK, "mace_l0_moments: bad shapes");
   if (ni == 0) return;
-  l0_moments_kernel<<<l0_grid((int)ni), 32 * L0_WARPS, 0, at::cuda::getCurrentCUDAStream()>>>(
+  TORCH_CHECK(h3.stride(0) % 4 == 0 && reinterpret_cast<uintptr_t>(h3.data_ptr<float>()) % 16 == 0,
+              "mace_l0_moments: h3 rows must start on 16-byte boundaries");
+  constexpr int kStageBytes = L0_WARPS * 2 * L0_MSUB * NK * (int)sizeof(float);
+  C10_CUDA_CHECK(cudaFuncSetAttribute(l0_moments_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes));
+  l0_moments_kernel<<<l0_grid((int)ni), 32 * L0_WARPS, kStageBytes, at::cuda::getCurrentCUDAStream()>>>(
       h3.data_ptr<float>(), e_chunk0, pos.data_ptr<float>(), cell.data_ptr<float>(), batch_idx.data_ptr<int>(),
       eptr.data_ptr<int>(), esend.data_ptr<int>(), eS.data_ptr<int>(), species.data_ptr<int>(), (int)A.size(1), (int)i0,
       (int)ni, (float)rmax, A.data_ptr<float>(), (int)h3.stride(0));

@@ -48,6 +48,47 @@ __global__ void bin_atoms_kernel(int64_t n, const T* __restrict__ pos, const T* 
   bin_id[i] = (int64_t)I[6] + lin;
 }
 
+// Per-system bounds of the fractional coordinates (needed for the bin origin / extent of non-periodic directions), in
+// one pass over the atoms: block-wide min / max in shared memory when the whole block belongs to one system (atoms are
+// sorted by system), thread-level atomics otherwise.  Bounds are kept as order-preserving integer codes of floats.
+__device__ __forceinline__ int float_order_code(float f) {
+  const int i = __float_as_int(f);
+  return i >= 0 ? i : i ^ 0x7fffffff;
+}
+template <typename T>
+__global__ void frac_bounds_kernel(int64_t n, const T* __restrict__ pos, const T* __restrict__ cell_inv,
+                                   const int* __restrict__ batch_idx, int* __restrict__ lo, int* __restrict__ hi) {
+  __shared__ int s_lo[3], s_hi[3], s_first, s_same;
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  const bool live = i < n;
+  const int s = live ? batch_idx[i] : -1;
+  if (threadIdx.x == 0) {
+    s_first = s; s_same = 1;
+    for (int c = 0; c < 3; ++c) { s_lo[c] = 0x7fffffff; s_hi[c] = (int)0x80000000; }
+  }
+  __syncthreads();
+  if (live && s != s_first) s_same = 0;  // benign race: every writer stores the same value
+  __syncthreads();
+  int code[3] = {0, 0, 0};
+  if (live) {
+    const T* Hi = cell_inv + 9 * s;
+    const T x = pos[3 * i], y = pos[3 * i + 1], z = pos[3 * i + 2];
+    for (int c = 0; c < 3; ++c)
+      code[c] = float_order_code((float)((double)x * Hi[c] + (double)y * Hi[3 + c] + (double)z * Hi[6 + c]));
+  }
+  if (s_same) {
+    if (live)
+      for (int c = 0; c < 3; ++c) { atomicMin(&s_lo[c], code[c]); atomicMax(&s_hi[c], code[c]); }
+    __syncthreads();
+    if (threadIdx.x < 3 && s_first >= 0) {
+      atomicMin(lo + 3 * s_first + threadIdx.x, s_lo[threadIdx.x]);
+      atomicMax(hi + 3 * s_first + threadIdx.x, s_hi[threadIdx.x]);
+    }
+  } else if (live) {
+    for (int c = 0; c < 3; ++c) { atomicMin(lo + 3 * s + c, code[c]); atomicMax(hi + 3 * s + c, code[c]); }
+  }
+}
+
 template <typename T>
 __global__ void search_kernel(int64_t n, const T* __restrict__ pos, const T* __restrict__ cell,
                               const int* __restrict__ batch_idx, const int* __restrict__ fi,
@@ -196,12 +237,34 @@ void neighbor_matrix_build(const Tensor& pos, const Tensor& cell, const Tensor& 
   Tensor celld = cell.to(at::kDouble);
   Tensor inv = at::linalg_inv(celld);                                    // [B,3,3]
   Tensor face = at::reciprocal(inv.norm(2, {1}));                         // [B,3] distance per unit fractional
-  Tensor bidx = batch_idx.to(at::kLong);
-  Tensor frac = at::bmm(pos.to(at::kDouble).unsqueeze(1), inv.index_select(0, bidx)).squeeze(1);  // [N,3]
   Tensor pbcb = pbc.to(at::kBool);
-  Tensor idx3 = bidx.unsqueeze(1).expand({n, 3});
-  Tensor fmin = at::full({B, 3}, 1e300, fopt).scatter_reduce(0, idx3, frac, "amin", true);
-  Tensor fmax = at::full({B, 3}, -1e300, fopt).scatter_reduce(0, idx3, frac, "amax", true);
+  Tensor fmin, fmax;
+  if (pos.is_cuda()) {
+    // one kernel instead of five per-atom library operations (cast, gather of the inverse cells, batched product, two
+    // scatter-reductions); the float bounds are widened by a few ulps so that every atom lies inside them
+    Tensor lo = at::full({B, 3}, (int64_t)0x7fffffff, pos.options().dtype(at::kInt));
+    Tensor hi = at::full({B, 3}, (int64_t)INT32_MIN, pos.options().dtype(at::kInt));
+    Tensor inv_p = inv.to(pos.scalar_type()).contiguous();
+    const int64_t nb_ = (n + kThreads - 1) / kThreads;
+    AT_DISPATCH_FLOATING_TYPES(pos.scalar_type(), "frac_bounds", [&] {
+      frac_bounds_kernel<scalar_t><<<(unsigned)nb_, kThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
+          n, pos.data_ptr<scalar_t>(), inv_p.data_ptr<scalar_t>(), batch_idx.data_ptr<int>(), lo.data_ptr<int>(), hi.data_ptr<int>());
+    });
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    auto decode = [](const Tensor& code) {
+      return at::where(code >= 0, code, at::bitwise_xor(code, at::full_like(code, (int64_t)0x7fffffff))).view(at::kFloat).to(at::kDouble);
+    };
+    fmin = at::nan_to_num(decode(lo), 0.0, 0.0, 0.0);  // a system without atoms keeps the initial codes
+    fmax = at::nan_to_num(decode(hi), 0.0, 0.0, 0.0);
+    fmin = fmin - (fmin.abs() * 4e-7 + 1e-7);
+    fmax = fmax + (fmax.abs() * 4e-7 + 1e-7);
+  } else {
+    Tensor bidx = batch_idx.to(at::kLong);
+    Tensor frac = at::bmm(pos.to(at::kDouble).unsqueeze(1), inv.index_select(0, bidx)).squeeze(1);  // [N,3]
+    Tensor idx3 = bidx.unsqueeze(1).expand({n, 3});
+    fmin = at::full({B, 3}, 1e300, fopt).scatter_reduce(0, idx3, frac, "amin", true);
+    fmax = at::full({B, 3}, -1e300, fopt).scatter_reduce(0, idx3, frac, "amax", true);
+  }
   Tensor origin = at::where(pbcb, at::zeros_like(fmin), fmin);
   Tensor extent = at::where(pbcb, at::ones_like(fmin), (fmax - fmin) + 1e-6);
   Tensor natoms = (batch_ptr.slice(0, 1) - batch_ptr.slice(0, 0, B)).to(at::kDouble);  // [B]
