@@ -527,7 +527,10 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
     node_e = model.atomic_energies.to(pos.dtype)[species] + node_e * scale + shift
     ew = None if energy_weights is None else energy_weights[:n].to(pos.dtype)
     e_sum = node_e if ew is None else node_e * ew
-    energy = torch.zeros(num_graphs, dtype=torch.float64, device=dev).index_add_(0, batch[:n], e_sum.double()).to(pos.dtype)
+    if num_graphs == 1:  # one system: a plain float64 sum instead of an indexed accumulation
+        energy = e_sum.sum(dtype=torch.float64).reshape(1).to(pos.dtype)
+    else:
+        energy = torch.zeros(num_graphs, dtype=torch.float64, device=dev).index_add_(0, batch[:n], e_sum.double()).to(pos.dtype)
     out: dict[str, torch.Tensor | None] = {"energy": energy, "node_energy": node_e, "forces": None, "stress": None,
                                             "hessian": None}
     if not (compute_force or compute_stress):
