@@ -184,3 +184,61 @@ def test_grouped_gemm_matches_fp32_reference():
     assert float((wide[:, :256].double() - ref64).abs().max()) < 2e-3 * float(ref64.abs().max())
     assert float(wide[:, 256:].abs().max()) == 0.0
     assert gemm.check_errors(a) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("width", [3, 8, 512])
+def test_halo_kernels_against_index_ops_single_process(width):
+    """The peer-memory halo kernels on ONE GPU: three buffers of this process stand for three ranks' arenas (the kernels only
+    see pointer tables).  Pull = gather of the owners' rows (+ optional shift), push-add / pull-add = scatter-add of the
+    holders' ghost rows into the owners' rows, `used` masks skip rows; all against plain index operations."""
+    from nvalchemi_toolkit_b200.ops import _native
+    from nvalchemi_toolkit_b200.parallel.symmetric import P2PContext
+
+    assert _native.available()
+    ops = torch.ops.nvalchemi
+    dev = torch.device("cuda", 0)
+    n_own, n_ghost, world = 200, 96, 3
+    cap = n_own + n_ghost
+    p2p = P2PContext.single_process(4 * cap * width * 2 + (1 << 16), dev, world)
+    buf, ptrs = p2p.arena.alloc((cap, width))
+    g = torch.Generator(device="cpu").manual_seed(width)
+    arenas = []
+    for r in range(world):  # fill every "rank's" copy of the buffer through its base pointer
+        view = p2p.arena._bufs[r][p2p.arena.offset_of(buf): p2p.arena.offset_of(buf) + 4 * cap * width].view(torch.float32).reshape(cap, width)
+        view.copy_(torch.randn(cap, width, generator=g))
+        arenas.append(view)
+    home_rank = torch.randint(1, world, (n_ghost,), generator=g).to(torch.int32).to(dev)
+    home_row = torch.randperm(n_own, generator=g)[:n_ghost].to(torch.int32).to(dev)
+    shift = torch.randn(n_ghost, width, generator=g).to(dev) if width == 3 else None
+    used = (torch.rand(n_ghost, generator=g) < 0.7).to(torch.uint8).to(dev)
+    before = [a.clone() for a in arenas]
+    # pull: ghost row k of rank 0 <- row home_row[k] of rank home_rank[k]
+    ops.halo_pull_rows(buf, n_own, home_rank, home_row, shift, ptrs, None)
+    want = torch.stack([before[int(r)][int(j)] for r, j in zip(home_rank.tolist(), home_row.tolist())])
+    want = want + shift if shift is not None else want
+    assert torch.equal(arenas[0][n_own:], want) and torch.equal(arenas[0][:n_own], before[0][:n_own])
+    arenas[0][n_own:].copy_(before[0][n_own:])
+    ops.halo_pull_rows(buf, n_own, home_rank, home_row, shift, ptrs, used)
+    m = used.bool()
+    assert torch.equal(arenas[0][n_own:][m], want[m]) and torch.equal(arenas[0][n_own:][~m], before[0][n_own:][~m])
+    # push-add: ghost rows of rank 0 are added into their owners' rows
+    for a, b in zip(arenas, before):
+        a.copy_(b)
+    ops.halo_push_add_rows(buf, n_own, home_rank, home_row, ptrs, None)
+    for r in range(1, world):
+        sel = home_rank == r
+        ref = before[r].clone().index_add_(0, home_row[sel].long(), before[0][n_own:][sel])
+        assert torch.allclose(arenas[r], ref, atol=1e-6)
+    # pull-add (the owner's view): rank 0 owns rows dst_row[k], whose copies sit on rank peer[k] at row peer_row[k]
+    for a, b in zip(arenas, before):
+        a.copy_(b)
+    n_send = 80
+    dst_row = torch.randint(0, n_own, (n_send,), generator=g).to(torch.int32).to(dev)
+    peer = torch.randint(1, world, (n_send,), generator=g).to(torch.int32).to(dev)
+    peer_row = (n_own + torch.randperm(n_ghost, generator=g)[:n_send]).to(torch.int32).to(dev)
+    ops.halo_pull_add_rows(buf, dst_row, peer, peer_row, ptrs, None, None)
+    copies = torch.stack([before[int(r)][int(j)] for r, j in zip(peer.tolist(), peer_row.tolist())])
+    ref = before[0].clone().index_add_(0, dst_row.long(), copies)
+    assert torch.allclose(arenas[0], ref, atol=1e-5)
+    assert p2p.status() == 0
