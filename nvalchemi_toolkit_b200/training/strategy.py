@@ -255,8 +255,7 @@ class TrainingStrategy(HookRegistryMixin):
         loader = loader if loader is not None else (cfg.data if cfg is not None else None)
         if loader is None:
             return None
-        model = self.inference_model or (self.models["main"] if self.single_model_input else self.models)
-        with ValidationLoop(self, model, cfg) as loop:
+        with ValidationLoop.from_training_strategy(self, cfg) as loop:
             summary = loop.run(loader)
         self.last_validation = summary
         step_schedulers(self._lr_schedulers, self._opt_cfgs, "validation", summary)

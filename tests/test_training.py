@@ -276,3 +276,30 @@ def test_asynchronous_checkpoint_holds_the_snapshot_not_the_live_weights(tmp_pat
     bad = ck.save_checkpoint(tmp_path, 8, {"main": torch.nn.Embedding(5, 3)}, [], [], [], {}, asynchronous=True)
     with pytest.raises(ValueError, match="spec.json disagrees"):
         bad.wait()
+
+
+def test_validation_loop_restores_gradients_and_supports_metrics_and_own_loss():
+    from nvalchemi_toolkit_b200.training.validation import ValidationConfig, ValidationLoop, ensure_reiterable
+
+    data = _dataset(8)
+    st = _strategy(num_steps=1)
+    st.train_batch(Batch.from_data_list(data[:4]))
+    model = st.models["main"]
+    grads = {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
+    assert grads and model.training
+    seen = []
+    cfg = ValidationConfig(data=_loader(data[4:]), loss_fn=EnergyMSELoss(weight=1.0) + ForceMSELoss(weight=0.0),
+                           metrics={"energy_mae": lambda pred, b: (pred["energy"].reshape(-1) - b.energy.reshape(-1)).abs().mean()},
+                           batch_callback=lambda b, p, l: seen.append(b.num_graphs))
+    out = ValidationLoop.from_training_strategy(st, cfg).execute()
+    assert out["num_graphs"] == 4 and out["num_batches"] == len(seen) and "metric/energy_mae" in out and out["step"] == 1
+    assert abs(out["total_loss"] - out[[k for k in out if k.startswith("EnergyMSE")][0]]) < 1e-9  # forces weigh nothing here
+    assert model.training
+    for n, p in model.named_parameters():
+        if n in grads:
+            assert torch.equal(p.grad, grads[n])
+    with pytest.raises(TypeError, match="re-iterable"):
+        ValidationConfig(data=iter(_loader(data)))
+    with pytest.raises(ValueError, match="every_n_steps"):
+        ValidationConfig(every_n_steps=0)
+    assert ensure_reiterable([1, 2]) == [1, 2]
