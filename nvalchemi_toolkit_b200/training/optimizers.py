@@ -2,12 +2,39 @@
 """Declarative optimiser / scheduler configuration (reference ``nvalchemi/training/optimizers.py:111-447``)."""
 from __future__ import annotations
 
-from typing import Any
+import inspect
+import re
+from typing import Any, Callable, Mapping
 
 import torch
-from pydantic import BaseModel, ConfigDict, Field
+from pydantic import BaseModel, ConfigDict, Field, model_validator
 
 from nvalchemi_toolkit_b200._serialization import import_from_path, type_to_path
+
+
+def check_kwargs(cls: Any, kwargs: Mapping[str, Any], label: str) -> None:
+    """Reject keyword arguments the constructor does not accept at configuration time (reference
+    ``training/optimizers.py:56-82``): a typo such as ``weight_decy`` should fail when the recipe is read, not after the data
+    pipeline and the model are built.  Constructors that take ``**kwargs`` accept everything."""
+    try:
+        params = inspect.signature(cls.__init__ if isinstance(cls, type) else cls).parameters
+    except (TypeError, ValueError):
+        return
+    if any(p.kind is inspect.Parameter.VAR_KEYWORD for p in params.values()):
+        return
+    unknown = sorted(k for k in kwargs if k not in params)
+    if unknown:
+        accepted = sorted(k for k in params if k not in ("self", "params", "optimizer"))
+        raise ValueError(f"{label} {getattr(cls, '__name__', cls)} does not accept {unknown}; accepted: {accepted}")
+
+
+class ParamGroupSpec(BaseModel):
+    """Parameters whose qualified name matches ``pattern`` (``re.search``) form a group with their own optimiser options,
+    e.g. ``ParamGroupSpec(pattern=r"bias$|norm", options={"weight_decay": 0.0})`` or a smaller ``lr`` for a pretrained trunk.
+    The first matching spec wins; parameters no spec matches use the config's ``kwargs``."""
+
+    pattern: str
+    options: dict[str, Any] = Field(default_factory=dict)
 
 
 class OptimizerConfig(BaseModel):
@@ -21,9 +48,44 @@ class OptimizerConfig(BaseModel):
     scheduler_kwargs: dict[str, Any] = Field(default_factory=dict)
     scheduler_metric: str | None = None
     scheduler_interval: str = "step"  # "step" | "epoch" | "validation"
+    #: maps the validation summary to the number a metric-driven scheduler steps on (default: ``summary[scheduler_metric]``)
+    scheduler_metric_adapter: Callable[[Mapping[str, Any]], float] | None = None
+    param_groups: list[ParamGroupSpec] = Field(default_factory=list)
+
+    @model_validator(mode="after")
+    def _validate(self) -> "OptimizerConfig":
+        if self.scheduler_interval not in ("step", "epoch", "validation"):
+            raise ValueError(f"scheduler_interval must be 'step', 'epoch' or 'validation', got {self.scheduler_interval!r}")
+        cls = import_from_path(self.cls) if isinstance(self.cls, str) else self.cls
+        check_kwargs(cls, self.kwargs, "optimizer")
+        for g in self.param_groups:
+            re.compile(g.pattern)
+            check_kwargs(cls, g.options, "optimizer (parameter group)")
+        if self.scheduler_cls is not None:
+            scls = import_from_path(self.scheduler_cls) if isinstance(self.scheduler_cls, str) else self.scheduler_cls
+            check_kwargs(scls, self.scheduler_kwargs, "scheduler")
+        return self
+
+    def group_parameters(self, named: list[tuple[str, torch.nn.Parameter]]) -> Any:
+        """``named`` parameters split into optimiser parameter groups according to ``param_groups``."""
+        if not self.param_groups:
+            return [p for _, p in named]
+        buckets: list[list[torch.nn.Parameter]] = [[] for _ in self.param_groups]
+        rest: list[torch.nn.Parameter] = []
+        for name, p in named:
+            for i, g in enumerate(self.param_groups):
+                if re.search(g.pattern, name):
+                    buckets[i].append(p)
+                    break
+            else:
+                rest.append(p)
+        groups = [{"params": b, **g.options} for b, g in zip(buckets, self.param_groups) if b]
+        return ([{"params": rest}] if rest else []) + groups
 
     def build(self, params: Any) -> tuple[torch.optim.Optimizer, Any]:
         cls = import_from_path(self.cls) if isinstance(self.cls, str) else self.cls
+        if params and isinstance(params[0], tuple):  # (name, parameter) pairs: apply the group specs
+            params = self.group_parameters(list(params))
         opt = cls(params, **self.kwargs)
         sched = None
         if self.scheduler_cls is not None:
@@ -36,7 +98,8 @@ class OptimizerConfig(BaseModel):
                 "scheduler_cls": None if self.scheduler_cls is None else (
                     self.scheduler_cls if isinstance(self.scheduler_cls, str) else type_to_path(self.scheduler_cls)),
                 "scheduler_kwargs": dict(self.scheduler_kwargs), "scheduler_metric": self.scheduler_metric,
-                "scheduler_interval": self.scheduler_interval}
+                "scheduler_interval": self.scheduler_interval,
+                "param_groups": [g.model_dump() for g in self.param_groups]}
 
 
 def setup_optimizers(models: dict[str, torch.nn.Module], configs: dict[str, list[OptimizerConfig]],
@@ -50,7 +113,7 @@ def setup_optimizers(models: dict[str, torch.nn.Module], configs: dict[str, list
         if name_filter is not None:
             named = [(n, p) for n, p in named if f"{key}.{n}" in name_filter or n in name_filter]
         for cfg in cfgs if isinstance(cfgs, (list, tuple)) else [cfgs]:
-            o, s = cfg.build([p for _, p in named])
+            o, s = cfg.build([(f"{key}.{n}", p) for n, p in named] if cfg.param_groups else [p for _, p in named])
             opts.append(o)
             scheds.append(s)
             keys.append(key)
@@ -72,7 +135,9 @@ def step_schedulers(scheds: list, configs: list[OptimizerConfig], interval: str,
         if s is None or c.scheduler_interval != interval:
             continue
         if isinstance(s, torch.optim.lr_scheduler.ReduceLROnPlateau):
-            if metrics is not None and c.scheduler_metric in metrics:
+            if metrics is not None and c.scheduler_metric_adapter is not None:
+                s.step(float(c.scheduler_metric_adapter(metrics)))
+            elif metrics is not None and c.scheduler_metric in metrics:
                 s.step(float(metrics[c.scheduler_metric]))
         else:
             s.step()

@@ -303,3 +303,29 @@ def test_validation_loop_restores_gradients_and_supports_metrics_and_own_loss():
     with pytest.raises(ValueError, match="every_n_steps"):
         ValidationConfig(every_n_steps=0)
     assert ensure_reiterable([1, 2]) == [1, 2]
+
+
+def test_optimizer_config_checks_kwargs_and_builds_parameter_groups():
+    from nvalchemi_toolkit_b200.training.optimizers import OptimizerConfig, ParamGroupSpec, setup_optimizers, step_schedulers
+
+    with pytest.raises(ValueError, match="weight_decy"):
+        OptimizerConfig(cls=torch.optim.AdamW, kwargs={"lr": 1e-3, "weight_decy": 0.1})
+    with pytest.raises(ValueError, match="scheduler"):
+        OptimizerConfig(scheduler_cls=torch.optim.lr_scheduler.StepLR, scheduler_kwargs={"step_sz": 3})
+    with pytest.raises(ValueError, match="scheduler_interval"):
+        OptimizerConfig(scheduler_interval="sometimes")
+    net = torch.nn.Sequential(torch.nn.Linear(4, 8), torch.nn.LayerNorm(8), torch.nn.Linear(8, 1))
+    cfg = OptimizerConfig(cls="torch.optim.AdamW", kwargs={"lr": 1e-3, "weight_decay": 0.1},
+                          param_groups=[ParamGroupSpec(pattern=r"bias$|\.1\.", options={"weight_decay": 0.0}),
+                                        ParamGroupSpec(pattern=r"\.2\.weight", options={"lr": 1e-4})],
+                          scheduler_cls=torch.optim.lr_scheduler.ReduceLROnPlateau, scheduler_kwargs={"patience": 0, "factor": 0.5},
+                          scheduler_interval="validation", scheduler_metric_adapter=lambda m: m["a"] + m["b"])
+    opts, scheds, keys = setup_optimizers({"main": net}, {"main": [cfg]})
+    groups = opts[0].param_groups
+    assert keys == ["main"] and len(groups) == 3
+    assert [g["weight_decay"] for g in groups] == [0.1, 0.0, 0.1] and [g["lr"] for g in groups] == [1e-3, 1e-3, 1e-4]
+    assert sum(len(g["params"]) for g in groups) == 6 and len(groups[1]["params"]) == 4  # three biases + the norm weight
+    step_schedulers(scheds, [cfg], "validation", {"a": 1.0, "b": 1.0})
+    step_schedulers(scheds, [cfg], "validation", {"a": 2.0, "b": 1.0})  # worse: the plateau scheduler halves every lr
+    assert [g["lr"] for g in opts[0].param_groups] == [5e-4, 5e-4, 5e-5]
+    assert cfg.to_spec()["param_groups"][0]["options"] == {"weight_decay": 0.0}
