@@ -154,7 +154,14 @@ class DistributedPipeline:
         if self._pending_send is not None:
             self._pending_send.wait()
             self._pending_send = None
+        # comm_mode of the stage: "sync" completes the receive before the step and the send right after posting it (no
+        # overlap, simplest to reason about); "async_recv" overlaps the receive with the step but completes the send at
+        # once; "fully_async" also leaves the send in flight until the start of the next iteration
+        mode = getattr(st, "comm_mode", "fully_async")
         recv = Batch.irecv(st.prior_rank, template, device=dev) if st.prior_rank is not None else None
+        early: Batch | None = None
+        if recv is not None and mode == "sync":
+            early, recv = recv.wait(), None
         graduated: Batch | None = None
         batch = st.active_batch
         if batch is not None and batch.num_graphs > 0:
@@ -174,8 +181,8 @@ class DistributedPipeline:
                 batch = rest
             st.active_batch = batch
             st._primed_for = batch if graduated is None else None
-        if recv is not None:
-            incoming = recv.wait()
+        if recv is not None or early is not None:
+            incoming = early if early is not None else recv.wait()
             if incoming.num_graphs:
                 n_old = st.active_batch.num_graphs if st.active_batch is not None else 0
                 st._recv_to_batch(self._strip(incoming, st))
@@ -187,6 +194,9 @@ class DistributedPipeline:
             out = graduated if graduated is not None else template
             self._pending_send = out.isend(st.next_rank, template=template)
             self._keepalive = out
+            if mode != "fully_async":
+                self._pending_send.wait()
+                self._pending_send = None
         elif graduated is not None and st.sinks:
             st._overflow_to_sinks(graduated)
         elif graduated is not None:

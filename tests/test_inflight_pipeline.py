@@ -105,7 +105,7 @@ def test_inflight_batching_processes_every_system():
     assert sorted(done.num_nodes_list) == sorted([4, 9, 6, 12, 3, 7, 5, 8])
 
 
-def _pipeline_worker(rank, world, port, q):
+def _pipeline_worker(rank, world, port, q, comm_mode="async_recv"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     import torch.distributed as dist
 
@@ -117,8 +117,8 @@ def _pipeline_worker(rank, world, port, q):
         sampler = SizeAwareSampler(ds, max_atoms=24, max_batch_size=3)
         sink = HostMemory()
         relax = FIRE(model, dt=0.1, convergence_hook=ConvergenceHook.from_fmax(1e9), sampler=sampler, device_type="cpu",
-                     max_batch_size=3)
-        md = DemoDynamics(model, n_steps=3, dt=0.05, sinks=[sink], device_type="cpu", max_batch_size=8)
+                     max_batch_size=3, comm_mode=comm_mode)
+        md = DemoDynamics(model, n_steps=3, dt=0.05, sinks=[sink], device_type="cpu", max_batch_size=8, comm_mode=comm_mode)
         pipe = relax | md
         pipe.setup()
         pipe.run(max_iterations=200)
@@ -129,12 +129,15 @@ def _pipeline_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_two_stage_pipeline_gloo():
+@pytest.mark.parametrize("comm_mode", ["sync", "async_recv", "fully_async"])
+def test_two_stage_pipeline_gloo(comm_mode):
+    """Every communication mode (blocking hand-off, overlapped receive, overlapped receive and send) delivers every system."""
     import torch.multiprocessing as mp
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_pipeline_worker, args=(r, 2, 29577, q)) for r in range(2)]
+    port = 29577 + ["sync", "async_recv", "fully_async"].index(comm_mode)
+    procs = [ctx.Process(target=_pipeline_worker, args=(r, 2, port, q, comm_mode)) for r in range(2)]
     for p in procs:
         p.start()
     res = sorted(q.get(timeout=120) for _ in range(2))
