@@ -34,11 +34,11 @@ from nvalchemi_toolkit_b200.distributed.graph_padder import (COOPadder, DenseBat
                                                              cap_agreement_group, resolve_cap)
 from nvalchemi_toolkit_b200.distributed import helpers
 from nvalchemi_toolkit_b200.distributed.pipeline2d import DomainPipeline
-from nvalchemi_toolkit_b200.distributed.static_halo import (StaticHaloRouting, halo_exchange_fixed, halo_forward_static,
+from nvalchemi_toolkit_b200.distributed.static_halo import (StaticHalo, StaticHaloRouting, halo_exchange_fixed, halo_forward_static,
                                                             halo_scatter_correct_static)
 from nvalchemi_toolkit_b200.distributed.peer_halo import PeerFailure, PeerHaloEngine, build_pull_tables, peer_memory_available
 
-__all__ = ["StaticHaloRouting", "halo_exchange_fixed", "halo_forward_static", "halo_scatter_correct_static", "CompilePolicy", "ForceStrategy", "DomainConfig", "HookScope", "StrategyKind", "SpatialPartitioner", "IndexPartitioner", "factor_grid", "MLIPSpec",
+__all__ = ["StaticHalo", "StaticHaloRouting", "halo_exchange_fixed", "halo_forward_static", "halo_scatter_correct_static", "CompilePolicy", "ForceStrategy", "DomainConfig", "HookScope", "StrategyKind", "SpatialPartitioner", "IndexPartitioner", "factor_grid", "MLIPSpec",
            "Consolidation", "get_spec", "register_spec", "HaloExchange", "ShardedBatch", "DistributedModel", "DistributedPipelineModel",
            "consolidate_outputs", "DomainParallel", "DomainPipeline", "DynamicsCoordinator", "ShardTensor", "halo_forward",
            "halo_scatter_correct", "helpers", "all_gather_rows", "all_to_all_rows", "SPEC_LJ_HALO", "SPEC_PAIR_HALO",

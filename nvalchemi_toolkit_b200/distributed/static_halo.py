@@ -149,3 +149,49 @@ def halo_scatter_correct_static(padded: torch.Tensor, routing: StaticHaloRouting
     """After a scatter that left partial sums on ghost rows: fold them into the owners, then refresh every ghost row with
     its owner's completed value, so that owned AND ghost rows hold the full sums.  Differentiable, fixed shapes."""
     return _ScatterCorrectStatic.apply(padded, routing)
+
+
+class StaticHalo:
+    """Capacity management around :class:`StaticHaloRouting`: capacities come from ``graph_padder.resolve_cap`` (grow-only,
+    bucketed, agreed over the ranks of the exchange's group), the routing tensors are re-packed in place after every
+    rebuild of the exchange, and only a capacity overflow allocates new tensors (``generation`` then changes: the signal
+    for a consumer that captured a CUDA graph over the old ones to capture again)."""
+
+    def __init__(self, halo: HaloExchange) -> None:
+        self.halo = halo
+        self.caps: dict[str, int] = {}
+        self.routing: StaticHaloRouting | None = None
+        self.generation = 0
+        self._packed_build = -1
+
+    def sync(self, n_owned: int) -> StaticHaloRouting:
+        """Routing for the exchange's CURRENT plan (call after ``halo.build``; cheap when nothing changed)."""
+        from nvalchemi_toolkit_b200.distributed.graph_padder import cap_agreement_group, resolve_cap
+
+        halo = self.halo
+        if self.routing is not None and self._packed_build == halo.num_builds and int(self.routing.n_owned) == n_owned:
+            return self.routing
+        dev = halo.send_index.device
+        per_peer = max(max(halo.send_splits, default=0), max(halo.recv_splits, default=0))
+        with cap_agreement_group(halo.group, dev):
+            max_send = resolve_cap(self.caps, "max_send", per_peer)
+            n_padded = resolve_cap(self.caps, "n_padded", n_owned + halo.n_ghost)
+        r = self.routing
+        if r is None or r.max_send != max_send or r.n_padded != n_padded:
+            _, world = _world(halo.group)
+            self.routing = StaticHaloRouting.allocate(world, max_send, n_padded, dev, halo.group)
+            self.generation += 1
+        self.routing.update_(halo, n_owned)
+        self._packed_build = halo.num_builds
+        return self.routing
+
+    def pad(self, owned: torch.Tensor) -> torch.Tensor:
+        """``[n_owned, ...] -> [n_padded, ...]`` with zero ghost and unused rows (input of :func:`halo_forward_static`)."""
+        r = self.routing
+        out = owned.new_zeros((r.n_padded,) + tuple(owned.shape[1:]))
+        out[: owned.shape[0]] = owned
+        return out
+
+    def refresh(self, owned: torch.Tensor) -> torch.Tensor:
+        """Owned rows -> padded tensor with current ghost rows (differentiable)."""
+        return halo_forward_static(self.pad(owned), self.routing)

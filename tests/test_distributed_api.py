@@ -817,3 +817,25 @@ def test_wired_autograd_group_is_decomposed_as_one_model():
         assert abs(res[r][1] - float(ref["energy"].reshape(-1)[0])) < 1e-8
         assert torch.allclose(torch.tensor(res[r][0], dtype=torch.float64), ref["forces"], atol=1e-8)
         assert abs(res[r][2] - 8.5) < 1e-9 and 0 < res[r][3] < batch.num_nodes
+
+
+def test_static_halo_capacities_grow_only_and_repack_in_place():
+    from nvalchemi_toolkit_b200.distributed.static_halo import StaticHalo
+
+    sh = ShardedBatch.from_batch(_lj_batch(2), DomainConfig(cutoff=4.0))
+    st = StaticHalo(sh.halo)
+    r1 = st.sync(sh.n_owned)
+    assert st.generation == 1 and r1.max_send >= max(sh.halo.send_splits) and r1.n_padded >= sh.n_owned + sh.n_ghost
+    assert r1.max_send % 16 == 0 and r1.n_padded % 16 == 0
+    x = torch.randn(sh.n_owned, 3, dtype=torch.float64)
+    full = st.refresh(x)
+    assert torch.allclose(full[: sh.n_owned + sh.n_ghost], halo_forward(x, sh.halo))
+    ptr = r1.send_index.data_ptr()
+    sh.halo.build(sh.owned.positions.detach(), sh.global_ids)     # same geometry, new plan generation
+    r2 = st.sync(sh.n_owned)
+    assert r2 is r1 and st.generation == 1 and r2.send_index.data_ptr() == ptr
+    if max(sh.halo.send_splits) > 16:                             # pretend the first plan was tiny: the next sync must grow
+        st.caps["max_send"], st.routing.max_send = 16, 16
+        sh.halo.num_builds += 1
+        r3 = st.sync(sh.n_owned)
+        assert st.generation == 2 and r3.max_send > 16 and r3 is not r1
