@@ -839,3 +839,43 @@ def test_static_halo_capacities_grow_only_and_repack_in_place():
         sh.halo.num_builds += 1
         r3 = st.sync(sh.n_owned)
         assert st.generation == 2 and r3.max_send > 16 and r3 is not r1
+
+
+@pytest.mark.gpu
+def test_static_halo_replays_in_a_cuda_graph_across_rebuilds():
+    """The point of the fixed shapes: a ghost refresh captured ONCE in a CUDA graph keeps working after the exchange was
+    rebuilt for moved atoms, because the routing tensors it reads are re-packed in place."""
+    from nvalchemi_toolkit_b200.distributed.static_halo import StaticHalo
+
+    batch = _lj_batch(3).to("cuda")
+    sh = ShardedBatch.from_batch(batch, DomainConfig(cutoff=5.0, skin=0.5))
+    st = StaticHalo(sh.halo)
+    routing = st.sync(sh.n_owned)
+    x = torch.randn(sh.n_owned, 4, device="cuda", dtype=torch.float64)
+    static_in = st.pad(x)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):  # warm-up outside the capture
+            halo_forward_static_out = st.refresh(x)
+    torch.cuda.current_stream().wait_stream(side)
+    from nvalchemi_toolkit_b200.distributed.static_halo import halo_forward_static
+
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        static_out = halo_forward_static(static_in, routing)
+    graph.replay()
+    torch.cuda.synchronize()
+    n, ng = sh.n_owned, sh.n_ghost
+    assert torch.allclose(static_out[: n + ng], halo_forward(x, sh.halo))
+    # move atoms across the periodic boundary, rebuild the plan, re-pack in place, replay the SAME graph
+    sh.owned.positions.add_(1.7)
+    sh.halo.build(sh.owned.positions.detach(), sh.global_ids)
+    assert st.sync(sh.n_owned) is routing
+    x2 = torch.randn_like(x)
+    static_in.zero_()
+    static_in[:n].copy_(x2)
+    graph.replay()
+    torch.cuda.synchronize()
+    ng2 = sh.halo.n_ghost
+    assert torch.allclose(static_out[: n + ng2], halo_forward(x2, sh.halo)) and bool((static_out[n + ng2:] == 0).all())
