@@ -347,5 +347,109 @@ def spec_show(job: str) -> None:
     click.echo(json.dumps(TrainingJobSpec.from_file(job).model_dump(mode="json"), indent=2))
 
 
+# ---- dry-run review of a job file ---------------------------------------------------------------------------------
+def job_warnings(job: TrainingJobSpec) -> list[tuple[str, str]]:
+    """``(severity, message)`` findings a reviewer would raise before spending GPU hours on the job (reference
+    ``training/cli.py`` ``_training_warnings``): paths that do not exist, no validation data, no checkpoints, a plateau
+    scheduler without the validation it listens to, force training without forces in the active outputs, a fine-tune
+    that trains nothing."""
+    out: list[tuple[str, str]] = []
+    for label, value in (("data.train", job.data.train), ("data.validation", job.data.validation),
+                         ("model.checkpoint", job.model.checkpoint), ("finetune.checkpoint", job.finetune.checkpoint if job.finetune else None)):
+        if value is not None and "://" not in str(value) and not Path(value).exists():
+            out.append(("error", f"{label}: path '{value}' does not exist"))
+    if job.data.validation is None:
+        out.append(("warning", "no validation data: over-fitting will go unnoticed and metric-driven schedulers cannot step"))
+    elif job.validation is None:
+        out.append(("warning", "validation data is given but no validation schedule (validation: {every_n_epochs: 1})"))
+    if job.checkpoint_every_n_steps is None and job.checkpoint_every_n_epochs is None and not any(
+            "Checkpoint" in h.cls for h in job.hooks):
+        out.append(("warning", "no checkpoint cadence and no checkpoint hook: a crash loses the run"))
+    o = job.optimizer
+    if o.scheduler_cls and "ReduceLROnPlateau" in o.scheduler_cls:
+        if o.scheduler_interval != "validation" or job.data.validation is None:
+            out.append(("error", "ReduceLROnPlateau steps on a validation metric: set scheduler_interval: validation and give "
+                                 "validation data"))
+        if not o.scheduler_metric:
+            out.append(("warning", "ReduceLROnPlateau without scheduler_metric: defaulting is ambiguous, name the loss key"))
+    losses = [str(term.get("cls", "")) for term in job.loss]
+    if any("Force" in c for c in losses) and "forces" not in job.active_outputs:
+        out.append(("error", "the loss has a force term but 'forces' is not in active_outputs"))
+    if any("Stress" in c for c in losses) and "stress" not in job.active_outputs:
+        out.append(("error", "the loss has a stress term but 'stress' is not in active_outputs"))
+    if job.finetune is not None and not job.finetune.trainable:
+        out.append(("info", "fine-tune without a trainable filter: every parameter is trained (full fine-tune)"))
+    if job.num_steps is not None and job.checkpoint_every_n_steps and job.checkpoint_every_n_steps > job.num_steps:
+        out.append(("warning", "checkpoint_every_n_steps exceeds num_steps: only the final checkpoint will be written"))
+    if float(o.kwargs.get("lr", 1e-3)) > 0.1:
+        out.append(("warning", f"learning rate {o.kwargs.get('lr')} is unusually large for Adam-family optimisers"))
+    return out
+
+
+def lr_preview(job: TrainingJobSpec, total_steps: int, samples: int = 12) -> list[tuple[int, float]]:
+    """Learning rate at ``samples`` points of the run, by stepping the configured scheduler on a dummy parameter (schedulers
+    driven by validation metrics stay at the base rate)."""
+    import torch
+
+    o = job.optimizer
+    p = torch.nn.Parameter(torch.zeros(1))
+    opt = import_from_path(o.cls)([p], **o.kwargs)
+    sched = None
+    if o.scheduler_cls and "ReduceLROnPlateau" not in o.scheduler_cls and o.scheduler_interval == "step":
+        sched = import_from_path(o.scheduler_cls)(opt, **o.scheduler_kwargs)
+    marks = sorted({int(round(i * max(total_steps - 1, 0) / max(samples - 1, 1))) for i in range(samples)})
+    out, step = [], 0
+    for target in marks:
+        while step < target:
+            opt.step()
+            if sched is not None:
+                sched.step()
+            step += 1
+        out.append((target, float(opt.param_groups[0]["lr"])))
+    return out
+
+
+def render_report(job: TrainingJobSpec, steps_per_epoch: int | None = None) -> str:
+    """Plain-text review of a job: what will run, in which hook order, with which learning-rate curve, and the warnings."""
+    lines = ["== job ==", f"model      {job.model.cls}" + (f"  <- {job.model.checkpoint}" if job.model.checkpoint else ""),
+             f"data       train={job.data.train}  validation={job.data.validation}  batch_size={job.data.batch_size}",
+             f"budget     " + (f"{job.num_epochs} epochs" if job.num_epochs is not None else f"{job.num_steps} steps"),
+             f"loss       " + " + ".join(f"{t.get('weight', 1.0)} x {t.get('cls')}" for t in job.loss),
+             f"optimizer  {job.optimizer.cls} {job.optimizer.kwargs}" + (
+                 f"  scheduler {job.optimizer.scheduler_cls} {job.optimizer.scheduler_kwargs} every {job.optimizer.scheduler_interval}"
+                 if job.optimizer.scheduler_cls else ""),
+             f"outputs    {job.output_dir}  checkpoints every " + (
+                 f"{job.checkpoint_every_n_steps} steps" if job.checkpoint_every_n_steps else f"{job.checkpoint_every_n_epochs} epochs")]
+    if job.hooks:
+        lines.append("== hooks (registration order) ==")
+        for h in job.hooks:
+            klass = import_from_path(h.cls)
+            stage = getattr(klass, "stage", None)
+            lines.append(f"  {h.cls.split('.')[-1]:<28} stage={getattr(stage, 'name', 'several')}  priority={getattr(klass, 'priority', 0)}")
+    total = job.num_steps if job.num_steps is not None else (job.num_epochs or 1) * (steps_per_epoch or 100)
+    lines.append(f"== learning rate over {total} optimiser steps" + ("" if job.num_steps is not None or steps_per_epoch else
+                                                                       " (assuming 100 steps per epoch)") + " ==")
+    curve = lr_preview(job, total)
+    top = max(v for _, v in curve) or 1.0
+    for step, lr in curve:
+        lines.append(f"  step {step:>8}  lr {lr:.3e}  " + "#" * max(1, int(round(30 * lr / top))))
+    found = job_warnings(job)
+    lines.append("== findings ==")
+    lines += [f"  [{sev}] {msg}" for sev, msg in found] or ["  none"]
+    return "\n".join(lines)
+
+
+@spec.command("report")
+@click.argument("job", type=click.Path(exists=True))
+@click.option("--steps-per-epoch", type=int, default=None, help="for the learning-rate preview of epoch-budgeted jobs")
+@click.option("--strict", is_flag=True, help="exit with status 1 when a finding has severity 'error'")
+def spec_report(job: str, steps_per_epoch: int | None, strict: bool) -> None:
+    """Dry-run review of a job file: summary, hook order, learning-rate preview, findings."""
+    parsed = TrainingJobSpec.from_file(job)
+    click.echo(render_report(parsed, steps_per_epoch))
+    if strict and any(sev == "error" for sev, _ in job_warnings(parsed)):
+        raise click.ClickException("the job file has findings of severity 'error'")
+
+
 if __name__ == "__main__":
     sys.exit(main())

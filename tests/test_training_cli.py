@@ -76,3 +76,26 @@ def test_run_resume_and_finetune(tmp_path):
     assert res.exit_code == 0, res.output
     assert json.loads((tmp_path / "ft" / "report.json").read_text())["steps"] == 3
     assert r.invoke(cli.main, ["train", "resume", str(job), "--output-dir", str(tmp_path / "nothing")]).exit_code != 0
+
+
+def test_spec_report_previews_the_schedule_and_lists_findings(tmp_path):
+    path = _job(tmp_path, num_steps=50, hooks=[cli.ComponentSpec(cls="nvalchemi_toolkit_b200.training.hooks.library.GradientClipHook",
+                                                                  kwargs={"max_norm": 1.0})])
+    r = CliRunner()
+    out = r.invoke(cli.main, ["spec", "report", str(path)])
+    assert out.exit_code == 0, out.output
+    text = out.output
+    assert "GradientClipHook" in text and "learning rate over 50 optimiser steps" in text and "none" in text.split("== findings ==")[1]
+    job = cli.TrainingJobSpec.from_file(path)
+    curve = cli.lr_preview(job, 50, samples=3)
+    assert curve[0] == (0, 1e-2) and abs(curve[-1][1] - 1e-2 * 0.9 ** 49) < 1e-12
+    bad = job.model_copy(update={"data": job.data.model_copy(update={"train": str(tmp_path / "missing.zarr"), "validation": None}),
+                                 "active_outputs": ["energy"], "checkpoint_every_n_epochs": None,
+                                 "optimizer": cli.OptimizerSpec(cls="torch.optim.Adam", kwargs={"lr": 0.5},
+                                                                scheduler_cls="torch.optim.lr_scheduler.ReduceLROnPlateau")})
+    found = cli.job_warnings(bad)
+    text = " | ".join(m for _, m in found)
+    assert "does not exist" in text and "no validation data" in text and "no checkpoint cadence" in text
+    assert "ReduceLROnPlateau steps on a validation metric" in text and "force term" in text and "unusually large" in text
+    bad.to_file(tmp_path / "bad.yaml")
+    assert r.invoke(cli.main, ["spec", "report", str(tmp_path / "bad.yaml"), "--strict"]).exit_code != 0
