@@ -13,6 +13,8 @@ kernels are ``k_B T`` in eV.
 """
 from __future__ import annotations
 
+from typing import Any
+
 import torch
 
 from nvalchemi_toolkit_b200.dynamics._units import KB_EV
@@ -446,3 +448,108 @@ def affine_rows_(x, A, batch_idx, y=None, C=None, forces=None, masses=None, kick
     if k is not None and not kick_first:
         out = out + k
     x.copy_(out)
+
+
+# ---- isobaric ensembles: functional pieces of the MTK integrators ----------------------------------------------------
+# Reference op family ``dynamics/_ops/npt_nph.py:59-911``.  State is explicit (tensors in, tensors updated in place), so the
+# same functions serve the NPT / NPH classes, user-written integrators and tests.  ``v_g`` is the 3 x 3 strain rate of the
+# cell per system, ``coupling`` one of "isotropic" / "anisotropic" / "triclinic".
+def compute_pressure_tensor(kinetic_tensors: torch.Tensor, stress: torch.Tensor, volumes: torch.Tensor) -> torch.Tensor:
+    """``P = K / V - sigma`` per system (``K = sum m v (x) v``; ``sigma`` tensile positive, eV / A^3)."""
+    return kinetic_tensors / volumes.reshape(-1, 1, 1) - stress.reshape(-1, 3, 3)
+
+
+def compute_scalar_pressure(pressure_tensors: torch.Tensor) -> torch.Tensor:
+    """``tr(P) / 3`` per system."""
+    return torch.diagonal(pressure_tensors.reshape(-1, 3, 3), dim1=1, dim2=2).sum(-1) / 3.0
+
+
+def compute_barostat_mass(ndof: torch.Tensor, kT: torch.Tensor, barostat_time: torch.Tensor) -> torch.Tensor:
+    """``W = (N_f + 3) kT tau_b^2`` (Martyna-Tobias-Klein)."""
+    return (ndof + 3.0) * kT * barostat_time ** 2
+
+
+def project_cell_force(g: torch.Tensor, coupling: str) -> torch.Tensor:
+    """Restrict a 3 x 3 generalised force to the degrees of freedom of the coupling mode (identity multiple, diagonal,
+    symmetric)."""
+    if coupling == "triclinic":
+        return 0.5 * (g + g.transpose(-1, -2))
+    d = torch.diagonal(g, dim1=1, dim2=2)
+    if coupling == "isotropic":
+        d = d.mean(-1, keepdim=True).expand(-1, 3)
+    elif coupling != "anisotropic":
+        raise ValueError("coupling must be 'isotropic', 'anisotropic' or 'triclinic'")
+    return torch.diag_embed(d)
+
+
+def npt_barostat_half_step(v_g: torch.Tensor, pressure_tensors: torch.Tensor, target_pressure: torch.Tensor, volumes: torch.Tensor,
+                           ke2: torch.Tensor, ndof: torch.Tensor, barostat_mass: torch.Tensor, dt: torch.Tensor,
+                           coupling: str = "isotropic") -> torch.Tensor:
+    """``v_g += dt/2 [V (P - p_ext 1) + (2 KE / N_f) 1] / W``, projected on the coupling mode; in place, returns ``v_g``."""
+    eye = torch.eye(3, dtype=v_g.dtype, device=v_g.device)
+    g = volumes.reshape(-1, 1, 1) * (pressure_tensors - target_pressure.reshape(-1, 1, 1) * eye) + (ke2 / ndof).reshape(-1, 1, 1) * eye
+    return v_g.add_(0.5 * dt.reshape(-1, 1, 1) * project_cell_force(g, coupling) / barostat_mass.reshape(-1, 1, 1))
+
+
+nph_barostat_half_step = npt_barostat_half_step
+
+
+def npt_cell_damping(v_g: torch.Tensor, ndof: torch.Tensor, dt: torch.Tensor) -> torch.Tensor:
+    """``exp(-dt/2 (v_g + tr(v_g) / N_f 1))`` per system: what the cell motion does to the particle velocities."""
+    tr = torch.diagonal(v_g, dim1=1, dim2=2).sum(-1) / ndof
+    eye = torch.eye(3, dtype=v_g.dtype, device=v_g.device)
+    return torch.linalg.matrix_exp(-0.5 * dt.reshape(-1, 1, 1) * (v_g + tr.reshape(-1, 1, 1) * eye))
+
+
+def npt_velocity_half_step(velocities: torch.Tensor, forces: torch.Tensor, masses: torch.Tensor, v_g: torch.Tensor,
+                           ndof: torch.Tensor, dt: torch.Tensor, batch_idx: torch.Tensor, kick_first: bool = False) -> None:
+    """Damping by the cell motion and the half kick ``v += dt/2 F/m`` in one per-atom kernel (``kick_first`` mirrors the
+    order for the opening half of a step)."""
+    affine_rows_(velocities, npt_cell_damping(v_g, ndof, dt), batch_idx, forces=forces, masses=masses, kick=0.5 * dt,
+                 kick_first=kick_first)
+
+
+nph_velocity_half_step = npt_velocity_half_step
+
+
+def npt_position_update(positions: torch.Tensor, velocities: torch.Tensor, v_g: torch.Tensor, dt: torch.Tensor,
+                        batch_idx: torch.Tensor) -> torch.Tensor:
+    """``r <- r exp(dt v_g) + dt v exp(dt v_g / 2)`` (one per-atom kernel); returns ``exp(dt v_g)`` for the cell update."""
+    d = dt.reshape(-1, 1, 1)
+    grow = torch.linalg.matrix_exp(d * v_g)
+    affine_rows_(positions, grow, batch_idx, y=velocities, C=d * torch.linalg.matrix_exp(0.5 * d * v_g))
+    return grow
+
+
+def npt_cell_update(cell: torch.Tensor, grow: torch.Tensor) -> torch.Tensor:
+    """Lattice vectors (rows) follow the same map as the positions: ``h <- h exp(dt v_g)``; in place."""
+    c = cell.reshape(-1, 3, 3)
+    c.copy_(c @ grow)
+    return cell
+
+
+def npt_thermostat_half_step(velocities: torch.Tensor, masses: torch.Tensor, batch_idx: torch.Tensor, v_g: torch.Tensor,
+                             state: dict, ndof: torch.Tensor, barostat_mass: torch.Tensor, coupling: str, chain_length: int,
+                             ke_reduce: Any = None) -> None:
+    """Half step of the two Nose-Hoover chains: particles (``eta`` / ``eta_dot``) and barostat (``xi`` / ``xi_dot``).
+    ``state`` holds ``kT, tau_t, tau_b, dt`` and the chain variables; velocities and ``v_g`` are scaled in place."""
+    m = ndof.shape[0]
+    ke2 = 2.0 * compute_kinetic_energy(velocities, masses, batch_idx, m)
+    if ke_reduce is not None:
+        ke2 = ke_reduce(ke2)
+    Q = nhc_compute_masses(ndof, state["kT"], state["tau_t"], chain_length)
+    velocity_rescale(velocities, nhc_chain_scalar(ke2, state["eta"], state["eta_dot"], Q, state["kT"], ndof, state["dt"]), batch_idx)
+    n_b = torch.full_like(ndof, {"isotropic": 1.0, "anisotropic": 3.0, "triclinic": 6.0}[coupling])
+    kb2 = barostat_mass * (v_g ** 2).sum((-1, -2)) * (1.0 / 3.0 if coupling == "isotropic" else 1.0)
+    Qb = nhc_compute_masses(n_b, state["kT"], state["tau_b"], chain_length)
+    v_g.mul_(nhc_chain_scalar(kb2, state["xi"], state["xi_dot"], Qb, state["kT"], n_b, state["dt"]).reshape(-1, 1, 1))
+
+
+def stress_to_cell_force(cell: torch.Tensor, stress: torch.Tensor, factor: torch.Tensor | float = 1.0) -> torch.Tensor:
+    """Generalised force on the lattice vectors for variable-cell relaxation: ``dE/d(strain) = V sigma`` (sigma tensile
+    positive), so the force on the cell rows is ``-V h sigma / factor`` (``factor`` balances cell against atomic degrees of
+    freedom, typically the atom count)."""
+    c, s = cell.reshape(-1, 3, 3), stress.reshape(-1, 3, 3)
+    vol = torch.linalg.det(c).abs()
+    f = factor if isinstance(factor, torch.Tensor) else torch.full_like(vol, float(factor))
+    return -(vol[:, None, None] * torch.matmul(c, s)) / f[:, None, None]

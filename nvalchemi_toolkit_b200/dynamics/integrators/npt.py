@@ -26,9 +26,7 @@ def compute_kinetic_tensor(velocities: torch.Tensor, masses: torch.Tensor, batch
     return _ops.compute_kinetic_tensor(velocities, masses, batch_idx, m)
 
 
-def compute_pressure_tensor(kinetic_tensor: torch.Tensor, stress: torch.Tensor, volume: torch.Tensor) -> torch.Tensor:
-    """``P = K / V - sigma`` (``sigma`` tensile positive)."""
-    return kinetic_tensor / volume[:, None, None] - stress
+compute_pressure_tensor = _ops.compute_pressure_tensor
 
 
 class NPT(BaseDynamics):
@@ -73,40 +71,22 @@ class NPT(BaseDynamics):
 
     def _barostat_mass(self, batch: Batch) -> torch.Tensor:
         s = self._state
-        return (self._ndof(batch) + 3.0) * s["kT"] * s["tau_b"] ** 2
+        return _ops.compute_barostat_mass(self._ndof(batch), s["kT"], s["tau_b"])
 
     def _project(self, g: torch.Tensor) -> torch.Tensor:
         """Restrict a 3 x 3 generalised force to the degrees of freedom of the coupling mode."""
-        if self.pressure_coupling == "triclinic":
-            return 0.5 * (g + g.transpose(-1, -2))
-        d = torch.diagonal(g, dim1=1, dim2=2)
-        if self.pressure_coupling == "isotropic":
-            d = d.mean(-1, keepdim=True).expand(-1, 3)
-        return torch.diag_embed(d)
+        return _ops.project_cell_force(g, self.pressure_coupling)
 
     def _thermostat_half(self, batch: Batch) -> None:
         if not self._thermostat:
             return
-        s, m = self._state, batch.num_graphs
-        ndof = self._ndof(batch)
-        ke2 = 2.0 * _ops.compute_kinetic_energy(batch.velocities, batch.atomic_masses, batch.batch_idx, m)
-        if self.ke_reduce is not None:
-            ke2 = self.ke_reduce(ke2)
-        Q = nhc_compute_masses(ndof, s["kT"], s["tau_t"], self.chain_length)
-        scale = nhc_chain_update(ke2, s["eta"], s["eta_dot"], Q, s["kT"], ndof, s["dt"])
-        _ops.velocity_rescale(batch.velocities, scale, batch.batch_idx)
-        W = self._barostat_mass(batch)
-        n_b = {"isotropic": 1.0, "anisotropic": 3.0, "triclinic": 6.0}[self.pressure_coupling]
-        nb = torch.full_like(ndof, n_b)
-        kb2 = W * (s["v_g"] ** 2).sum((-1, -2)) * (1.0 / 3.0 if self.pressure_coupling == "isotropic" else 1.0)
-        Qb = nhc_compute_masses(nb, s["kT"], s["tau_b"], self.chain_length)
-        sb = nhc_chain_update(kb2, s["xi"], s["xi_dot"], Qb, s["kT"], nb, s["dt"])
-        s["v_g"].mul_(sb.reshape(-1, 1, 1))
+        _ops.npt_thermostat_half_step(batch.velocities, batch.atomic_masses, batch.batch_idx, self._state["v_g"], self._state,
+                                      self._ndof(batch), self._barostat_mass(batch), self.pressure_coupling,
+                                      self.chain_length, ke_reduce=self.ke_reduce)
 
     def _barostat_half(self, batch: Batch) -> None:
         s, m = self._state, batch.num_graphs
-        cell = batch.cell.reshape(m, 3, 3)
-        vol = torch.linalg.det(cell).abs()
+        vol = torch.linalg.det(batch.cell.reshape(m, 3, 3)).abs()
         K = compute_kinetic_tensor(batch.velocities, batch.atomic_masses, batch.batch_idx, m)
         if self.ke_reduce is not None:
             K = self.ke_reduce(K)
@@ -114,40 +94,30 @@ class NPT(BaseDynamics):
         stress = torch.zeros_like(K) if stress is None else stress.reshape(m, 3, 3)
         P = compute_pressure_tensor(K, stress, vol)
         ke2 = torch.diagonal(K, dim1=1, dim2=2).sum(-1)
-        ndof = self._ndof(batch)
-        W = self._barostat_mass(batch)
-        eye = torch.eye(3, dtype=P.dtype, device=P.device)
-        g = (vol.reshape(-1, 1, 1) * (P - s["p_ext"].reshape(-1, 1, 1) * eye) + (ke2 / ndof).reshape(-1, 1, 1) * eye)
-        s["v_g"].add_(0.5 * s["dt"].reshape(-1, 1, 1) * self._project(g) / W.reshape(-1, 1, 1))
+        _ops.npt_barostat_half_step(s["v_g"], P, s["p_ext"], vol, ke2, self._ndof(batch), self._barostat_mass(batch), s["dt"],
+                                    self.pressure_coupling)
 
     def _damping(self, batch: Batch) -> torch.Tensor:
         """``exp(-dt/2 (v_g + tr(v_g) / N_f))`` per system."""
-        s = self._state
-        tr = torch.diagonal(s["v_g"], dim1=1, dim2=2).sum(-1) / self._ndof(batch)
-        eye = torch.eye(3, dtype=tr.dtype, device=tr.device)
-        return torch.linalg.matrix_exp(-0.5 * s["dt"].reshape(-1, 1, 1) * (s["v_g"] + tr.reshape(-1, 1, 1) * eye))
+        return _ops.npt_cell_damping(self._state["v_g"], self._ndof(batch), self._state["dt"])
 
     def _velocity_half(self, batch: Batch) -> None:
         """Damp by the cell motion, then half kick (one fused per-atom kernel)."""
         s = self._state
-        _ops.affine_rows_(batch.velocities, self._damping(batch), batch.batch_idx, forces=batch.forces,
-                          masses=batch.atomic_masses, kick=0.5 * s["dt"], kick_first=False)
+        _ops.npt_velocity_half_step(batch.velocities, batch.forces, batch.atomic_masses, s["v_g"], self._ndof(batch), s["dt"],
+                                    batch.batch_idx, kick_first=False)
 
     def _velocity_half_reverse(self, batch: Batch) -> None:
         """Half kick, then damp (the mirror image of :meth:`_velocity_half`)."""
         s = self._state
-        _ops.affine_rows_(batch.velocities, self._damping(batch), batch.batch_idx, forces=batch.forces,
-                          masses=batch.atomic_masses, kick=0.5 * s["dt"], kick_first=True)
+        _ops.npt_velocity_half_step(batch.velocities, batch.forces, batch.atomic_masses, s["v_g"], self._ndof(batch), s["dt"],
+                                    batch.batch_idx, kick_first=True)
 
     def _drift(self, batch: Batch) -> None:
         """``r <- r exp(dt v_g) + dt v exp(dt v_g / 2)``; the lattice vectors (cell rows) follow ``exp(dt v_g)``."""
-        s, m = self._state, batch.num_graphs
-        dt = s["dt"].reshape(-1, 1, 1)
-        grow = torch.linalg.matrix_exp(dt * s["v_g"])
-        half = dt * torch.linalg.matrix_exp(0.5 * dt * s["v_g"])
-        _ops.affine_rows_(batch.positions, grow, batch.batch_idx, y=batch.velocities, C=half)
-        cell = batch.cell.reshape(m, 3, 3)
-        cell.copy_(cell @ grow)
+        s = self._state
+        grow = _ops.npt_position_update(batch.positions, batch.velocities, s["v_g"], s["dt"], batch.batch_idx)
+        _ops.npt_cell_update(batch.cell, grow)
 
     # -- step ------------------------------------------------------------------------
     def pre_update(self, batch: Batch) -> None:

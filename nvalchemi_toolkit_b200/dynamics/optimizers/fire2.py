@@ -117,11 +117,9 @@ class _CellFilterMixin:
         m = batch.num_graphs
         cell = batch.cell.reshape(m, 3, 3)
         stress = batch.stress.reshape(m, 3, 3)
-        vol = torch.linalg.det(cell).abs()
         n_at = batch.num_nodes_per_graph.to(cell.dtype)
         factor = n_at if self.cell_factor is None else torch.full_like(n_at, self.cell_factor)
-        # dE/d(strain) = V sigma (sigma tensile positive), so the generalised force on the cell rows is -V cell @ sigma
-        cell_force = -(vol[:, None, None] * torch.matmul(cell, stress)) / factor[:, None, None]
+        cell_force = _ops.stress_to_cell_force(cell, stress, factor)
         frac = torch.einsum("ni,nij->nj", batch.positions, torch.linalg.inv(cell)[batch.batch_idx.long()])
         old_cell = cell.clone()
         step_fn(cell_force)

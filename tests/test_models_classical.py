@@ -216,3 +216,51 @@ def test_fire2_kernel_matches_tensor_expressions(device, monkeypatch):
             assert torch.allclose(a.double(), b.double(), rtol=1e-8, atol=1e-9)
         if seams:
             assert got[5][:4] == ["sum", "sum", "sum", "max"]
+
+
+def test_functional_npt_ops():
+    """The exported pieces of the MTK integrators: pressure tensor, scalar pressure, barostat mass, projection on the coupling
+    mode, barostat half step, position / cell update (volume follows exp(dt tr v_g)), cell force of a hydrostatic stress."""
+    from nvalchemi_toolkit_b200.dynamics import _ops
+
+    torch.manual_seed(0)
+    m = 2
+    K = torch.randn(m, 3, 3, dtype=torch.float64)
+    K = K @ K.transpose(1, 2)
+    sigma = 0.01 * torch.randn(m, 3, 3, dtype=torch.float64)
+    vol = torch.tensor([100.0, 250.0], dtype=torch.float64)
+    P = _ops.compute_pressure_tensor(K, sigma, vol)
+    assert torch.allclose(P, K / vol[:, None, None] - sigma)
+    assert torch.allclose(_ops.compute_scalar_pressure(P), torch.stack([p.trace() / 3 for p in P]))
+    ndof, kT, tau = torch.tensor([30.0, 60.0], dtype=torch.float64), torch.tensor([0.02, 0.03], dtype=torch.float64), torch.tensor([5.0, 7.0], dtype=torch.float64)
+    W = _ops.compute_barostat_mass(ndof, kT, tau)
+    assert torch.allclose(W, (ndof + 3) * kT * tau ** 2)
+    g = torch.randn(m, 3, 3, dtype=torch.float64)
+    iso, ani, tri = (_ops.project_cell_force(g, c) for c in ("isotropic", "anisotropic", "triclinic"))
+    assert torch.allclose(iso, torch.diag_embed(torch.diagonal(g, dim1=1, dim2=2).mean(-1, keepdim=True).expand(-1, 3)))
+    assert torch.allclose(ani, torch.diag_embed(torch.diagonal(g, dim1=1, dim2=2))) and torch.allclose(tri, tri.transpose(1, 2))
+    with pytest.raises(ValueError):
+        _ops.project_cell_force(g, "cubic")
+    v_g = torch.zeros(m, 3, 3, dtype=torch.float64)
+    dt = torch.tensor([0.5, 0.5], dtype=torch.float64)
+    p_ext = torch.tensor([0.0, 0.001], dtype=torch.float64)
+    ke2 = torch.diagonal(K, dim1=1, dim2=2).sum(-1)
+    _ops.npt_barostat_half_step(v_g, P, p_ext, vol, ke2, ndof, W, dt, "triclinic")
+    eye = torch.eye(3, dtype=torch.float64)
+    want = 0.5 * dt[:, None, None] * _ops.project_cell_force(vol[:, None, None] * (P - p_ext[:, None, None] * eye) + (ke2 / ndof)[:, None, None] * eye, "triclinic") / W[:, None, None]
+    assert torch.allclose(v_g, want) and _ops.nph_barostat_half_step is _ops.npt_barostat_half_step
+    n = 7
+    bidx = torch.tensor([0, 0, 0, 1, 1, 1, 1], dtype=torch.int32)
+    pos, vel = torch.randn(n, 3, dtype=torch.float64), torch.randn(n, 3, dtype=torch.float64)
+    cell = torch.stack([torch.eye(3, dtype=torch.float64) * 5, torch.eye(3, dtype=torch.float64) * 6])
+    v_g = 0.01 * torch.randn(m, 3, 3, dtype=torch.float64)
+    p0, c0 = pos.clone(), cell.clone()
+    grow = _ops.npt_position_update(pos, vel, v_g, dt, bidx)
+    _ops.npt_cell_update(cell, grow)
+    b = bidx.long()
+    half = dt[:, None, None] * torch.linalg.matrix_exp(0.5 * dt[:, None, None] * v_g)
+    assert torch.allclose(pos, torch.einsum("ni,nij->nj", p0, grow[b]) + torch.einsum("ni,nij->nj", vel, half[b]))
+    ratio = torch.linalg.det(cell) / torch.linalg.det(c0)
+    assert torch.allclose(ratio, torch.exp(dt * torch.diagonal(v_g, dim1=1, dim2=2).sum(-1)))
+    f = _ops.stress_to_cell_force(c0, -0.002 * eye.expand(m, 3, 3), factor=2.0)   # compressive stress pushes the cell outwards
+    assert torch.allclose(f, 0.002 * torch.linalg.det(c0)[:, None, None] * c0 / 2.0)
