@@ -163,52 +163,128 @@ class MultiDataset:
         return self.datasets[k].get_metadata(j)
 
 
+def counts_from_weights(weights: Sequence[float], total: int) -> list[int]:
+    """Integer sample counts proportional to ``weights`` that sum to ``total`` exactly (largest-remainder rounding), so an
+    epoch draws a deterministic number of samples from every dataset instead of a multinomial one."""
+    w = torch.tensor(list(weights), dtype=torch.float64)
+    if w.numel() == 0 or bool((w < 0).any()) or float(w.sum()) <= 0:
+        raise ValueError("weights must be non-negative with a positive sum")
+    exact = w / w.sum() * total
+    base = exact.floor().long()
+    rest = int(total - int(base.sum()))
+    if rest:
+        order = torch.argsort(exact - base, descending=True, stable=True)[:rest]
+        base[order] += 1
+    return base.tolist()
+
+
 class MultiDatasetSampler:
-    """Draws ``num_samples`` global indices: dataset by weight, then uniformly inside it; shards over ranks."""
+    """Global indices of a :class:`MultiDataset` at per-dataset rates (reference ``data/datapipes/samplers.py:237-420``).
+
+    ``weights`` (default: the dataset lengths, i.e. proportional sampling) fix how many of the ``num_samples`` indices of an
+    epoch come from each dataset (exact counts, not a multinomial draw).  ``replacement=False`` walks a fresh permutation
+    of each dataset and wraps around when a dataset is asked for more samples than it has (every sample is seen before any
+    repeats); ``shuffle=False`` keeps storage order.  Ranks take strided shares of the same epoch order; ``drop_last``
+    trims the order to a multiple of the world size, otherwise it is padded by repeating its head so that every rank
+    draws the same number of samples."""
 
     def __init__(self, multi: MultiDataset, num_samples: int | None = None, seed: int = 0, rank: int = 0,
-                 world_size: int = 1) -> None:
+                 world_size: int = 1, weights: Sequence[float] | None = None, replacement: bool = True, shuffle: bool = True,
+                 drop_last: bool = False) -> None:
         self.multi, self.seed, self.rank, self.world_size, self.epoch = multi, seed, rank, world_size, 0
         self.num_samples = num_samples if num_samples is not None else len(multi)
+        if self.num_samples < 1:
+            raise ValueError(f"num_samples must be >= 1, got {self.num_samples}")
+        self.lengths = [len(d) for d in multi.datasets]
+        self.weights = list(weights) if weights is not None else (
+            list(multi.weights) if any(w != 1.0 for w in multi.weights) else [float(n) for n in self.lengths])
+        if len(self.weights) != len(self.lengths):
+            raise ValueError("one weight per dataset")
+        if any(w > 0 and n == 0 for w, n in zip(self.weights, self.lengths)):
+            raise ValueError("an empty dataset cannot have a positive sampling weight")
+        self.replacement, self.shuffle, self.drop_last = replacement, shuffle, drop_last
 
     def set_epoch(self, epoch: int) -> None:
         self.epoch = epoch
 
+    def _per_rank(self) -> int:
+        n, w = self.num_samples, self.world_size
+        return n // w if self.drop_last else math.ceil(n / w)
+
     def __len__(self) -> int:
-        return math.ceil(self.num_samples / self.world_size)
+        return self._per_rank()
+
+    def epoch_order(self) -> list[int]:
+        """The epoch's global order before sharding (the same on every rank)."""
+        g = torch.Generator().manual_seed(self.seed + self.epoch)
+        counts = counts_from_weights(self.weights, self.num_samples)
+        parts = []
+        for k, (cnt, n) in enumerate(zip(counts, self.lengths)):
+            if cnt == 0:
+                continue
+            if self.replacement and self.shuffle:
+                local = torch.randint(0, n, (cnt,), generator=g)
+            else:
+                reps = -(-cnt // n)
+                chunks = [torch.randperm(n, generator=g) if self.shuffle else torch.arange(n) for _ in range(reps)]
+                local = torch.cat(chunks)[:cnt]
+            parts.append(local + self.multi.offsets[k])
+        order = torch.cat(parts)
+        if self.shuffle:
+            order = order[torch.randperm(order.numel(), generator=g)]
+        return order.tolist()
 
     def __iter__(self) -> Iterator[int]:
-        g = torch.Generator().manual_seed(self.seed + self.epoch)
-        w = torch.tensor(self.multi.weights, dtype=torch.float64)
-        which = torch.multinomial(w / w.sum(), self.num_samples, replacement=True, generator=g)
-        sizes = torch.tensor([len(d) for d in self.multi.datasets])
-        inner = (torch.rand(self.num_samples, generator=g) * sizes[which]).long()
-        idx = (torch.tensor(self.multi.offsets[:-1])[which] + inner).tolist()
-        return iter(idx[self.rank:: self.world_size])
+        order = self.epoch_order()
+        per, w = self._per_rank(), self.world_size
+        if self.drop_last:
+            order = order[: per * w]
+        elif len(order) < per * w:
+            order = order + order[: per * w - len(order)]
+        return iter(order[self.rank:: w])
 
 
 class MultiDatasetBatchSampler:
-    """Batches of indices from a :class:`MultiDatasetSampler`."""
+    """Batches of indices from a :class:`MultiDatasetSampler`.  ``homogeneous=True`` keeps every batch inside ONE dataset
+    (multi-fidelity training where datasets carry different label sets or loss heads): indices are bucketed per dataset in
+    the sampler's order and a batch is emitted whenever a bucket fills; the partial buckets follow at the end of the epoch
+    unless ``drop_last``."""
 
-    def __init__(self, sampler: MultiDatasetSampler, batch_size: int, drop_last: bool = False) -> None:
-        self.sampler, self.batch_size, self.drop_last = sampler, batch_size, drop_last
+    def __init__(self, sampler: MultiDatasetSampler, batch_size: int, drop_last: bool = False, homogeneous: bool = False) -> None:
+        self.sampler, self.batch_size, self.drop_last, self.homogeneous = sampler, batch_size, drop_last, homogeneous
 
     def set_epoch(self, epoch: int) -> None:
         self.sampler.set_epoch(epoch)
 
     def __iter__(self) -> Iterator[list[int]]:
-        buf: list[int] = []
-        for i in self.sampler:
-            buf.append(i)
-            if len(buf) == self.batch_size:
+        if not self.homogeneous:
+            buf: list[int] = []
+            for i in self.sampler:
+                buf.append(i)
+                if len(buf) == self.batch_size:
+                    yield buf
+                    buf = []
+            if buf and not self.drop_last:
                 yield buf
-                buf = []
-        if buf and not self.drop_last:
-            yield buf
+            return
+        buckets: dict[int, list[int]] = {}
+        for i in self.sampler:
+            k = self.sampler.multi.locate(i)[0]
+            b = buckets.setdefault(k, [])
+            b.append(i)
+            if len(b) == self.batch_size:
+                yield b
+                buckets[k] = []
+        if not self.drop_last:
+            for k in sorted(buckets):
+                if buckets[k]:
+                    yield buckets[k]
 
     def __len__(self) -> int:
         n = len(self.sampler)
-        return n // self.batch_size if self.drop_last else math.ceil(n / self.batch_size)
+        if not self.homogeneous:
+            return n // self.batch_size if self.drop_last else math.ceil(n / self.batch_size)
+        return sum(1 for _ in self)  # depends on how the epoch's indices fall into the buckets
 
 
 class DataLoader:

@@ -242,3 +242,40 @@ def test_decoded_chunk_cache_sees_rewrites(tmp_path):
 
     os.utime(b._chunk_path(0), ns=(time.time_ns(), time.time_ns() + 1_000_000))
     assert a.read(2, 3)[0, 0] == 99.0 and len(calls) == 2
+
+
+def test_multidataset_sampler_counts_epochs_sharding_and_homogeneous_batches():
+    from nvalchemi_toolkit_b200.data.datapipes import counts_from_weights
+
+    assert counts_from_weights([1, 1, 1], 10) == [4, 3, 3] and counts_from_weights([3, 1], 8) == [6, 2]
+    with pytest.raises(ValueError):
+        counts_from_weights([0, 0], 5)
+    a = InMemoryDataset(_data(6))
+    b = InMemoryDataset(_data(3))
+    multi = MultiDataset([a, b])
+    # proportional by length, without replacement: one epoch of len(multi) samples is a permutation of everything
+    s = MultiDatasetSampler(multi, replacement=False, seed=3)
+    assert sorted(s) == list(range(9))
+    first = list(s)
+    s.set_epoch(1)
+    assert list(s) != first and sorted(s) == list(range(9))
+    # explicit rates: exact counts; the small dataset wraps around only after every sample was seen
+    s = MultiDatasetSampler(multi, num_samples=12, weights=[1, 1], replacement=False, seed=0)
+    idx = list(s)
+    from_b = [i for i in idx if i >= 6]
+    assert len(idx) == 12 and len(from_b) == 6 and sorted(from_b) == [6, 6, 7, 7, 8, 8]
+    assert list(MultiDatasetSampler(multi, shuffle=False, replacement=False)) == list(range(9))
+    # ranks draw equally many samples; together they cover the epoch order (padded by its head)
+    shards = [list(MultiDatasetSampler(multi, num_samples=10, seed=5, rank=r, world_size=4)) for r in range(4)]
+    order = MultiDatasetSampler(multi, num_samples=10, seed=5).epoch_order()
+    assert [len(x) for x in shards] == [3, 3, 3, 3]
+    merged = [shards[i % 4][i // 4] for i in range(12)]
+    assert merged[:10] == order and merged[10:] == order[:2]
+    assert [len(list(MultiDatasetSampler(multi, num_samples=10, rank=r, world_size=4, drop_last=True))) for r in range(4)] == [2] * 4
+    # every batch inside one dataset
+    bs = MultiDatasetBatchSampler(MultiDatasetSampler(multi, num_samples=18, weights=[2, 1], seed=2), batch_size=4, homogeneous=True)
+    batches = list(bs)
+    assert sum(len(x) for x in batches) == 18 and len(bs) == len(batches)
+    assert all(len({multi.locate(i)[0] for i in x}) == 1 for x in batches)
+    with pytest.raises(ValueError, match="empty dataset"):
+        MultiDatasetSampler(MultiDataset([a, InMemoryDataset([])]), weights=[1, 1])
