@@ -80,8 +80,15 @@ class NeighborListHook:
         batch = ctx.batch
         cell, pbc = _nb.cell_and_pbc(batch)
         key = (batch.num_nodes, batch.num_graphs, batch.device, batch.positions.dtype)
-        fresh = self._bufs is None or key != self._shape_key or \
-            (self._bufs is not None and not torch.equal(self._batch_ptr, batch.batch_ptr))
+        fresh = self._bufs is None or key != self._shape_key
+        if not fresh:
+            # same CSR pointer OBJECT, not written since (tensor version counter): the segmentation is unchanged and no
+            # device comparison (= host synchronisation) is needed; only a different or modified tensor is compared
+            ptr = batch.batch_ptr
+            seen = getattr(self, "_batch_ptr_seen", None)
+            if seen is None or seen[0] is not ptr or seen[1] != ptr._version:
+                fresh = not torch.equal(self._batch_ptr, ptr)
+                self._batch_ptr_seen = (ptr, ptr._version)
         if fresh:
             k = self._max_neighbors
             if k is None:
@@ -90,6 +97,7 @@ class NeighborListHook:
                     k = min(k, (batch.max_num_nodes + 15) // 16 * 16)
             self._shape_key = key
             self._batch_ptr = batch.batch_ptr.clone()
+            self._batch_ptr_seen = (batch.batch_ptr, batch.batch_ptr._version)
             self._alloc(batch, k)
             self._build(batch, cell, pbc, None)
             if self.skin > 0.0:
