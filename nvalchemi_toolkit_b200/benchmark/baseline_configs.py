@@ -105,12 +105,24 @@ def relax(args: argparse.Namespace) -> dict:
     share = args.systems // world
     data = SupercellStream(share, seed=1, offset=rank * share)
     wrapper = _mace(device, [13, 26, 28, 29]).eval()
-    sampler = SizeAwareSampler(data, max_atoms=args.max_atoms, max_batch_size=args.max_batch)
-    sink = HostMemory(capacity=share)
-    fire = FIRE(wrapper, dt=args.dt, convergence_hook=ConvergenceHook.from_fmax(args.fmax),
-                hooks=wrapper.make_neighbor_hooks(max_neighbors=args.max_neighbors))
-    flow = FusedStage(sub_stages=[(0, fire)], sampler=sampler, sinks=[sink], refill_frequency=args.refill_frequency,
-                      device_type=device.type)
+
+    def workflow(stream: Any, capacity: int) -> tuple[Any, Any]:
+        sampler = SizeAwareSampler(stream, max_atoms=args.max_atoms, max_batch_size=args.max_batch)
+        sink = HostMemory(capacity=capacity)
+        fire = FIRE(wrapper, dt=args.dt, convergence_hook=ConvergenceHook.from_fmax(args.fmax),
+                    hooks=wrapper.make_neighbor_hooks(max_neighbors=args.max_neighbors))
+        return FusedStage(sub_stages=[(0, fire)], sampler=sampler, sinks=[sink], refill_frequency=args.refill_frequency,
+                          device_type=device.type), sink
+
+    # untimed: the stream is materialised in host memory (the timed region measures relaxation, not the synthetic data
+    # generator) and a short relaxation of a separate small stream warms up allocator pools, lazily built weight packs and
+    # first-use library initialisation
+    for i in range(len(data)):
+        data[i]
+    if args.warmup_systems > 0:
+        warm, _ = workflow(SupercellStream(min(args.warmup_systems, share), seed=99), args.warmup_systems)
+        warm.run(n_steps=args.max_steps)
+    flow, sink = workflow(data, share)
     if device.type == "cuda":
         torch.cuda.synchronize()
     if world > 1:
@@ -302,6 +314,7 @@ def main(argv: list[str] | None = None) -> int:
     r.add_argument("--dt", type=float, default=0.1)
     r.add_argument("--refill-frequency", type=int, default=5)
     r.add_argument("--max-steps", type=int, default=None)
+    r.add_argument("--warmup-systems", type=int, default=128, help="systems of the untimed warm-up relaxation (0: none)")
     t = sub.add_parser("train")
     t.add_argument("--structures", type=int, default=1024, help="size of the synthetic training set (whole job)")
     t.add_argument("--batch", type=int, default=8,

@@ -229,13 +229,24 @@ L0_MOMENTS_MAX_SPECIES = 4
 RADIAL_CACHE = os.environ.get("NVA_RADIAL_CACHE", "1") != "0"
 
 
+_free_memory_seen: dict[torch.device, tuple[int, int]] = {}  # device -> (free bytes at the last query, evaluations it stays valid for)
+
+
 def _radial_cache_fits(dev: torch.device, num_edges: int, layers: int) -> bool:
     if not RADIAL_CACHE or dev.type != "cuda":
         return False
+    need = num_edges * 512 * layers
+    hit = _free_memory_seen.get(dev)
+    if hit is not None and hit[1] > 0 and need < 0.02 * hit[0]:
+        # far below the last reading (small batches of an inflight-batching run): the driver query (about a millisecond)
+        # is not repeated for every evaluation
+        _free_memory_seen[dev] = (hit[0], hit[1] - 1)
+        return True
     free, _total = torch.cuda.mem_get_info(dev)
     free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
     free += sum(b.numel() * 4 for b in _h3_pool.values() if b.device == dev)  # storage already set aside for this
-    return num_edges * 512 * layers < 0.3 * free
+    _free_memory_seen[dev] = (free, 256)
+    return need < 0.3 * free
 
 
 def _l0_weights(ip: Any, w_last: torch.Tensor, table: torch.Tensor, c: int, avg: float) -> list[torch.Tensor]:
@@ -316,24 +327,25 @@ def _skip(ip: Any, h: torch.Tensor, species: torch.Tensor, nz: int, transpose: b
             gemm.grouped(_rows2d(h), packed, out.view(out.shape[0], -1), c, groups, alpha=1.0 / math.sqrt(c * nz),
                          accumulate=accumulate_into is not None)
         return out
-    out = h.new_zeros(h.shape[0], n_dst, c)
+    # several species: one grouped launch per species over ALL rows, selected per row by a mask (no index lists, no host
+    # synchronisation; the extra arithmetic is nz small K = C products per row)
+    out = accumulate_into if accumulate_into is not None else h.new_zeros(h.shape[0], n_dst, c)
+    tmp = h.new_empty(h.shape[0], n_dst, c)
+    full = len(shared) == len(dst_ls)
     for z in range(nz):
-        rows = torch.nonzero(species == z).squeeze(1)
-        if rows.numel() == 0:
-            continue
-        hz = h[rows]
-        oz = h.new_zeros(rows.numel(), n_dst, c)
-        for i, l in shared:
+        packed, rows = _packed(ip, f"skip{z}_t" if transpose else f"skip{z}", [ip.skip],
+                               lambda z=z: [ip.skip[i, z].t() if transpose else ip.skip[i, z] for i, _ in shared])
+        groups = []
+        for b, (i, l) in enumerate(shared):
             so = sum(2 * k + 1 for k in src_ls[: src_ls.index(l)])
             do = sum(2 * k + 1 for k in dst_ls[: dst_ls.index(l)])
-            w = ip.skip[i, z] / math.sqrt(c * nz)
-            w = w.t() if transpose else w
-            for m in range(2 * l + 1):
-                gemm.matmul(hz[:, so + m], w, out=oz[:, do + m])
-        out[rows] = oz
-    if accumulate_into is not None:
-        accumulate_into += out
-        return accumulate_into
+            groups += [((so + m) * c, c, rows[b], (do + m) * c) for m in range(2 * l + 1)]
+        if not groups:
+            break
+        if not full:
+            tmp.zero_()
+        gemm.grouped(_rows2d(h), packed, tmp.view(tmp.shape[0], -1), c, groups, alpha=1.0 / math.sqrt(c * nz))
+        out.addcmul_(tmp, (species == z).to(h.dtype)[:, None, None])
     return out
 
 

@@ -37,9 +37,13 @@ def cell_and_pbc(batch: Batch) -> tuple[torch.Tensor, torch.Tensor]:
         pbc = torch.zeros(b, 3, dtype=torch.bool, device=dev)
     cell = cell.reshape(b, 3, 3)
     # non-periodic systems may carry a zero cell: use identity so fractional coordinates are defined
-    degenerate = torch.linalg.det(cell.double()).abs() < 1e-12
-    if bool(degenerate.any()):
-        cell = torch.where(degenerate[:, None, None], torch.eye(3, dtype=dtype, device=dev), cell)
+    # (explicit 3 x 3 determinant and an unconditional select: no library call, no host synchronisation per step)
+    c = cell.double()
+    det = (c[:, 0, 0] * (c[:, 1, 1] * c[:, 2, 2] - c[:, 1, 2] * c[:, 2, 1])
+           - c[:, 0, 1] * (c[:, 1, 0] * c[:, 2, 2] - c[:, 1, 2] * c[:, 2, 0])
+           + c[:, 0, 2] * (c[:, 1, 0] * c[:, 2, 1] - c[:, 1, 1] * c[:, 2, 0]))
+    degenerate = det.abs() < 1e-12
+    cell = torch.where(degenerate[:, None, None], torch.eye(3, dtype=cell.dtype, device=dev), cell)
     return cell.contiguous(), pbc.reshape(b, 3).to(torch.bool).contiguous()
 
 
