@@ -10,7 +10,7 @@ import torch
 from nvalchemi_toolkit_b200.benchmark import build
 from nvalchemi_toolkit_b200.dynamics import NVTLangevin, _ops
 from nvalchemi_toolkit_b200.models.dftd3 import DFTD3ModelWrapper, DFTD3Parameters
-from nvalchemi_toolkit_b200.models.ewald import PMEModelWrapper
+from nvalchemi_toolkit_b200.models.pme import PMEModelWrapper
 from nvalchemi_toolkit_b200.models.mace import MACEWrapper
 from nvalchemi_toolkit_b200.models.pipeline import PipelineGroup, PipelineModelWrapper
 

@@ -5,7 +5,8 @@ from types import SimpleNamespace
 
 from nvalchemi_toolkit_b200.benchmark import build
 from nvalchemi_toolkit_b200.models._electrostatics import COULOMB_EV_A
-from nvalchemi_toolkit_b200.models.ewald import EwaldModelWrapper, PMEModelWrapper
+from nvalchemi_toolkit_b200.models.ewald import EwaldModelWrapper
+from nvalchemi_toolkit_b200.models.pme import PMEModelWrapper
 import torch
 
 exact = -1.7475645946 * COULOMB_EV_A / (5.64 / 2)

@@ -233,7 +233,7 @@ class WaterStream:
 def _water_model(device: torch.device, channels: int) -> Any:
     """MACE (2 layers, ``channels`` x (0e + 1o), lmax 3, correlation 3, 5 A) + DFT-D3(BJ) + PME (alpha 0.3 / A, 1 A mesh)."""
     from nvalchemi_toolkit_b200.models.dftd3 import DFTD3ModelWrapper, DFTD3Parameters
-    from nvalchemi_toolkit_b200.models.ewald import PMEModelWrapper
+    from nvalchemi_toolkit_b200.models.pme import PMEModelWrapper
     from nvalchemi_toolkit_b200.models.mace import MACE, MACEConfig, MACEWrapper
     from nvalchemi_toolkit_b200.models.pipeline import PipelineGroup, PipelineModelWrapper
 

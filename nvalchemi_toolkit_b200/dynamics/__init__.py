@@ -19,7 +19,7 @@ def __getattr__(name: str):
             "DataSink": "nvalchemi_toolkit_b200.dynamics.sinks", "GPUBuffer": "nvalchemi_toolkit_b200.dynamics.sinks",
             "HostMemory": "nvalchemi_toolkit_b200.dynamics.sinks", "ZarrData": "nvalchemi_toolkit_b200.dynamics.sinks",
             "NVTNoseHoover": "nvalchemi_toolkit_b200.dynamics.integrators.nvt_nose_hoover",
-            "NPT": "nvalchemi_toolkit_b200.dynamics.integrators.npt", "NPH": "nvalchemi_toolkit_b200.dynamics.integrators.npt",
+            "NPT": "nvalchemi_toolkit_b200.dynamics.integrators.npt", "NPH": "nvalchemi_toolkit_b200.dynamics.integrators.nph",
             "FIRE2": "nvalchemi_toolkit_b200.dynamics.optimizers.fire2",
             "FIREVariableCell": "nvalchemi_toolkit_b200.dynamics.optimizers.fire_cell",
             "FIRE2VariableCell": "nvalchemi_toolkit_b200.dynamics.optimizers.fire2"}

@@ -132,13 +132,10 @@ class NPT(BaseDynamics):
         self._thermostat_half(batch)
 
 
-class NPH(NPT):
-    __dd_thermo_kind__ = "nph"
-    _thermostat = False
+def __getattr__(name: str) -> Any:
+    """``NPH`` lives in :mod:`nvalchemi_toolkit_b200.dynamics.integrators.nph`; importing it from here still works."""
+    if name == "NPH":
+        from nvalchemi_toolkit_b200.dynamics.integrators.nph import NPH
 
-    def __init__(self, model: Any, dt: float, pressure: float, barostat_time: float,
-                 pressure_coupling: str = "isotropic", temperature: float = 300.0, n_steps: int | None = None,
-                 hooks: list | None = None, convergence_hook: Any = None, **kwargs: Any) -> None:
-        super().__init__(model=model, dt=dt, temperature=temperature, pressure=pressure, barostat_time=barostat_time,
-                         thermostat_time=barostat_time, pressure_coupling=pressure_coupling, n_steps=n_steps, hooks=hooks,
-                         convergence_hook=convergence_hook, **kwargs)
+        return NPH
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -184,23 +184,10 @@ class EwaldModelWrapper(_CoulombBase):
     """Direct reciprocal sum: cost ``O(N K)``; exact to the chosen accuracy; best below ~10^4 atoms."""
 
 
-class PMEModelWrapper(_CoulombBase):
-    """Smooth particle-mesh Ewald (B-spline order ``spline_order``, mesh from ``mesh_spacing`` or the accuracy)."""
+def __getattr__(name: str) -> Any:
+    """``PMEModelWrapper`` moved to :mod:`nvalchemi_toolkit_b200.models.pme`; the old import path keeps working."""
+    if name == "PMEModelWrapper":
+        from nvalchemi_toolkit_b200.models.pme import PMEModelWrapper
 
-    method = "pme"
-
-    def __init__(self, cutoff: float = 10.0, accuracy: float = 1e-6, alpha: float | None = None, spline_order: int = 5,
-                 mesh_spacing: float | None = None, mesh_dims: tuple[int, int, int] | None = None, **kw: Any) -> None:
-        super().__init__(cutoff=cutoff, accuracy=accuracy, alpha=alpha, spline_order=spline_order,
-                         mesh_spacing=mesh_spacing, mesh_dims=mesh_dims, **kw)
-        self.order, self.mesh_spacing, self.mesh_dims = int(spline_order), mesh_spacing, mesh_dims
-
-    def _build_setup(self, cell: torch.Tensor) -> Any:
-        dims = tuple(self.mesh_dims) if self.mesh_dims is not None else es.pme_mesh_dims(
-            cell, self.alpha, self.accuracy, self.mesh_spacing, self.order)
-        moduli = tuple(es.bspline_moduli(n, self.order).to(cell.device) for n in dims)
-        return dims, moduli
-
-    def _recip(self, positions, charges, cell, setup, a0, a1, weights, reduce):
-        dims, moduli = setup
-        return es.recip_mesh(positions, charges, cell, self.alpha, dims, self.order, moduli, a0, a1, weights, reduce)
+        return PMEModelWrapper
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

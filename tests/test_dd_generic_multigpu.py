@@ -29,7 +29,7 @@ def _worker(rank: int, world: int, port: int, q) -> None:
         from nvalchemi_toolkit_b200.benchmark import build
         from nvalchemi_toolkit_b200.distributed import DistributedModel, DomainConfig, DomainParallel, ShardedBatch, ShardTensor
         from nvalchemi_toolkit_b200.dynamics import NVE, DynamicsStage, _ops
-        from nvalchemi_toolkit_b200.models.ewald import PMEModelWrapper
+        from nvalchemi_toolkit_b200.models.pme import PMEModelWrapper
 
         res = {}
         # ---- NVE trajectory, float64

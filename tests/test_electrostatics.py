@@ -9,7 +9,8 @@ import torch
 
 from nvalchemi_toolkit_b200 import AtomicData, Batch
 from nvalchemi_toolkit_b200.models import _electrostatics as es
-from nvalchemi_toolkit_b200.models.ewald import EwaldModelWrapper, PMEModelWrapper
+from nvalchemi_toolkit_b200.models.ewald import EwaldModelWrapper
+from nvalchemi_toolkit_b200.models.pme import PMEModelWrapper
 
 
 def _nacl(n=2, a=5.64, noise=0.0, seed=0, charge_noise=0.0):

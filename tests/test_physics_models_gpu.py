@@ -19,7 +19,8 @@ def _run(model, batch):
 
 @pytest.mark.parametrize("kind", ["ewald", "pme"])
 def test_coulomb_models_cuda_match_cpu(kind):
-    from nvalchemi_toolkit_b200.models.ewald import EwaldModelWrapper, PMEModelWrapper
+    from nvalchemi_toolkit_b200.models.ewald import EwaldModelWrapper
+    from nvalchemi_toolkit_b200.models.pme import PMEModelWrapper
     from tests.test_electrostatics import _nacl
 
     cls = EwaldModelWrapper if kind == "ewald" else PMEModelWrapper
