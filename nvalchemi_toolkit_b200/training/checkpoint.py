@@ -332,6 +332,32 @@ def save_checkpoint(root: str | Path, step: int, models: dict[str, torch.nn.Modu
     return PendingCheckpoint(root, th, box)
 
 
+
+def build_models_from_checkpoint(root: str | Path, checkpoint_index: int | None = None, map_location: Any = "cpu",
+                                 strict: bool = True) -> dict[str, torch.nn.Module]:
+    """Instantiate every model of a checkpoint from its ``spec.json`` (``cls_path`` + constructor keywords) and load the
+    weights of the chosen index (default: the manifest's latest).  The classes must be importable; nothing but tensors is
+    unpickled."""
+    from nvalchemi_toolkit_b200._serialization import import_from_path
+
+    root = Path(root)
+    man = CheckpointManifest(root)
+    idx = man.checkpoint_index if checkpoint_index in (None, -1) else int(checkpoint_index)
+    models: dict[str, torch.nn.Module] = {}
+    for name in man.data["models"]:
+        spec = json.loads((root / "models" / name / "spec.json").read_text())
+        kwargs = {k: v for k, v in spec.items() if k not in ("cls_path", "timestamp")}
+        module = import_from_path(spec["cls_path"])(**kwargs)
+        state_file = root / "models" / name / "checkpoints" / f"{idx}.pt"
+        if not state_file.exists():
+            raise FileNotFoundError(f"model '{name}' has no weights for checkpoint index {idx} under {root}")
+        _unwrap(module).load_state_dict(torch.load(state_file, map_location=map_location, weights_only=True), strict=strict)
+        models[name] = module
+    if not models:
+        raise FileNotFoundError(f"{root} holds no model component")
+    return models
+
+
 def read_strategy_metadata(root: str | Path, checkpoint_index: int | None = None) -> dict[str, Any]:
     root = Path(root)
     man = CheckpointManifest(root)

@@ -329,3 +329,38 @@ def test_optimizer_config_checks_kwargs_and_builds_parameter_groups():
     step_schedulers(scheds, [cfg], "validation", {"a": 2.0, "b": 1.0})  # worse: the plateau scheduler halves every lr
     assert [g["lr"] for g in opts[0].param_groups] == [5e-4, 5e-4, 5e-5]
     assert cfg.to_spec()["param_groups"][0]["options"] == {"weight_decay": 0.0}
+
+
+def test_finetune_from_pretrained_checkpoint_inherits_weights_only(tmp_path):
+    """A new fine-tuning run from a checkpoint directory: models rebuilt from their specs with the saved weights, loss and
+    optimiser classes optionally reused (with the fine-tuning learning rate), counters and optimiser state fresh."""
+    from nvalchemi_toolkit_b200.training.finetune import DEFAULT_FINETUNE_LR, FineTuningStrategy
+
+    data = _dataset(8)
+    st = _strategy(num_steps=3)
+    st.run(_loader(data))
+    st.save_checkpoint(tmp_path / "src")
+    ft = FineTuningStrategy.from_pretrained_checkpoint(tmp_path / "src", use_original_loss=True, use_original_opt_class=True,
+                                                       trainable=[r"projection"], num_steps=2, devices=["cpu"])
+    assert ft.step_count == 0 and ft.num_steps == 2
+    for (n, a), (_, b) in zip(st.models["main"].state_dict().items(), ft.models["main"].state_dict().items()):
+        assert torch.equal(a, b), n
+    cfg = ft.optimizer_configs["main"][0]
+    assert cfg.kwargs["lr"] == DEFAULT_FINETUNE_LR and type(ft.loss_fn).__name__ == type(st.loss_fn).__name__
+    before = {n: p.detach().clone() for n, p in ft.models["main"].named_parameters()}
+    ft.run(_loader(data))
+    named = dict(ft.models["main"].named_parameters())
+    changed = [n for n, p in named.items() if not torch.equal(p, before[n])]
+    # the optimiser moves the projection only; the embedding table renormalises its rows in the forward pass (max_norm)
+    assert "model.projection.weight" in changed and set(changed) <= {"model.projection.weight", "model.embedding.weight"}
+    assert all(not named[n].requires_grad for n in named if "projection" not in n) and ft.step_count == 2
+    assert [len(g["params"]) for o in ft._optimizers for g in o.param_groups] == [1]
+    with pytest.raises(ValueError, match="optimiser"):
+        import json
+
+        meta = json.loads((tmp_path / "src" / "strategy.json").read_text())
+        meta["spec"]["optimizer_configs"] = {}
+        (tmp_path / "src" / "strategy.json").write_text(json.dumps(meta))
+        idx_file = sorted((tmp_path / "src" / "strategy" / "checkpoints").glob("*.json"))[-1]
+        idx_file.write_text(json.dumps(meta))
+        FineTuningStrategy.from_pretrained_checkpoint(tmp_path / "src", use_original_opt_class=True, num_steps=1, devices=["cpu"])
