@@ -25,6 +25,11 @@ class WrapPeriodicHook:
     def __call__(self, ctx: Any, stage: Enum) -> None:
         b = ctx.batch
         cell, pbc = getattr(b, "cell", None), getattr(b, "pbc", None)
-        if cell is None or pbc is None or not bool(pbc.any()):
+        if cell is None or pbc is None:
+            return
+        seen = getattr(self, "_pbc_seen", None)
+        if seen is None or seen[0] is not pbc or seen[1] != pbc._version:  # one host read per pbc tensor, not per step
+            self._pbc_seen = seen = (pbc, pbc._version, bool(pbc.any()))
+        if not seen[2]:
             return
         b.positions.copy_(_ops.wrap_positions(b.positions, cell.reshape(-1, 3, 3), b.batch_idx, pbc.reshape(-1, 3)))
