@@ -391,3 +391,69 @@ void halo_pull_add_rows(at::Tensor buf, const at::Tensor& dst_row, const at::Ten
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("halo_pull_add_rows(Tensor(a!) buf, Tensor dst_row, Tensor peer, Tensor peer_row, Tensor ptrs, Tensor? used_ptrs=None, Tensor? used_index=None) -> ()", &nva::halo_pull_add_rows);
 }
+
+namespace nva {
+// Reverse halo of the position gradient FUSED with what consumes it: thread i owns atom i, adds the gradients that other
+// ranks accumulated on their ghost copies of the atom (plain peer loads through the symmetric buffer's address table,
+// copies listed per owned row in CSR form) to its own, writes the force and, when a velocity array is given, applies the
+// closing half kick of velocity Verlet / Langevin BAOAB, v += dt/2 F / m, in the same pass: the gradient of a boundary atom
+// crosses NVLink once and is never written back to memory as an intermediate.
+//   copy_ptr [n_owned + 1], copy_peer / copy_row / copy_used_index [S]: ghost copies of owned row i are entries
+//   copy_ptr[i] .. copy_ptr[i + 1]; `used_ptrs` (optional) = the holders' per-ghost "some edge used this row" bytes.
+__global__ void halo_force_finalize_kernel(int n_owned, const float* __restrict__ gpos, const int* __restrict__ copy_ptr,
+                                           const int* __restrict__ copy_peer, const int* __restrict__ copy_row,
+                                           const int* __restrict__ copy_used_index, const int64_t* __restrict__ ptrs,
+                                           const int64_t* __restrict__ used_ptrs, float* __restrict__ forces,
+                                           float* __restrict__ vel, const float* __restrict__ mass,
+                                           const float* __restrict__ dt, const int* __restrict__ batch_idx) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_owned) return;
+  float g0 = gpos[3 * i], g1 = gpos[3 * i + 1], g2 = gpos[3 * i + 2];
+  for (int k = copy_ptr[i]; k < copy_ptr[i + 1]; ++k) {
+    const int p = copy_peer[k];
+    if (used_ptrs != nullptr && reinterpret_cast<const uint8_t*>(used_ptrs[p])[copy_used_index[k]] == 0) continue;
+    const float* src = reinterpret_cast<const float*>(ptrs[p]) + 3 * (int64_t)copy_row[k];
+    g0 += src[0]; g1 += src[1]; g2 += src[2];
+  }
+  const float f0 = -g0, f1 = -g1, f2 = -g2;
+  forces[3 * i] = f0; forces[3 * i + 1] = f1; forces[3 * i + 2] = f2;
+  if (vel != nullptr) {
+    const float h = 0.5f * dt[batch_idx[i]] / mass[i];
+    vel[3 * i] += h * f0; vel[3 * i + 1] += h * f1; vel[3 * i + 2] += h * f2;
+  }
+}
+
+void halo_force_finalize(const at::Tensor& gpos, const at::Tensor& copy_ptr, const at::Tensor& copy_peer,
+                         const at::Tensor& copy_row, const at::Tensor& copy_used_index, const at::Tensor& ptrs,
+                         const c10::optional<at::Tensor>& used_ptrs, at::Tensor forces,
+                         const c10::optional<at::Tensor>& velocities, const c10::optional<at::Tensor>& masses,
+                         const c10::optional<at::Tensor>& dt, const c10::optional<at::Tensor>& batch_idx) {
+  c10::cuda::CUDAGuard guard(gpos.device());
+  NVA_CHECK_CONTIG(gpos); NVA_CHECK_CONTIG(forces);
+  const int64_t n = forces.size(0);
+  if (n == 0) return;
+  TORCH_CHECK(gpos.scalar_type() == at::kFloat && forces.scalar_type() == at::kFloat && gpos.size(0) >= n &&
+                  copy_ptr.numel() == n + 1 && copy_ptr.scalar_type() == at::kInt,
+              "halo_force_finalize: float32 gradients / forces and an int32 CSR pointer of n_owned + 1 entries");
+  TORCH_CHECK(copy_peer.numel() == copy_row.numel() && copy_peer.numel() == copy_used_index.numel(),
+              "halo_force_finalize: copy tables of different lengths");
+  const bool kick = velocities.has_value();
+  if (kick) {
+    TORCH_CHECK(masses.has_value() && dt.has_value() && batch_idx.has_value(), "halo_force_finalize: velocities need masses, dt, batch_idx");
+    TORCH_CHECK(velocities->scalar_type() == at::kFloat && velocities->is_contiguous() && velocities->size(0) >= n &&
+                    masses->scalar_type() == at::kFloat && dt->scalar_type() == at::kFloat && batch_idx->scalar_type() == at::kInt,
+                "halo_force_finalize: float32 velocities / masses / dt and int32 batch_idx");
+  }
+  halo_force_finalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      (int)n, gpos.data_ptr<float>(), copy_ptr.data_ptr<int>(), copy_peer.data_ptr<int>(), copy_row.data_ptr<int>(),
+      copy_used_index.data_ptr<int>(), ptrs.data_ptr<int64_t>(),
+      used_ptrs.has_value() ? used_ptrs->data_ptr<int64_t>() : nullptr, forces.data_ptr<float>(),
+      kick ? velocities->data_ptr<float>() : nullptr, kick ? masses->data_ptr<float>() : nullptr,
+      kick ? dt->data_ptr<float>() : nullptr, kick ? batch_idx->data_ptr<int>() : nullptr);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+}  // namespace nva
+
+TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
+  m.def("halo_force_finalize(Tensor gpos, Tensor copy_ptr, Tensor copy_peer, Tensor copy_row, Tensor copy_used_index, Tensor ptrs, Tensor? used_ptrs, Tensor(a!) forces, Tensor(b!)? velocities=None, Tensor? masses=None, Tensor? dt=None, Tensor? batch_idx=None) -> ()", &nva::halo_force_finalize);
+}

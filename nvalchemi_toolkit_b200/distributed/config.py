@@ -42,6 +42,11 @@ class DomainConfig(BaseModel):
     #: ghost rows through peer-mapped memory and this package's NVLink kernels (True), through ``torch.distributed``
     #: collectives only (False), or peer memory whenever the model, device and process group allow it (None)
     peer_memory: bool | None = None
+    #: peer-memory engine with an integrator whose closing update is the plain half kick (NVE, NVT Langevin): the kernel that
+    #: collects the ghost copies' position gradients also writes the forces and applies ``v += dt/2 F/m``, and the
+    #: integrator's own closing update is skipped.  Hooks that run between AFTER_COMPUTE and BEFORE_POST_UPDATE then see the
+    #: velocities AFTER the kick; switch off if a hook depends on the velocities of the half step.
+    fuse_integrator_finalize: bool = True
 
     @model_validator(mode="after")
     def _defaults(self) -> "DomainConfig":

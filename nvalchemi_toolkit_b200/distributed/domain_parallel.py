@@ -190,8 +190,22 @@ class DomainParallel:
             dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
         return bool(int(ok))
 
+    def _fusable_finalize(self) -> bool:
+        """The closing velocity update can ride on the force-return kernel of the peer-memory engine: plain half kick,
+        float32 contiguous state, and no re-partition inside the compute phase (it would replace the velocity tensor)."""
+        engine = getattr(self.model, "engine", None)
+        if engine is None or not self.config.fuse_integrator_finalize or not self.async_migration:
+            return False
+        if not getattr(self.dynamics, "__dd_half_kick_finalize__", False) or not getattr(engine, "fused_force_return", False):
+            return False
+        owned, state = self.sharded.owned, getattr(self.dynamics, "_state", None) or {}
+        v, m, dt = getattr(owned, "velocities", None), getattr(owned, "atomic_masses", None), state.get("dt")
+        return (v is not None and m is not None and dt is not None and v.dtype == torch.float32 and v.is_contiguous()
+                and m.dtype == torch.float32 and dt.dtype == torch.float32 and owned.batch_idx.dtype == torch.int32)
+
     def step(self) -> ShardedBatch:
         sh, dyn = self.sharded, self.dynamics
+        fuse = False
         if sh is None:
             raise RuntimeError("call partition(batch) first")
         if self.async_migration and sh.consume_rebuild_check():
@@ -209,9 +223,18 @@ class DomainParallel:
                 if self.async_migration:
                     sh.dispatch_rebuild_check()  # positions are final for this step; the flag is read at the next one
             elif fn == "compute":
-                self.compute(check_rebuild=not self.async_migration)
+                fuse = self._fusable_finalize()
+                if fuse:
+                    owned = sh.owned
+                    self.model.engine.fused_finalize = (owned.velocities, owned.atomic_masses, dyn._state["dt"], owned.batch_idx)
+                try:
+                    self.compute(check_rebuild=not self.async_migration)
+                finally:
+                    if fuse:
+                        self.model.engine.fused_finalize = None
             elif fn == "post":
-                dyn.post_update(sh.owned)
+                if not fuse:  # else the force-return kernel already applied the closing half kick
+                    dyn.post_update(sh.owned)
         self.converged = self._global_convergence(sh.owned)
         if self.converged:
             dyn._call_hooks(DynamicsStage.ON_CONVERGE, sh.owned)

@@ -90,6 +90,12 @@ class PeerHaloEngine:
     reverse_pull = True
 
     phase_events: list | None = None
+    #: ``(velocities, masses, dt per system, batch_idx)`` of the owned atoms: when set (by ``DomainParallel`` for integrators
+    #: whose closing update is the plain half kick) the kernel that collects the ghost copies' position gradients also
+    #: writes the forces and applies ``v += dt/2 F/m`` (reverse halo fused with the integrator update)
+    fused_finalize: tuple | None = None
+    #: collect forces with the fused kernel (one thread per owned atom, copies in CSR form) instead of pull-add + negate
+    fused_force_return: bool = True
 
     def __init__(self, wrapper: Any, config: Any, group: Any = None, max_neighbors: int | None = None) -> None:
         self.wrapper, self.model, self.config = wrapper, wrapper.model, config
@@ -177,6 +183,13 @@ class PeerHaloEngine:
         self.ghost_used.zero_()
         self.send_row, self.send_peer = tables["send_row"], tables["send_peer"]
         self.send_used_index, self.send_peer_row = tables["send_used_index"], tables["send_peer_row"]
+        # the same send entries grouped by owned row (CSR): the fused force return reads every copy of a row in one thread
+        order = torch.argsort(self.send_row.long(), stable=True)
+        self.copy_peer = self.send_peer[order].contiguous()
+        self.copy_row = self.send_peer_row[order].to(torch.int32).contiguous()
+        self.copy_used_index = self.send_used_index[order].to(torch.int32).contiguous()
+        self.copy_ptr = torch.zeros(n + 1, dtype=torch.int32, device=dev)
+        torch.cumsum(torch.bincount(self.send_row.long(), minlength=n), 0, out=self.copy_ptr[1:])
         self._nl = self._nl_ref = self._csr = None
         self._sums = torch.zeros(10, dtype=torch.float64, device=dev)
         self._bound = key

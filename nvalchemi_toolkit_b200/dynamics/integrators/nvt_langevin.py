@@ -16,6 +16,8 @@ from nvalchemi_toolkit_b200.dynamics.base import BaseDynamics
 
 
 class NVTLangevin(BaseDynamics):
+    #: the closing update is ``v += dt/2 F/m`` and nothing else: a domain decomposition may fuse it with its force return
+    __dd_half_kick_finalize__ = True
     __needs_keys__ = {"forces"}
     __provides_keys__ = {"positions", "velocities"}
     __dd_thermo_kind__ = "local"

@@ -549,6 +549,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
         return out
 
     grad_pos = dd.gpos if dd is not None else torch.zeros_like(pos)
+    fused_forces: torch.Tensor | None = None
 
     def tangent_chunks(ws_: list, kept: list | None) -> Any:
         """``(i0, i1, e0, e1, h3 [E, 2, 64])``: what the forward pass kept, else recomputed chunk by chunk."""
@@ -614,7 +615,14 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
                 rev = (dd.send_row, dd.send_peer, dd.send_peer_row)
                 if li > 0:
                     ops.halo_pull_add_rows(du, *rev, du_ptrs, dd.used_ptrs, dd.send_used_index)
-                if li == 0:
+                if li == 0 and getattr(dd, "fused_force_return", False) and hasattr(dd, "copy_ptr"):
+                    # reverse halo of the position gradient fused with its consumers: forces and, when the integrator's
+                    # closing update is the plain half kick, the velocities (one pass, one thread per owned atom)
+                    fused_forces = torch.empty(n, 3, dtype=grad_pos.dtype, device=dev)
+                    fin = getattr(dd, "fused_finalize", None)
+                    ops.halo_force_finalize(grad_pos, dd.copy_ptr, dd.copy_peer, dd.copy_row, dd.copy_used_index, dd.gpos_ptrs,
+                                            dd.used_ptrs, fused_forces, *(fin if fin is not None else (None, None, None, None)))
+                elif li == 0:
                     ops.halo_pull_add_rows(grad_pos, *rev, dd.gpos_ptrs, dd.used_ptrs, dd.send_used_index)
             else:
                 if li > 0:
@@ -633,7 +641,7 @@ def forward(model: Any, data: dict[str, torch.Tensor], species: torch.Tensor, ba
             dh = _per_l_linear(du, ip.linear_up, ip.l_in, transpose=True)
             _skip(ip, dh_tot, species, nz, transpose=True, accumulate_into=dh)
         saved[li] = None
-    out["forces"] = -grad_pos[:n]
+    out["forces"] = fused_forces if fused_forces is not None else -grad_pos[:n]
     if compute_stress:
         vol = torch.linalg.det(cell).abs().double()
         sg = strain_grad.reshape(num_graphs, 3, 3)

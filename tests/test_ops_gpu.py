@@ -242,3 +242,61 @@ def test_halo_kernels_against_index_ops_single_process(width):
     ref = before[0].clone().index_add_(0, dst_row.long(), copies)
     assert torch.allclose(arenas[0], ref, atol=1e-5)
     assert p2p.status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kick", [False, True])
+def test_fused_force_return_and_half_kick_single_process(kick):
+    """``halo_force_finalize``: owned gradient + the ghost copies' gradients on other (emulated) ranks -> force, and with a
+    velocity array the closing half kick, against index operations; masked copies are skipped."""
+    from nvalchemi_toolkit_b200.ops import _native
+    from nvalchemi_toolkit_b200.parallel.symmetric import P2PContext
+
+    assert _native.available()
+    ops = torch.ops.nvalchemi
+    dev = torch.device("cuda", 0)
+    n_own, n_ghost, world = 300, 120, 3
+    cap = n_own + n_ghost
+    p2p = P2PContext.single_process(4 * cap * 3 + n_ghost + (1 << 16), dev, world)
+    gpos, ptrs = p2p.arena.alloc((cap, 3))
+    used, used_ptrs = p2p.arena.alloc((n_ghost,), torch.uint8)
+    g = torch.Generator().manual_seed(11)
+    views, used_views = [], []
+    for r in range(world):
+        raw = p2p.arena._bufs[r]
+        v = raw[p2p.arena.offset_of(gpos): p2p.arena.offset_of(gpos) + 4 * cap * 3].view(torch.float32).reshape(cap, 3)
+        v.copy_(torch.randn(cap, 3, generator=g))
+        u = raw[p2p.arena.offset_of(used): p2p.arena.offset_of(used) + n_ghost]
+        u.copy_((torch.rand(n_ghost, generator=g) < 0.75).to(torch.uint8))
+        views.append(v)
+        used_views.append(u)
+    # every third owned row has one or two copies on the other "ranks"
+    rows, peers, prow = [], [], []
+    for i in range(0, n_own, 3):
+        for c in range(1 + (i % 2)):
+            rows.append(i)
+            peers.append(1 + (i + c) % (world - 1))
+            prow.append(int(torch.randint(0, n_ghost, (1,), generator=g)))
+    rows_t = torch.tensor(rows)
+    copy_ptr = torch.zeros(n_own + 1, dtype=torch.int32)
+    copy_ptr[1:] = torch.cumsum(torch.bincount(rows_t, minlength=n_own), 0)
+    copy_peer = torch.tensor(peers, dtype=torch.int32, device=dev)
+    copy_used_index = torch.tensor(prow, dtype=torch.int32, device=dev)
+    copy_row = (copy_used_index + n_own).contiguous()
+    forces = torch.empty(n_own, 3, device=dev)
+    vel0 = torch.randn(n_own, 3, generator=g).to(dev)
+    vel = vel0.clone()
+    mass = (1.0 + torch.rand(n_own, generator=g)).to(dev)
+    dt = torch.tensor([0.37], device=dev)
+    bidx = torch.zeros(n_own, dtype=torch.int32, device=dev)
+    extra = (vel, mass, dt, bidx) if kick else (None, None, None, None)
+    ops.halo_force_finalize(gpos, copy_ptr.to(dev), copy_peer, copy_row, copy_used_index, ptrs, used_ptrs, forces, *extra)
+    want = views[0][:n_own].clone()
+    for i, p, j in zip(rows, peers, prow):
+        if int(used_views[p][j]):
+            want[i] += views[p][n_own + j]
+    assert torch.allclose(forces, -want, atol=1e-6)
+    if kick:
+        assert torch.allclose(vel, vel0 + 0.5 * dt * (-want) / mass[:, None], atol=1e-6)
+    else:
+        assert torch.equal(vel, vel0)
