@@ -55,9 +55,22 @@ __device__ __forceinline__ int float_order_code(float f) {
   const int i = __float_as_int(f);
   return i >= 0 ? i : i ^ 0x7fffffff;
 }
+// Ghost pull folded into the first pass over the atoms (domain decomposition on peer memory): rows >= ghost_row0 of `pos`
+// are ghost atoms whose current position lives on another rank; the thread reads it from the owner through the symmetric
+// buffer's address table (plain peer load), adds the lattice shift of the image and stores it into the local row, so the
+// binning, the search and every later kernel see it without a separate halo kernel.
+struct GhostPull {
+  int64_t row0;             // first ghost row; < 0: no pull
+  const int* home_rank;     // [n - row0]
+  const int* home_row;
+  const float* shift;       // [n - row0, 3]
+  const int64_t* src_ptrs;  // [world] base addresses of the position buffer on every rank
+};
+
 template <typename T>
-__global__ void frac_bounds_kernel(int64_t n, const T* __restrict__ pos, const T* __restrict__ cell_inv,
-                                   const int* __restrict__ batch_idx, int* __restrict__ lo, int* __restrict__ hi) {
+__global__ void frac_bounds_kernel(int64_t n, T* __restrict__ pos, const T* __restrict__ cell_inv,
+                                   const int* __restrict__ batch_idx, int* __restrict__ lo, int* __restrict__ hi,
+                                   GhostPull gp) {
   __shared__ int s_lo[3], s_hi[3], s_first, s_same;
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   const bool live = i < n;
@@ -72,7 +85,15 @@ __global__ void frac_bounds_kernel(int64_t n, const T* __restrict__ pos, const T
   int code[3] = {0, 0, 0};
   if (live) {
     const T* Hi = cell_inv + 9 * s;
-    const T x = pos[3 * i], y = pos[3 * i + 1], z = pos[3 * i + 2];
+    T x, y, z;
+    if (gp.row0 >= 0 && i >= gp.row0) {
+      const int64_t g = i - gp.row0;
+      const float* src = reinterpret_cast<const float*>(gp.src_ptrs[gp.home_rank[g]]) + 3 * (int64_t)gp.home_row[g];
+      x = (T)(src[0] + gp.shift[3 * g]); y = (T)(src[1] + gp.shift[3 * g + 1]); z = (T)(src[2] + gp.shift[3 * g + 2]);
+      pos[3 * i] = x; pos[3 * i + 1] = y; pos[3 * i + 2] = z;
+    } else {
+      x = pos[3 * i]; y = pos[3 * i + 1]; z = pos[3 * i + 2];
+    }
     for (int c = 0; c < 3; ++c)
       code[c] = float_order_code((float)((double)x * Hi[c] + (double)y * Hi[3 + c] + (double)z * Hi[6 + c]));
   }
@@ -225,7 +246,9 @@ void search_cpu(int64_t n, const T* pos, const T* cell, const int* batch_idx, co
 void neighbor_matrix_build(const Tensor& pos, const Tensor& cell, const Tensor& pbc, const Tensor& batch_idx,
                            const Tensor& batch_ptr, double cutoff, bool half_list, Tensor out_matrix,
                            Tensor out_num, Tensor out_shifts, const c10::optional<Tensor>& rebuild_flags,
-                           int64_t num_rows) {
+                           int64_t num_rows, const c10::optional<Tensor>& ghost_home_rank,
+                           const c10::optional<Tensor>& ghost_home_row, const c10::optional<Tensor>& ghost_shift,
+                           const c10::optional<Tensor>& ghost_src_ptrs, int64_t ghost_row0) {
   c10::cuda::OptionalCUDAGuard guard(pos.is_cuda() ? c10::make_optional(pos.device()) : c10::nullopt);
   NVA_CHECK_CONTIG(pos); NVA_CHECK_CONTIG(cell); NVA_CHECK_CONTIG(out_matrix); NVA_CHECK_CONTIG(out_shifts);
   int64_t n = pos.size(0), B = cell.size(0), K = out_matrix.size(1);
@@ -246,9 +269,19 @@ void neighbor_matrix_build(const Tensor& pos, const Tensor& cell, const Tensor& 
     Tensor hi = at::full({B, 3}, (int64_t)INT32_MIN, pos.options().dtype(at::kInt));
     Tensor inv_p = inv.to(pos.scalar_type()).contiguous();
     const int64_t nb_ = (n + kThreads - 1) / kThreads;
+    GhostPull gp{-1, nullptr, nullptr, nullptr, nullptr};
+    if (ghost_row0 >= 0 && ghost_home_rank.has_value()) {
+      TORCH_CHECK(pos.scalar_type() == at::kFloat && ghost_home_row.has_value() && ghost_shift.has_value() && ghost_src_ptrs.has_value(),
+                  "neighbor_matrix_build: the ghost pull needs float32 positions and all four ghost tables");
+      TORCH_CHECK(ghost_home_rank->numel() == n - ghost_row0 && ghost_home_row->numel() == n - ghost_row0 &&
+                      ghost_shift->numel() == 3 * (n - ghost_row0) && ghost_shift->is_contiguous(),
+                  "neighbor_matrix_build: ghost tables must cover rows ghost_row0 .. n");
+      gp = GhostPull{ghost_row0, ghost_home_rank->data_ptr<int>(), ghost_home_row->data_ptr<int>(), ghost_shift->data_ptr<float>(),
+                     ghost_src_ptrs->data_ptr<int64_t>()};
+    }
     AT_DISPATCH_FLOATING_TYPES(pos.scalar_type(), "frac_bounds", [&] {
       frac_bounds_kernel<scalar_t><<<(unsigned)nb_, kThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
-          n, pos.data_ptr<scalar_t>(), inv_p.data_ptr<scalar_t>(), batch_idx.data_ptr<int>(), lo.data_ptr<int>(), hi.data_ptr<int>());
+          n, pos.data_ptr<scalar_t>(), inv_p.data_ptr<scalar_t>(), batch_idx.data_ptr<int>(), lo.data_ptr<int>(), hi.data_ptr<int>(), gp);
     });
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     auto decode = [](const Tensor& code) {
@@ -383,5 +416,5 @@ void csr_fill(const Tensor& nm, const c10::optional<Tensor>& shifts, const Tenso
 
 TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("csr_fill(Tensor nm, Tensor? shifts, Tensor eptr, Tensor(a!) esend, Tensor(b!) erecv, Tensor(c!) eS) -> ()", &nva::csr_fill);
-  m.def("neighbor_matrix_build(Tensor positions, Tensor cell, Tensor pbc, Tensor batch_idx, Tensor batch_ptr, float cutoff, bool half_list, Tensor(a!) out_matrix, Tensor(b!) out_num, Tensor(c!) out_shifts, Tensor? rebuild_flags=None, int num_rows=-1) -> ()", &nva::neighbor_matrix_build);
+  m.def("neighbor_matrix_build(Tensor(d!) positions, Tensor cell, Tensor pbc, Tensor batch_idx, Tensor batch_ptr, float cutoff, bool half_list, Tensor(a!) out_matrix, Tensor(b!) out_num, Tensor(c!) out_shifts, Tensor? rebuild_flags=None, int num_rows=-1, Tensor? ghost_home_rank=None, Tensor? ghost_home_row=None, Tensor? ghost_shift=None, Tensor? ghost_src_ptrs=None, int ghost_row0=-1) -> ()", &nva::neighbor_matrix_build);
 }

@@ -96,6 +96,9 @@ class PeerHaloEngine:
     fused_finalize: tuple | None = None
     #: collect forces with the fused kernel (one thread per owned atom, copies in CSR form) instead of pull-add + negate
     fused_force_return: bool = True
+    #: let the first kernel of the neighbour build fetch the ghost positions from their owners (no separate pull kernel);
+    #: applies when the list is rebuilt every step (``neighbor_skin == 0``), else the pull kernel runs
+    fold_ghost_pull: bool = True
 
     def __init__(self, wrapper: Any, config: Any, group: Any = None, max_neighbors: int | None = None) -> None:
         self.wrapper, self.model, self.config = wrapper, wrapper.model, config
@@ -195,7 +198,7 @@ class PeerHaloEngine:
         self._bound = key
 
     # ------------------------------------------------------------------ neighbour list over owned + ghost rows
-    def _neighbors(self, pos_local: torch.Tensor, cell: torch.Tensor) -> Any:
+    def _neighbors(self, pos_local: torch.Tensor, cell: torch.Tensor, ghost_pull: tuple | None = None) -> Any:
         from nvalchemi_toolkit_b200.models.mace import native
 
         n, n_local = self.n_owned, pos_local.shape[0]
@@ -211,7 +214,7 @@ class PeerHaloEngine:
                             torch.empty(n, dtype=torch.int32, device=pos_local.device),
                             torch.empty(n, k, 3, dtype=torch.int32, device=pos_local.device))
             nm, num, sh = _nb.neighbor_matrix(pos_local, cell, self.pbc, self.batch_idx, self.batch_ptr, self.cutoff + skin, k,
-                                              False, out=self._nl, num_rows=n)
+                                              False, out=self._nl, num_rows=n, ghost_pull=ghost_pull)
             csr = native.build_csr(nm, num, sh)
             if csr.max_count <= k:
                 break
@@ -238,11 +241,15 @@ class PeerHaloEngine:
         if ng:
             torch.matmul(self.ghost_image, cell, out=self.ghost_shift)
         self.p2p.barrier()  # every rank's owned rows are in place (and last step's readers are done)
-        _nops.halo_pull_rows(self.pos_buf, n, self.ghost_home_rank, self.ghost_home_row, self.ghost_shift, self.pos_ptrs)
-        mark("ghost_positions")
         pos_local = self.pos_buf[: n + ng]
         cell3 = cell.reshape(1, 3, 3).contiguous()
-        csr = self._neighbors(pos_local, cell3)
+        fold = self.fold_ghost_pull and self.neighbor_skin == 0.0 and ng > 0
+        if not fold:
+            _nops.halo_pull_rows(self.pos_buf, n, self.ghost_home_rank, self.ghost_home_row, self.ghost_shift, self.pos_ptrs)
+        mark("ghost_positions")
+        # (with `fold` the first kernel of the neighbour build fetches the ghost positions from their owners itself)
+        csr = self._neighbors(pos_local, cell3, (n, self.ghost_home_rank, self.ghost_home_row, self.ghost_shift, self.pos_ptrs)
+                              if fold else None)
         mark("neighbor_list")
         want_f, want_s = "forces" in active, "stress" in active
         out = native.forward(self.model, {"positions": pos_local, "cell": cell3, "_csr": csr}, self.species,

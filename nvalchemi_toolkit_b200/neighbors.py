@@ -50,12 +50,15 @@ def cell_and_pbc(batch: Batch) -> tuple[torch.Tensor, torch.Tensor]:
 def neighbor_matrix(positions: torch.Tensor, cell: torch.Tensor, pbc: torch.Tensor, batch_idx: torch.Tensor,
                     batch_ptr: torch.Tensor, cutoff: float, max_neighbors: int, half_list: bool = False,
                     out: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
-                    rebuild_flags: torch.Tensor | None = None, num_rows: int | None = None
+                    rebuild_flags: torch.Tensor | None = None, num_rows: int | None = None,
+                    ghost_pull: tuple[int, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor] | None = None
                     ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Dense neighbour search.  Returns ``(matrix [N,K] int32 padded with N, counts [N] int32, shifts [N,K,3] int32)``.
 
     With ``num_rows`` only the first ``num_rows`` atoms get a neighbour row (all atoms remain candidates): under domain
-    decomposition ghost atoms send but do not receive, so their rows are never read."""
+    decomposition ghost atoms send but do not receive, so their rows are never read.  ``ghost_pull = (first ghost row,
+    home_rank, home_row, shift [G, 3], src_ptrs)`` (peer-memory decomposition, float32 CUDA): the first pass over the atoms
+    fetches the ghost rows of ``positions`` from their owners and stores them IN ``positions`` before binning."""
     n = positions.shape[0]
     dev = positions.device
     if out is None:
@@ -67,10 +70,16 @@ def neighbor_matrix(positions: torch.Tensor, cell: torch.Tensor, pbc: torch.Tens
     if n == 0:
         return nm, num, sh
     if _native.require(positions):
+        if ghost_pull is not None and not (positions.is_contiguous() and positions.dtype == torch.float32):
+            raise ValueError("ghost_pull writes the ghost rows into `positions`: pass a contiguous float32 tensor")
         _nops.neighbor_matrix_build(positions.detach().contiguous(), cell, pbc, batch_idx.to(torch.int32),
                                                   batch_ptr.to(torch.int32), float(cutoff), bool(half_list), nm, num, sh,
-                                                  rebuild_flags, -1 if num_rows is None else int(num_rows))
+                                                  rebuild_flags, -1 if num_rows is None else int(num_rows),
+                                                  *((None, None, None, None, -1) if ghost_pull is None else
+                                                    (ghost_pull[1], ghost_pull[2], ghost_pull[3], ghost_pull[4], int(ghost_pull[0]))))
         return nm, num, sh
+    if ghost_pull is not None:
+        raise RuntimeError("ghost_pull needs the native library and CUDA positions")
     if num_rows is not None and num_rows < n:
         full = _neighbor_matrix_torch(positions.detach(), cell, pbc, batch_idx, cutoff, torch.full((n, nm.shape[1]), n, dtype=torch.int32, device=dev),
                                       torch.zeros(n, dtype=torch.int32, device=dev),

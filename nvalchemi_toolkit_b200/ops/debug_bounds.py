@@ -118,14 +118,14 @@ def check(op: str, schema: Any, args: tuple, kwargs: dict) -> None:
             _range(op, "num_neighbors", nn, 0, int(nm.shape[1]) + 1)
 
     world = None
-    for k in ("src_ptrs", "dst_ptrs", "ptrs", "u_ptrs"):
+    for k in ("src_ptrs", "dst_ptrs", "ptrs", "u_ptrs", "ghost_src_ptrs"):
         if isinstance(b.get(k), torch.Tensor):
             world = int(b[k].numel())
             break
-    for k in ("home_rank", "peer"):
+    for k in ("home_rank", "peer", "ghost_home_rank"):
         if isinstance(b.get(k), torch.Tensor):
             _range(op, k, b[k], 0, world)
-    for k in ("home_row", "peer_row", "dst_row"):
+    for k in ("home_row", "peer_row", "dst_row", "ghost_home_row"):
         if isinstance(b.get(k), torch.Tensor):
             hi = _rows(b.get("buf")) if (k == "dst_row" and op == "halo_pull_add_rows") else None
             _range(op, k, b[k], 0, hi)

@@ -300,3 +300,44 @@ def test_fused_force_return_and_half_kick_single_process(kick):
         assert torch.allclose(vel, vel0 + 0.5 * dt * (-want) / mass[:, None], atol=1e-6)
     else:
         assert torch.equal(vel, vel0)
+
+
+@pytest.mark.gpu
+def test_neighbor_build_fetches_ghost_positions_itself():
+    """``ghost_pull``: the first kernel of the neighbour build loads the ghost rows from their owners' buffers (here two
+    local buffers behind a pointer table), adds the image shift and stores them; rows, counts and shifts equal those of a
+    separate pull followed by the plain build."""
+    from nvalchemi_toolkit_b200 import neighbors as nb
+
+    dev = "cuda"
+    g = torch.Generator().manual_seed(5)
+    box = 12.0
+    n_own, n_ghost = 700, 260
+    own = (torch.rand(n_own, 3, generator=g) * torch.tensor([box / 2, box, box])).to(dev)
+    other = (torch.rand(900, 3, generator=g) * torch.tensor([box / 2, box, box]) + torch.tensor([box / 2, 0, 0])).to(dev)
+    ptrs = torch.tensor([own.data_ptr(), other.data_ptr()], dtype=torch.int64, device=dev)
+    home_rank = torch.ones(n_ghost, dtype=torch.int32, device=dev)
+    home_row = torch.randperm(900, generator=g)[:n_ghost].to(torch.int32).to(dev)
+    shift = torch.zeros(n_ghost, 3, device=dev)
+    shift[::2, 0] = -box  # every other ghost is the periodic image on the far side
+    cell = (torch.eye(3, device=dev) * box).reshape(1, 3, 3)
+    pbc = torch.zeros(1, 3, dtype=torch.bool, device=dev)
+    n = n_own + n_ghost
+    bidx = torch.zeros(n, dtype=torch.int32, device=dev)
+    bptr = torch.tensor([0, n], dtype=torch.int32, device=dev)
+    ref = torch.zeros(n, 3, device=dev)
+    ref[:n_own] = own
+    torch.ops.nvalchemi.halo_pull_rows(ref, n_own, home_rank, home_row, shift, ptrs)
+    want = nb.neighbor_matrix(ref, cell, pbc, bidx, bptr, 3.0, 96, num_rows=n_own)
+    got_pos = torch.full((n, 3), float("nan"), device=dev)
+    got_pos[:n_own] = own
+    got = nb.neighbor_matrix(got_pos, cell, pbc, bidx, bptr, 3.0, 96, num_rows=n_own,
+                             ghost_pull=(n_own, home_rank, home_row, shift, ptrs))
+    assert torch.equal(got_pos, ref)
+    assert torch.equal(got[1][:n_own], want[1][:n_own]) and int(want[1][:n_own].max()) > 0
+
+    def canon(nm, num):
+        cols = torch.arange(nm.shape[1], device=dev)[None, :] < num[:n_own, None]
+        return torch.where(cols, nm[:n_own], torch.full_like(nm[:n_own], n)).sort(dim=1).values
+
+    assert torch.equal(canon(got[0], got[1]), canon(want[0], want[1]))
