@@ -5,7 +5,13 @@ Reference: ``nvalchemi/training/losses/{composition,terms,reductions,schedules}.
 ``predictions[prediction_key]`` with ``batch[target_key]``; terms compose with ``+`` and ``*`` into a
 ``ComposedLossFunction`` whose call returns ``{"total_loss": ..., "<name>": ...}``.  Weights may be constants or
 schedules evaluated at ``(step, epoch)``.  Per-atom quantities are first reduced per graph (sum or mean over the graph's
-atoms) so large systems do not dominate a batch."""
+atoms) so large systems do not dominate a batch.
+
+Every term runs the same five steps (reference ``composition.py:280-527``): align dtypes (``dtype_policy``), validate
+shapes, build a validity mask (padding rows of padded ``[B, V_max, ...]`` tensors; with ``ignore_nonfinite`` also every
+target entry that is NaN / inf, i.e. a missing label), evaluate the elementwise residual with invalid targets replaced
+(so neither the value nor the gradient sees them) and reduce: per graph first (``per_sample_loss`` keeps the detached
+per-graph values of the last call), then over the graphs that have at least one valid entry."""
 from __future__ import annotations
 
 import math
@@ -85,24 +91,114 @@ def frobenius_mse(pred: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------ terms
+DTYPE_POLICIES = ("strict", "prediction_to_target", "target_to_prediction")
+
+
+def align_dtypes(pred: torch.Tensor, target: torch.Tensor, policy: str, who: str = "loss") -> tuple[torch.Tensor, torch.Tensor]:
+    """``strict`` raises on a mismatch; the other two cast one side (reference ``composition.py:65-79``)."""
+    if policy not in DTYPE_POLICIES:
+        raise ValueError(f"dtype_policy must be one of {DTYPE_POLICIES}, got {policy!r}")
+    if pred.dtype == target.dtype:
+        return pred, target
+    if policy == "strict":
+        raise TypeError(f"{who}: prediction is {pred.dtype}, target is {target.dtype}; pick dtype_policy="
+                        "'prediction_to_target' or 'target_to_prediction' to cast one side")
+    return (pred.to(target.dtype), target) if policy == "prediction_to_target" else (pred, target.to(pred.dtype))
+
+
+def node_counts(num_nodes_per_graph: torch.Tensor) -> torch.Tensor:
+    """Per-graph atom counts from explicit counts ``[B]`` or a padded validity mask ``[B, V_max]``."""
+    t = num_nodes_per_graph
+    return t.sum(-1) if t.dtype == torch.bool or t.dim() == 2 else t
+
+
+def padded_node_mask(num_nodes_per_graph: torch.Tensor, v_max: int) -> torch.Tensor:
+    t = num_nodes_per_graph
+    if t.dim() == 2:
+        if t.shape[1] != v_max:
+            raise ValueError(f"node mask has {t.shape[1]} columns, the padded tensor {v_max}")
+        return t.to(torch.bool)
+    return torch.arange(v_max, device=t.device)[None, :] < t.reshape(-1, 1)
+
+
 class BaseLossFunction:
-    """One weighted term.  Subclasses implement ``per_graph(pred, target, batch) -> [B]``."""
+    """One weighted term.  Subclasses implement ``residual(pred, target, batch) -> elementwise tensor`` (same leading
+    shape as ``pred``) and choose ``level`` (``"graph"``: one row per graph; ``"node"``: one row per atom, dense
+    ``[V, ...]`` with ``batch.batch_idx`` or padded ``[B, V_max, ...]`` with ``batch.num_nodes_per_graph``)."""
 
     default_key = "energy"
+    level = "graph"
+    #: the prediction is a derivative of the model output (forces, stress): evaluation needs autograd switched on
+    requires_eval_grad: bool | None = False
 
     def __init__(self, target_key: str | None = None, prediction_key: str | None = None, weight: Any = 1.0,
-                 name: str | None = None, dtype: torch.dtype | None = None) -> None:
+                 name: str | None = None, dtype: torch.dtype | None = None, ignore_nonfinite: bool = False,
+                 dtype_policy: str = "target_to_prediction") -> None:
+        if dtype_policy not in DTYPE_POLICIES:
+            raise ValueError(f"dtype_policy must be one of {DTYPE_POLICIES}, got {dtype_policy!r}")
         self.target_key = target_key or self.default_key
         self.prediction_key = prediction_key or self.target_key
         self.weight = weight
         self.name = name or f"{type(self).__name__}[{self.prediction_key}]"
         self.dtype = dtype
+        self.ignore_nonfinite = bool(ignore_nonfinite)
+        self.dtype_policy = dtype_policy
+        self.per_sample_loss: torch.Tensor | None = None
 
     def weight_at(self, step: int, epoch: int) -> float:
         return float(self.weight(step, epoch)) if callable(self.weight) else float(self.weight)
 
-    def per_graph(self, pred: torch.Tensor, target: torch.Tensor, batch: Any) -> torch.Tensor:  # pragma: no cover
+    # ---- the overridable steps
+    def validate(self, pred: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+        """Targets stored flat (``[B]`` energies, Voigt-free ``[B, 9]`` stresses) are viewed in the prediction's shape;
+        a different element count is an error."""
+        if target.shape != pred.shape:
+            if target.numel() != pred.numel():
+                raise ValueError(f"loss term {self.name}: prediction has shape {tuple(pred.shape)}, target {tuple(target.shape)}")
+            target = target.reshape(pred.shape)
+        return target
+
+    def normalize(self, pred: torch.Tensor, target: torch.Tensor, batch: Any) -> tuple[torch.Tensor, torch.Tensor]:
+        return pred, target
+
+    def residual(self, pred: torch.Tensor, target: torch.Tensor, batch: Any) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
+
+    def graph_weights(self, batch: Any, ref: torch.Tensor) -> torch.Tensor | None:
+        """Optional weights of the graphs in the final average (default: every graph with a valid entry counts once)."""
+        return None
+
+    # ---- shared machinery
+    def _valid(self, pred: torch.Tensor, target: torch.Tensor, batch: Any) -> torch.Tensor | None:
+        valid = None
+        if self.level == "node" and pred.dim() >= 3:
+            counts = getattr(batch, "num_nodes_per_graph", None)
+            if counts is None:
+                raise KeyError(f"loss term {self.name}: padded [B, V_max, ...] tensors need batch.num_nodes_per_graph")
+            valid = padded_node_mask(counts, pred.shape[1]).reshape(pred.shape[:2] + (1,) * (pred.dim() - 2)).expand_as(pred)
+        if self.ignore_nonfinite:
+            finite = torch.isfinite(target)
+            valid = finite if valid is None else valid & finite
+        return valid
+
+    def _reduce(self, res: torch.Tensor, valid: torch.Tensor | None, batch: Any) -> torch.Tensor:
+        dense_nodes = self.level == "node" and res.dim() == 2
+        ones = torch.ones_like(res) if valid is None else valid.to(res.dtype)
+        if dense_nodes:
+            idx, b = batch.batch_idx.long(), int(batch.num_graphs)
+            tot = torch.zeros(b, dtype=res.dtype, device=res.device).index_add_(0, idx, res.sum(-1))
+            cnt = torch.zeros(b, dtype=res.dtype, device=res.device).index_add_(0, idx, ones.sum(-1))
+        else:
+            tot, cnt = res.reshape(res.shape[0], -1).sum(-1), ones.reshape(res.shape[0], -1).sum(-1)
+        per_graph = tot / cnt.clamp_min(1)
+        self.per_sample_loss = per_graph.detach()
+        if self.level == "node" and not getattr(self, "normalize_by_atom_count", True):
+            return tot.sum() / cnt.sum().clamp_min(1)  # one mean over every valid component of the batch
+        w = (cnt > 0).to(res.dtype)
+        gw = self.graph_weights(batch, res)
+        if gw is not None:
+            w = w * gw.reshape(-1).to(res.dtype)
+        return (per_graph * w).sum() / w.sum().clamp_min(torch.finfo(res.dtype).tiny)
 
     def __call__(self, predictions: dict, batch: Any, step: int = 0, epoch: int = 0) -> torch.Tensor:
         pred = predictions.get(self.prediction_key)
@@ -113,10 +209,24 @@ class BaseLossFunction:
             raise KeyError(f"loss term {self.name}: target '{self.target_key}' missing from the batch")
         if self.dtype is not None:
             pred, target = pred.to(self.dtype), target.to(self.dtype)
-        return self.per_graph(pred, target.to(pred.dtype).reshape(pred.shape), batch).mean()
+        pred, target = align_dtypes(pred, target, self.dtype_policy, f"loss term {self.name}")
+        target = self.validate(pred, target)
+        valid = self._valid(pred, target, batch)
+        if valid is not None:
+            target = torch.where(valid, target, pred.detach())  # an invalid entry has residual 0 and gradient 0
+        pred, target = self.normalize(pred, target, batch)
+        res = self.residual(pred, target, batch)
+        if valid is not None:
+            if valid.shape != res.shape:  # a per-row residual (vector norm) is valid when all its components are
+                valid = valid.all(-1, keepdim=True)
+            res = res * valid.to(res.dtype)
+        return self._reduce(res, valid, batch)
 
     def __add__(self, other: "BaseLossFunction | ComposedLossFunction") -> "ComposedLossFunction":
         return ComposedLossFunction([self]) + other
+
+    def __radd__(self, other: Any) -> "ComposedLossFunction | BaseLossFunction":
+        return self if other == 0 else ComposedLossFunction([self]).__add__(other)  # sum([...]) starts from 0
 
     def __mul__(self, factor: Any) -> "BaseLossFunction":
         import copy
@@ -131,10 +241,18 @@ class BaseLossFunction:
 
     __rmul__ = __mul__
 
+    def _options(self) -> dict[str, Any]:
+        return {}
+
     def to_spec(self) -> dict[str, Any]:
         w = self.weight.to_spec() if isinstance(self.weight, LossWeightSchedule) else self.weight
-        return {"cls": type(self).__name__, "target_key": self.target_key, "prediction_key": self.prediction_key,
-                "weight": w if not callable(w) else 1.0, "name": self.name}
+        spec = {"cls": type(self).__name__, "target_key": self.target_key, "prediction_key": self.prediction_key,
+                "weight": w if not callable(w) else 1.0, "name": self.name, **self._options()}
+        if self.ignore_nonfinite:
+            spec["ignore_nonfinite"] = True
+        if self.dtype_policy != "target_to_prediction":
+            spec["dtype_policy"] = self.dtype_policy
+        return spec
 
 
 def _huber(d: torch.Tensor, delta: float) -> torch.Tensor:
@@ -143,22 +261,38 @@ def _huber(d: torch.Tensor, delta: float) -> torch.Tensor:
 
 
 class EnergyMSELoss(BaseLossFunction):
-    """Squared error of the per-atom-normalised energy."""
+    """Squared error of the energy, per atom by default.  ``atom_weighted`` (needs ``per_atom``): graphs enter the batch
+    average in proportion to their atom counts, ``sum_i N_i (dE_i / N_i)^2 / sum_i N_i`` (the reduction of reference
+    ``terms.py:143-268``); default: every labelled graph counts once."""
 
-    def __init__(self, *a: Any, per_atom: bool = True, **k: Any) -> None:
+    def __init__(self, *a: Any, per_atom: bool = True, atom_weighted: bool = False, **k: Any) -> None:
         super().__init__(*a, **k)
-        self.per_atom = per_atom
+        if atom_weighted and not per_atom:
+            raise ValueError("atom_weighted=True needs per_atom=True")
+        self.per_atom, self.atom_weighted = per_atom, atom_weighted
 
-    def _norm(self, batch: Any, ref: torch.Tensor) -> torch.Tensor:
-        return batch.num_nodes_per_graph.to(ref.dtype).clamp_min(1).reshape(-1, 1) if self.per_atom else 1.0
+    def _counts(self, batch: Any, ref: torch.Tensor) -> torch.Tensor:
+        return node_counts(batch.num_nodes_per_graph).to(ref.dtype).clamp_min(1)
 
-    def per_graph(self, pred, target, batch):
-        return (((pred - target) / self._norm(batch, pred)) ** 2).reshape(pred.shape[0], -1).mean(-1)
+    def normalize(self, pred, target, batch):
+        if not self.per_atom:
+            return pred, target
+        n = self._counts(batch, pred).reshape((-1,) + (1,) * (pred.dim() - 1))
+        return pred / n, target / n
+
+    def graph_weights(self, batch, ref):
+        return self._counts(batch, ref) if self.atom_weighted else None
+
+    def residual(self, pred, target, batch):
+        return (pred - target) ** 2
+
+    def _options(self):
+        return {"per_atom": self.per_atom, **({"atom_weighted": True} if self.atom_weighted else {})}
 
 
 class EnergyMAELoss(EnergyMSELoss):
-    def per_graph(self, pred, target, batch):
-        return ((pred - target) / self._norm(batch, pred)).abs().reshape(pred.shape[0], -1).mean(-1)
+    def residual(self, pred, target, batch):
+        return (pred - target).abs()
 
 
 class EnergyHuberLoss(EnergyMSELoss):
@@ -166,15 +300,32 @@ class EnergyHuberLoss(EnergyMSELoss):
         super().__init__(*a, **k)
         self.delta = delta
 
-    def per_graph(self, pred, target, batch):
-        return _huber((pred - target) / self._norm(batch, pred), self.delta).reshape(pred.shape[0], -1).mean(-1)
+    def residual(self, pred, target, batch):
+        return _huber(pred - target, self.delta)
+
+    def _options(self):
+        return {**super()._options(), "delta": self.delta}
 
 
 class ForceMSELoss(BaseLossFunction):
-    default_key = "forces"
+    """Squared error of the force components.  Dense ``[V, 3]`` forces are grouped by ``batch.batch_idx``; padded
+    ``[B, V_max, 3]`` forces skip the padding rows named by ``batch.num_nodes_per_graph`` (counts ``[B]`` or a mask
+    ``[B, V_max]``).  ``normalize_by_atom_count=True``: mean per graph, then mean over graphs (graph-balanced);
+    ``False``: one mean over every valid component of the batch (reference ``terms.py:475-695``)."""
 
-    def per_graph(self, pred, target, batch):
-        return per_graph_mean((pred - target) ** 2, batch.batch_idx, batch.num_graphs)
+    default_key = "forces"
+    level = "node"
+    requires_eval_grad = True
+
+    def __init__(self, *a: Any, normalize_by_atom_count: bool = True, **k: Any) -> None:
+        super().__init__(*a, **k)
+        self.normalize_by_atom_count = bool(normalize_by_atom_count)
+
+    def residual(self, pred, target, batch):
+        return (pred - target) ** 2
+
+    def _options(self):
+        return {} if self.normalize_by_atom_count else {"normalize_by_atom_count": False}
 
 
 class ForceHuberLoss(ForceMSELoss):
@@ -182,20 +333,26 @@ class ForceHuberLoss(ForceMSELoss):
         super().__init__(*a, **k)
         self.delta = delta
 
-    def per_graph(self, pred, target, batch):
-        return per_graph_mean(_huber(pred - target, self.delta), batch.batch_idx, batch.num_graphs)
+    def residual(self, pred, target, batch):
+        return _huber(pred - target, self.delta)
+
+    def _options(self):
+        return {**super()._options(), "delta": self.delta}
 
 
 class ForceL2NormLoss(ForceMSELoss):
-    def per_graph(self, pred, target, batch):
-        return per_graph_mean((pred - target).norm(dim=-1, keepdim=True), batch.batch_idx, batch.num_graphs)
+    """Mean length of the force error vector (not squared): less sensitive to a few atoms with large forces."""
+
+    def residual(self, pred, target, batch):
+        return (pred - target).norm(dim=-1, keepdim=True)
 
 
 class StressMSELoss(BaseLossFunction):
     default_key = "stress"
+    requires_eval_grad = True
 
-    def per_graph(self, pred, target, batch):
-        return frobenius_mse(pred, target)
+    def residual(self, pred, target, batch):
+        return (pred - target) ** 2
 
 
 class StressHuberLoss(StressMSELoss):
@@ -203,8 +360,11 @@ class StressHuberLoss(StressMSELoss):
         super().__init__(*a, **k)
         self.delta = delta
 
-    def per_graph(self, pred, target, batch):
-        return _huber(pred - target, self.delta).reshape(pred.shape[0], -1).mean(-1)
+    def residual(self, pred, target, batch):
+        return _huber(pred - target, self.delta)
+
+    def _options(self):
+        return {"delta": self.delta}
 
 
 TERMS = {c.__name__: c for c in (EnergyMSELoss, EnergyMAELoss, EnergyHuberLoss, ForceMSELoss, ForceHuberLoss,
@@ -212,40 +372,144 @@ TERMS = {c.__name__: c for c in (EnergyMSELoss, EnergyMAELoss, EnergyHuberLoss, 
 
 
 class ComposedLossFunction:
-    def __init__(self, terms: list[BaseLossFunction]) -> None:
-        self.terms = list(terms)
+    """Weighted sum of terms.  The call returns ``{"total_loss": ..., "<term name>": detached value, ...}``.
+
+    ``normalize_weights=True`` divides the weights in force at ``(step, epoch)`` by their sum, so schedules steer the
+    RELATIVE share of the terms and the learning rate alone sets the scale (the reference's default,
+    ``composition.py:609-660``; here it is opt-in).  ``dtype_policy`` overrides the policy of every term for calls made
+    through this composition, without touching the term objects (they may be shared)."""
+
+    def __init__(self, terms: list[BaseLossFunction], normalize_weights: bool = False, dtype_policy: str | None = None) -> None:
+        flat: list[BaseLossFunction] = []
+        for t in terms:
+            if isinstance(t, ComposedLossFunction):
+                flat.extend(t.terms)
+            elif isinstance(t, BaseLossFunction):
+                flat.append(t)
+            else:
+                raise TypeError(f"loss terms must be BaseLossFunction or ComposedLossFunction, got {type(t).__name__}")
+        if not flat:
+            raise ValueError("a composed loss needs at least one term")
+        names = [t.name for t in flat]
+        if len(set(names)) != len(names):
+            dup = sorted({n for n in names if names.count(n) > 1})
+            raise ValueError(f"loss term names must be unique (they key the output dictionary): {dup}; pass name=...")
+        if dtype_policy is not None and dtype_policy not in DTYPE_POLICIES:
+            raise ValueError(f"dtype_policy must be one of {DTYPE_POLICIES} or None, got {dtype_policy!r}")
+        self.terms = flat
+        self.normalize_weights = bool(normalize_weights)
+        self.dtype_policy = dtype_policy
 
     def __add__(self, other: "BaseLossFunction | ComposedLossFunction") -> "ComposedLossFunction":
         extra = other.terms if isinstance(other, ComposedLossFunction) else [other]
-        return ComposedLossFunction(self.terms + list(extra))
+        return ComposedLossFunction(self.terms + list(extra), self.normalize_weights, self.dtype_policy)
+
+    def __radd__(self, other: Any) -> "ComposedLossFunction":
+        return self if other == 0 else self.__add__(other)
 
     def __mul__(self, factor: Any) -> "ComposedLossFunction":
-        return ComposedLossFunction([t * factor for t in self.terms])
+        return ComposedLossFunction([t * factor for t in self.terms], self.normalize_weights, self.dtype_policy)
 
     __rmul__ = __mul__
 
     def required_predictions(self) -> set[str]:
         return {t.prediction_key for t in self.terms}
 
+    @property
+    def requires_eval_grad(self) -> bool:
+        """Some term compares a derivative of the model output: evaluation must keep autograd on."""
+        return any(bool(t.requires_eval_grad) for t in self.terms)
+
+    def weights_at(self, step: int = 0, epoch: int = 0) -> dict[str, float]:
+        w = {t.name: t.weight_at(step, epoch) for t in self.terms}
+        if self.normalize_weights:
+            total = sum(w.values())
+            if total == 0.0:
+                raise ValueError(f"loss weights sum to zero at step {step}, epoch {epoch}: {w}")
+            w = {k: v / total for k, v in w.items()}
+        return w
+
     def __call__(self, predictions: dict, batch: Any, step: int = 0, epoch: int = 0) -> dict[str, torch.Tensor]:
         out: dict[str, torch.Tensor] = {}
         total = None
+        weights = self.weights_at(step, epoch)
         for t in self.terms:
-            val = t(predictions, batch, step, epoch)
+            if self.dtype_policy is not None and t.dtype_policy != self.dtype_policy:
+                keep, t.dtype_policy = t.dtype_policy, self.dtype_policy
+                try:
+                    val = t(predictions, batch, step, epoch)
+                finally:
+                    t.dtype_policy = keep
+            else:
+                val = t(predictions, batch, step, epoch)
             out[t.name] = val.detach()
-            w = t.weight_at(step, epoch)
+            w = weights[t.name]
             total = val * w if total is None else total + val * w
         out["total_loss"] = total
         return out
+
+    def per_sample_losses(self) -> dict[str, torch.Tensor]:
+        """Detached per-graph values of the last call, by term (for error histograms and outlier reports)."""
+        return {t.name: t.per_sample_loss for t in self.terms if t.per_sample_loss is not None}
 
     def to_spec(self) -> list[dict[str, Any]]:
         return [t.to_spec() for t in self.terms]
 
     @classmethod
-    def from_spec(cls, spec: list[dict[str, Any]]) -> "ComposedLossFunction":
+    def from_spec(cls, spec: list[dict[str, Any]], **kwargs: Any) -> "ComposedLossFunction":
         terms = []
         for s in spec:
             kw = {k: v for k, v in s.items() if k != "cls"}
             kw["weight"] = schedule_from_spec(kw.get("weight", 1.0))
             terms.append(TERMS[s["cls"]](**kw))
-        return cls(terms)
+        return cls(terms, **kwargs)
+
+
+def as_composed_loss(loss: "BaseLossFunction | ComposedLossFunction | list") -> ComposedLossFunction:
+    """A single term, a list of terms / spec dictionaries or a composition -> a composition."""
+    if isinstance(loss, ComposedLossFunction):
+        return loss
+    if isinstance(loss, BaseLossFunction):
+        return ComposedLossFunction([loss])
+    if isinstance(loss, (list, tuple)):
+        if loss and all(isinstance(x, dict) for x in loss):
+            return ComposedLossFunction.from_spec(list(loss))
+        return ComposedLossFunction(list(loss))
+    raise TypeError(f"cannot build a loss from {type(loss).__name__}")
+
+
+def loss_target_keys(loss: "BaseLossFunction | ComposedLossFunction") -> tuple[str, ...]:
+    """Batch attributes the loss reads as labels, in term order without repeats."""
+    seen: dict[str, None] = {}
+    for t in as_composed_loss(loss).terms:
+        seen.setdefault(t.target_key)
+    return tuple(seen)
+
+
+def assemble_loss_targets(loss: "BaseLossFunction | ComposedLossFunction", batch: Any, strict: bool = True) -> dict[str, torch.Tensor]:
+    """The labels of ``batch`` the loss needs (reference ``composition.py:1113-1173``).  ``strict``: a missing label
+    raises with the list of what the batch does carry; otherwise it is left out (pair with ``ignore_nonfinite`` terms
+    only when the collate step fills missing labels with NaN)."""
+    out: dict[str, torch.Tensor] = {}
+    for key in loss_target_keys(loss):
+        value = getattr(batch, key, None)
+        if value is None:
+            if strict:
+                have = sorted(k for k in getattr(batch, "keys", lambda: [])())
+                raise KeyError(f"batch carries no label '{key}' (fields: {have})")
+            continue
+        out[key] = value
+    return out
+
+
+def compute_supervised_loss(model_fn: Callable[[Any], dict], loss: "BaseLossFunction | ComposedLossFunction", batch: Any,
+                            step: int = 0, epoch: int = 0) -> tuple[dict[str, torch.Tensor], dict]:
+    """One supervised evaluation: check the labels, run the model, check that it produced what the terms compare,
+    evaluate.  Returns ``(losses, predictions)``."""
+    composed = as_composed_loss(loss)
+    assemble_loss_targets(composed, batch)
+    preds = model_fn(batch)
+    missing = sorted(composed.required_predictions() - set(preds))
+    if missing:
+        raise KeyError(f"the model returned {sorted(preds)}, the loss also needs {missing}")
+    return composed(preds, batch, step=step, epoch=epoch), preds

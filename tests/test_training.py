@@ -364,3 +364,122 @@ def test_finetune_from_pretrained_checkpoint_inherits_weights_only(tmp_path):
         idx_file = sorted((tmp_path / "src" / "strategy" / "checkpoints").glob("*.json"))[-1]
         idx_file.write_text(json.dumps(meta))
         FineTuningStrategy.from_pretrained_checkpoint(tmp_path / "src", use_original_opt_class=True, num_steps=1, devices=["cpu"])
+
+
+class _Labels:
+    """Minimal stand-in for a batch: the attributes the loss terms read."""
+
+    def __init__(self, **fields):
+        self.__dict__.update(fields)
+
+    def keys(self):
+        return list(self.__dict__)
+
+
+def _mixed_batch():
+    return _Labels(num_graphs=3, batch_idx=torch.tensor([0, 0, 1, 1, 1, 2]), num_nodes_per_graph=torch.tensor([2, 3, 1]),
+                   energy=torch.tensor([1.0, float("nan"), 3.0]),
+                   forces=torch.arange(18, dtype=torch.float32).reshape(6, 3) / 10)
+
+
+def test_loss_terms_skip_missing_labels_in_value_and_gradient():
+    from nvalchemi_toolkit_b200.training.losses import EnergyMSELoss, ForceL2NormLoss, ForceMSELoss
+
+    b = _mixed_batch()
+    b.forces[2:5] = float("nan")  # graph 1 carries no force labels either
+    pe = torch.tensor([[1.5], [2.0], [2.0]], requires_grad=True)
+    pf = torch.zeros(6, 3, requires_grad=True)
+    loss = EnergyMSELoss(ignore_nonfinite=True) + ForceMSELoss(ignore_nonfinite=True) + ForceL2NormLoss(ignore_nonfinite=True, name="l2")
+    out = loss({"energy": pe, "forces": pf}, b)
+    out["total_loss"].backward()
+    # energy per atom: graphs 0 and 2 -> ((0.5/2)^2 + (1/1)^2) / 2
+    assert float(out["EnergyMSELoss[energy]"]) == pytest.approx((0.0625 + 1.0) / 2)
+    f = b.forces
+    want_f = (f[:2].pow(2).mean() + f[5:].pow(2).mean()) / 2
+    assert float(out["ForceMSELoss[forces]"]) == pytest.approx(float(want_f), rel=1e-6)
+    want_l2 = (f[:2].norm(dim=-1).mean() + f[5:].norm(dim=-1).mean()) / 2
+    assert float(out["l2"]) == pytest.approx(float(want_l2), rel=1e-6)
+    assert torch.isfinite(pe.grad).all() and float(pe.grad[1].abs()) == 0.0
+    assert torch.isfinite(pf.grad).all() and float(pf.grad[2:5].abs().sum()) == 0.0
+    assert loss.per_sample_losses()["ForceMSELoss[forces]"].tolist()[1] == 0.0
+    # every label missing: the value is 0, not NaN
+    b.energy = torch.full((3,), float("nan"))
+    assert float(EnergyMSELoss(ignore_nonfinite=True)({"energy": pe.detach()}, b)) == 0.0
+    # without the option a missing label poisons the value (the default stays strict about data)
+    assert not torch.isfinite(EnergyMSELoss()({"energy": pe.detach()}, b))
+
+
+def test_force_loss_reductions_dense_and_padded_agree():
+    from nvalchemi_toolkit_b200.training.losses import ForceMSELoss
+
+    b = _mixed_batch()
+    g = torch.Generator().manual_seed(0)
+    pf = torch.randn(6, 3, generator=g)
+    balanced = ForceMSELoss()({"forces": pf}, b)
+    d2 = (pf - b.forces) ** 2
+    assert float(balanced) == pytest.approx(float((d2[:2].mean() + d2[2:5].mean() + d2[5:].mean()) / 3), rel=1e-6)
+    flat = ForceMSELoss(normalize_by_atom_count=False)({"forces": pf}, b)
+    assert float(flat) == pytest.approx(float(d2.mean()), rel=1e-6)
+    # the same data padded to [B, V_max, 3]; padding rows hold garbage that must not count
+    pad_p, pad_t = torch.full((3, 3, 3), 7.0), torch.full((3, 3, 3), -5.0)
+    for gi, (lo, hi) in enumerate([(0, 2), (2, 5), (5, 6)]):
+        pad_p[gi, : hi - lo], pad_t[gi, : hi - lo] = pf[lo:hi], b.forces[lo:hi]
+    for counts in (torch.tensor([2, 3, 1]), torch.tensor([[1, 1, 0], [1, 1, 1], [1, 0, 0]], dtype=torch.bool)):
+        pb = _Labels(num_graphs=3, num_nodes_per_graph=counts, forces=pad_t)
+        assert float(ForceMSELoss()({"forces": pad_p}, pb)) == pytest.approx(float(balanced), rel=1e-6)
+        assert float(ForceMSELoss(normalize_by_atom_count=False)({"forces": pad_p}, pb)) == pytest.approx(float(flat), rel=1e-6)
+
+
+def test_energy_atom_weighted_reduction_and_dtype_policies():
+    from nvalchemi_toolkit_b200.training.losses import ComposedLossFunction, EnergyMSELoss
+
+    b = _mixed_batch()
+    b.energy = torch.tensor([1.0, 2.0, 3.0])
+    pe = torch.tensor([[2.0], [5.0], [3.5]])
+    n = torch.tensor([2.0, 3.0, 1.0])
+    per_atom_sq = ((pe[:, 0] - b.energy) / n) ** 2
+    assert float(EnergyMSELoss(atom_weighted=True)({"energy": pe}, b)) == pytest.approx(float((n * per_atom_sq).sum() / n.sum()))
+    assert float(EnergyMSELoss()({"energy": pe}, b)) == pytest.approx(float(per_atom_sq.mean()))
+    with pytest.raises(ValueError, match="per_atom"):
+        EnergyMSELoss(per_atom=False, atom_weighted=True)
+    with pytest.raises(ValueError, match="shape"):
+        EnergyMSELoss()({"energy": pe[:2]}, b)
+    b.energy = b.energy.double()
+    with pytest.raises(TypeError, match="dtype_policy"):
+        EnergyMSELoss(dtype_policy="strict")({"energy": pe}, b)
+    strict = EnergyMSELoss(dtype_policy="strict")
+    out = ComposedLossFunction([strict], dtype_policy="prediction_to_target")({"energy": pe}, b)
+    assert out["total_loss"].dtype == torch.float64 and strict.dtype_policy == "strict"
+
+
+def test_composed_loss_weight_normalisation_targets_and_supervised_helper():
+    from nvalchemi_toolkit_b200.training import (as_composed_loss, assemble_loss_targets, compute_supervised_loss,
+                                                 loss_target_keys)
+    from nvalchemi_toolkit_b200.training.losses import ComposedLossFunction, EnergyMSELoss, ForceMSELoss, LinearWeight
+
+    e, f = EnergyMSELoss(weight=1.0), ForceMSELoss(weight=LinearWeight(1.0, 3.0, 10))
+    loss = ComposedLossFunction([e, f], normalize_weights=True)
+    assert loss.weights_at(0) == {e.name: 0.5, f.name: 0.5}
+    assert loss.weights_at(10) == {e.name: 0.25, f.name: 0.75}
+    with pytest.raises(ValueError, match="sum to zero"):
+        ComposedLossFunction([EnergyMSELoss(weight=0.0)], normalize_weights=True).weights_at(0)
+    with pytest.raises(ValueError, match="unique"):
+        ComposedLossFunction([EnergyMSELoss(), EnergyMSELoss()])
+    nested = ComposedLossFunction([ComposedLossFunction([e]), f])
+    assert [t.name for t in nested.terms] == [e.name, f.name] and nested.requires_eval_grad
+    assert not as_composed_loss(e).requires_eval_grad
+    assert loss_target_keys(sum([e, f, EnergyMSELoss(name="again")])) == ("energy", "forces")
+    b = _mixed_batch()
+    b.energy = torch.tensor([1.0, 2.0, 3.0])
+    assert set(assemble_loss_targets(loss, b)) == {"energy", "forces"}
+    del b.__dict__["forces"]
+    with pytest.raises(KeyError, match="forces"):
+        assemble_loss_targets(loss, b)
+    assert set(assemble_loss_targets(loss, b, strict=False)) == {"energy"}
+    with pytest.raises(KeyError, match="also needs"):
+        compute_supervised_loss(lambda batch: {"energy": torch.zeros(3, 1)}, nested, _mixed_batch())
+    losses, preds = compute_supervised_loss(lambda batch: {"energy": torch.zeros(3, 1)}, e, b)
+    assert set(preds) == {"energy"} and float(losses["total_loss"]) > 0
+    round_trip = ComposedLossFunction.from_spec(ComposedLossFunction([EnergyMSELoss(atom_weighted=True, ignore_nonfinite=True),
+                                                                      ForceMSELoss(normalize_by_atom_count=False)]).to_spec())
+    assert round_trip.terms[0].atom_weighted and round_trip.terms[0].ignore_nonfinite and not round_trip.terms[1].normalize_by_atom_count
