@@ -5,10 +5,13 @@ from nvalchemi_toolkit_b200.hooks.reporting._core import (DEFAULT_REPORT_STAGES,
                                                          ScalarSnapshot, collect_scalars, extract_dynamics_scalars,
                                                          extract_loss_scalars, extract_optimizer_lr_scalars,
                                                          extract_progress_scalars, reduce_scalars_across_ranks)
+from nvalchemi_toolkit_b200.hooks.reporting._layouts import (BaseDashboardLayout, CompactLayout, DynamicsLayout,
+                                                            TrainingLayout, resolve_layout, text_plot)
 from nvalchemi_toolkit_b200.hooks.reporting._reporters import (JSONLReporter, RichLayout, RichReporter,
                                                               TensorBoardReporter, sparkline)
 
 __all__ = ["DEFAULT_REPORT_STAGES", "Reporter", "ReporterMessage", "ReportingErrorPolicy", "ReportingOrchestrator",
            "ReportingState", "ScalarSnapshot", "collect_scalars", "extract_dynamics_scalars", "extract_loss_scalars",
            "extract_optimizer_lr_scalars", "extract_progress_scalars", "reduce_scalars_across_ranks", "JSONLReporter",
-           "RichLayout", "RichReporter", "TensorBoardReporter", "sparkline"]
+           "RichLayout", "RichReporter", "TensorBoardReporter", "sparkline", "BaseDashboardLayout", "CompactLayout",
+           "DynamicsLayout", "TrainingLayout", "resolve_layout", "text_plot"]

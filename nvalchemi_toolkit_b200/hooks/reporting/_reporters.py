@@ -14,6 +14,7 @@ from typing import Any, Mapping, Sequence
 from nvalchemi_toolkit_b200._optional import OptionalDependency
 from nvalchemi_toolkit_b200.hooks.reporting._core import (ReportingState, ScalarCallback, ScalarSnapshot, collect_scalars,
                                                          reduce_scalars_across_ranks)
+from nvalchemi_toolkit_b200.hooks.reporting._layouts import resolve_layout, text_plot
 
 _BARS = " ▁▂▃▄▅▆▇█"
 
@@ -32,12 +33,6 @@ class RichLayout(str, Enum):
     TRAIN = "train"
     DYNAMICS = "dynamics"
     COMPACT = "compact"
-
-
-_LAYOUT_KEYS = {RichLayout.TRAIN: ("loss/", "lr/", "validation/", "progress/"),
-                RichLayout.DYNAMICS: ("dynamics/", "progress/"), RichLayout.COMPACT: ("loss/total", "dynamics/fmax", "progress/step")}
-_LAYOUT_PLOTS = {RichLayout.TRAIN: ("loss/total",), RichLayout.DYNAMICS: ("dynamics/fmax", "dynamics/temperature"),
-                 RichLayout.COMPACT: ()}
 
 
 class _ScalarReporterBase:
@@ -77,7 +72,10 @@ class RichReporter(_ScalarReporterBase):
         super().__init__(custom_scalars, include_losses, include_optimizer_lrs, include_dynamics_scalars, rank_reduction,
                          rank_zero_only)
         self.title, self.precision, self.max_scalars = title, precision, max_scalars
-        self.layout = RichLayout(layout) if layout is not None else RichLayout.AUTO
+        # a name (RichLayout / str), None = auto, or any object with select_rows() / select_plots()
+        self.layout = RichLayout(layout) if isinstance(layout, str) else (RichLayout.AUTO if layout is None else layout)
+        if not isinstance(self.layout, RichLayout):
+            resolve_layout(self.layout)  # fails now, not at the first report
         self.plot_keys, self.max_plots, self.plot_height = plot_keys, max_plots, plot_height
         self.refresh_per_second, self.console, self.screen, self.transient = refresh_per_second, console, screen, transient
         self.strict_layout = strict_layout
@@ -86,19 +84,20 @@ class RichReporter(_ScalarReporterBase):
         self._live: Any = None
         self.last_snapshot: ScalarSnapshot | None = None
 
-    def _resolve_layout(self, snap: ScalarSnapshot) -> RichLayout:
-        if self.layout != RichLayout.AUTO:
-            return self.layout
-        return RichLayout.TRAIN if any(k.startswith("loss/") for k in snap.scalars) else RichLayout.DYNAMICS
+    def _resolve_layout(self, snap: ScalarSnapshot) -> Any:
+        return resolve_layout(self.layout, snap.scalars)
 
-    def _select(self, snap: ScalarSnapshot, layout: RichLayout) -> list[tuple[str, float]]:
-        prefixes = _LAYOUT_KEYS[layout]
-        chosen = [(k, v) for k, v in sorted(snap.scalars.items()) if any(k.startswith(p) for p in prefixes)]
-        extra = [(k, v) for k, v in sorted(snap.scalars.items()) if (k, v) not in chosen]
-        if self.strict_layout:
-            extra = []
-        rows = chosen + extra
-        return rows[: self.max_scalars] if self.max_scalars is not None else rows
+    def _select(self, snap: ScalarSnapshot, layout: Any) -> list[tuple[str, float]]:
+        return layout.select_rows(snap.scalars, self.max_scalars, self.strict_layout)
+
+    def _plot_panel(self, key: str, layout: Any, width: int) -> Any:
+        from rich.panel import Panel
+
+        h = list(self.history[key])
+        log = bool(getattr(layout, "is_log", lambda *_: False)(key, h))
+        rows = text_plot(h, width=width, height=self.plot_height, precision=4, log=log)
+        title = f"{key}  last {h[-1]:.{self.precision}g}  min {min(h):.4g}  max {max(h):.4g}" + ("  (log)" if log else "")
+        return Panel("\n".join(rows), title=title, height=self.plot_height + 2)
 
     def render(self, snap: ScalarSnapshot, state: ReportingState) -> Any:
         from rich.console import Group
@@ -106,23 +105,41 @@ class RichReporter(_ScalarReporterBase):
         from rich.table import Table
 
         layout = self._resolve_layout(snap)
-        table = Table(title=f"{self.title}  step {snap.step}" + (f"  epoch {snap.epoch}" if snap.epoch is not None else ""),
-                      expand=True)
+        head = f"{self.title} ({getattr(layout, 'name', 'custom')})  step {snap.step}"
+        if snap.epoch is not None:
+            head += f"  epoch {snap.epoch}"
+        table = Table(title=head, caption=getattr(layout, "latest_title", None), expand=True)
         table.add_column("scalar")
         table.add_column("value", justify="right")
         table.add_column("history")
         for k, v in self._select(snap, layout):
             table.add_row(k, f"{v:.{self.precision}g}", sparkline(self.history.get(k, ()), 30))
         parts: list[Any] = [table]
-        keys = list(self.plot_keys) if self.plot_keys is not None else list(_LAYOUT_PLOTS[layout])
-        for k in keys[: self.max_plots]:
-            if k in self.history and len(self.history[k]) > 1:
-                h = list(self.history[k])
-                parts.append(Panel(sparkline(h, 80), title=f"{k}  min {min(h):.4g}  max {max(h):.4g}", height=3))
+        width = 80
+        if self.console is not None and getattr(self.console, "width", None):
+            width = max(20, int(self.console.width) - 20)
+        for k in layout.select_plots(self.history, self.plot_keys, self.max_plots, self.strict_layout):
+            parts.append(self._plot_panel(k, layout, width))
         recent = [m for m in list(state.messages)[-3:]]
         if recent:
             parts.append(Panel("\n".join(f"[{m.level}] {m.text}" for m in recent), title="messages"))
         return Group(*parts)
+
+    def preview(self, layout: Any = None, n: int = 120) -> Any:
+        """Static dashboard drawn from the layout's synthetic curves: what the live view will look like, without a run
+        (documentation, choosing ``plot_keys`` / ``plot_height``).  The reporter's own history is left untouched."""
+        chosen = resolve_layout(layout if layout is not None else (self.layout if self.layout != RichLayout.AUTO else "train"))
+        curves = chosen.preview_history(n)
+        keep_history, keep_layout = self.history, self.layout
+        self.history = {k: deque(v, maxlen=max(self._history_size, n)) for k, v in curves.items()}
+        self.layout = chosen
+        try:
+            snap = ScalarSnapshot(step=n - 1, epoch=getattr(chosen, "preview_epoch", None),
+                                  stage=getattr(chosen, "preview_stage", "AFTER_STEP"),
+                                  scalars={k: v[-1] for k, v in curves.items()})
+            return self.render(snap, ReportingState())
+        finally:
+            self.history, self.layout = keep_history, keep_layout
 
     def __enter__(self) -> "RichReporter":
         if self._is_writer_rank():

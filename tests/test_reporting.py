@@ -128,3 +128,60 @@ def test_cross_rank_scalar_reduction_unions_keys():
     for r in range(2):
         mean, mx = res[r]
         assert mean == {"a": 1.5, "only0": 5.0, "only1": 9.0} and mx == {"a": 2.0, "only0": 5.0, "only1": 9.0}
+
+
+def test_text_plot_rows_levels_and_log_scale():
+    from nvalchemi_toolkit_b200.hooks.reporting import text_plot
+
+    rows = text_plot([1, 2, 3, 4, 5, 4, 3, 2, 1], width=9, height=3)
+    assert len(rows) == 3 and rows[0].startswith("5 ┤") and rows[-1].startswith("1 ┤")
+    cells = [r.split("┤")[1] for r in rows]
+    assert all(len(c) == 9 for c in cells)
+    assert cells[0][4] == "█" and cells[0][0] == " " and cells[2][4] == "█"  # the peak fills all rows, the ends only the bottom
+    assert text_plot([], height=4) == [] and text_plot([float("nan")], height=4) == []
+    # more points than columns: resampled to the width, the newest point is kept
+    long = text_plot(list(range(1000)), width=50, height=2)
+    assert len(long[0].split("┤")[1]) == 50 and long[0].startswith("999")
+    log = text_plot([1000.0, 100.0, 10.0, 1.0], width=4, height=3, log=True)
+    heights = [sum(1 for r in log if r.split("┤")[1][i] != " ") for i in range(4)]
+    assert heights == [3, 2, 1, 1] and log[0].startswith("1000") and log[-1].lstrip().startswith("1 ┤")
+
+
+def test_dashboard_layouts_select_rows_plots_and_preview():
+    from rich.console import Console
+
+    from nvalchemi_toolkit_b200.hooks.reporting import (BaseDashboardLayout, DynamicsLayout, RichReporter, TrainingLayout,
+                                                        resolve_layout)
+
+    scalars = {"progress/step": 3.0, "lr/group0": 1e-3, "loss/forces": 0.2, "loss/total": 0.5, "custom/x": 1.0}
+    t = TrainingLayout()
+    assert [k for k, _ in t.select_rows(scalars)] == ["loss/total", "loss/forces", "lr/group0", "progress/step", "custom/x"]
+    assert [k for k, _ in t.select_rows(scalars, strict=True)][-1] == "progress/step"
+    assert [k for k, _ in t.select_rows(scalars, max_scalars=2)] == ["loss/total", "loss/forces"]
+    hist = {"loss/total": [1.0, 0.5], "custom/x": [1.0, 2.0], "lr/group0": [1e-3], "progress/step": [0.0, 1.0]}
+    assert t.select_plots(hist, None, 3) == ["loss/total", "custom/x"]  # one-point and progress series are not plotted
+    assert t.select_plots(hist, ["custom/x", "missing"], 3) == ["custom/x"]
+    assert isinstance(resolve_layout(None, scalars), TrainingLayout)
+    assert isinstance(resolve_layout("auto", {"dynamics/fmax": 1.0}), DynamicsLayout)
+    with pytest.raises(ValueError, match="unknown layout"):
+        resolve_layout("fancy")
+    with pytest.raises(TypeError, match="select_rows"):
+        RichReporter(layout=object())
+
+    class EnergyOnly(BaseDashboardLayout):
+        name = "energy-only"
+        row_prefixes = ("dynamics/energy",)
+        preferred_plots = ("dynamics/energy",)
+
+        def preview_history(self, n=120):
+            return {"dynamics/energy": [float(-i) for i in range(n)], "dynamics/fmax": [1.0] * n}
+
+    console = Console(width=90, record=True, force_terminal=False)
+    rep = RichReporter(console=console, layout=EnergyOnly(), plot_height=4, strict_layout=True)
+    rep.history["kept"] = [1.0]
+    console.print(rep.preview())
+    text = console.export_text()
+    assert "energy-only" in text and "dynamics/energy" in text and "dynamics/fmax" not in text
+    assert text.count("┤") == 4 and list(rep.history) == ["kept"]  # one plot of plot_height rows; own history untouched
+    console.print(RichReporter(console=console, plot_height=3, max_plots=2).preview("train"))
+    assert "loss/total" in console.export_text()
