@@ -26,11 +26,22 @@ class ValidationReport:
     spec_name: str
     suggestion: str | None = None
     attempts: list[dict[str, Any]] = field(default_factory=list)
+    #: the spec that reproduces the single-process result (declared, inferred or repaired); ``None`` when none did
+    spec: Any = None
+    #: what the trace of the single-process run saw, when the spec was inferred
+    trace: str | None = None
+    #: one sentence: what to do with this report
+    next_action: str = ""
+
+    def spec_dict(self) -> dict | None:
+        """The working spec as plain data (``MLIPSpec.from_dict`` restores it; ``MLIPSpec.save`` writes it to a file)."""
+        return None if self.spec is None else self.spec.to_dict()
 
     def __str__(self) -> str:
         head = "PASS" if self.ok else "FAIL"
         diffs = ", ".join(f"{k} {v:.3e}" for k, v in self.max_abs_diff.items())
         tail = f"; suggestion: {self.suggestion}" if self.suggestion else ""
+        tail += f"\n  next: {self.next_action}" if self.next_action else ""
         return f"[{head}] {self.spec_name} on {self.world_size} ranks: {diffs}{tail}"
 
 
@@ -110,13 +121,32 @@ def _diff(ref: dict, res: dict, keys: tuple[str, ...]) -> dict[str, float]:
 
 def trace_and_validate(model_factory: Callable, batch_factory: Callable, world_size: int = 2, *, cutoff: float,
                        skin: float = 0.0, spec: Any = None, atol: float = 1e-6, port: int = 29733,
-                       keys: tuple[str, ...] = ("energy", "forces", "stress"), auto_fix: bool = True) -> ValidationReport:
-    """``model_factory`` / ``batch_factory`` must be importable top-level callables (they run in spawned processes)."""
+                       keys: tuple[str, ...] = ("energy", "forces", "stress"), auto_fix: bool = True,
+                       infer: bool | None = None) -> ValidationReport:
+    """``model_factory`` / ``batch_factory`` must be importable top-level callables (they run in spawned processes).
+
+    The spec under test is ``spec``, else the one the model declares (``distribution_spec()``), else one inferred from
+    a trace of the single-process run (:func:`~nvalchemi_toolkit_b200.distributed.infer_spec.infer_spec`).  ``infer=True``
+    always traces and uses the declared spec only as a prior (its non-default fields win)."""
+    from nvalchemi_toolkit_b200.distributed.infer_spec import infer_spec
     from nvalchemi_toolkit_b200.distributed.spec import Consolidation
 
     model = model_factory()
     ref = _reference(model, batch_factory())
-    base = spec if spec is not None else model.distribution_spec()
+    declared = spec
+    if declared is None and hasattr(model, "distribution_spec"):
+        try:
+            declared = model.distribution_spec()
+        except NotImplementedError:
+            declared = None
+    trace_text = None
+    if infer or (infer is None and declared is None):
+        base, summary = infer_spec(model, batch_factory(), prior=declared)
+        trace_text = summary.describe()
+    elif declared is None:
+        raise ValueError("the model declares no distribution spec: pass spec=... or allow inference (infer=None / True)")
+    else:
+        base = declared
     cfg = {"cutoff": cutoff, "skin": skin}
     attempts = []
 
@@ -127,12 +157,16 @@ def trace_and_validate(model_factory: Callable, batch_factory: Callable, world_s
         attempts.append({"label": label, "ok": ok, "diff": d, "atoms_with_missing_neighbors": missing})
         return ok, d
 
-    ok, d = attempt(base, "declared spec", port)
+    ok, d = attempt(base, "inferred spec" if trace_text is not None else "declared spec", port)
     suggestion = None
+    working = base if ok else None
     if not ok and auto_fix:
         fixes = [(replace(base, message_passes=base.message_passes + 1), f"message_passes={base.message_passes + 1} (deeper halo)")]
         other = Consolidation.WEIGHTED_ENERGY if base.consolidation == Consolidation.DIRECT_MASKED else Consolidation.DIRECT_MASKED
         fixes.append((replace(base, consolidation=other), f"consolidation={other.value}"))
+        if not base.refresh_per_layer:
+            fixes.append((replace(base, refresh_per_layer=True),
+                          "refresh_per_layer=True (ghost rows refreshed before every gather, sums over owned rows only)"))
         for i, (s, label) in enumerate(fixes):
             try:
                 fixed, _ = attempt(s, label, port + 1 + i)
@@ -140,9 +174,19 @@ def trace_and_validate(model_factory: Callable, batch_factory: Callable, world_s
                 attempts.append({"label": label, "ok": False, "error": repr(exc)})
                 continue
             if fixed:
-                suggestion = label
+                suggestion, working = label, s
                 break
-    return ValidationReport(ok, d, world_size, base.name, suggestion, attempts)
+    if ok:
+        action = ("use the inferred spec: return it from the wrapper's distribution_spec() or save it with "
+                  "report.spec.save(path)") if trace_text is not None else "nothing to do: the declared spec reproduces the single-process result"
+    elif working is not None:
+        action = f"change the spec: {suggestion}; the repaired spec is report.spec"
+    else:
+        missing = max((a.get("atoms_with_missing_neighbors", 0) or 0) for a in attempts)
+        action = (f"{missing} owned atoms miss neighbours in their sub-domain: increase the ghost depth (cutoff / skin / "
+                  "message_passes)" if missing else
+                  "no automatic repair matched: run layer_diff(...) to find the first layer whose owned rows deviate")
+    return ValidationReport(ok, d, world_size, base.name, suggestion, attempts, working, trace_text, action)
 
 
 # ---- layer-by-layer comparison (reference ``nvalchemi/distributed/validate/layer_diagnostics.py``) ---------------

@@ -282,3 +282,42 @@ def test_layer_diff_locates_the_first_deviating_layer():
     by_name = {r["module"]: r["ok"] for r in bad}
     assert by_name["net.emb"] and by_name["net.mix.0"]        # inputs of the first aggregation are still exact
     assert not by_name["net.mix.2"] and not by_name["net.out"]  # stale ghost rows have reached the owned atoms
+
+
+def _undeclared_mpnn():
+    m = _mpnn_wrapper()
+    m.distribution_spec = lambda strategy=None: None
+    return m
+
+
+def test_spec_inferred_from_a_trace_counts_message_passes_and_validates():
+    """No declared spec: the trace of one single-process forward counts three neighbour aggregations on the way to the
+    energy, sees the model differentiate internally, and the spec built from that reproduces the forces on two ranks."""
+    from nvalchemi_toolkit_b200.distributed.infer_spec import infer_spec
+    from nvalchemi_toolkit_b200.distributed.spec import Consolidation, MLIPSpec
+    from nvalchemi_toolkit_b200.distributed.validate import trace_and_validate
+
+    spec, summary = infer_spec(_undeclared_mpnn(), _batch_factory())
+    assert spec.message_passes == 3 and summary.node_scatters == 3 and summary.system_reductions == 1
+    assert summary.deep_gathers == 2 and summary.used_autograd           # layers 2 and 3 read aggregated features
+    assert spec.consolidation == Consolidation.WEIGHTED_ENERGY and spec.node_outputs == ("forces",)
+    assert spec.extensive_outputs == ("energy",)
+    # a declared field wins over the trace, the rest is filled in
+    prior = MLIPSpec("mine", refresh_per_layer=True)
+    merged, _ = infer_spec(_undeclared_mpnn(), _batch_factory(), prior=prior)
+    assert merged.name == "mine" and merged.refresh_per_layer and merged.message_passes == 3
+    assert spec.refresh_per_layer and "owned-only reductions" in spec.notes  # the model sums over atoms itself
+    rep = trace_and_validate(_undeclared_mpnn, _batch_factory, 2, cutoff=3.0, port=29687, atol=1e-8)
+    assert rep.ok and rep.attempts[0]["label"] == "inferred spec" and "3 message pass" in rep.trace
+    assert "inferred spec" in rep.next_action and MLIPSpec.from_dict(rep.spec_dict()).message_passes == 3
+
+
+def test_opaque_neighbour_operator_is_given_one_message_pass():
+    from nvalchemi_toolkit_b200.distributed.infer_spec import infer_spec
+    from nvalchemi_toolkit_b200.models.lj import LennardJonesModelWrapper
+    from tests.helpers import fcc_supercell
+
+    model = LennardJonesModelWrapper(epsilon=0.01, sigma=2.3, cutoff=5.0)
+    batch = Batch.from_data_list([fcc_supercell(3, a=3.61, z=29, noise=0.05, seed=1)])
+    spec, summary = infer_spec(model, batch)
+    assert spec.message_passes == 1 and "opaque operator" in spec.notes and "energy" in spec.extensive_outputs
