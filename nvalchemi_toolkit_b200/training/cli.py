@@ -77,6 +77,9 @@ class TrainingJobSpec(BaseModel):
     data: DataSpec
     loss: list[dict[str, Any]] = Field(default_factory=lambda: [
         {"cls": "EnergyMSELoss", "weight": 1.0}, {"cls": "ForceMSELoss", "weight": 10.0}])
+    #: dtype policy applied to every loss term (``None``: each term's own) and weight normalisation of the composition
+    loss_dtype_policy: str | None = None
+    normalize_loss_weights: bool = False
     optimizer: OptimizerSpec = Field(default_factory=OptimizerSpec)
     num_epochs: int | None = None
     num_steps: int | None = None
@@ -118,14 +121,57 @@ class TrainingJobSpec(BaseModel):
             path.write_text(json.dumps(data, indent=2))
 
 
-def template_spec() -> TrainingJobSpec:
+MODEL_TEMPLATES: dict[str, dict[str, Any]] = {
+    "mace": {"cls": "nvalchemi_toolkit_b200.models.mace.MACEWrapper",
+             "kwargs": {"atomic_numbers": [1, 6, 8], "channels": 64, "r_max": 5.0}, "cutoff": 5.0},
+    "aimnet2": {"cls": "nvalchemi_toolkit_b200.models.aimnet2.AIMNet2Wrapper", "kwargs": {}, "cutoff": 5.0},
+    "demo": {"cls": "nvalchemi_toolkit_b200.models.demo.DemoModelWrapper", "kwargs": {}, "cutoff": None},
+    "custom": {"cls": "my_package.my_module.MyModelWrapper", "kwargs": {}, "cutoff": 5.0},
+}
+
+
+def template_spec(workflow: str = "train", model: str = "mace", dataset: str = "data/train.zarr",
+                  validation_path: str | None = "data/val.zarr", output_dir: str = "runs/job", lr: float | None = None,
+                  num_steps: int | None = None, num_epochs: int | None = None, device: str | None = None,
+                  trainable: tuple[str, ...] = (), checkpoint: str | None = None, loss_dtype_policy: str | None = None,
+                  validation_every_epochs: int | None = None, validation_every_steps: int | None = None,
+                  batch_size: int = 16) -> TrainingJobSpec:
+    """A job file to start from (reference ``training/cli.py:1671-2030``: ``init`` per workflow and model family).
+
+    ``workflow="finetune"`` adds the fine-tuning block (checkpoint to start from, patterns of the parameters that stay
+    trainable), lowers the default learning rate to the fine-tuning default and drops the scheduler; ``model`` picks the
+    wrapper class and its constructor arguments (``custom``: a placeholder import path to edit)."""
+    from nvalchemi_toolkit_b200.training.finetune import DEFAULT_FINETUNE_LR
+
+    if workflow not in ("train", "finetune"):
+        raise ValueError(f"workflow must be 'train' or 'finetune', got {workflow!r}")
+    if model not in MODEL_TEMPLATES:
+        raise ValueError(f"model must be one of {sorted(MODEL_TEMPLATES)}, got {model!r}")
+    if num_steps is not None and num_epochs is not None:
+        raise ValueError("give at most one of num_steps / num_epochs")
+    m = MODEL_TEMPLATES[model]
+    fine = workflow == "finetune"
+    if num_steps is None and num_epochs is None:
+        num_epochs = 10
+    if validation_path is None:
+        validation = None
+    elif validation_every_steps is not None:
+        validation = ValidationSpec(every_n_steps=validation_every_steps, every_n_epochs=None)
+    else:
+        validation = ValidationSpec(every_n_epochs=validation_every_epochs or 1)
+    optimizer = OptimizerSpec(kwargs={"lr": lr if lr is not None else (DEFAULT_FINETUNE_LR if fine else 1e-3)},
+                              scheduler_cls=None if fine else "torch.optim.lr_scheduler.ExponentialLR",
+                              scheduler_kwargs={} if fine else {"gamma": 0.999})
+    finetune = None
+    if fine:
+        finetune = FineTuneSpec(checkpoint=checkpoint or "checkpoints/pretrained", trainable=list(trainable) or ["readout"])
+    elif trainable or checkpoint:
+        raise ValueError("--trainable / --checkpoint belong to the finetune workflow")
     return TrainingJobSpec(
-        model=ComponentSpec(cls="nvalchemi_toolkit_b200.models.mace.MACEWrapper",
-                            kwargs={"atomic_numbers": [1, 6, 8], "channels": 64, "r_max": 5.0}),
-        data=DataSpec(train="data/train.zarr", validation="data/val.zarr", batch_size=16, neighbor_cutoff=5.0),
-        num_epochs=10, validation=ValidationSpec(every_n_epochs=1),
-        optimizer=OptimizerSpec(kwargs={"lr": 1e-3}, scheduler_cls="torch.optim.lr_scheduler.ExponentialLR",
-                                scheduler_kwargs={"gamma": 0.999}))
+        model=ComponentSpec(cls=m["cls"], kwargs=dict(m["kwargs"])),
+        data=DataSpec(train=dataset, validation=validation_path, batch_size=batch_size, neighbor_cutoff=m["cutoff"]),
+        num_epochs=num_epochs, num_steps=num_steps, validation=validation, optimizer=optimizer, finetune=finetune,
+        output_dir=output_dir, devices=[device] if device else None, loss_dtype_policy=loss_dtype_policy)
 
 
 # ---- building and running ------------------------------------------------------------------------------------------
@@ -193,7 +239,7 @@ def build_job(spec: TrainingJobSpec) -> tuple[Any, Any, Any]:
     if spec.validation is not None and val is not None:
         vcfg = ValidationConfig(data=val, every_n_steps=spec.validation.every_n_steps,
                                 every_n_epochs=spec.validation.every_n_epochs)
-    kw = dict(optimizer_configs=OptimizerConfig(**spec.optimizer.model_dump()), loss_fn=ComposedLossFunction.from_spec(spec.loss),
+    kw = dict(optimizer_configs=OptimizerConfig(**spec.optimizer.model_dump()), loss_fn=ComposedLossFunction.from_spec(spec.loss, normalize_weights=spec.normalize_loss_weights, dtype_policy=spec.loss_dtype_policy),
               num_epochs=spec.num_epochs, num_steps=spec.num_steps, hooks=hooks, validation_config=vcfg,
               devices=spec.devices)
     if spec.finetune is not None:
@@ -309,21 +355,89 @@ def finetune(job: str, checkpoint: str | None, trainable: tuple[str, ...]) -> No
     run_job(spec)
 
 
-@main.command("init")
-@click.argument("path", type=click.Path())
-@click.option("--force", is_flag=True)
-def init(path: str, force: bool) -> None:
-    """Write a template job file (JSON or YAML by extension)."""
-    if Path(path).exists() and not force:
+def _emit(payload: dict[str, Any], path: str | None, force: bool) -> None:
+    """A job / schema document to a file (JSON or YAML by extension) or to the terminal."""
+    if path is None:
+        click.echo(json.dumps(payload, indent=2))
+        return
+    target = Path(path)
+    if target.exists() and not force:
         raise click.ClickException(f"{path} exists (use --force)")
-    template_spec().to_file(path)
+    target.parent.mkdir(parents=True, exist_ok=True)
+    if target.suffix in (".yaml", ".yml"):
+        import yaml
+
+        target.write_text(yaml.safe_dump(payload, sort_keys=False))
+    else:
+        target.write_text(json.dumps(payload, indent=2))
     click.echo(f"wrote {path}")
 
 
-@main.command("schema")
-def schema() -> None:
-    """Print the JSON schema of a job file."""
-    click.echo(json.dumps(TrainingJobSpec.model_json_schema(), indent=2))
+def _template_options(fn: Any) -> Any:
+    for opt in reversed([
+        click.option("--workflow", type=click.Choice(["train", "finetune"]), default="train", show_default=True),
+        click.option("--model", type=click.Choice(sorted(MODEL_TEMPLATES)), default="mace", show_default=True),
+        click.option("--dataset", default="data/train.zarr", show_default=True, help="training store"),
+        click.option("--validation-path", default="data/val.zarr", show_default=True, help="'' for none"),
+        click.option("--validation-every-epochs", type=int, default=None),
+        click.option("--validation-every-steps", type=int, default=None),
+        click.option("--output-dir", default="runs/job", show_default=True),
+        click.option("--lr", type=float, default=None, help="default: 1e-3 (train), the fine-tuning default (finetune)"),
+        click.option("--num-steps", type=int, default=None),
+        click.option("--num-epochs", type=int, default=None),
+        click.option("--batch-size", type=int, default=16, show_default=True),
+        click.option("--device", default=None, help="e.g. cuda:0 (default: chosen at run time)"),
+        click.option("--checkpoint", default=None, help="finetune: checkpoint directory to start from"),
+        click.option("--trainable", multiple=True, help="finetune: parameter-name patterns that stay trainable"),
+        click.option("--loss-dtype-policy", type=click.Choice(["strict", "prediction_to_target", "target_to_prediction"]),
+                     default=None),
+    ]):
+        fn = opt(fn)
+    return fn
+
+
+def _template_from_options(kw: dict[str, Any]) -> TrainingJobSpec:
+    kw = dict(kw)
+    kw["validation_path"] = kw["validation_path"] or None
+    kw["trainable"] = tuple(kw.get("trainable") or ())
+    try:
+        return template_spec(**kw)
+    except ValueError as exc:
+        raise click.ClickException(str(exc)) from exc
+
+
+@main.command("init")
+@click.argument("path", type=click.Path(), required=False)
+@click.option("--force", is_flag=True)
+@_template_options
+def init(path: str | None, force: bool, **options: Any) -> None:
+    """Write a template job file (JSON or YAML by extension; to the terminal without PATH)."""
+    _emit(_template_from_options(options).model_dump(mode="json"), path, force)
+
+
+@main.group("schema", invoke_without_command=True)
+@click.pass_context
+def schema(ctx: click.Context) -> None:
+    """JSON schema of a job file and templates, for authoring job files offline."""
+    if ctx.invoked_subcommand is None:
+        click.echo(json.dumps(TrainingJobSpec.model_json_schema(), indent=2))
+
+
+@schema.command("dump")
+@click.option("--out", "output", type=click.Path(), default=None, help="write the schema to this file")
+@click.option("--force", is_flag=True)
+def schema_dump(output: str | None, force: bool) -> None:
+    """The JSON schema of a job file."""
+    _emit(TrainingJobSpec.model_json_schema(), output, force)
+
+
+@schema.command("template")
+@click.option("--out", "output", type=click.Path(), default=None, help="write the template to this file")
+@click.option("--force", is_flag=True)
+@_template_options
+def schema_template(output: str | None, force: bool, **options: Any) -> None:
+    """A template job for one workflow and model family (same options as ``init``)."""
+    _emit(_template_from_options(options).model_dump(mode="json"), output, force)
 
 
 @main.group()

@@ -99,3 +99,44 @@ def test_spec_report_previews_the_schedule_and_lists_findings(tmp_path):
     assert "ReduceLROnPlateau steps on a validation metric" in text and "force term" in text and "unusually large" in text
     bad.to_file(tmp_path / "bad.yaml")
     assert r.invoke(cli.main, ["spec", "report", str(tmp_path / "bad.yaml"), "--strict"]).exit_code != 0
+
+
+def test_init_templates_per_workflow_and_schema_subcommands(tmp_path):
+    r = CliRunner()
+    out = r.invoke(cli.main, ["init", "--workflow", "finetune", "--model", "aimnet2", "--trainable", "readout", "--trainable",
+                              "embed.*", "--num-steps", "500", "--checkpoint", "ckpt/base", "--validation-path", "",
+                              "--loss-dtype-policy", "prediction_to_target"])
+    assert out.exit_code == 0, out.output
+    job = cli.TrainingJobSpec.model_validate(json.loads(out.output))  # printed to the terminal, and a valid job
+    assert job.finetune.checkpoint == "ckpt/base" and job.finetune.trainable == ["readout", "embed.*"]
+    assert job.num_steps == 500 and job.num_epochs is None and job.validation is None and job.data.validation is None
+    assert job.optimizer.kwargs["lr"] == pytest.approx(1e-4) and job.optimizer.scheduler_cls is None
+    assert job.model.cls.endswith("AIMNet2Wrapper") and job.loss_dtype_policy == "prediction_to_target"
+    # options of the other workflow are refused, as are two budgets
+    assert r.invoke(cli.main, ["init", "--trainable", "readout"]).exit_code != 0
+    assert r.invoke(cli.main, ["init", "--num-steps", "5", "--num-epochs", "2"]).exit_code != 0
+    # YAML by extension; validation cadence in steps
+    path = tmp_path / "sub" / "job.yaml"
+    out = r.invoke(cli.main, ["init", str(path), "--model", "demo", "--validation-every-steps", "50", "--device", "cpu"])
+    assert out.exit_code == 0 and path.exists()
+    job = cli.TrainingJobSpec.from_file(path)
+    assert job.validation.every_n_steps == 50 and job.validation.every_n_epochs is None and job.devices == ["cpu"]
+    assert job.data.neighbor_cutoff is None  # the demo model needs no neighbour list
+    # schema group: bare call and `dump` agree; `template` takes the same options as `init`
+    bare = json.loads(r.invoke(cli.main, ["schema"]).output)
+    dumped = tmp_path / "schema.json"
+    assert r.invoke(cli.main, ["schema", "dump", "--out", str(dumped)]).exit_code == 0
+    assert json.loads(dumped.read_text()) == bare and "loss_dtype_policy" in bare["properties"]
+    templ = r.invoke(cli.main, ["schema", "template", "--workflow", "finetune", "--model", "mace"])
+    assert json.loads(templ.output)["finetune"]["trainable"] == ["readout"]
+
+
+def test_job_loss_options_reach_the_composed_loss(tmp_path):
+    job = cli.template_spec(model="demo", dataset=str(tmp_path / "none.zarr"), validation_path=None, num_steps=1,
+                            loss_dtype_policy="target_to_prediction")
+    job.normalize_loss_weights = True
+    from nvalchemi_toolkit_b200.training import ComposedLossFunction
+
+    loss = ComposedLossFunction.from_spec(job.loss, normalize_weights=job.normalize_loss_weights, dtype_policy=job.loss_dtype_policy)
+    w = loss.weights_at(0)
+    assert sum(w.values()) == pytest.approx(1.0) and loss.dtype_policy == "target_to_prediction"
