@@ -97,6 +97,38 @@ class Dataset:
     def __getitem__(self, idx: int) -> tuple[Any, dict[str, Any]]:
         return self._finish(*self.reader.read(idx))
 
+    @property
+    def field_names(self) -> list[str]:
+        """Names of the tensors a sample carries (from the reader's level table, else from sample 0)."""
+        levels = getattr(self.reader, "field_levels", None)
+        if levels:
+            return sorted(levels)
+        return sorted(self.reader.read(0)[0]) if len(self) else []
+
+    def get_batch(self, indices: Sequence[int]) -> Batch:
+        """One ``Batch`` from a fused read of ``indices`` (the reader sees them as one window)."""
+        items = [self._finish(d, m) for d, m in self.reader.read_many(list(indices))]
+        for _, m in items:
+            ev = m.get("_event") if isinstance(m, dict) else None
+            if ev is not None:
+                torch.cuda.current_stream().wait_event(ev)
+        if self.raw:
+            return Batch.from_raw_dicts([it for it, _ in items], field_levels=getattr(self.reader, "field_levels", {}))
+        return Batch.from_data_list([it for it, _ in items])
+
+    def close(self) -> None:
+        """Stop the read workers (pending reads are abandoned) and close the reader."""
+        self._pool.shutdown(wait=False, cancel_futures=True)
+        close = getattr(self.reader, "close", None)
+        if callable(close):
+            close()
+
+    def __enter__(self) -> "Dataset":
+        return self
+
+    def __exit__(self, *exc: Any) -> None:
+        self.close()
+
     def fetch(self, indices: Sequence[int]) -> "cf.Future[list[tuple[Any, dict[str, Any]]]]":
         """Asynchronous fused read of several samples (one reader window)."""
         return self._pool.submit(lambda: [self._finish(d, m) for d, m in self.reader.read_many(list(indices))])
@@ -285,6 +317,109 @@ class MultiDatasetBatchSampler:
         if not self.homogeneous:
             return n // self.batch_size if self.drop_last else math.ceil(n / self.batch_size)
         return sum(1 for _ in self)  # depends on how the epoch's indices fall into the buckets
+
+
+def num_batches_from_policy(policy: str, lengths: Sequence[int], per_batch: Sequence[int], batch_size: int, replacement: bool) -> int:
+    """Epoch length of a fixed-composition sampler (reference ``samplers.py:196-235``).  ``dataset_size``: as many batches
+    as the concatenated data fill (with replacement) or as the first dataset to run out allows (without);
+    ``min_size`` / ``max_size``: until the first / the last contributing dataset has been seen once (``max_size`` makes
+    the smaller ones repeat, so it needs ``replacement``)."""
+    pairs = [(n, c) for n, c in zip(lengths, per_batch) if c > 0]
+    if not pairs:
+        raise ValueError("at least one dataset must contribute samples to a batch")
+    if replacement:
+        lo, hi = min(-(-n // c) for n, c in pairs), max(-(-n // c) for n, c in pairs)
+    else:
+        lo, hi = min(n // c for n, c in pairs), max(n // c for n, c in pairs)
+    if policy == "dataset_size":
+        return -(-sum(lengths) // batch_size) if replacement else lo
+    if policy == "min_size":
+        return lo
+    if policy == "max_size":
+        if not replacement and hi > lo:
+            raise ValueError("epoch_policy='max_size' repeats the smaller datasets: it needs replacement=True")
+        return hi
+    raise ValueError("epoch_policy must be 'dataset_size', 'min_size' or 'max_size'")
+
+
+class FixedCompositionBatchSampler:
+    """Every batch holds the SAME number of samples from each dataset (reference ``samplers.py:423-789``).
+
+    ``weights`` (default: the dataset lengths) are turned into per-batch counts with :func:`counts_from_weights`, so with
+    ``weights=[3, 1]`` and ``batch_size=8`` each batch has 6 samples of the first dataset and 2 of the second, whatever
+    their sizes: a small high-fidelity set is seen at a fixed rate in every optimiser step instead of in bursts.
+    Without ``replacement`` each dataset is walked through a fresh permutation per epoch (no repeats inside an epoch; the
+    epoch ends when the policy says so); with it the permutation wraps around.  Ranks take strided shares of the epoch's
+    batches; ``drop_last`` trims the number of batches to a multiple of the world size, otherwise the head of the epoch
+    is repeated so that every rank runs the same number of steps."""
+
+    def __init__(self, multi: MultiDataset, batch_size: int, weights: Sequence[float] | None = None,
+                 num_batches: int | None = None, epoch_policy: str = "dataset_size", replacement: bool = True,
+                 shuffle: bool = True, seed: int = 0, rank: int = 0, world_size: int = 1, drop_last: bool = False) -> None:
+        self.multi, self.batch_size, self.replacement, self.shuffle = multi, int(batch_size), replacement, shuffle
+        self.seed, self.rank, self.world_size, self.drop_last, self.epoch = seed, rank, world_size, drop_last, 0
+        self.lengths = [len(d) for d in multi.datasets]
+        w = list(weights) if weights is not None else [float(n) for n in self.lengths]
+        if len(w) != len(self.lengths):
+            raise ValueError("one weight per dataset")
+        self.samples_per_dataset = counts_from_weights(w, self.batch_size)
+        if any(c > 0 and n == 0 for c, n in zip(self.samples_per_dataset, self.lengths)):
+            raise ValueError("an empty dataset cannot contribute to a batch")
+        if not replacement and any(c > n for c, n in zip(self.samples_per_dataset, self.lengths)):
+            raise ValueError("a dataset is smaller than its share of one batch: use replacement=True")
+        self.num_batches = int(num_batches) if num_batches is not None else num_batches_from_policy(
+            epoch_policy, self.lengths, self.samples_per_dataset, self.batch_size, replacement)
+        if self.num_batches < 1:
+            raise ValueError("the epoch would hold no batch")
+        if not replacement:
+            most = min(n // c for n, c in zip(self.lengths, self.samples_per_dataset) if c > 0)
+            if self.num_batches > most:
+                raise ValueError(f"{self.num_batches} batches without replacement need more samples than the smallest "
+                                 f"contributing dataset holds ({most} batches at most)")
+
+    @classmethod
+    def balanced(cls, multi: MultiDataset, batch_size: int, **kwargs: Any) -> "FixedCompositionBatchSampler":
+        """Equal shares of every batch for all datasets."""
+        return cls(multi, batch_size, weights=[1.0] * len(multi.datasets), **kwargs)
+
+    def set_epoch(self, epoch: int) -> None:
+        self.epoch = epoch
+
+    def _per_rank(self) -> int:
+        return self.num_batches // self.world_size if self.drop_last else -(-self.num_batches // self.world_size)
+
+    def __len__(self) -> int:
+        return self._per_rank()
+
+    def epoch_batches(self) -> list[list[int]]:
+        """All batches of the epoch before sharding (the same on every rank)."""
+        g = torch.Generator().manual_seed(self.seed + self.epoch)
+        streams = []
+        for n, c in zip(self.lengths, self.samples_per_dataset):
+            need = c * self.num_batches
+            if need == 0:
+                streams.append(None)
+                continue
+            reps = -(-need // n)
+            streams.append(torch.cat([torch.randperm(n, generator=g) if self.shuffle else torch.arange(n) for _ in range(reps)])[:need])
+        out = []
+        for b in range(self.num_batches):
+            parts = [st[b * c: (b + 1) * c] + off for st, c, off in zip(streams, self.samples_per_dataset, self.multi.offsets)
+                     if st is not None]
+            batch = torch.cat(parts)
+            if self.shuffle:
+                batch = batch[torch.randperm(batch.numel(), generator=g)]
+            out.append(batch.tolist())
+        return out
+
+    def __iter__(self) -> Iterator[list[int]]:
+        batches = self.epoch_batches()
+        per, w = self._per_rank(), self.world_size
+        if self.drop_last:
+            batches = batches[: per * w]
+        elif len(batches) < per * w:
+            batches = batches + batches[: per * w - len(batches)]
+        return iter(batches[self.rank:: w])
 
 
 class DataLoader:

@@ -279,3 +279,53 @@ def test_multidataset_sampler_counts_epochs_sharding_and_homogeneous_batches():
     assert all(len({multi.locate(i)[0] for i in x}) == 1 for x in batches)
     with pytest.raises(ValueError, match="empty dataset"):
         MultiDatasetSampler(MultiDataset([a, InMemoryDataset([])]), weights=[1, 1])
+
+
+def test_fixed_composition_batches_policies_and_sharding():
+    from nvalchemi_toolkit_b200.data.datapipes import FixedCompositionBatchSampler, num_batches_from_policy
+
+    big, small = InMemoryDataset(_data(12)), InMemoryDataset(_data(4))
+    multi = MultiDataset([big, small])
+    s = FixedCompositionBatchSampler(multi, batch_size=8, weights=[3, 1], replacement=False, seed=1)
+    assert s.samples_per_dataset == [6, 2] and s.num_batches == 2 and len(s) == 2
+    batches = list(s)
+    for b in batches:
+        assert sum(i < 12 for i in b) == 6 and sum(i >= 12 for i in b) == 2    # the same composition in every batch
+    flat = [i for b in batches for i in b]
+    assert len(set(flat)) == len(flat) == 16                                    # no repeats inside the epoch
+    s.set_epoch(1)
+    assert list(s) != batches
+    # policies: until the first / last dataset has been seen once
+    assert num_batches_from_policy("min_size", [12, 4], [4, 4], 8, True) == 1
+    assert num_batches_from_policy("max_size", [12, 4], [4, 4], 8, True) == 3
+    assert num_batches_from_policy("dataset_size", [12, 4], [4, 4], 8, True) == 2
+    with pytest.raises(ValueError, match="replacement"):
+        num_batches_from_policy("max_size", [12, 4], [4, 4], 8, False)
+    bal = FixedCompositionBatchSampler.balanced(multi, 8, epoch_policy="max_size", seed=0)
+    assert bal.samples_per_dataset == [4, 4] and bal.num_batches == 3
+    small_seen = [i for b in bal.epoch_batches() for i in b if i >= 12]
+    assert len(small_seen) == 12 and set(small_seen) == {12, 13, 14, 15}         # the small set wrapped around three times
+    assert small_seen[:4] != small_seen[4:8] or small_seen[4:8] != small_seen[8:]  # ... through fresh permutations
+    # two ranks: strided shares of the same epoch; three batches are padded to four unless drop_last
+    r0 = FixedCompositionBatchSampler.balanced(multi, 8, epoch_policy="max_size", rank=0, world_size=2)
+    r1 = FixedCompositionBatchSampler.balanced(multi, 8, epoch_policy="max_size", rank=1, world_size=2)
+    assert len(r0) == len(r1) == 2 and list(r0)[0] == bal.epoch_batches()[0] and list(r1)[1] == bal.epoch_batches()[0]
+    d0 = FixedCompositionBatchSampler.balanced(multi, 8, epoch_policy="max_size", rank=0, world_size=2, drop_last=True)
+    assert len(d0) == 1 and len(list(d0)) == 1
+    with pytest.raises(ValueError, match="smaller than its share"):
+        FixedCompositionBatchSampler(multi, 16, weights=[1, 1], replacement=False)
+    # through the loader: batches arrive with the composition intact
+    loader = DataLoader(multi, batch_sampler=FixedCompositionBatchSampler(multi, 8, weights=[3, 1], replacement=False))
+    assert [b.num_graphs for b in loader] == [8, 8]
+
+
+def test_dataset_field_names_get_batch_and_close(tmp_path):
+    w = AtomicDataZarrWriter(tmp_path / "s.zarr")
+    data = _data(5)
+    w.write(data)
+    with Dataset(AtomicDataZarrReader(tmp_path / "s.zarr")) as ds:
+        assert {"positions", "atomic_numbers"} <= set(ds.field_names)
+        b = ds.get_batch([3, 0])
+        assert b.num_graphs == 2 and torch.allclose(b[0].positions, data[3].positions)
+    with pytest.raises(RuntimeError):
+        ds.fetch([0])  # the worker pool is gone after close
