@@ -72,24 +72,31 @@ void halo_push_rows(const Tensor& src, const Tensor& idx, const Tensor& dst_row,
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
-// out[i] = scale * sum_r buf_r[i]; every rank reads all peers (one-shot all-reduce; sized for the
-// latency-bound few-MB gradient buckets of MLIP training).  float4 path when aligned.
-__global__ void p2p_allreduce_kernel(int64_t n, const int64_t* __restrict__ buf_ptrs, int world, float scale,
-                                     float* __restrict__ out) {
-  int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 4;
+// out[i] = scale * sum_r buf_r[i]; every rank reads all peers in rank order (one-shot all-reduce; sized for the
+// latency-bound few-MB gradient buckets of MLIP training and for the float64 structure-factor / charge-mesh sums of the
+// Ewald and particle-mesh models: the sum order is fixed, so every rank obtains bitwise the same result).
+// 16-byte vector path (V = 4 floats or 2 doubles) when the element range allows.
+template <typename T, int V>
+__global__ void p2p_allreduce_kernel(int64_t n, const int64_t* __restrict__ buf_ptrs, int world, T scale, T* __restrict__ out) {
+  struct alignas(16) Vec { T v[V]; };
+  int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * V;
   if (i >= n) return;
-  if (i + 4 <= n) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (i + V <= n) {
+    Vec acc;
+#pragma unroll
+    for (int c = 0; c < V; ++c) acc.v[c] = T(0);
     for (int r = 0; r < world; ++r) {
-      float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(buf_ptrs[r]) + i);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      Vec x = *reinterpret_cast<const Vec*>(reinterpret_cast<const T*>(buf_ptrs[r]) + i);
+#pragma unroll
+      for (int c = 0; c < V; ++c) acc.v[c] += x.v[c];
     }
-    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-    *reinterpret_cast<float4*>(out + i) = acc;
+#pragma unroll
+    for (int c = 0; c < V; ++c) acc.v[c] *= scale;
+    *reinterpret_cast<Vec*>(out + i) = acc;
   } else {
     for (int64_t k = i; k < n; ++k) {
-      float acc = 0.f;
-      for (int r = 0; r < world; ++r) acc += reinterpret_cast<const float*>(buf_ptrs[r])[k];
+      T acc = T(0);
+      for (int r = 0; r < world; ++r) acc += reinterpret_cast<const T*>(buf_ptrs[r])[k];
       out[k] = acc * scale;
     }
   }
@@ -99,10 +106,98 @@ void p2p_allreduce(const Tensor& buf_ptrs, int64_t world, double scale, Tensor o
   c10::cuda::CUDAGuard guard(out.device());
   int64_t n = out.numel();
   if (n == 0) return;
+  TORCH_CHECK(out.is_contiguous(), "p2p_allreduce: output must be contiguous");
   TORCH_CHECK((reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0, "p2p_allreduce: output must be 16-byte aligned");
-  int64_t threads = (n + 3) / 4;
-  p2p_allreduce_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
-      n, buf_ptrs.data_ptr<int64_t>(), (int)world, (float)scale, out.data_ptr<float>());
+  TORCH_CHECK(buf_ptrs.numel() >= world, "p2p_allreduce: address table shorter than the world size");
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (out.scalar_type() == at::kDouble) {
+    int64_t threads = (n + 1) / 2;
+    p2p_allreduce_kernel<double, 2><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
+        n, buf_ptrs.data_ptr<int64_t>(), (int)world, scale, out.data_ptr<double>());
+  } else {
+    TORCH_CHECK(out.scalar_type() == at::kFloat, "p2p_allreduce: float32 or float64 buffers");
+    int64_t threads = (n + 3) / 4;
+    p2p_allreduce_kernel<float, 4><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
+        n, buf_ptrs.data_ptr<int64_t>(), (int)world, (float)scale, out.data_ptr<float>());
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// Small all-reduce in ONE launch (push form).  Block b owns elements [b * chunk, (b + 1) * chunk): it stores its chunk
+// into slot `rank` of EVERY rank's scratch region (remote stores, nothing waits for them), publishes `epoch` in flag
+// (b, rank) of every rank, waits (bounded) until the flags (b, r) of all ranks r have arrived in its own flag row, and
+// then adds the `world` slots of its LOCAL scratch region in rank order.  Blocks never wait for other blocks of the same
+// GPU, only for the block with the same index on the peers, and every block publishes before it waits, so no launch
+// order can deadlock.  Two slot sets alternate with the parity of `epoch`: a rank can start call k + 2 (same parity as
+// k) only after every peer has entered call k + 1, i.e. after it finished reading the slots of call k, so no closing
+// rendezvous is needed.  Layout of a scratch region: [parity][rank][slot_elems]; of a flag row: [block][rank].
+constexpr int kPushBlocks = 16;
+constexpr int kPushThreads = 512;
+
+template <typename T>
+__global__ void p2p_allreduce_push_kernel(const T* src, T* out, int64_t n, int64_t chunk,  // src may alias out
+                                          const int64_t* __restrict__ scratch_ptrs, int64_t slot_elems,
+                                          const int64_t* __restrict__ flag_ptrs, int rank, int world, int epoch, T scale,
+                                          int* __restrict__ err) {
+  __shared__ int s_ok;
+  const int b = blockIdx.x, t = threadIdx.x;
+  const int64_t lo = (int64_t)b * chunk;
+  const int64_t hi = lo + chunk < n ? lo + chunk : n;
+  const int64_t set = (int64_t)(epoch & 1) * world;
+  if (t == 0) s_ok = 1;
+  for (int r = 0; r < world; ++r) {
+    T* dst = reinterpret_cast<T*>(scratch_ptrs[r]) + (set + rank) * slot_elems;
+    for (int64_t i = lo + t; i < hi; i += kPushThreads) dst[i] = src[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (t < world) {
+    volatile int* peer = reinterpret_cast<volatile int*>(flag_ptrs[t]);
+    peer[b * 32 + rank] = epoch;
+    volatile int* mine = reinterpret_cast<volatile int*>(flag_ptrs[rank]);
+    bool ok = false;
+    for (int it = 0; it < 4000000; ++it) {  // about a second
+      if (mine[b * 32 + t] >= epoch) { ok = true; break; }
+      __nanosleep(250);
+    }
+    if (!ok) { atomicExch(err, 100 + t); s_ok = 0; }
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (!s_ok) return;  // a peer never arrived: the status word says which; the output is left untouched
+  const volatile T* base = reinterpret_cast<const volatile T*>(scratch_ptrs[rank]) + set * slot_elems;
+  for (int64_t i = lo + t; i < hi; i += kPushThreads) {
+    T acc = T(0);
+    for (int r = 0; r < world; ++r) acc += base[r * slot_elems + i];
+    out[i] = acc * scale;
+  }
+}
+
+void p2p_allreduce_push(const Tensor& src, const Tensor& scratch_ptrs, int64_t slot_elems, const Tensor& flag_ptrs, int64_t rank,
+                        int64_t world, int64_t epoch, double scale, Tensor err, Tensor out) {
+  c10::cuda::CUDAGuard guard(src.device());
+  NVA_CHECK_CONTIG(src);
+  NVA_CHECK_CONTIG(out);
+  const int64_t n = src.numel();
+  if (n == 0) return;
+  TORCH_CHECK(out.numel() == n && out.scalar_type() == src.scalar_type(), "p2p_allreduce_push: out must match src");
+  TORCH_CHECK(n <= slot_elems, "p2p_allreduce_push: ", n, " elements exceed the slot size ", slot_elems);
+  TORCH_CHECK(world >= 1 && world <= 32 && rank >= 0 && rank < world, "p2p_allreduce_push: up to 32 ranks");
+  TORCH_CHECK(scratch_ptrs.numel() >= world && flag_ptrs.numel() >= world, "p2p_allreduce_push: address tables shorter than the world size");
+  int blocks = (int)((n + 511) / 512);  // one element per thread up to 16 blocks: the latency of the remote stores is spread
+  blocks = blocks < 1 ? 1 : (blocks > kPushBlocks ? kPushBlocks : blocks);
+  const int64_t chunk = (n + blocks - 1) / blocks;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (src.scalar_type() == at::kDouble) {
+    p2p_allreduce_push_kernel<double><<<blocks, kPushThreads, 0, stream>>>(
+        src.data_ptr<double>(), out.data_ptr<double>(), n, chunk, scratch_ptrs.data_ptr<int64_t>(), slot_elems,
+        flag_ptrs.data_ptr<int64_t>(), (int)rank, (int)world, (int)epoch, scale, err.data_ptr<int>());
+  } else {
+    TORCH_CHECK(src.scalar_type() == at::kFloat, "p2p_allreduce_push: float32 or float64 tensors");
+    p2p_allreduce_push_kernel<float><<<blocks, kPushThreads, 0, stream>>>(
+        src.data_ptr<float>(), out.data_ptr<float>(), n, chunk, scratch_ptrs.data_ptr<int64_t>(), slot_elems,
+        flag_ptrs.data_ptr<int64_t>(), (int)rank, (int)world, (int)epoch, (float)scale, err.data_ptr<int>());
+  }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -112,6 +207,7 @@ TORCH_LIBRARY_FRAGMENT(nvalchemi, m) {
   m.def("p2p_barrier(Tensor flag_ptrs, int rank, int world, int epoch, Tensor(a!) err) -> ()", &nva::p2p_barrier);
   m.def("halo_push_rows(Tensor src, Tensor idx, Tensor dst_row, Tensor peer, Tensor? shift, Tensor dst_ptrs) -> ()", &nva::halo_push_rows);
   m.def("p2p_allreduce(Tensor buf_ptrs, int world, float scale, Tensor(a!) out) -> ()", &nva::p2p_allreduce);
+  m.def("p2p_allreduce_push(Tensor src, Tensor scratch_ptrs, int slot_elems, Tensor flag_ptrs, int rank, int world, int epoch, float scale, Tensor(a!) err, Tensor(b!) out) -> ()", &nva::p2p_allreduce_push);
 }
 
 namespace nva {

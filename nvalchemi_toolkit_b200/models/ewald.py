@@ -104,9 +104,15 @@ class _CoulombBase(nn.Module, BaseModelMixin):
         if dd is not None and dd[1] > 1:
             import torch.distributed as dist
 
-            def reduce(t: torch.Tensor, _g: Any = dd[0]) -> torch.Tensor:
-                dist.all_reduce(t, group=_g)
-                return t
+            from nvalchemi_toolkit_b200.parallel.symmetric import peer_reducer
+
+            # structure factors / charge meshes are summed through peer memory where the ranks share NVLink (ordered
+            # float64 peer loads between two flag barriers); elsewhere through the library collective
+            reduce = peer_reducer(dd[0], pos.device)
+            if reduce is None:
+                def reduce(t: torch.Tensor, _g: Any = dd[0]) -> torch.Tensor:
+                    dist.all_reduce(t, group=_g)
+                    return t
         alpha = torch.full((nb,), self.alpha, dtype=torch.float64, device=pos.device)
         e_atom, forces, virial, phi = es.real_space(pos, q, cells, data.neighbor_matrix,
                                                     getattr(data, "neighbor_matrix_shifts", None), data.num_neighbors,

@@ -151,6 +151,10 @@ class P2PContext:
         if check == "lazy":
             self.check(wait=False)
         n = view.numel()
+        if view.dtype not in (torch.float32, torch.float64):
+            raise TypeError(f"allreduce_ sums float32 or float64 buffers, got {view.dtype}")
+        if view.dtype == torch.float64:
+            use_multimem = False  # the in-switch path is written for float4 groups; doubles use ordered peer loads
         if use_multimem is None:
             use_multimem = self.arena.multicast_ptr != 0 and n % 4 == 0 and os.environ.get("NVA_MULTIMEM", "1") != "0"
         self.barrier()
@@ -173,3 +177,85 @@ class P2PContext:
 
     def release_transient(self) -> None:
         self.arena.offset = self.persistent_offset
+
+
+class PeerReducer:
+    """In-place sum of a tensor over the ranks of a group through peer memory: callable ``reducer(t) -> t``.
+
+    Used where a model needs a GLOBAL sum in the middle of its evaluation (structure factors and charge meshes of the
+    Ewald / particle-mesh models under domain decomposition, float64): the tensor is copied into a symmetric scratch
+    buffer, a flag barrier orders the copies, every rank adds up all ranks' buffers in rank order with 16-byte peer
+    loads (:func:`p2p_allreduce`) straight into ``t``, and a closing barrier keeps a fast rank from overwriting its
+    scratch buffer while a slow one still reads it.  Payloads up to ``SMALL_BYTES`` (structure factors, net charges,
+    dipoles: latency-bound) take ONE launch instead of four: ``p2p_allreduce_push`` stores the values into every rank's
+    slot, publishes a flag per block, waits for the peers' flags and adds its local slots; two slot sets alternate so no
+    closing rendezvous is needed.  The fixed order makes the result bitwise identical on every rank,
+    which keeps replicated follow-up work (the reciprocal-space virial) in step.  Tensors that are not float32 / float64
+    CUDA tensors, or larger than the scratch buffer, go through ``torch.distributed.all_reduce``."""
+
+    SMALL_BYTES = 256 << 10  # payloads up to this size take the single-launch push kernel
+
+    def __init__(self, group: dist.ProcessGroup | None, device: torch.device, capacity_bytes: int = 64 << 20,
+                 _context: "P2PContext | None" = None) -> None:
+        self.group, self.device, self.capacity = group, device, int(capacity_bytes)
+        world = _context.world if _context is not None else dist.get_world_size(group)
+        small = 2 * world * self.SMALL_BYTES + 16 * 32 * 4 + 1024
+        self.ctx = _context if _context is not None else P2PContext(self.capacity + small, device, group)
+        self.scratch, self.ptrs = self.ctx.arena.alloc((self.capacity,), torch.uint8)
+        # single-launch path: [parity][rank][SMALL_BYTES] slots and a [block][rank] flag row per rank
+        self.push_scratch, self.push_ptrs = self.ctx.arena.alloc((2 * world * self.SMALL_BYTES,), torch.uint8)
+        self.push_flags, self.push_flag_ptrs = self.ctx.arena.alloc((16 * 32,), torch.int32)
+        self.push_epoch = 0
+        self.ctx.persistent_offset = self.ctx.arena.offset
+        self.calls = 0      # reductions done through peer memory
+        self.small_calls = 0  # ... of which by the single-launch kernel
+        self.fallbacks = 0  # ... through the library collective
+
+    def __call__(self, t: torch.Tensor) -> torch.Tensor:
+        nbytes = t.numel() * t.element_size()
+        if not t.is_cuda or t.dtype not in (torch.float32, torch.float64) or nbytes > self.capacity or nbytes == 0:
+            self.fallbacks += 1
+            if self.ctx.world > 1 and dist.is_initialized():
+                dist.all_reduce(t, group=self.group)
+            return t
+        flat = t if t.is_contiguous() else t.contiguous()
+        if nbytes <= self.SMALL_BYTES:
+            # one kernel: push my values into every rank's slot, flag, wait for the peers' flags, add the local slots
+            self.push_epoch += 1
+            _nops.p2p_allreduce_push(flat.reshape(-1), self.push_ptrs, self.SMALL_BYTES // t.element_size(), self.push_flag_ptrs,
+                                     self.ctx.rank, self.ctx.world, self.push_epoch, 1.0, self.ctx.err, flat.reshape(-1))
+            if flat is not t:
+                t.copy_(flat)
+            self.calls += 1
+            self.small_calls += 1
+            return t
+        view = self.scratch[:nbytes].view(t.dtype)
+        view.copy_(flat.reshape(-1))
+        out = flat.reshape(-1)
+        if out.data_ptr() % 16:  # a slice of a larger tensor: reduce into an aligned temporary
+            out = torch.empty_like(view)
+        self.ctx.allreduce_(view, out=out, use_multimem=False, ptrs=self.ptrs)
+        if out.data_ptr() != t.data_ptr() or flat is not t:
+            t.copy_(out.reshape(t.shape))
+        self.calls += 1
+        return t
+
+
+_REDUCERS: dict[tuple[int, int], "PeerReducer | None"] = {}
+
+
+def peer_reducer(group: dist.ProcessGroup | None, device: torch.device) -> "PeerReducer | None":
+    """The group's shared :class:`PeerReducer` (created on first use: a collective, so every rank of the group must ask
+    in the same place), or ``None`` where peer memory is not an option: CPU tensors, a backend other than NCCL, or
+    ``NVA_PEER_REDUCE=0``."""
+    import os
+
+    if device.type != "cuda" or not dist.is_initialized() or os.environ.get("NVA_PEER_REDUCE", "1") == "0":
+        return None
+    g = group if group is not None else dist.group.WORLD
+    if "nccl" not in str(dist.get_backend(g)):
+        return None
+    key = (id(g), device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _REDUCERS:
+        _REDUCERS[key] = PeerReducer(g, device)
+    return _REDUCERS[key]

@@ -69,6 +69,10 @@ def _worker(rank: int, world: int, port: int, q) -> None:
         o2 = pme2(single)
         res["pme_f_err"] = float((forces - o2["forces"]).abs().max())
         res["pme_e_err"] = abs(float(out["energy"]) - float(o2["energy"]))
+        from nvalchemi_toolkit_b200.parallel.symmetric import peer_reducer
+
+        red = peer_reducer(None, dev)  # the mesh and net-charge sums of the evaluation above went through peer memory
+        res["peer_reductions"], res["library_reductions"], res["peer_status"] = red.calls, red.fallbacks, red.ctx.status()
         q.put((rank, res))
         dist.barrier()
         dist.destroy_process_group()
@@ -97,4 +101,5 @@ def test_generic_domain_layer_over_nccl():
         assert res["owned"] > 0 and res["ghosts"] > 0
         assert res["x_err"] < 1e-8
         assert res["pme_f_err"] < 1e-8 and res["pme_e_err"] < 1e-7
+        assert res["peer_reductions"] >= 2 and res["library_reductions"] == 0 and res["peer_status"] == 0
     assert results[0]["owned"] + results[1]["owned"] == 864

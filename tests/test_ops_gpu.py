@@ -341,3 +341,54 @@ def test_neighbor_build_fetches_ghost_positions_itself():
         return torch.where(cols, nm[:n_own], torch.full_like(nm[:n_own], n)).sort(dim=1).values
 
     assert torch.equal(canon(got[0], got[1]), canon(want[0], want[1]))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,n", [(torch.float64, 4097), (torch.float64, 1), (torch.float32, 4099)])
+def test_peer_allreduce_kernel_sums_in_rank_order(dtype, n):
+    """``p2p_allreduce`` over three buffers behind an address table (one device): scaled sum, vector body and scalar
+    tail, float32 and float64; the float64 result equals the rank-ordered sum bit for bit."""
+    dev = "cuda"
+    g = torch.Generator().manual_seed(n)
+    bufs = [torch.randn(n + 3, generator=g, dtype=dtype).to(dev)[:n] for _ in range(3)]
+    bufs = [b.clone() for b in bufs]  # fresh allocations: 16-byte aligned starts
+    ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
+    out = torch.empty(n, dtype=dtype, device=dev)
+    torch.ops.nvalchemi.p2p_allreduce(ptrs, 3, 0.5, out)
+    want = ((bufs[0] + bufs[1]) + bufs[2]) * 0.5
+    assert torch.equal(out, want)
+    with pytest.raises(RuntimeError, match="float32 or float64"):
+        torch.ops.nvalchemi.p2p_allreduce(ptrs, 3, 1.0, torch.empty(8, dtype=torch.float16, device=dev))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+def test_single_launch_push_allreduce_with_an_emulated_peer(dtype):
+    """``p2p_allreduce_push`` on one device: the second "rank" is a plain buffer whose contribution and flags the test
+    writes in advance (what that rank's kernel would have stored), so the kernel finds its peer already arrived.  Checks
+    the sum, the values pushed into the peer's slots, the alternation of the two slot sets and several blocks."""
+    from nvalchemi_toolkit_b200.parallel.symmetric import P2PContext, PeerReducer
+
+    dev = torch.device("cuda", 0)
+    small = PeerReducer.SMALL_BYTES
+    ctx = P2PContext.single_process((1 << 20) + 4 * small + (1 << 16), dev, world=2)
+    red = PeerReducer(None, dev, capacity_bytes=1 << 20, _context=ctx)
+    esize = torch.empty(0, dtype=dtype).element_size()
+    slot = small // esize
+    mine_region = red.push_scratch.view(dtype).reshape(2, 2, slot)                 # [parity][rank][slot]
+    off = ctx.arena.offset_of(red.push_scratch)
+    peer_region = ctx.arena._bufs[1][off: off + 4 * small].view(dtype).reshape(2, 2, slot)
+    flags = red.push_flags.view(16, 32)
+    g = torch.Generator().manual_seed(3)
+    for call, n in enumerate([20000, 1, 4097], start=1):
+        x = torch.randn(n, generator=g, dtype=dtype).to(dev)
+        peer = torch.randn(n, generator=g, dtype=dtype).to(dev)
+        parity = call & 1
+        mine_region[parity, 1, :n] = peer          # the peer's push into my slot set ...
+        flags[:, 1] = call                          # ... and its flags, one per block
+        x0, want = x.clone(), x + peer
+        got = red(x)
+        assert got is x and torch.equal(x, want)
+        assert torch.equal(peer_region[parity, 0, :n], x0)  # my values arrived in the peer's slot for rank 0
+        assert int(ctx.arena._bufs[1][ctx.arena.offset_of(red.push_flags):].view(torch.int32)[0]) == call
+    assert red.small_calls == 3 and red.fallbacks == 0 and ctx.status() == 0

@@ -56,6 +56,37 @@ def _worker(rank: int, world: int, port: int, q) -> None:
         torch.cuda.synchronize()
         res["nccl_us"] = t0.elapsed_time(t1) * 100.0
         res["status"] = ctx.status()
+        # float64 sums through the shared reducer: odd lengths, a scalar, a non-contiguous tensor, a misaligned slice
+        from nvalchemi_toolkit_b200.parallel.symmetric import peer_reducer
+
+        red = peer_reducer(None, dev)
+        g = torch.Generator(device=dev).manual_seed(7 + rank)
+        base = torch.randn(2003, 2, generator=g, device=dev, dtype=torch.float64)
+        cases = {"odd": base.clone(), "scalar": base.sum(), "strided": base.t()[:, ::2], "slice": base.reshape(-1)[1:1000]}
+        worst = 0.0
+        for name, t in cases.items():
+            want = t.clone().contiguous()
+            dist.all_reduce(want)
+            got = red(t if name in ("strided", "slice") else t.clone())  # views: the non-contiguous and the misaligned path
+            worst = max(worst, float((got - want).abs().max()))
+        res["f64_err"], res["f64_calls"], res["f64_fallbacks"] = worst, red.calls, red.fallbacks
+        gathered = [torch.empty_like(base) for _ in range(world)]
+        mine = red(base.clone())
+        dist.all_gather(gathered, mine)
+        res["f64_bitwise_same"] = all(torch.equal(gathered[0], x) for x in gathered)
+        sk = torch.randn(4096, 2, device=dev, dtype=torch.float64)
+        for fn, key in ((red, "f64_peer_us"), (lambda t: dist.all_reduce(t), "f64_nccl_us")):
+            for _ in range(3):
+                fn(sk)
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(20):
+                fn(sk)
+            t1.record()
+            torch.cuda.synchronize()
+            res[key] = t0.elapsed_time(t1) * 50.0
+        res["status"] = max(res["status"], red.ctx.status())
         q.put((rank, res))
         dist.barrier()
         dist.destroy_process_group()
@@ -85,6 +116,7 @@ def test_peer_allreduce_matches_nccl():
         assert res["p2p"] < 1e-4
         if res["multicast"]:
             assert res["multimem"] < 1e-4
+        assert res["f64_err"] < 1e-12 and res["f64_calls"] >= 4 and res["f64_fallbacks"] == 0 and res["f64_bitwise_same"]
     print("\nall-reduce of 4 MiB on", world, "GPUs:", {k: round(v, 1) for k, v in results[0].items() if k.endswith("_us")},
           "multicast:", results[0]["multicast"])
 

@@ -1,0 +1,233 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Property-based tests (hypothesis): invariants that must hold for ANY input of the stated shape, checked against
+brute-force or list-based restatements written here."""
+import itertools
+import math
+
+import pytest
+import torch
+from hypothesis import given, settings
+from hypothesis import strategies as st
+
+from nvalchemi_toolkit_b200 import Batch
+from nvalchemi_toolkit_b200 import neighbors as nb
+from tests.helpers import random_batch, random_molecule
+
+SETTINGS = dict(max_examples=25, deadline=None)
+
+
+# ---------------------------------------------------------------------------------------------------- neighbour lists
+def _brute_force(pos, cell, pbc, cutoff):
+    """{(i, j, sx, sy, sz)} with |r_j + S.cell - r_i| < cutoff, enumerating enough periodic images explicitly."""
+    inv = torch.linalg.inv(cell)
+    heights = 1.0 / inv.norm(dim=0)                      # distance between opposite faces, per lattice direction
+    reach = [int(math.ceil(cutoff / float(h))) if p else 0 for h, p in zip(heights, pbc)]
+    out = set()
+    n = pos.shape[0]
+    for s in itertools.product(*[range(-r, r + 1) for r in reach]):
+        shift = torch.tensor(s, dtype=pos.dtype) @ cell
+        d = (pos[None, :, :] + shift - pos[:, None, :]).norm(dim=-1)
+        hit = d < cutoff
+        if s == (0, 0, 0):
+            hit &= ~torch.eye(n, dtype=torch.bool)
+        for i, j in hit.nonzero().tolist():
+            out.add((i, j) + s)
+    return out
+
+
+@settings(**SETTINGS)
+@given(seed=st.integers(0, 10_000), n=st.integers(2, 24), pbc=st.tuples(st.booleans(), st.booleans(), st.booleans()),
+       skew=st.floats(0.0, 0.45), cutoff=st.floats(1.5, 4.5))
+def test_neighbor_matrix_equals_brute_force_on_random_triclinic_cells(seed, n, pbc, skew, cutoff):
+    g = torch.Generator().manual_seed(seed)
+    cell = torch.diag(4.0 + 3.0 * torch.rand(3, generator=g, dtype=torch.float64))
+    cell[1, 0], cell[2, 0], cell[2, 1] = skew * cell[0, 0], -skew * cell[0, 0], skew * cell[1, 1]
+    pos = torch.rand(n, 3, generator=g, dtype=torch.float64) @ cell
+    pbc_t = torch.tensor(pbc)
+    bidx, bptr = torch.zeros(n, dtype=torch.int32), torch.tensor([0, n], dtype=torch.int32)
+    nm, num, sh = nb.neighbor_matrix(pos, cell[None], pbc_t[None], bidx, bptr, cutoff, 512)
+    got = set()
+    for i in range(n):
+        for k in range(int(num[i])):
+            got.add((i, int(nm[i, k])) + tuple(int(x) for x in sh[i, k]))
+    want = _brute_force(pos, cell, pbc, cutoff)
+    # pairs within 1e-9 of the cutoff may fall on either side
+    def near(entry):
+        i, j, *s = entry
+        d = (pos[j] + torch.tensor(s, dtype=pos.dtype) @ cell - pos[i]).norm()
+        return abs(float(d) - cutoff) < 1e-9
+    assert {e for e in got ^ want if not near(e)} == set()
+    assert int(num.sum()) == len(got)  # no duplicate (j, shift) entries in a row
+
+
+@settings(**SETTINGS)
+@given(seed=st.integers(0, 10_000), sizes=st.lists(st.integers(1, 9), min_size=1, max_size=5))
+def test_neighbor_lists_never_cross_systems_of_a_batch(seed, sizes):
+    b = random_batch(sizes, seed=seed, periodic=True)
+    nb.compute_neighbors(b, 4.0)
+    owner = b.batch_idx.long()
+    n = b.num_nodes
+    for i in range(n):
+        for k in range(int(b.num_neighbors[i])):
+            assert owner[int(b.neighbor_matrix[i, k])] == owner[i]
+    assert bool((b.neighbor_matrix[torch.arange(b.neighbor_matrix.shape[1])[None, :] >= b.num_neighbors[:, None]] == n).all())
+
+
+# ---------------------------------------------------------------------------------------------------- batches
+@settings(**SETTINGS)
+@given(seed=st.integers(0, 10_000), sizes=st.lists(st.integers(1, 7), min_size=1, max_size=6), edges=st.integers(0, 5))
+def test_batch_round_trip_and_selection(seed, sizes, edges):
+    data = [random_molecule(n, seed + i, n_edges=edges) for i, n in enumerate(sizes)]
+    b = Batch.from_data_list(data)
+    assert b.num_graphs == len(sizes) and b.num_nodes == sum(sizes)
+    assert b.batch_ptr.tolist() == [0] + list(itertools.accumulate(sizes))
+    back = b.to_data_list()
+    for d, e in zip(data, back):
+        assert torch.equal(d.positions, e.positions) and torch.equal(d.atomic_numbers, e.atomic_numbers)
+        if edges:
+            assert torch.equal(d.neighbor_list, e.neighbor_list)       # edge indices come back system-local
+    g = torch.Generator().manual_seed(seed)
+    pick = torch.randperm(len(sizes), generator=g)[: max(1, len(sizes) // 2)].tolist()
+    sub = b.index_select(pick)
+    assert sub.num_graphs == len(pick) and sub.num_nodes == sum(sizes[i] for i in pick)
+    for k, i in enumerate(pick):
+        assert torch.equal(sub[k].positions, data[i].positions)
+    both = Batch.from_data_list(data)
+    both.append(sub)
+    assert both.num_graphs == len(sizes) + len(pick) and torch.equal(both[len(sizes)].positions, data[pick[0]].positions)
+
+
+@settings(**SETTINGS)
+@given(seed=st.integers(0, 10_000), sizes=st.lists(st.integers(1, 6), min_size=2, max_size=6),
+       incoming=st.lists(st.integers(1, 6), min_size=1, max_size=5))
+def test_put_and_defrag_keep_exactly_the_systems_a_list_would(seed, sizes, incoming):
+    """Graduate a random subset, compact, then refill from a source batch: the live systems equal what plain Python list
+    operations on the per-system data give, in order."""
+    g = torch.Generator().manual_seed(seed)
+    data = [random_molecule(n, seed + i) for i, n in enumerate(sizes)]
+    src_data = [random_molecule(n, seed + 100 + i) for i, n in enumerate(incoming)]
+    cap_atoms = sum(sizes) + sum(incoming)
+    buf = Batch.empty(num_systems=len(sizes) + len(incoming), num_nodes=cap_atoms, num_edges=0, template=Batch.from_data_list(data))
+    buf.put(Batch.from_data_list(data), torch.ones(len(sizes), dtype=torch.bool))
+    gone = torch.rand(len(sizes), generator=g) < 0.5
+    buf.defrag(gone)
+    expect = [d for d, x in zip(data, gone.tolist()) if not x]
+    take = torch.rand(len(incoming), generator=g) < 0.7
+    buf.put(Batch.from_data_list(src_data), take)
+    expect += [d for d, x in zip(src_data, take.tolist()) if x]
+    assert buf.num_graphs == len(expect)
+    for k, d in enumerate(expect):
+        assert torch.equal(buf[k].positions, d.positions) and torch.equal(buf[k].atomic_numbers, d.atomic_numbers)
+
+
+# ---------------------------------------------------------------------------------------------------- storage
+@settings(max_examples=20, deadline=None)
+@given(seed=st.integers(0, 10_000), rows=st.integers(1, 200), width=st.integers(1, 5), chunk=st.integers(1, 64),
+       shards=st.sampled_from([None, 1, 2, 4]), compressor=st.sampled_from([None, "gzip", "zstd"]),
+       dtype=st.sampled_from(["float32", "float64", "int64", "uint8"]))
+def test_zarr_array_round_trips_any_chunking(tmp_path_factory, seed, rows, width, chunk, shards, compressor, dtype):
+    """Appends of uneven sizes, a partial overwrite and range reads return exactly what was written, whatever the chunk
+    size, shard size, codec and element type."""
+    import numpy as np
+
+    from nvalchemi_toolkit_b200.data.zarr_store import ZarrArray, ZarrArrayConfig
+
+    rng = np.random.default_rng(seed)
+    full = (rng.standard_normal((rows, width)) * 100).astype(dtype)
+    cfg = ZarrArrayConfig(chunk_rows=chunk, compressor=compressor, shard_rows=None if shards is None else shards * chunk)
+    arr = ZarrArray.create(tmp_path_factory.mktemp("z") / "a", (0, width), dtype, cfg)
+    pos = 0
+    while pos < rows:
+        step = int(rng.integers(1, max(2, rows // 3 + 1)))
+        arr.append(full[pos: pos + step])
+        pos += step
+    assert arr.shape == (rows, width)
+    lo = int(rng.integers(0, rows))
+    hi = int(rng.integers(lo, rows)) + 1
+    patch = (rng.standard_normal((hi - lo, width)) * 7).astype(dtype)
+    arr.write(lo, patch)
+    full[lo:hi] = patch
+    again = ZarrArray(arr.path)  # a fresh handle reads the files, not a cache
+    assert np.array_equal(again.read(), full)
+    a, b = sorted(int(x) for x in rng.integers(0, rows + 1, size=2))
+    assert np.array_equal(again.read(a, b), full[a:b])
+
+
+# ---------------------------------------------------------------------------------------------------- sampling / losses
+@settings(**SETTINGS)
+@given(weights=st.lists(st.floats(0.0, 50.0), min_size=1, max_size=8), total=st.integers(0, 500))
+def test_counts_from_weights_are_exact_and_within_one_of_proportional(weights, total):
+    from nvalchemi_toolkit_b200.data.datapipes import counts_from_weights
+
+    if sum(weights) <= 0:
+        with pytest.raises(ValueError):
+            counts_from_weights(weights, total)
+        return
+    counts = counts_from_weights(weights, total)
+    assert sum(counts) == total and all(c >= 0 for c in counts)
+    for c, w in zip(counts, weights):
+        assert abs(c - total * w / sum(weights)) < 1.0 + 1e-9
+        assert w > 0 or c == 0
+
+
+@settings(**SETTINGS)
+@given(seed=st.integers(0, 10_000), sizes=st.lists(st.integers(1, 6), min_size=1, max_size=6), frac=st.floats(0.0, 1.0))
+def test_masked_losses_equal_losses_on_the_labelled_subset(seed, sizes, frac):
+    """``ignore_nonfinite``: the value equals the plain loss evaluated on the labelled graphs only, and predictions of
+    unlabelled graphs receive exactly zero gradient."""
+    from nvalchemi_toolkit_b200.training.losses import EnergyMSELoss, ForceMSELoss
+
+    g = torch.Generator().manual_seed(seed)
+    b = random_batch(sizes, seed=seed)
+    nG, n = len(sizes), sum(sizes)
+    b.energy = torch.randn(nG, 1, generator=g)
+    b.forces = torch.randn(n, 3, generator=g)
+    missing = torch.rand(nG, generator=g) < frac
+    pe = torch.randn(nG, 1, generator=g, requires_grad=True)
+    pf = torch.randn(n, 3, generator=g, requires_grad=True)
+    labelled = (~missing).nonzero().reshape(-1).tolist()
+    energy, forces = b.energy.clone(), b.forces.clone()
+    b.energy = torch.where(missing[:, None], torch.full_like(energy, float("nan")), energy)
+    atom_missing = missing[b.batch_idx.long()]
+    b.forces = torch.where(atom_missing[:, None], torch.full_like(forces, float("inf")), forces)
+    le = EnergyMSELoss(ignore_nonfinite=True)({"energy": pe}, b)
+    lf = ForceMSELoss(ignore_nonfinite=True)({"forces": pf}, b)
+    (le + lf).backward()
+    assert torch.isfinite(pe.grad).all() and torch.isfinite(pf.grad).all()
+    assert float(pe.grad[missing].abs().sum()) == 0.0 and float(pf.grad[atom_missing].abs().sum()) == 0.0
+    if not labelled:
+        assert float(le.detach()) == 0.0 and float(lf.detach()) == 0.0
+        return
+    sub = b.index_select(labelled)
+    sub.energy, sub.forces = energy[labelled], forces[~atom_missing]
+    want_e = EnergyMSELoss()({"energy": pe.detach()[labelled]}, sub)
+    want_f = ForceMSELoss()({"forces": pf.detach()[~atom_missing]}, sub)
+    assert float(le.detach()) == pytest.approx(float(want_e), rel=1e-5, abs=1e-7)
+    assert float(lf.detach()) == pytest.approx(float(want_f), rel=1e-5, abs=1e-7)
+
+
+# ---------------------------------------------------------------------------------------------------- decomposition
+@settings(**SETTINGS)
+@given(seed=st.integers(0, 10_000), world=st.sampled_from([1, 2, 3, 4, 6, 8, 12]), n=st.integers(1, 200),
+       pbc=st.tuples(st.booleans(), st.booleans(), st.booleans()), skew=st.floats(0.0, 0.4))
+def test_spatial_partition_owns_every_atom_once_and_neighbours_are_mutual(seed, world, n, pbc, skew):
+    from nvalchemi_toolkit_b200.distributed.partitioner import SpatialPartitioner
+
+    g = torch.Generator().manual_seed(seed)
+    cell = torch.diag(20.0 + 20.0 * torch.rand(3, generator=g, dtype=torch.float64))
+    cell[1, 0], cell[2, 1] = skew * cell[0, 0], -skew * cell[1, 1]
+    part = SpatialPartitioner(cell, torch.tensor(pbc), world, cutoff=4.0)
+    assert part.grid[0] * part.grid[1] * part.grid[2] == world
+    # atoms anywhere in space (also outside the cell): wrapped or clamped into exactly one box
+    pos = (torch.rand(n, 3, generator=g, dtype=torch.float64) * 3.0 - 1.0) @ cell
+    owner = part.assign_atoms_to_ranks(pos)
+    assert owner.shape == (n,) and int(owner.min()) >= 0 and int(owner.max()) < world
+    assert bool(part.keeps_owner(pos, owner)[(part.fractional(pos) >= 0).all(-1) & (part.fractional(pos) < 1).all(-1)].all())
+    frac = part.fractional(pos)
+    inside = ((frac >= 0) & (frac < 1)).all(-1)
+    for r in range(world):
+        lo, hi = part.box(r)
+        mine = inside & (owner == r)
+        assert bool(((frac[mine] >= lo - 1e-12) & (frac[mine] <= hi + 1e-12)).all())
+        for other in part.neighbor_ranks(r):
+            assert other != r and r in part.neighbor_ranks(other)
