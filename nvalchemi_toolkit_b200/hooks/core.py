@@ -88,6 +88,11 @@ class HookRegistryMixin:
             raise ValueError(f"Hook frequency must be a positive integer, got {freq}")
         if stage is not None:
             hook.stage = stage
+        on_register = getattr(hook, "on_register", None)
+        if on_register is not None:
+            if not callable(on_register):
+                raise TypeError(f"Hook {type(hook).__name__}.on_register must be callable.")
+            on_register(self)  # first: hooks that work for several engines pick their default stage here
         custom = getattr(hook, "_runs_on_stage", None) is not None
         if getattr(hook, "stage", None) is None and not custom:
             raise TypeError(
@@ -101,11 +106,6 @@ class HookRegistryMixin:
                 f"Hook {hook!r} has stage={hook.stage!r} (type {type(hook.stage).__name__}), but this engine "
                 f"only accepts {names} stages."
             )
-        on_register = getattr(hook, "on_register", None)
-        if on_register is not None:
-            if not callable(on_register):
-                raise TypeError(f"Hook {type(hook).__name__}.on_register must be callable.")
-            on_register(self)
         self.hooks.append(hook)
 
     def _build_context(self, batch: Any) -> HookContext:
