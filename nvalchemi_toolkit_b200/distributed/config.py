@@ -30,6 +30,9 @@ class DomainConfig(BaseModel):
     strategy: StrategyKind = StrategyKind.HALO
     compile: bool = False                      # API parity only: True warns (kernels are hand-written, nothing is traced)
     require_nondegenerate: bool = True
+    #: raise (instead of warning on rank 0) when some rank's ghost layer covers the whole system: such a run is correct
+    #: but exercises no halo boundary, so tests of the decomposition should switch this on
+    strict_partition_health: bool = False
     mesh: Any = None
     mesh_dim: str = "domain"
     grid_dims: tuple[int, int, int] | None = None

@@ -59,6 +59,45 @@ def consolidate_outputs(out: dict, sharded: ShardedBatch, spec: MLIPSpec, halo: 
     return res
 
 
+def partition_health_verdict(n_owned: int, n_padded: int, group: Any, device: Any) -> tuple[bool, bool, int]:
+    """``(any_empty, any_trivial, n_global)``, identical on every rank (reference ``distributed_model.py:200-227``):
+    some rank owns nothing; some rank's owned + ghost rows already cover every atom (correct, but that rank does the
+    whole system's work).  One SUM for the atom count and one MAX over the two flags, so that no rank acts alone."""
+    import torch.distributed as dist
+
+    total = torch.tensor([float(n_owned)], dtype=torch.float64, device=device)
+    flags_in = None
+    if dist.is_available() and dist.is_initialized():
+        dist.all_reduce(total, group=group)
+    n_global = int(round(float(total)))
+    flags_in = torch.tensor([int(n_owned == 0), int(n_padded >= n_global)], dtype=torch.int32, device=device)
+    if dist.is_available() and dist.is_initialized():
+        dist.all_reduce(flags_in, op=dist.ReduceOp.MAX, group=group)
+    return bool(flags_in[0]), bool(flags_in[1]), n_global
+
+
+def resolve_partition_health(any_empty: bool, any_trivial: bool, n_global: int, *, world_size: int, strict: bool,
+                             rank: int) -> str | None:
+    """Act on a verdict (no collectives: every rank holds the same flags and therefore does the same thing).  An empty
+    rank is always an error.  A trivial decomposition (a rank whose halo covers the whole system) raises when ``strict``
+    (a force-equivalence check would prove nothing about the halo path), else rank 0 warns.  Returns the message."""
+    if any_empty:
+        raise RuntimeError(f"degenerate domain decomposition: a rank owns no atoms (world size {world_size}, {n_global} "
+                           "atoms); use fewer ranks or a larger system")
+    if not any_trivial or world_size == 1:
+        return None
+    msg = (f"trivial domain decomposition: a rank's ghost layer already covers all {n_global} atoms, so it evaluates the "
+           "whole system and nothing is gained from the decomposition (box / ranks <= about 2 x ghost width); use fewer "
+           "ranks or a larger system")
+    if strict:
+        raise RuntimeError(msg + " (strict_partition_health=True)")
+    if rank == 0:
+        import warnings
+
+        warnings.warn(msg + "; results are still correct", RuntimeWarning, stacklevel=3)
+    return msg
+
+
 def _keep_owned_senders(padded: Any, n_owned: int) -> None:
     """Edge partition for folding policies: a rank keeps the edges whose SENDER it owns (the receiver may be a ghost, its
     partial sum is folded into the owner afterwards), so every edge is evaluated exactly once over all ranks.  Rows of
@@ -108,6 +147,8 @@ class DistributedModel(nn.Module):
             raise ValueError("domain decomposition needs a full neighbour list (each owned row must be complete)")
         self._halo_builds = -1
         self.last_dispatch_stats: dict = {}
+        self.partition_health: str | None = None  # message of the one-time check (None: healthy or not yet run)
+        self._health_checked = False
 
     @property
     def wants_local_periodic(self) -> bool:
@@ -123,6 +164,13 @@ class DistributedModel(nn.Module):
             return consolidate_outputs(dict(out), sharded, spec)
         halo = sharded.halo_for(spec.ghost_width(self.config.cutoff, self.config.skin)) if self.own_halo else sharded.halo
         padded = sharded.padded_batch(halo)
+        if not self._health_checked:  # once, at the first halo forward (two small collectives)
+            self._health_checked = True
+            empty, trivial, n_global = partition_health_verdict(sharded.n_owned, sharded.n_owned + halo.n_ghost, self.group,
+                                                                padded.positions.device)
+            self.partition_health = resolve_partition_health(
+                empty and self.config.require_nondegenerate, trivial, n_global, world_size=sharded.world,
+                strict=self.config.strict_partition_health, rank=sharded.rank)
         if self.neighbor_hook is not None:
             if halo.num_builds != self._halo_builds:  # ghost rows changed identity: start from a fresh list
                 self.neighbor_hook._bufs = None

@@ -79,8 +79,14 @@ class ShardedBatch:
                                   hysteresis=config.migration_hysteresis)
         owner = part.assign_atoms_to_ranks(batch.positions)
         mine = torch.nonzero(owner == rank, as_tuple=False).flatten()
-        if config.require_nondegenerate and mine.numel() == 0:
-            raise RuntimeError(f"rank {rank} owns no atoms; use fewer ranks or set require_nondegenerate=False")
+        # The assignment is computed from the replicated system, so every rank sees every rank's count and all of them
+        # raise together (a rank that raised alone would leave the others waiting in their next collective).
+        counts = torch.bincount(owner.reshape(-1).long(), minlength=world)
+        empty = torch.nonzero(counts == 0).flatten().tolist()
+        if config.require_nondegenerate and empty:
+            raise RuntimeError(f"degenerate domain decomposition: rank(s) {empty} of {world} own no atoms of the "
+                               f"{batch.num_nodes}-atom system (rank grid {part.grid}); use fewer ranks, a larger system, "
+                               "or set require_nondegenerate=False")
         node = {k: v[mine] for k, v in _node_fields(batch).items()}
         owned = _make_batch(node, _system_fields(batch), batch)
         return cls(owned, mine.to(torch.int64), batch.num_nodes, part, config, spec, group, local_periodic=local_periodic)

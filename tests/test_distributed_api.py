@@ -879,3 +879,82 @@ def test_static_halo_replays_in_a_cuda_graph_across_rebuilds():
     torch.cuda.synchronize()
     ng2 = sh.halo.n_ghost
     assert torch.allclose(static_out[: n + ng2], halo_forward(x2, sh.halo)) and bool((static_out[n + ng2:] == 0).all())
+
+
+def _health_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import warnings
+
+        from nvalchemi_toolkit_b200.distributed.distributed_model import partition_health_verdict
+
+        torch.set_num_threads(1)
+        res = {}
+        # every rank reaches the same verdict although only rank 1 is empty / only rank 0 is trivial
+        res["verdict_empty"] = partition_health_verdict(0 if rank == 1 else 10, 12, None, "cpu")
+        res["verdict_trivial"] = partition_health_verdict(10, 20 if rank == 0 else 12, None, "cpu")
+        res["verdict_fine"] = partition_health_verdict(10, 14, None, "cpu")
+        model = _lj()
+        # 3 x 5.26 A box on two ranks with a 6 A ghost layer: each rank's halo holds every other atom
+        small = _lj_batch(3)
+        cfg = DomainConfig(cutoff=6.0, skin=0.0)
+        sh = ShardedBatch.from_batch(small, cfg, model.distribution_spec())
+        dm = DistributedModel(model, cfg)
+        with warnings.catch_warnings(record=True) as caught:
+            warnings.simplefilter("always")
+            dm(sh)
+            dm(sh)  # checked once
+        res["warned"] = sum("trivial domain decomposition" in str(w.message) for w in caught)
+        res["message"] = dm.partition_health
+        strict = DomainConfig(cutoff=6.0, skin=0.0, strict_partition_health=True)
+        try:
+            DistributedModel(model, strict)(ShardedBatch.from_batch(small, strict, model.distribution_spec()))
+            res["strict"] = "ran"
+        except RuntimeError as exc:
+            res["strict"] = str(exc)
+        # all atoms in one half of the box: the other rank would own nothing, and BOTH ranks raise
+        lopsided = _lj_batch(3)
+        lopsided["positions"] = lopsided.positions * torch.tensor([0.3, 1.0, 1.0], dtype=torch.float64) + torch.tensor(
+            [1.0, 0.0, 0.0], dtype=torch.float64)  # x within [1, 6] A of a 15.8 A box, clear of the periodic seam
+        try:
+            ShardedBatch.from_batch(lopsided, DomainConfig(cutoff=6.0, skin=0.0, grid_dims=(2, 1, 1)), model.distribution_spec())
+            res["empty"] = "built"
+        except RuntimeError as exc:
+            res["empty"] = str(exc)
+        q.put((rank, res))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_partition_health_verdict_is_collective_and_acted_on_identically():
+    import torch.multiprocessing as mp
+
+    from nvalchemi_toolkit_b200.distributed.distributed_model import resolve_partition_health
+
+    # the pure part: what each verdict leads to
+    assert resolve_partition_health(False, False, 100, world_size=4, strict=True, rank=0) is None
+    with pytest.raises(RuntimeError, match="owns no atoms"):
+        resolve_partition_health(True, False, 100, world_size=4, strict=False, rank=2)
+    with pytest.raises(RuntimeError, match="strict_partition_health"):
+        resolve_partition_health(False, True, 100, world_size=4, strict=True, rank=1)
+    assert resolve_partition_health(False, True, 100, world_size=1, strict=True, rank=0) is None  # one rank: nothing to gain anyway
+    with pytest.warns(RuntimeWarning, match="trivial domain decomposition"):
+        msg = resolve_partition_health(False, True, 100, world_size=2, strict=False, rank=0)
+    assert "100 atoms" in msg
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_health_worker, args=(r, 2, 29697, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=240) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+    for r in range(2):
+        assert res[r]["verdict_empty"] == (True, True, 10)   # 10 atoms in total, and rank 0's 12 padded rows cover them
+        assert res[r]["verdict_trivial"] == (False, True, 20) and res[r]["verdict_fine"] == (False, False, 20)
+        assert "trivial domain decomposition" in res[r]["message"]
+        assert "strict_partition_health" in res[r]["strict"]
+        assert "own no atoms" in res[r]["empty"] and "[1]" in res[r]["empty"]
+    assert res[0]["warned"] == 1 and res[1]["warned"] == 0  # rank 0 speaks, once
