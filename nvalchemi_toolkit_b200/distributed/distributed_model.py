@@ -114,6 +114,23 @@ def _keep_owned_senders(padded: Any, n_owned: int) -> None:
     num.copy_(valid.sum(1).to(num.dtype))
 
 
+def _keep_edges(padded: Any, keep: torch.Tensor) -> None:
+    """Edge-list form of the two rules above: every edge ``(receiver, sender)`` exists on each rank that holds both
+    atoms, so a per-receiver sum must see it on exactly one of them.  The edge group is rebuilt from the kept rows (one
+    system per padded batch, so the per-system edge count is the number kept).  Reference: the edge-list branch of
+    ``nvalchemi/distributed/distributed_model.py`` marks such rows as padding for the wrappers to drop."""
+    from nvalchemi_toolkit_b200.data.level_storage import SegmentedLevelStorage
+
+    edges = padded._storage.groups["edges"]
+    data = {k: v[keep] for k, v in edges.data.items()}
+    n = int(next(iter(data.values())).shape[0]) if data else 0
+    counts = torch.zeros(padded.num_graphs, dtype=torch.int32, device=keep.device)
+    if n:
+        owner = padded.batch_idx.long()[data["neighbor_list"][:, 0]]
+        counts = torch.bincount(owner, minlength=padded.num_graphs).to(torch.int32)
+    padded._storage.groups["edges"] = SegmentedLevelStorage(data, counts, num_elements=n, device=padded.device)
+
+
 class DistributedModel(nn.Module):
     def __init__(self, model: Any, config: DomainConfig, spec: MLIPSpec | None = None, group: Any = None,
                  max_neighbors: int | None = None, own_halo: bool = False) -> None:
@@ -176,10 +193,17 @@ class DistributedModel(nn.Module):
                 self.neighbor_hook._bufs = None
                 self._halo_builds = halo.num_builds
             self.neighbor_hook(SimpleNamespace(batch=padded), None)
+            coo = getattr(padded, "neighbor_matrix", None) is None  # an edge-list model (``NeighborListFormat.COO``)
             if spec.consolidation == Consolidation.DIRECT_MASKED or (spec.refresh_per_layer and not self._policy_folds()):
-                padded.num_neighbors[sharded.n_owned:] = 0  # ghost atoms send, they do not receive
+                if coo:
+                    _keep_edges(padded, padded.neighbor_list[:, 0] < sharded.n_owned)
+                else:
+                    padded.num_neighbors[sharded.n_owned:] = 0  # ghost atoms send, they do not receive
             elif spec.refresh_per_layer and halo.n_ghost > 0:
-                _keep_owned_senders(padded, sharded.n_owned)  # fold policy: every edge lives on its sender's owner
+                if coo:
+                    _keep_edges(padded, padded.neighbor_list[:, 1] < sharded.n_owned)
+                else:
+                    _keep_owned_senders(padded, sharded.n_owned)  # fold policy: every edge lives on its sender's owner
         if spec.refresh_per_layer and halo.n_ghost > 0:
             from nvalchemi_toolkit_b200.distributed.dispatch import HaloDispatchMode
 

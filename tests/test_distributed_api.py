@@ -958,3 +958,65 @@ def test_partition_health_verdict_is_collective_and_acted_on_identically():
         assert "strict_partition_health" in res[r]["strict"]
         assert "own no atoms" in res[r]["empty"] and "[1]" in res[r]["empty"]
     assert res[0]["warned"] == 1 and res[1]["warned"] == 0  # rank 0 speaks, once
+
+
+def _coo_pair_model():
+    """A pair potential that reads an EDGE LIST (``NeighborListFormat.COO``) and knows nothing about decomposition."""
+    from nvalchemi_toolkit_b200.distributed.spec import Consolidation, MLIPSpec
+    from nvalchemi_toolkit_b200.models.base import ModelConfig, NeighborConfig, NeighborListFormat
+
+    class CooPair(torch.nn.Module, BaseModelMixin):
+        def __init__(self):
+            super().__init__()
+            self.model_config = ModelConfig(outputs=frozenset({"energy", "forces"}),
+                                            neighbor_config=NeighborConfig(cutoff=4.0, format=NeighborListFormat.COO))
+
+        def forward(self, data, **kw):
+            nl = data.neighbor_list.long()
+            i, j = nl[:, 0], nl[:, 1]
+            r = data.positions[j] - data.positions[i]
+            shifts = getattr(data, "shifts", None)
+            if shifts is not None:
+                r = r + shifts.to(r.dtype)
+            d = r.norm(dim=-1)
+            n = data.positions.shape[0]
+            e_atom = torch.zeros(n, dtype=r.dtype).index_add_(0, i, 0.25 * (d - 4.0) ** 2)   # half of each pair's energy
+            forces = torch.zeros(n, 3, dtype=r.dtype).index_add_(0, i, ((d - 4.0) / d)[:, None] * r)
+            energy = torch.zeros(data.num_graphs, dtype=r.dtype).index_add_(0, data.batch_idx.long(), e_atom)
+            return {"energy": energy.reshape(-1, 1), "forces": forces}
+
+        def distribution_spec(self, strategy=None):
+            return MLIPSpec("coo_pair", message_passes=1, consolidation=Consolidation.DIRECT_MASKED)
+
+    return CooPair()
+
+
+def test_edge_list_model_keeps_only_edges_of_owned_receivers():
+    """One rank, periodic images as ghosts: every edge between two local atoms exists in the padded edge list, and only
+    those whose receiver is owned may count; energy and forces equal the periodic single-process evaluation."""
+    model = _coo_pair_model()
+    batch = Batch.from_data_list([fcc_supercell(3, a=3.9, z=29, noise=0.1, seed=5, dtype=torch.float64)])
+    ref = _reference(model, batch.clone())
+    cfg = DomainConfig(cutoff=4.0, skin=0.0)
+    sh = ShardedBatch.from_batch(batch, cfg, model.distribution_spec())
+    dm = DistributedModel(model, cfg)
+    out = dm(sh)
+    assert sh.n_ghost > 0
+    assert torch.allclose(out["forces"], ref["forces"], atol=1e-10) and torch.allclose(out["energy"], ref["energy"], atol=1e-9)
+    # without the filter the ghost receivers' edges would have been counted as well
+    padded = sh.padded_batch(sh.halo)
+    dm.neighbor_hook._bufs = None
+    from types import SimpleNamespace
+
+    dm.neighbor_hook(SimpleNamespace(batch=padded), None)
+    every = int(padded.neighbor_list.shape[0])
+    kept = int((padded.neighbor_list[:, 0] < sh.n_owned).sum())
+    assert kept == int(ref_edges(batch, model)) and every > kept
+
+
+def ref_edges(batch, model):
+    from types import SimpleNamespace
+
+    b = batch.clone()
+    NeighborListHook(model.model_config.neighbor_config)(SimpleNamespace(batch=b), None)
+    return b.neighbor_list.shape[0]
