@@ -231,3 +231,61 @@ def test_spatial_partition_owns_every_atom_once_and_neighbours_are_mutual(seed, 
         assert bool(((frac[mine] >= lo - 1e-12) & (frac[mine] <= hi + 1e-12)).all())
         for other in part.neighbor_ranks(r):
             assert other != r and r in part.neighbor_ranks(other)
+
+
+# ---------------------------------------------------------------------------------------------------- level storages
+@settings(**SETTINGS)
+@given(seed=st.integers(0, 10_000), ops=st.lists(st.sampled_from(["put", "defrag"]), min_size=1, max_size=8))
+def test_level_storages_follow_a_list_model_through_random_put_and_defrag(seed, ops):
+    """A fixed-capacity segmented storage (atoms of several systems) and a uniform one (one row per system) driven by
+    the same random sequence of appends and compactions always hold exactly what a Python list of segments holds."""
+    from nvalchemi_toolkit_b200.data.level_storage import SegmentedLevelStorage, UniformLevelStorage
+
+    g = torch.Generator().manual_seed(seed)
+    seg_cap, elem_cap = 12, 60
+    seg = SegmentedLevelStorage({"x": torch.zeros(elem_cap, 2), "z": torch.zeros(elem_cap, dtype=torch.int64)},
+                                torch.zeros(seg_cap, dtype=torch.int32), num_segments=0, num_elements=0,
+                                segment_capacity=seg_cap, element_capacity=elem_cap)
+    uni = UniformLevelStorage({"e": torch.zeros(seg_cap, 1)}, num_valid=0, capacity=seg_cap)
+    model: list[tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = []   # (x rows, z rows, e row) per live segment
+    for op in ops:
+        if op == "put":
+            k = int(torch.randint(1, 4, (1,), generator=g))
+            lens = torch.randint(1, 6, (k,), generator=g)
+            xs = [torch.randn(int(n), 2, generator=g) for n in lens]
+            zs = [torch.randint(1, 90, (int(n),), generator=g) for n in lens]
+            es = torch.randn(k, 1, generator=g)
+            src = SegmentedLevelStorage({"x": torch.cat(xs), "z": torch.cat(zs)}, lens.to(torch.int32))
+            src_u = UniformLevelStorage({"e": es})
+            take = torch.nonzero(torch.rand(k, generator=g) < 0.7).flatten()
+            # what fits, in order (the storages raise when asked for more than they can hold)
+            fit = []
+            n_seg, n_el = len(model), sum(m[0].shape[0] for m in model)
+            for t in take.tolist():
+                if n_seg + 1 <= seg_cap and n_el + int(lens[t]) <= elem_cap:
+                    fit.append(t)
+                    n_seg, n_el = n_seg + 1, n_el + int(lens[t])
+            fit_t = torch.tensor(fit, dtype=torch.int64)
+            seg.put(src, fit_t)
+            uni.put(src_u, fit_t)
+            model += [(xs[t], zs[t], es[t]) for t in fit]
+            if take.numel() > len(fit) and take.numel() > 0:
+                with pytest.raises(ValueError):
+                    huge = SegmentedLevelStorage({"x": torch.zeros(elem_cap + 1, 2), "z": torch.zeros(elem_cap + 1, dtype=torch.int64)},
+                                                 torch.tensor([elem_cap + 1], dtype=torch.int32))
+                    seg.put(huge, torch.tensor([0]))
+        else:
+            if not model:
+                continue
+            keep = torch.nonzero(torch.rand(len(model), generator=g) < 0.6).flatten()
+            seg.defrag(keep)
+            uni.defrag(keep)
+            model = [model[i] for i in keep.tolist()]
+        assert seg.num_segments == uni.num_valid == len(model)
+        assert seg.num_elements == sum(m[0].shape[0] for m in model)
+        assert seg.batch_ptr.tolist() == [0] + list(itertools.accumulate(m[0].shape[0] for m in model))
+        if model:
+            assert torch.equal(seg["x"], torch.cat([m[0] for m in model])) and torch.equal(seg["z"], torch.cat([m[1] for m in model]))
+            assert torch.equal(uni["e"], torch.stack([m[2] for m in model]))
+            assert seg.batch_idx.tolist() == [i for i, m in enumerate(model) for _ in range(m[0].shape[0])]
+        assert seg.free_segments() == seg_cap - len(model) and uni.free_rows() == seg_cap - len(model)
