@@ -84,3 +84,24 @@ def test_pipeline_benchmark_two_lanes_of_two_stages(tmp_path):
     line = [ln for ln in res.stdout.splitlines() if ln.startswith("{")][-1]
     out = json.loads(line)
     assert out["lanes"] == 2 and out["systems_finished"] == 6 and out["unit"] == "atom-steps/s" and out["value"] > 0
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.gpu
+def test_halo_bandwidth_benchmark_single_process_mode():
+    """The halo-kernel benchmark in its one-GPU mode (peers are local buffers): every kernel runs, the byte counts follow
+    from the arguments and the status word stays clear."""
+    import subprocess
+    import sys
+
+    out = subprocess.run([sys.executable, "-m", "nvalchemi_toolkit_b200.benchmark.halo_bandwidth", "--single-process", "--rows", "4096",
+                          "--owned", "8192", "--peers", "2", "--iters", "3"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    res = json.loads(out.stdout.strip().splitlines()[-1])
+    assert res["single_process"] and res["world"] == 3 and res["ghost_rows"] == 4096 and res["status"] == 0
+    for key, width in (("pull_features_512", 512), ("push_add_features_512", 512), ("pull_add_features_512", 512),
+                       ("pull_positions_3", 3), ("push_add_positions_3", 3), ("pull_add_positions_3", 3)):
+        assert res[key]["bytes"] == 4096 * width * 4 and res[key]["ms"] > 0 and res[key]["gbs"] > 0
+    assert "barrier_us" not in res

@@ -392,3 +392,58 @@ def test_single_launch_push_allreduce_with_an_emulated_peer(dtype):
         assert torch.equal(peer_region[parity, 0, :n], x0)  # my values arrived in the peer's slot for rank 0
         assert int(ctx.arena._bufs[1][ctx.arena.offset_of(red.push_flags):].view(torch.int32)[0]) == call
     assert red.small_calls == 3 and red.fallbacks == 0 and ctx.status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(8))
+def test_native_neighbor_search_equals_brute_force_on_random_cells(seed):
+    """Cell-list kernels on random triclinic cells with mixed periodicity, several systems per batch and both precisions
+    against an explicit enumeration of periodic images (pairs within 1e-4 of the cutoff may fall on either side)."""
+    import itertools
+    import math
+
+    from nvalchemi_toolkit_b200 import neighbors as nb
+
+    g = torch.Generator().manual_seed(seed)
+    dtype = torch.float64 if seed % 2 else torch.float32
+    n_sys = 1 + seed % 3
+    cutoff = 2.0 + 0.4 * seed
+    cells, pbcs, poss, sizes = [], [], [], []
+    for s in range(n_sys):
+        cell = torch.diag(5.0 + 4.0 * torch.rand(3, generator=g, dtype=torch.float64))
+        skew = 0.4 * torch.rand(1, generator=g).item()
+        cell[1, 0], cell[2, 0], cell[2, 1] = skew * cell[0, 0], -skew * cell[0, 0], skew * cell[1, 1]
+        n = int(torch.randint(20, 120, (1,), generator=g))
+        cells.append(cell)
+        pbcs.append(torch.rand(3, generator=g) < 0.7)
+        poss.append((torch.rand(n, 3, generator=g, dtype=torch.float64) * 1.4 - 0.2) @ cell)  # some atoms outside the cell
+        sizes.append(n)
+    pos = torch.cat(poss)
+    ptr = [0] + list(itertools.accumulate(sizes))
+    bidx = torch.cat([torch.full((n,), s, dtype=torch.int32) for s, n in enumerate(sizes)])
+    dev = "cuda"
+    nm, num, sh = nb.neighbor_matrix(pos.to(dtype).to(dev), torch.stack(cells).to(dtype).to(dev), torch.stack(pbcs).to(dev),
+                                     bidx.to(dev), torch.tensor(ptr, dtype=torch.int32, device=dev), cutoff, 1024)
+    nm, num, sh = nm.cpu(), num.cpu(), sh.cpu()
+    got = set()
+    for i in range(pos.shape[0]):
+        for k in range(int(num[i])):
+            got.add((i, int(nm[i, k])) + tuple(int(x) for x in sh[i, k]))
+    assert len(got) == int(num.sum())
+    want, tol = set(), 1e-4
+    borderline = set()
+    for s in range(n_sys):
+        cell, pbc, lo = cells[s], pbcs[s].tolist(), ptr[s]
+        p = poss[s].to(dtype).double()  # the coordinates the kernel saw
+        heights = 1.0 / torch.linalg.inv(cell).norm(dim=0)
+        extent = (p @ torch.linalg.inv(cell))
+        span = (extent.max(0).values - extent.min(0).values)
+        reach = [int(math.ceil(cutoff / float(h) + float(w))) if per else 0 for h, w, per in zip(heights, span, pbc)]
+        for shift in itertools.product(*[range(-r, r + 1) for r in reach]):
+            d = (p[None, :, :] + torch.tensor(shift, dtype=torch.float64) @ cell - p[:, None, :]).norm(dim=-1)
+            if shift == (0, 0, 0):
+                d.fill_diagonal_(float("inf"))
+            for i, j in (d < cutoff + tol).nonzero().tolist():
+                entry = (lo + i, lo + j) + shift
+                (want if d[i, j] < cutoff - tol else borderline).add(entry)
+    assert want <= got and got <= (want | borderline), (len(want - got), len(got - want - borderline))
