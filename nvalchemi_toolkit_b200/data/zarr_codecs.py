@@ -184,7 +184,9 @@ def encode(arr: np.ndarray, codecs: Sequence[dict], dtype: np.dtype) -> bytes:
     if names[ser] == "sharding_indexed":
         raw = encode_shard(arr, codecs[ser]["configuration"], dtype)
     else:
-        raw = np.ascontiguousarray(arr).astype(dtype.newbyteorder("<") if dtype.itemsize > 1 else dtype, copy=False).tobytes()
+        endian = codecs[ser].get("configuration", {}).get("endian", "little")
+        order = "<" if endian == "little" else ">"
+        raw = np.ascontiguousarray(arr).astype(dtype.newbyteorder(order) if dtype.itemsize > 1 else dtype, copy=False).tobytes()
     for c in codecs[ser + 1:]:
         n, cfg = c["name"], c.get("configuration", {})
         if n == "gzip":

@@ -329,3 +329,25 @@ def test_dataset_field_names_get_batch_and_close(tmp_path):
         assert b.num_graphs == 2 and torch.allclose(b[0].positions, data[3].positions)
     with pytest.raises(RuntimeError):
         ds.fetch([0])  # the worker pool is gone after close
+
+
+def test_crc32c_known_vectors_and_codec_checks():
+    """Castagnoli CRC against the published check values (RFC 3720 appendix B.4) and the codec-chain validation."""
+    import numpy as np
+
+    from nvalchemi_toolkit_b200.data import zarr_codecs
+
+    assert zarr_codecs.crc32c(b"") == 0
+    assert zarr_codecs.crc32c(b"123456789") == 0xE3069283
+    assert zarr_codecs.crc32c(bytes(32)) == 0x8A9136AA
+    assert zarr_codecs.crc32c(bytes([0xFF] * 32)) == 0x62A8AB43
+    assert zarr_codecs.crc32c(bytes(range(32))) == 0x46DD794E
+    with pytest.raises((ValueError, NotImplementedError)):
+        zarr_codecs.check_supported([{"name": "bytes", "configuration": {"endian": "little"}}, {"name": "lz77-homebrew"}])
+    chain = [{"name": "bytes", "configuration": {"endian": "little"}}, {"name": "gzip", "configuration": {"level": 1}}]
+    arr = np.arange(24, dtype="<f4").reshape(4, 6)
+    raw = zarr_codecs.encode(arr, chain, np.dtype("float32"))
+    assert np.array_equal(zarr_codecs.decode(raw, chain, np.dtype("float32"), [4, 6]), arr)
+    big = [{"name": "bytes", "configuration": {"endian": "big"}}]
+    assert zarr_codecs.encode(arr, big, np.dtype("float32")) == arr.astype(">f4").tobytes()
+    assert np.array_equal(zarr_codecs.decode(arr.astype(">f4").tobytes(), big, np.dtype("float32"), [4, 6]), arr)
