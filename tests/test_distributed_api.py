@@ -1020,3 +1020,79 @@ def ref_edges(batch, model):
     b = batch.clone()
     NeighborListHook(model.model_config.neighbor_config)(SimpleNamespace(batch=b), None)
     return b.neighbor_list.shape[0]
+
+
+def _helpers_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nvalchemi_toolkit_b200.distributed import helpers
+
+        torch.set_num_threads(1)
+        model = _lj()
+        batch = _lj_batch(4)
+        cfg = DomainConfig(cutoff=6.0, skin=0.0)
+        sh = ShardedBatch.from_batch(batch, cfg, model.distribution_spec())
+        n, ng = sh.n_owned, sh.n_ghost
+        gid = sh.global_ids
+        res = {"n": n, "ng": ng}
+        # a per-atom quantity known globally: f(global id)
+        feat = torch.stack([gid.double(), (gid * gid).double()], dim=1)
+        padded = helpers.refresh_ghosts(feat, sh)
+        ghost_gid = sh.halo.forward(gid.double().reshape(-1, 1)).reshape(-1).long()
+        res["refresh_ok"] = bool(torch.equal(padded[:n], feat) and torch.equal(padded[n:, 1], (ghost_gid * ghost_gid).double()))
+        # ghost rows each contribute 1: an owner receives as many as it has copies elsewhere; the total is conserved
+        back = helpers.scatter_to_owners(torch.ones(ng, 1, dtype=torch.float64), torch.zeros(n, 1, dtype=torch.float64), sh)
+        total = back.sum().reshape(1)
+        dist.all_reduce(total)
+        ghosts = torch.tensor([float(ng)])
+        dist.all_reduce(ghosts)
+        res["scatter_total"], res["ghost_total"] = float(total), float(ghosts)
+        # weighted per-system sums over owned + ghost rows equal the global sum once reduced
+        w = sh.owned_mask().double()
+        bidx = torch.zeros(n + ng, dtype=torch.long)
+        s = helpers.system_sum(padded[:, 0], bidx, 1, weights=w, distributed=True)
+        res["system_sum"] = float(s)
+        # uniform charge shift to a target total, with global sums and counts
+        q_local = torch.sin(torch.cat([gid, ghost_gid]).double())
+        fixed = helpers.total_charge_correction(q_local, torch.tensor([2.5], dtype=torch.float64), bidx, weights=w, distributed=True)
+        tot = (fixed * w).sum().reshape(1)
+        dist.all_reduce(tot)
+        res["charge_total"] = float(tot)
+        res["charge_shift_uniform"] = float((fixed - q_local).std())
+        rows = helpers.gather_replicated(torch.full((rank + 1, 2), float(rank)))
+        res["gathered"] = rows[:, 0].tolist()
+        q.put((rank, res))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_model_author_helpers_single_process_and_two_ranks():
+    import torch.multiprocessing as mp
+
+    from nvalchemi_toolkit_b200.distributed import helpers
+
+    # no process group: identities and plain local reductions
+    x = torch.arange(6.0).reshape(3, 2)
+    assert helpers.refresh_ghosts(x) is x and helpers.scatter_to_owners(torch.ones(2, 2), x) is x and helpers.to_local(x) is x
+    s = helpers.system_sum(torch.tensor([1.0, 2.0, 3.0, 4.0]), torch.tensor([0, 0, 1, 1]), 2, weights=torch.tensor([1, 0, 1, 1]))
+    assert s.tolist() == [1.0, 7.0]
+    fixed = helpers.total_charge_correction(torch.tensor([0.1, 0.2, 0.3, -0.2]), torch.tensor([0.0, 1.0]), torch.tensor([0, 0, 1, 1]))
+    assert torch.allclose(fixed, torch.tensor([-0.05, 0.05, 0.75, 0.25]))
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_helpers_worker, args=(r, 2, 29699, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=240) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+    n_total = res[0]["n"] + res[1]["n"]
+    assert n_total == 256
+    for r in range(2):
+        assert res[r]["ng"] > 0 and res[r]["refresh_ok"]
+        assert res[r]["scatter_total"] == res[r]["ghost_total"] > 0
+        assert res[r]["system_sum"] == pytest.approx(n_total * (n_total - 1) / 2)
+        assert res[r]["charge_total"] == pytest.approx(2.5, abs=1e-9) and res[r]["charge_shift_uniform"] < 1e-12
+        assert res[r]["gathered"] == [0.0, 1.0, 1.0]
