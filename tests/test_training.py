@@ -483,3 +483,47 @@ def test_composed_loss_weight_normalisation_targets_and_supervised_helper():
     round_trip = ComposedLossFunction.from_spec(ComposedLossFunction([EnergyMSELoss(atom_weighted=True, ignore_nonfinite=True),
                                                                       ForceMSELoss(normalize_by_atom_count=False)]).to_spec())
     assert round_trip.terms[0].atom_weighted and round_trip.terms[0].ignore_nonfinite and not round_trip.terms[1].normalize_by_atom_count
+
+
+def test_runtime_helpers_freeze_and_mode_contexts_and_rank_resolution(monkeypatch):
+    from types import SimpleNamespace
+
+    from nvalchemi_toolkit_b200.training import distributed as tdist
+    from nvalchemi_toolkit_b200.training import runtime
+
+    models = {"main": torch.nn.Linear(2, 2), "teacher": torch.nn.Linear(2, 2)}
+    models["teacher"].bias.requires_grad_(False)  # already frozen by the user: must stay frozen afterwards
+    models["teacher"].eval()
+    with runtime.freeze_unconfigured_models(models, {"main": object()}):
+        assert all(p.requires_grad for p in models["main"].parameters())
+        assert not any(p.requires_grad for p in models["teacher"].parameters())
+    assert models["teacher"].weight.requires_grad and not models["teacher"].bias.requires_grad
+    with runtime.train_configured_models(models, {"main": object()}):
+        assert models["main"].training and not models["teacher"].training
+        models["teacher"].train()  # whatever happens inside ...
+    assert models["main"].training and not models["teacher"].training  # ... the modes of before come back
+    try:
+        with runtime.freeze_unconfigured_models(models, {}):
+            raise KeyError("boom")
+    except KeyError:
+        pass
+    assert models["main"].weight.requires_grad  # restored on the error path too
+    moved = runtime.move_to_devices(models, ["cpu"])
+    assert set(moved) == {"main", "teacher"} and moved["teacher"].weight.device.type == "cpu"
+    with pytest.raises(NotImplementedError, match="DDPHook"):
+        runtime.configure_parallelism("fsdp")
+    runtime.configure_parallelism("none")
+    with pytest.raises(TypeError):
+        runtime.validate_training_fn(lambda batch: None)
+    runtime.validate_training_fn(lambda model, batch: None)
+    # rank resolution: a manager object wins, then the process group, then the launcher's environment
+    manager = SimpleNamespace(rank=3, world_size=8, local_rank=1)
+    assert (tdist.get_rank(manager), tdist.get_world_size(manager), tdist.get_local_rank(manager)) == (3, 8, 1)
+    monkeypatch.setenv("RANK", "5")
+    monkeypatch.setenv("WORLD_SIZE", "6")
+    monkeypatch.setenv("LOCAL_RANK", "2")
+    assert (tdist.get_rank(), tdist.get_world_size(), tdist.get_local_rank()) == (5, 6, 2)
+    t = torch.tensor([2.0])
+    assert tdist.all_reduce(t, "max") is t and float(t) == 2.0  # no process group: identity
+    tdist.barrier()
+    tdist.destroy_distributed()
