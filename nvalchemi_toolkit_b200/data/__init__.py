@@ -7,4 +7,20 @@ from nvalchemi_toolkit_b200.data.level_storage import (
 )
 
 __all__ = ["AtomicData", "Batch", "DataMixin", "LevelSchema", "MultiLevelStorage", "SegmentedLevelStorage",
-           "UniformLevelStorage"]
+           "UniformLevelStorage", "AtomicDataZarrReader", "AtomicDataZarrWriter", "BatchDatasetProtocol", "Compose",
+           "DataLoader", "Dataset", "InMemoryDataset", "MultiDataset", "Reader", "transforms"]
+
+_LAZY = {"AtomicDataZarrReader": "zarr_store", "AtomicDataZarrWriter": "zarr_store", "ZarrWriteConfig": "zarr_store",
+         "ZarrArrayConfig": "zarr_store", "BatchDatasetProtocol": "datapipes", "Compose": "transforms", "DataLoader": "datapipes",
+         "Dataset": "datapipes", "InMemoryDataset": "datapipes", "MultiDataset": "datapipes", "Reader": "datapipes",
+         "MultiDatasetSampler": "datapipes", "MultiDatasetBatchSampler": "datapipes", "FixedCompositionBatchSampler": "datapipes"}
+
+
+def __getattr__(name: str):  # datapipes and Zarr IO load on first use
+    import importlib
+
+    if name in ("transforms", "datapipes", "zarr_store"):
+        return importlib.import_module(f"nvalchemi_toolkit_b200.data.{name}")
+    if name in _LAZY:
+        return getattr(importlib.import_module(f"nvalchemi_toolkit_b200.data.{_LAZY[name]}"), name)
+    raise AttributeError(name)

@@ -11,7 +11,7 @@ from __future__ import annotations
 import abc
 import concurrent.futures as cf
 import math
-from typing import Any, Callable, Iterator, Sequence
+from typing import Any, Callable, Iterator, Protocol, Sequence
 
 import torch
 
@@ -40,22 +40,7 @@ class Reader(abc.ABC):
         return int(d["positions"].shape[0]), int(m.get("num_edges", 0))
 
 
-class Compose:
-    """Chain of ``(data, meta) -> (data, meta)`` transforms."""
-
-    def __init__(self, transforms: Sequence[Callable]) -> None:
-        self.transforms = list(transforms)
-
-    def __call__(self, data: Any, meta: dict[str, Any]) -> tuple[Any, dict[str, Any]]:
-        for t in self.transforms:
-            data, meta = t(data, meta)
-        return data, meta
-
-    def __add__(self, other: "Compose | Callable") -> "Compose":
-        return Compose(self.transforms + (other.transforms if isinstance(other, Compose) else [other]))
-
-    def __len__(self) -> int:
-        return len(self.transforms)
+from nvalchemi_toolkit_b200.data.transforms import Compose  # noqa: E402,F401  (kept importable from here)
 
 
 def _to_atomic_data(d: dict[str, torch.Tensor], levels: dict[str, str]) -> AtomicData:
@@ -67,6 +52,18 @@ def _to_atomic_data(d: dict[str, torch.Tensor], levels: dict[str, str]) -> Atomi
         lvl = levels.get(k, "node")
         {"node": data.add_node_property, "edge": data.add_edge_property, "system": data.add_system_property}[lvl](k, v)
     return data
+
+
+class BatchDatasetProtocol(Protocol):
+    """What :class:`DataLoader` and the samplers need from a dataset (reference ``datapipes/dataset.py:78-142``):
+    a length, indexed samples ``(item, metadata)``, ``get_metadata(i) -> (num_atoms, num_edges)`` for size-aware
+    sampling and, optionally, ``fetch(indices) -> Future[list[(item, metadata)]]`` for windowed asynchronous reads."""
+
+    def __len__(self) -> int: ...
+
+    def __getitem__(self, idx: int) -> tuple[Any, dict[str, Any]]: ...
+
+    def get_metadata(self, idx: int) -> tuple[int, int]: ...
 
 
 class Dataset:

@@ -28,8 +28,16 @@ from nvalchemi_toolkit_b200.distributed.ops import (ShardTensor, distributed_all
 from nvalchemi_toolkit_b200.distributed.storage_policy import (GraphParallelPolicy, HaloStoragePolicy, PlainShard,
                                                                RefreshOnlyHaloPolicy, StoragePolicy, policy_from_dict,
                                                                policy_to_dict)
-from nvalchemi_toolkit_b200.distributed.dispatch import (AdapterRegistry, FunctionAdapter, HaloDispatchMode, MethodAdapter,
-                                                         ModuleForwardAdapter, OpAdapter, current_dispatch)
+from nvalchemi_toolkit_b200.distributed.dispatch import (AdapterRegistry, AdapterStatus, FunctionAdapter, HaloDispatchMode,
+                                                         JitAdapter, MethodAdapter, ModuleForwardAdapter, OpAdapter,
+                                                         PythonAdapter, current_dispatch)
+from nvalchemi_toolkit_b200.distributed.output_kinds import OutputKind, OutputSpec, Reduce
+from nvalchemi_toolkit_b200.distributed.context import current_dd_context, reshard_by_destination
+from nvalchemi_toolkit_b200.distributed._runtime import (DistributedManager, collective_device, resolve_global_rank,
+                                                         resolve_world_size)
+from nvalchemi_toolkit_b200.distributed.helpers import (autograd_target, distributed_method, localize,
+                                                        neighbor_refresh_adapters, refresh_neighbors, scatter_to_owners,
+                                                        system_sum, to_local)
 from nvalchemi_toolkit_b200.distributed.graph_padder import (COOPadder, DenseBatchPadder, DensePadder, GraphPadder,
                                                              cap_agreement_group, resolve_cap)
 from nvalchemi_toolkit_b200.distributed import helpers
@@ -48,4 +56,25 @@ __all__ = ["StaticHalo", "StaticHaloRouting", "halo_exchange_fixed", "halo_forwa
            "RefreshOnlyHaloPolicy", "GraphParallelPolicy", "policy_to_dict", "policy_from_dict", "HaloDispatchMode",
            "current_dispatch", "OpAdapter", "FunctionAdapter", "MethodAdapter", "ModuleForwardAdapter", "AdapterRegistry",
            "GraphPadder", "COOPadder", "DensePadder", "DenseBatchPadder", "resolve_cap", "cap_agreement_group",
-           "PeerHaloEngine", "PeerFailure", "build_pull_tables", "peer_memory_available"]
+           "PeerHaloEngine", "PeerFailure", "build_pull_tables", "peer_memory_available", "AdapterStatus", "JitAdapter",
+           "PythonAdapter", "OutputKind", "OutputSpec", "Reduce", "current_dd_context", "reshard_by_destination",
+           "collective_device", "resolve_global_rank", "resolve_world_size", "autograd_target", "distributed_method",
+           "localize", "neighbor_refresh_adapters", "refresh_neighbors", "scatter_to_owners", "system_sum", "to_local",
+           "trace_and_validate", "infer_spec", "ParticleHaloConfig", "DistributionSpec", "Scope", "DistributedManager"]
+
+#: reference names for objects that exist here under another name
+ParticleHaloConfig = DomainConfig   # ghost width, skin and rank grid of the particle halo live on the domain config
+DistributionSpec = MLIPSpec         # storage policy and adapters are fields of the one spec class
+Scope = HookScope
+
+
+def __getattr__(name: str):  # these spawn processes / trace models: loaded on first use
+    if name == "trace_and_validate":
+        from nvalchemi_toolkit_b200.distributed.validate import trace_and_validate
+
+        return trace_and_validate
+    if name == "infer_spec":
+        from nvalchemi_toolkit_b200.distributed.infer_spec import infer_spec
+
+        return infer_spec
+    raise AttributeError(name)

@@ -30,7 +30,7 @@ from torch.overrides import TorchFunctionMode
 from nvalchemi_toolkit_b200.distributed.storage_policy import RefreshOnlyHaloPolicy
 
 __all__ = ["HaloDispatchMode", "current_dispatch", "OpAdapter", "FunctionAdapter", "MethodAdapter",
-           "ModuleForwardAdapter", "AdapterRegistry"]
+           "ModuleForwardAdapter", "AdapterRegistry", "PythonAdapter", "JitAdapter", "AdapterStatus"]
 
 _ACTIVE: contextvars.ContextVar["HaloDispatchMode | None"] = contextvars.ContextVar("nva_halo_dispatch", default=None)
 
@@ -262,27 +262,133 @@ class ModuleForwardAdapter(MethodAdapter):
         super().__init__(module_cls, "forward", **kw)
 
 
+class PythonAdapter:
+    """Replace a module-level helper ``module_path.attr_name`` for the duration of a distributed forward (reference
+    ``_core/adapter.py:827-900``): helpers of third-party packages whose single-process assumptions break on a padded
+    sub-domain (an output size read from ``index[-1] + 1``, a sum over all local rows that must skip ghost rows).
+    ``replacement`` receives the same arguments as the original; it may be set after construction (a wrapper's
+    ``distributed_setup`` knows the partition) but must be there when the adapter is installed."""
+
+    kind = "python"
+
+    def __init__(self, module_path: str, attr_name: str, replacement: Callable | None = None) -> None:
+        self.module_path, self.attr_name, self.replacement = module_path, attr_name, replacement
+        self.install_site = _call_site()
+
+    def target(self) -> str:
+        return f"{self.module_path}.{self.attr_name}"
+
+    def _owner(self) -> Any:
+        import importlib
+
+        return importlib.import_module(self.module_path)
+
+    def _replacement_for(self, original: Callable) -> Callable:
+        if self.replacement is None:
+            raise RuntimeError(f"{type(self).__name__}({self.target()}): no replacement was given before install")
+        return self.replacement
+
+    def install(self) -> Callable:
+        owner = self._owner()
+        original = getattr(owner, self.attr_name)
+        setattr(owner, self.attr_name, self._replacement_for(original))
+        return original
+
+    def restore(self, original: Callable) -> None:
+        setattr(self._owner(), self.attr_name, original)
+
+
+class JitAdapter(PythonAdapter):
+    """The same for a ``torch.jit.script``-ed helper, which the dispatch mode cannot see into.  ``mode="eager"`` swaps
+    in ``replacement`` (a plain-Python restatement whose gathers and scatters the mode does see); ``mode="marshal"``
+    keeps the scripted function and treats it as an opaque operator: stale node inputs (``node_inputs``) are refreshed
+    before the call, node outputs (``node_outputs``) are folded / marked stale after it, exactly like
+    :class:`OpAdapter` (reference ``_core/adapter.py:717-825``)."""
+
+    kind = "jit"
+
+    def __init__(self, module_path: str, attr_name: str, replacement: Callable | None = None, mode: str = "eager",
+                 node_inputs: Iterable[int | str] = (), node_outputs: Iterable[int] = (), reduce_outputs: Iterable[int] = ()) -> None:
+        if mode not in ("eager", "marshal"):
+            raise ValueError(f"mode must be 'eager' or 'marshal', got {mode!r}")
+        if mode == "eager" and replacement is None:
+            raise ValueError("mode='eager' needs a replacement")
+        super().__init__(module_path, attr_name, replacement)
+        self.mode = mode
+        self._op = OpAdapter(node_inputs, node_outputs, reduce_outputs)
+
+    def _replacement_for(self, original: Callable) -> Callable:
+        return self._op.wrap(original) if self.mode == "marshal" else super()._replacement_for(original)
+
+
+def _call_site() -> str:
+    """``file:line`` of the first frame outside this module (where an adapter was declared)."""
+    import inspect
+
+    for frame in inspect.stack()[2:]:
+        if frame.filename != __file__:
+            return f"{frame.filename.rsplit('/', 1)[-1]}:{frame.lineno}"
+    return ""
+
+
+class AdapterStatus:
+    """One adapter's life-cycle state, as listed by :meth:`AdapterRegistry.list_active`: ``kind`` (``op`` / ``python`` /
+    ``jit``), ``target`` (what was replaced), ``state`` (``pending``, ``installed``, ``restored``, ``failed``), ``error``
+    (text of the exception when the install failed) and ``install_site`` (where the adapter was declared)."""
+
+    def __init__(self, kind: str, target: str, state: str = "pending", error: str | None = None, install_site: str = "") -> None:
+        self.kind, self.target, self.state, self.error, self.install_site = kind, target, state, error, install_site
+
+    def __repr__(self) -> str:
+        tail = f", error={self.error!r}" if self.error else ""
+        return f"AdapterStatus({self.kind} {self.target}: {self.state}{tail})"
+
+
 class AdapterRegistry:
     """Installs a set of adapters for the duration of a ``with`` block (or between ``install`` / ``restore``)."""
 
-    def __init__(self, adapters: Iterable[FunctionAdapter] = ()) -> None:
+    def __init__(self, adapters: Iterable[Any] = ()) -> None:
         self.adapters = list(adapters)
-        self._originals: list[tuple[FunctionAdapter, Callable]] = []
+        self._originals: list[tuple[Any, Callable]] = []
+        self._status: dict[int, AdapterStatus] = {}
+        for a in self.adapters:
+            self._track(a)
 
-    def register(self, adapter: FunctionAdapter) -> "AdapterRegistry":
+    def _track(self, a: Any) -> AdapterStatus:
+        target = a.target() if hasattr(a, "target") else f"{getattr(getattr(a, 'owner', None), '__name__', a.__class__.__name__)}.{getattr(a, 'name', '?')}"
+        st = AdapterStatus(getattr(a, "kind", "op"), target, install_site=getattr(a, "install_site", ""))
+        self._status[id(a)] = st
+        return st
+
+    def register(self, adapter: Any) -> "AdapterRegistry":
         self.adapters.append(adapter)
+        self._track(adapter)
         return self
 
     def install(self) -> None:
+        """Install every adapter; if one fails, those already installed are put back and the error is re-raised (the
+        failed one is listed with ``state="failed"``)."""
         if self._originals:
             return
         for a in self.adapters:
-            self._originals.append((a, a.install()))
+            st = self._status[id(a)]
+            try:
+                self._originals.append((a, a.install()))
+                st.state, st.error = "installed", None
+            except Exception as exc:  # noqa: BLE001 - recorded, then re-raised after the roll-back
+                st.state, st.error = "failed", f"{type(exc).__name__}: {exc}"
+                self.restore()
+                raise
 
     def restore(self) -> None:
         for a, original in reversed(self._originals):
             a.restore(original)
+            self._status[id(a)].state = "restored"
         self._originals.clear()
+
+    def list_active(self) -> list[AdapterStatus]:
+        """Status of every registered adapter (what is swapped in this process right now, and what failed)."""
+        return [self._status[id(a)] for a in self.adapters]
 
     def __enter__(self) -> "AdapterRegistry":
         self.install()

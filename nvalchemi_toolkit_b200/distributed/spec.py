@@ -112,6 +112,14 @@ class MLIPSpec:
             return cutoff + skin
         return max(1, self.message_passes) * (cutoff + skin)
 
+    def with_outputs(self, outputs: "dict[str, object]") -> "MLIPSpec":
+        """The spec with its output lists taken from per-output declarations (``{"stress": OutputSpec(OutputKind.PER_GRAPH,
+        Reduce.ALL_REDUCE), ...}``, see ``distributed/output_kinds.py``)."""
+        from nvalchemi_toolkit_b200.distributed.output_kinds import lower_outputs
+
+        node, extensive = lower_outputs(outputs)
+        return self.with_(node_outputs=node, extensive_outputs=extensive)
+
     def with_(self, **changes: object) -> "MLIPSpec":
         from dataclasses import replace
 

@@ -7,8 +7,12 @@ from nvalchemi_toolkit_b200.dynamics.demo import DemoDynamics
 from nvalchemi_toolkit_b200.dynamics.integrators import NVE, NVTLangevin
 from nvalchemi_toolkit_b200.dynamics.optimizers import FIRE
 
+from nvalchemi_toolkit_b200.hooks.core import Hook
+
 __all__ = ["BaseDynamics", "BufferConfig", "ConvergenceHook", "DynamicsStage", "FusedStage", "DemoDynamics", "NVE",
-           "NVTLangevin", "FIRE"]
+           "NVTLangevin", "FIRE", "Hook", "DistributedPipeline", "SizeAwareSampler", "DataSink", "GPUBuffer", "HostMemory",
+           "ZarrData", "NVTNoseHoover", "NPT", "NPH", "FIRE2", "FIREVariableCell", "FIRE2VariableCell",
+           "initialize_velocities", "hooks", "integrators", "optimizers"]
 
 
 def __getattr__(name: str):
@@ -25,4 +29,10 @@ def __getattr__(name: str):
             "FIRE2VariableCell": "nvalchemi_toolkit_b200.dynamics.optimizers.fire2"}
     if name in lazy:
         return getattr(importlib.import_module(lazy[name]), name)
+    if name == "initialize_velocities":
+        from nvalchemi_toolkit_b200.dynamics._ops import initialize_velocities
+
+        return initialize_velocities
+    if name in ("hooks", "integrators", "optimizers", "sinks", "sampler", "pipeline"):
+        return importlib.import_module(f"nvalchemi_toolkit_b200.dynamics.{name}")
     raise AttributeError(name)

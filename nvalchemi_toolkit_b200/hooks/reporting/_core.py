@@ -90,6 +90,25 @@ def _to_float(value: Any, name: str) -> float:
     return float(value)
 
 
+def extract_scalars(values: Mapping[str, object], *, prefix: str | None = None) -> dict[str, float]:
+    """Flatten a nested mapping of scalar leaves (numbers, one-element tensors) into ``{"a/b/c": float}``; ``None``
+    leaves are skipped (reference ``hooks/reporting/_scalars.py:447-485``).  A non-string key is a ``TypeError``, a
+    tensor with several elements a ``ValueError``."""
+    out: dict[str, float] = {}
+    root = prefix.strip("/") if prefix else ""
+    for name, value in values.items():
+        if not isinstance(name, str):
+            raise TypeError(f"scalar keys must be strings, got {type(name).__name__}")
+        if value is None:
+            continue
+        key = f"{root}/{name.strip('/')}" if root else name.strip("/")
+        if isinstance(value, Mapping):
+            out.update(extract_scalars(value, prefix=key))
+        else:
+            out[key] = _to_float(value, key)
+    return out
+
+
 def _is_training(ctx: Any) -> bool:
     return hasattr(ctx, "optimizers") and hasattr(ctx, "epoch")
 

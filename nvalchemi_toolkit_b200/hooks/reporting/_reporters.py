@@ -9,7 +9,7 @@ import json
 from collections import deque
 from enum import Enum
 from pathlib import Path
-from typing import Any, Mapping, Sequence
+from typing import Any, Mapping, Protocol, Sequence
 
 from nvalchemi_toolkit_b200._optional import OptionalDependency
 from nvalchemi_toolkit_b200.hooks.reporting._core import (ReportingState, ScalarCallback, ScalarSnapshot, collect_scalars,
@@ -169,6 +169,17 @@ class RichReporter(_ScalarReporterBase):
             from rich.console import Console
 
             (self.console or Console()).print(view)
+
+
+class TensorBoardWriter(Protocol):
+    """The part of ``torch.utils.tensorboard.SummaryWriter`` that :class:`TensorBoardReporter` calls: anything with these
+    three methods can be injected as ``writer=`` (tests, other event sinks)."""
+
+    def add_scalar(self, tag: str, scalar_value: float, global_step: int | None = None) -> None: ...
+
+    def flush(self) -> None: ...
+
+    def close(self) -> None: ...
 
 
 class TensorBoardReporter(_ScalarReporterBase):

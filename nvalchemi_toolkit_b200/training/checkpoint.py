@@ -25,7 +25,7 @@ import os
 import threading
 from datetime import datetime, timezone
 from pathlib import Path
-from typing import Any
+from typing import Any, Callable, Mapping, Sequence
 
 import torch
 
@@ -370,12 +370,28 @@ def read_strategy_metadata(root: str | Path, checkpoint_index: int | None = None
     return json.loads(f.read_text()) if f.exists() else {}
 
 
+#: ``(component, saved_spec, current_spec) -> None``; raise to veto a restore
+CheckpointValidator = Callable[[str, Mapping[str, Any], Mapping[str, Any]], None]
+
+
+def same_class_validator(component: str, saved: Mapping[str, Any], current: Mapping[str, Any]) -> None:
+    """Veto restoring weights into a different class than the one that was saved."""
+    if saved and saved.get("cls_path") != current.get("cls_path"):
+        raise ValueError(f"{component}: checkpoint holds {saved.get('cls_path')}, the model being restored is "
+                         f"{current.get('cls_path')}")
+
+
 def load_checkpoint(root: str | Path, models: dict[str, torch.nn.Module], optimizers: list | None = None,
                     schedulers: list | None = None, hooks: list | None = None, step: int | None = None,
-                    map_location: Any = "cpu", strict: bool = True, optimizer_keys: list[str] | None = None
-                    ) -> dict[str, Any]:
+                    map_location: Any = "cpu", strict: bool = True, optimizer_keys: list[str] | None = None,
+                    validators: "Sequence[CheckpointValidator] | None" = None) -> dict[str, Any]:
     """Restores states in place and returns the strategy metadata (counters) of the chosen checkpoint index
-    (``step``; default: the manifest's latest)."""
+    (``step``; default: the manifest's latest).
+
+    ``validators``: callables ``(component, saved_spec, current_spec) -> None`` run for every model BEFORE any state is
+    touched (``component`` is ``"models/<name>"``; the specs are the ``spec.json`` record and :func:`model_spec` of the
+    model being restored); one that raises aborts the load with nothing modified (reference ``_checkpoint.py:101``).
+    :func:`same_class_validator` is a ready-made one."""
     root = Path(root)
     man = CheckpointManifest(root)
     idx = man.checkpoint_index if step is None else int(step)
@@ -385,6 +401,13 @@ def load_checkpoint(root: str | Path, models: dict[str, torch.nn.Module], optimi
     def read(f: Path) -> Any:
         return torch.load(f, map_location=map_location, weights_only=True)
 
+    if validators:
+        for name, m in models.items():
+            spec_file = root / "models" / name / "spec.json"
+            saved = json.loads(spec_file.read_text()) if spec_file.exists() else {}
+            current = model_spec(_unwrap(m))
+            for check in validators:
+                check(f"models/{name}", saved, current)
     for name, m in models.items():
         f = root / "models" / name / "checkpoints" / f"{idx}.pt"
         if f.exists():

@@ -15,7 +15,7 @@ per-graph values of the last call), then over the graphs that have at least one 
 from __future__ import annotations
 
 import math
-from typing import Any, Callable
+from typing import Any, Callable, Protocol
 
 import torch
 
@@ -121,6 +121,27 @@ def padded_node_mask(num_nodes_per_graph: torch.Tensor, v_max: int) -> torch.Ten
     return torch.arange(v_max, device=t.device)[None, :] < t.reshape(-1, 1)
 
 
+class ReductionContext(dict):
+    """What the reduction of a term needs to know about the batch besides the two tensors: ``num_graphs``, ``batch_idx``
+    (dense node-level terms) and ``node_counts`` (per-graph atom counts, from explicit counts or a padding mask).
+    Built once per call by :meth:`BaseLossFunction.reduction_context`; custom terms may add entries in ``normalize``."""
+
+    @classmethod
+    def from_batch(cls, batch: Any) -> "ReductionContext":
+        ctx = cls(num_graphs=getattr(batch, "num_graphs", None), batch_idx=getattr(batch, "batch_idx", None))
+        counts = getattr(batch, "num_nodes_per_graph", None)
+        if counts is not None:
+            ctx["node_counts"] = node_counts(counts)
+        return ctx
+
+
+class LossTargetAssemblyProtocol(Protocol):
+    """A callable that collects the labels a loss needs from a batch (``assemble_loss_targets`` is the stock one; a
+    strategy may be given another, e.g. one that reads labels from a side file keyed by sample id)."""
+
+    def __call__(self, loss: Any, batch: Any, strict: bool = True) -> dict[str, torch.Tensor]: ...
+
+
 class BaseLossFunction:
     """One weighted term.  Subclasses implement ``residual(pred, target, batch) -> elementwise tensor`` (same leading
     shape as ``pred``) and choose ``level`` (``"graph"``: one row per graph; ``"node"``: one row per atom, dense
@@ -147,6 +168,9 @@ class BaseLossFunction:
 
     def weight_at(self, step: int, epoch: int) -> float:
         return float(self.weight(step, epoch)) if callable(self.weight) else float(self.weight)
+
+    def reduction_context(self, batch: Any) -> ReductionContext:
+        return ReductionContext.from_batch(batch)
 
     # ---- the overridable steps
     def validate(self, pred: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
@@ -272,7 +296,10 @@ class EnergyMSELoss(BaseLossFunction):
         self.per_atom, self.atom_weighted = per_atom, atom_weighted
 
     def _counts(self, batch: Any, ref: torch.Tensor) -> torch.Tensor:
-        return node_counts(batch.num_nodes_per_graph).to(ref.dtype).clamp_min(1)
+        ctx = self.reduction_context(batch)
+        if "node_counts" not in ctx:
+            raise KeyError(f"loss term {self.name}: per-atom normalisation needs batch.num_nodes_per_graph")
+        return ctx["node_counts"].to(ref.dtype).clamp_min(1)
 
     def normalize(self, pred, target, batch):
         if not self.per_atom:
@@ -463,6 +490,15 @@ class ComposedLossFunction:
             kw["weight"] = schedule_from_spec(kw.get("weight", 1.0))
             terms.append(TERMS[s["cls"]](**kw))
         return cls(terms, **kwargs)
+
+
+DTypePolicy = str  # one of ``DTYPE_POLICIES``
+ComposedLossOutput = dict  # ``{"total_loss": tensor, "<term name>": detached tensor, ...}``
+
+
+def loss_component_to_spec(term: "BaseLossFunction") -> dict[str, Any]:
+    """The JSON record of one term (what ``ComposedLossFunction.to_spec`` lists; ``from_spec`` rebuilds it)."""
+    return term.to_spec()
 
 
 def as_composed_loss(loss: "BaseLossFunction | ComposedLossFunction | list") -> ComposedLossFunction:

@@ -141,3 +141,16 @@ def step_schedulers(scheds: list, configs: list[OptimizerConfig], interval: str,
                 s.step(float(metrics[c.scheduler_metric]))
         else:
             s.step()
+
+
+def step_lr_schedulers(scheds: list, configs: "list[OptimizerConfig] | None" = None, interval: str = "step",
+                       metrics: dict | None = None) -> None:
+    """Step learning-rate schedulers (the reference's name, ``training/optimizers.py:404-447``).  With their
+    ``OptimizerConfig`` list only those of the given ``interval`` step, metric-driven ones with ``metrics``; without it
+    every scheduler that is not metric-driven steps once."""
+    if configs is not None:
+        step_schedulers(scheds, configs, interval, metrics)
+        return
+    for s in scheds:
+        if s is not None and not isinstance(s, torch.optim.lr_scheduler.ReduceLROnPlateau):
+            s.step()

@@ -11,7 +11,7 @@ models differentiate the energy for forces even in evaluation), per-batch callba
 and extra metrics computed from predictions and batch."""
 from __future__ import annotations
 
-from typing import Any, Callable, Iterable, Iterator, Mapping
+from typing import Any, Callable, Iterable, Iterator, Mapping, Protocol
 
 import torch
 from pydantic import BaseModel, ConfigDict, field_validator, model_validator
@@ -19,6 +19,13 @@ from pydantic import BaseModel, ConfigDict, field_validator, model_validator
 from nvalchemi_toolkit_b200.training.distributed import all_reduce
 
 Metric = Callable[[Any, Any], "torch.Tensor | float"]
+
+
+class BatchValidationCallback(Protocol):
+    """``ValidationConfig.batch_callback``: called once per validation batch with the batch, the model's predictions and
+    the loss dictionary (parity plots, error histograms, outlier dumps)."""
+
+    def __call__(self, batch: Any, predictions: dict, losses: dict) -> None: ...
 
 
 def ensure_reiterable(value: Any) -> Any:
