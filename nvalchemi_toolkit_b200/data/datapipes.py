@@ -66,6 +66,20 @@ class BatchDatasetProtocol(Protocol):
     def get_metadata(self, idx: int) -> tuple[int, int]: ...
 
 
+class DistributedSamplerProtocol(Protocol):
+    """A sampler that hands each rank its share of an epoch (``torch.utils.data.DistributedSampler`` satisfies it, and so
+    do the multi-dataset samplers below): ``num_replicas``, ``rank``, ``set_epoch(epoch)``, iteration over indices."""
+
+    num_replicas: int
+    rank: int
+
+    def set_epoch(self, epoch: int) -> None: ...
+
+    def __iter__(self) -> Iterator[int]: ...
+
+    def __len__(self) -> int: ...
+
+
 class Dataset:
     """Samples as ``(AtomicData, metadata)``; implements the sampler protocol (``get_metadata``)."""
 
@@ -232,6 +246,10 @@ class MultiDatasetSampler:
         if any(w > 0 and n == 0 for w, n in zip(self.weights, self.lengths)):
             raise ValueError("an empty dataset cannot have a positive sampling weight")
         self.replacement, self.shuffle, self.drop_last = replacement, shuffle, drop_last
+
+    @property
+    def num_replicas(self) -> int:
+        return self.world_size
 
     def set_epoch(self, epoch: int) -> None:
         self.epoch = epoch
@@ -499,3 +517,7 @@ class DataLoader:
             for b in window:
                 yield self._collate(items[pos: pos + len(b)])
                 pos += len(b)
+
+
+from nvalchemi_toolkit_b200.data.zarr_store import (AtomicDataZarrReader, AtomicDataZarrWriter, ZarrArrayConfig,  # noqa: E402,F401
+                                                    ZarrWriteConfig)

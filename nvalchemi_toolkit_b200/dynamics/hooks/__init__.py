@@ -5,5 +5,8 @@ from nvalchemi_toolkit_b200.dynamics.hooks.library import (
     NaNDetectorHook, SnapshotHook,
 )
 
+from nvalchemi_toolkit_b200.hooks.profiling import TorchProfilerHook
+from nvalchemi_toolkit_b200.hooks.stage_timing import StageTimingHook
+
 __all__ = ["AlignCellHook", "ConvergedSnapshotHook", "EnergyDriftMonitorHook", "FreezeAtomsHook", "LoggingHook",
-           "MaxForceClampHook", "NaNDetectorHook", "SnapshotHook"]
+           "MaxForceClampHook", "NaNDetectorHook", "SnapshotHook", "StageTimingHook", "TorchProfilerHook"]

@@ -17,3 +17,7 @@ __all__ = ["DEFAULT_REPORT_STAGES", "Reporter", "ReporterMessage", "ReportingErr
            "RichLayout", "RichReporter", "TensorBoardReporter", "sparkline", "BaseDashboardLayout", "CompactLayout",
            "DynamicsLayout", "TrainingLayout", "resolve_layout", "text_plot", "extract_scalars", "ScalarCallback",
            "TensorBoardWriter"]
+
+#: the layout classes under the names the reference exports them
+BaseRichLayout, TrainingRichLayout, DynamicsRichLayout = BaseDashboardLayout, TrainingLayout, DynamicsLayout
+__all__ += ["BaseRichLayout", "TrainingRichLayout", "DynamicsRichLayout"]

@@ -2,9 +2,11 @@
 """Training hooks (reference ``nvalchemi/training/hooks``)."""
 from nvalchemi_toolkit_b200.training.hooks.library import (
     CheckpointHook, DDPHook, EMAHook, FusedGradAllReduceHook, GradientAccumulationHook, GradientClipHook,
-    LossSpikeSkipHook, MixedPrecisionHook, ModulePatchHook, TrainableParameterHook, TrainingUpdateOrchestrator,
+    LossSpikeSkipHook, MixedPrecisionHook, ModulePatchHook, TrainableParameterHook, TrainingUpdateHook,
+    TrainingUpdateOrchestrator,
 )
+from nvalchemi_toolkit_b200.hooks.profiling import TorchProfilerHook
 
 __all__ = ["CheckpointHook", "DDPHook", "EMAHook", "FusedGradAllReduceHook", "GradientAccumulationHook",
            "GradientClipHook", "LossSpikeSkipHook", "MixedPrecisionHook", "ModulePatchHook", "TrainableParameterHook",
-           "TrainingUpdateOrchestrator"]
+           "TrainingUpdateOrchestrator", "TrainingUpdateHook", "TorchProfilerHook"]

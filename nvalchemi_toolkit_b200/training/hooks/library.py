@@ -28,6 +28,26 @@ class _Base:
     priority = 0
 
 
+class TrainingUpdateHook(_Base):
+    """Base of the hooks that shape ONE optimiser update: gradient accumulation, mixed precision, clipping, skipping of
+    loss spikes (reference ``training/hooks/update.py:197-340``).
+
+    They follow the plain hook protocol (``__call__(ctx, stage)``) and talk to the strategy and to each other through
+    the training context instead of return values: ``ctx.loss`` may be replaced before the backward pass (scaling),
+    ``ctx.accumulating = True`` keeps the previous gradients, ``ctx.skip_optimizer_step = True`` vetoes the optimiser and
+    scheduler step of this batch (any hook may set it; later hooks read it and skip work that assumes a step, e.g.
+    clipping), ``ctx.sync_gradients`` says whether this micro-batch ends with a step.  ``priority`` orders hooks that
+    share a stage, lower first: 10 accumulation, 20 mixed precision, 30 clipping, 40 spike skipping, default 50.
+    ``a + b`` builds a :class:`TrainingUpdateOrchestrator` that dispatches them in that order."""
+
+    priority = 50
+
+    def __add__(self, other: Any) -> "TrainingUpdateOrchestrator":
+        mine = self.hooks if isinstance(self, TrainingUpdateOrchestrator) else [self]
+        theirs = other.hooks if isinstance(other, TrainingUpdateOrchestrator) else [other]
+        return TrainingUpdateOrchestrator(list(mine) + list(theirs))
+
+
 # ------------------------------------------------------------------ data parallel
 class DDPHook(_Base):
     """Wraps the configured models in ``DistributedDataParallel`` at SETUP and shards the dataloader."""
@@ -257,7 +277,7 @@ class FusedGradAllReduceHook(_Base):
 
 
 # ------------------------------------------------------------------ update policies
-class GradientAccumulationHook(_Base):
+class GradientAccumulationHook(TrainingUpdateHook):
     """Steps the optimiser every ``steps`` batches; gradients accumulate in between (loss scaled by ``1/steps``)."""
 
     priority = 10
@@ -279,7 +299,7 @@ class GradientAccumulationHook(_Base):
             ctx.skip_optimizer_step = True
 
 
-class MixedPrecisionHook(_Base):
+class MixedPrecisionHook(TrainingUpdateHook):
     """Autocast around forward + loss, scaled backward, ``GradScaler`` step (claims both DO slots)."""
 
     priority = 20
@@ -321,7 +341,7 @@ class MixedPrecisionHook(_Base):
         self.scaler.load_state_dict(state["scaler"])
 
 
-class GradientClipHook(_Base):
+class GradientClipHook(TrainingUpdateHook):
     stage = S.BEFORE_OPTIMIZER_STEP
     priority = 30
 
@@ -335,7 +355,7 @@ class GradientClipHook(_Base):
             self.last_norm = float(torch.nn.utils.clip_grad_norm_(params, self.max_norm, self.norm_type))
 
 
-class LossSpikeSkipHook(_Base):
+class LossSpikeSkipHook(TrainingUpdateHook):
     """Skips the update when the loss exceeds ``factor`` x its running mean (or is not finite)."""
 
     stage = S.BEFORE_OPTIMIZER_STEP
@@ -366,7 +386,7 @@ class LossSpikeSkipHook(_Base):
         self.mean, self.seen, self.skipped = state["mean"], state["seen"], state["skipped"]
 
 
-class TrainingUpdateOrchestrator(_Base):
+class TrainingUpdateOrchestrator(TrainingUpdateHook):
     """Runs a set of update hooks in priority order at each stage they subscribe to (priority-ordered veto chain)."""
 
     def __init__(self, hooks: list[Any]) -> None:

@@ -106,6 +106,24 @@ def align_dtypes(pred: torch.Tensor, target: torch.Tensor, policy: str, who: str
     return (pred.to(target.dtype), target) if policy == "prediction_to_target" else (pred, target.to(pred.dtype))
 
 
+def assert_same_shape(pred: torch.Tensor, target: torch.Tensor, *, name: str, prediction_key: str | None = None,
+                      target_key: str | None = None, strict: bool = False) -> None:
+    """``ValueError`` when the two tensors cannot be compared: different dtypes first (usually the real bug), then the
+    shapes: identical with ``strict``, else broadcast-compatible (reference ``composition.py:169-260``; elementwise
+    terms should ask for ``strict``, because ``[B, 1]`` against ``[B, 3]`` broadcasts silently)."""
+    who = f"loss term {name}" + (f" ({prediction_key} vs {target_key})" if prediction_key or target_key else "")
+    if pred.dtype != target.dtype:
+        raise ValueError(f"{who}: prediction is {pred.dtype}, target is {target.dtype}")
+    if strict:
+        if pred.shape != target.shape:
+            raise ValueError(f"{who}: shapes {tuple(pred.shape)} and {tuple(target.shape)} differ")
+        return
+    try:
+        torch.broadcast_shapes(pred.shape, target.shape)
+    except RuntimeError as exc:
+        raise ValueError(f"{who}: shapes {tuple(pred.shape)} and {tuple(target.shape)} do not broadcast") from exc
+
+
 def node_counts(num_nodes_per_graph: torch.Tensor) -> torch.Tensor:
     """Per-graph atom counts from explicit counts ``[B]`` or a padded validity mask ``[B, V_max]``."""
     t = num_nodes_per_graph

@@ -163,3 +163,47 @@ def test_small_distributed_helpers_and_manager_without_a_process_group(monkeypat
     DistributedManager.cleanup()
     assert not DistributedManager.is_initialized()
     del ShardTensor
+
+
+SECOND_LEVEL = {
+    "dynamics.hooks": """AlignCellHook ConvergedSnapshotHook EnergyDriftMonitorHook FreezeAtomsHook LoggingHook MaxForceClampHook
+        NaNDetectorHook SnapshotHook StageTimingHook TorchProfilerHook""",
+    "training.hooks": """CheckpointHook DDPHook EMAHook MixedPrecisionHook ModulePatchHook TorchProfilerHook
+        TrainableParameterHook TrainingUpdateHook TrainingUpdateOrchestrator""",
+    "training.losses": """BaseLossFunction ComposedLossFunction ComposedLossOutput DTypePolicy LossTargetAssemblyProtocol
+        LossWeightSchedule ReductionContext assemble_loss_targets assert_same_shape frobenius_mse loss_component_to_spec
+        per_graph_mean per_graph_sum""",
+    "dynamics.integrators": "NPH NPT NVE NVTLangevin NVTNoseHoover",
+    "dynamics.optimizers": "FIRE FIRE2 FIRE2VariableCell FIREVariableCell",
+    "hooks.reporting": """BaseRichLayout DEFAULT_REPORT_STAGES DynamicsRichLayout Reporter ReportingOrchestrator RichReporter
+        TensorBoardWriter TrainingRichLayout extract_scalars""",
+    "data.datapipes": """AtomicDataZarrReader AtomicDataZarrWriter BatchDatasetProtocol DataLoader Dataset
+        DistributedSamplerProtocol InMemoryDataset MultiDataset MultiDatasetBatchSampler MultiDatasetSampler Reader
+        ZarrArrayConfig ZarrWriteConfig""",
+}
+
+
+@pytest.mark.parametrize("package", sorted(SECOND_LEVEL))
+def test_second_level_reference_names_resolve(package):
+    mod = importlib.import_module(f"nvalchemi_toolkit_b200.{package}")
+    assert [n for n in SECOND_LEVEL[package].split() if not hasattr(mod, n)] == []
+
+
+def test_update_hooks_compose_in_priority_order_and_shape_checks():
+    from nvalchemi_toolkit_b200.training.hooks import (GradientAccumulationHook, GradientClipHook, LossSpikeSkipHook,
+                                                       MixedPrecisionHook, TrainingUpdateHook, TrainingUpdateOrchestrator)
+    from nvalchemi_toolkit_b200.training.losses import assert_same_shape
+
+    chain = LossSpikeSkipHook() + GradientClipHook(1.0) + MixedPrecisionHook() + GradientAccumulationHook(4)
+    assert isinstance(chain, TrainingUpdateOrchestrator)
+    assert [type(h).__name__ for h in chain.hooks] == ["GradientAccumulationHook", "MixedPrecisionHook", "GradientClipHook",
+                                                      "LossSpikeSkipHook"]
+    assert all(isinstance(h, TrainingUpdateHook) for h in chain.hooks)
+    a, b = torch.zeros(4, 1), torch.zeros(4, 3)
+    assert_same_shape(a, b, name="x")                                   # broadcast-compatible passes by default ...
+    with pytest.raises(ValueError, match="differ"):
+        assert_same_shape(a, b, name="x", strict=True)                  # ... and is what strict is for
+    with pytest.raises(ValueError, match="do not broadcast"):
+        assert_same_shape(torch.zeros(4, 2), b, name="x")
+    with pytest.raises(ValueError, match="float64"):
+        assert_same_shape(a, b.double(), name="x", prediction_key="p", target_key="t")
