@@ -267,3 +267,60 @@ def layer_diff(model_factory: Callable, batch_factory: Callable, world_size: int
         d = float((a - b).abs().max()) if a.shape == b.shape else float("inf")
         report.append({"module": name, "ok": d <= atol, "max_abs_diff": d})
     return report
+
+
+# ---- scripted helpers (reference ``nvalchemi/distributed/validate/scripted_diagnostics.py``) -----------------------
+@dataclass
+class ScriptedOpReport:
+    """TorchScript objects reachable from a model.  The dispatch mode of the distributed forward is a
+    ``TorchFunctionMode``: it does not see the tensor operations INSIDE a scripted module or function, so a scripted
+    message-passing block needs an adapter (``JitAdapter`` for a module-level function, ``ModuleForwardAdapter`` for a
+    scripted sub-module) before ``refresh_per_layer`` can be trusted."""
+
+    modules: list[str] = field(default_factory=list)     # dotted names of scripted sub-modules
+    functions: list[str] = field(default_factory=list)   # "package.module.name" of scripted module-level functions
+
+    @property
+    def found(self) -> bool:
+        return bool(self.modules or self.functions)
+
+    def advice(self) -> str:
+        if not self.found:
+            return "no scripted code found: gathers and scatters are visible to the dispatch mode"
+        lines = []
+        if self.functions:
+            lines.append("scripted functions (declare JitAdapter(module, name, mode='marshal', node_inputs=..., node_outputs=...) "
+                         "or give a plain-Python replacement): " + ", ".join(self.functions))
+        if self.modules:
+            lines.append("scripted sub-modules (declare ModuleForwardAdapter(cls, node_inputs=..., node_outputs=...)): "
+                         + ", ".join(self.modules))
+        return "; ".join(lines)
+
+
+def detect_scripted_ops(model: Any) -> ScriptedOpReport:
+    """Scan ``model`` for scripted sub-modules and the Python modules that define its sub-module classes for scripted
+    module-level functions."""
+    import sys
+
+    report = ScriptedOpReport()
+    if not isinstance(model, torch.nn.Module):
+        return report
+    seen_py: set[str] = set()
+    for name, sub in model.named_modules():
+        if isinstance(sub, torch.jit.ScriptModule):
+            report.modules.append(name or type(sub).__name__)
+        mod_name = type(sub).__module__
+        if mod_name in seen_py or mod_name.startswith("torch."):
+            continue
+        seen_py.add(mod_name)
+        py = sys.modules.get(mod_name)
+        for attr, value in (vars(py).items() if py is not None else ()):
+            if isinstance(value, torch.jit.ScriptFunction):
+                report.functions.append(f"{mod_name}.{attr}")
+    report.functions.sort()
+    return report
+
+
+#: names under which the reference exports the report types
+TraceReport = ValidationReport
+Attempt = dict

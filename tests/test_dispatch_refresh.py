@@ -321,3 +321,30 @@ def test_opaque_neighbour_operator_is_given_one_message_pass():
     batch = Batch.from_data_list([fcc_supercell(3, a=3.61, z=29, noise=0.05, seed=1)])
     spec, summary = infer_spec(model, batch)
     assert spec.message_passes == 1 and "opaque operator" in spec.notes and "energy" in spec.extensive_outputs
+
+
+@torch.jit.script
+def _scripted_sum(x: torch.Tensor, idx: torch.Tensor, n: int) -> torch.Tensor:
+    return torch.zeros(n, x.shape[1], dtype=x.dtype).index_add_(0, idx, x)
+
+
+def test_scripted_code_is_reported_with_the_adapter_to_declare():
+    from nvalchemi_toolkit_b200.distributed.validate import ScriptedOpReport, detect_scripted_ops
+
+    class Plain(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = torch.nn.Linear(2, 2)
+
+    class WithScriptedBlock(Plain):
+        def __init__(self):
+            super().__init__()
+            self.block = torch.jit.script(torch.nn.Sequential(torch.nn.Linear(2, 2), torch.nn.Tanh()))
+
+    rep = detect_scripted_ops(WithScriptedBlock())
+    assert isinstance(rep, ScriptedOpReport) and rep.found and rep.modules[0] == "block"
+    assert any(f.endswith("test_dispatch_refresh._scripted_sum") for f in rep.functions)   # defined beside the model class
+    assert "JitAdapter" in rep.advice() and "ModuleForwardAdapter" in rep.advice()
+    clean = detect_scripted_ops(torch.nn.Linear(2, 2))
+    assert not clean.found and "no scripted code" in clean.advice()
+    assert not detect_scripted_ops(object()).found
