@@ -6,7 +6,11 @@ path is PyTorch plus hand-written sm_100a CUDA kernels (``torch.ops.nvalchemi.*`
 NVLink peer-to-peer communication kernels.
 """
 __version__ = "0.1.0"
+version = __version__  # the reference package spells it this way
 
+from nvalchemi_toolkit_b200._optional import MissingDependencyError, OptionalDependency  # noqa: F401
 from nvalchemi_toolkit_b200._typing import AtomCategory  # noqa: F401
 from nvalchemi_toolkit_b200.data import AtomicData, Batch  # noqa: F401
 from nvalchemi_toolkit_b200.ops import compat as _compat  # noqa: F401,E402  registers the reference's operator names
+
+OptionalDependencyError = MissingDependencyError  # the reference's name for the same error
