@@ -89,5 +89,15 @@ print(f"rank {rank}: {sharded.n_owned} owned + {sharded.n_ghost} ghosts (a 3-cut
       f"{dm.last_dispatch_stats.get('refreshes', 0)} ghost refreshes; E = {float(out['energy']):.6f} eV; "
       f"max |F - F_single| = {err:.2e}", flush=True)
 assert err < 1e-8
+
+# Had the wrapper declared nothing, one traced single-process forward proposes the spec: it counts the neighbour
+# aggregations on the way to the energy (three here) and sees that the model sums over atoms itself.
+from nvalchemi_toolkit_b200.distributed.infer_spec import infer_spec  # noqa: E402
+
+proposed, seen = infer_spec(model, ref)
+if rank == 0:
+    print(f"trace: {seen.describe()}\nproposed: message_passes={proposed.message_passes}, "
+          f"consolidation={proposed.consolidation.value}, refresh_per_layer={proposed.refresh_per_layer}", flush=True)
+assert proposed.message_passes == spec.message_passes and proposed.refresh_per_layer
 if dist.is_initialized():
     dist.destroy_process_group()
