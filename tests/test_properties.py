@@ -289,3 +289,33 @@ def test_level_storages_follow_a_list_model_through_random_put_and_defrag(seed, 
             assert torch.equal(uni["e"], torch.stack([m[2] for m in model]))
             assert seg.batch_idx.tolist() == [i for i, m in enumerate(model) for _ in range(m[0].shape[0])]
         assert seg.free_segments() == seg_cap - len(model) and uni.free_rows() == seg_cap - len(model)
+
+
+# ---------------------------------------------------------------------------------------------------- integrators
+@settings(max_examples=8, deadline=None)
+@given(seed=st.integers(0, 1000), n_cells=st.sampled_from([2, 3]), dt=st.floats(0.5, 2.0), steps=st.integers(3, 12))
+def test_velocity_verlet_is_time_reversible_and_conserves_momentum(seed, n_cells, dt, steps):
+    """NVE with a conservative pair potential: total momentum stays put, and after flipping the velocities the same
+    number of steps retraces the trajectory to the starting point (float64, tolerances of rounding only)."""
+    from nvalchemi_toolkit_b200.dynamics import NVE, _ops
+    from nvalchemi_toolkit_b200.models.lj import LennardJonesModelWrapper
+    from tests.helpers import fcc_supercell
+
+    batch = Batch.from_data_list([fcc_supercell(n_cells, a=5.26, z=18, noise=0.05, seed=seed, dtype=torch.float64)])
+    model = LennardJonesModelWrapper(epsilon=0.0104, sigma=3.4, cutoff=6.0, switch_width=1.0)
+    model.model_config.active_outputs = {"energy", "forces"}
+    _ops.initialize_velocities(batch.velocities, batch.atomic_masses, 120.0, batch.batch_idx, random_seed=seed)
+    x0, v0 = batch.positions.clone(), batch.velocities.clone()
+    p0 = (batch.atomic_masses[:, None] * v0).sum(0)
+    dyn = NVE(model, dt=dt, hooks=model.make_neighbor_hooks())
+    from nvalchemi_toolkit_b200.dynamics import DynamicsStage
+
+    dyn._call_hooks(DynamicsStage.BEFORE_COMPUTE, batch)   # the batch carries placeholder forces (zeros): evaluate the
+    dyn.compute(batch)                                      # real ones before the first half kick
+    dyn.run(batch, steps)
+    p1 = (batch.atomic_masses[:, None] * batch.velocities).sum(0)
+    assert torch.allclose(p1, p0, atol=1e-9)
+    assert float((batch.positions - x0).abs().max()) > 1e-4          # it did move
+    batch.velocities.mul_(-1.0)
+    dyn.run(batch, steps)
+    assert torch.allclose(batch.positions, x0, atol=1e-9) and torch.allclose(-batch.velocities, v0, atol=1e-9)
