@@ -319,3 +319,76 @@ def test_velocity_verlet_is_time_reversible_and_conserves_momentum(seed, n_cells
     batch.velocities.mul_(-1.0)
     dyn.run(batch, steps)
     assert torch.allclose(batch.positions, x0, atol=1e-9) and torch.allclose(-batch.velocities, v0, atol=1e-9)
+
+
+# ---------------------------------------------------------------------------------------------------- inflight sampler
+@settings(**SETTINGS)
+@given(seed=st.integers(0, 10_000), sizes=st.lists(st.integers(1, 12), min_size=1, max_size=14), max_atoms=st.integers(12, 40),
+       max_batch=st.one_of(st.none(), st.integers(1, 6)), bin_width=st.integers(1, 5), shuffle=st.booleans())
+def test_size_aware_sampler_respects_budgets_and_hands_out_each_sample_once(seed, sizes, max_atoms, max_batch, bin_width, shuffle):
+    from nvalchemi_toolkit_b200.data.datapipes import InMemoryDataset
+    from nvalchemi_toolkit_b200.dynamics.sampler import SizeAwareSampler
+
+    import random as _random
+
+    _random.seed(seed)
+    data = [random_molecule(n, seed + i) for i, n in enumerate(sizes)]
+    sampler = SizeAwareSampler(InMemoryDataset(data), max_atoms=max_atoms, max_batch_size=max_batch, bin_width=bin_width,
+                               shuffle=shuffle)
+    first = sampler.build_initial_batch()
+    assert first.num_nodes <= max_atoms and (max_batch is None or first.num_graphs <= max_batch)
+    seen_ids = first.system_id.reshape(-1).tolist() if getattr(first, "system_id", None) is not None else []
+    handed = sorted(first.num_nodes_per_graph.tolist())
+    # free a random slot budget repeatedly until the supply is exhausted
+    g = torch.Generator().manual_seed(seed)
+    for _ in range(4 * len(sizes)):
+        if sampler.exhausted:
+            break
+        budget = int(torch.randint(1, max_atoms + 1, (1,), generator=g))
+        got = sampler.request_replacements_budget(atom_budget=budget, max_count=3)
+        assert sum(d.num_nodes for d in got) <= budget and len(got) <= 3
+        handed += [d.num_nodes for d in got]
+        seen_ids += [int(d.system_id) for d in got if getattr(d, "system_id", None) is not None]
+        one = sampler.request_replacement(budget, 10 ** 9)
+        if one is not None:
+            assert one.num_nodes <= budget
+            handed.append(one.num_nodes)
+            if getattr(one, "system_id", None) is not None:
+                seen_ids.append(int(one.system_id))
+    assert len(seen_ids) == len(set(seen_ids))                      # ids are unique over the whole run
+    remaining = len(sampler)
+    assert len(handed) + remaining == len(sizes)                    # nothing handed out twice, nothing lost
+    if sampler.exhausted:
+        assert sorted(handed) == sorted(sizes)
+        assert sampler.request_replacement(max_atoms, 10 ** 9) is None
+
+
+@settings(**SETTINGS)
+@given(seed=st.integers(0, 10_000), lengths=st.lists(st.integers(1, 9), min_size=1, max_size=4), world=st.integers(1, 4),
+       replacement=st.booleans(), shuffle=st.booleans(), drop_last=st.booleans(), extra=st.integers(0, 7))
+def test_multidataset_sampler_shards_one_epoch_order_evenly(seed, lengths, world, replacement, shuffle, drop_last, extra):
+    from nvalchemi_toolkit_b200.data.datapipes import InMemoryDataset, MultiDataset, MultiDatasetSampler, counts_from_weights
+
+    multi = MultiDataset([InMemoryDataset([random_molecule(2, seed + 10 * k + i) for i in range(n)]) for k, n in enumerate(lengths)])
+    num_samples = len(multi) + extra
+    ranks = [MultiDatasetSampler(multi, num_samples=num_samples, seed=seed, rank=r, world_size=world, replacement=replacement,
+                                 shuffle=shuffle, drop_last=drop_last) for r in range(world)]
+    shares = [list(s) for s in ranks]
+    per = num_samples // world if drop_last else -(-num_samples // world)
+    assert all(len(sh) == per == len(s) for sh, s in zip(shares, ranks))          # every rank runs the same number of steps
+    order = ranks[0].epoch_order()
+    assert all(r.epoch_order() == order for r in ranks)                            # one order, known to all ranks
+    merged = [shares[i % world][i // world] for i in range(per * world)]           # undo the strided split
+    head = order[: per * world] if drop_last else order + order[: per * world - len(order)]
+    assert merged == head
+    # exact per-dataset counts in the epoch, proportional to the dataset lengths
+    want = counts_from_weights([float(n) for n in lengths], num_samples)
+    got = [sum(1 for i in order if multi.locate(i)[0] == k) for k in range(len(lengths))]
+    assert got == want
+    if not replacement:
+        for k, n in enumerate(lengths):                                            # no repeats before a dataset is exhausted
+            mine = [i for i in order if multi.locate(i)[0] == k]
+            assert len(set(mine)) == min(len(mine), n)
+    for s in ranks:
+        s.set_epoch(1)
+    assert ranks[0].epoch_order() == ranks[-1].epoch_order()
