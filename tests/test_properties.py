@@ -392,3 +392,41 @@ def test_multidataset_sampler_shards_one_epoch_order_evenly(seed, lengths, world
     for s in ranks:
         s.set_epoch(1)
     assert ranks[0].epoch_order() == ranks[-1].epoch_order()
+
+
+# ---------------------------------------------------------------------------------------------------- halo exchange
+@settings(max_examples=15, deadline=None)
+@given(seed=st.integers(0, 10_000), n_cells=st.sampled_from([2, 3]), cutoff=st.floats(2.5, 6.0), width=st.integers(1, 4),
+       pbc=st.tuples(st.booleans(), st.booleans(), st.booleans()))
+def test_halo_forward_and_reverse_are_adjoint_and_ghosts_are_images(seed, n_cells, cutoff, width, pbc):
+    """One rank, periodic images as ghosts: the reverse exchange is the transpose of the forward one
+    (<forward(x), y> = <x, reverse(y)>, which is what makes forces on ghost copies return correctly), and every ghost
+    position is its owner's position displaced by a lattice vector."""
+    from nvalchemi_toolkit_b200.distributed import DomainConfig, ShardedBatch
+    from nvalchemi_toolkit_b200.distributed.spec import SPEC_LJ_HALO
+    from tests.helpers import fcc_supercell
+
+    d = fcc_supercell(n_cells, a=4.0, z=29, noise=0.1, seed=seed, dtype=torch.float64)
+    d.pbc = torch.tensor(pbc)
+    batch = Batch.from_data_list([d])
+    sh = ShardedBatch.from_batch(batch, DomainConfig(cutoff=cutoff, skin=0.0), SPEC_LJ_HALO)
+    halo, n, ng = sh.halo, sh.n_owned, sh.n_ghost
+    assert n == batch.num_nodes
+    if not any(pbc):
+        assert ng == 0
+        return
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, width, generator=g, dtype=torch.float64)
+    y = torch.randn(ng, width, generator=g, dtype=torch.float64)
+    lhs = (halo.forward(x) * y).sum()
+    rhs = (x * halo.reverse_add(y, torch.zeros_like(x))).sum()
+    assert float(lhs) == pytest.approx(float(rhs), rel=1e-10, abs=1e-10)
+    padded = sh.padded_batch(halo)
+    owner_row = halo.forward(torch.arange(n, dtype=torch.float64).reshape(-1, 1)).reshape(-1).long()
+    disp = padded.positions[n:] - padded.positions[:n][owner_row]   # owned rows may have been wrapped into the cell
+    frac = disp @ torch.linalg.inv(batch.cell.reshape(3, 3))
+    assert torch.allclose(frac, frac.round(), atol=1e-9) and bool((frac.round().abs().sum(-1) > 0).all())
+    assert bool((frac.round()[:, ~torch.tensor(pbc)] == 0).all())     # no images along open directions
+    # every ghost lies within the ghost width of the cell (it could be somebody's neighbour), none deep inside
+    inside = (padded.positions[n:] @ torch.linalg.inv(batch.cell.reshape(3, 3)))
+    assert bool(((inside < 0) | (inside > 1)).any(-1).all())
