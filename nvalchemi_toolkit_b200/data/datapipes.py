@@ -151,6 +151,16 @@ class InMemoryDataset(Dataset):
     class _ListReader(Reader):
         def __init__(self, items: Sequence[AtomicData]) -> None:
             self.items = list(items)
+            # level of every field (custom ones included), so that fused reads rebuild samples with the right levels
+            self._levels: dict[str, str] = {}
+            for d in self.items:
+                for k in d._tensor_items():
+                    if k not in self._levels and d.level_of(k) is not None:
+                        self._levels[k] = d.level_of(k)
+
+        @property
+        def field_levels(self) -> dict[str, str]:
+            return self._levels
 
         def __len__(self) -> int:
             return len(self.items)

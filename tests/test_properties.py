@@ -430,3 +430,43 @@ def test_halo_forward_and_reverse_are_adjoint_and_ghosts_are_images(seed, n_cell
     # every ghost lies within the ghost width of the cell (it could be somebody's neighbour), none deep inside
     inside = (padded.positions[n:] @ torch.linalg.inv(batch.cell.reshape(3, 3)))
     assert bool(((inside < 0) | (inside > 1)).any(-1).all())
+
+
+# ---------------------------------------------------------------------------------------------------- data loader
+@settings(**SETTINGS)
+@given(seed=st.integers(0, 10_000), n=st.integers(1, 23), batch_size=st.integers(1, 6), world=st.integers(1, 4),
+       shuffle=st.booleans(), drop_last=st.booleans(), epoch=st.integers(0, 3))
+def test_dataloader_epochs_resume_points_and_rank_shares(seed, n, batch_size, world, shuffle, drop_last, epoch):
+    """Every rank sees the same number of batches; together the ranks cover every sample; a loader told to resume at
+    batch k yields exactly the tail of the epoch; the order depends on (seed, epoch) only."""
+    from nvalchemi_toolkit_b200.data.datapipes import DataLoader, InMemoryDataset
+
+    data = [random_molecule(1 + i % 3, seed + i) for i in range(n)]
+    for i, d in enumerate(data):
+        d.add_system_property("tag", torch.tensor([[float(i)]]))
+
+    def tags(loader):
+        return [[int(t) for t in b.tag.reshape(-1).tolist()] for b in loader]
+
+    loaders = []
+    for r in range(world):
+        dl = DataLoader(InMemoryDataset(data), batch_size=batch_size, shuffle=shuffle, drop_last=drop_last, seed=seed)
+        dl.set_distributed(r, world)
+        dl.set_epoch(epoch)
+        loaders.append(dl)
+    per_rank = [tags(dl) for dl in loaders]
+    assert len({len(x) for x in per_rank}) == 1 and all(len(dl) == len(per_rank[0]) for dl in loaders)
+    seen = {t for x in per_rank for b in x for t in b}
+    if not drop_last:
+        assert seen == set(range(n))
+    assert all(len(b) == batch_size for x in per_rank for b in x[:-1])
+    again = tags(loaders[0])
+    assert again == per_rank[0]                                   # same (seed, epoch): same order
+    if shuffle and n > 4 and world == 1:
+        loaders[0].set_epoch(epoch + 1)
+        assert tags(loaders[0]) != per_rank[0] or n <= batch_size
+        loaders[0].set_epoch(epoch)
+    k = len(per_rank[0]) // 2
+    loaders[0].set_epoch_step(k)
+    assert tags(loaders[0]) == per_rank[0][k:]
+    assert tags(loaders[0]) == per_rank[0]                        # the resume point applies to one iteration only
