@@ -256,17 +256,27 @@ class AtomicData(BaseModel, DataMixin):
             return "system"
         return None
 
+    def _claim(self, key: str, level: str) -> None:
+        """A field lives on ONE level: registering a name that another level already owns (built-in fields included,
+        e.g. the per-system ``spin`` or ``charge``) would make batches collate it twice with different shapes."""
+        current = self.level_of(key)
+        if current is not None and current != level:
+            raise ValueError(f"'{key}' is already a {current}-level field; choose another name for the {level}-level quantity")
+
     def add_node_property(self, key: str, value: torch.Tensor, node_dim: int = 0) -> None:
+        self._claim(key, "node")
         if value.shape[node_dim] != self.num_nodes:
             raise ValueError(f"{key}: expected {self.num_nodes} rows, got {value.shape[node_dim]}")
         object.__setattr__(self, key, value) if key in type(self).model_fields else self._set_extra(key, value)
         self.__node_keys__.add(key)
 
     def add_edge_property(self, key: str, value: torch.Tensor) -> None:
+        self._claim(key, "edge")
         object.__setattr__(self, key, value) if key in type(self).model_fields else self._set_extra(key, value)
         self.__edge_keys__.add(key)
 
     def add_system_property(self, key: str, value: torch.Tensor) -> None:
+        self._claim(key, "system")
         object.__setattr__(self, key, value) if key in type(self).model_fields else self._set_extra(key, value)
         self.__system_keys__.add(key)
 
